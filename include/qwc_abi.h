@@ -1,0 +1,262 @@
+/*
+ * C ABI of the sm_100a decode-step kernels.
+ *
+ * Every `qwc_*` launcher below that carries a reference citation has exactly the
+ * signature the reference's Rust FFI declares in crates/qwc-cuda/src/ffi.rs, so the
+ * shared library can be linked in place of the reference's libqwc_kernels.a:
+ *   - all pointers are DEVICE pointers unless the comment says "host";
+ *   - shapes are `int`, the CUDA stream is always the last argument;
+ *   - the return value is a cudaError_t carried as `int` (0 = success); bad, NULL or
+ *     out-of-range arguments give cudaErrorInvalidValue (1) before anything is launched;
+ *   - the callee never allocates, frees, retains a pointer or synchronises, and every
+ *     launcher is legal inside cudaStreamBeginCapture (ThreadLocal).
+ *
+ * `qwc_stream` is a cudaStream_t.  The header has no CUDA include on purpose: it is
+ * what a cgo / Rust-bindgen / ctypes binding reads.
+ */
+#ifndef QWC_ABI_H
+#define QWC_ABI_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef void* qwc_stream;
+
+/* ------------------------------------------------------------------ */
+/* Shape selection (additive; no reference counterpart)                 */
+/* ------------------------------------------------------------------ */
+
+/*
+ * The reference bakes its model dimensions in as constexpr
+ * (cuda/delta_net.cu:36-38 value heads 48, cuda/paged_attention.cu:21 page 64).
+ * The legacy-signature launchers below read the two dimensions that differ between
+ * the reference checkpoint and the synthetic 27B-shaped model from this process-wide
+ * setting.  Defaults reproduce the reference: 48 value heads, 64-token pages.
+ * Supported: delta_value_heads in {32, 48}; kv_page_size in {16, 64}.
+ * Host call; not thread-safe against concurrent launches.
+ */
+typedef struct qwc_shape {
+    int delta_value_heads;
+    int kv_page_size;
+} qwc_shape;
+
+int qwc_configure(const qwc_shape* shape);
+void qwc_get_shape(qwc_shape* shape);
+
+/* Sticky device-side status word: 0, or the code of the first bounded wait that gave up
+ * (see qwc_device_status_reset).  Host call; synchronises the device. */
+int qwc_device_status(void);
+int qwc_device_status_reset(void);
+
+/* ------------------------------------------------------------------ */
+/* NVFP4 W4A16 projections                                              */
+/* ------------------------------------------------------------------ */
+
+/*
+ * Y[b, n] = sum_k e2m1(W[n, k]) * e4m3(S[n, k / 16]) / weight_global_scale * X[b, k].
+ * Replaces crates/qwc-cuda/src/ffi.rs:352-362 (cuda/nvfp4.cu:489-537).
+ * packed: u8[out, in/2], low nibble = even k.  scales: e4m3 in the 128x4 swizzled
+ * block-scale layout of cuda/nvfp4.cu:33-39 (rows padded to 128, groups to 4).
+ * input bf16[batch, in], output bf16[batch, out].  in_features % 256 == 0.
+ * batch 1..32 (the reference stops at 8), one pass over the weights for all rows.
+ */
+int qwc_nvfp4_w4a16(const void* packed, const void* scales, const void* input, void* output,
+                    int out_features, int in_features, int batch, float weight_global_scale,
+                    qwc_stream stream);
+
+/*
+ * H[b, n] = silu(gate(x))[n] * up(x)[n], two NVFP4 matrices sharing one input.
+ * Replaces crates/qwc-cuda/src/ffi.rs:383-396 (cuda/nvfp4.cu:585-643).  batch 1..32.
+ */
+int qwc_nvfp4_swiglu_w4a16(const void* gate_packed, const void* gate_scales, const void* up_packed,
+                           const void* up_scales, const void* input, void* output,
+                           int out_features, int in_features, int batch, float gate_global_scale,
+                           float up_global_scale, qwc_stream stream);
+
+/* ------------------------------------------------------------------ */
+/* Packed paged FP8 attention                                           */
+/* ------------------------------------------------------------------ */
+
+/*
+ * Decode attention for `rows` query rows (row_base .. row_base + rows), 24 query heads
+ * packed six to a KV head, head_dim 256, e4m3 K/V pages u8[num_blocks, 4, PAGE, 256].
+ * Replaces crates/qwc-cuda/src/ffi.rs:520-537 (cuda/paged_attention.cu:1913-1958).
+ * query bf16[*, 24, 256]; query_gate_projection bf16[*, 24, 512] or NULL (sigmoid gate
+ * from the second half of each head); block_tables u32[*, max_blocks];
+ * context_lengths u32[*]; output bf16[*, 24, 256].
+ * workspace holds split-context partials: per (row, head, partition) max f32, sum f32 and
+ * 256 f16 values = rows * 24 * partitions * 520 bytes; ignored when partitions == 1,
+ * too small -> cudaErrorInvalidValue.  tile_size must be 6 (one decode row per tile);
+ * larger tiles (segments of one sequence) are prefill shapes -> cudaErrorNotSupported.
+ */
+int qwc_paged_attention_packed_fp8(const void* query, const void* query_gate_projection,
+                                   const void* key_cache, const void* value_cache,
+                                   const void* block_tables, const void* context_lengths,
+                                   void* output, void* workspace, size_t workspace_bytes, int rows,
+                                   int row_base, int max_blocks, int tile_size, int partitions,
+                                   float softmax_scale, qwc_stream stream);
+
+/*
+ * Same, with per-KV-head dequantisation scales f32[4] for K and V (device pointers, either
+ * may be NULL = 1.0) and an explicit page size.  No reference counterpart: the reference
+ * cache is unscaled (cuda/attention_prepare.cu:139-142).
+ */
+int qwc_paged_attention_packed_fp8_scaled(const void* query, const void* query_gate_projection,
+                                          const void* key_cache, const void* value_cache,
+                                          const void* block_tables, const void* context_lengths,
+                                          const float* key_scales, const float* value_scales,
+                                          void* output, void* workspace, size_t workspace_bytes,
+                                          int rows, int row_base, int max_blocks, int page_size,
+                                          int partitions, float softmax_scale, qwc_stream stream);
+
+/* Host helper: bytes of split-context workspace for (rows, partitions). */
+size_t qwc_paged_attention_packed_workspace_bytes(int rows, int partitions);
+
+/* ------------------------------------------------------------------ */
+/* Gated DeltaNet, int8 state                                           */
+/* ------------------------------------------------------------------ */
+
+/*
+ * One recurrent step for `batch` slots: state i8[capacity, Hv, 128, 128] with per-row
+ * scales f32[capacity, Hv, 128], addressed through state_slots u32[batch] (NULL = slot b).
+ * q, k f32[batch, 16, 128]; v f32[batch, Hv, 128]; alpha, beta f32[batch, Hv];
+ * kq f32[batch, 16]; out f32[batch, Hv, 128].  Hv from qwc_configure.
+ * Replaces crates/qwc-cuda/src/ffi.rs:164-178 (cuda/delta_net.cu:1220-1237).
+ */
+int qwc_delta_decode_int8(void* state, float* state_scales, const void* state_slots, const void* q,
+                          const void* k, const void* v, const void* alpha, const void* beta,
+                          const void* kq, void* out, int state_capacity, int batch,
+                          qwc_stream stream);
+
+/*
+ * conv1d update + SiLU + q/k/v split, then L2 normalisation, k.q, alpha and beta.
+ * Replaces crates/qwc-cuda/src/ffi.rs:284-304 (cuda/delta_prepare.cu:249-316).
+ */
+int qwc_delta_prepare_decode(const void* mixed_qkv, const void* a_projection,
+                             const void* b_projection, const void* conv_weight, const void* a_log,
+                             const void* dt_bias, void* conv_state, const void* state_slots,
+                             void* query, void* key, void* value, void* alpha, void* beta, void* kq,
+                             int state_capacity, int batch, int mixed_stride, int gate_stride,
+                             qwc_stream stream);
+
+/*
+ * RMSNormGated over 128-wide value heads: bf16(out) -> norm -> * weight -> * silu(z).
+ * Replaces crates/qwc-cuda/src/ffi.rs:339-348 (cuda/delta_output.cu:68-91).
+ */
+int qwc_delta_gated_rmsnorm(const float* input, const void* gate, const void* weight, void* output,
+                            int batch, float epsilon, int gate_stride, qwc_stream stream);
+
+/* ------------------------------------------------------------------ */
+/* Step glue                                                            */
+/* ------------------------------------------------------------------ */
+
+/*
+ * QK-norm (1 + w), partial RoPE on the first 64 dims, query -> bf16, K/V of the new token
+ * -> e4m3 at (physical_blocks[b], block_offsets[b]).
+ * Replaces crates/qwc-cuda/src/ffi.rs:588-604 (cuda/attention_prepare.cu:199-228).
+ */
+int qwc_prepare_attention_decode_fp8(const void* query_gate_projection, const void* key_projection,
+                                     const void* value_projection, const void* query_norm_weight,
+                                     const void* key_norm_weight, const void* cosine,
+                                     const void* sine, const void* physical_blocks,
+                                     const void* block_offsets, void* query, void* key_cache,
+                                     void* value_cache, int batch, float epsilon,
+                                     qwc_stream stream);
+
+/* Same with per-KV-head scales (values are divided by the scale before the fp8 store) and an
+ * explicit page size and projection row strides.  No reference counterpart. */
+int qwc_prepare_attention_decode_fp8_scaled(
+    const void* query_gate_projection, const void* key_projection, const void* value_projection,
+    const void* query_norm_weight, const void* key_norm_weight, const void* cosine,
+    const void* sine, const void* physical_blocks, const void* block_offsets,
+    const float* key_scales, const float* value_scales, void* query, void* key_cache,
+    void* value_cache, int batch, int page_size, int query_stride, int key_stride,
+    int value_stride, float epsilon, qwc_stream stream);
+
+/*
+ * residual <- bf16(residual + input) when residual != NULL; output = x * rsqrt(mean x^2 + eps)
+ * * (1 + w), bf16.  Replaces crates/qwc-cuda/src/ffi.rs:440-449 (cuda/rmsnorm.cu:220-241).
+ */
+int qwc_rmsnorm_bf16(const void* input, void* residual, const void* weight, void* output, int batch,
+                     int hidden, float epsilon, qwc_stream stream);
+
+/* Replaces crates/qwc-cuda/src/ffi.rs:71-80 (cuda/vocab_fp8.cu:702-722). */
+int qwc_fp8_embedding_gather(const void* table, const void* row_scales, const void* token_ids,
+                             void* output, int batch, int cols, int vocab, qwc_stream stream);
+
+/* logits f32[batch, vocab] = (e4m3 W . bf16 hidden) * row_scale.
+ * Replaces crates/qwc-cuda/src/ffi.rs:94-103 and :131-140 (cuda/vocab_fp8.cu:746,823).
+ * Both entry points accept batch 1..qwc_fp8_max_batched_logits(). */
+int qwc_fp8_lm_head(const void* weights, const void* row_scales, const void* hidden, void* logits,
+                    int batch, int hidden_size, int vocab, qwc_stream stream);
+int qwc_fp8_lm_head_batched(const void* weights, const void* row_scales, const void* hidden,
+                            void* logits, int batch, int hidden_size, int vocab, qwc_stream stream);
+int qwc_fp8_max_logits_batch(void);    /* crates/qwc-cuda/src/ffi.rs:142 */
+int qwc_fp8_max_batched_logits(void);  /* crates/qwc-cuda/src/ffi.rs:144 */
+
+/* Two-stage greedy argmax, ties -> lower index.
+ * Replaces crates/qwc-cuda/src/ffi.rs:625-634 (cuda/sampling.cu:94-118). */
+int qwc_argmax(const float* logits, float* partial_values, uint32_t* partial_indices,
+               uint32_t* output, int vocab, int batch, int parts, qwc_stream stream);
+
+/* ------------------------------------------------------------------ */
+/* Device-side ragged-batch packing (additive; replaces host loops)     */
+/* ------------------------------------------------------------------ */
+
+/*
+ * Persistent device tables, one entry per state slot:
+ *   seq_tokens u32[capacity]            tokens held, including the one this step appends
+ *   seq_blocks u32[capacity, max_blocks] physical page ids in logical order
+ *
+ * qwc_page_table_apply applies `count` host-decided edits (device array of
+ * {slot, index, value, kind}: kind 0 sets seq_blocks[slot][index] = value,
+ * kind 1 sets seq_tokens[slot] = value, kind 2 adds value to seq_tokens[slot]).
+ * It does on the device what CacheManager::append_token / release do to the host maps
+ * (crates/qwc-runtime/src/cache.rs:411-449).
+ */
+typedef struct qwc_table_edit {
+    uint32_t slot;
+    uint32_t index;
+    uint32_t value;
+    uint32_t kind;
+} qwc_table_edit;
+
+int qwc_page_table_apply(uint32_t* seq_tokens, uint32_t* seq_blocks, const qwc_table_edit* edits,
+                         int count, int capacity, int max_blocks, qwc_stream stream);
+
+/*
+ * Builds every per-row array the decode step reads, on the device, from the tables above:
+ * what BatchLayout::build (crates/qwc-runtime/src/layout.rs:54-152) and
+ * Executor::upload_layout_decode (crates/qwc-engine/src/executor.rs:1939-1990) build on the
+ * host and upload with eight blocking copies.
+ *
+ * Row selection: row_slots u32[rows] gives the batch order; or row_slots == NULL and
+ * slot_active u8[capacity] != NULL, in which case the rows are the active slots in ascending
+ * order (prefix-sum compaction) and *row_count receives their number (<= rows).
+ *
+ * Outputs (all device): state_slots u32[rows], positions u32[rows], context_lengths u32[rows],
+ * physical_blocks u32[rows], block_offsets u32[rows], block_tables u32[rows, max_blocks]
+ * (zero padded), block_table_offsets u32[rows + 1] (exclusive prefix sum of page counts),
+ * block_ids u32[sum pages] (may be NULL), cosine / sine bf16[rows, 64] gathered from
+ * rope_table bf16[max_positions, 2, 64].  status u32[1] receives 0 or the first error
+ * (1 slot out of range or empty, 2 duplicate slot, 4 missing pages, 8 position beyond table).
+ */
+int qwc_pack_decode_batch(const uint32_t* row_slots, const uint8_t* slot_active,
+                          const uint32_t* seq_tokens, const uint32_t* seq_blocks,
+                          const void* rope_table, int max_positions, uint32_t* row_count,
+                          uint32_t* state_slots, uint32_t* positions, uint32_t* context_lengths,
+                          uint32_t* physical_blocks, uint32_t* block_offsets,
+                          uint32_t* block_tables, uint32_t* block_table_offsets,
+                          uint32_t* block_ids, void* cosine, void* sine, uint32_t* status,
+                          int rows, int capacity, int max_blocks, int page_size,
+                          qwc_stream stream);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* QWC_ABI_H */

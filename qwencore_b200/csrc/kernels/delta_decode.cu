@@ -1,0 +1,248 @@
+// Gated DeltaNet recurrent decode step on int8 state with a per-row fp32 scale.
+//
+// Replaces crates/qwc-cuda/cuda/delta_net.cu:1220-1237 (qwc_delta_decode_int8) behind the
+// same C signature.  Arithmetic per state row (cuda/delta_net.cu:99-119,137-175):
+//   s = float(code) * scale;  u = s.k;  w = s.q;  c = beta (v - alpha u)
+//   s <- alpha s + c k;  out = alpha w + c (k.q)
+//   peak = max|s|; inverse = 127 / peak; code = rint(s * inverse); scale = peak * (1/127)
+//
+// The op reads and rewrites 16 KiB + 512 B per (slot, value head) and nothing else of
+// size, so it is bound by HBM read+write bandwidth.  Layout for sm_100a:
+//   * one CTA per (value head, slot, row split); the state tile is brought into shared
+//     memory by bulk-async copies (TMA 1-D) in 4 KiB quarters, each signalling its own
+//     mbarrier, so the first rows are processed while the rest are in flight, and the
+//     requantised tile leaves by one bulk store;
+//   * four CTAs are resident per SM (64 KiB of state in flight per SM);
+//   * four lanes share a row (32 codes each), so the three per-row reductions cost two
+//     shuffle steps; k and q stay in registers for all rows of the tile;
+//   * the elementwise fp32 work uses the packed f32x2 pipe, and both int8 <-> fp32
+//     conversions are bit tricks on the 2^23 binade (exact, round-to-nearest-even),
+//     which keeps the instruction count under what the memory stream allows.
+//
+// The requantiser rounds exactly as the reference's: multiply by `127 / peak` in fp32,
+// round to nearest even, scale = peak * (1/127); a zero row stores codes 0 and scale 0.
+
+#include "common.cuh"
+
+namespace qwc {
+namespace {
+
+constexpr int kDim = kDeltaHeadDim;  // 128 x 128 state per head
+constexpr int kThreads = 128;
+constexpr int kPartRows = 32;        // rows per bulk copy / per CTA iteration
+constexpr int kMaxParts = kDim / kPartRows;
+
+__device__ __forceinline__ float2 f2(float a, float b) { return make_float2(a, b); }
+
+__global__ void __launch_bounds__(kThreads, 4) delta_decode_int8_kernel(
+    int8_t* __restrict__ state, float* __restrict__ state_scales, const uint32_t* __restrict__ state_slots,
+    const float* __restrict__ q, const float* __restrict__ k, const float* __restrict__ v,
+    const float* __restrict__ alpha, const float* __restrict__ beta, const float* __restrict__ kq,
+    float* __restrict__ out, int v_heads, int* status) {
+    __shared__ __align__(128) uint8_t tile[kDim * kDim];
+    __shared__ __align__(16) float row_scale[kDim];
+    __shared__ float out_rows[kDim];
+    __shared__ uint64_t bars[kMaxParts];
+    __shared__ int failed;
+
+    const int h = blockIdx.x;
+    const int b = blockIdx.y;
+    const int rows_here = kDim / gridDim.z;
+    const int row_begin = blockIdx.z * rows_here;
+    const int slot = state_slots == nullptr ? b : static_cast<int>(state_slots[b]);
+    const int hk = h / (v_heads / kDeltaKeyHeads);
+    const int parts = (rows_here + kPartRows - 1) / kPartRows;
+    const int part_rows = rows_here < kPartRows ? rows_here : kPartRows;
+
+    int8_t* S = state + (static_cast<size_t>(slot) * v_heads + h) * (kDim * kDim) + row_begin * kDim;
+    float* scales = state_scales + (static_cast<size_t>(slot) * v_heads + h) * kDim + row_begin;
+
+    if (threadIdx.x == 0) {
+        failed = 0;
+        for (int part = 0; part < parts; ++part) {
+            mbar_init(&bars[part], 1);
+        }
+        mbar_fence_init();
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        for (int part = 0; part < parts; ++part) {
+            const uint32_t bytes = part_rows * kDim;
+            mbar_arrive_expect_tx(&bars[part], bytes + (part == 0 ? rows_here * 4 : 0));
+            bulk_g2s(tile + part * kPartRows * kDim, S + part * kPartRows * kDim, bytes, &bars[part]);
+            if (part == 0) {
+                bulk_g2s(row_scale, scales, rows_here * 4, &bars[0]);
+            }
+        }
+    }
+
+    const int lane = threadIdx.x & 31;
+    const int warp = threadIdx.x >> 5;
+    const int sub = lane & 3;        // which quarter of the row this lane owns
+    const int row_in_warp = lane >> 2;
+
+    // Columns of this lane: [16 sub, 16 sub + 16) and [64 + 16 sub, 64 + 16 sub + 16).
+    float2 kk[16], qq[16];
+    {
+        const float* kp = k + (static_cast<size_t>(b) * kDeltaKeyHeads + hk) * kDim;
+        const float* qp = q + (static_cast<size_t>(b) * kDeltaKeyHeads + hk) * kDim;
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const float4 kv = *reinterpret_cast<const float4*>(kp + 64 * half + 16 * sub + 4 * i);
+                const float4 qv = *reinterpret_cast<const float4*>(qp + 64 * half + 16 * sub + 4 * i);
+                kk[half * 8 + 2 * i] = f2(kv.x, kv.y);
+                kk[half * 8 + 2 * i + 1] = f2(kv.z, kv.w);
+                qq[half * 8 + 2 * i] = f2(qv.x, qv.y);
+                qq[half * 8 + 2 * i + 1] = f2(qv.z, qv.w);
+            }
+        }
+    }
+    const float a = alpha[static_cast<size_t>(b) * v_heads + h];
+    const float bt = beta[static_cast<size_t>(b) * v_heads + h];
+    const float kq_token = kq[static_cast<size_t>(b) * kDeltaKeyHeads + hk];
+    const float* vp = v + (static_cast<size_t>(b) * v_heads + h) * kDim + row_begin;
+
+    constexpr float kMagic = 12582912.0f;        // 1.5 * 2^23
+    constexpr float kMagicBiased = 12583040.0f;  // kMagic + 128
+
+    for (int part = 0; part < parts; ++part) {
+        const bool arrived = mbar_wait_bounded(&bars[part], 0, kStatusDeltaTileWait, status);
+        if (!arrived) {
+            failed = 1;
+            break;
+        }
+        const int local = part * kPartRows + warp * 8 + row_in_warp;
+        if (warp * 8 >= part_rows) {
+            continue;  // whole warp beyond the split's rows
+        }
+        uint8_t* row_ptr = tile + local * kDim + 16 * sub;
+        const uint4 c0 = *reinterpret_cast<const uint4*>(row_ptr);
+        const uint4 c1 = *reinterpret_cast<const uint4*>(row_ptr + 64);
+        const float scale = row_scale[local];
+        const float v_row = vp[local];
+
+        const uint32_t words[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
+        float2 s[16];
+        const float2 bias = f2(-kMagicBiased, -kMagicBiased);
+        const float2 scale2 = f2(scale, scale);
+        float2 u2 = f2(0.0f, 0.0f), w2 = f2(0.0f, 0.0f);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const uint32_t x = words[i] ^ 0x80808080u;
+            const float2 lo = f2(__uint_as_float(__byte_perm(x, 0x4B400000u, 0x7650)),
+                                 __uint_as_float(__byte_perm(x, 0x4B400000u, 0x7651)));
+            const float2 hi = f2(__uint_as_float(__byte_perm(x, 0x4B400000u, 0x7652)),
+                                 __uint_as_float(__byte_perm(x, 0x4B400000u, 0x7653)));
+            s[2 * i] = __fmul2_rn(__fadd2_rn(lo, bias), scale2);
+            s[2 * i + 1] = __fmul2_rn(__fadd2_rn(hi, bias), scale2);
+            u2 = __ffma2_rn(s[2 * i], kk[2 * i], u2);
+            w2 = __ffma2_rn(s[2 * i], qq[2 * i], w2);
+            u2 = __ffma2_rn(s[2 * i + 1], kk[2 * i + 1], u2);
+            w2 = __ffma2_rn(s[2 * i + 1], qq[2 * i + 1], w2);
+        }
+        float u = u2.x + u2.y;
+        float w = w2.x + w2.y;
+        u += __shfl_xor_sync(0xffffffffu, u, 1);
+        w += __shfl_xor_sync(0xffffffffu, w, 1);
+        u += __shfl_xor_sync(0xffffffffu, u, 2);
+        w += __shfl_xor_sync(0xffffffffu, w, 2);
+
+        const float c = bt * (v_row - a * u);
+        const float contribution = a * w + c * kq_token;
+
+        const float2 a2 = f2(a, a);
+        const float2 cc = f2(c, c);
+        float peak = 0.0f;
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+            s[i] = __ffma2_rn(cc, kk[i], __fmul2_rn(a2, s[i]));
+            peak = fmaxf(peak, fmaxf(fabsf(s[i].x), fabsf(s[i].y)));
+        }
+        peak = fmaxf(peak, __shfl_xor_sync(0xffffffffu, peak, 1));
+        peak = fmaxf(peak, __shfl_xor_sync(0xffffffffu, peak, 2));
+
+        const float inverse = peak == 0.0f ? 0.0f : __fdiv_rn(127.0f, peak);
+        const float2 inverse2 = f2(inverse, inverse);
+        const float2 magic2 = f2(kMagic, kMagic);
+        uint32_t packed[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const float2 y0 = __fadd2_rn(__fmul2_rn(s[2 * i], inverse2), magic2);
+            const float2 y1 = __fadd2_rn(__fmul2_rn(s[2 * i + 1], inverse2), magic2);
+            const uint32_t lo = __byte_perm(__float_as_uint(y0.x), __float_as_uint(y0.y), 0x0040);
+            const uint32_t hi = __byte_perm(__float_as_uint(y1.x), __float_as_uint(y1.y), 0x0040);
+            packed[i] = __byte_perm(lo, hi, 0x5410);
+        }
+        *reinterpret_cast<uint4*>(row_ptr) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+        *reinterpret_cast<uint4*>(row_ptr + 64) = make_uint4(packed[4], packed[5], packed[6], packed[7]);
+        if (sub == 0) {
+            row_scale[local] = __fmul_rn(peak, 1.0f / 127.0f);
+            out_rows[local] = contribution;
+        }
+    }
+
+    fence_proxy_async();
+    __syncthreads();
+    if (failed) {
+        return;
+    }
+    if (threadIdx.x == 0) {
+        bulk_s2g(S, tile, rows_here * kDim);
+        bulk_s2g(scales, row_scale, rows_here * 4);
+        bulk_commit();
+    }
+    float* op = out + (static_cast<size_t>(b) * v_heads + h) * kDim + row_begin;
+    for (int i = threadIdx.x; i < rows_here; i += kThreads) {
+        op[i] = out_rows[i];
+    }
+    if (threadIdx.x == 0) {
+        bulk_wait_all_read();
+    }
+}
+
+// Row splits so that the grid has at least two CTAs per SM
+// (same purpose as splits_for, cuda/delta_net.cu:1184-1200).
+int splits_for(int batch, int v_heads) {
+    int sms = 148;
+    int device = 0;
+    if (cudaGetDevice(&device) == cudaSuccess) {
+        int value = 0;
+        if (cudaDeviceGetAttribute(&value, cudaDevAttrMultiProcessorCount, device) == cudaSuccess && value > 0) {
+            sms = value;
+        }
+    }
+    const int base = v_heads * batch;
+    int split = 1;
+    while (split < 16 && base * split < 2 * sms) {
+        split *= 2;
+    }
+    return split;
+}
+
+}  // namespace
+}  // namespace qwc
+
+extern "C" int qwc_delta_decode_int8(void* state, float* state_scales, const void* state_slots, const void* q,
+                                     const void* k, const void* v, const void* alpha, const void* beta,
+                                     const void* kq, void* out, int state_capacity, int batch,
+                                     cudaStream_t stream) {
+    if (state == nullptr || state_scales == nullptr || q == nullptr || k == nullptr || v == nullptr ||
+        alpha == nullptr || beta == nullptr || kq == nullptr || out == nullptr || state_capacity < batch ||
+        batch <= 0 || batch > qwc::kMaxDecodeBatch) {
+        return cudaErrorInvalidValue;
+    }
+    const int v_heads = qwc::current_shape().delta_value_heads;
+    int* status = qwc::status_ptr();
+    if (status == nullptr) {
+        return cudaErrorInvalidValue;
+    }
+    const dim3 grid(v_heads, batch, qwc::splits_for(batch, v_heads));
+    qwc::delta_decode_int8_kernel<<<grid, qwc::kThreads, 0, stream>>>(
+        static_cast<int8_t*>(state), state_scales, static_cast<const uint32_t*>(state_slots),
+        static_cast<const float*>(q), static_cast<const float*>(k), static_cast<const float*>(v),
+        static_cast<const float*>(alpha), static_cast<const float*>(beta), static_cast<const float*>(kq),
+        static_cast<float*>(out), v_heads, status);
+    return cudaGetLastError();
+}

@@ -1,0 +1,607 @@
+// NVFP4 W4A16 weight-streaming GEMV / skinny GEMM for 1..32 activation rows.
+//
+// Replaces the launchers of crates/qwc-cuda/cuda/nvfp4.cu:489-537 and :585-643 behind the
+// same C signatures.  The arithmetic contract is the reference's
+// (crates/qwc-cuda/src/nvfp4.rs:597-635): W[n,k] = e2m1(nibble) * e4m3(scale[n, k/16]) /
+// global, fp32 accumulation, bf16 output.
+//
+// Design for sm_100a.  The op is HBM-bound (4.5 bits per weight, read once), so the
+// kernel is organised around keeping ~50 KB of 128-bit weight loads in flight per SM:
+//   * one CTA per SM; each warp owns 16 or 32 weight rows and walks K in 128-element
+//     chunks, prefetching the next chunks' nibbles and block scales into registers with
+//     16-byte streaming loads (L1 no-allocate);
+//   * the e2m1 nibbles are expanded to f16 by the hardware converter and multiplied by
+//     their e4m3 block scale in f16 - the product has at most six significant bits, so
+//     it is exact - directly into mma.sync A fragments: the dequantised weights never
+//     touch shared memory;
+//   * the activation rows are the B operand: converted bf16 -> f16 once per CTA into a
+//     double-buffered shared tile laid out so every B-fragment read is a conflict-free
+//     16-byte access, and shared by all warps; 8, 16 or 32 rows cost the same weight
+//     traffic (one pass over W for every row of the batch);
+//   * narrow outputs (N = 5120) do not give 148 SMs enough rows, so K is split across a
+//     thread-block cluster and the partial sums are reduced through distributed shared
+//     memory: split-K across SMs without a global workspace or atomics.
+//
+// Row / scale mapping.  The block scales arrive in the 128x4 swizzled layout
+// (cuda/nvfp4.cu:33-39): one 16-byte unit holds rows {r, r+32, r+64, r+96} x 4 groups.
+// A thread's MMA rows are chosen from exactly that set, so one 16-byte load brings the
+// scales of all its rows for a 64-element K span.
+//
+// Activations with |x| > 65504 saturate in the f16 conversion; the weights themselves
+// are exact.
+
+#include <cooperative_groups.h>
+
+#include "common.cuh"
+
+namespace cg = cooperative_groups;
+
+namespace qwc {
+namespace {
+
+constexpr int kChunk = 128;      // K elements per chunk: 64 bytes of nibbles per row
+constexpr int kStageChunks = 4;  // chunks per activation stage (512 K elements)
+constexpr int kMaxWarps = 16;
+constexpr int kMaxBatch = 32;
+
+struct GemvParams {
+    const uint8_t* packed[2];
+    const uint8_t* scales[2];
+    const __nv_bfloat16* x;
+    __nv_bfloat16* y;
+    const float* row_scales;  // kFp8Rows: per-row fp32 scale
+    float* y_f32;             // kFp8Rows: fp32 output
+    float inverse_scale[2];
+    int out_features;
+    int in_features;
+    int batch;
+    int num_tiles;
+    int tiles_per_cta;
+    int splits;
+};
+
+// Weight formats served by the one streaming kernel.
+constexpr int kNvfp4 = 0;        // e2m1 nibbles + e4m3 block scales, bf16 out
+constexpr int kNvfp4Swiglu = 1;  // two such matrices, silu(gate) * up epilogue
+constexpr int kFp8Rows = 2;      // e4m3 bytes + one fp32 scale per row, fp32 out (lm_head)
+
+template <int NT, int MT, int MODE>
+struct Config {
+    static constexpr bool SWIGLU = MODE == kNvfp4Swiglu;
+    static constexpr bool FP8 = MODE == kFp8Rows;
+    static constexpr int kRows = SWIGLU ? 4 : 2 * MT;  // weight rows per thread
+    static constexpr int kMTiles = SWIGLU ? 2 : MT;    // m16 tiles per warp
+    static constexpr int kUnits = SWIGLU ? 2 : 1;      // 16-byte scale units per chunk
+    static constexpr int kVec = FP8 ? 2 : 1;           // 16-byte weight loads per row per chunk
+    static constexpr int kPrefetch = (kRows == 2 && !FP8) ? 4 : 2;
+    static constexpr int kStageBytes = kStageChunks * NT * 4 * 512;
+    static constexpr int kSmemBytes = 2 * kStageBytes;
+};
+
+template <int NT, int MT, int MODE>
+__global__ void __launch_bounds__(kMaxWarps * 32, 1) nvfp4_gemv_kernel(const GemvParams p) {
+    using C = Config<NT, MT, MODE>;
+    constexpr bool SWIGLU = C::SWIGLU;
+    constexpr bool FP8 = C::FP8;
+    constexpr int V = C::kVec;
+    constexpr int R = C::kRows;
+    constexpr int PF = C::kPrefetch;
+
+    extern __shared__ __align__(16) unsigned char smem[];
+
+    const int lane = threadIdx.x & 31;
+    const int warp = threadIdx.x >> 5;
+    const int g = lane >> 2;
+    const int t = lane & 3;
+    const int threads = blockDim.x;
+
+    const int row_group = blockIdx.x / p.splits;
+    const int split = blockIdx.x - row_group * p.splits;
+    const int tile = row_group * p.tiles_per_cta + warp;
+    const bool active = warp < p.tiles_per_cta && tile < p.num_tiles;
+
+    const int K = p.in_features;
+    const int chunks = K / kChunk;
+    const int c_begin = static_cast<int>(static_cast<long long>(chunks) * split / p.splits);
+    const int c_end = static_cast<int>(static_cast<long long>(chunks) * (split + 1) / p.splits);
+    const int group_blocks = K / 64;
+
+    // Rows of this thread and the word of the scale unit that belongs to each.
+    int rows[R];
+    int scale_word[R];
+    int row_block, rho;
+    if (SWIGLU || MT == 1) {
+        row_block = tile >> 3;
+        const int u = tile & 7;
+        rho = 8 * (u & 3) + g;
+        const int hi = u >> 2;
+#pragma unroll
+        for (int i = 0; i < R; ++i) {
+            rows[i] = 128 * row_block + rho + 32 * (2 * hi + (i & 1));
+            scale_word[i] = 2 * hi + (i & 1);
+        }
+    } else {
+        row_block = tile >> 2;
+        rho = 8 * (tile & 3) + g;
+#pragma unroll
+        for (int i = 0; i < R; ++i) {
+            rows[i] = 128 * row_block + rho + 32 * i;
+            scale_word[i] = i;
+        }
+    }
+
+    const uint8_t* weight_ptr[R];
+    bool row_ok[R];
+#pragma unroll
+    for (int i = 0; i < R; ++i) {
+        const int matrix = SWIGLU ? (i >> 1) : 0;
+        row_ok[i] = active && rows[i] < p.out_features;
+        // Bytes per weight row: K / 2 nibbles, or K e4m3 bytes.
+        weight_ptr[i] = p.packed[matrix] + static_cast<size_t>(row_ok[i] ? rows[i] : 0) * (FP8 ? K : K / 2) + 16 * t;
+    }
+    const uint8_t* scale_ptr[C::kUnits];
+#pragma unroll
+    for (int m = 0; m < C::kUnits; ++m) {
+        scale_ptr[m] = p.scales[m] + (static_cast<size_t>(active ? row_block : 0) * group_blocks + (t >> 1)) * 512 +
+                       rho * 16;
+    }
+
+    uint4 wq[PF][R][V];
+    uint4 sq[PF][C::kUnits];
+
+    auto load_chunk = [&](int slot, int c) {
+        if (c < c_end) {
+#pragma unroll
+            for (int i = 0; i < R; ++i) {
+#pragma unroll
+                for (int v = 0; v < V; ++v) {
+                    // A quad covers 64 contiguous bytes of the row per load instruction.
+                    wq[slot][i][v] = row_ok[i] ? ldg_stream(weight_ptr[i] + static_cast<size_t>(c) * (64 * V) + 64 * v)
+                                               : make_uint4(0, 0, 0, 0);
+                }
+            }
+            if (!FP8) {
+#pragma unroll
+                for (int m = 0; m < C::kUnits; ++m) {
+                    sq[slot][m] = active ? ldg_stream(scale_ptr[m] + static_cast<size_t>(c) * 1024)
+                                         : make_uint4(0, 0, 0, 0);
+                }
+            }
+        }
+    };
+
+    // ---- activation staging: bf16 global -> f16 shared, B-fragment order ----------
+    // A staging unit is 32 bytes of one token row: 16 elements = two 16-byte pieces.
+    // Shared layout per stage: [chunk][n tile][piece 0..3][lane][16 B], so that the
+    // B fragments of lane (g, t) for steps 2*piece and 2*piece+1 are one 16-byte read.
+    constexpr int kHeld = 2;
+    uint4 held[kHeld][2];
+    auto stage_units = [&](int stage) {
+        const int first = c_begin + stage * kStageChunks;
+        const int n = min(kStageChunks, c_end - first);
+        return n * NT * 64;
+    };
+    auto unit_source = [&](int stage, int u, bool& valid) {
+        const int jj = u & 1;
+        const int tt = (u >> 1) & 3;
+        const int gg = (u >> 3) & 7;
+        const int rest = u >> 6;
+        const int n = rest % NT;
+        const int cc = rest / NT;
+        const int token = 8 * n + gg;
+        valid = token < p.batch;
+        // Element e of lane (g, t) is k = 32 t + e for nibbles (one 16-byte load per row);
+        // for bytes the two loads sit 64 bytes apart: k = 16 t + e, then 64 + 16 t + (e - 16).
+        const int k = (c_begin + stage * kStageChunks + cc) * kChunk + (FP8 ? 64 * jj + 16 * tt : 32 * tt + 16 * jj);
+        return p.x + static_cast<size_t>(valid ? token : 0) * K + k;
+    };
+    auto unit_store = [&](unsigned char* buffer, int u, const uint4& lo, const uint4& hi) {
+        const int jj = u & 1;
+        const int tt = (u >> 1) & 3;
+        const int gg = (u >> 3) & 7;
+        const int rest = u >> 6;  // cc * NT + n
+        const uint32_t in[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
+        uint32_t out[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            out[i] = bf16x2_to_f16x2(in[i]);
+        }
+        unsigned char* base = buffer + ((rest * 4 + 2 * jj) * 32 + 4 * gg + tt) * 16;
+        *reinterpret_cast<uint4*>(base) = make_uint4(out[0], out[1], out[2], out[3]);
+        *reinterpret_cast<uint4*>(base + 512) = make_uint4(out[4], out[5], out[6], out[7]);
+    };
+    auto stage_issue = [&](int stage) {
+        const int total = stage_units(stage);
+#pragma unroll
+        for (int h = 0; h < kHeld; ++h) {
+            const int u = threadIdx.x + h * threads;
+            if (u < total) {
+                bool valid;
+                const __nv_bfloat16* src = unit_source(stage, u, valid);
+                if (valid) {
+                    held[h][0] = *reinterpret_cast<const uint4*>(src);
+                    held[h][1] = *reinterpret_cast<const uint4*>(src + 8);
+                } else {
+                    held[h][0] = make_uint4(0, 0, 0, 0);
+                    held[h][1] = make_uint4(0, 0, 0, 0);
+                }
+            }
+        }
+    };
+    auto stage_commit = [&](int stage) {
+        unsigned char* buffer = smem + (stage & 1) * C::kStageBytes;
+        const int total = stage_units(stage);
+#pragma unroll
+        for (int h = 0; h < kHeld; ++h) {
+            const int u = threadIdx.x + h * threads;
+            if (u < total) {
+                unit_store(buffer, u, held[h][0], held[h][1]);
+            }
+        }
+        // Small CTAs have more units than two per thread: the rest go through directly.
+        for (int u = threadIdx.x + kHeld * threads; u < total; u += threads) {
+            bool valid;
+            const __nv_bfloat16* src = unit_source(stage, u, valid);
+            uint4 lo = make_uint4(0, 0, 0, 0), hi = lo;
+            if (valid) {
+                lo = *reinterpret_cast<const uint4*>(src);
+                hi = *reinterpret_cast<const uint4*>(src + 8);
+            }
+            unit_store(buffer, u, lo, hi);
+        }
+    };
+
+    float acc[C::kMTiles][NT][4];
+#pragma unroll
+    for (int m = 0; m < C::kMTiles; ++m) {
+#pragma unroll
+        for (int n = 0; n < NT; ++n) {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                acc[m][n][j] = 0.0f;
+            }
+        }
+    }
+
+    auto compute_chunk = [&](const unsigned char* xs, const uint4 (&w)[R][V], const uint4 (&s)[C::kUnits]) {
+        // Block scales of this thread's two 16-element groups, per row, broadcast to f16x2.
+        uint32_t scale_lo[R], scale_hi[R];
+#pragma unroll
+        for (int i = 0; i < (FP8 ? 0 : R); ++i) {
+            const uint4& unit = s[SWIGLU ? (i >> 1) : 0];
+            const int sel = scale_word[i];
+            const uint32_t word = sel == 0 ? unit.x : (sel == 1 ? unit.y : (sel == 2 ? unit.z : unit.w));
+            const uint32_t pair = cvt_e4m3x2_to_f16x2(word >> (16 * (t & 1)));
+            scale_lo[i] = __byte_perm(pair, 0, 0x1010);
+            scale_hi[i] = __byte_perm(pair, 0, 0x3232);
+        }
+#pragma unroll
+        for (int sp = 0; sp < 4; ++sp) {
+            uint4 b[NT];
+#pragma unroll
+            for (int n = 0; n < NT; ++n) {
+                b[n] = *reinterpret_cast<const uint4*>(xs + ((n * 4 + sp) * 32 + lane) * 16);
+            }
+#pragma unroll
+            for (int m = 0; m < C::kMTiles; ++m) {
+                uint32_t h0[4], h1[4];
+                if (FP8) {
+                    // Elements 8 sp .. 8 sp + 7 are bytes 8 sp .. of the thread's 32: two words.
+                    const uint4& v0 = w[2 * m][sp >> 1];
+                    const uint4& v1 = w[2 * m + 1][sp >> 1];
+                    const uint32_t a0 = (sp & 1) ? v0.z : v0.x, a1 = (sp & 1) ? v0.w : v0.y;
+                    const uint32_t b0 = (sp & 1) ? v1.z : v1.x, b1 = (sp & 1) ? v1.w : v1.y;
+                    cvt_e4m3x4_to_f16x2(a0, h0[0], h0[1]);
+                    cvt_e4m3x4_to_f16x2(a1, h0[2], h0[3]);
+                    cvt_e4m3x4_to_f16x2(b0, h1[0], h1[1]);
+                    cvt_e4m3x4_to_f16x2(b1, h1[2], h1[3]);
+                } else {
+                    const uint32_t w0[4] = {w[2 * m][0].x, w[2 * m][0].y, w[2 * m][0].z, w[2 * m][0].w};
+                    const uint32_t w1[4] = {w[2 * m + 1][0].x, w[2 * m + 1][0].y, w[2 * m + 1][0].z,
+                                            w[2 * m + 1][0].w};
+                    cvt_e2m1x8_to_f16x2(w0[sp], h0);
+                    cvt_e2m1x8_to_f16x2(w1[sp], h1);
+                    const uint32_t s0 = sp < 2 ? scale_lo[2 * m] : scale_hi[2 * m];
+                    const uint32_t s1 = sp < 2 ? scale_lo[2 * m + 1] : scale_hi[2 * m + 1];
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        h0[j] = hmul2_bits(h0[j], s0);
+                        h1[j] = hmul2_bits(h1[j], s1);
+                    }
+                }
+#pragma unroll
+                for (int n = 0; n < NT; ++n) {
+                    mma_f16_16816(acc[m][n], h0[0], h1[0], h0[1], h1[1], b[n].x, b[n].y);
+                    mma_f16_16816(acc[m][n], h0[2], h1[2], h0[3], h1[3], b[n].z, b[n].w);
+                }
+            }
+        }
+    };
+
+    // ---- main loop ------------------------------------------------------------------
+    const int num_stages = (c_end - c_begin + kStageChunks - 1) / kStageChunks;
+#pragma unroll
+    for (int slot = 0; slot < PF; ++slot) {
+        load_chunk(slot, c_begin + slot);
+    }
+    if (num_stages > 0) {
+        stage_issue(0);
+        stage_commit(0);
+    }
+    for (int stage = 0; stage < num_stages; ++stage) {
+        __syncthreads();  // stage visible; the other buffer is free again
+        const bool more = stage + 1 < num_stages;
+        if (more) {
+            stage_issue(stage + 1);
+        }
+        const unsigned char* xs = smem + (stage & 1) * C::kStageBytes;
+        const int first = c_begin + stage * kStageChunks;
+#pragma unroll
+        for (int q = 0; q < kStageChunks; ++q) {
+            const int c = first + q;
+            if (c < c_end) {
+                if (active) {
+                    compute_chunk(xs + q * (NT * 4 * 512), wq[q % PF], sq[q % PF]);
+                }
+                load_chunk(q % PF, c + PF);
+            }
+        }
+        if (more) {
+            stage_commit(stage + 1);
+        }
+    }
+
+    // ---- split-K reduction through distributed shared memory ------------------------
+    if (p.splits > 1) {
+        cg::cluster_group cluster = cg::this_cluster();
+        float* reduce = reinterpret_cast<float*>(smem);
+        __syncthreads();
+        if (split != 0) {
+#pragma unroll
+            for (int m = 0; m < C::kMTiles; ++m) {
+#pragma unroll
+                for (int n = 0; n < NT; ++n) {
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        reduce[((m * NT + n) * 4 + j) * threads + threadIdx.x] = acc[m][n][j];
+                    }
+                }
+            }
+        }
+        cluster.sync();
+        if (split == 0) {
+            for (int r = 1; r < p.splits; ++r) {
+                const float* peer = cluster.map_shared_rank(reduce, r);
+#pragma unroll
+                for (int m = 0; m < C::kMTiles; ++m) {
+#pragma unroll
+                    for (int n = 0; n < NT; ++n) {
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            acc[m][n][j] += peer[((m * NT + n) * 4 + j) * threads + threadIdx.x];
+                        }
+                    }
+                }
+            }
+        }
+        cluster.sync();
+        if (split != 0) {
+            return;
+        }
+    }
+
+    // ---- epilogue ---------------------------------------------------------------------
+    if (!active) {
+        return;
+    }
+    const int N = p.out_features;
+#pragma unroll
+    for (int n = 0; n < NT; ++n) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int token = 8 * n + 2 * t + (j & 1);
+            if (token >= p.batch) {
+                continue;
+            }
+            if (SWIGLU) {
+                const int i = j >> 1;  // rows[0], rows[1] (gate) pair with rows[2], rows[3] (up)
+                if (!row_ok[i]) {
+                    continue;
+                }
+                const float gate = acc[0][n][j] * p.inverse_scale[0];
+                const float up = acc[1][n][j] * p.inverse_scale[1];
+                const float silu = gate / (1.0f + __expf(-gate));
+                p.y[static_cast<size_t>(token) * N + rows[i]] = __float2bfloat16(silu * up);
+            } else {
+#pragma unroll
+                for (int m = 0; m < C::kMTiles; ++m) {
+                    const int i = 2 * m + (j >> 1);
+                    if (!row_ok[i]) {
+                        continue;
+                    }
+                    if (FP8) {
+                        p.y_f32[static_cast<size_t>(token) * N + rows[i]] = acc[m][n][j] * p.row_scales[rows[i]];
+                    } else {
+                        p.y[static_cast<size_t>(token) * N + rows[i]] =
+                            __float2bfloat16(acc[m][n][j] * p.inverse_scale[0]);
+                    }
+                }
+            }
+        }
+    }
+}
+
+// ---- host side ----------------------------------------------------------------------
+
+int sm_count() {
+    static int cached[64] = {};
+    int device = 0;
+    cudaGetDevice(&device);
+    if (device < 0 || device >= 64) {
+        return 148;
+    }
+    if (cached[device] == 0) {
+        int sms = 0;
+        if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || sms <= 0) {
+            sms = 148;
+        }
+        cached[device] = sms;
+    }
+    return cached[device];
+}
+
+struct Plan {
+    int tiles_per_cta;
+    int splits;
+    int ctas;
+};
+
+// Picks warps per CTA and the K split so that one wave of CTAs covers the SMs evenly.
+Plan choose_plan(int num_tiles, int chunks, int sms) {
+    Plan best = {1, 1, num_tiles};
+    double best_score = -1.0;
+    for (int splits = 1; splits <= 8; splits *= 2) {
+        if (chunks / splits < 4 && splits > 1) {
+            break;
+        }
+        const int clusters = sms / splits;
+        if (clusters == 0) {
+            break;
+        }
+        int tiles_per_cta = (num_tiles + clusters - 1) / clusters;
+        tiles_per_cta = tiles_per_cta < 1 ? 1 : (tiles_per_cta > kMaxWarps ? kMaxWarps : tiles_per_cta);
+        const int row_groups = (num_tiles + tiles_per_cta - 1) / tiles_per_cta;
+        const int ctas = row_groups * splits;
+        const int waves = (ctas + sms - 1) / sms;
+        const int slice = (chunks + splits - 1) / splits;
+        const double useful = static_cast<double>(num_tiles) * chunks;
+        const double spent = static_cast<double>(waves) * sms * tiles_per_cta * slice;
+        double score = useful / spent;
+        // Few warps per SM cannot keep enough loads in flight; a wider split costs a
+        // cluster reduction.
+        const double depth = tiles_per_cta >= 8 ? 1.0 : (0.5 + tiles_per_cta / 16.0);
+        score *= depth;
+        score *= 1.0 - 0.015 * (splits == 1 ? 0 : (splits == 2 ? 1 : (splits == 4 ? 2 : 3)));
+        if (score > best_score) {
+            best_score = score;
+            best = {tiles_per_cta, splits, ctas};
+        }
+    }
+    return best;
+}
+
+template <int NT, int MT, int MODE>
+cudaError_t launch(const GemvParams& base, cudaStream_t stream) {
+    using C = Config<NT, MT, MODE>;
+    constexpr bool SWIGLU = C::SWIGLU;
+    GemvParams p = base;
+    const int row_blocks = (p.out_features + 127) / 128;
+    p.num_tiles = row_blocks * ((SWIGLU || MT == 1) ? 8 : 4);
+    const Plan plan = choose_plan(p.num_tiles, p.in_features / kChunk, sm_count());
+    p.tiles_per_cta = plan.tiles_per_cta;
+    p.splits = plan.splits;
+
+    static const cudaError_t opted = cudaFuncSetAttribute(
+        nvfp4_gemv_kernel<NT, MT, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
+    if (opted != cudaSuccess) {
+        return opted;
+    }
+
+    cudaLaunchConfig_t config = {};
+    config.gridDim = dim3(plan.ctas);
+    config.blockDim = dim3(plan.tiles_per_cta * 32);
+    config.dynamicSmemBytes = C::kSmemBytes;
+    config.stream = stream;
+    cudaLaunchAttribute attribute[1];
+    attribute[0].id = cudaLaunchAttributeClusterDimension;
+    attribute[0].val.clusterDim.x = plan.splits;
+    attribute[0].val.clusterDim.y = 1;
+    attribute[0].val.clusterDim.z = 1;
+    config.attrs = attribute;
+    config.numAttrs = plan.splits > 1 ? 1 : 0;
+    return cudaLaunchKernelEx(&config, nvfp4_gemv_kernel<NT, MT, MODE>, p);
+}
+
+template <int MODE>
+cudaError_t dispatch(const GemvParams& p, cudaStream_t stream) {
+    const int wide_tiles = ((p.out_features + 127) / 128) * 4;
+    const bool wide = MODE == kNvfp4 && wide_tiles >= 2 * sm_count();
+    if (p.batch <= 8) {
+        return launch<1, 1, MODE>(p, stream);
+    }
+    if (p.batch <= 16) {
+        return wide ? launch<2, 2, MODE>(p, stream) : launch<2, 1, MODE>(p, stream);
+    }
+    return wide ? launch<4, 2, MODE>(p, stream) : launch<4, 1, MODE>(p, stream);
+}
+
+}  // namespace
+
+// Entry for the FP8 vocabulary head (vocab_head.cu): same streaming kernel, byte weights.
+cudaError_t launch_fp8_rows(const void* weights, const float* row_scales, const void* hidden, float* logits,
+                            int batch, int hidden_size, int vocab, cudaStream_t stream) {
+    GemvParams p = {};
+    p.packed[0] = p.packed[1] = static_cast<const uint8_t*>(weights);
+    p.scales[0] = p.scales[1] = static_cast<const uint8_t*>(weights);
+    p.x = static_cast<const __nv_bfloat16*>(hidden);
+    p.row_scales = row_scales;
+    p.y_f32 = logits;
+    p.inverse_scale[0] = p.inverse_scale[1] = 1.0f;
+    p.out_features = vocab;
+    p.in_features = hidden_size;
+    p.batch = batch;
+    return dispatch<kFp8Rows>(p, stream);
+}
+
+namespace {
+
+}  // namespace
+}  // namespace qwc
+
+extern "C" int qwc_nvfp4_w4a16(const void* packed, const void* scales, const void* input, void* output,
+                               int out_features, int in_features, int batch, float weight_global_scale,
+                               cudaStream_t stream) {
+    if (packed == nullptr || scales == nullptr || input == nullptr || output == nullptr || out_features <= 0 ||
+        in_features <= 0 || in_features % 256 != 0 || batch <= 0 || batch > qwc::kMaxBatch ||
+        !(weight_global_scale > 0.0f)) {
+        return cudaErrorInvalidValue;
+    }
+    qwc::GemvParams p = {};
+    p.packed[0] = static_cast<const uint8_t*>(packed);
+    p.scales[0] = static_cast<const uint8_t*>(scales);
+    p.packed[1] = p.packed[0];
+    p.scales[1] = p.scales[0];
+    p.x = static_cast<const __nv_bfloat16*>(input);
+    p.y = static_cast<__nv_bfloat16*>(output);
+    p.inverse_scale[0] = 1.0f / weight_global_scale;
+    p.inverse_scale[1] = p.inverse_scale[0];
+    p.out_features = out_features;
+    p.in_features = in_features;
+    p.batch = batch;
+    return qwc::dispatch<qwc::kNvfp4>(p, stream);
+}
+
+extern "C" int qwc_nvfp4_swiglu_w4a16(const void* gate_packed, const void* gate_scales, const void* up_packed,
+                                      const void* up_scales, const void* input, void* output, int out_features,
+                                      int in_features, int batch, float gate_global_scale, float up_global_scale,
+                                      cudaStream_t stream) {
+    if (gate_packed == nullptr || gate_scales == nullptr || up_packed == nullptr || up_scales == nullptr ||
+        input == nullptr || output == nullptr || out_features <= 0 || in_features <= 0 ||
+        in_features % 256 != 0 || batch <= 0 || batch > qwc::kMaxBatch || !(gate_global_scale > 0.0f) ||
+        !(up_global_scale > 0.0f)) {
+        return cudaErrorInvalidValue;
+    }
+    qwc::GemvParams p = {};
+    p.packed[0] = static_cast<const uint8_t*>(gate_packed);
+    p.scales[0] = static_cast<const uint8_t*>(gate_scales);
+    p.packed[1] = static_cast<const uint8_t*>(up_packed);
+    p.scales[1] = static_cast<const uint8_t*>(up_scales);
+    p.x = static_cast<const __nv_bfloat16*>(input);
+    p.y = static_cast<__nv_bfloat16*>(output);
+    p.inverse_scale[0] = 1.0f / gate_global_scale;
+    p.inverse_scale[1] = 1.0f / up_global_scale;
+    p.out_features = out_features;
+    p.in_features = in_features;
+    p.batch = batch;
+    return qwc::dispatch<qwc::kNvfp4Swiglu>(p, stream);
+}

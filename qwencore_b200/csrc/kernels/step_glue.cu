@@ -1,0 +1,517 @@
+// Small per-row kernels between the streaming ops of the decode step: embedding gather,
+// residual RMSNorm, DeltaNet pre- and post-processing, QK-norm + RoPE + FP8 page write,
+// vocabulary head entry points and greedy argmax.  Each is a few hundred KB of traffic
+// per layer, so the aim is few launches and wide accesses, not roofline.
+//
+// Rounding points follow the reference kernels exactly (file:line at each launcher).
+
+#include "common.cuh"
+
+namespace qwc {
+
+cudaError_t launch_fp8_rows(const void* weights, const float* row_scales, const void* hidden, float* logits,
+                            int batch, int hidden_size, int vocab, cudaStream_t stream);
+
+namespace {
+
+constexpr int kThreads = 256;
+
+__device__ __forceinline__ float fp8_to_float(uint8_t raw) {
+    __nv_fp8_e4m3 value;
+    value.__x = raw;
+    return static_cast<float>(value);
+}
+
+__device__ __forceinline__ uint8_t to_fp8(float value) {
+    __nv_fp8_e4m3 converted(value);
+    return converted.__x;
+}
+
+__device__ __forceinline__ float sigmoidf_fast(float x) { return 1.0f / (1.0f + __expf(-x)); }
+
+// Sum over the CTA; every thread receives the total.  `scratch` holds one float per warp.
+__device__ __forceinline__ float block_sum(float value, float* scratch) {
+    value = warp_sum(value);
+    const int lane = threadIdx.x & 31;
+    const int warp = threadIdx.x >> 5;
+    __syncthreads();
+    if (lane == 0) {
+        scratch[warp] = value;
+    }
+    __syncthreads();
+    float total = 0.0f;
+    for (int w = 0; w < (blockDim.x >> 5); ++w) {
+        total += scratch[w];
+    }
+    return total;
+}
+
+// ---- embedding gather (cuda/vocab_fp8.cu:113-136) ---------------------------------
+__global__ void embedding_gather_kernel(const uint8_t* __restrict__ table, const float* __restrict__ row_scales,
+                                        const uint32_t* __restrict__ token_ids, __nv_bfloat16* __restrict__ output,
+                                        int cols, int vocab) {
+    const uint32_t token = token_ids[blockIdx.x];
+    const size_t output_base = static_cast<size_t>(blockIdx.x) * cols;
+    const bool valid = token < static_cast<uint32_t>(vocab);
+    const float scale = valid ? row_scales[token] : 0.0f;
+    const size_t table_base = static_cast<size_t>(valid ? token : 0) * cols;
+    for (int column = threadIdx.x; column < cols; column += blockDim.x) {
+        const float value = valid ? fp8_to_float(table[table_base + column]) * scale : 0.0f;
+        output[output_base + column] = __float2bfloat16(value);
+    }
+}
+
+// ---- residual RMSNorm (cuda/rmsnorm.cu:85-149) --------------------------------------
+// One CTA per row; the rounded bf16 row stays in registers between the two passes.
+constexpr int kNormMaxPerThread = 10;  // 8 * 256 * 10 = 20480 columns at most
+
+__global__ void __launch_bounds__(kThreads) rmsnorm_bf16_kernel(const __nv_bfloat16* __restrict__ input,
+                                                                __nv_bfloat16* __restrict__ residual,
+                                                                const __nv_bfloat16* __restrict__ weight,
+                                                                __nv_bfloat16* __restrict__ output, int hidden,
+                                                                float epsilon) {
+    __shared__ float scratch[kThreads / 32];
+    const size_t base = static_cast<size_t>(blockIdx.x) * hidden;
+    const int vectors = hidden / 8;
+    uint4 held[kNormMaxPerThread];
+    float sum = 0.0f;
+#pragma unroll
+    for (int i = 0; i < kNormMaxPerThread; ++i) {
+        const int vec = threadIdx.x + i * kThreads;
+        if (vec < vectors) {
+            uint4 raw = *reinterpret_cast<const uint4*>(input + base + 8 * vec);
+            uint32_t words[4] = {raw.x, raw.y, raw.z, raw.w};
+            if (residual != nullptr) {
+                const uint4 res = *reinterpret_cast<const uint4*>(residual + base + 8 * vec);
+                const uint32_t rw[4] = {res.x, res.y, res.z, res.w};
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const float lo = __uint_as_float(words[j] << 16) + __uint_as_float(rw[j] << 16);
+                    const float hi = __uint_as_float(words[j] & 0xffff0000u) + __uint_as_float(rw[j] & 0xffff0000u);
+                    __nv_bfloat162 rounded = __floats2bfloat162_rn(lo, hi);
+                    words[j] = *reinterpret_cast<uint32_t*>(&rounded);
+                }
+                raw = make_uint4(words[0], words[1], words[2], words[3]);
+                *reinterpret_cast<uint4*>(residual + base + 8 * vec) = raw;
+            }
+            held[i] = raw;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const float lo = __uint_as_float(words[j] << 16);
+                const float hi = __uint_as_float(words[j] & 0xffff0000u);
+                sum = fmaf(lo, lo, sum);
+                sum = fmaf(hi, hi, sum);
+            }
+        }
+    }
+    const float total = block_sum(sum, scratch);
+    const float inverse = rsqrtf(total / static_cast<float>(hidden) + epsilon);
+#pragma unroll
+    for (int i = 0; i < kNormMaxPerThread; ++i) {
+        const int vec = threadIdx.x + i * kThreads;
+        if (vec < vectors) {
+            const uint4 w4 = *reinterpret_cast<const uint4*>(weight + 8 * vec);
+            const uint32_t ww[4] = {w4.x, w4.y, w4.z, w4.w};
+            const uint32_t xw[4] = {held[i].x, held[i].y, held[i].z, held[i].w};
+            uint32_t out[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const float lo = __uint_as_float(xw[j] << 16) * inverse * (1.0f + __uint_as_float(ww[j] << 16));
+                const float hi = __uint_as_float(xw[j] & 0xffff0000u) * inverse *
+                                 (1.0f + __uint_as_float(ww[j] & 0xffff0000u));
+                __nv_bfloat162 rounded = __floats2bfloat162_rn(lo, hi);
+                out[j] = *reinterpret_cast<uint32_t*>(&rounded);
+            }
+            *reinterpret_cast<uint4*>(output + base + 8 * vec) = make_uint4(out[0], out[1], out[2], out[3]);
+        }
+    }
+}
+
+// ---- DeltaNet prepare (cuda/delta_prepare.cu:44-86,168-245), one launch -------------
+// One CTA per (key head, row): 128 threads = the 128 dims of the head.  The CTA updates
+// the conv history of its q and k channels and of the value heads that share this key
+// head, applies SiLU, L2-normalises q and k, and writes k.q, alpha and beta.
+__device__ __forceinline__ float softplusf_ref(float value) {
+    if (value > 20.0f) {
+        return value;
+    }
+    if (value < -20.0f) {
+        return __expf(value);
+    }
+    return log1pf(__expf(value));
+}
+
+__device__ __forceinline__ float conv_update(const __nv_bfloat16* __restrict__ mixed_row,
+                                             const __nv_bfloat16* __restrict__ conv_weight,
+                                             float* __restrict__ conv_state, size_t slot_base, int channel) {
+    float* history = conv_state + (slot_base + channel) * 3;
+    const float current = __bfloat162float(mixed_row[channel]);
+    const __nv_bfloat16* weight = conv_weight + static_cast<size_t>(channel) * 4;
+    float convolved = __bfloat162float(weight[0]) * history[0];
+    convolved = fmaf(__bfloat162float(weight[1]), history[1], convolved);
+    convolved = fmaf(__bfloat162float(weight[2]), history[2], convolved);
+    convolved = fmaf(__bfloat162float(weight[3]), current, convolved);
+    const float h1 = history[1];
+    const float h2 = history[2];
+    history[0] = h1;
+    history[1] = h2;
+    history[2] = current;
+    return __bfloat162float(__float2bfloat16(convolved * sigmoidf_fast(convolved)));
+}
+
+__global__ void __launch_bounds__(kDeltaHeadDim) delta_prepare_kernel(
+    const __nv_bfloat16* __restrict__ mixed_qkv, const __nv_bfloat16* __restrict__ a_projection,
+    const __nv_bfloat16* __restrict__ b_projection, const __nv_bfloat16* __restrict__ conv_weight,
+    const __nv_bfloat16* __restrict__ a_log, const __nv_bfloat16* __restrict__ dt_bias,
+    float* __restrict__ conv_state, const uint32_t* __restrict__ state_slots, float* __restrict__ query,
+    float* __restrict__ key, float* __restrict__ value, float* __restrict__ alpha, float* __restrict__ beta,
+    float* __restrict__ kq, int mixed_stride, int gate_stride, int v_heads) {
+    __shared__ float scratch[kDeltaHeadDim / 32];
+    const int head = blockIdx.x;
+    const int batch = blockIdx.y;
+    const int dimension = threadIdx.x;
+    const int ratio = v_heads / kDeltaKeyHeads;
+    const int qk_elements = kDeltaKeyHeads * kDeltaHeadDim;
+    const int channels = 2 * qk_elements + v_heads * kDeltaHeadDim;
+    const uint32_t slot = state_slots[batch];
+    const size_t slot_base = static_cast<size_t>(slot) * channels;
+    const __nv_bfloat16* mixed_row = mixed_qkv + static_cast<size_t>(batch) * mixed_stride;
+
+    const float q = conv_update(mixed_row, conv_weight, conv_state, slot_base, head * kDeltaHeadDim + dimension);
+    const float k =
+        conv_update(mixed_row, conv_weight, conv_state, slot_base, qk_elements + head * kDeltaHeadDim + dimension);
+    for (int r = 0; r < ratio; ++r) {
+        const int value_head = head * ratio + r;
+        const float v = conv_update(mixed_row, conv_weight, conv_state, slot_base,
+                                    2 * qk_elements + value_head * kDeltaHeadDim + dimension);
+        value[(static_cast<size_t>(batch) * v_heads + value_head) * kDeltaHeadDim + dimension] = v;
+    }
+
+    const float q_sum = block_sum(q * q, scratch);
+    const float k_sum = block_sum(k * k, scratch);
+    const float q_inverse = rsqrtf(q_sum + 1e-6f) * (1.0f / sqrtf(128.0f));
+    const float k_inverse = rsqrtf(k_sum + 1e-6f);
+    const float normalized_q = q * q_inverse;
+    const float normalized_k = k * k_inverse;
+    const size_t base = (static_cast<size_t>(batch) * kDeltaKeyHeads + head) * kDeltaHeadDim;
+    query[base + dimension] = normalized_q;
+    key[base + dimension] = normalized_k;
+    const float kq_sum = block_sum(normalized_q * normalized_k, scratch);
+    if (dimension == 0) {
+        kq[static_cast<size_t>(batch) * kDeltaKeyHeads + head] = kq_sum;
+    }
+    if (dimension < ratio) {
+        const int value_head = head * ratio + dimension;
+        const size_t gate_read = static_cast<size_t>(batch) * gate_stride + value_head;
+        const size_t gate_offset = static_cast<size_t>(batch) * v_heads + value_head;
+        const float projected_a = __bfloat162float(a_projection[gate_read]);
+        const float projected_b = __bfloat162float(b_projection[gate_read]);
+        const float log_a = __bfloat162float(a_log[value_head]);
+        const float bias = __bfloat162float(dt_bias[value_head]);
+        const float log_decay = -__expf(log_a) * softplusf_ref(projected_a + bias);
+        alpha[gate_offset] = __expf(log_decay);
+        beta[gate_offset] = sigmoidf_fast(projected_b);
+    }
+}
+
+// ---- gated RMSNorm over value heads (cuda/delta_output.cu:20-64) --------------------
+__global__ void __launch_bounds__(kDeltaHeadDim) gated_rmsnorm_kernel(const float* __restrict__ input,
+                                                                      const __nv_bfloat16* __restrict__ gate,
+                                                                      const __nv_bfloat16* __restrict__ weight,
+                                                                      __nv_bfloat16* __restrict__ output,
+                                                                      float epsilon, int gate_stride, int heads) {
+    __shared__ float scratch[kDeltaHeadDim / 32];
+    const int head = blockIdx.x;
+    const int batch = blockIdx.y;
+    const int dimension = threadIdx.x;
+    const size_t offset = (static_cast<size_t>(batch) * heads + head) * kDeltaHeadDim + dimension;
+    const size_t gate_offset = static_cast<size_t>(batch) * gate_stride + head * kDeltaHeadDim + dimension;
+    const float value = __bfloat162float(__float2bfloat16(input[offset]));
+    const float sum = block_sum(value * value, scratch);
+    const float inverse = rsqrtf(sum / static_cast<float>(kDeltaHeadDim) + epsilon);
+    const __nv_bfloat16 normalized = __float2bfloat16(value * inverse);
+    const __nv_bfloat16 weighted =
+        __float2bfloat16(__bfloat162float(weight[dimension]) * __bfloat162float(normalized));
+    const float gate_value = __bfloat162float(gate[gate_offset]);
+    const float silu = gate_value / (1.0f + __expf(-gate_value));
+    output[offset] = __float2bfloat16(__bfloat162float(weighted) * silu);
+}
+
+// ---- QK-norm + partial RoPE + FP8 page write (cuda/attention_prepare.cu:52-143) -----
+// One launch: blockIdx.x < 24 are query heads, the next 4 are KV heads.
+__global__ void __launch_bounds__(kHeadDim) prepare_attention_kernel(
+    const __nv_bfloat16* __restrict__ query_gate_projection, const __nv_bfloat16* __restrict__ key_projection,
+    const __nv_bfloat16* __restrict__ value_projection, const __nv_bfloat16* __restrict__ query_norm_weight,
+    const __nv_bfloat16* __restrict__ key_norm_weight, const __nv_bfloat16* __restrict__ cosine,
+    const __nv_bfloat16* __restrict__ sine, const uint32_t* __restrict__ physical_blocks,
+    const uint32_t* __restrict__ block_offsets, const float* __restrict__ key_scales,
+    const float* __restrict__ value_scales, __nv_bfloat16* __restrict__ query, uint8_t* __restrict__ key_cache,
+    uint8_t* __restrict__ value_cache, int page_size, int query_stride, int key_stride, int value_stride,
+    float epsilon) {
+    __shared__ float scratch[kHeadDim / 32];
+    __shared__ __nv_bfloat16 normalized[kHeadDim];
+    const int batch = blockIdx.y;
+    const int dimension = threadIdx.x;
+    const bool is_query = blockIdx.x < kQueryHeads;
+    const int head = is_query ? blockIdx.x : blockIdx.x - kQueryHeads;
+    const __nv_bfloat16* raw_row =
+        is_query ? query_gate_projection + static_cast<size_t>(batch) * query_stride + head * (2 * kHeadDim)
+                 : key_projection + static_cast<size_t>(batch) * key_stride + head * kHeadDim;
+    const __nv_bfloat16* norm_weight = is_query ? query_norm_weight : key_norm_weight;
+    const float raw = __bfloat162float(raw_row[dimension]);
+    const float sum = block_sum(raw * raw, scratch);
+    const float inverse = rsqrtf(sum / static_cast<float>(kHeadDim) + epsilon);
+    normalized[dimension] = __float2bfloat16(raw * inverse * (1.0f + __bfloat162float(norm_weight[dimension])));
+    __syncthreads();
+    float rotated_value = __bfloat162float(normalized[dimension]);
+    if (dimension < kRopeDim) {
+        const int half = kRopeDim / 2;
+        const int paired = dimension < half ? dimension + half : dimension - half;
+        const float rotated = __bfloat162float(normalized[paired]) * (dimension < half ? -1.0f : 1.0f);
+        const float c = __bfloat162float(cosine[static_cast<size_t>(batch) * kRopeDim + dimension]);
+        const float s = __bfloat162float(sine[static_cast<size_t>(batch) * kRopeDim + dimension]);
+        rotated_value = rotated_value * c + rotated * s;
+    }
+    if (is_query) {
+        query[(static_cast<size_t>(batch) * kQueryHeads + head) * kHeadDim + dimension] =
+            __float2bfloat16(rotated_value);
+        return;
+    }
+    const size_t cache_base =
+        ((static_cast<size_t>(physical_blocks[batch]) * kKvHeads + head) * page_size + block_offsets[batch]) *
+        kHeadDim;
+    const float k_inverse = key_scales ? 1.0f / key_scales[head] : 1.0f;
+    const float v_inverse = value_scales ? 1.0f / value_scales[head] : 1.0f;
+    const float v = __bfloat162float(
+        value_projection[static_cast<size_t>(batch) * value_stride + head * kHeadDim + dimension]);
+    key_cache[cache_base + dimension] = to_fp8(rotated_value * k_inverse);
+    value_cache[cache_base + dimension] = to_fp8(v * v_inverse);
+}
+
+// ---- greedy argmax (cuda/sampling.cu:11-92) -------------------------------------------
+__device__ __forceinline__ bool better(float value, uint32_t index, float best, uint32_t best_index) {
+    return value > best || (value == best && index < best_index);
+}
+
+__device__ void reduce_candidate(float& value, uint32_t& index, float* shared_values, uint32_t* shared_indices) {
+#pragma unroll
+    for (int off = 16; off > 0; off >>= 1) {
+        const float other = __shfl_xor_sync(0xffffffffu, value, off);
+        const uint32_t other_index = __shfl_xor_sync(0xffffffffu, index, off);
+        if (better(other, other_index, value, index)) {
+            value = other;
+            index = other_index;
+        }
+    }
+    const int lane = threadIdx.x & 31;
+    const int warp = threadIdx.x >> 5;
+    if (lane == 0) {
+        shared_values[warp] = value;
+        shared_indices[warp] = index;
+    }
+    __syncthreads();
+    if (warp == 0) {
+        value = lane < (blockDim.x >> 5) ? shared_values[lane] : -INFINITY;
+        index = lane < (blockDim.x >> 5) ? shared_indices[lane] : UINT32_MAX;
+#pragma unroll
+        for (int off = 16; off > 0; off >>= 1) {
+            const float other = __shfl_xor_sync(0xffffffffu, value, off);
+            const uint32_t other_index = __shfl_xor_sync(0xffffffffu, index, off);
+            if (better(other, other_index, value, index)) {
+                value = other;
+                index = other_index;
+            }
+        }
+    }
+}
+
+__global__ void __launch_bounds__(kThreads) argmax_parts_kernel(const float* __restrict__ logits,
+                                                                float* __restrict__ partial_values,
+                                                                uint32_t* __restrict__ partial_indices, int vocab) {
+    __shared__ float shared_values[kThreads / 32];
+    __shared__ uint32_t shared_indices[kThreads / 32];
+    const int batch = blockIdx.y;
+    const float* row = logits + static_cast<size_t>(batch) * vocab;
+    float best = -INFINITY;
+    uint32_t best_index = UINT32_MAX;
+    for (int column = blockIdx.x * kThreads + threadIdx.x; column < vocab; column += gridDim.x * kThreads) {
+        const float value = row[column];
+        if (better(value, static_cast<uint32_t>(column), best, best_index)) {
+            best = value;
+            best_index = static_cast<uint32_t>(column);
+        }
+    }
+    reduce_candidate(best, best_index, shared_values, shared_indices);
+    if (threadIdx.x == 0) {
+        const size_t offset = static_cast<size_t>(batch) * gridDim.x + blockIdx.x;
+        partial_values[offset] = best;
+        partial_indices[offset] = best_index;
+    }
+}
+
+__global__ void __launch_bounds__(kThreads) argmax_reduce_kernel(const float* __restrict__ partial_values,
+                                                                 const uint32_t* __restrict__ partial_indices,
+                                                                 uint32_t* __restrict__ output, int parts) {
+    __shared__ float shared_values[kThreads / 32];
+    __shared__ uint32_t shared_indices[kThreads / 32];
+    const int batch = blockIdx.x;
+    float best = -INFINITY;
+    uint32_t best_index = UINT32_MAX;
+    for (int part = threadIdx.x; part < parts; part += kThreads) {
+        const size_t offset = static_cast<size_t>(batch) * parts + part;
+        const float value = partial_values[offset];
+        const uint32_t index = partial_indices[offset];
+        if (better(value, index, best, best_index)) {
+            best = value;
+            best_index = index;
+        }
+    }
+    reduce_candidate(best, best_index, shared_values, shared_indices);
+    if (threadIdx.x == 0) {
+        output[batch] = best_index;
+    }
+}
+
+constexpr int kMaxLogitsRows = 32;
+
+}  // namespace
+}  // namespace qwc
+
+using namespace qwc;
+
+extern "C" int qwc_fp8_embedding_gather(const void* table, const void* row_scales, const void* token_ids,
+                                        void* output, int batch, int cols, int vocab, cudaStream_t stream) {
+    if (table == nullptr || row_scales == nullptr || token_ids == nullptr || output == nullptr || batch <= 0 ||
+        cols <= 0 || vocab <= 0) {
+        return cudaErrorInvalidValue;
+    }
+    embedding_gather_kernel<<<batch, kThreads, 0, stream>>>(
+        static_cast<const uint8_t*>(table), static_cast<const float*>(row_scales),
+        static_cast<const uint32_t*>(token_ids), static_cast<__nv_bfloat16*>(output), cols, vocab);
+    return cudaGetLastError();
+}
+
+extern "C" int qwc_rmsnorm_bf16(const void* input, void* residual, const void* weight, void* output, int batch,
+                                int hidden, float epsilon, cudaStream_t stream) {
+    if (input == nullptr || weight == nullptr || output == nullptr || batch <= 0 || batch > kMaxStepRows ||
+        hidden <= 0 || hidden % 256 != 0 || hidden > 8 * kThreads * kNormMaxPerThread || !isfinite(epsilon) ||
+        epsilon <= 0.0f) {
+        return cudaErrorInvalidValue;
+    }
+    rmsnorm_bf16_kernel<<<batch, kThreads, 0, stream>>>(
+        static_cast<const __nv_bfloat16*>(input), static_cast<__nv_bfloat16*>(residual),
+        static_cast<const __nv_bfloat16*>(weight), static_cast<__nv_bfloat16*>(output), hidden, epsilon);
+    return cudaGetLastError();
+}
+
+extern "C" int qwc_delta_prepare_decode(const void* mixed_qkv, const void* a_projection, const void* b_projection,
+                                        const void* conv_weight, const void* a_log, const void* dt_bias,
+                                        void* conv_state, const void* state_slots, void* query, void* key,
+                                        void* value, void* alpha, void* beta, void* kq, int state_capacity,
+                                        int batch, int mixed_stride, int gate_stride, cudaStream_t stream) {
+    const int v_heads = current_shape().delta_value_heads;
+    const int channels = 2 * kDeltaKeyHeads * kDeltaHeadDim + v_heads * kDeltaHeadDim;
+    if (mixed_qkv == nullptr || a_projection == nullptr || b_projection == nullptr || conv_weight == nullptr ||
+        a_log == nullptr || dt_bias == nullptr || conv_state == nullptr || state_slots == nullptr ||
+        query == nullptr || key == nullptr || value == nullptr || alpha == nullptr || beta == nullptr ||
+        kq == nullptr || state_capacity < batch || batch <= 0 || batch > kMaxDecodeBatch ||
+        mixed_stride < channels || gate_stride < v_heads) {
+        return cudaErrorInvalidValue;
+    }
+    const dim3 grid(kDeltaKeyHeads, batch);
+    delta_prepare_kernel<<<grid, kDeltaHeadDim, 0, stream>>>(
+        static_cast<const __nv_bfloat16*>(mixed_qkv), static_cast<const __nv_bfloat16*>(a_projection),
+        static_cast<const __nv_bfloat16*>(b_projection), static_cast<const __nv_bfloat16*>(conv_weight),
+        static_cast<const __nv_bfloat16*>(a_log), static_cast<const __nv_bfloat16*>(dt_bias),
+        static_cast<float*>(conv_state), static_cast<const uint32_t*>(state_slots), static_cast<float*>(query),
+        static_cast<float*>(key), static_cast<float*>(value), static_cast<float*>(alpha),
+        static_cast<float*>(beta), static_cast<float*>(kq), mixed_stride, gate_stride, v_heads);
+    return cudaGetLastError();
+}
+
+extern "C" int qwc_delta_gated_rmsnorm(const float* input, const void* gate, const void* weight, void* output,
+                                       int batch, float epsilon, int gate_stride, cudaStream_t stream) {
+    const int heads = current_shape().delta_value_heads;
+    if (input == nullptr || gate == nullptr || weight == nullptr || output == nullptr || batch <= 0 ||
+        batch > kMaxStepRows || !isfinite(epsilon) || epsilon <= 0.0f || gate_stride < heads * kDeltaHeadDim) {
+        return cudaErrorInvalidValue;
+    }
+    const dim3 grid(heads, batch);
+    gated_rmsnorm_kernel<<<grid, kDeltaHeadDim, 0, stream>>>(
+        input, static_cast<const __nv_bfloat16*>(gate), static_cast<const __nv_bfloat16*>(weight),
+        static_cast<__nv_bfloat16*>(output), epsilon, gate_stride, heads);
+    return cudaGetLastError();
+}
+
+extern "C" int qwc_prepare_attention_decode_fp8_scaled(
+    const void* query_gate_projection, const void* key_projection, const void* value_projection,
+    const void* query_norm_weight, const void* key_norm_weight, const void* cosine, const void* sine,
+    const void* physical_blocks, const void* block_offsets, const float* key_scales, const float* value_scales,
+    void* query, void* key_cache, void* value_cache, int batch, int page_size, int query_stride, int key_stride,
+    int value_stride, float epsilon, cudaStream_t stream) {
+    if (query_gate_projection == nullptr || key_projection == nullptr || value_projection == nullptr ||
+        query_norm_weight == nullptr || key_norm_weight == nullptr || cosine == nullptr || sine == nullptr ||
+        physical_blocks == nullptr || block_offsets == nullptr || query == nullptr || key_cache == nullptr ||
+        value_cache == nullptr || batch <= 0 || batch > kMaxStepRows || !isfinite(epsilon) || epsilon <= 0.0f ||
+        (page_size != 16 && page_size != 64) || query_stride < kQueryHeads * 2 * kHeadDim ||
+        key_stride < kKvHeads * kHeadDim || value_stride < kKvHeads * kHeadDim) {
+        return cudaErrorInvalidValue;
+    }
+    const dim3 grid(kQueryHeads + kKvHeads, batch);
+    prepare_attention_kernel<<<grid, kHeadDim, 0, stream>>>(
+        static_cast<const __nv_bfloat16*>(query_gate_projection), static_cast<const __nv_bfloat16*>(key_projection),
+        static_cast<const __nv_bfloat16*>(value_projection), static_cast<const __nv_bfloat16*>(query_norm_weight),
+        static_cast<const __nv_bfloat16*>(key_norm_weight), static_cast<const __nv_bfloat16*>(cosine),
+        static_cast<const __nv_bfloat16*>(sine), static_cast<const uint32_t*>(physical_blocks),
+        static_cast<const uint32_t*>(block_offsets), key_scales, value_scales, static_cast<__nv_bfloat16*>(query),
+        static_cast<uint8_t*>(key_cache), static_cast<uint8_t*>(value_cache), page_size, query_stride, key_stride,
+        value_stride, epsilon);
+    return cudaGetLastError();
+}
+
+extern "C" int qwc_prepare_attention_decode_fp8(const void* query_gate_projection, const void* key_projection,
+                                                const void* value_projection, const void* query_norm_weight,
+                                                const void* key_norm_weight, const void* cosine, const void* sine,
+                                                const void* physical_blocks, const void* block_offsets, void* query,
+                                                void* key_cache, void* value_cache, int batch, float epsilon,
+                                                cudaStream_t stream) {
+    return qwc_prepare_attention_decode_fp8_scaled(
+        query_gate_projection, key_projection, value_projection, query_norm_weight, key_norm_weight, cosine, sine,
+        physical_blocks, block_offsets, nullptr, nullptr, query, key_cache, value_cache, batch,
+        current_shape().kv_page_size, kQueryHeads * 2 * kHeadDim, kKvHeads * kHeadDim, kKvHeads * kHeadDim, epsilon,
+        stream);
+}
+
+extern "C" int qwc_fp8_max_logits_batch(void) { return kMaxLogitsRows; }
+extern "C" int qwc_fp8_max_batched_logits(void) { return kMaxLogitsRows; }
+
+extern "C" int qwc_fp8_lm_head_batched(const void* weights, const void* row_scales, const void* hidden,
+                                       void* logits, int batch, int hidden_size, int vocab, cudaStream_t stream) {
+    if (weights == nullptr || row_scales == nullptr || hidden == nullptr || logits == nullptr || batch <= 0 ||
+        batch > kMaxLogitsRows || hidden_size <= 0 || hidden_size % 256 != 0 || vocab <= 0) {
+        return cudaErrorInvalidValue;
+    }
+    return launch_fp8_rows(weights, static_cast<const float*>(row_scales), hidden, static_cast<float*>(logits),
+                           batch, hidden_size, vocab, stream);
+}
+
+extern "C" int qwc_fp8_lm_head(const void* weights, const void* row_scales, const void* hidden, void* logits,
+                               int batch, int hidden_size, int vocab, cudaStream_t stream) {
+    return qwc_fp8_lm_head_batched(weights, row_scales, hidden, logits, batch, hidden_size, vocab, stream);
+}
+
+extern "C" int qwc_argmax(const float* logits, float* partial_values, uint32_t* partial_indices, uint32_t* output,
+                          int vocab, int batch, int parts, cudaStream_t stream) {
+    if (logits == nullptr || partial_values == nullptr || partial_indices == nullptr || output == nullptr ||
+        vocab <= 0 || batch <= 0 || batch > kMaxDecodeBatch || parts <= 0 || parts > kThreads) {
+        return cudaErrorInvalidValue;
+    }
+    const dim3 grid(parts, batch);
+    argmax_parts_kernel<<<grid, kThreads, 0, stream>>>(logits, partial_values, partial_indices, vocab);
+    const cudaError_t launched = cudaGetLastError();
+    if (launched != cudaSuccess) {
+        return launched;
+    }
+    argmax_reduce_kernel<<<batch, kThreads, 0, stream>>>(partial_values, partial_indices, output, parts);
+    return cudaGetLastError();
+}
