@@ -102,8 +102,10 @@ int qwc_paged_attention_packed_fp8(const void* query, const void* query_gate_pro
 
 /*
  * Same, with per-KV-head dequantisation scales f32[4] for K and V (device pointers, either
- * may be NULL = 1.0) and an explicit page size.  No reference counterpart: the reference
- * cache is unscaled (cuda/attention_prepare.cu:139-142).
+ * may be NULL = 1.0), an explicit page size, and the row stride (in elements) of
+ * query_gate_projection so that [q; gate] may sit inside a wider fused projection row
+ * (0 = 24 * 512, the reference layout).  No reference counterpart: the reference cache is
+ * unscaled (cuda/attention_prepare.cu:139-142).
  */
 int qwc_paged_attention_packed_fp8_scaled(const void* query, const void* query_gate_projection,
                                           const void* key_cache, const void* value_cache,
@@ -111,7 +113,8 @@ int qwc_paged_attention_packed_fp8_scaled(const void* query, const void* query_g
                                           const float* key_scales, const float* value_scales,
                                           void* output, void* workspace, size_t workspace_bytes,
                                           int rows, int row_base, int max_blocks, int page_size,
-                                          int partitions, float softmax_scale, qwc_stream stream);
+                                          int gate_stride, int partitions, float softmax_scale,
+                                          qwc_stream stream);
 
 /* Host helper: bytes of split-context workspace for (rows, partitions). */
 size_t qwc_paged_attention_packed_workspace_bytes(int rows, int partitions);

@@ -1,0 +1,209 @@
+/*
+ * C API of the host side that sits above the kernel ABI (qwc_abi.h): the runtime
+ * (cache manager, scheduler, batch layout) and the decode executor.
+ *
+ * These are the C++ counterparts of the reference's Rust host crates, exposed with plain
+ * pointers and integers so that tests, the benchmark and foreign callers can drive them:
+ *   qwc_cache_*      crates/qwc-runtime/src/cache.rs      (CacheManager, KvPool, StatePool)
+ *   qwc_scheduler_*  crates/qwc-runtime/src/scheduler.rs  (Scheduler)
+ *   qwc_layout_*     crates/qwc-runtime/src/layout.rs     (BatchLayout::build)
+ *   qwc_engine_*     crates/qwc-engine/src/executor.rs    (Executor: decode path, :878-1112)
+ * Error codes are the enum discriminants documented at each function; 0 is success.
+ */
+#ifndef QWC_ENGINE_H
+#define QWC_ENGINE_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#include "qwc_abi.h"
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---------------------------------------------------------------------------------- */
+/* Cache manager (crates/qwc-runtime/src/cache.rs:300-449,571-594)                     */
+/* Rejected: 1 NoStateSlot, 2 NoKvBlocks, 3 AlreadyAdmitted, 4 UnknownSequence,         */
+/*           5 NothingToRollback                                                        */
+/* ---------------------------------------------------------------------------------- */
+typedef struct qwc_cache qwc_cache;
+
+qwc_cache* qwc_cache_new(size_t state_slots, size_t kv_blocks, size_t block_size);
+void qwc_cache_free(qwc_cache* cache);
+int qwc_cache_admit(qwc_cache* cache, uint32_t id, size_t prompt_tokens);
+int qwc_cache_append_token(qwc_cache* cache, uint32_t id);
+int qwc_cache_rollback_token(qwc_cache* cache, uint32_t id);
+void qwc_cache_release(qwc_cache* cache, uint32_t id);
+/* Returns 0 and fills the outputs, or 4 when the sequence is unknown.  `blocks` receives at
+ * most `max_blocks` page ids; *num_blocks the real count. */
+int qwc_cache_sequence(const qwc_cache* cache, uint32_t id, uint32_t* state_slot, size_t* tokens,
+                       uint32_t* blocks, size_t max_blocks, size_t* num_blocks);
+size_t qwc_cache_free_blocks(const qwc_cache* cache);
+size_t qwc_cache_states_in_use(const qwc_cache* cache);
+size_t qwc_cache_active(const qwc_cache* cache);
+/* need / free of the last NoKvBlocks rejection */
+void qwc_cache_last_shortage(const qwc_cache* cache, size_t* need, size_t* free_blocks);
+/* Moves the table edits recorded since the last call into `edits` (at most `max_edits`);
+ * returns how many were pending. */
+size_t qwc_cache_drain_edits(qwc_cache* cache, qwc_table_edit* edits, size_t max_edits);
+
+/* ---------------------------------------------------------------------------------- */
+/* Scheduler (crates/qwc-runtime/src/scheduler.rs:190-668)                              */
+/* SubmitError: 1 Duplicate, 2 EmptyPrompt, 3 NoOutputTokens, 4 NoStateCapacity,         */
+/*              5 ContextTooLong                                                         */
+/* SchedulerError: 1 BatchInFlight, 2 NoBatchInFlight, 3 SequenceInFlight,               */
+/*                 4 InvalidStopped, 5 DuplicateStopped, 6 Invariant, 7 Cache            */
+/* ---------------------------------------------------------------------------------- */
+typedef struct qwc_scheduler qwc_scheduler;
+
+typedef struct qwc_prefill_chunk {
+    uint32_t id;
+    uint32_t offset;
+    uint32_t tokens;
+} qwc_prefill_chunk;
+
+typedef struct qwc_completion {
+    uint32_t id;
+    uint32_t generated_tokens;
+    uint32_t reason; /* 0 Length, 1 Stopped */
+} qwc_completion;
+
+qwc_scheduler* qwc_scheduler_new(size_t max_num_seqs, size_t max_num_batched_tokens, size_t state_slots,
+                                 size_t kv_blocks, size_t block_size);
+void qwc_scheduler_free(qwc_scheduler* scheduler);
+int qwc_scheduler_submit(qwc_scheduler* scheduler, uint32_t id, size_t prompt_tokens, size_t max_new_tokens);
+/* Plans the next batch.  Returns 0 with the batch (possibly empty: *num_decode == 0 and
+ * *num_prefill == 0 means nothing to run), or a SchedulerError.  Buffers must hold
+ * max_num_seqs entries. */
+int qwc_scheduler_next_batch(qwc_scheduler* scheduler, uint32_t* decode_ids, size_t* num_decode,
+                             qwc_prefill_chunk* prefill, size_t* num_prefill);
+int qwc_scheduler_complete_batch(qwc_scheduler* scheduler, const uint32_t* stopped, size_t num_stopped,
+                                 qwc_completion* completed, size_t max_completed, size_t* num_completed);
+int qwc_scheduler_abort_batch(qwc_scheduler* scheduler);
+/* *removed receives 1 when the request existed. */
+int qwc_scheduler_cancel(qwc_scheduler* scheduler, uint32_t id, int* removed);
+/* -1 when the request is not active */
+long long qwc_scheduler_remaining_tokens(const qwc_scheduler* scheduler, uint32_t id);
+size_t qwc_scheduler_waiting(const qwc_scheduler* scheduler);
+size_t qwc_scheduler_active(const qwc_scheduler* scheduler);
+size_t qwc_scheduler_committed_kv_blocks(const qwc_scheduler* scheduler);
+/* The scheduler's own cache manager (borrowed; do not free). */
+qwc_cache* qwc_scheduler_cache(qwc_scheduler* scheduler);
+
+/* ---------------------------------------------------------------------------------- */
+/* Batch layout (crates/qwc-runtime/src/layout.rs:54-152)                               */
+/* LayoutError: 1 MissingSequence, 2 DuplicateSequence, 3 InvalidPrefillRange,           */
+/*              4 MissingKvBlocks, 5 IntegerOverflow                                     */
+/* ---------------------------------------------------------------------------------- */
+/* Builds the CSR metadata of a batch on the host.  Output arrays must hold num_decode +
+ * num_prefill (+1 for the two offset arrays) entries; block_ids `max_block_ids`.
+ * *offender receives the sequence id an error refers to. */
+int qwc_layout_build(const qwc_cache* cache, const uint32_t* decode_ids, size_t num_decode,
+                     const qwc_prefill_chunk* prefill, size_t num_prefill, uint32_t* seq_ids,
+                     uint32_t* state_slots, uint32_t* position_starts, uint32_t* context_lens,
+                     uint32_t* token_offsets, uint32_t* block_table_offsets, uint32_t* block_ids,
+                     size_t max_block_ids, uint32_t* offender);
+
+/* ---------------------------------------------------------------------------------- */
+/* Decode executor (crates/qwc-engine/src/executor.rs:395-546,878-1112,1774-1990)        */
+/* ---------------------------------------------------------------------------------- */
+typedef struct qwc_engine qwc_engine;
+
+typedef struct qwc_engine_config {
+    int num_layers;              /* 64; every `full_attention_interval`-th layer is full attention */
+    int full_attention_interval; /* 4 */
+    int hidden;                  /* 5120 */
+    int intermediate;            /* 17408 */
+    int vocab;                   /* 151936 */
+    int delta_value_heads;       /* 32 (reference checkpoint: 48) */
+    int kv_page_size;            /* 16 (reference: 64) */
+    int max_batch;               /* rows of the largest step; one CUDA graph per batch size */
+    int max_context;             /* per-sequence context cap; sets the block-table width */
+    int kv_pool_blocks;          /* physical KV pages shared by all sequences */
+    int state_slots;             /* DeltaNet state slots */
+    unsigned long long seed;     /* synthetic weights and caches */
+    int split_rank;              /* column split of every projection (latency mode): this rank */
+    int split_size;              /* ... of this many; 1 = off.  Needs max_batch == 1. */
+    int use_graph;               /* 1: replay a captured graph per batch size (default path) */
+    int attention_partitions;    /* 0 = choose from max_batch and max_context */
+} qwc_engine_config;
+
+/* Fills `config` with the synthetic 27B-shaped model of the benchmark. */
+void qwc_engine_default_config(qwc_engine_config* config);
+
+/* Allocates every resident buffer, generates seeded synthetic weights, KV pages and
+ * DeltaNet state on the device.  Returns a cudaError_t. */
+int qwc_engine_create(const qwc_engine_config* config, qwc_engine** engine);
+void qwc_engine_destroy(qwc_engine* engine);
+
+/* Joins a NCCL communicator for the column-split mode.  `unique_id` is the 128-byte
+ * ncclUniqueId made by rank 0 (qwc_engine_nccl_unique_id) and distributed by the caller.
+ * Returns 0, or a negative code when libnccl cannot be loaded / initialised. */
+int qwc_engine_nccl_unique_id(void* unique_id_128);
+int qwc_engine_init_split(qwc_engine* engine, const void* unique_id_128);
+
+/* Device pointer and size of a named resident tensor, for tests that read weights and
+ * caches back.  Layer-indexed names take the layer number; others ignore it.  Returns 0 or 1. */
+int qwc_engine_tensor(qwc_engine* engine, const char* name, int layer, void** device_ptr, size_t* bytes);
+
+/* Bytes the decode step must move for `rows` rows with the given total context tokens:
+ * weights, DeltaNet state read+write, KV read.  The roofline numerator. */
+typedef struct qwc_step_traffic {
+    double weight_bytes;
+    double state_bytes;
+    double kv_bytes;
+    double gemv_bytes_per_step; /* NVFP4 projection weights only (the dominant kernel) */
+    int gemv_launches_per_step;
+    int kernel_launches_per_step;
+} qwc_step_traffic;
+void qwc_engine_traffic(const qwc_engine* engine, int rows, double context_tokens, qwc_step_traffic* out);
+
+/* Applies table edits (host array) to the device page table: one H2D copy and one kernel. */
+int qwc_engine_apply_edits(qwc_engine* engine, const qwc_table_edit* edits, size_t count);
+
+/*
+ * One decode step for `rows` rows.  Host inputs: row_slots u32[rows] (batch order),
+ * tokens u32[rows], optional table edits to apply first.  Copies them to the device, packs
+ * the ragged batch on the device, runs the 64-layer step (graph replay), and copies the
+ * greedy tokens back into sampled u32[rows].  Synchronous.  Mirrors
+ * Executor::execute_layout for a pure-decode layout (executor.rs:878-905,947-951).
+ * Returns a cudaError_t; a packing error (status word of qwc_pack_decode_batch) is returned
+ * as 0x1000 + status.
+ */
+int qwc_engine_decode(qwc_engine* engine, const uint32_t* row_slots, const uint32_t* tokens,
+                      const qwc_table_edit* edits, size_t num_edits, int rows, uint32_t* sampled);
+
+/* Same step with inputs already resident (the arrays of the previous call are reused) and no
+ * copies: only the graph replay.  For device-only timing. */
+int qwc_engine_replay(qwc_engine* engine, int rows);
+/* The stream the engine works on (cudaStream_t), for event timing by the caller. */
+qwc_stream qwc_engine_stream(qwc_engine* engine);
+
+/* Event timeline of one eager (un-captured) step, as Timeline / Executor::mark
+ * (crates/qwc-cuda/src/timeline.rs:17-77, executor.rs:586-591): per phase label the summed
+ * milliseconds and launch count.  Returns the number of phases written. */
+typedef struct qwc_phase_time {
+    char label[24];
+    float milliseconds;
+    int launches;
+} qwc_phase_time;
+int qwc_engine_profile_step(qwc_engine* engine, int rows, qwc_phase_time* phases, int max_phases);
+
+/*
+ * One iteration of the serving worker loop (crates/qwc-engine/src/bin/serve.rs:806-1074,
+ * decode part): scheduler.next_batch -> layout check -> table edits -> decode step ->
+ * scheduler.complete_batch.  Prefill chunks are accounted but not computed (the synthetic
+ * caches already hold data for the prompt).  On any error before or at the launch the batch
+ * is rolled back with abort_batch.  *num_decoded receives the rows decoded, `completed` the
+ * finished requests.  Returns 0, 0x2000 + SchedulerError, 0x3000 + LayoutError or a
+ * cudaError_t.
+ */
+int qwc_worker_step(qwc_engine* engine, qwc_scheduler* scheduler, uint32_t eos_token, size_t* num_decoded,
+                    qwc_completion* completed, size_t max_completed, size_t* num_completed);
+
+#ifdef __cplusplus
+}
+#endif
+
+#endif /* QWC_ENGINE_H */

@@ -1,0 +1,511 @@
+// See runtime.h.  Behaviour follows crates/qwc-runtime/src/{cache,scheduler,layout}.rs.
+#include "runtime.h"
+
+#include <algorithm>
+#include <limits>
+#include <unordered_set>
+
+namespace qwc {
+namespace runtime {
+
+// ---- pools ---------------------------------------------------------------------------
+
+StatePool::StatePool(size_t capacity) : capacity_(capacity) {
+    // cache.rs:79: (0..capacity).rev() so that pop() hands out 0 first
+    free_.reserve(capacity);
+    for (size_t i = capacity; i > 0; --i) {
+        free_.push_back(static_cast<uint32_t>(i - 1));
+    }
+}
+
+std::optional<uint32_t> StatePool::acquire() {
+    if (free_.empty()) {
+        return std::nullopt;
+    }
+    const uint32_t slot = free_.back();
+    free_.pop_back();
+    return slot;
+}
+
+void StatePool::release(uint32_t slot) { free_.push_back(slot); }
+
+KvPool::KvPool(size_t capacity, size_t block_size) : block_size_(block_size), capacity_(capacity), refs_(capacity, 0) {
+    free_.reserve(capacity);
+    for (size_t i = capacity; i > 0; --i) {
+        free_.push_back(static_cast<uint32_t>(i - 1));
+    }
+}
+
+bool KvPool::acquire(size_t n, std::vector<uint32_t>* out) {
+    if (free_.size() < n) {
+        return false;
+    }
+    out->clear();
+    for (size_t i = 0; i < n; ++i) {
+        const uint32_t block = free_.back();
+        free_.pop_back();
+        refs_[block] = 1;
+        out->push_back(block);
+    }
+    return true;
+}
+
+void KvPool::retain(const std::vector<uint32_t>& blocks) {
+    for (uint32_t block : blocks) {
+        refs_[block] += 1;
+    }
+}
+
+void KvPool::release(const std::vector<uint32_t>& blocks) {
+    for (uint32_t block : blocks) {
+        if (refs_[block] > 0 && --refs_[block] == 0) {
+            free_.push_back(block);
+        }
+    }
+}
+
+// ---- cache manager -------------------------------------------------------------------
+
+CacheManager::CacheManager(size_t state_slots, size_t kv_blocks, size_t block_size)
+    : states_(state_slots), kv_(kv_blocks, block_size) {}
+
+Rejected CacheManager::admit(SeqId id, size_t prompt_tokens) {
+    if (seqs_.count(id)) {
+        return Rejected::AlreadyAdmitted;
+    }
+    const size_t need = kv_.blocks_for(prompt_tokens);
+    // cache.rs:386-390: the slot is checked before the blocks are taken
+    if (states_.empty()) {
+        return Rejected::NoStateSlot;
+    }
+    std::vector<uint32_t> blocks;
+    if (!kv_.acquire(need, &blocks)) {
+        last_need_ = need;
+        last_free_ = kv_.free_blocks();
+        return Rejected::NoKvBlocks;
+    }
+    const uint32_t slot = *states_.acquire();
+    for (size_t i = 0; i < blocks.size(); ++i) {
+        edits_.push_back({slot, static_cast<uint32_t>(i), blocks[i], 0});
+    }
+    edits_.push_back({slot, 0, static_cast<uint32_t>(prompt_tokens), 1});
+    Sequence seq;
+    seq.state_slot = slot;
+    seq.blocks = std::move(blocks);
+    seq.tokens = prompt_tokens;
+    seqs_.emplace(id, std::move(seq));
+    return Rejected::None;
+}
+
+Rejected CacheManager::append_token(SeqId id) {
+    auto it = seqs_.find(id);
+    if (it == seqs_.end()) {
+        return Rejected::UnknownSequence;
+    }
+    Sequence& seq = it->second;
+    const size_t need = kv_.blocks_for(seq.tokens + 1);
+    if (need > seq.blocks.size()) {
+        const size_t extra = need - seq.blocks.size();
+        std::vector<uint32_t> more;
+        if (!kv_.acquire(extra, &more)) {
+            last_need_ = extra;
+            last_free_ = kv_.free_blocks();
+            return Rejected::NoKvBlocks;
+        }
+        for (uint32_t block : more) {
+            edits_.push_back({seq.state_slot, static_cast<uint32_t>(seq.blocks.size()), block, 0});
+            seq.blocks.push_back(block);
+        }
+    }
+    seq.tokens += 1;
+    edits_.push_back({seq.state_slot, 0, static_cast<uint32_t>(seq.tokens), 1});
+    return Rejected::None;
+}
+
+Rejected CacheManager::rollback_token(SeqId id) {
+    auto it = seqs_.find(id);
+    if (it == seqs_.end()) {
+        return Rejected::UnknownSequence;
+    }
+    Sequence& seq = it->second;
+    if (seq.tokens == 0) {
+        return Rejected::NothingToRollback;
+    }
+    seq.tokens -= 1;
+    const size_t keep = kv_.blocks_for(seq.tokens);
+    std::vector<uint32_t> released(seq.blocks.begin() + keep, seq.blocks.end());
+    seq.blocks.resize(keep);
+    kv_.release(released);
+    edits_.push_back({seq.state_slot, 0, static_cast<uint32_t>(seq.tokens), 1});
+    return Rejected::None;
+}
+
+void CacheManager::release(SeqId id) {
+    auto it = seqs_.find(id);
+    if (it == seqs_.end()) {
+        return;
+    }
+    states_.release(it->second.state_slot);
+    kv_.release(it->second.blocks);
+    edits_.push_back({it->second.state_slot, 0, 0, 1});
+    seqs_.erase(it);
+}
+
+const Sequence* CacheManager::sequence(SeqId id) const {
+    auto it = seqs_.find(id);
+    return it == seqs_.end() ? nullptr : &it->second;
+}
+
+std::vector<TableEdit> CacheManager::drain_edits() {
+    std::vector<TableEdit> out;
+    out.swap(edits_);
+    return out;
+}
+
+// ---- scheduler -------------------------------------------------------------------------
+
+size_t Batch::num_tokens() const {
+    size_t total = decode.size();
+    for (const PrefillChunk& chunk : prefill) {
+        total += chunk.tokens;
+    }
+    return total;
+}
+
+Scheduler::Scheduler(SchedulerConfig config, CacheManager cache) : config_(config), cache_(std::move(cache)) {}
+
+SubmitError Scheduler::submit(Request request) {
+    const bool queued =
+        std::any_of(waiting_.begin(), waiting_.end(), [&](const Request& r) { return r.id == request.id; });
+    if (active_.count(request.id) || queued) {
+        return SubmitError::Duplicate;
+    }
+    if (request.prompt_tokens == 0) {
+        return SubmitError::EmptyPrompt;
+    }
+    if (request.max_new_tokens == 0) {
+        return SubmitError::NoOutputTokens;
+    }
+    if (cache_.states().capacity() == 0) {
+        return SubmitError::NoStateCapacity;
+    }
+    size_t context = request.prompt_tokens + request.max_new_tokens;
+    if (context < request.prompt_tokens) {
+        context = std::numeric_limits<size_t>::max();  // saturating_add
+    }
+    if (cache_.kv().blocks_for(context) > cache_.kv().capacity()) {
+        return SubmitError::ContextTooLong;
+    }
+    waiting_.push_back(request);
+    return SubmitError::None;
+}
+
+SchedulerError Scheduler::set_phase(SeqId id, Phase expected, Phase next) {
+    auto it = active_.find(id);
+    if (it == active_.end() || it->second.phase != expected) {
+        return SchedulerError::Invariant;
+    }
+    it->second.phase = next;
+    return SchedulerError::None;
+}
+
+SchedulerError Scheduler::admit_one(std::optional<SeqId>* admitted) {
+    admitted->reset();
+    const size_t candidates = waiting_.size();
+    for (size_t i = 0; i < candidates; ++i) {
+        const Request request = waiting_.front();
+        waiting_.pop_front();
+        const size_t lifetime = request.prompt_tokens + request.max_new_tokens;
+        const size_t reserved = cache_.kv().blocks_for(lifetime);
+        // scheduler.rs:615-620: lifetime commitment prevents a decode deadlock
+        if (reserved > cache_.kv().capacity() - committed_kv_blocks_) {
+            waiting_.push_back(request);
+            continue;
+        }
+        const Rejected outcome = cache_.admit(request.id, request.prompt_tokens);
+        switch (outcome) {
+            case Rejected::None:
+                committed_kv_blocks_ += reserved;
+                active_.emplace(request.id, ActiveRequest{request, reserved, 0, 0, Phase::PrefillReady});
+                *admitted = request.id;
+                return SchedulerError::None;
+            case Rejected::NoStateSlot:
+                waiting_.push_front(request);
+                return SchedulerError::None;
+            case Rejected::NoKvBlocks:
+                waiting_.push_back(request);
+                break;
+            default:
+                return SchedulerError::Cache;
+        }
+    }
+    return SchedulerError::None;
+}
+
+SchedulerError Scheduler::next_batch(Batch* out, bool* has_batch) {
+    *has_batch = false;
+    if (in_flight_) {
+        return SchedulerError::BatchInFlight;
+    }
+    Batch batch;
+    const size_t decode_candidates = decode_ready_.size();
+    for (size_t i = 0; i < decode_candidates; ++i) {
+        if (batch.num_seqs() == config_.max_num_seqs || batch.num_tokens() == config_.max_num_batched_tokens) {
+            break;
+        }
+        const SeqId id = decode_ready_.front();
+        decode_ready_.pop_front();
+        const Rejected outcome = cache_.append_token(id);
+        if (outcome == Rejected::None) {
+            const SchedulerError phase = set_phase(id, Phase::DecodeReady, Phase::DecodeInFlight);
+            if (phase != SchedulerError::None) {
+                return phase;
+            }
+            batch.decode.push_back(id);
+        } else if (outcome == Rejected::NoKvBlocks) {
+            decode_ready_.push_back(id);
+        } else {
+            return SchedulerError::Cache;
+        }
+    }
+
+    while (batch.num_seqs() < config_.max_num_seqs && batch.num_tokens() < config_.max_num_batched_tokens) {
+        SeqId id;
+        if (!prefill_ready_.empty()) {
+            id = prefill_ready_.front();
+            prefill_ready_.pop_front();
+        } else {
+            std::optional<SeqId> admitted;
+            const SchedulerError err = admit_one(&admitted);
+            if (err != SchedulerError::None) {
+                return err;
+            }
+            if (!admitted) {
+                break;
+            }
+            id = *admitted;
+        }
+        auto it = active_.find(id);
+        if (it == active_.end() || it->second.phase != Phase::PrefillReady) {
+            return SchedulerError::Invariant;
+        }
+        const size_t remaining = it->second.request.prompt_tokens - it->second.prefilled;
+        const size_t budget = config_.max_num_batched_tokens - batch.num_tokens();
+        const size_t tokens = std::min(remaining, budget);
+        const size_t offset = it->second.prefilled;
+        if (cache_.sequence(id) == nullptr) {
+            return SchedulerError::Invariant;
+        }
+        const SchedulerError phase = set_phase(id, Phase::PrefillReady, Phase::PrefillInFlight);
+        if (phase != SchedulerError::None) {
+            return phase;
+        }
+        batch.prefill.push_back({id, offset, tokens});
+    }
+
+    if (batch.empty()) {
+        return SchedulerError::None;
+    }
+    in_flight_ = batch;
+    *out = std::move(batch);
+    *has_batch = true;
+    return SchedulerError::None;
+}
+
+SchedulerError Scheduler::complete_batch(const std::vector<SeqId>& stopped, std::vector<Completion>* completed) {
+    completed->clear();
+    if (!in_flight_) {
+        return SchedulerError::NoBatchInFlight;
+    }
+    std::unordered_set<SeqId> stopped_set;
+    for (SeqId id : stopped) {
+        if (!stopped_set.insert(id).second) {
+            return SchedulerError::DuplicateStopped;
+        }
+        if (std::find(in_flight_->decode.begin(), in_flight_->decode.end(), id) == in_flight_->decode.end()) {
+            return SchedulerError::InvalidStopped;
+        }
+    }
+    Batch batch = std::move(*in_flight_);
+    in_flight_.reset();
+    for (const PrefillChunk& chunk : batch.prefill) {
+        auto it = active_.find(chunk.id);
+        if (it == active_.end() || it->second.phase != Phase::PrefillInFlight) {
+            return SchedulerError::Invariant;
+        }
+        it->second.prefilled += chunk.tokens;
+        if (it->second.prefilled == it->second.request.prompt_tokens) {
+            it->second.phase = Phase::DecodeReady;
+            decode_ready_.push_back(chunk.id);
+        } else {
+            it->second.phase = Phase::PrefillReady;
+            prefill_ready_.push_back(chunk.id);
+        }
+    }
+    for (SeqId id : batch.decode) {
+        auto it = active_.find(id);
+        if (it == active_.end() || it->second.phase != Phase::DecodeInFlight) {
+            return SchedulerError::Invariant;
+        }
+        ActiveRequest& active = it->second;
+        active.generated = std::min(active.generated + 1, active.request.max_new_tokens);
+        const bool was_stopped = stopped_set.count(id) != 0;
+        if (was_stopped || active.generated >= active.request.max_new_tokens) {
+            completed->push_back({id, active.generated, was_stopped ? FinishReason::Stopped : FinishReason::Length});
+            committed_kv_blocks_ -= active.reserved_blocks;
+            cache_.release(id);
+            active_.erase(it);
+        } else {
+            active.phase = Phase::DecodeReady;
+            decode_ready_.push_back(id);
+        }
+    }
+    return SchedulerError::None;
+}
+
+SchedulerError Scheduler::abort_batch() {
+    if (!in_flight_) {
+        return SchedulerError::NoBatchInFlight;
+    }
+    Batch batch = std::move(*in_flight_);
+    in_flight_.reset();
+    for (auto it = batch.prefill.rbegin(); it != batch.prefill.rend(); ++it) {
+        const SchedulerError phase = set_phase(it->id, Phase::PrefillInFlight, Phase::PrefillReady);
+        if (phase != SchedulerError::None) {
+            return phase;
+        }
+        prefill_ready_.push_front(it->id);
+    }
+    for (auto it = batch.decode.rbegin(); it != batch.decode.rend(); ++it) {
+        if (cache_.rollback_token(*it) != Rejected::None) {
+            return SchedulerError::Cache;
+        }
+        const SchedulerError phase = set_phase(*it, Phase::DecodeInFlight, Phase::DecodeReady);
+        if (phase != SchedulerError::None) {
+            return phase;
+        }
+        decode_ready_.push_front(*it);
+    }
+    return SchedulerError::None;
+}
+
+SchedulerError Scheduler::cancel(SeqId id, bool* removed) {
+    *removed = false;
+    if (in_flight_) {
+        const bool decoding =
+            std::find(in_flight_->decode.begin(), in_flight_->decode.end(), id) != in_flight_->decode.end();
+        const bool prefilling = std::any_of(in_flight_->prefill.begin(), in_flight_->prefill.end(),
+                                            [&](const PrefillChunk& c) { return c.id == id; });
+        if (decoding || prefilling) {
+            return SchedulerError::SequenceInFlight;
+        }
+    }
+    auto queued = std::find_if(waiting_.begin(), waiting_.end(), [&](const Request& r) { return r.id == id; });
+    if (queued != waiting_.end()) {
+        waiting_.erase(queued);
+        *removed = true;
+        return SchedulerError::None;
+    }
+    auto it = active_.find(id);
+    if (it != active_.end()) {
+        prefill_ready_.erase(std::remove(prefill_ready_.begin(), prefill_ready_.end(), id), prefill_ready_.end());
+        decode_ready_.erase(std::remove(decode_ready_.begin(), decode_ready_.end(), id), decode_ready_.end());
+        committed_kv_blocks_ -= it->second.reserved_blocks;
+        cache_.release(id);
+        active_.erase(it);
+        *removed = true;
+    }
+    return SchedulerError::None;
+}
+
+std::optional<size_t> Scheduler::remaining_tokens(SeqId id) const {
+    auto it = active_.find(id);
+    if (it == active_.end()) {
+        return std::nullopt;
+    }
+    return it->second.request.max_new_tokens - it->second.generated;
+}
+
+// ---- batch layout ----------------------------------------------------------------------
+
+namespace {
+
+LayoutError push_sequence(BatchLayout* layout, SeqId id, uint32_t state_slot, size_t position, size_t context,
+                          size_t tokens, const CacheManager& cache) {
+    const Sequence* seq = cache.sequence(id);
+    if (seq == nullptr) {
+        return LayoutError::MissingSequence;
+    }
+    const size_t blocks = cache.kv().blocks_for(context);
+    if (blocks > seq->blocks.size()) {
+        return LayoutError::MissingKvBlocks;
+    }
+    constexpr size_t kMax = std::numeric_limits<uint32_t>::max();
+    const size_t total_tokens = layout->num_tokens() + tokens;
+    if (position > kMax || context > kMax || total_tokens > kMax || layout->block_ids.size() + blocks > kMax) {
+        return LayoutError::IntegerOverflow;
+    }
+    layout->seq_ids.push_back(id);
+    layout->state_slots.push_back(state_slot);
+    layout->position_starts.push_back(static_cast<uint32_t>(position));
+    layout->context_lens.push_back(static_cast<uint32_t>(context));
+    layout->token_offsets.push_back(static_cast<uint32_t>(total_tokens));
+    layout->block_ids.insert(layout->block_ids.end(), seq->blocks.begin(), seq->blocks.begin() + blocks);
+    layout->block_table_offsets.push_back(static_cast<uint32_t>(layout->block_ids.size()));
+    return LayoutError::None;
+}
+
+}  // namespace
+
+LayoutError BatchLayout::build(const Batch& batch, const CacheManager& cache, BatchLayout* out, SeqId* offender) {
+    BatchLayout layout;
+    layout.num_decode = static_cast<uint32_t>(batch.decode.size());
+    layout.token_offsets.push_back(0);
+    layout.block_table_offsets.push_back(0);
+    std::unordered_set<SeqId> seen;
+    auto fail = [&](LayoutError error, SeqId id) {
+        if (offender != nullptr) {
+            *offender = id;
+        }
+        return error;
+    };
+    for (SeqId id : batch.decode) {
+        if (!seen.insert(id).second) {
+            return fail(LayoutError::DuplicateSequence, id);
+        }
+        const Sequence* seq = cache.sequence(id);
+        if (seq == nullptr) {
+            return fail(LayoutError::MissingSequence, id);
+        }
+        if (seq->tokens == 0) {
+            return fail(LayoutError::IntegerOverflow, id);  // checked_sub(1) on the decode position
+        }
+        const LayoutError pushed = push_sequence(&layout, id, seq->state_slot, seq->tokens - 1, seq->tokens, 1, cache);
+        if (pushed != LayoutError::None) {
+            return fail(pushed, id);
+        }
+    }
+    for (const PrefillChunk& chunk : batch.prefill) {
+        if (!seen.insert(chunk.id).second) {
+            return fail(LayoutError::DuplicateSequence, chunk.id);
+        }
+        const Sequence* seq = cache.sequence(chunk.id);
+        if (seq == nullptr) {
+            return fail(LayoutError::MissingSequence, chunk.id);
+        }
+        const size_t context = chunk.offset + chunk.tokens;
+        if (chunk.tokens == 0 || context > seq->tokens) {
+            return fail(LayoutError::InvalidPrefillRange, chunk.id);
+        }
+        const LayoutError pushed =
+            push_sequence(&layout, chunk.id, seq->state_slot, chunk.offset, context, chunk.tokens, cache);
+        if (pushed != LayoutError::None) {
+            return fail(pushed, chunk.id);
+        }
+    }
+    *out = std::move(layout);
+    return LayoutError::None;
+}
+
+}  // namespace runtime
+}  // namespace qwc

@@ -1,0 +1,234 @@
+// Host-side runtime: two-resource cache manager, continuous-batching scheduler and the
+// CSR batch layout.  C++ restatement of the reference's CUDA-free `qwc-runtime` crate
+// (crates/qwc-runtime/src/{cache,scheduler,layout}.rs) with the same names, argument
+// meaning and error behaviour, so that the decode step keeps the scheduler / KV-cache /
+// slot API it is driven by.  Prefix-cache snapshots (cache.rs:457-569) belong to the
+// prefill path and are not carried over.
+#pragma once
+
+#include <cstddef>
+#include <cstdint>
+#include <deque>
+#include <optional>
+#include <unordered_map>
+#include <vector>
+
+namespace qwc {
+namespace runtime {
+
+using SeqId = uint32_t;
+
+// crates/qwc-runtime/src/cache.rs:33-45
+enum class Rejected : int {
+    None = 0,
+    NoStateSlot = 1,
+    NoKvBlocks = 2,
+    AlreadyAdmitted = 3,
+    UnknownSequence = 4,
+    NothingToRollback = 5,
+};
+
+// crates/qwc-runtime/src/cache.rs:64-104: identical, indivisible slots; LIFO free list that
+// hands out 0, 1, 2, ... first.
+class StatePool {
+public:
+    explicit StatePool(size_t capacity);
+    std::optional<uint32_t> acquire();
+    void release(uint32_t slot);
+    size_t capacity() const { return capacity_; }
+    size_t in_use() const { return capacity_ - free_.size(); }
+    bool empty() const { return free_.empty(); }
+
+private:
+    size_t capacity_;
+    std::vector<uint32_t> free_;
+};
+
+// crates/qwc-runtime/src/cache.rs:112-182: paged KV pool with reference counts.
+class KvPool {
+public:
+    KvPool(size_t capacity, size_t block_size);
+    size_t blocks_for(size_t tokens) const { return (tokens + block_size_ - 1) / block_size_; }
+    size_t free_blocks() const { return free_.size(); }
+    size_t capacity() const { return capacity_; }
+    size_t block_size() const { return block_size_; }
+    bool acquire(size_t n, std::vector<uint32_t>* out);
+    void retain(const std::vector<uint32_t>& blocks);
+    void release(const std::vector<uint32_t>& blocks);
+
+private:
+    size_t block_size_;
+    size_t capacity_;
+    std::vector<uint32_t> free_;
+    std::vector<uint32_t> refs_;
+};
+
+// crates/qwc-runtime/src/cache.rs:185-191
+struct Sequence {
+    uint32_t state_slot = 0;
+    std::vector<uint32_t> blocks;
+    size_t tokens = 0;
+};
+
+// One change of the device-resident tables caused by a cache operation
+// (same layout as qwc_table_edit in the kernel ABI).
+struct TableEdit {
+    uint32_t slot;
+    uint32_t index;
+    uint32_t value;
+    uint32_t kind;  // 0 set block, 1 set tokens, 2 add tokens
+};
+
+// crates/qwc-runtime/src/cache.rs:300-449,571-594.  Every mutation is also recorded as table
+// edits so the device copy of (tokens, blocks) per slot can follow without a rebuild.
+class CacheManager {
+public:
+    CacheManager(size_t state_slots, size_t kv_blocks, size_t block_size);
+    Rejected admit(SeqId id, size_t prompt_tokens);
+    Rejected append_token(SeqId id);
+    Rejected rollback_token(SeqId id);
+    void release(SeqId id);
+    const Sequence* sequence(SeqId id) const;
+    size_t active() const { return seqs_.size(); }
+    const StatePool& states() const { return states_; }
+    const KvPool& kv() const { return kv_; }
+    // need / free of the last NoKvBlocks rejection (cache.rs:37)
+    size_t last_need() const { return last_need_; }
+    size_t last_free() const { return last_free_; }
+    // Edits accumulated since the last drain, in order.
+    std::vector<TableEdit> drain_edits();
+
+private:
+    StatePool states_;
+    KvPool kv_;
+    std::unordered_map<SeqId, Sequence> seqs_;
+    std::vector<TableEdit> edits_;
+    size_t last_need_ = 0;
+    size_t last_free_ = 0;
+};
+
+// crates/qwc-runtime/src/scheduler.rs:12-35
+struct SchedulerConfig {
+    size_t max_num_seqs;
+    size_t max_num_batched_tokens;
+};
+
+struct Request {
+    SeqId id;
+    size_t prompt_tokens;
+    size_t max_new_tokens;
+};
+
+struct PrefillChunk {
+    SeqId id;
+    size_t offset;
+    size_t tokens;
+};
+
+struct Batch {
+    std::vector<PrefillChunk> prefill;
+    std::vector<SeqId> decode;
+    size_t num_seqs() const { return prefill.size() + decode.size(); }
+    size_t num_tokens() const;
+    bool empty() const { return prefill.empty() && decode.empty(); }
+};
+
+enum class FinishReason : int { Length = 0, Stopped = 1 };
+
+struct Completion {
+    SeqId id;
+    size_t generated_tokens;
+    FinishReason reason;
+};
+
+// crates/qwc-runtime/src/scheduler.rs:105-112
+enum class SubmitError : int {
+    None = 0,
+    Duplicate = 1,
+    EmptyPrompt = 2,
+    NoOutputTokens = 3,
+    NoStateCapacity = 4,
+    ContextTooLong = 5,
+};
+
+// crates/qwc-runtime/src/scheduler.rs:135-144
+enum class SchedulerError : int {
+    None = 0,
+    BatchInFlight = 1,
+    NoBatchInFlight = 2,
+    SequenceInFlight = 3,
+    InvalidStopped = 4,
+    DuplicateStopped = 5,
+    Invariant = 6,
+    Cache = 7,
+};
+
+// crates/qwc-runtime/src/scheduler.rs:190-668: FIFO admission, round-robin decode, one batch
+// in flight, full rollback of a batch that was planned but not executed.
+class Scheduler {
+public:
+    Scheduler(SchedulerConfig config, CacheManager cache);
+    SubmitError submit(Request request);
+    // Returns None with *has_batch == false when there is nothing to run.
+    SchedulerError next_batch(Batch* batch, bool* has_batch);
+    SchedulerError complete_batch(const std::vector<SeqId>& stopped, std::vector<Completion>* completed);
+    SchedulerError abort_batch();
+    SchedulerError cancel(SeqId id, bool* removed);
+    std::optional<size_t> remaining_tokens(SeqId id) const;
+    size_t waiting() const { return waiting_.size(); }
+    size_t active() const { return active_.size(); }
+    size_t committed_kv_blocks() const { return committed_kv_blocks_; }
+    const CacheManager& cache() const { return cache_; }
+    CacheManager& cache_mut() { return cache_; }
+    const Batch* in_flight() const { return in_flight_ ? &*in_flight_ : nullptr; }
+
+private:
+    enum class Phase { PrefillReady, PrefillInFlight, DecodeReady, DecodeInFlight };
+    struct ActiveRequest {
+        Request request;
+        size_t reserved_blocks;
+        size_t prefilled;
+        size_t generated;
+        Phase phase;
+    };
+    SchedulerError admit_one(std::optional<SeqId>* admitted);
+    SchedulerError set_phase(SeqId id, Phase expected, Phase next);
+
+    SchedulerConfig config_;
+    CacheManager cache_;
+    std::deque<Request> waiting_;
+    std::deque<SeqId> prefill_ready_;
+    std::deque<SeqId> decode_ready_;
+    std::unordered_map<SeqId, ActiveRequest> active_;
+    size_t committed_kv_blocks_ = 0;
+    std::optional<Batch> in_flight_;
+};
+
+// crates/qwc-runtime/src/layout.rs:11-17
+enum class LayoutError : int {
+    None = 0,
+    MissingSequence = 1,
+    DuplicateSequence = 2,
+    InvalidPrefillRange = 3,
+    MissingKvBlocks = 4,
+    IntegerOverflow = 5,
+};
+
+// crates/qwc-runtime/src/layout.rs:37-52: struct-of-arrays, u32, decode rows first.
+struct BatchLayout {
+    uint32_t num_decode = 0;
+    std::vector<SeqId> seq_ids;
+    std::vector<uint32_t> state_slots;
+    std::vector<uint32_t> position_starts;
+    std::vector<uint32_t> context_lens;
+    std::vector<uint32_t> token_offsets;
+    std::vector<uint32_t> block_table_offsets;
+    std::vector<uint32_t> block_ids;
+
+    static LayoutError build(const Batch& batch, const CacheManager& cache, BatchLayout* out, SeqId* offender);
+    size_t num_seqs() const { return seq_ids.size(); }
+    size_t num_tokens() const { return token_offsets.empty() ? 0 : token_offsets.back(); }
+};
+
+}  // namespace runtime
+}  // namespace qwc

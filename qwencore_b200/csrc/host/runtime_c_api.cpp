@@ -1,0 +1,184 @@
+// C entry points of the host runtime (include/qwc_engine.h, cache / scheduler / layout part).
+#include <algorithm>
+#include <cstring>
+
+#include "../../../include/qwc_engine.h"
+#include "runtime.h"
+#include "runtime_handles.h"
+
+using namespace qwc::runtime;
+
+extern "C" {
+
+qwc_cache* qwc_cache_new(size_t state_slots, size_t kv_blocks, size_t block_size) {
+    if (block_size == 0) {
+        return nullptr;
+    }
+    auto* handle = new qwc_cache;
+    handle->owned.reset(new CacheManager(state_slots, kv_blocks, block_size));
+    handle->cache = handle->owned.get();
+    return handle;
+}
+
+void qwc_cache_free(qwc_cache* cache) {
+    if (cache != nullptr && cache->owned) {
+        delete cache;
+    }
+}
+
+int qwc_cache_admit(qwc_cache* cache, uint32_t id, size_t prompt_tokens) {
+    return static_cast<int>(cache->cache->admit(id, prompt_tokens));
+}
+
+int qwc_cache_append_token(qwc_cache* cache, uint32_t id) { return static_cast<int>(cache->cache->append_token(id)); }
+
+int qwc_cache_rollback_token(qwc_cache* cache, uint32_t id) {
+    return static_cast<int>(cache->cache->rollback_token(id));
+}
+
+void qwc_cache_release(qwc_cache* cache, uint32_t id) { cache->cache->release(id); }
+
+int qwc_cache_sequence(const qwc_cache* cache, uint32_t id, uint32_t* state_slot, size_t* tokens, uint32_t* blocks,
+                       size_t max_blocks, size_t* num_blocks) {
+    const Sequence* seq = cache->cache->sequence(id);
+    if (seq == nullptr) {
+        return static_cast<int>(Rejected::UnknownSequence);
+    }
+    if (state_slot != nullptr) {
+        *state_slot = seq->state_slot;
+    }
+    if (tokens != nullptr) {
+        *tokens = seq->tokens;
+    }
+    if (num_blocks != nullptr) {
+        *num_blocks = seq->blocks.size();
+    }
+    if (blocks != nullptr) {
+        std::copy_n(seq->blocks.begin(), std::min(max_blocks, seq->blocks.size()), blocks);
+    }
+    return 0;
+}
+
+size_t qwc_cache_free_blocks(const qwc_cache* cache) { return cache->cache->kv().free_blocks(); }
+size_t qwc_cache_states_in_use(const qwc_cache* cache) { return cache->cache->states().in_use(); }
+size_t qwc_cache_active(const qwc_cache* cache) { return cache->cache->active(); }
+
+void qwc_cache_last_shortage(const qwc_cache* cache, size_t* need, size_t* free_blocks) {
+    *need = cache->cache->last_need();
+    *free_blocks = cache->cache->last_free();
+}
+
+size_t qwc_cache_drain_edits(qwc_cache* cache, qwc_table_edit* edits, size_t max_edits) {
+    static_assert(sizeof(qwc_table_edit) == sizeof(TableEdit), "edit layouts must match");
+    const std::vector<TableEdit> pending = cache->cache->drain_edits();
+    const size_t n = std::min(max_edits, pending.size());
+    if (n > 0 && edits != nullptr) {
+        std::memcpy(edits, pending.data(), n * sizeof(TableEdit));
+    }
+    return pending.size();
+}
+
+qwc_scheduler* qwc_scheduler_new(size_t max_num_seqs, size_t max_num_batched_tokens, size_t state_slots,
+                                 size_t kv_blocks, size_t block_size) {
+    if (max_num_seqs == 0 || max_num_batched_tokens == 0 || block_size == 0) {
+        return nullptr;  // SchedulerConfig::new asserts both limits are positive
+    }
+    auto* handle = new qwc_scheduler{
+        Scheduler(SchedulerConfig{max_num_seqs, max_num_batched_tokens}, CacheManager(state_slots, kv_blocks, block_size)),
+        {}};
+    handle->cache_view.cache = &handle->scheduler.cache_mut();
+    return handle;
+}
+
+void qwc_scheduler_free(qwc_scheduler* scheduler) { delete scheduler; }
+
+int qwc_scheduler_submit(qwc_scheduler* scheduler, uint32_t id, size_t prompt_tokens, size_t max_new_tokens) {
+    return static_cast<int>(scheduler->scheduler.submit(Request{id, prompt_tokens, max_new_tokens}));
+}
+
+int qwc_scheduler_next_batch(qwc_scheduler* scheduler, uint32_t* decode_ids, size_t* num_decode,
+                             qwc_prefill_chunk* prefill, size_t* num_prefill) {
+    Batch batch;
+    bool has_batch = false;
+    *num_decode = 0;
+    *num_prefill = 0;
+    const SchedulerError error = scheduler->scheduler.next_batch(&batch, &has_batch);
+    if (error != SchedulerError::None || !has_batch) {
+        return static_cast<int>(error);
+    }
+    *num_decode = batch.decode.size();
+    *num_prefill = batch.prefill.size();
+    std::copy(batch.decode.begin(), batch.decode.end(), decode_ids);
+    for (size_t i = 0; i < batch.prefill.size(); ++i) {
+        prefill[i] = {batch.prefill[i].id, static_cast<uint32_t>(batch.prefill[i].offset),
+                      static_cast<uint32_t>(batch.prefill[i].tokens)};
+    }
+    return 0;
+}
+
+int qwc_scheduler_complete_batch(qwc_scheduler* scheduler, const uint32_t* stopped, size_t num_stopped,
+                                 qwc_completion* completed, size_t max_completed, size_t* num_completed) {
+    std::vector<SeqId> stopped_ids(stopped, stopped + num_stopped);
+    std::vector<Completion> done;
+    const SchedulerError error = scheduler->scheduler.complete_batch(stopped_ids, &done);
+    *num_completed = done.size();
+    for (size_t i = 0; i < done.size() && i < max_completed; ++i) {
+        completed[i] = {done[i].id, static_cast<uint32_t>(done[i].generated_tokens),
+                        static_cast<uint32_t>(done[i].reason)};
+    }
+    return static_cast<int>(error);
+}
+
+int qwc_scheduler_abort_batch(qwc_scheduler* scheduler) { return static_cast<int>(scheduler->scheduler.abort_batch()); }
+
+int qwc_scheduler_cancel(qwc_scheduler* scheduler, uint32_t id, int* removed) {
+    bool was = false;
+    const SchedulerError error = scheduler->scheduler.cancel(id, &was);
+    *removed = was ? 1 : 0;
+    return static_cast<int>(error);
+}
+
+long long qwc_scheduler_remaining_tokens(const qwc_scheduler* scheduler, uint32_t id) {
+    const auto remaining = scheduler->scheduler.remaining_tokens(id);
+    return remaining ? static_cast<long long>(*remaining) : -1;
+}
+
+size_t qwc_scheduler_waiting(const qwc_scheduler* scheduler) { return scheduler->scheduler.waiting(); }
+size_t qwc_scheduler_active(const qwc_scheduler* scheduler) { return scheduler->scheduler.active(); }
+size_t qwc_scheduler_committed_kv_blocks(const qwc_scheduler* scheduler) {
+    return scheduler->scheduler.committed_kv_blocks();
+}
+qwc_cache* qwc_scheduler_cache(qwc_scheduler* scheduler) { return &scheduler->cache_view; }
+
+int qwc_layout_build(const qwc_cache* cache, const uint32_t* decode_ids, size_t num_decode,
+                     const qwc_prefill_chunk* prefill, size_t num_prefill, uint32_t* seq_ids, uint32_t* state_slots,
+                     uint32_t* position_starts, uint32_t* context_lens, uint32_t* token_offsets,
+                     uint32_t* block_table_offsets, uint32_t* block_ids, size_t max_block_ids, uint32_t* offender) {
+    Batch batch;
+    batch.decode.assign(decode_ids, decode_ids + num_decode);
+    for (size_t i = 0; i < num_prefill; ++i) {
+        batch.prefill.push_back({prefill[i].id, prefill[i].offset, prefill[i].tokens});
+    }
+    BatchLayout layout;
+    SeqId bad = 0;
+    const LayoutError error = BatchLayout::build(batch, *cache->cache, &layout, &bad);
+    if (error != LayoutError::None) {
+        if (offender != nullptr) {
+            *offender = bad;
+        }
+        return static_cast<int>(error);
+    }
+    if (layout.block_ids.size() > max_block_ids) {
+        return static_cast<int>(LayoutError::IntegerOverflow);
+    }
+    std::copy(layout.seq_ids.begin(), layout.seq_ids.end(), seq_ids);
+    std::copy(layout.state_slots.begin(), layout.state_slots.end(), state_slots);
+    std::copy(layout.position_starts.begin(), layout.position_starts.end(), position_starts);
+    std::copy(layout.context_lens.begin(), layout.context_lens.end(), context_lens);
+    std::copy(layout.token_offsets.begin(), layout.token_offsets.end(), token_offsets);
+    std::copy(layout.block_table_offsets.begin(), layout.block_table_offsets.end(), block_table_offsets);
+    std::copy(layout.block_ids.begin(), layout.block_ids.end(), block_ids);
+    return 0;
+}
+
+}  // extern "C"

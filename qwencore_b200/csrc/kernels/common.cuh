@@ -109,17 +109,30 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
     return done != 0;
 }
 
-// Bounded wait: gives up after ~2^22 polls (hundreds of milliseconds), records `code`
-// in the status word and returns false; callers then skip the data and exit cleanly.
+// Bounded wait: gives up after ~20 ms of polling (a bulk copy completes in microseconds),
+// records `code` in the status word and returns false; callers then skip the data and
+// exit cleanly.  Kernels that wait also return at once when the status word is already
+// set, so one failed wait cannot serialise into a long stall over the whole grid.
 __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity, int code,
                                                   int* status) {
-    for (int spin = 0; spin < (1 << 22); ++spin) {
-        if (mbar_try_wait(bar, parity)) {
-            return true;
+    const long long start = clock64();
+    for (;;) {
+#pragma unroll 1
+        for (int spin = 0; spin < 128; ++spin) {
+            if (mbar_try_wait(bar, parity)) {
+                return true;
+            }
+        }
+        if (clock64() - start > 40000000ll) {
+            break;
         }
     }
     atomicCAS(status, 0, code);
     return false;
+}
+
+__device__ __forceinline__ bool status_is_set(const int* status) {
+    return *reinterpret_cast<const volatile int*>(status) != 0;
 }
 
 // Global -> shared bulk copy; both addresses 16-byte aligned, bytes % 16 == 0.

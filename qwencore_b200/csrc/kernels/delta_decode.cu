@@ -45,6 +45,9 @@ __global__ void __launch_bounds__(kThreads, 4) delta_decode_int8_kernel(
     __shared__ uint64_t bars[kMaxParts];
     __shared__ int failed;
 
+    if (status_is_set(status)) {
+        return;
+    }
     const int h = blockIdx.x;
     const int b = blockIdx.y;
     const int rows_here = kDim / gridDim.z;

@@ -7,9 +7,12 @@
 //
 // Design for sm_100a.  The op is HBM-bound (4.5 bits per weight, read once), so the
 // kernel is organised around keeping ~50 KB of 128-bit weight loads in flight per SM:
-//   * one CTA per SM; each warp owns 16 or 32 weight rows and walks K in 128-element
-//     chunks, prefetching the next chunks' nibbles and block scales into registers with
-//     16-byte streaming loads (L1 no-allocate);
+//   * one CTA per SM; each warp owns 16 or 32 weight rows and a private two-stage ring
+//     in shared memory; every stage is filled by bulk-async copies (TMA 1-D) of 256
+//     contiguous bytes per weight row plus the 128-byte pieces of the swizzled block
+//     scales, completing on the warp's own mbarrier.  256-byte runs per row matter:
+//     a probe on this part reads 64-byte runs over 34816 rows at 3.6 TB/s and 256-byte
+//     runs at 5.4 TB/s (DRAM page locality), and the copies cost no registers;
 //   * the e2m1 nibbles are expanded to f16 by the hardware converter and multiplied by
 //     their e4m3 block scale in f16 - the product has at most six significant bits, so
 //     it is exact - directly into mma.sync A fragments: the dequantised weights never
@@ -39,10 +42,13 @@ namespace cg = cooperative_groups;
 namespace qwc {
 namespace {
 
-constexpr int kChunk = 128;      // K elements per chunk: 64 bytes of nibbles per row
-constexpr int kStageChunks = 4;  // chunks per activation stage (512 K elements)
+constexpr int kChunk = 128;   // K elements per chunk: 64 bytes of nibbles (128 of e4m3) per row
+constexpr int kRowRun = 256;  // bytes of one weight row fetched by one bulk copy
+constexpr int kRowPitch = 320;  // shared-memory pitch of a row: 16-byte groups of rows g, g+1 differ by 4
+constexpr int kWeightStages = 2;
 constexpr int kMaxWarps = 16;
 constexpr int kMaxBatch = 32;
+constexpr int kSmemLimit = 232448 - 1024;  // 227 KiB opt-in limit minus static barriers
 
 struct GemvParams {
     const uint8_t* packed[2];
@@ -58,6 +64,7 @@ struct GemvParams {
     int num_tiles;
     int tiles_per_cta;
     int splits;
+    int* status;
 };
 
 // Weight formats served by the one streaming kernel.
@@ -71,11 +78,19 @@ struct Config {
     static constexpr bool FP8 = MODE == kFp8Rows;
     static constexpr int kRows = SWIGLU ? 4 : 2 * MT;  // weight rows per thread
     static constexpr int kMTiles = SWIGLU ? 2 : MT;    // m16 tiles per warp
-    static constexpr int kUnits = SWIGLU ? 2 : 1;      // 16-byte scale units per chunk
-    static constexpr int kVec = FP8 ? 2 : 1;           // 16-byte weight loads per row per chunk
-    static constexpr int kPrefetch = (kRows == 2 && !FP8) ? 4 : 2;
-    static constexpr int kStageBytes = kStageChunks * NT * 4 * 512;
-    static constexpr int kSmemBytes = 2 * kStageBytes;
+    static constexpr int kUnits = FP8 ? 0 : (SWIGLU ? 2 : 1);  // scale sets per warp
+    static constexpr int kVec = FP8 ? 2 : 1;           // 16-byte weight reads per row per chunk
+    static constexpr int kChunkBytes = FP8 ? 128 : 64; // bytes of one row per chunk
+    static constexpr int kStageChunks = kRowRun / kChunkBytes;  // chunks per weight stage: 4 or 2
+    static constexpr int kWarpRows = 8 * kRows;        // weight rows staged per warp: 16 or 32
+    static constexpr int kScaleBytes = kUnits * kStageChunks * 2 * 128;
+    static constexpr int kWarpStageBytes = kWarpRows * kRowPitch + kScaleBytes;
+    static constexpr int kWarpBytes = kWeightStages * kWarpStageBytes;
+    static constexpr int kXChunks = (NT == 4 || FP8) ? 2 : 4;   // chunks per activation stage
+    static constexpr int kXStageBytes = kXChunks * NT * 4 * 512;
+    static constexpr int kXBytes = 2 * kXStageBytes;
+    static constexpr int kMaxTiles =
+        (kSmemLimit - kXBytes) / kWarpBytes < kMaxWarps ? (kSmemLimit - kXBytes) / kWarpBytes : kMaxWarps;
 };
 
 template <int NT, int MT, int MODE>
@@ -85,9 +100,11 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) nvfp4_gemv_kernel(const Gem
     constexpr bool FP8 = C::FP8;
     constexpr int V = C::kVec;
     constexpr int R = C::kRows;
-    constexpr int PF = C::kPrefetch;
+    constexpr int WC = C::kStageChunks;
+    constexpr int XC = C::kXChunks;
 
-    extern __shared__ __align__(16) unsigned char smem[];
+    extern __shared__ __align__(128) unsigned char smem[];
+    __shared__ uint64_t full[kMaxWarps][kWeightStages];
 
     const int lane = threadIdx.x & 31;
     const int warp = threadIdx.x >> 5;
@@ -98,75 +115,73 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) nvfp4_gemv_kernel(const Gem
     const int row_group = blockIdx.x / p.splits;
     const int split = blockIdx.x - row_group * p.splits;
     const int tile = row_group * p.tiles_per_cta + warp;
-    const bool active = warp < p.tiles_per_cta && tile < p.num_tiles;
+    const bool active = warp < p.tiles_per_cta && tile < p.num_tiles && !status_is_set(p.status);
 
     const int K = p.in_features;
     const int chunks = K / kChunk;
     const int c_begin = static_cast<int>(static_cast<long long>(chunks) * split / p.splits);
     const int c_end = static_cast<int>(static_cast<long long>(chunks) * (split + 1) / p.splits);
     const int group_blocks = K / 64;
+    const int row_bytes = FP8 ? K : K / 2;
 
-    // Rows of this thread and the word of the scale unit that belongs to each.
+    unsigned char* x_base = smem;
+    unsigned char* ring = smem + C::kXBytes + warp * C::kWarpBytes;
+
+    // Row of staged slot `i` (0..R-1) for fragment row group `gg`, and the word of the
+    // 16-byte scale unit that belongs to it.
+    const int row_block = (SWIGLU || MT == 1) ? (tile >> 3) : (tile >> 2);
+    const int quad = (SWIGLU || MT == 1) ? (tile & 3) : (tile & 3);
+    const int hi = (SWIGLU || MT == 1) ? ((tile & 7) >> 2) : 0;
+    auto row_of = [&](int i, int gg) {
+        const int j = (SWIGLU || MT == 1) ? (2 * hi + (i & 1)) : i;
+        return 128 * row_block + 8 * quad + gg + 32 * j;
+    };
     int rows[R];
-    int scale_word[R];
-    int row_block, rho;
-    if (SWIGLU || MT == 1) {
-        row_block = tile >> 3;
-        const int u = tile & 7;
-        rho = 8 * (u & 3) + g;
-        const int hi = u >> 2;
-#pragma unroll
-        for (int i = 0; i < R; ++i) {
-            rows[i] = 128 * row_block + rho + 32 * (2 * hi + (i & 1));
-            scale_word[i] = 2 * hi + (i & 1);
-        }
-    } else {
-        row_block = tile >> 2;
-        rho = 8 * (tile & 3) + g;
-#pragma unroll
-        for (int i = 0; i < R; ++i) {
-            rows[i] = 128 * row_block + rho + 32 * i;
-            scale_word[i] = i;
-        }
-    }
-
-    const uint8_t* weight_ptr[R];
     bool row_ok[R];
 #pragma unroll
     for (int i = 0; i < R; ++i) {
-        const int matrix = SWIGLU ? (i >> 1) : 0;
+        rows[i] = row_of(i, g);
         row_ok[i] = active && rows[i] < p.out_features;
-        // Bytes per weight row: K / 2 nibbles, or K e4m3 bytes.
-        weight_ptr[i] = p.packed[matrix] + static_cast<size_t>(row_ok[i] ? rows[i] : 0) * (FP8 ? K : K / 2) + 16 * t;
-    }
-    const uint8_t* scale_ptr[C::kUnits];
-#pragma unroll
-    for (int m = 0; m < C::kUnits; ++m) {
-        scale_ptr[m] = p.scales[m] + (static_cast<size_t>(active ? row_block : 0) * group_blocks + (t >> 1)) * 512 +
-                       rho * 16;
     }
 
-    uint4 wq[PF][R][V];
-    uint4 sq[PF][C::kUnits];
+    // ---- weight staging: one bulk copy per row and stage, one mbarrier per stage -------
+    if (lane == 0) {
+        for (int s = 0; s < kWeightStages; ++s) {
+            mbar_init(&full[warp][s], 1);
+        }
+        mbar_fence_init();
+    }
+    __syncwarp();
 
-    auto load_chunk = [&](int slot, int c) {
-        if (c < c_end) {
-#pragma unroll
-            for (int i = 0; i < R; ++i) {
-#pragma unroll
-                for (int v = 0; v < V; ++v) {
-                    // A quad covers 64 contiguous bytes of the row per load instruction.
-                    wq[slot][i][v] = row_ok[i] ? ldg_stream(weight_ptr[i] + static_cast<size_t>(c) * (64 * V) + 64 * v)
-                                               : make_uint4(0, 0, 0, 0);
-                }
-            }
-            if (!FP8) {
-#pragma unroll
-                for (int m = 0; m < C::kUnits; ++m) {
-                    sq[slot][m] = active ? ldg_stream(scale_ptr[m] + static_cast<size_t>(c) * 1024)
-                                         : make_uint4(0, 0, 0, 0);
-                }
-            }
+    const int my_copy_row = row_of(lane >> 3, lane & 7);
+    const bool my_copy_ok = active && lane < C::kWarpRows && my_copy_row < p.out_features;
+    const int valid_rows = __popc(__ballot_sync(0xffffffffu, my_copy_ok));
+    const uint8_t* my_copy_src =
+        p.packed[SWIGLU ? (lane >> 4) : 0] + static_cast<size_t>(my_copy_ok ? my_copy_row : 0) * row_bytes;
+    // lanes 0..(kUnits * 2 WC - 1) copy the 128-byte scale pieces: unit = lane / (2 WC), piece = lane % (2 WC)
+    const bool my_scale_lane = !FP8 && active && lane < C::kUnits * 2 * WC;
+    const uint8_t* my_scale_src =
+        FP8 ? nullptr
+            : p.scales[SWIGLU ? (lane / (2 * WC)) : 0] +
+                  (static_cast<size_t>(active ? row_block : 0) * group_blocks + (lane % (2 * WC))) * 512 + quad * 128;
+
+    auto issue_weights = [&](int stage) {
+        const int slot = stage % kWeightStages;
+        const int first = c_begin + stage * WC;
+        const int n = min(WC, c_end - first);
+        unsigned char* dst = ring + slot * C::kWarpStageBytes;
+        if (lane == 0) {
+            const uint32_t bytes = valid_rows * n * C::kChunkBytes + (FP8 ? 0 : C::kUnits * n * 2 * 128);
+            mbar_arrive_expect_tx(&full[warp][slot], bytes);
+        }
+        __syncwarp();
+        if (my_copy_ok) {
+            bulk_g2s(dst + lane * kRowPitch, my_copy_src + static_cast<size_t>(first) * C::kChunkBytes,
+                     n * C::kChunkBytes, &full[warp][slot]);
+        }
+        if (my_scale_lane && (lane % (2 * WC)) < 2 * n) {
+            bulk_g2s(dst + C::kWarpRows * kRowPitch + lane * 128,
+                     my_scale_src + static_cast<size_t>(first) * 1024, 128, &full[warp][slot]);
         }
     };
 
@@ -177,8 +192,8 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) nvfp4_gemv_kernel(const Gem
     constexpr int kHeld = 2;
     uint4 held[kHeld][2];
     auto stage_units = [&](int stage) {
-        const int first = c_begin + stage * kStageChunks;
-        const int n = min(kStageChunks, c_end - first);
+        const int first = c_begin + stage * XC;
+        const int n = min(XC, c_end - first);
         return n * NT * 64;
     };
     auto unit_source = [&](int stage, int u, bool& valid) {
@@ -190,17 +205,17 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) nvfp4_gemv_kernel(const Gem
         const int cc = rest / NT;
         const int token = 8 * n + gg;
         valid = token < p.batch;
-        // Element e of lane (g, t) is k = 32 t + e for nibbles (one 16-byte load per row);
-        // for bytes the two loads sit 64 bytes apart: k = 16 t + e, then 64 + 16 t + (e - 16).
-        const int k = (c_begin + stage * kStageChunks + cc) * kChunk + (FP8 ? 64 * jj + 16 * tt : 32 * tt + 16 * jj);
+        // Element e of lane (g, t) is k = 32 t + e for nibbles (one 16-byte read per row);
+        // for bytes the two reads sit 64 bytes apart: k = 16 t + e, then 64 + 16 t + (e - 16).
+        const int k = (c_begin + stage * XC + cc) * kChunk + (FP8 ? 64 * jj + 16 * tt : 32 * tt + 16 * jj);
         return p.x + static_cast<size_t>(valid ? token : 0) * K + k;
     };
-    auto unit_store = [&](unsigned char* buffer, int u, const uint4& lo, const uint4& hi) {
+    auto unit_store = [&](unsigned char* buffer, int u, const uint4& lo, const uint4& hi4) {
         const int jj = u & 1;
         const int tt = (u >> 1) & 3;
         const int gg = (u >> 3) & 7;
         const int rest = u >> 6;  // cc * NT + n
-        const uint32_t in[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
+        const uint32_t in[8] = {lo.x, lo.y, lo.z, lo.w, hi4.x, hi4.y, hi4.z, hi4.w};
         uint32_t out[8];
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
@@ -229,7 +244,7 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) nvfp4_gemv_kernel(const Gem
         }
     };
     auto stage_commit = [&](int stage) {
-        unsigned char* buffer = smem + (stage & 1) * C::kStageBytes;
+        unsigned char* buffer = x_base + (stage & 1) * C::kXStageBytes;
         const int total = stage_units(stage);
 #pragma unroll
         for (int h = 0; h < kHeld; ++h) {
@@ -242,12 +257,12 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) nvfp4_gemv_kernel(const Gem
         for (int u = threadIdx.x + kHeld * threads; u < total; u += threads) {
             bool valid;
             const __nv_bfloat16* src = unit_source(stage, u, valid);
-            uint4 lo = make_uint4(0, 0, 0, 0), hi = lo;
+            uint4 lo = make_uint4(0, 0, 0, 0), hi4 = lo;
             if (valid) {
                 lo = *reinterpret_cast<const uint4*>(src);
-                hi = *reinterpret_cast<const uint4*>(src + 8);
+                hi4 = *reinterpret_cast<const uint4*>(src + 8);
             }
-            unit_store(buffer, u, lo, hi);
+            unit_store(buffer, u, lo, hi4);
         }
     };
 
@@ -263,17 +278,37 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) nvfp4_gemv_kernel(const Gem
         }
     }
 
-    auto compute_chunk = [&](const unsigned char* xs, const uint4 (&w)[R][V], const uint4 (&s)[C::kUnits]) {
+    // One chunk: `ws` is the warp's weight stage, `q` the chunk inside it, `xs` the chunk's
+    // activation block.
+    auto compute_chunk = [&](const unsigned char* xs, const unsigned char* ws, int q) {
+        uint4 w[R][V];
+#pragma unroll
+        for (int i = 0; i < R; ++i) {
+#pragma unroll
+            for (int v = 0; v < V; ++v) {
+                w[i][v] = *reinterpret_cast<const uint4*>(ws + (8 * i + g) * kRowPitch + q * C::kChunkBytes + 64 * v +
+                                                          16 * t);
+            }
+        }
         // Block scales of this thread's two 16-element groups, per row, broadcast to f16x2.
         uint32_t scale_lo[R], scale_hi[R];
+        if (!FP8) {
 #pragma unroll
-        for (int i = 0; i < (FP8 ? 0 : R); ++i) {
-            const uint4& unit = s[SWIGLU ? (i >> 1) : 0];
-            const int sel = scale_word[i];
-            const uint32_t word = sel == 0 ? unit.x : (sel == 1 ? unit.y : (sel == 2 ? unit.z : unit.w));
-            const uint32_t pair = cvt_e4m3x2_to_f16x2(word >> (16 * (t & 1)));
-            scale_lo[i] = __byte_perm(pair, 0, 0x1010);
-            scale_hi[i] = __byte_perm(pair, 0, 0x3232);
+            for (int m = 0; m < C::kUnits; ++m) {
+                const uint4 unit = *reinterpret_cast<const uint4*>(ws + C::kWarpRows * kRowPitch +
+                                                                   (m * 2 * WC + 2 * q + (t >> 1)) * 128 + g * 16);
+#pragma unroll
+                for (int i = 0; i < R; ++i) {
+                    if ((SWIGLU ? (i >> 1) : 0) != m) {
+                        continue;
+                    }
+                    const int sel = (SWIGLU || MT == 1) ? (2 * hi + (i & 1)) : i;
+                    const uint32_t word = sel == 0 ? unit.x : (sel == 1 ? unit.y : (sel == 2 ? unit.z : unit.w));
+                    const uint32_t pair = cvt_e4m3x2_to_f16x2(word >> (16 * (t & 1)));
+                    scale_lo[i] = __byte_perm(pair, 0, 0x1010);
+                    scale_hi[i] = __byte_perm(pair, 0, 0x3232);
+                }
+            }
         }
 #pragma unroll
         for (int sp = 0; sp < 4; ++sp) {
@@ -319,35 +354,53 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) nvfp4_gemv_kernel(const Gem
     };
 
     // ---- main loop ------------------------------------------------------------------
-    const int num_stages = (c_end - c_begin + kStageChunks - 1) / kStageChunks;
+    const int total_chunks = c_end - c_begin;
+    const int num_wstages = (total_chunks + WC - 1) / WC;
+    const int num_xstages = (total_chunks + XC - 1) / XC;
+    bool alive = active;
+    if (alive) {
 #pragma unroll
-    for (int slot = 0; slot < PF; ++slot) {
-        load_chunk(slot, c_begin + slot);
+        for (int s = 0; s < kWeightStages; ++s) {
+            if (s < num_wstages) {
+                issue_weights(s);
+            }
+        }
     }
-    if (num_stages > 0) {
+    if (num_xstages > 0) {
         stage_issue(0);
         stage_commit(0);
     }
-    for (int stage = 0; stage < num_stages; ++stage) {
-        __syncthreads();  // stage visible; the other buffer is free again
-        const bool more = stage + 1 < num_stages;
-        if (more) {
-            stage_issue(stage + 1);
+    for (int wstage = 0; wstage < num_wstages; ++wstage) {
+        const int slot = wstage % kWeightStages;
+        if (alive) {
+            const bool arrived =
+                mbar_wait_bounded(&full[warp][slot], (wstage / kWeightStages) & 1, kStatusGemvWait, p.status);
+            alive = __all_sync(0xffffffffu, arrived);
         }
-        const unsigned char* xs = smem + (stage & 1) * C::kStageBytes;
-        const int first = c_begin + stage * kStageChunks;
+        const unsigned char* ws = ring + slot * C::kWarpStageBytes;
 #pragma unroll
-        for (int q = 0; q < kStageChunks; ++q) {
-            const int c = first + q;
-            if (c < c_end) {
-                if (active) {
-                    compute_chunk(xs + q * (NT * 4 * 512), wq[q % PF], sq[q % PF]);
+        for (int q = 0; q < WC; ++q) {
+            const int rel = wstage * WC + q;
+            if (rel < total_chunks) {
+                const int xstage = rel / XC;
+                const bool more = xstage + 1 < num_xstages;
+                if (rel % XC == 0) {
+                    __syncthreads();  // activation stage visible; the other buffer is free again
+                    if (more) {
+                        stage_issue(xstage + 1);
+                    }
                 }
-                load_chunk(q % PF, c + PF);
+                if (alive) {
+                    compute_chunk(x_base + (xstage & 1) * C::kXStageBytes + (rel % XC) * (NT * 4 * 512), ws, q);
+                }
+                if (more && (rel % XC == XC - 1)) {
+                    stage_commit(xstage + 1);
+                }
             }
         }
-        if (more) {
-            stage_commit(stage + 1);
+        __syncwarp();
+        if (alive && wstage + kWeightStages < num_wstages) {
+            issue_weights(wstage + kWeightStages);
         }
     }
 
@@ -391,7 +444,7 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) nvfp4_gemv_kernel(const Gem
     }
 
     // ---- epilogue ---------------------------------------------------------------------
-    if (!active) {
+    if (!alive) {
         return;
     }
     const int N = p.out_features;
@@ -457,7 +510,7 @@ struct Plan {
 };
 
 // Picks warps per CTA and the K split so that one wave of CTAs covers the SMs evenly.
-Plan choose_plan(int num_tiles, int chunks, int sms) {
+Plan choose_plan(int num_tiles, int chunks, int sms, int max_tiles) {
     Plan best = {1, 1, num_tiles};
     double best_score = -1.0;
     for (int splits = 1; splits <= 8; splits *= 2) {
@@ -469,7 +522,7 @@ Plan choose_plan(int num_tiles, int chunks, int sms) {
             break;
         }
         int tiles_per_cta = (num_tiles + clusters - 1) / clusters;
-        tiles_per_cta = tiles_per_cta < 1 ? 1 : (tiles_per_cta > kMaxWarps ? kMaxWarps : tiles_per_cta);
+        tiles_per_cta = tiles_per_cta < 1 ? 1 : (tiles_per_cta > max_tiles ? max_tiles : tiles_per_cta);
         const int row_groups = (num_tiles + tiles_per_cta - 1) / tiles_per_cta;
         const int ctas = row_groups * splits;
         const int waves = (ctas + sms - 1) / sms;
@@ -479,7 +532,7 @@ Plan choose_plan(int num_tiles, int chunks, int sms) {
         double score = useful / spent;
         // Few warps per SM cannot keep enough loads in flight; a wider split costs a
         // cluster reduction.
-        const double depth = tiles_per_cta >= 8 ? 1.0 : (0.5 + tiles_per_cta / 16.0);
+        const double depth = tiles_per_cta >= max_tiles / 2 ? 1.0 : (0.5 + tiles_per_cta / (1.0 * max_tiles));
         score *= depth;
         score *= 1.0 - 0.015 * (splits == 1 ? 0 : (splits == 2 ? 1 : (splits == 4 ? 2 : 3)));
         if (score > best_score) {
@@ -497,20 +550,28 @@ cudaError_t launch(const GemvParams& base, cudaStream_t stream) {
     GemvParams p = base;
     const int row_blocks = (p.out_features + 127) / 128;
     p.num_tiles = row_blocks * ((SWIGLU || MT == 1) ? 8 : 4);
-    const Plan plan = choose_plan(p.num_tiles, p.in_features / kChunk, sm_count());
+    const Plan plan = choose_plan(p.num_tiles, p.in_features / kChunk, sm_count(), C::kMaxTiles);
     p.tiles_per_cta = plan.tiles_per_cta;
     p.splits = plan.splits;
+    p.status = status_ptr();
+    if (p.status == nullptr) {
+        return cudaErrorInvalidValue;
+    }
 
     static const cudaError_t opted = cudaFuncSetAttribute(
-        nvfp4_gemv_kernel<NT, MT, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes);
+        nvfp4_gemv_kernel<NT, MT, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit);
     if (opted != cudaSuccess) {
         return opted;
     }
+    // The split-K reduction reuses the front of the buffer: kAcc floats per thread.
+    const int reduce_bytes = plan.splits > 1 ? C::kMTiles * NT * 16 * plan.tiles_per_cta * 32 : 0;
+    int smem_bytes = C::kXBytes + plan.tiles_per_cta * C::kWarpBytes;
+    smem_bytes = smem_bytes < reduce_bytes ? reduce_bytes : smem_bytes;
 
     cudaLaunchConfig_t config = {};
     config.gridDim = dim3(plan.ctas);
     config.blockDim = dim3(plan.tiles_per_cta * 32);
-    config.dynamicSmemBytes = C::kSmemBytes;
+    config.dynamicSmemBytes = smem_bytes;
     config.stream = stream;
     cudaLaunchAttribute attribute[1];
     attribute[0].id = cudaLaunchAttributeClusterDimension;

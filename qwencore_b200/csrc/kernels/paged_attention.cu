@@ -86,10 +86,13 @@ __global__ void __launch_bounds__(kThreads, 1) paged_attention_packed_kernel(
     const uint32_t* __restrict__ block_tables, const uint32_t* __restrict__ context_lengths,
     const float* __restrict__ key_scales, const float* __restrict__ value_scales,
     __nv_bfloat16* __restrict__ output, float* __restrict__ partial_stats, __half* __restrict__ partial_out,
-    int max_blocks, int row_base, int page_size, float softmax_scale, int* status) {
+    int max_blocks, int row_base, int page_size, int gate_stride, float softmax_scale, int* status) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
     Smem& sm = *reinterpret_cast<Smem*>(smem_raw);
 
+    if (status_is_set(status)) {
+        return;
+    }
     const int kv_head = blockIdx.x;
     const int row = row_base + blockIdx.y;
     const int part = blockIdx.z;
@@ -331,7 +334,7 @@ __global__ void __launch_bounds__(kThreads, 1) paged_attention_packed_kernel(
         __nv_bfloat16* op = output + (static_cast<size_t>(row) * kQueryHeads + head) * kHeadDim;
         const __nv_bfloat16* gp =
             query_gate_projection
-                ? query_gate_projection + (static_cast<size_t>(row) * kQueryHeads + head) * (2 * kHeadDim) + kHeadDim
+                ? query_gate_projection + static_cast<size_t>(row) * gate_stride + head * (2 * kHeadDim) + kHeadDim
                 : nullptr;
 #pragma unroll
         for (int a = 0; a < 4; ++a) {
@@ -362,7 +365,7 @@ __global__ void __launch_bounds__(kThreads, 1) paged_attention_packed_kernel(
 __global__ void __launch_bounds__(256) reduce_partitions_kernel(
     const float* __restrict__ partial_stats, const __half* __restrict__ partial_out,
     const __nv_bfloat16* __restrict__ query_gate_projection, __nv_bfloat16* __restrict__ output, int pairs,
-    int partitions, int row_base) {
+    int partitions, int row_base, int gate_stride) {
     const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
     const int lane = threadIdx.x & 31;
     if (warp >= pairs) {
@@ -400,7 +403,7 @@ __global__ void __launch_bounds__(256) reduce_partitions_kernel(
     float gates[8] = {1.0f, 1.0f, 1.0f, 1.0f, 1.0f, 1.0f, 1.0f, 1.0f};
     if (query_gate_projection != nullptr) {
         const uint4 graw = *reinterpret_cast<const uint4*>(
-            query_gate_projection + (static_cast<size_t>(row) * kQueryHeads + head) * (2 * kHeadDim) + kHeadDim + 8 * lane);
+            query_gate_projection + static_cast<size_t>(row) * gate_stride + head * (2 * kHeadDim) + kHeadDim + 8 * lane);
         const uint32_t words[4] = {graw.x, graw.y, graw.z, graw.w};
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
@@ -423,7 +426,13 @@ cudaError_t launch_attention(const void* query, const void* query_gate_projectio
                              const void* value_cache, const void* block_tables, const void* context_lengths,
                              const float* key_scales, const float* value_scales, void* output, void* workspace,
                              size_t workspace_bytes, int rows, int row_base, int max_blocks, int page_size,
-                             int partitions, float softmax_scale, cudaStream_t stream) {
+                             int gate_stride, int partitions, float softmax_scale, cudaStream_t stream) {
+    if (gate_stride == 0) {
+        gate_stride = kQueryHeads * 2 * kHeadDim;
+    }
+    if (gate_stride < kQueryHeads * 2 * kHeadDim || gate_stride % 8 != 0) {
+        return cudaErrorInvalidValue;
+    }
     if (query == nullptr || key_cache == nullptr || value_cache == nullptr || block_tables == nullptr ||
         context_lengths == nullptr || output == nullptr || rows <= 0 || rows > kMaxStepRows || row_base < 0 ||
         max_blocks <= 0 || partitions <= 0 || partitions > 65535 || !isfinite(softmax_scale) ||
@@ -452,7 +461,7 @@ cudaError_t launch_attention(const void* query, const void* query_gate_projectio
             static_cast<const uint8_t*>(key_cache), static_cast<const uint8_t*>(value_cache),
             static_cast<const uint32_t*>(block_tables), static_cast<const uint32_t*>(context_lengths), key_scales,
             value_scales, static_cast<__nv_bfloat16*>(output), nullptr, nullptr, max_blocks, row_base, page_size,
-            softmax_scale, status);
+            gate_stride, softmax_scale, status);
         return cudaGetLastError();
     }
     const size_t partials = static_cast<size_t>(rows) * kQueryHeads * partitions;
@@ -467,7 +476,7 @@ cudaError_t launch_attention(const void* query, const void* query_gate_projectio
         static_cast<const uint8_t*>(key_cache), static_cast<const uint8_t*>(value_cache),
         static_cast<const uint32_t*>(block_tables), static_cast<const uint32_t*>(context_lengths), key_scales,
         value_scales, static_cast<__nv_bfloat16*>(output), partial_stats, partial_out, max_blocks, row_base,
-        page_size, softmax_scale, status);
+        page_size, gate_stride, softmax_scale, status);
     const cudaError_t launched = cudaGetLastError();
     if (launched != cudaSuccess) {
         return launched;
@@ -475,7 +484,7 @@ cudaError_t launch_attention(const void* query, const void* query_gate_projectio
     const int pairs = rows * kQueryHeads;
     reduce_partitions_kernel<<<(pairs + 7) / 8, 256, 0, stream>>>(
         partial_stats, partial_out, static_cast<const __nv_bfloat16*>(query_gate_projection),
-        static_cast<__nv_bfloat16*>(output), pairs, partitions, row_base);
+        static_cast<__nv_bfloat16*>(output), pairs, partitions, row_base, gate_stride);
     return cudaGetLastError();
 }
 
@@ -503,7 +512,7 @@ extern "C" int qwc_paged_attention_packed_fp8(const void* query, const void* que
     }
     return qwc::launch_attention(query, query_gate_projection, key_cache, value_cache, block_tables,
                                  context_lengths, nullptr, nullptr, output, workspace, workspace_bytes, rows,
-                                 row_base, max_blocks, qwc::current_shape().kv_page_size, partitions,
+                                 row_base, max_blocks, qwc::current_shape().kv_page_size, 0, partitions,
                                  softmax_scale, stream);
 }
 
@@ -513,8 +522,10 @@ extern "C" int qwc_paged_attention_packed_fp8_scaled(const void* query, const vo
                                                      const float* key_scales, const float* value_scales,
                                                      void* output, void* workspace, size_t workspace_bytes,
                                                      int rows, int row_base, int max_blocks, int page_size,
-                                                     int partitions, float softmax_scale, cudaStream_t stream) {
+                                                     int gate_stride, int partitions, float softmax_scale,
+                                                     cudaStream_t stream) {
     return qwc::launch_attention(query, query_gate_projection, key_cache, value_cache, block_tables,
                                  context_lengths, key_scales, value_scales, output, workspace, workspace_bytes,
-                                 rows, row_base, max_blocks, page_size, partitions, softmax_scale, stream);
+                                 rows, row_base, max_blocks, page_size, gate_stride, partitions, softmax_scale,
+                                 stream);
 }

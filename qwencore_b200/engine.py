@@ -1,0 +1,388 @@
+"""ctypes front-end of `include/qwc_engine.h`: cache manager, scheduler, batch layout, executor.
+
+The classes keep the reference's names and error behaviour (crates/qwc-runtime/src/cache.rs,
+scheduler.rs, layout.rs; crates/qwc-engine/src/executor.rs): a rejected operation raises the
+matching exception with the reference's enum discriminant as `code`.
+"""
+
+from __future__ import annotations
+
+import ctypes
+from ctypes import POINTER, byref, c_char, c_char_p, c_double, c_float, c_int, c_longlong, c_size_t, c_uint32, c_void_p
+
+import numpy as np
+
+from . import abi
+
+lib = abi.lib
+
+REJECTED = {1: "NoStateSlot", 2: "NoKvBlocks", 3: "AlreadyAdmitted", 4: "UnknownSequence", 5: "NothingToRollback"}
+SUBMIT_ERROR = {1: "Duplicate", 2: "EmptyPrompt", 3: "NoOutputTokens", 4: "NoStateCapacity", 5: "ContextTooLong"}
+SCHEDULER_ERROR = {1: "BatchInFlight", 2: "NoBatchInFlight", 3: "SequenceInFlight", 4: "InvalidStopped",
+                   5: "DuplicateStopped", 6: "Invariant", 7: "Cache"}
+LAYOUT_ERROR = {1: "MissingSequence", 2: "DuplicateSequence", 3: "InvalidPrefillRange", 4: "MissingKvBlocks",
+                5: "IntegerOverflow"}
+
+
+class RuntimeError_(Exception):
+    def __init__(self, kind: str, code: int, names: dict):
+        super().__init__(f"{kind}::{names.get(code, code)}")
+        self.kind = kind
+        self.code = code
+        self.name = names.get(code, str(code))
+
+
+class PrefillChunk(ctypes.Structure):
+    _fields_ = [("id", c_uint32), ("offset", c_uint32), ("tokens", c_uint32)]
+
+
+class Completion(ctypes.Structure):
+    _fields_ = [("id", c_uint32), ("generated_tokens", c_uint32), ("reason", c_uint32)]
+
+
+class EngineConfig(ctypes.Structure):
+    _fields_ = [("num_layers", c_int), ("full_attention_interval", c_int), ("hidden", c_int),
+                ("intermediate", c_int), ("vocab", c_int), ("delta_value_heads", c_int), ("kv_page_size", c_int),
+                ("max_batch", c_int), ("max_context", c_int), ("kv_pool_blocks", c_int), ("state_slots", c_int),
+                ("seed", ctypes.c_ulonglong), ("split_rank", c_int), ("split_size", c_int), ("use_graph", c_int),
+                ("attention_partitions", c_int)]
+
+
+class StepTraffic(ctypes.Structure):
+    _fields_ = [("weight_bytes", c_double), ("state_bytes", c_double), ("kv_bytes", c_double),
+                ("gemv_bytes_per_step", c_double), ("gemv_launches_per_step", c_int),
+                ("kernel_launches_per_step", c_int)]
+
+
+class PhaseTime(ctypes.Structure):
+    _fields_ = [("label", c_char * 24), ("milliseconds", c_float), ("launches", c_int)]
+
+
+P = c_void_p
+ENGINE_SYMBOLS = {
+    "qwc_cache_new": (P, [c_size_t, c_size_t, c_size_t]),
+    "qwc_cache_free": (None, [P]),
+    "qwc_cache_admit": (c_int, [P, c_uint32, c_size_t]),
+    "qwc_cache_append_token": (c_int, [P, c_uint32]),
+    "qwc_cache_rollback_token": (c_int, [P, c_uint32]),
+    "qwc_cache_release": (None, [P, c_uint32]),
+    "qwc_cache_sequence": (c_int, [P, c_uint32, POINTER(c_uint32), POINTER(c_size_t), P, c_size_t, POINTER(c_size_t)]),
+    "qwc_cache_free_blocks": (c_size_t, [P]),
+    "qwc_cache_states_in_use": (c_size_t, [P]),
+    "qwc_cache_active": (c_size_t, [P]),
+    "qwc_cache_last_shortage": (None, [P, POINTER(c_size_t), POINTER(c_size_t)]),
+    "qwc_cache_drain_edits": (c_size_t, [P, P, c_size_t]),
+    "qwc_scheduler_new": (P, [c_size_t, c_size_t, c_size_t, c_size_t, c_size_t]),
+    "qwc_scheduler_free": (None, [P]),
+    "qwc_scheduler_submit": (c_int, [P, c_uint32, c_size_t, c_size_t]),
+    "qwc_scheduler_next_batch": (c_int, [P, P, POINTER(c_size_t), P, POINTER(c_size_t)]),
+    "qwc_scheduler_complete_batch": (c_int, [P, P, c_size_t, P, c_size_t, POINTER(c_size_t)]),
+    "qwc_scheduler_abort_batch": (c_int, [P]),
+    "qwc_scheduler_cancel": (c_int, [P, c_uint32, POINTER(c_int)]),
+    "qwc_scheduler_remaining_tokens": (c_longlong, [P, c_uint32]),
+    "qwc_scheduler_waiting": (c_size_t, [P]),
+    "qwc_scheduler_active": (c_size_t, [P]),
+    "qwc_scheduler_committed_kv_blocks": (c_size_t, [P]),
+    "qwc_scheduler_cache": (P, [P]),
+    "qwc_layout_build": (c_int, [P, P, c_size_t, P, c_size_t, P, P, P, P, P, P, P, c_size_t, POINTER(c_uint32)]),
+    "qwc_engine_default_config": (None, [POINTER(EngineConfig)]),
+    "qwc_engine_create": (c_int, [POINTER(EngineConfig), POINTER(P)]),
+    "qwc_engine_destroy": (None, [P]),
+    "qwc_engine_nccl_unique_id": (c_int, [P]),
+    "qwc_engine_init_split": (c_int, [P, P]),
+    "qwc_engine_tensor": (c_int, [P, c_char_p, c_int, POINTER(P), POINTER(c_size_t)]),
+    "qwc_engine_traffic": (None, [P, c_int, c_double, POINTER(StepTraffic)]),
+    "qwc_engine_apply_edits": (c_int, [P, P, c_size_t]),
+    "qwc_engine_decode": (c_int, [P, P, P, P, c_size_t, c_int, P]),
+    "qwc_engine_replay": (c_int, [P, c_int]),
+    "qwc_engine_stream": (P, [P]),
+    "qwc_engine_profile_step": (c_int, [P, c_int, POINTER(PhaseTime), c_int]),
+    "qwc_worker_step": (c_int, [P, P, c_uint32, POINTER(c_size_t), P, c_size_t, POINTER(c_size_t)]),
+}
+for _name, (_restype, _argtypes) in ENGINE_SYMBOLS.items():
+    _function = getattr(lib, _name)
+    _function.restype = _restype
+    _function.argtypes = _argtypes
+
+
+def _u32(values) -> np.ndarray:
+    return np.ascontiguousarray(values, dtype=np.uint32)
+
+
+class CacheManager:
+    """crates/qwc-runtime/src/cache.rs:300-449,571-594"""
+
+    def __init__(self, state_slots: int, kv_blocks: int, block_size: int, _borrowed=None):
+        if _borrowed is not None:
+            self._handle, self._owned = _borrowed, False
+            return
+        if block_size <= 0:
+            raise ValueError("KV block size must be positive")  # cache.rs:124
+        self._handle = lib.qwc_cache_new(state_slots, kv_blocks, block_size)
+        self._owned = True
+
+    def __del__(self):
+        if getattr(self, "_owned", False) and self._handle:
+            lib.qwc_cache_free(self._handle)
+            self._handle = None
+
+    def _check(self, code: int) -> None:
+        if code != 0:
+            raise RuntimeError_("Rejected", code, REJECTED)
+
+    def admit(self, seq_id: int, prompt_tokens: int) -> None:
+        self._check(lib.qwc_cache_admit(self._handle, seq_id, prompt_tokens))
+
+    def append_token(self, seq_id: int) -> None:
+        self._check(lib.qwc_cache_append_token(self._handle, seq_id))
+
+    def rollback_token(self, seq_id: int) -> None:
+        self._check(lib.qwc_cache_rollback_token(self._handle, seq_id))
+
+    def release(self, seq_id: int) -> None:
+        lib.qwc_cache_release(self._handle, seq_id)
+
+    def sequence(self, seq_id: int):
+        slot, tokens, count = c_uint32(), c_size_t(), c_size_t()
+        if lib.qwc_cache_sequence(self._handle, seq_id, byref(slot), byref(tokens), None, 0, byref(count)) != 0:
+            return None
+        blocks = np.zeros(max(1, count.value), dtype=np.uint32)
+        lib.qwc_cache_sequence(self._handle, seq_id, byref(slot), byref(tokens), blocks.ctypes.data_as(P),
+                               blocks.size, byref(count))
+        return {"state_slot": slot.value, "tokens": tokens.value, "blocks": blocks[:count.value].tolist()}
+
+    def free_blocks(self) -> int:
+        return lib.qwc_cache_free_blocks(self._handle)
+
+    def states_in_use(self) -> int:
+        return lib.qwc_cache_states_in_use(self._handle)
+
+    def active(self) -> int:
+        return lib.qwc_cache_active(self._handle)
+
+    def last_shortage(self):
+        need, free = c_size_t(), c_size_t()
+        lib.qwc_cache_last_shortage(self._handle, byref(need), byref(free))
+        return need.value, free.value
+
+    def drain_edits(self, capacity: int = 1 << 16) -> np.ndarray:
+        """Pending device-table edits as u32[n, 4] = (slot, index, value, kind)."""
+        buffer = np.zeros((capacity, 4), dtype=np.uint32)
+        pending = lib.qwc_cache_drain_edits(self._handle, buffer.ctypes.data_as(P), capacity)
+        if pending > capacity:
+            raise OverflowError("edit buffer too small")
+        return buffer[:pending].copy()
+
+
+class Scheduler:
+    """crates/qwc-runtime/src/scheduler.rs:190-668"""
+
+    def __init__(self, max_num_seqs: int, max_num_batched_tokens: int, state_slots: int, kv_blocks: int,
+                 block_size: int = 64):
+        if max_num_seqs <= 0 or max_num_batched_tokens <= 0:
+            raise ValueError("batch limits must be positive")  # scheduler.rs:22-30
+        self._handle = lib.qwc_scheduler_new(max_num_seqs, max_num_batched_tokens, state_slots, kv_blocks, block_size)
+        self.max_num_seqs = max_num_seqs
+        self.cache = CacheManager(0, 0, 1, _borrowed=lib.qwc_scheduler_cache(self._handle))
+
+    def __del__(self):
+        if getattr(self, "_handle", None):
+            lib.qwc_scheduler_free(self._handle)
+            self._handle = None
+
+    def submit(self, seq_id: int, prompt_tokens: int, max_new_tokens: int) -> None:
+        code = lib.qwc_scheduler_submit(self._handle, seq_id, prompt_tokens, max_new_tokens)
+        if code != 0:
+            raise RuntimeError_("SubmitError", code, SUBMIT_ERROR)
+
+    def next_batch(self):
+        decode = np.zeros(self.max_num_seqs, dtype=np.uint32)
+        prefill = (PrefillChunk * self.max_num_seqs)()
+        n_decode, n_prefill = c_size_t(), c_size_t()
+        code = lib.qwc_scheduler_next_batch(self._handle, decode.ctypes.data_as(P), byref(n_decode), prefill,
+                                            byref(n_prefill))
+        if code != 0:
+            raise RuntimeError_("SchedulerError", code, SCHEDULER_ERROR)
+        if n_decode.value == 0 and n_prefill.value == 0:
+            return None
+        return {"decode": decode[:n_decode.value].tolist(),
+                "prefill": [(c.id, c.offset, c.tokens) for c in prefill[:n_prefill.value]]}
+
+    def complete_batch(self, stopped=()):
+        stopped = _u32(list(stopped))
+        done = (Completion * self.max_num_seqs)()
+        count = c_size_t()
+        code = lib.qwc_scheduler_complete_batch(self._handle, stopped.ctypes.data_as(P), stopped.size, done,
+                                                self.max_num_seqs, byref(count))
+        if code != 0:
+            raise RuntimeError_("SchedulerError", code, SCHEDULER_ERROR)
+        return [(c.id, c.generated_tokens, "Stopped" if c.reason else "Length") for c in done[:count.value]]
+
+    def abort_batch(self) -> None:
+        code = lib.qwc_scheduler_abort_batch(self._handle)
+        if code != 0:
+            raise RuntimeError_("SchedulerError", code, SCHEDULER_ERROR)
+
+    def cancel(self, seq_id: int) -> bool:
+        removed = c_int()
+        code = lib.qwc_scheduler_cancel(self._handle, seq_id, byref(removed))
+        if code != 0:
+            raise RuntimeError_("SchedulerError", code, SCHEDULER_ERROR)
+        return bool(removed.value)
+
+    def remaining_tokens(self, seq_id: int):
+        value = lib.qwc_scheduler_remaining_tokens(self._handle, seq_id)
+        return None if value < 0 else value
+
+    def waiting(self) -> int:
+        return lib.qwc_scheduler_waiting(self._handle)
+
+    def active(self) -> int:
+        return lib.qwc_scheduler_active(self._handle)
+
+    def committed_kv_blocks(self) -> int:
+        return lib.qwc_scheduler_committed_kv_blocks(self._handle)
+
+
+def build_layout(cache: CacheManager, decode=(), prefill=(), max_block_ids: int = 1 << 16):
+    """BatchLayout::build (crates/qwc-runtime/src/layout.rs:54-86)."""
+    decode = _u32(list(decode))
+    chunks = (PrefillChunk * max(1, len(prefill)))(*[PrefillChunk(*c) for c in prefill])
+    n = decode.size + len(prefill)
+    out = {name: np.zeros(n + extra, dtype=np.uint32) for name, extra in
+           [("seq_ids", 0), ("state_slots", 0), ("position_starts", 0), ("context_lens", 0), ("token_offsets", 1),
+            ("block_table_offsets", 1)]}
+    block_ids = np.zeros(max_block_ids, dtype=np.uint32)
+    offender = c_uint32()
+    code = lib.qwc_layout_build(cache._handle, decode.ctypes.data_as(P), decode.size, chunks, len(prefill),
+                                *[out[k].ctypes.data_as(P) for k in ("seq_ids", "state_slots", "position_starts",
+                                                                     "context_lens", "token_offsets",
+                                                                     "block_table_offsets")],
+                                block_ids.ctypes.data_as(P), max_block_ids, byref(offender))
+    if code != 0:
+        error = RuntimeError_("LayoutError", code, LAYOUT_ERROR)
+        error.offender = offender.value
+        raise error
+    out["num_decode"] = int(decode.size)
+    out["block_ids"] = block_ids[: int(out["block_table_offsets"][-1])].copy()
+    return {k: (v.tolist() if isinstance(v, np.ndarray) else v) for k, v in out.items()}
+
+
+def default_config(**overrides) -> EngineConfig:
+    config = EngineConfig()
+    lib.qwc_engine_default_config(byref(config))
+    for key, value in overrides.items():
+        if not hasattr(config, key):
+            raise AttributeError(key)
+        setattr(config, key, value)
+    return config
+
+
+class Engine:
+    """The decode executor (crates/qwc-engine/src/executor.rs, decode path)."""
+
+    def __init__(self, config: EngineConfig):
+        self.config = config
+        handle = P()
+        abi.check(lib.qwc_engine_create(byref(config), byref(handle)), "qwc_engine_create")
+        self._handle = handle
+
+    def close(self) -> None:
+        if getattr(self, "_handle", None):
+            lib.qwc_engine_destroy(self._handle)
+            self._handle = None
+
+    def __del__(self):
+        self.close()
+
+    @property
+    def stream(self) -> int:
+        return lib.qwc_engine_stream(self._handle)
+
+    def tensor_ptr(self, name: str, layer: int = 0):
+        pointer, size = P(), c_size_t()
+        if lib.qwc_engine_tensor(self._handle, name.encode(), layer, byref(pointer), byref(size)) != 0:
+            raise KeyError(f"{name}[{layer}]")
+        return pointer.value, size.value
+
+    def read(self, name: str, layer: int = 0, dtype=np.uint8) -> np.ndarray:
+        """Copies a resident tensor to the host (tests only)."""
+        import torch
+
+        pointer, size = self.tensor_ptr(name, layer)
+        out = np.empty(size // np.dtype(dtype).itemsize, dtype=dtype)
+        torch.cuda.synchronize()
+        cudart = torch.cuda.cudart()
+        code = cudart.cudaMemcpy(out.ctypes.data, pointer, size, cudart.cudaMemcpyKind(2))
+        if int(code) != 0:
+            raise abi.QwcError(int(code), "cudaMemcpy D2H")
+        return out
+
+    def write(self, name: str, layer: int, values: np.ndarray) -> None:
+        import torch
+
+        pointer, size = self.tensor_ptr(name, layer)
+        values = np.ascontiguousarray(values)
+        assert values.nbytes == size, (values.nbytes, size)
+        cudart = torch.cuda.cudart()
+        code = cudart.cudaMemcpy(pointer, values.ctypes.data, size, cudart.cudaMemcpyKind(1))
+        if int(code) != 0:
+            raise abi.QwcError(int(code), "cudaMemcpy H2D")
+
+    def traffic(self, rows: int, context_tokens: float) -> StepTraffic:
+        out = StepTraffic()
+        lib.qwc_engine_traffic(self._handle, rows, float(context_tokens), byref(out))
+        return out
+
+    def apply_edits(self, edits: np.ndarray) -> None:
+        edits = np.ascontiguousarray(edits, dtype=np.uint32).reshape(-1, 4)
+        abi.check(lib.qwc_engine_apply_edits(self._handle, edits.ctypes.data_as(P), edits.shape[0]),
+                  "qwc_engine_apply_edits")
+
+    def install_sequence(self, slot: int, tokens: int, blocks) -> None:
+        """Makes `slot` hold a sequence of `tokens` tokens in the given pages (device tables only)."""
+        edits = [(slot, i, int(b), 0) for i, b in enumerate(blocks)] + [(slot, 0, tokens, 1)]
+        self.apply_edits(np.array(edits, dtype=np.uint32))
+
+    def decode(self, row_slots, tokens, edits=None) -> np.ndarray:
+        row_slots, tokens = _u32(row_slots), _u32(tokens)
+        edits = np.zeros((0, 4), np.uint32) if edits is None else np.ascontiguousarray(edits, np.uint32).reshape(-1, 4)
+        sampled = np.zeros(row_slots.size, dtype=np.uint32)
+        abi.check(lib.qwc_engine_decode(self._handle, row_slots.ctypes.data_as(P), tokens.ctypes.data_as(P),
+                                        edits.ctypes.data_as(P), edits.shape[0], row_slots.size,
+                                        sampled.ctypes.data_as(P)), "qwc_engine_decode")
+        return sampled
+
+    def replay(self, rows: int) -> None:
+        abi.check(lib.qwc_engine_replay(self._handle, rows), "qwc_engine_replay")
+
+    def profile_step(self, rows: int):
+        phases = (PhaseTime * 32)()
+        count = lib.qwc_engine_profile_step(self._handle, rows, phases, 32)
+        if count < 0:
+            raise abi.QwcError(-count, "qwc_engine_profile_step")
+        return [(p.label.decode(), p.milliseconds, p.launches) for p in phases[:count]]
+
+    def worker_step(self, scheduler: Scheduler, eos_token: int = 0xFFFFFFFF):
+        decoded, count = c_size_t(), c_size_t()
+        done = (Completion * scheduler.max_num_seqs)()
+        code = lib.qwc_worker_step(self._handle, scheduler._handle, eos_token, byref(decoded), done,
+                                   scheduler.max_num_seqs, byref(count))
+        if code != 0:
+            raise abi.QwcError(code, "qwc_worker_step")
+        return decoded.value, [(c.id, c.generated_tokens, "Stopped" if c.reason else "Length")
+                               for c in done[:count.value]]
+
+    def init_split(self, unique_id: bytes) -> None:
+        buffer = ctypes.create_string_buffer(unique_id, 128)
+        code = lib.qwc_engine_init_split(self._handle, buffer)
+        if code != 0:
+            raise abi.QwcError(code, "qwc_engine_init_split")
+
+
+def nccl_unique_id() -> bytes:
+    buffer = ctypes.create_string_buffer(128)
+    code = lib.qwc_engine_nccl_unique_id(buffer)
+    if code != 0:
+        raise abi.QwcError(code, "qwc_engine_nccl_unique_id")
+    return buffer.raw

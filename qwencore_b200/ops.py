@@ -100,7 +100,7 @@ def packed_partition_count(rows: int, context: int, sms: int = 148) -> int:
 
 def gated_packed(query, query_gate_projection, key_cache, value_cache, block_tables, context_lengths,
                  max_blocks_per_sequence: int, output, rows: int, row_base: int, partitions: int, workspace,
-                 page_size: int, key_scales=None, value_scales=None) -> None:
+                 page_size: int, key_scales=None, value_scales=None, gate_stride: int = 0) -> None:
     """crates/qwc-cuda/src/paged_attention.rs:373-421 (PackedShape::Rows)."""
     end = row_base + rows
     assert query.numel() >= end * NUM_ATTN_HEADS * ATTN_HEAD_DIM
@@ -110,7 +110,7 @@ def gated_packed(query, query_gate_projection, key_cache, value_cache, block_tab
     abi.check(abi.lib.qwc_paged_attention_packed_fp8_scaled(
         _p(query), _p(query_gate_projection), _p(key_cache), _p(value_cache), _p(block_tables), _p(context_lengths),
         _p(key_scales), _p(value_scales), _p(output), _p(workspace), workspace_bytes, rows, row_base,
-        max_blocks_per_sequence, page_size, partitions, 1.0 / math.sqrt(ATTN_HEAD_DIM), _stream()),
+        max_blocks_per_sequence, page_size, gate_stride, partitions, 1.0 / math.sqrt(ATTN_HEAD_DIM), _stream()),
         "qwc_paged_attention_packed_fp8_scaled")
 
 

@@ -33,13 +33,19 @@ def u32_out(torch, *shape, fill=0):
     return dev(torch, np.full(shape, fill, dtype=np.uint32))
 
 
-def assert_rms_close(got, want, what, bound=RMS_BOUND):
+def assert_rms_close(got, want, what, bound=RMS_BOUND, bf16_grid=True):
+    """max|got - want| <= bound * RMS(want).  A bf16 output cannot meet that bound by itself
+    beyond 2.6 RMS (its grid step there exceeds 1e-2 RMS), so for bf16 outputs one grid step
+    of the expected value (at most 2^-7 relative) is allowed on top."""
     got = np.asarray(got, dtype=np.float64)
     want = np.asarray(want, dtype=np.float64)
     rms = np.sqrt(np.mean(want ** 2))
-    err = np.max(np.abs(got - want))
     assert np.isfinite(got).all(), f"{what}: non-finite output"
-    assert err <= bound * rms, f"{what}: max abs err {err:.4g} > {bound} * rms {rms:.4g}"
+    allowed = bound * rms + (2.0 ** -7 * np.abs(want) if bf16_grid else 0.0)
+    excess = np.abs(got - want) - allowed
+    worst = np.unravel_index(np.argmax(excess), excess.shape)
+    assert excess[worst] <= 0, (f"{what}: |{got[worst]:.6g} - {want[worst]:.6g}| exceeds {bound} * rms "
+                                f"{rms:.4g} at {worst}")
 
 
 @pytest.fixture(scope="module")
@@ -394,7 +400,7 @@ def test_fp8_lm_head_and_argmax(cuda, ops, batch):
     ops.argmax(logits, pv, pi, tokens, vocab, batch, parts)
     torch.cuda.synchronize()
     got = host(logits)
-    assert_rms_close(got, want, "lm_head")
+    assert_rms_close(got, want, "lm_head", bf16_grid=False)
     # argmax of the GPU logits is exact; against the oracle logits it agrees wherever the top-2 gap is clear
     assert np.array_equal(host(tokens), oracle.argmax(got, vocab, batch))
     ordered = np.sort(want, axis=1)
