@@ -147,6 +147,10 @@ int qwc_engine_init_split(qwc_engine* engine, const void* unique_id_128);
  * caches back.  Layer-indexed names take the layer number; others ignore it.  Returns 0 or 1. */
 int qwc_engine_tensor(qwc_engine* engine, const char* name, int layer, void** device_ptr, size_t* bytes);
 
+/* Synchronous copies of a named tensor to / from host memory (`bytes` must equal its size). */
+int qwc_engine_read(qwc_engine* engine, const char* name, int layer, void* host, size_t bytes);
+int qwc_engine_write(qwc_engine* engine, const char* name, int layer, const void* host, size_t bytes);
+
 /* Bytes the decode step must move for `rows` rows with the given total context tokens:
  * weights, DeltaNet state read+write, KV read.  The roofline numerator. */
 typedef struct qwc_step_traffic {

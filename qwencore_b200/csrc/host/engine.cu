@@ -835,6 +835,26 @@ int qwc_engine_tensor(qwc_engine* e, const char* name, int layer, void** device_
     return 1;
 }
 
+int qwc_engine_read(qwc_engine* e, const char* name, int layer, void* host, size_t bytes) {
+    void* device = nullptr;
+    size_t size = 0;
+    if (host == nullptr || qwc_engine_tensor(e, name, layer, &device, &size) != 0 || size != bytes) {
+        return cudaErrorInvalidValue;
+    }
+    QWC_TRY(cudaStreamSynchronize(e->stream));
+    return cudaMemcpy(host, device, bytes, cudaMemcpyDeviceToHost);
+}
+
+int qwc_engine_write(qwc_engine* e, const char* name, int layer, const void* host, size_t bytes) {
+    void* device = nullptr;
+    size_t size = 0;
+    if (host == nullptr || qwc_engine_tensor(e, name, layer, &device, &size) != 0 || size != bytes) {
+        return cudaErrorInvalidValue;
+    }
+    QWC_TRY(cudaStreamSynchronize(e->stream));
+    return cudaMemcpy(device, host, bytes, cudaMemcpyHostToDevice);
+}
+
 void qwc_engine_traffic(const qwc_engine* e, int rows, double context_tokens, qwc_step_traffic* out) {
     std::memset(out, 0, sizeof(*out));
     int gemv = 0, kernels = 2 /*pack*/ + 1 /*embed*/ + 1 /*norm*/ + 1 /*lm_head*/ + 2 /*argmax*/;

@@ -91,6 +91,8 @@ ENGINE_SYMBOLS = {
     "qwc_engine_nccl_unique_id": (c_int, [P]),
     "qwc_engine_init_split": (c_int, [P, P]),
     "qwc_engine_tensor": (c_int, [P, c_char_p, c_int, POINTER(P), POINTER(c_size_t)]),
+    "qwc_engine_read": (c_int, [P, c_char_p, c_int, P, c_size_t]),
+    "qwc_engine_write": (c_int, [P, c_char_p, c_int, P, c_size_t]),
     "qwc_engine_traffic": (None, [P, c_int, c_double, POINTER(StepTraffic)]),
     "qwc_engine_apply_edits": (c_int, [P, P, c_size_t]),
     "qwc_engine_decode": (c_int, [P, P, P, P, c_size_t, c_int, P]),
@@ -307,27 +309,16 @@ class Engine:
 
     def read(self, name: str, layer: int = 0, dtype=np.uint8) -> np.ndarray:
         """Copies a resident tensor to the host (tests only)."""
-        import torch
-
-        pointer, size = self.tensor_ptr(name, layer)
+        _, size = self.tensor_ptr(name, layer)
         out = np.empty(size // np.dtype(dtype).itemsize, dtype=dtype)
-        torch.cuda.synchronize()
-        cudart = torch.cuda.cudart()
-        code = cudart.cudaMemcpy(out.ctypes.data, pointer, size, cudart.cudaMemcpyKind(2))
-        if int(code) != 0:
-            raise abi.QwcError(int(code), "cudaMemcpy D2H")
+        abi.check(lib.qwc_engine_read(self._handle, name.encode(), layer, out.ctypes.data_as(P), size),
+                  "qwc_engine_read")
         return out
 
     def write(self, name: str, layer: int, values: np.ndarray) -> None:
-        import torch
-
-        pointer, size = self.tensor_ptr(name, layer)
         values = np.ascontiguousarray(values)
-        assert values.nbytes == size, (values.nbytes, size)
-        cudart = torch.cuda.cudart()
-        code = cudart.cudaMemcpy(pointer, values.ctypes.data, size, cudart.cudaMemcpyKind(1))
-        if int(code) != 0:
-            raise abi.QwcError(int(code), "cudaMemcpy H2D")
+        abi.check(lib.qwc_engine_write(self._handle, name.encode(), layer, values.ctypes.data_as(P), values.nbytes),
+                  "qwc_engine_write")
 
     def traffic(self, rows: int, context_tokens: float) -> StepTraffic:
         out = StepTraffic()
