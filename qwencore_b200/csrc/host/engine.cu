@@ -857,7 +857,7 @@ int qwc_engine_write(qwc_engine* e, const char* name, int layer, const void* hos
 
 void qwc_engine_traffic(const qwc_engine* e, int rows, double context_tokens, qwc_step_traffic* out) {
     std::memset(out, 0, sizeof(*out));
-    int gemv = 0, kernels = 2 /*pack*/ + 1 /*embed*/ + 1 /*norm*/ + 1 /*lm_head*/ + 2 /*argmax*/;
+    int gemv = 0, kernels = 3 /*table edits + pack*/ + 1 /*embed*/ + 1 /*norm*/ + 1 /*lm_head*/ + 2 /*argmax*/;
     double gemv_bytes = 0.0;
     for (const Layer& l : e->layers) {
         gemv_bytes += static_cast<double>(l.gate.weight_bytes() + l.up.weight_bytes() + l.down.weight_bytes());
