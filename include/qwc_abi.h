@@ -116,6 +116,35 @@ int qwc_paged_attention_packed_fp8_scaled(const void* query, const void* query_g
                                           int gate_stride, int partitions, float softmax_scale,
                                           qwc_stream stream);
 
+/*
+ * Packed attention for callers that cannot allocate device memory.  No counterpart in the
+ * reference, whose wrappers always own a workspace buffer.
+ *
+ * Same arithmetic and arguments as qwc_paged_attention_packed_fp8_scaled, without the workspace
+ * pair: the split-context partials go to a scratch array built into the library (6 389 760 bytes
+ * of device memory per GPU that loads it, held until the process exits).  Intended for a caller
+ * that gave its whole memory budget away at start-up, a language binding with no allocator of
+ * its own, or a tool attached to a running server.  The call itself performs no cudaMalloc,
+ * cudaFree or other allocating call.
+ *
+ * Limit: rows * partitions <= qwc_paged_attention_packed_noalloc_max_pairs() (512); anything
+ * larger is refused with cudaErrorInvalidValue before a launch.  The first call on a device
+ * looks the scratch address up (cudaGetSymbolAddress with that device current) and should
+ * therefore be made before any stream capture begins.  All calls share the one array: it keeps
+ * whatever the previous call left (every slot a call reads it has written first, so nothing has
+ * to be cleared), and two calls whose kernels overlap on the GPU - different streams, or
+ * different host threads - race on it.  Callers that need concurrency pass their own workspace
+ * to the _scaled entry point instead.
+ */
+int qwc_paged_attention_packed_fp8_noalloc(const void* query, const void* query_gate_projection,
+                                           const void* key_cache, const void* value_cache,
+                                           const void* block_tables, const void* context_lengths,
+                                           const float* key_scales, const float* value_scales,
+                                           void* output, int rows, int row_base, int max_blocks,
+                                           int page_size, int gate_stride, int partitions,
+                                           float softmax_scale, qwc_stream stream);
+int qwc_paged_attention_packed_noalloc_max_pairs(void);
+
 /* Host helper: bytes of split-context workspace for (rows, partitions). */
 size_t qwc_paged_attention_packed_workspace_bytes(int rows, int partitions);
 

@@ -49,6 +49,9 @@ KERNEL_SYMBOLS = {
     "qwc_paged_attention_packed_fp8_scaled": (c_int, [P, P, P, P, P, P, P, P, P, P, c_size_t, c_int, c_int,
                                                       c_int, c_int, c_int, c_int, c_float, P]),
     "qwc_paged_attention_packed_workspace_bytes": (c_size_t, [c_int, c_int]),
+    "qwc_paged_attention_packed_fp8_noalloc": (c_int, [P, P, P, P, P, P, P, P, P, c_int, c_int, c_int, c_int, c_int,
+                                                       c_int, c_float, P]),
+    "qwc_paged_attention_packed_noalloc_max_pairs": (c_int, []),
     "qwc_delta_decode_int8": (c_int, [P, P, P, P, P, P, P, P, P, P, c_int, c_int, P]),
     "qwc_delta_prepare_decode": (c_int, [P] * 14 + [c_int, c_int, c_int, c_int, P]),
     "qwc_delta_gated_rmsnorm": (c_int, [P, P, P, P, c_int, c_float, c_int, P]),

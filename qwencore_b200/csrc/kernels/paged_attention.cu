@@ -488,6 +488,45 @@ cudaError_t launch_attention(const void* query, const void* query_gate_projectio
     return cudaGetLastError();
 }
 
+// ---- built-in scratch for callers that cannot allocate ------------------------------------
+//
+// Split-context partials normally live in a workspace the caller allocates.  Some callers have
+// no way to do that: a process that handed its whole VRAM budget out at start-up and refuses
+// any later cudaMalloc (the reference engine enforces such a ceiling), a thin foreign-language
+// binding that can pass pointers it was given but owns no device allocator, or a diagnostic
+// attached to a running server.  For them the library carries its own scratch: a fixed array
+// in device memory, sized for kStaticPartialPairs (row, partition) pairs.  It exists once per
+// GPU that loads the library and stays resident until the process exits.
+constexpr int kStaticPartialPairs = 512;  // rows * partitions, e.g. 32 rows x 16 partitions
+constexpr size_t kStaticScratchBytes = static_cast<size_t>(kStaticPartialPairs) * kQueryHeads * kPartialBytes;
+static __device__ __align__(256) unsigned char g_static_partials[kStaticScratchBytes];
+
+// Device address of the array above for the current device.  In host code the symbol's name is
+// only a handle, never an address a kernel may be given, so the address is asked of the runtime
+// once per device (with that device current) and remembered.
+cudaError_t static_partials_address(void** out) {
+    constexpr int kMaxDevices = 64;
+    static void* cached[kMaxDevices] = {};
+    int device = 0;
+    cudaError_t err = cudaGetDevice(&device);
+    if (err != cudaSuccess) {
+        return err;
+    }
+    if (device < 0 || device >= kMaxDevices) {
+        return cudaErrorInvalidDevice;
+    }
+    if (cached[device] == nullptr) {
+        void* address = nullptr;
+        err = cudaGetSymbolAddress(&address, g_static_partials);
+        if (err != cudaSuccess) {
+            return err;
+        }
+        cached[device] = address;
+    }
+    *out = cached[device];
+    return cudaSuccess;
+}
+
 }  // namespace
 }  // namespace qwc
 
@@ -529,3 +568,33 @@ extern "C" int qwc_paged_attention_packed_fp8_scaled(const void* query, const vo
                                  rows, row_base, max_blocks, page_size, gate_stride, partitions, softmax_scale,
                                  stream);
 }
+
+extern "C" int qwc_paged_attention_packed_fp8_noalloc(const void* query, const void* query_gate_projection,
+                                                      const void* key_cache, const void* value_cache,
+                                                      const void* block_tables, const void* context_lengths,
+                                                      const float* key_scales, const float* value_scales,
+                                                      void* output, int rows, int row_base, int max_blocks,
+                                                      int page_size, int gate_stride, int partitions,
+                                                      float softmax_scale, cudaStream_t stream) {
+    if (rows <= 0 || partitions <= 0) {
+        return cudaErrorInvalidValue;
+    }
+    // The built-in scratch holds kStaticPartialPairs (row, partition) pairs and not one more.
+    if (static_cast<long long>(rows) * partitions > qwc::kStaticPartialPairs) {
+        return cudaErrorInvalidValue;
+    }
+    void* scratch = nullptr;
+    const cudaError_t resolved = qwc::static_partials_address(&scratch);
+    if (resolved != cudaSuccess) {
+        return resolved;
+    }
+    // Every partial slot of this call is written by the CTA that owns it (an empty partition
+    // stores sum = 0, which the merge skips), so nothing left over from an earlier call is read
+    // and nothing needs clearing first.
+    return qwc::launch_attention(query, query_gate_projection, key_cache, value_cache, block_tables,
+                                 context_lengths, key_scales, value_scales, output, scratch,
+                                 qwc::kStaticScratchBytes, rows, row_base, max_blocks, page_size, gate_stride,
+                                 partitions, softmax_scale, stream);
+}
+
+extern "C" int qwc_paged_attention_packed_noalloc_max_pairs(void) { return qwc::kStaticPartialPairs; }

@@ -114,6 +114,20 @@ def gated_packed(query, query_gate_projection, key_cache, value_cache, block_tab
         "qwc_paged_attention_packed_fp8_scaled")
 
 
+def gated_packed_noalloc(query, query_gate_projection, key_cache, value_cache, block_tables, context_lengths,
+                         max_blocks_per_sequence: int, output, rows: int, row_base: int, partitions: int,
+                         page_size: int, key_scales=None, value_scales=None, gate_stride: int = 0) -> None:
+    """Packed attention on the library's built-in scratch, for callers that cannot allocate a workspace.
+
+    rows * partitions must not exceed `qwc_paged_attention_packed_noalloc_max_pairs()`; calls share
+    the scratch, so overlapping calls on different streams race.  Make the first call on a device
+    outside any stream capture."""
+    abi.check(abi.lib.qwc_paged_attention_packed_fp8_noalloc(
+        _p(query), _p(query_gate_projection), _p(key_cache), _p(value_cache), _p(block_tables), _p(context_lengths),
+        _p(key_scales), _p(value_scales), _p(output), rows, row_base, max_blocks_per_sequence, page_size, gate_stride,
+        partitions, 1.0 / math.sqrt(ATTN_HEAD_DIM), _stream()), "qwc_paged_attention_packed_fp8_noalloc")
+
+
 def gated_packed_legacy(query, query_gate_projection, key_cache, value_cache, block_tables, context_lengths,
                         max_blocks_per_sequence: int, output, rows: int, row_base: int, partitions: int,
                         workspace, tile_size: int = GQA_GROUP) -> None:
