@@ -40,6 +40,12 @@
 namespace cg = cooperative_groups;
 
 namespace qwc {
+
+// tcgen05 path for 9..32 rows (nvfp4_umma.cu).
+cudaError_t launch_nvfp4_umma(const void* packed0, const void* scales0, const void* packed1, const void* scales1,
+                              const void* x, void* y, int out_features, int in_features, int batch, float inverse0,
+                              float inverse1, bool swiglu, cudaStream_t stream);
+
 namespace {
 
 constexpr int kChunk = 128;   // K elements per chunk: 64 bytes of nibbles (128 of e4m3) per row
@@ -510,22 +516,24 @@ struct Plan {
 };
 
 // Picks warps per CTA and the K split so that one wave of CTAs covers the SMs evenly.
-Plan choose_plan(int num_tiles, int chunks, int sms, int max_tiles) {
+// `resident_clusters[i]` is how many clusters of 1 << i CTAs the device holds at once: a cluster
+// must sit inside one GPC, so this is less than sms / size for sizes that do not divide a GPC.
+Plan choose_plan(int num_tiles, int chunks, int sms, int max_tiles, const int (&resident_clusters)[4]) {
     Plan best = {1, 1, num_tiles};
     double best_score = -1.0;
-    for (int splits = 1; splits <= 8; splits *= 2) {
+    for (int splits = 1, index = 0; splits <= 8; splits *= 2, ++index) {
         if (chunks / splits < 4 && splits > 1) {
             break;
         }
-        const int clusters = sms / splits;
-        if (clusters == 0) {
-            break;
+        const int clusters = splits == 1 ? sms : resident_clusters[index];
+        if (clusters <= 0) {
+            continue;
         }
         int tiles_per_cta = (num_tiles + clusters - 1) / clusters;
         tiles_per_cta = tiles_per_cta < 1 ? 1 : (tiles_per_cta > max_tiles ? max_tiles : tiles_per_cta);
         const int row_groups = (num_tiles + tiles_per_cta - 1) / tiles_per_cta;
         const int ctas = row_groups * splits;
-        const int waves = (ctas + sms - 1) / sms;
+        const int waves = (row_groups + clusters - 1) / clusters;
         const int slice = (chunks + splits - 1) / splits;
         const double useful = static_cast<double>(num_tiles) * chunks;
         const double spent = static_cast<double>(waves) * sms * tiles_per_cta * slice;
@@ -550,7 +558,40 @@ cudaError_t launch(const GemvParams& base, cudaStream_t stream) {
     GemvParams p = base;
     const int row_blocks = (p.out_features + 127) / 128;
     p.num_tiles = row_blocks * ((SWIGLU || MT == 1) ? 8 : 4);
-    const Plan plan = choose_plan(p.num_tiles, p.in_features / kChunk, sm_count(), C::kMaxTiles);
+    static const cudaError_t opted = cudaFuncSetAttribute(
+        nvfp4_gemv_kernel<NT, MT, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit);
+    if (opted != cudaSuccess) {
+        return opted;
+    }
+    // Resident clusters of 1, 2, 4 and 8 full-size CTAs, asked of the driver once.
+    struct Residency {
+        int clusters[4];
+    };
+    static const Residency residency = []() {
+        Residency r = {};
+        for (int index = 0; index < 4; ++index) {
+            cudaLaunchConfig_t probe = {};
+            probe.gridDim = dim3((1 << index) * 64);
+            probe.blockDim = dim3(C::kMaxTiles * 32);
+            probe.dynamicSmemBytes = C::kXBytes + C::kMaxTiles * C::kWarpBytes;
+            cudaLaunchAttribute attribute[1];
+            attribute[0].id = cudaLaunchAttributeClusterDimension;
+            attribute[0].val.clusterDim.x = 1 << index;
+            attribute[0].val.clusterDim.y = 1;
+            attribute[0].val.clusterDim.z = 1;
+            probe.attrs = attribute;
+            probe.numAttrs = 1;
+            int clusters = 0;
+            if (cudaOccupancyMaxActiveClusters(&clusters, nvfp4_gemv_kernel<NT, MT, MODE>, &probe) != cudaSuccess) {
+                clusters = 0;
+                (void)cudaGetLastError();
+            }
+            r.clusters[index] = clusters;
+        }
+        return r;
+    }();
+    const Plan plan =
+        choose_plan(p.num_tiles, p.in_features / kChunk, sm_count(), C::kMaxTiles, residency.clusters);
     p.tiles_per_cta = plan.tiles_per_cta;
     p.splits = plan.splits;
     p.status = status_ptr();
@@ -558,11 +599,6 @@ cudaError_t launch(const GemvParams& base, cudaStream_t stream) {
         return cudaErrorInvalidValue;
     }
 
-    static const cudaError_t opted = cudaFuncSetAttribute(
-        nvfp4_gemv_kernel<NT, MT, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit);
-    if (opted != cudaSuccess) {
-        return opted;
-    }
     // The split-K reduction reuses the front of the buffer: kAcc floats per thread.
     const int reduce_bytes = plan.splits > 1 ? C::kMTiles * NT * 16 * plan.tiles_per_cta * 32 : 0;
     int smem_bytes = C::kXBytes + plan.tiles_per_cta * C::kWarpBytes;
@@ -589,6 +625,12 @@ cudaError_t dispatch(const GemvParams& p, cudaStream_t stream) {
     const bool wide = MODE == kNvfp4 && wide_tiles >= 2 * sm_count();
     if (p.batch <= 8) {
         return launch<1, 1, MODE>(p, stream);
+    }
+    if (MODE != kFp8Rows) {
+        // Above eight rows the legacy tensor path cannot keep up with the weight stream.
+        return launch_nvfp4_umma(p.packed[0], p.scales[0], p.packed[1], p.scales[1], p.x, p.y, p.out_features,
+                                 p.in_features, p.batch, p.inverse_scale[0], p.inverse_scale[1],
+                                 MODE == kNvfp4Swiglu, stream);
     }
     if (p.batch <= 16) {
         return wide ? launch<2, 2, MODE>(p, stream) : launch<2, 1, MODE>(p, stream);

@@ -1,0 +1,757 @@
+// NVFP4 W4A16 skinny GEMM for 9..32 activation rows on the 5th-generation tensor cores.
+//
+// Same contract as nvfp4_gemv.cu (crates/qwc-cuda/cuda/nvfp4.cu:489-537, :585-643); this file
+// serves the batches where the legacy mma.sync path runs out of tensor throughput: a profile of
+// that kernel shows its HMMA pipe at 15 % for 8 rows at 40 % of HBM bandwidth, i.e. above 100 %
+// for 32 rows at full bandwidth.  Here the product runs as tcgen05.mma (M = 128 weight rows,
+// N = 16 or 32 activation rows, K = 16 per instruction, f16 inputs, fp32 accumulators in TMEM).
+//
+// One CTA per SM works on two 128-row tiles (plain GEMV: 256 consecutive rows; SwiGLU: the gate
+// rows and the up rows of the same 128 outputs) and a K slice; K slices of one row group form a
+// thread-block cluster and are reduced through distributed shared memory.  K is walked in stages
+// of 256 elements (two 128-element chunks), each CTA starting at a different stage.
+//
+//   warps 0-15  dequantise.  Thread = one weight row = one TMEM lane; warps 0-7 take the even
+//               chunks, warps 8-15 the odd ones.  A thread reads 64 bytes of its row per chunk
+//               from the shared-memory ring, widens e2m1 pairs with the hardware converter,
+//               multiplies by the e4m3 block scale in f16 (exact) and writes the 128 scaled
+//               weights as the A operand into one of three TMEM buffers with tcgen05.st.
+//   warp 16     producer: per stage one tiled TMA copy per tile (a box of 128 rows x 128 bytes,
+//               128-byte swizzle, so that the row-per-thread reads above are free of bank
+//               conflicts) and one bulk copy of the swizzled scale tiles (contiguous over K for a
+//               128-row block), into a three-stage ring.  One instruction moves 16 KiB: a copy
+//               per weight row is limited by the copy issue rate, not by HBM.
+//   warps 17-18 issue tcgen05.mma, one warp per tile: A from TMEM, B (activations, K-major core
+//               matrices) from shared memory, and tcgen05.commit to hand buffers back.  The
+//               instructions sit in an elect.sync region: issued from `lane == 0` they cost three
+//               times as many cycles each.
+//   warps 19-22 convert the activation rows bf16 -> f16 into the B layout; warp w owns operand
+//               stage w and every fourth chunk, and stages the bf16 rows with cp.async two of its
+//               chunks ahead.
+//
+// Every wait is bounded; a wait that gives up records a code in the status word, the CTA skips
+// its stores, frees its TMEM and returns.
+
+#include <cooperative_groups.h>
+#include <cuda.h>
+
+#include "common.cuh"
+
+namespace cg = cooperative_groups;
+
+namespace qwc {
+namespace {
+
+constexpr int kChunkK = 128;                  // K elements per chunk
+constexpr int kStageChunks = 2;               // chunks per weight stage: 128 bytes of nibbles per row
+constexpr int kBoxRowBytes = 128;
+constexpr int kTileRows = 128;
+constexpr int kTiles = 2;
+constexpr int kBoxBytes = kTileRows * kBoxRowBytes;       // 16 KiB, multiple of the 1 KiB swizzle period
+constexpr int kScaleStageBytes = kStageChunks * 2 * 512;  // scale tiles of 512 bytes per 128-row block and 64 K
+constexpr int kTileStageBytes = kBoxBytes + kScaleStageBytes;
+constexpr int kWeightStages = 3;
+constexpr int kXStages = 4;
+constexpr int kRawBuffers = 2;  // bf16 chunks in flight per converting warp (cp.async), besides the one in work
+constexpr int kABuffers = 3;
+constexpr int kRowWarps = 8;                     // one thread per weight row of the two tiles
+constexpr int kDequantSets = 2;                  // set s dequantises the chunks with index = s (mod 2)
+constexpr int kDequantWarps = kRowWarps * kDequantSets;
+constexpr int kProducerWarp = kDequantWarps;
+constexpr int kMmaWarp = kDequantWarps + 1;
+static_assert(kDequantSets == kStageChunks, "each dequantising warp reads one chunk of every stage");
+constexpr int kConvertWarps = 4;
+constexpr int kMmaWarps = 2;  // one issuing warp per tile
+constexpr int kFirstConvertWarp = kMmaWarp + kMmaWarps;
+constexpr int kThreads = (kDequantWarps + 1 + kMmaWarps + kConvertWarps) * 32;
+constexpr int kTmemColumns = 512;
+constexpr int kAccumulatorColumn = kABuffers * 64;
+constexpr int kAccumulators = 1;  // independent accumulation chains per tile, summed in the epilogue
+constexpr int kTileColumns = kAccumulatorColumn + 32 * kAccumulators;  // three 64-column A buffers + the accumulators
+static_assert(kTiles * kTileColumns <= kTmemColumns, "tensor memory budget");
+static_assert(kTileStageBytes % 1024 == 0, "swizzled boxes start on 1 KiB boundaries");
+
+struct UmmaParams {
+    const uint8_t* packed[2];
+    const uint8_t* scales[2];
+    const __nv_bfloat16* x;
+    __nv_bfloat16* y;
+    float inverse_scale[2];
+    int out_features;
+    int in_features;
+    int batch;
+    int n_pad;       // 16 or 32
+    int swiglu;
+    int row_groups;  // 128-row (swiglu) or 256-row groups
+    int splits;
+    int* status;
+};
+
+
+struct Barriers {
+    uint64_t w_full[kWeightStages];
+    uint64_t w_empty[kWeightStages];
+    uint64_t a_ready[kTiles][kABuffers];
+    uint64_t a_free[kTiles][kABuffers];
+    uint64_t x_full[kXStages];
+    uint64_t x_free[kXStages];
+    uint64_t d_ready;
+    uint32_t tmem_base;
+    int failed;
+};
+
+__device__ __forceinline__ bool wait_or_fail(uint64_t* bar, uint32_t parity, Barriers* b, int* status) {
+    if (mbar_try_wait(bar, parity)) {
+        return true;
+    }
+    const long long start = clock64();
+    for (;;) {
+#pragma unroll 1
+        for (int spin = 0; spin < 64; ++spin) {
+            if (mbar_try_wait(bar, parity)) {
+                return true;
+            }
+        }
+        if (*reinterpret_cast<volatile int*>(&b->failed) != 0) {
+            return false;
+        }
+        if (clock64() - start > 40000000ll) {
+            break;
+        }
+    }
+    atomicCAS(status, 0, kStatusGemvWait);
+    *reinterpret_cast<volatile int*>(&b->failed) = 1;
+    return false;
+}
+
+// True in exactly one lane of a converged warp.  The compiler keeps the operands of what that lane
+// issues in uniform registers; `lane == 0` instead costs a register move per operand per instruction.
+__device__ __forceinline__ bool elect_one() {
+    uint32_t elected;
+    asm volatile("{\n.reg .pred p;\nelect.sync _|p, 0xffffffff;\nselp.u32 %0, 1, 0, p;\n}\n" : "=r"(elected));
+    return elected != 0;
+}
+
+__device__ __forceinline__ uint64_t smem_descriptor(uint32_t address, uint32_t leading_bytes, uint32_t stride_bytes) {
+    // K-major, no swizzle: start address, leading (K) and stride (N) byte offsets in 16-byte units, version 1.
+    const uint64_t lo = ((address >> 4) & 0x3FFFu) | (static_cast<uint64_t>((leading_bytes >> 4) & 0x3FFFu) << 16);
+    const uint64_t hi = ((stride_bytes >> 4) & 0x3FFFu) | (1u << 14);
+    return lo | (hi << 32);
+}
+
+__device__ __forceinline__ void umma_f16(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc,
+                                         uint32_t accumulate) {
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "setp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n"
+        "}\n" ::"r"(d_tmem),
+        "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
+                 : "memory");
+}
+
+__device__ __forceinline__ void tma_box_g2s(void* smem_dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(
+            smem_u32(smem_dst)),
+        "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(smem_u32(bar))
+        : "memory");
+}
+
+__device__ __forceinline__ void tmem_store16(uint32_t taddr, const uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};" ::"r"(
+            taddr),
+        "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
+        "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+        : "memory");
+}
+
+__device__ __forceinline__ void tmem_load32(uint32_t taddr, float (&v)[32]) {
+    uint32_t r[32];
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,"
+        "%29,%30,%31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr)
+        : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 32; ++i) {
+        v[i] = __uint_as_float(r[i]);
+    }
+}
+
+__global__ void __launch_bounds__(kThreads, 1)
+    nvfp4_umma_kernel(const __grid_constant__ CUtensorMap map0, const __grid_constant__ CUtensorMap map1,
+                      const UmmaParams p) {
+    extern __shared__ unsigned char smem_raw[];
+    __shared__ Barriers bars;
+    // 128-byte-swizzled boxes need a 1 KiB-aligned shared address.
+    unsigned char* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const int row_group = blockIdx.x / p.splits;
+    const int split = blockIdx.x - row_group * p.splits;
+    const int K = p.in_features;
+    // K is cut into stages of 256 elements; a slice is a whole number of stages.  Each CTA walks its
+    // slice from a different starting stage and wraps around: CTAs that all read the same activation
+    // chunk at the same moment queue on the few L2 slices that hold it.
+    const int stages_in_k = K / (kChunkK * kStageChunks);
+    const int s_begin = static_cast<int>(static_cast<long long>(stages_in_k) * split / p.splits);
+    const int s_end = static_cast<int>(static_cast<long long>(stages_in_k) * (split + 1) / p.splits);
+    const int num_wstages = s_end - s_begin;
+    const int total_chunks = num_wstages * kStageChunks;
+    const int first_stage = num_wstages > 0 ? (row_group * 7 + split) % num_wstages : 0;
+    const int group_blocks = K / 64;
+    const int n_pad = p.n_pad;
+    const int x_stage_bytes = n_pad * kChunkK * 2;
+
+    unsigned char* weight_ring = smem;                                                   // [stage][tile][box | scales]
+    unsigned char* x_ring = smem + kWeightStages * kTiles * kTileStageBytes;             // [xstage][...]
+    unsigned char* raw_ring = x_ring + kXStages * 32 * kChunkK * 2;                      // [warp][buffer][unit][16]
+
+    // First row of each tile and the matrix it comes from.
+    int tile_row0[kTiles];
+    const uint8_t* tile_scales[kTiles];
+#pragma unroll
+    for (int t = 0; t < kTiles; ++t) {
+        tile_row0[t] = p.swiglu ? row_group * kTileRows : (row_group * kTiles + t) * kTileRows;
+        tile_scales[t] = p.scales[t];  // the launcher repeats matrix 0 when there is no second one
+    }
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < kWeightStages; ++s) {
+            mbar_init(&bars.w_full[s], 1);
+            mbar_init(&bars.w_empty[s], kDequantWarps);
+        }
+        for (int t = 0; t < kTiles; ++t) {
+            for (int b = 0; b < kABuffers; ++b) {
+                mbar_init(&bars.a_ready[t][b], 4);
+                mbar_init(&bars.a_free[t][b], 1);
+            }
+        }
+        for (int s = 0; s < kXStages; ++s) {
+            mbar_init(&bars.x_full[s], 1);
+            mbar_init(&bars.x_free[s], kMmaWarps);
+        }
+        mbar_init(&bars.d_ready, kMmaWarps);
+        bars.failed = status_is_set(p.status) ? 1 : 0;
+        bars.tmem_base = 0;
+        mbar_fence_init();
+    }
+    __syncthreads();
+    if (warp == kMmaWarp) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&bars.tmem_base)),
+                     "r"(kTmemColumns)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_base = bars.tmem_base;
+
+    float result[32];
+    bool have_result = false;
+
+    if (warp < kDequantWarps) {
+        // ---------------- dequantise: thread = row ----------------
+        const int set = warp / kRowWarps;
+        const int tile = (warp >> 2) & 1;
+        const int quarter = warp & 3;
+        const int local_row = quarter * 32 + lane;
+        const uint32_t lane_address = tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + tile * kTileColumns;
+        const int row_offset = local_row * kBoxRowBytes;
+        const int row_swizzle = local_row & 7;
+        const int scale_offset = (local_row & 31) * 16 + (local_row >> 5) * 4;
+        bool ok = true;
+        int previous_buf = -1;
+        int previous_slot = -1;  // >= 0: the previous chunk was the last reader of that ring slot
+        // Hands a finished chunk to the tensor-core warp and its ring slot back to the producer.
+        auto retire_previous = [&]() {
+            if (previous_buf >= 0) {
+                asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+                asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                __syncwarp();
+                if (lane == 0) {
+                    mbar_arrive(&bars.a_ready[tile][previous_buf]);
+                    if (previous_slot >= 0) {
+                        mbar_arrive(&bars.w_empty[previous_slot]);
+                    }
+                }
+                previous_buf = -1;
+                previous_slot = -1;
+            }
+        };
+        for (int c = set; c < total_chunks && ok; c += kDequantSets) {
+            const int wstage = c / kStageChunks;
+            const int slot = wstage % kWeightStages;
+            const int q = set;
+            ok = wait_or_fail(&bars.w_full[slot], (wstage / kWeightStages) & 1, &bars, p.status);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) {
+                break;
+            }
+            const unsigned char* stage = weight_ring + (slot * kTiles + tile) * kTileStageBytes;
+            const unsigned char* row = stage + row_offset;
+            const unsigned char* scale_tiles = stage + kBoxBytes + q * 1024 + scale_offset;
+            uint4 raw[4];
+#pragma unroll
+            for (int part = 0; part < 4; ++part) {
+                raw[part] = *reinterpret_cast<const uint4*>(row + (((q * 4 + part) ^ row_swizzle) << 4));
+            }
+            // 8 block scales of this chunk: two words of four e4m3 (cuda/nvfp4.cu:33-39 layout)
+            const uint32_t scale_word0 = *reinterpret_cast<const uint32_t*>(scale_tiles);
+            const uint32_t scale_word1 = *reinterpret_cast<const uint32_t*>(scale_tiles + 512);
+            const int buf = c % kABuffers;
+            ok = wait_or_fail(&bars.a_free[tile][buf], ((c / kABuffers) & 1) ^ 1, &bars, p.status);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) {
+                break;
+            }
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            uint32_t scale2[8];
+#pragma unroll
+            for (int gb = 0; gb < 2; ++gb) {
+                uint32_t lo, hi;
+                cvt_e4m3x4_to_f16x2(gb == 0 ? scale_word0 : scale_word1, lo, hi);
+                scale2[gb * 4 + 0] = __byte_perm(lo, 0, 0x1010);
+                scale2[gb * 4 + 1] = __byte_perm(lo, 0, 0x3232);
+                scale2[gb * 4 + 2] = __byte_perm(hi, 0, 0x1010);
+                scale2[gb * 4 + 3] = __byte_perm(hi, 0, 0x3232);
+            }
+#pragma unroll
+            for (int part = 0; part < 4; ++part) {
+                const uint32_t words[4] = {raw[part].x, raw[part].y, raw[part].z, raw[part].w};
+                uint32_t out[16];
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    uint32_t h[4];
+                    cvt_e2m1x8_to_f16x2(words[i], h);
+                    const uint32_t s = scale2[part * 2 + (i >> 1)];
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        out[i * 4 + j] = hmul2_bits(h[j], s);
+                    }
+                }
+                tmem_store16(lane_address + buf * 64 + part * 16, out);
+            }
+            previous_buf = buf;
+            previous_slot = slot;  // this warp reads one chunk per stage
+            retire_previous();
+        }
+        if (ok && set == 0) {
+            ok = wait_or_fail(&bars.d_ready, 0, &bars, p.status);
+            ok = __all_sync(0xffffffffu, ok);
+        }
+        if (ok && set == 0) {
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            // n_pad == 16 reads 32 columns too; the upper half is unused TMEM of this tile
+            tmem_load32(lane_address + kAccumulatorColumn, result);
+#pragma unroll
+            for (int extra = 1; extra < kAccumulators; ++extra) {
+                float more[32];
+                tmem_load32(lane_address + kAccumulatorColumn + extra * 32, more);
+#pragma unroll
+                for (int i = 0; i < 32; ++i) {
+                    result[i] += more[i];
+                }
+            }
+            have_result = true;
+        }
+    } else if (warp == kProducerWarp) {
+        // ---------------- producer: weights and scales ----------------
+        bool ok = true;
+        int k_stage = first_stage;
+        for (int wstage = 0; wstage < num_wstages && ok; ++wstage) {
+            const int slot = wstage % kWeightStages;
+            const int first = (s_begin + k_stage) * kStageChunks;  // first 128-element chunk of this stage
+            k_stage = k_stage + 1 == num_wstages ? 0 : k_stage + 1;
+            ok = wait_or_fail(&bars.w_empty[slot], ((wstage / kWeightStages) & 1) ^ 1, &bars, p.status);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) {
+                break;
+            }
+            if (elect_one()) {
+                constexpr int n = kStageChunks;
+                // A box is always delivered whole (rows or bytes outside the matrix arrive as zeros)
+                // and the scale storage is padded to whole 128-row blocks; a tile that starts past
+                // the matrix has no scale block at all and keeps whatever the slot held (its rows
+                // are never stored).
+                int scale_tiles_present = 0;
+#pragma unroll
+                for (int t = 0; t < kTiles; ++t) {
+                    scale_tiles_present += tile_row0[t] < p.out_features ? 1 : 0;
+                }
+                mbar_arrive_expect_tx(&bars.w_full[slot], kTiles * kBoxBytes + scale_tiles_present * n * 1024);
+#pragma unroll
+                for (int t = 0; t < kTiles; ++t) {
+                    unsigned char* stage = weight_ring + (slot * kTiles + t) * kTileStageBytes;
+                    tma_box_g2s(stage, t == 1 ? &map1 : &map0, first * 64, tile_row0[t], &bars.w_full[slot]);
+                    if (tile_row0[t] < p.out_features) {
+                        bulk_g2s(stage + kBoxBytes,
+                                 tile_scales[t] + (static_cast<size_t>(tile_row0[t] >> 7) * group_blocks + 2 * first) * 512,
+                                 n * 1024, &bars.w_full[slot]);
+                    }
+                }
+            }
+            __syncwarp();
+        }
+    } else if (warp < kFirstConvertWarp) {
+        // ---------------- tensor-core issue ----------------
+        // One warp per tile.  The whole warp waits; only the instructions themselves sit in the
+        // elected lane's region, which the compiler then runs on the uniform datapath.
+        const int t = warp - kMmaWarp;
+        const uint32_t idesc = (1u << 4) | (static_cast<uint32_t>(n_pad >> 3) << 17) | (8u << 24);
+        // K cores are n_pad * 16 bytes apart, 8-row groups 128 bytes; one instruction takes two K cores
+        const uint64_t desc_base = smem_descriptor(smem_u32(x_ring), n_pad * 16, 128);
+        const uint64_t desc_step = static_cast<uint64_t>((2 * n_pad * 16) >> 4);
+        const uint64_t desc_stage = static_cast<uint64_t>(x_stage_bytes >> 4);
+        const uint32_t a_tile = tmem_base + t * kTileColumns;
+        const uint32_t d_tile = a_tile + kAccumulatorColumn;
+        bool ok = true;
+        int buf = 0, xs = 0;
+        uint32_t a_parity = 0, x_parity = 0;
+        for (int c = 0; c < total_chunks && ok; ++c) {
+            ok = wait_or_fail(&bars.x_full[xs], x_parity, &bars, p.status);
+            if (ok) {
+                ok = wait_or_fail(&bars.a_ready[t][buf], a_parity, &bars, p.status);
+            }
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) {
+                break;
+            }
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            if (elect_one()) {
+                uint64_t b_desc = desc_base + desc_stage * xs;
+                const uint32_t a0 = a_tile + buf * 64;
+                const uint32_t later = c > 0 ? 1u : 0u;
+#pragma unroll
+                for (int s = 0; s < 8; ++s) {
+                    umma_f16(d_tile + (s % kAccumulators) * 32, a0 + s * 8, b_desc, idesc, s >= kAccumulators ? 1u : later);
+                    b_desc += desc_step;
+                }
+                umma_commit(&bars.a_free[t][buf]);
+                umma_commit(&bars.x_free[xs]);
+                if (c == total_chunks - 1) {
+                    umma_commit(&bars.d_ready);
+                }
+            }
+            __syncwarp();
+            if (++buf == kABuffers) {
+                buf = 0;
+                a_parity ^= 1;
+            }
+            if (++xs == kXStages) {
+                xs = 0;
+                x_parity ^= 1;
+            }
+        }
+    } else {
+        // ---------------- activation rows: bf16 -> f16, K-major core matrices ----------------
+        // Converting warp w owns operand stage w and the chunks w, w + 4, ...  Lane = activation row
+        // (two half-warps take the two halves of the K cores when only 16 rows are padded in).  The
+        // bf16 rows come global -> shared with cp.async, two chunks ahead of the one being converted,
+        // into staging that is private to the lane; then 16 bytes at a time: load, convert, store in
+        // the operand layout (K cores n_pad * 16 bytes apart, rows 16 bytes apart).
+        static_assert(kConvertWarps == kXStages, "one converting warp per operand stage");
+        const int w = warp - kFirstConvertWarp;
+        const int token = lane & (n_pad - 1);
+        const int half = n_pad == 16 ? lane >> 4 : 0;
+        const int units = n_pad == 16 ? 8 : 16;          // 16-byte units per lane and chunk
+        const int source_step = n_pad == 16 ? 16 : 8;    // bf16 elements between a lane's units
+        const bool real = token < p.batch;
+        const __nv_bfloat16* source = p.x + (real ? static_cast<size_t>(token) * K + half * 8 : 0);
+        const uint32_t copy_bytes = real ? 16u : 0u;     // padding rows are zero-filled
+        const uint32_t staging = smem_u32(raw_ring) + w * kRawBuffers * (32 * kChunkK * 2) + lane * 16;
+        unsigned char* stage = x_ring + w * x_stage_bytes + half * (n_pad * 16) + (token >> 3) * 128 + (token & 7) * 16;
+        // position of this warp's next chunk to fetch in the CTA's rotated walk over K
+        int fetch_stage = first_stage + w / kStageChunks;
+        fetch_stage -= fetch_stage >= num_wstages ? num_wstages : 0;
+        int fetch_chunk = w;
+        int fetch_buffer = 0;
+        auto fetch = [&]() {
+            if (fetch_chunk < total_chunks) {
+                const int k0 = ((s_begin + fetch_stage) * kStageChunks + (w % kStageChunks)) * kChunkK;
+                const __nv_bfloat16* from = source + (real ? k0 : 0);
+                const uint32_t to = staging + fetch_buffer * (32 * kChunkK * 2);
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                    if (i < units) {
+                        asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(to + i * 512),
+                                     "l"(from + (real ? i * source_step : 0)), "r"(copy_bytes)
+                                     : "memory");
+                    }
+                }
+                fetch_chunk += kConvertWarps;
+                fetch_stage += kConvertWarps / kStageChunks;
+                fetch_stage -= fetch_stage >= num_wstages ? num_wstages : 0;
+                fetch_buffer ^= 1;
+            }
+            asm volatile("cp.async.commit_group;" ::: "memory");
+        };
+        static_assert(kConvertWarps % kStageChunks == 0 && kRawBuffers == 2, "fetch bookkeeping");
+        bool ok = true;
+        fetch();
+        fetch();
+        int buffer = 0;
+        uint32_t parity = 1;  // the first use of a stage finds it free
+        for (int c = w; c < total_chunks && ok; c += kConvertWarps) {
+            asm volatile("cp.async.wait_group 1;" ::: "memory");
+            ok = wait_or_fail(&bars.x_free[w], parity, &bars, p.status);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) {
+                break;
+            }
+            parity ^= 1;
+            const uint32_t from = staging + buffer * (32 * kChunkK * 2);
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+                if (i < units) {
+                    uint4 raw;
+                    asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];"
+                                 : "=r"(raw.x), "=r"(raw.y), "=r"(raw.z), "=r"(raw.w)
+                                 : "r"(from + i * 512));
+                    *reinterpret_cast<uint4*>(stage + i * 512) = make_uint4(
+                        bf16x2_to_f16x2(raw.x), bf16x2_to_f16x2(raw.y), bf16x2_to_f16x2(raw.z), bf16x2_to_f16x2(raw.w));
+                }
+            }
+            fence_proxy_async();
+            __syncwarp();
+            if (lane == 0) {
+                mbar_arrive(&bars.x_full[w]);
+            }
+            buffer ^= 1;
+            fetch();  // refills the staging buffer just read
+        }
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
+    }
+
+    // ---------------- split-K reduction, epilogue ----------------
+    __syncthreads();
+    const bool failed = *reinterpret_cast<volatile int*>(&bars.failed) != 0;
+    if (p.splits > 1) {
+        cg::cluster_group cluster = cg::this_cluster();
+        float* reduce = reinterpret_cast<float*>(smem);  // [32][256] floats: the weight ring is idle now
+        if (split != 0 && have_result) {
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+                reduce[i * (kRowWarps * 32) + threadIdx.x] = result[i];
+            }
+        }
+        cluster.sync();
+        if (split == 0 && have_result) {
+            for (int r = 1; r < p.splits; ++r) {
+                const float* peer = cluster.map_shared_rank(reduce, r);
+#pragma unroll
+                for (int i = 0; i < 32; ++i) {
+                    result[i] += peer[i * (kRowWarps * 32) + threadIdx.x];
+                }
+            }
+        }
+        cluster.sync();
+    }
+
+    if (!failed && have_result && split == 0) {
+        const int tile = warp >> 2;
+        const int local_row = (warp & 3) * 32 + lane;
+        const int row = (p.swiglu ? row_group * kTileRows : (row_group * kTiles + tile) * kTileRows) + local_row;
+        if (p.swiglu) {
+            // gate accumulators sit in tile 0, up in tile 1: exchange through shared memory
+            float* exchange = reinterpret_cast<float*>(smem) + 32 * kRowWarps * 32;  // [32][128]
+            if (tile == 1) {
+#pragma unroll
+                for (int i = 0; i < 32; ++i) {
+                    exchange[i * kTileRows + local_row] = result[i] * p.inverse_scale[1];
+                }
+            }
+            asm volatile("bar.sync 1, 256;" ::: "memory");  // the eight dequantising warps only
+            if (tile == 0 && row < p.out_features) {
+#pragma unroll
+                for (int token = 0; token < 32; ++token) {
+                    if (token < p.batch) {
+                        const float gate = result[token] * p.inverse_scale[0];
+                        const float up = exchange[token * kTileRows + local_row];
+                        const float silu = gate / (1.0f + __expf(-gate));
+                        p.y[static_cast<size_t>(token) * p.out_features + row] = __float2bfloat16(silu * up);
+                    }
+                }
+            }
+        } else if (row < p.out_features) {
+#pragma unroll
+            for (int token = 0; token < 32; ++token) {
+                if (token < p.batch) {
+                    p.y[static_cast<size_t>(token) * p.out_features + row] =
+                        __float2bfloat16(result[token] * p.inverse_scale[0]);
+                }
+            }
+        }
+    }
+
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == kMmaWarp) {
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemColumns) : "memory");
+    }
+}
+
+using EncodeTiled = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                 const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                 CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+// The driver's tensor-map encoder, looked up through the runtime so that libcuda is not a link dependency.
+EncodeTiled tensor_map_encoder() {
+    static const EncodeTiled encoder = []() -> EncodeTiled {
+        void* entry = nullptr;
+        cudaDriverEntryPointQueryResult found = cudaDriverEntryPointSymbolNotFound;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &entry, cudaEnableDefault, &found) != cudaSuccess ||
+            found != cudaDriverEntryPointSuccess) {
+            return nullptr;
+        }
+        return reinterpret_cast<EncodeTiled>(entry);
+    }();
+    return encoder;
+}
+
+// Packed nibbles as a [rows][K / 2] byte matrix, fetched in boxes of 128 rows x 128 bytes.
+cudaError_t encode_weight_map(CUtensorMap* map, const void* packed, int out_features, int in_features) {
+    const EncodeTiled encode = tensor_map_encoder();
+    if (encode == nullptr) {
+        return cudaErrorNotSupported;
+    }
+    const cuuint64_t dims[2] = {static_cast<cuuint64_t>(in_features / 2), static_cast<cuuint64_t>(out_features)};
+    const cuuint64_t strides[1] = {static_cast<cuuint64_t>(in_features / 2)};
+    const cuuint32_t box[2] = {kBoxRowBytes, kTileRows};
+    const cuuint32_t element_strides[2] = {1, 1};
+    const CUresult result =
+        encode(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(packed), dims, strides, box, element_strides,
+               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return result == CUDA_SUCCESS ? cudaSuccess : cudaErrorInvalidValue;
+}
+
+int sm_count_umma() {
+    int device = 0, sms = 148;
+    if (cudaGetDevice(&device) == cudaSuccess) {
+        int value = 0;
+        if (cudaDeviceGetAttribute(&value, cudaDevAttrMultiProcessorCount, device) == cudaSuccess && value > 0) {
+            sms = value;
+        }
+    }
+    return sms;
+}
+
+}  // namespace
+
+
+cudaError_t launch_nvfp4_umma(const void* packed0, const void* scales0, const void* packed1, const void* scales1,
+                              const void* x, void* y, int out_features, int in_features, int batch, float inverse0,
+                              float inverse1, bool swiglu, cudaStream_t stream) {
+    UmmaParams p = {};
+    p.packed[0] = static_cast<const uint8_t*>(packed0);
+    p.scales[0] = static_cast<const uint8_t*>(scales0);
+    p.packed[1] = static_cast<const uint8_t*>(swiglu ? packed1 : packed0);
+    p.scales[1] = static_cast<const uint8_t*>(swiglu ? scales1 : scales0);
+    p.x = static_cast<const __nv_bfloat16*>(x);
+    p.y = static_cast<__nv_bfloat16*>(y);
+    p.inverse_scale[0] = inverse0;
+    p.inverse_scale[1] = inverse1;
+    p.out_features = out_features;
+    p.in_features = in_features;
+    p.batch = batch;
+    p.n_pad = batch <= 16 ? 16 : 32;
+    p.swiglu = swiglu ? 1 : 0;
+    const int rows_per_group = swiglu ? kTileRows : kTiles * kTileRows;
+    p.row_groups = (out_features + rows_per_group - 1) / rows_per_group;
+    CUtensorMap map0, map1;
+    cudaError_t encoded = encode_weight_map(&map0, p.packed[0], out_features, in_features);
+    if (encoded == cudaSuccess) {
+        encoded = encode_weight_map(&map1, p.packed[1], out_features, in_features);
+    }
+    if (encoded != cudaSuccess) {
+        return encoded;
+    }
+    const int smem_bytes =
+        kWeightStages * kTiles * kTileStageBytes + (kXStages + kConvertWarps * kRawBuffers) * 32 * kChunkK * 2 + 1024;
+    static const cudaError_t opted =
+        cudaFuncSetAttribute(nvfp4_umma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
+    if (opted != cudaSuccess) {
+        return opted;
+    }
+    // K split: the slices of a row group form a cluster, and a cluster must sit inside one GPC, so
+    // the number of clusters resident at once is asked of the driver per cluster size.  The cost of
+    // a plan is its waves times the chunks per slice, plus a term for the reduction.
+    struct Residency {
+        int clusters[9];
+    };
+    static const Residency residency = [smem_bytes]() {
+        Residency r = {};
+        for (int size = 1; size <= 8; ++size) {
+            cudaLaunchConfig_t probe = {};
+            probe.gridDim = dim3(size * 64);
+            probe.blockDim = dim3(kThreads);
+            probe.dynamicSmemBytes = smem_bytes;
+            cudaLaunchAttribute attribute[1];
+            attribute[0].id = cudaLaunchAttributeClusterDimension;
+            attribute[0].val.clusterDim.x = size;
+            attribute[0].val.clusterDim.y = 1;
+            attribute[0].val.clusterDim.z = 1;
+            probe.attrs = attribute;
+            probe.numAttrs = 1;
+            int clusters = 0;
+            if (cudaOccupancyMaxActiveClusters(&clusters, nvfp4_umma_kernel, &probe) != cudaSuccess) {
+                clusters = 0;
+                (void)cudaGetLastError();
+            }
+            r.clusters[size] = clusters;
+        }
+        return r;
+    }();
+    const int chunks = in_features / kChunkK;
+    int splits = 1;
+    double best_cost = 1e30;
+    for (int size = 1; size <= 8; ++size) {
+        const int clusters = size == 1 ? sm_count_umma() : residency.clusters[size];
+        if (clusters <= 0 || (size > 1 && chunks / size < 2 * kStageChunks)) {
+            continue;
+        }
+        const int waves = (p.row_groups + clusters - 1) / clusters;
+        const double cost = waves * (static_cast<double>((chunks + size - 1) / size) + 6.0) + 1.5 * (size - 1);
+        if (cost < best_cost) {
+            best_cost = cost;
+            splits = size;
+        }
+    }
+    p.splits = splits;
+    p.status = status_ptr();
+    if (p.status == nullptr) {
+        return cudaErrorInvalidValue;
+    }
+    cudaLaunchConfig_t config = {};
+    config.gridDim = dim3(p.row_groups * splits);
+    config.blockDim = dim3(kThreads);
+    config.dynamicSmemBytes = smem_bytes;
+    config.stream = stream;
+    cudaLaunchAttribute attribute[1];
+    attribute[0].id = cudaLaunchAttributeClusterDimension;
+    attribute[0].val.clusterDim.x = splits;
+    attribute[0].val.clusterDim.y = 1;
+    attribute[0].val.clusterDim.z = 1;
+    config.attrs = attribute;
+    config.numAttrs = splits > 1 ? 1 : 0;
+    return cudaLaunchKernelEx(&config, nvfp4_umma_kernel, map0, map1, p);
+}
+
+}  // namespace qwc
