@@ -623,7 +623,11 @@ template <int MODE>
 cudaError_t dispatch(const GemvParams& p, cudaStream_t stream) {
     const int wide_tiles = ((p.out_features + 127) / 128) * 4;
     const bool wide = MODE == kNvfp4 && wide_tiles >= 2 * sm_count();
-    if (p.batch <= 8) {
+    // The tcgen05 kernel streams weights faster than the mma.sync one at every batch size but has a
+    // longer start-up (TMEM allocation, first TMA round trip, cluster reduction): it takes over
+    // above eight rows, and below that for matrices of 30 MB and more.
+    const bool large = static_cast<long long>(p.out_features) * p.in_features >= 60ll * 1000 * 1000;
+    if (MODE == kFp8Rows ? p.batch <= 8 : (p.batch <= 8 && !large)) {
         return launch<1, 1, MODE>(p, stream);
     }
     if (MODE != kFp8Rows) {
