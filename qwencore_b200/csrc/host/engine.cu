@@ -650,13 +650,15 @@ int qwc_engine_create(const qwc_engine_config* config, qwc_engine** out) {
     QWC_STEP(gpu_alloc_t(e, &e->argmax_values, static_cast<size_t>(mb) * kArgmaxParts, true));
     QWC_STEP(gpu_alloc_t(e, &e->argmax_indices, static_cast<size_t>(mb) * kArgmaxParts, true));
 
-    // attention partitions: enough CTAs for two per SM, spans of at least 256 tokens
+    // Attention partitions: the cap on how many tasks one row may be cut into (the kernel sizes
+    // the tasks on the device from the contexts it finds).  Spans of at least 128 tokens, at most
+    // 4096 partial slots per head.
     if (c.attention_partitions > 0) {
         e->partitions = c.attention_partitions;
     } else {
-        const int ctas = kKvHeads * mb;
-        const int want = (2 * 148 + ctas - 1) / ctas;
-        const int most = (c.max_context + 255) / 256;
+        const int want = (c.max_context + 127) / 128;
+        int most = 4096 / mb;
+        most = most < 8 ? 8 : most;
         e->partitions = want < most ? want : most;
         if (e->partitions < 1) {
             e->partitions = 1;

@@ -8,22 +8,26 @@
 //
 // The op reads every K and V byte of the row's context once and nothing else of size,
 // so it is HBM-bound.  Layout for sm_100a:
-//   * grid (kv head, row, partition); the partition's span is cut on the device from
-//     the row's real context, so the launch shape depends only on capacity-level values
-//     and the step stays capturable in a CUDA graph;
-//   * KV moves in 4 KiB units (16 tokens x 256 B of one kv head: a whole 16-token page,
-//     or a quarter of a 64-token page) by bulk-async copies (TMA 1-D) into a 3-stage
-//     ring of 8 units (128 tokens, 64 KiB of K+V per stage) guarded by mbarriers -
-//     up to 192 KiB in flight per SM and no registers spent on loads;
+//   * a persistent grid of one CTA per SM.  The rows of a ragged batch differ in context by
+//     orders of magnitude, so the work is cut on the device into tasks of equal size: a task
+//     is (row, kv head, span of units_per_task 16-token units), units_per_task chosen from
+//     the sum of the rows' contexts so that every CTA gets about six tasks, and CTA c takes
+//     tasks c, c + grid, ...  The launch shape depends only on the SM count, so the step
+//     stays capturable in a CUDA graph whatever the contexts are;
+//   * inside a CTA one producer warp and eight consumer warps.  KV moves in 4 KiB units (16
+//     tokens x 256 B of one kv head: a whole 16-token page, or a quarter of a 64-token page)
+//     by bulk-async copies (TMA 1-D) into a 3-stage ring of 8 units (128 tokens, 64 KiB of
+//     K+V per stage) guarded by full/empty mbarriers; the producer runs ahead across task
+//     boundaries, so the ring never drains between tasks;
 //   * each unit lands 16 bytes further than a multiple of 4 KiB.  An MMA column tile is
 //     "token j of 8 different units", so the eight rows an ldmatrix or a fragment load
 //     touches fall in eight different 16-byte bank groups: conflict-free without a
 //     swizzled tensor map;
 //   * QK^T: the six heads of the group are rows of one m16 tile, e4m3 pairs are widened
-//     by the hardware converter straight into B fragments; PV: V is transposed on the
-//     fly by ldmatrix.trans on byte pairs and a byte permute; the four warps split the
-//     tokens for QK^T and the 256 output dims for PV, exchanging P through 2 KiB of
-//     shared memory.
+//     by the hardware converter straight into B fragments; each warp owns two column tiles
+//     and keeps four independent accumulation chains.  PV: V is transposed on the fly by
+//     ldmatrix.trans on byte pairs and a byte permute; the eight warps split the 256 output
+//     dims, exchanging P through 2 KiB of shared memory.
 //
 // Cache memory must hold finite e4m3 codes in every allocated page (a zero-initialised
 // pool, as the reference allocates it): positions past the context are masked by
@@ -34,8 +38,9 @@
 namespace qwc {
 namespace {
 
-constexpr int kThreads = 128;
-constexpr int kWarps = 4;
+constexpr int kConsumerWarps = 8;
+constexpr int kConsumerThreads = kConsumerWarps * 32;
+constexpr int kThreads = kConsumerThreads + 32;  // + the producer warp
 constexpr int kUnitTokens = 16;
 constexpr int kUnitBytes = kUnitTokens * kHeadDim;  // 4096
 constexpr int kUnitPitch = kUnitBytes + 16;         // staggered landing offset
@@ -45,14 +50,32 @@ constexpr int kStageBytes = kStageUnits * kUnitPitch;    // per K or V
 constexpr int kPartialFloats = 2;
 constexpr size_t kPartialBytes = 2 * sizeof(float) + kHeadDim * sizeof(__half);  // 520
 constexpr float kLog2e = 1.4426950408889634f;
+constexpr int kTasksPerCta = 6;       // target when the task size is chosen
+constexpr int kMaxCtaTasks = 64;      // list capacity; the plan keeps a CTA far below it
+constexpr int kPlanRows = 256;        // rows whose prefix fits the shared-memory table
+
+struct Task {
+    int row;
+    int kv_head;
+    int part;
+    int unit_begin;
+    int units;
+};
 
 struct Smem {
     uint8_t k[kStages][kStageBytes];
     uint8_t v[kStages][kStageBytes];
     uint2 p[kStageUnits][32];       // P as A fragments: [pv k-step][lane]
-    float warp_max[kWarps][8];
-    float warp_sum[kWarps][8];
+    float warp_max[kConsumerWarps][8];
+    float warp_sum[kConsumerWarps][8];
     uint64_t full[kStages];
+    uint64_t empty[kStages];
+    int first_pair[kPlanRows + 1];  // prefix sum of the rows' task counts (per kv head)
+    Task tasks[kMaxCtaTasks];
+    int task_count;
+    int units_per_task;
+    int issued;                     // stages the producer has put in flight
+    int consumed;                   // stages the consumers have finished
     int failed;
 };
 
@@ -79,6 +102,38 @@ __device__ __forceinline__ void cvt_e4m3x4(uint32_t word, uint32_t& lo, uint32_t
         : "r"(word));
 }
 
+__device__ __forceinline__ void consumer_sync() {
+    asm volatile("bar.sync 1, %0;" ::"n"(kConsumerThreads) : "memory");
+}
+
+// 16-token units per task.  Both kernels evaluate this from the same inputs.
+//   * at most `partitions` tasks per row: the workspace has that many partial slots;
+//   * about kTasksPerCta tasks per CTA, so that the CTAs finish together;
+//   * whole stages, so that only the last stage of a row is partly filled.
+__device__ __forceinline__ int plan_units_per_task(long long total_units, int capacity_units, int partitions,
+                                                   int ctas) {
+    if (partitions <= 1) {
+        return capacity_units > 0 ? capacity_units : 1;
+    }
+    const long long by_capacity = (capacity_units + partitions - 1) / partitions;
+    const long long by_balance = (total_units * kKvHeads + static_cast<long long>(ctas) * kTasksPerCta - 1) /
+                                 (static_cast<long long>(ctas) * kTasksPerCta);
+    long long units = by_capacity > by_balance ? by_capacity : by_balance;
+    units = (units + kStageUnits - 1) / kStageUnits * kStageUnits;
+    return static_cast<int>(units < kStageUnits ? kStageUnits : units);
+}
+
+// A context longer than the block table can describe is cut at the table's capacity.
+__device__ __forceinline__ int units_of_context(uint32_t context, int capacity_units) {
+    const uint32_t units = (context + kUnitTokens - 1) / kUnitTokens;
+    return static_cast<int>(units < static_cast<uint32_t>(capacity_units) ? units : capacity_units);
+}
+
+// Tasks of one row per kv head; a row without context still gets one (it stores zeros).
+__device__ __forceinline__ int parts_of_row(int units, int units_per_task) {
+    return units <= 0 ? 1 : (units + units_per_task - 1) / units_per_task;
+}
+
 template <bool kSplit>
 __global__ void __launch_bounds__(kThreads, 1) paged_attention_packed_kernel(
     const __nv_bfloat16* __restrict__ query, const __nv_bfloat16* __restrict__ query_gate_projection,
@@ -86,276 +141,389 @@ __global__ void __launch_bounds__(kThreads, 1) paged_attention_packed_kernel(
     const uint32_t* __restrict__ block_tables, const uint32_t* __restrict__ context_lengths,
     const float* __restrict__ key_scales, const float* __restrict__ value_scales,
     __nv_bfloat16* __restrict__ output, float* __restrict__ partial_stats, __half* __restrict__ partial_out,
-    int max_blocks, int row_base, int page_size, int gate_stride, float softmax_scale, int* status) {
+    int rows, int max_blocks, int row_base, int page_size, int gate_stride, int partitions, float softmax_scale,
+    int* status) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
     Smem& sm = *reinterpret_cast<Smem*>(smem_raw);
 
     if (status_is_set(status)) {
         return;
     }
-    const int kv_head = blockIdx.x;
-    const int row = row_base + blockIdx.y;
-    const int part = blockIdx.z;
-    const int partitions = gridDim.z;
     const int lane = threadIdx.x & 31;
     const int warp = threadIdx.x >> 5;
     const int g = lane >> 2;
     const int t = lane & 3;
-
-    const int context = static_cast<int>(context_lengths[row]);
-    const int total_units = (context + kUnitTokens - 1) / kUnitTokens;
-    const int units_per_part = (total_units + partitions - 1) / partitions;
-    const int unit_begin = part * units_per_part;
-    const int unit_end = min(total_units, unit_begin + units_per_part);
-    const int my_units = max(0, unit_end - unit_begin);
-    const int num_stages = (my_units + kStageUnits - 1) / kStageUnits;
     const int units_per_page = page_size / kUnitTokens;
-    const uint32_t* table = block_tables + static_cast<size_t>(row) * max_blocks;
+    const int capacity_units = max_blocks * units_per_page;
 
+    // ---- plan: task size, the rows' task counts, this CTA's task list ---------------------
     // Stale bytes of a partly filled stage are multiplied by zero probabilities, so they
-    // must be finite: clear the value ring once.
+    // must be finite: clear the value ring once (every later byte comes from the cache).
     for (int i = threadIdx.x; i < kStages * kStageBytes / 16; i += kThreads) {
         reinterpret_cast<uint4*>(&sm.v[0][0])[i] = make_uint4(0, 0, 0, 0);
     }
-    if (threadIdx.x == 0) {
-        sm.failed = 0;
-        for (int s = 0; s < kStages; ++s) {
-            mbar_init(&sm.full[s], 1);
+    if (warp == 0) {
+        long long total_units = 0;
+        for (int r = lane; r < rows; r += 32) {
+            total_units += units_of_context(context_lengths[row_base + r], capacity_units);
         }
-        mbar_fence_init();
+#pragma unroll
+        for (int offset = 16; offset > 0; offset >>= 1) {
+            total_units += __shfl_xor_sync(0xffffffffu, total_units, offset);
+        }
+        const int units_per_task = plan_units_per_task(total_units, capacity_units, kSplit ? partitions : 1, gridDim.x);
+        // prefix of the rows' task counts: a warp scan per 32 rows
+        int carry = 0;
+        for (int base = 0; base < rows; base += 32) {
+            const int r = base + lane;
+            const int mine =
+                r < rows ? parts_of_row(units_of_context(context_lengths[row_base + r], capacity_units), units_per_task) : 0;
+            int inclusive = mine;
+#pragma unroll
+            for (int offset = 1; offset < 32; offset <<= 1) {
+                const int other = __shfl_up_sync(0xffffffffu, inclusive, offset);
+                if (lane >= offset) {
+                    inclusive += other;
+                }
+            }
+            if (r < rows) {
+                sm.first_pair[r] = carry + inclusive - mine;
+            }
+            carry += __shfl_sync(0xffffffffu, inclusive, 31);
+        }
+        if (lane == 0) {
+            sm.first_pair[rows] = carry;
+            sm.units_per_task = units_per_task;
+            sm.failed = 0;
+            sm.issued = 0;
+            for (int s = 0; s < kStages; ++s) {
+                mbar_init(&sm.full[s], 1);
+                mbar_init(&sm.empty[s], kConsumerWarps);
+            }
+            mbar_fence_init();
+        }
+        __syncwarp();
+        // task ids of this CTA: c, c + grid, ...; id = pair * kKvHeads + kv head
+        const int total_tasks = carry * kKvHeads;
+        int count = 0;
+        for (int base = 0; base < kMaxCtaTasks; base += 32) {
+            const int index = base + lane;
+            const long long id = static_cast<long long>(blockIdx.x) + static_cast<long long>(index) * gridDim.x;
+            if (id < total_tasks) {
+                const int pair = static_cast<int>(id / kKvHeads);
+                int row = 0;
+                while (row + 1 < rows && sm.first_pair[row + 1] <= pair) {
+                    ++row;
+                }
+                const int part = pair - sm.first_pair[row];
+                const int row_units = units_of_context(context_lengths[row_base + row], capacity_units);
+                Task task;
+                task.row = row_base + row;
+                task.kv_head = static_cast<int>(id % kKvHeads);
+                task.part = part;
+                task.unit_begin = part * units_per_task;
+                task.units = max(0, min(units_per_task, row_units - task.unit_begin));
+                sm.tasks[index] = task;
+                ++count;
+            }
+        }
+        count = __reduce_add_sync(0xffffffffu, count);
+        if (lane == 0) {
+            sm.task_count = count;
+        }
     }
     fence_proxy_async();
     __syncthreads();
+    const int task_count = sm.task_count;
 
-    auto issue_stage = [&](int stage_index) {
-        const int slot = stage_index % kStages;
-        const int first = unit_begin + stage_index * kStageUnits;
-        const int count = min(kStageUnits, unit_end - first);
-        mbar_arrive_expect_tx(&sm.full[slot], static_cast<uint32_t>(count) * 2 * kUnitBytes);
-        for (int u = 0; u < count; ++u) {
-            const int unit = first + u;
-            const uint32_t physical = table[unit / units_per_page];
-            const size_t offset =
-                ((static_cast<size_t>(physical) * kKvHeads + kv_head) * page_size +
-                 static_cast<size_t>(unit % units_per_page) * kUnitTokens) *
-                kHeadDim;
-            bulk_g2s(&sm.k[slot][u * kUnitPitch], key_cache + offset, kUnitBytes, &sm.full[slot]);
-            bulk_g2s(&sm.v[slot][u * kUnitPitch], value_cache + offset, kUnitBytes, &sm.full[slot]);
-        }
-    };
-    if (threadIdx.x == 0) {
-        for (int s = 0; s < kStages && s < num_stages; ++s) {
-            issue_stage(s);
-        }
-    }
-
-    // Query A fragments for the 16 k-steps.  K fragment reads take 16-byte bank group
-    // u(t, m) = 2t + (m & 1) + 8 (m >> 1) of a token row in load m, so k-step (m, s)
-    // contracts dims 16 u + 4 s .. + 3 for t = 0..3: Q uses the same permutation.
-    uint32_t qa[16][2];
-    {
-        const int head = kv_head * kGqaGroup + g;
-        const __nv_bfloat16* qp = query + (static_cast<size_t>(row) * kQueryHeads + head) * kHeadDim;
-#pragma unroll
-        for (int m = 0; m < 4; ++m) {
-            const int unit = 2 * t + (m & 1) + 8 * (m >> 1);
-#pragma unroll
-            for (int s = 0; s < 4; ++s) {
-                if (g < kGqaGroup) {
-                    const uint2 raw = *reinterpret_cast<const uint2*>(qp + 16 * unit + 4 * s);
-                    qa[m * 4 + s][0] = pack_half2(__uint_as_float(raw.x << 16), __uint_as_float(raw.x & 0xffff0000u));
-                    qa[m * 4 + s][1] = pack_half2(__uint_as_float(raw.y << 16), __uint_as_float(raw.y & 0xffff0000u));
-                } else {
-                    qa[m * 4 + s][0] = 0;
-                    qa[m * 4 + s][1] = 0;
+    if (warp == kConsumerWarps) {
+        // ---------------- producer ----------------------------------------------------------
+        int n = 0;  // stages issued so far
+        bool ok = true;
+        for (int ti = 0; ti < task_count && ok; ++ti) {
+            const Task task = sm.tasks[ti];
+            const uint32_t* table = block_tables + static_cast<size_t>(task.row) * max_blocks;
+            const int stages = (task.units + kStageUnits - 1) / kStageUnits;
+            for (int st = 0; st < stages && ok; ++st, ++n) {
+                const int slot = n % kStages;
+                ok = mbar_wait_bounded(&sm.empty[slot], ((n / kStages) & 1) ^ 1, kStatusAttentionPageWait, status);
+                ok = __all_sync(0xffffffffu, ok) && *reinterpret_cast<volatile int*>(&sm.failed) == 0;
+                if (!ok) {
+                    break;
+                }
+                const int first = task.unit_begin + st * kStageUnits;
+                const int count = min(kStageUnits, task.units - st * kStageUnits);
+                if (lane == 0) {
+                    mbar_arrive_expect_tx(&sm.full[slot], static_cast<uint32_t>(count) * 2 * kUnitBytes);
+                }
+                __syncwarp();
+                if (lane < count) {
+                    const int unit = first + lane;
+                    const uint32_t physical = table[unit / units_per_page];
+                    const size_t offset = ((static_cast<size_t>(physical) * kKvHeads + task.kv_head) * page_size +
+                                           static_cast<size_t>(unit % units_per_page) * kUnitTokens) *
+                                          kHeadDim;
+                    bulk_g2s(&sm.k[slot][lane * kUnitPitch], key_cache + offset, kUnitBytes, &sm.full[slot]);
+                    bulk_g2s(&sm.v[slot][lane * kUnitPitch], value_cache + offset, kUnitBytes, &sm.full[slot]);
+                }
+                __syncwarp();
+                if (lane == 0) {
+                    *reinterpret_cast<volatile int*>(&sm.issued) = n + 1;
                 }
             }
         }
-    }
-
-    const float k_scale = key_scales ? key_scales[kv_head] : 1.0f;
-    const float score_scale = softmax_scale * k_scale * kLog2e;
-
-    float oacc[4][2][4];
-#pragma unroll
-    for (int a = 0; a < 4; ++a) {
-#pragma unroll
-        for (int b = 0; b < 2; ++b) {
-#pragma unroll
-            for (int c = 0; c < 4; ++c) {
-                oacc[a][b][c] = 0.0f;
-            }
-        }
-    }
-    float running_max = -INFINITY;  // log2 domain, shared by all warps
-    float running_sum = 0.0f;       // this warp's tokens only
-
-    const uint32_t v_base = smem_u32(&sm.v[0][0]);
-
-    for (int stage_index = 0; stage_index < num_stages; ++stage_index) {
-        const int slot = stage_index % kStages;
-        if (!mbar_wait_bounded(&sm.full[slot], (stage_index / kStages) & 1, kStatusAttentionPageWait, status)) {
-            sm.failed = 1;
-        }
-        const int first_token = (unit_begin + stage_index * kStageUnits) * kUnitTokens;
-
-        // ---- S = Q K^T for this warp's four column tiles (token j of each unit) ----
-        float sc[4][2];
-        float local_max = -INFINITY;
-#pragma unroll
-        for (int jj = 0; jj < 4; ++jj) {
-            const int j = 4 * warp + jj;
-            float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-            const uint8_t* krow = &sm.k[slot][g * kUnitPitch + j * kHeadDim];
-#pragma unroll
-            for (int m = 0; m < 4; ++m) {
-                const int unit = 2 * t + (m & 1) + 8 * (m >> 1);
-                const uint4 raw = *reinterpret_cast<const uint4*>(krow + 16 * unit);
-                const uint32_t words[4] = {raw.x, raw.y, raw.z, raw.w};
-#pragma unroll
-                for (int s = 0; s < 4; ++s) {
-                    uint32_t b0, b1;
-                    cvt_e4m3x4(words[s], b0, b1);
-                    mma_f16_16816(acc, qa[m * 4 + s][0], 0u, qa[m * 4 + s][1], 0u, b0, b1);
-                }
-            }
-            // acc[0], acc[1]: head g, tokens (unit 2t, j) and (unit 2t + 1, j)
-#pragma unroll
-            for (int e = 0; e < 2; ++e) {
-                const int token = first_token + (2 * t + e) * kUnitTokens + j;
-                const bool valid = token < context && (2 * t + e) < (unit_end - unit_begin - stage_index * kStageUnits);
-                sc[jj][e] = valid ? acc[e] * score_scale : -INFINITY;
-                local_max = fmaxf(local_max, sc[jj][e]);
-            }
-        }
-        local_max = fmaxf(local_max, __shfl_xor_sync(0xffffffffu, local_max, 1));
-        local_max = fmaxf(local_max, __shfl_xor_sync(0xffffffffu, local_max, 2));
-        if (t == 0) {
-            sm.warp_max[warp][g] = local_max;
-        }
-        __syncthreads();
-
-        float new_max = running_max;
-#pragma unroll
-        for (int w = 0; w < kWarps; ++w) {
-            new_max = fmaxf(new_max, sm.warp_max[w][g]);
-        }
-        const float rescale = new_max == -INFINITY ? 1.0f : exp2f(running_max - new_max);
-        running_max = new_max;
-        float row_sum = 0.0f;
-        uint32_t pfrag[2][2];
-#pragma unroll
-        for (int jj = 0; jj < 4; ++jj) {
-            const float p0 = new_max == -INFINITY ? 0.0f : exp2f(sc[jj][0] - new_max);
-            const float p1 = new_max == -INFINITY ? 0.0f : exp2f(sc[jj][1] - new_max);
-            row_sum += p0 + p1;
-            pfrag[jj >> 1][jj & 1] = pack_half2(p0, p1);
-        }
-        running_sum = running_sum * rescale + row_sum;
-        // PV k-step kk contracts tokens j = 2 kk and 2 kk + 1 of the eight units.
-        sm.p[2 * warp][lane] = make_uint2(pfrag[0][0], pfrag[0][1]);
-        sm.p[2 * warp + 1][lane] = make_uint2(pfrag[1][0], pfrag[1][1]);
-#pragma unroll
-        for (int a = 0; a < 4; ++a) {
-#pragma unroll
-            for (int b = 0; b < 2; ++b) {
-                oacc[a][b][0] *= rescale;
-                oacc[a][b][1] *= rescale;
-            }
-        }
-        __syncthreads();
-
-        // ---- O += P V for this warp's 64 output dims --------------------------------
-        const uint32_t v_slot = v_base + slot * kStageBytes;
-#pragma unroll
-        for (int kk = 0; kk < kStageUnits; ++kk) {
-            const uint2 pa = sm.p[kk][lane];
-#pragma unroll
-            for (int dp = 0; dp < 2; ++dp) {
-                const int matrix = lane >> 3;
-                const int token = 2 * kk + (matrix & 1);
-                const int dblock = 4 * warp + 2 * dp + (matrix >> 1);
-                uint32_t r[4];
-                ldmatrix_x4_trans(r, v_slot + (lane & 7) * kUnitPitch + token * kHeadDim + dblock * 16);
-#pragma unroll
-                for (int half = 0; half < 2; ++half) {
-                    // bytes (b0, b2 | b1, b3): low pair feeds the even dim, high pair the odd dim
-                    const uint32_t lo_tokens = __byte_perm(r[2 * half], 0, 0x3120);
-                    const uint32_t hi_tokens = __byte_perm(r[2 * half + 1], 0, 0x3120);
-                    uint32_t even0, odd0, even1, odd1;
-                    cvt_e4m3x4(lo_tokens, even0, odd0);
-                    cvt_e4m3x4(hi_tokens, even1, odd1);
-                    mma_f16_16816(oacc[2 * dp + half][0], pa.x, 0u, pa.y, 0u, even0, even1);
-                    mma_f16_16816(oacc[2 * dp + half][1], pa.x, 0u, pa.y, 0u, odd0, odd1);
-                }
-            }
-        }
-        __syncthreads();
-        if (threadIdx.x == 0 && stage_index + kStages < num_stages) {
-            issue_stage(stage_index + kStages);
-        }
-    }
-
-    // ---- combine the warps' sums, normalise, write ------------------------------------
-    running_sum += __shfl_xor_sync(0xffffffffu, running_sum, 1);
-    running_sum += __shfl_xor_sync(0xffffffffu, running_sum, 2);
-    if (t == 0) {
-        sm.warp_sum[warp][g] = running_sum;
-    }
-    __syncthreads();
-    if (sm.failed || g >= kGqaGroup) {
-        return;
-    }
-    float total = 0.0f;
-#pragma unroll
-    for (int w = 0; w < kWarps; ++w) {
-        total += sm.warp_sum[w][g];
-    }
-    const float v_scale = value_scales ? value_scales[kv_head] : 1.0f;
-    const float inverse = total > 0.0f ? v_scale / total : 0.0f;
-    const int head = kv_head * kGqaGroup + g;
-    const size_t pair = static_cast<size_t>(row - row_base) * kQueryHeads + head;
-
-    if (kSplit) {
-        if (warp == 0 && t == 0) {
-            float* stats = partial_stats + (pair * partitions + part) * kPartialFloats;
-            stats[0] = running_max;
-            stats[1] = total;
-        }
-        __half* po = partial_out + (pair * partitions + part) * kHeadDim;
-#pragma unroll
-        for (int a = 0; a < 4; ++a) {
-            const int d = 16 * (4 * warp + a) + 4 * t;
-            const uint2 packed = make_uint2(pack_half2(oacc[a][0][0] * inverse, oacc[a][1][0] * inverse),
-                                            pack_half2(oacc[a][0][1] * inverse, oacc[a][1][1] * inverse));
-            *reinterpret_cast<uint2*>(po + d) = packed;
+        if (!ok && lane == 0) {
+            *reinterpret_cast<volatile int*>(&sm.failed) = 1;
         }
     } else {
-        __nv_bfloat16* op = output + (static_cast<size_t>(row) * kQueryHeads + head) * kHeadDim;
-        const __nv_bfloat16* gp =
-            query_gate_projection
-                ? query_gate_projection + static_cast<size_t>(row) * gate_stride + head * (2 * kHeadDim) + kHeadDim
-                : nullptr;
+        // ---------------- consumers ---------------------------------------------------------
+        const uint32_t v_base = smem_u32(&sm.v[0][0]);
+        int n = 0;  // stages consumed so far
+        bool ok = true;
+        for (int ti = 0; ti < task_count && ok; ++ti) {
+            const Task task = sm.tasks[ti];
+            const int row = task.row;
+            const int kv_head = task.kv_head;
+            const int context = min(static_cast<int>(min(context_lengths[row], 0x7fffffffu)), capacity_units * kUnitTokens);
+
+            // Query A fragments for the 16 k-steps.  K fragment reads take 16-byte bank group
+            // u(t, m) = 2t + (m & 1) + 8 (m >> 1) of a token row in load m, so k-step (m, s)
+            // contracts dims 16 u + 4 s .. + 3 for t = 0..3: Q uses the same permutation.
+            uint32_t qa[16][2];
+            {
+                const int head = kv_head * kGqaGroup + g;
+                const __nv_bfloat16* qp = query + (static_cast<size_t>(row) * kQueryHeads + head) * kHeadDim;
 #pragma unroll
-        for (int a = 0; a < 4; ++a) {
-            const int d = 16 * (4 * warp + a) + 4 * t;
-            float values[4] = {oacc[a][0][0] * inverse, oacc[a][1][0] * inverse, oacc[a][0][1] * inverse,
-                               oacc[a][1][1] * inverse};
-            if (gp != nullptr) {
-                const uint2 graw = *reinterpret_cast<const uint2*>(gp + d);
-                const float gates[4] = {__uint_as_float(graw.x << 16), __uint_as_float(graw.x & 0xffff0000u),
-                                        __uint_as_float(graw.y << 16), __uint_as_float(graw.y & 0xffff0000u)};
+                for (int m = 0; m < 4; ++m) {
+                    const int unit = 2 * t + (m & 1) + 8 * (m >> 1);
 #pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    values[i] *= 1.0f / (1.0f + __expf(-gates[i]));
+                    for (int s = 0; s < 4; ++s) {
+                        if (g < kGqaGroup) {
+                            const uint2 raw = *reinterpret_cast<const uint2*>(qp + 16 * unit + 4 * s);
+                            qa[m * 4 + s][0] =
+                                pack_half2(__uint_as_float(raw.x << 16), __uint_as_float(raw.x & 0xffff0000u));
+                            qa[m * 4 + s][1] =
+                                pack_half2(__uint_as_float(raw.y << 16), __uint_as_float(raw.y & 0xffff0000u));
+                        } else {
+                            qa[m * 4 + s][0] = 0;
+                            qa[m * 4 + s][1] = 0;
+                        }
+                    }
                 }
             }
-            __nv_bfloat162 lo = __floats2bfloat162_rn(values[0], values[1]);
-            __nv_bfloat162 hi = __floats2bfloat162_rn(values[2], values[3]);
-            uint2 packed;
-            packed.x = *reinterpret_cast<uint32_t*>(&lo);
-            packed.y = *reinterpret_cast<uint32_t*>(&hi);
-            *reinterpret_cast<uint2*>(op + d) = packed;
+            const float k_scale = key_scales ? key_scales[kv_head] : 1.0f;
+            const float score_scale = softmax_scale * k_scale * kLog2e;
+
+            float oacc[2][2][4];
+#pragma unroll
+            for (int a = 0; a < 2; ++a) {
+#pragma unroll
+                for (int b = 0; b < 2; ++b) {
+#pragma unroll
+                    for (int c = 0; c < 4; ++c) {
+                        oacc[a][b][c] = 0.0f;
+                    }
+                }
+            }
+            float running_max = -INFINITY;  // log2 domain, shared by all warps
+            float running_sum = 0.0f;       // this warp's tokens only
+
+            const int stages = (task.units + kStageUnits - 1) / kStageUnits;
+            for (int st = 0; st < stages; ++st, ++n) {
+                const int slot = n % kStages;
+                if (*reinterpret_cast<volatile int*>(&sm.failed) != 0 ||
+                    !mbar_wait_bounded(&sm.full[slot], (n / kStages) & 1, kStatusAttentionPageWait, status)) {
+                    *reinterpret_cast<volatile int*>(&sm.failed) = 1;  // acted on after the next barrier, by all
+                }
+                const int first_token = (task.unit_begin + st * kStageUnits) * kUnitTokens;
+                const int units_here = task.units - st * kStageUnits;
+
+                // ---- S = Q K^T for this warp's two column tiles (tokens 2w, 2w + 1 of each unit)
+                float acc[2][2][4];
+#pragma unroll
+                for (int a = 0; a < 2; ++a) {
+#pragma unroll
+                    for (int b = 0; b < 2; ++b) {
+#pragma unroll
+                        for (int c = 0; c < 4; ++c) {
+                            acc[a][b][c] = 0.0f;
+                        }
+                    }
+                }
+                const uint8_t* krow = &sm.k[slot][g * kUnitPitch + (2 * warp) * kHeadDim];
+#pragma unroll
+                for (int m = 0; m < 4; ++m) {
+                    const int unit = 2 * t + (m & 1) + 8 * (m >> 1);
+                    const uint4 raw0 = *reinterpret_cast<const uint4*>(krow + 16 * unit);
+                    const uint4 raw1 = *reinterpret_cast<const uint4*>(krow + kHeadDim + 16 * unit);
+                    const uint32_t words[2][4] = {{raw0.x, raw0.y, raw0.z, raw0.w}, {raw1.x, raw1.y, raw1.z, raw1.w}};
+#pragma unroll
+                    for (int s = 0; s < 4; ++s) {
+#pragma unroll
+                        for (int tile = 0; tile < 2; ++tile) {
+                            uint32_t b0, b1;
+                            cvt_e4m3x4(words[tile][s], b0, b1);
+                            mma_f16_16816(acc[tile][s & 1], qa[m * 4 + s][0], 0u, qa[m * 4 + s][1], 0u, b0, b1);
+                        }
+                    }
+                }
+                // acc[tile][.][0], [1]: head g, tokens (unit 2t, j) and (unit 2t + 1, j), j = 2w + tile
+                float sc[2][2];
+                float local_max = -INFINITY;
+#pragma unroll
+                for (int tile = 0; tile < 2; ++tile) {
+#pragma unroll
+                    for (int e = 0; e < 2; ++e) {
+                        const int token = first_token + (2 * t + e) * kUnitTokens + 2 * warp + tile;
+                        const bool valid = token < context && (2 * t + e) < units_here;
+                        sc[tile][e] = valid ? (acc[tile][0][e] + acc[tile][1][e]) * score_scale : -INFINITY;
+                        local_max = fmaxf(local_max, sc[tile][e]);
+                    }
+                }
+                local_max = fmaxf(local_max, __shfl_xor_sync(0xffffffffu, local_max, 1));
+                local_max = fmaxf(local_max, __shfl_xor_sync(0xffffffffu, local_max, 2));
+                if (t == 0) {
+                    sm.warp_max[warp][g] = local_max;
+                }
+                consumer_sync();
+                ok = *reinterpret_cast<volatile int*>(&sm.failed) == 0;
+                if (!ok) {
+                    break;  // every consumer reads the flag after the same barrier and leaves together
+                }
+
+                float new_max = running_max;
+#pragma unroll
+                for (int w = 0; w < kConsumerWarps; ++w) {
+                    new_max = fmaxf(new_max, sm.warp_max[w][g]);
+                }
+                const float rescale = new_max == -INFINITY ? 1.0f : exp2f(running_max - new_max);
+                running_max = new_max;
+                float row_sum = 0.0f;
+                uint32_t pfrag[2];
+#pragma unroll
+                for (int tile = 0; tile < 2; ++tile) {
+                    const float p0 = new_max == -INFINITY ? 0.0f : exp2f(sc[tile][0] - new_max);
+                    const float p1 = new_max == -INFINITY ? 0.0f : exp2f(sc[tile][1] - new_max);
+                    row_sum += p0 + p1;
+                    pfrag[tile] = pack_half2(p0, p1);
+                }
+                running_sum = running_sum * rescale + row_sum;
+                // PV k-step kk contracts tokens j = 2 kk and 2 kk + 1 of the eight units: this warp's two tiles.
+                sm.p[warp][lane] = make_uint2(pfrag[0], pfrag[1]);
+#pragma unroll
+                for (int a = 0; a < 2; ++a) {
+#pragma unroll
+                    for (int b = 0; b < 2; ++b) {
+                        oacc[a][b][0] *= rescale;
+                        oacc[a][b][1] *= rescale;
+                    }
+                }
+                consumer_sync();
+
+                // ---- O += P V for this warp's 32 output dims --------------------------------
+                const uint32_t v_slot = v_base + slot * kStageBytes;
+                const int matrix = lane >> 3;
+                const uint32_t v_lane = v_slot + (lane & 7) * kUnitPitch + (matrix & 1) * kHeadDim +
+                                        (2 * warp + (matrix >> 1)) * 16;
+#pragma unroll
+                for (int kk = 0; kk < kStageUnits; ++kk) {
+                    const uint2 pa = sm.p[kk][lane];
+                    uint32_t r[4];
+                    ldmatrix_x4_trans(r, v_lane + 2 * kk * kHeadDim);
+#pragma unroll
+                    for (int half = 0; half < 2; ++half) {
+                        // bytes (b0, b2 | b1, b3): low pair feeds the even dim, high pair the odd dim
+                        const uint32_t lo_tokens = __byte_perm(r[2 * half], 0, 0x3120);
+                        const uint32_t hi_tokens = __byte_perm(r[2 * half + 1], 0, 0x3120);
+                        uint32_t even0, odd0, even1, odd1;
+                        cvt_e4m3x4(lo_tokens, even0, odd0);
+                        cvt_e4m3x4(hi_tokens, even1, odd1);
+                        mma_f16_16816(oacc[half][0], pa.x, 0u, pa.y, 0u, even0, even1);
+                        mma_f16_16816(oacc[half][1], pa.x, 0u, pa.y, 0u, odd0, odd1);
+                    }
+                }
+                __syncwarp();
+                if (lane == 0) {
+                    mbar_arrive(&sm.empty[slot]);
+                }
+            }
+            if (!ok) {
+                break;
+            }
+
+            // ---- combine the warps' sums, normalise, write --------------------------------
+            running_sum += __shfl_xor_sync(0xffffffffu, running_sum, 1);
+            running_sum += __shfl_xor_sync(0xffffffffu, running_sum, 2);
+            if (t == 0) {
+                sm.warp_sum[warp][g] = running_sum;
+            }
+            consumer_sync();
+            float total = 0.0f;
+#pragma unroll
+            for (int w = 0; w < kConsumerWarps; ++w) {
+                total += sm.warp_sum[w][g];
+            }
+            consumer_sync();  // the sums are read before the next task overwrites them
+            if (g < kGqaGroup) {
+                const float v_scale = value_scales ? value_scales[kv_head] : 1.0f;
+                const float inverse = total > 0.0f ? v_scale / total : 0.0f;
+                const int head = kv_head * kGqaGroup + g;
+                const size_t pair = static_cast<size_t>(row - row_base) * kQueryHeads + head;
+                if (kSplit) {
+                    const size_t slot_index = pair * partitions + task.part;
+                    if (warp == 0 && t == 0) {
+                        float* stats = partial_stats + slot_index * kPartialFloats;
+                        stats[0] = running_max;
+                        stats[1] = total;
+                    }
+                    __half* po = partial_out + slot_index * kHeadDim;
+#pragma unroll
+                    for (int a = 0; a < 2; ++a) {
+                        const int d = 16 * (2 * warp + a) + 4 * t;
+                        const uint2 packed = make_uint2(pack_half2(oacc[a][0][0] * inverse, oacc[a][1][0] * inverse),
+                                                        pack_half2(oacc[a][0][1] * inverse, oacc[a][1][1] * inverse));
+                        *reinterpret_cast<uint2*>(po + d) = packed;
+                    }
+                } else {
+                    __nv_bfloat16* op = output + (static_cast<size_t>(row) * kQueryHeads + head) * kHeadDim;
+                    const __nv_bfloat16* gp = query_gate_projection
+                                                  ? query_gate_projection + static_cast<size_t>(row) * gate_stride +
+                                                        head * (2 * kHeadDim) + kHeadDim
+                                                  : nullptr;
+#pragma unroll
+                    for (int a = 0; a < 2; ++a) {
+                        const int d = 16 * (2 * warp + a) + 4 * t;
+                        float values[4] = {oacc[a][0][0] * inverse, oacc[a][1][0] * inverse, oacc[a][0][1] * inverse,
+                                           oacc[a][1][1] * inverse};
+                        if (gp != nullptr) {
+                            const uint2 graw = *reinterpret_cast<const uint2*>(gp + d);
+                            const float gates[4] = {__uint_as_float(graw.x << 16), __uint_as_float(graw.x & 0xffff0000u),
+                                                    __uint_as_float(graw.y << 16), __uint_as_float(graw.y & 0xffff0000u)};
+#pragma unroll
+                            for (int i = 0; i < 4; ++i) {
+                                values[i] *= 1.0f / (1.0f + __expf(-gates[i]));
+                            }
+                        }
+                        __nv_bfloat162 lo = __floats2bfloat162_rn(values[0], values[1]);
+                        __nv_bfloat162 hi = __floats2bfloat162_rn(values[2], values[3]);
+                        uint2 packed;
+                        packed.x = *reinterpret_cast<uint32_t*>(&lo);
+                        packed.y = *reinterpret_cast<uint32_t*>(&hi);
+                        *reinterpret_cast<uint2*>(op + d) = packed;
+                    }
+                }
+            }
+        }
+        if (threadIdx.x == 0) {
+            sm.consumed = n;
+        }
+    }
+    __syncthreads();
+    // After a failed wait the CTA must not return while copies it issued are still landing:
+    // one thread waits (bounded) for the stages that were put in flight and never consumed.
+    if (threadIdx.x == 0 && sm.failed != 0) {
+        for (int i = sm.consumed; i < sm.issued; ++i) {
+            mbar_wait_bounded(&sm.full[i % kStages], (i / kStages) & 1, kStatusAttentionPageWait, status);
         }
     }
 }
@@ -364,23 +532,38 @@ __global__ void __launch_bounds__(kThreads, 1) paged_attention_packed_kernel(
 // (row, head), eight dims per lane (as cuda/paged_attention.cu:1736-1823).
 __global__ void __launch_bounds__(256) reduce_partitions_kernel(
     const float* __restrict__ partial_stats, const __half* __restrict__ partial_out,
-    const __nv_bfloat16* __restrict__ query_gate_projection, __nv_bfloat16* __restrict__ output, int pairs,
-    int partitions, int row_base, int gate_stride) {
+    const __nv_bfloat16* __restrict__ query_gate_projection, const uint32_t* __restrict__ context_lengths,
+    __nv_bfloat16* __restrict__ output, int rows, int partitions, int row_base, int gate_stride, int capacity_units,
+    int plan_ctas) {
     const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
     const int lane = threadIdx.x & 31;
+    const int pairs = rows * kQueryHeads;
     if (warp >= pairs) {
         return;
     }
+    // The same plan as the attention kernel made: this row has `used` partials, the rest of its
+    // slots were never written.
+    long long total_units = 0;
+    for (int r = lane; r < rows; r += 32) {
+        total_units += units_of_context(context_lengths[row_base + r], capacity_units);
+    }
+#pragma unroll
+    for (int offset = 16; offset > 0; offset >>= 1) {
+        total_units += __shfl_xor_sync(0xffffffffu, total_units, offset);
+    }
+    const int units_per_task = plan_units_per_task(total_units, capacity_units, partitions, plan_ctas);
+    const int used = parts_of_row(
+        units_of_context(context_lengths[row_base + warp / kQueryHeads], capacity_units), units_per_task);
     const float* stats = partial_stats + static_cast<size_t>(warp) * partitions * kPartialFloats;
     float maximum = -INFINITY;
-    for (int p = 0; p < partitions; ++p) {
+    for (int p = 0; p < used; ++p) {
         if (stats[2 * p + 1] > 0.0f) {
             maximum = fmaxf(maximum, stats[2 * p]);
         }
     }
     float denominator = 0.0f;
     float acc[8] = {0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f};
-    for (int p = 0; p < partitions; ++p) {
+    for (int p = 0; p < used; ++p) {
         const float sum = stats[2 * p + 1];
         if (!(sum > 0.0f)) {
             continue;
@@ -434,7 +617,7 @@ cudaError_t launch_attention(const void* query, const void* query_gate_projectio
         return cudaErrorInvalidValue;
     }
     if (query == nullptr || key_cache == nullptr || value_cache == nullptr || block_tables == nullptr ||
-        context_lengths == nullptr || output == nullptr || rows <= 0 || rows > kMaxStepRows || row_base < 0 ||
+        context_lengths == nullptr || output == nullptr || rows <= 0 || rows > kPlanRows || row_base < 0 ||
         max_blocks <= 0 || partitions <= 0 || partitions > 65535 || !isfinite(softmax_scale) ||
         softmax_scale <= 0.0f || (page_size != 16 && page_size != 64)) {
         return cudaErrorInvalidValue;
@@ -454,14 +637,24 @@ cudaError_t launch_attention(const void* query, const void* query_gate_projectio
     if (opted_split != cudaSuccess) {
         return opted_split;
     }
-    const dim3 grid(kKvHeads, rows, partitions);
+    // One CTA per SM, whatever the batch: the task list is cut on the device.  A CTA's list holds
+    // kMaxCtaTasks entries; the plan gives it kTasksPerCta + 1 plus one per row and kv head.
+    int device = 0, sms = 0;
+    if (cudaGetDevice(&device) != cudaSuccess ||
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || sms <= 0) {
+        return cudaErrorInvalidDevice;
+    }
+    if ((rows * kKvHeads + sms - 1) / sms + kTasksPerCta + 2 > kMaxCtaTasks) {
+        return cudaErrorInvalidValue;
+    }
+    const dim3 grid(sms);
     if (partitions == 1) {
         paged_attention_packed_kernel<false><<<grid, kThreads, shared, stream>>>(
             static_cast<const __nv_bfloat16*>(query), static_cast<const __nv_bfloat16*>(query_gate_projection),
             static_cast<const uint8_t*>(key_cache), static_cast<const uint8_t*>(value_cache),
             static_cast<const uint32_t*>(block_tables), static_cast<const uint32_t*>(context_lengths), key_scales,
-            value_scales, static_cast<__nv_bfloat16*>(output), nullptr, nullptr, max_blocks, row_base, page_size,
-            gate_stride, softmax_scale, status);
+            value_scales, static_cast<__nv_bfloat16*>(output), nullptr, nullptr, rows, max_blocks, row_base,
+            page_size, gate_stride, 1, softmax_scale, status);
         return cudaGetLastError();
     }
     const size_t partials = static_cast<size_t>(rows) * kQueryHeads * partitions;
@@ -475,8 +668,8 @@ cudaError_t launch_attention(const void* query, const void* query_gate_projectio
         static_cast<const __nv_bfloat16*>(query), static_cast<const __nv_bfloat16*>(query_gate_projection),
         static_cast<const uint8_t*>(key_cache), static_cast<const uint8_t*>(value_cache),
         static_cast<const uint32_t*>(block_tables), static_cast<const uint32_t*>(context_lengths), key_scales,
-        value_scales, static_cast<__nv_bfloat16*>(output), partial_stats, partial_out, max_blocks, row_base,
-        page_size, gate_stride, softmax_scale, status);
+        value_scales, static_cast<__nv_bfloat16*>(output), partial_stats, partial_out, rows, max_blocks, row_base,
+        page_size, gate_stride, partitions, softmax_scale, status);
     const cudaError_t launched = cudaGetLastError();
     if (launched != cudaSuccess) {
         return launched;
@@ -484,7 +677,8 @@ cudaError_t launch_attention(const void* query, const void* query_gate_projectio
     const int pairs = rows * kQueryHeads;
     reduce_partitions_kernel<<<(pairs + 7) / 8, 256, 0, stream>>>(
         partial_stats, partial_out, static_cast<const __nv_bfloat16*>(query_gate_projection),
-        static_cast<__nv_bfloat16*>(output), pairs, partitions, row_base, gate_stride);
+        static_cast<const uint32_t*>(context_lengths), static_cast<__nv_bfloat16*>(output), rows, partitions, row_base,
+        gate_stride, max_blocks * (page_size / kUnitTokens), sms);
     return cudaGetLastError();
 }
 
@@ -588,8 +782,8 @@ extern "C" int qwc_paged_attention_packed_fp8_noalloc(const void* query, const v
     if (resolved != cudaSuccess) {
         return resolved;
     }
-    // Every partial slot of this call is written by the CTA that owns it (an empty partition
-    // stores sum = 0, which the merge skips), so nothing left over from an earlier call is read
+    // Every partial slot the merge reads was written by this call (the merge recomputes which of
+    // a row's slots the attention kernel used), so nothing left over from an earlier call is read
     // and nothing needs clearing first.
     return qwc::launch_attention(query, query_gate_projection, key_cache, value_cache, block_tables,
                                  context_lengths, key_scales, value_scales, output, scratch,

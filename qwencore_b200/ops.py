@@ -86,15 +86,16 @@ def packed_workspace_bytes(rows: int, partitions: int) -> int:
 
 
 def packed_partition_count(rows: int, context: int, sms: int = 148) -> int:
-    """Context partitions for decode rows: enough CTAs for two per SM, spans of >= 256 tokens.
+    """Upper bound on the context partitions of a decode row, which sizes the workspace.
 
-    Same role as packed_partition_count (crates/qwc-cuda/src/paged_attention.rs:230-253);
-    the constants are for 148 SMs and 4 KiB copy units.
+    Same role as packed_partition_count (crates/qwc-cuda/src/paged_attention.rs:230-253), with a
+    different meaning of the result: the kernel cuts the rows into tasks of equal size on the
+    device (from the sum of the contexts it finds), and `partitions` only caps how many tasks one
+    row may become.  Spans of at least 128 tokens; at most 4096 partial slots per head.
     """
     assert rows > 0 and context > 0
-    ctas = NUM_KV_HEADS * rows
-    want = max(1, (2 * sms + ctas - 1) // ctas)
-    most = max(1, (context + 255) // 256)
+    want = max(1, (context + 127) // 128)
+    most = max(8, 4096 // rows)
     return max(1, min(want, most))
 
 

@@ -99,12 +99,22 @@ def test_decode_step_matches_oracle_for_two_steps(cuda, engine_module):
             assert clear.sum() >= 2, "test inputs must exercise the argmax comparison"
             tokens = want_tokens.copy()
             if step == 0:
-                # The first DeltaNet layer sees identical inputs up to one projection: its int8 codes
-                # agree to within one step on a fraction of a percent of the elements.
+                # The first DeltaNet layer sees identical inputs up to one projection, whose bf16
+                # outputs sit one grid step from the oracle's in a few elements per ten thousand.
+                # Such a step in a large element of v (0.5 at magnitude 64) moves that element's
+                # whole state row by several int8 codes, so: nearly every code within one step, the
+                # rest confined to a handful of rows, and the stored values equal by RMS.
                 used = sorted(set(layout["state_slots"].tolist()))
                 got = engine.read("state", 0, np.int8).reshape(model.layers[0]["state"].shape)
                 diff = np.abs(got.astype(np.int32) - model.layers[0]["state"].astype(np.int32))[used]
-                assert diff.max() <= 1 and np.mean(diff > 0) < 0.01
+                assert np.mean(diff > 0) < 0.01 and np.mean(diff > 1) < 2e-4
+                assert (diff.max(axis=-1) > 1).sum() <= 8, "more than a handful of state rows moved"
+                scales = engine.read("state_scales", 0, np.float32).reshape(model.layers[0]["state_scales"].shape)
+                got_values = got[used].astype(np.float32) * scales[used][..., None]
+                want_values = (model.layers[0]["state"][used].astype(np.float32) *
+                               model.layers[0]["state_scales"][used][..., None])
+                value_rms = np.sqrt(np.mean(want_values.astype(np.float64) ** 2))
+                assert np.sqrt(np.mean((got_values - want_values).astype(np.float64) ** 2)) <= 1e-2 * value_rms
 
         # recurrent state and KV pages after two steps
         for index, layer in enumerate(model.layers):
