@@ -163,6 +163,19 @@ __device__ __forceinline__ void bulk_wait_all() {
 }
 
 // Make generic-proxy shared-memory writes visible to the async proxy (bulk stores).
+// Programmatic dependent launch.  A kernel launched with the programmatic-serialization attribute
+// may start while its predecessor in the stream still runs; it must not touch anything the
+// predecessor writes before pdl_wait() returns (which is when the predecessor has completed and
+// its writes are visible).  pdl_launch_dependents() in the predecessor lets that early start happen
+// as soon as every one of its CTAs has issued it.  Both are no-ops in a plain launch.
+__device__ __forceinline__ void pdl_wait() {
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+
+__device__ __forceinline__ void pdl_launch_dependents() {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
 __device__ __forceinline__ void fence_proxy_async() {
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
 }

@@ -118,6 +118,7 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) nvfp4_gemv_kernel(const Gem
     const int t = lane & 3;
     const int threads = blockDim.x;
 
+    pdl_launch_dependents();
     const int row_group = blockIdx.x / p.splits;
     const int split = blockIdx.x - row_group * p.splits;
     const int tile = row_group * p.tiles_per_cta + warp;
@@ -372,6 +373,8 @@ __global__ void __launch_bounds__(kMaxWarps * 32, 1) nvfp4_gemv_kernel(const Gem
             }
         }
     }
+    // The weight copies above start before the kernel that produces the activations has finished.
+    pdl_wait();
     if (num_xstages > 0) {
         stage_issue(0);
         stage_commit(0);
@@ -609,13 +612,15 @@ cudaError_t launch(const GemvParams& base, cudaStream_t stream) {
     config.blockDim = dim3(plan.tiles_per_cta * 32);
     config.dynamicSmemBytes = smem_bytes;
     config.stream = stream;
-    cudaLaunchAttribute attribute[1];
-    attribute[0].id = cudaLaunchAttributeClusterDimension;
-    attribute[0].val.clusterDim.x = plan.splits;
-    attribute[0].val.clusterDim.y = 1;
-    attribute[0].val.clusterDim.z = 1;
+    cudaLaunchAttribute attribute[2];
+    attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attribute[0].val.programmaticStreamSerializationAllowed = 1;
+    attribute[1].id = cudaLaunchAttributeClusterDimension;
+    attribute[1].val.clusterDim.x = plan.splits;
+    attribute[1].val.clusterDim.y = 1;
+    attribute[1].val.clusterDim.z = 1;
     config.attrs = attribute;
-    config.numAttrs = plan.splits > 1 ? 1 : 0;
+    config.numAttrs = plan.splits > 1 ? 2 : 1;
     return cudaLaunchKernelEx(&config, nvfp4_gemv_kernel<NT, MT, MODE>, p);
 }
 

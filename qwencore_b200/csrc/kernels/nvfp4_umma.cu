@@ -200,6 +200,7 @@ __global__ void __launch_bounds__(kThreads, 1)
     // 128-byte-swizzled boxes need a 1 KiB-aligned shared address.
     unsigned char* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
 
+    pdl_launch_dependents();
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
     const int row_group = blockIdx.x / p.splits;
@@ -504,6 +505,9 @@ __global__ void __launch_bounds__(kThreads, 1)
         };
         static_assert(kConvertWarps % kStageChunks == 0 && kRawBuffers == 2, "fetch bookkeeping");
         bool ok = true;
+        // Weights, scales and the whole pipeline above start before the kernel that produces the
+        // activations has finished; only these loads wait for it.
+        pdl_wait();
         fetch();
         fetch();
         int buffer = 0;
@@ -744,13 +748,15 @@ cudaError_t launch_nvfp4_umma(const void* packed0, const void* scales0, const vo
     config.blockDim = dim3(kThreads);
     config.dynamicSmemBytes = smem_bytes;
     config.stream = stream;
-    cudaLaunchAttribute attribute[1];
-    attribute[0].id = cudaLaunchAttributeClusterDimension;
-    attribute[0].val.clusterDim.x = splits;
-    attribute[0].val.clusterDim.y = 1;
-    attribute[0].val.clusterDim.z = 1;
+    cudaLaunchAttribute attribute[2];
+    attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attribute[0].val.programmaticStreamSerializationAllowed = 1;
+    attribute[1].id = cudaLaunchAttributeClusterDimension;
+    attribute[1].val.clusterDim.x = splits;
+    attribute[1].val.clusterDim.y = 1;
+    attribute[1].val.clusterDim.z = 1;
     config.attrs = attribute;
-    config.numAttrs = splits > 1 ? 1 : 0;
+    config.numAttrs = splits > 1 ? 2 : 1;
     return cudaLaunchKernelEx(&config, nvfp4_umma_kernel, map0, map1, p);
 }
 

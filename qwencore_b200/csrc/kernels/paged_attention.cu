@@ -146,6 +146,7 @@ __global__ void __launch_bounds__(kThreads, 1) paged_attention_packed_kernel(
     extern __shared__ __align__(128) unsigned char smem_raw[];
     Smem& sm = *reinterpret_cast<Smem*>(smem_raw);
 
+    pdl_launch_dependents();
     if (status_is_set(status)) {
         return;
     }
@@ -535,6 +536,7 @@ __global__ void __launch_bounds__(256) reduce_partitions_kernel(
     const __nv_bfloat16* __restrict__ query_gate_projection, const uint32_t* __restrict__ context_lengths,
     __nv_bfloat16* __restrict__ output, int rows, int partitions, int row_base, int gate_stride, int capacity_units,
     int plan_ctas) {
+    pdl_launch_dependents();  // the output projection may start streaming its weights
     const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
     const int lane = threadIdx.x & 31;
     const int pairs = rows * kQueryHeads;

@@ -70,6 +70,7 @@ __global__ void __launch_bounds__(kThreads) rmsnorm_bf16_kernel(const __nv_bfloa
                                                                 const __nv_bfloat16* __restrict__ weight,
                                                                 __nv_bfloat16* __restrict__ output, int hidden,
                                                                 float epsilon) {
+    pdl_launch_dependents();  // the projection that follows may start streaming its weights
     __shared__ float scratch[kThreads / 32];
     const size_t base = static_cast<size_t>(blockIdx.x) * hidden;
     const int vectors = hidden / 8;
@@ -220,6 +221,7 @@ __global__ void __launch_bounds__(kDeltaHeadDim) gated_rmsnorm_kernel(const floa
                                                                       const __nv_bfloat16* __restrict__ weight,
                                                                       __nv_bfloat16* __restrict__ output,
                                                                       float epsilon, int gate_stride, int heads) {
+    pdl_launch_dependents();  // the projection that follows may start streaming its weights
     __shared__ float scratch[kDeltaHeadDim / 32];
     const int head = blockIdx.x;
     const int batch = blockIdx.y;
