@@ -55,6 +55,8 @@ __global__ void __launch_bounds__(kThreads) page_table_apply_kernel(uint32_t* __
                                                                     uint32_t* __restrict__ seq_blocks,
                                                                     const qwc_table_edit* __restrict__ edits,
                                                                     int count, int capacity, int max_blocks) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= count) {
         return;
@@ -81,6 +83,8 @@ __global__ void __launch_bounds__(kThreads) pack_rows_kernel(
     const uint32_t* __restrict__ seq_blocks, uint32_t* __restrict__ physical_blocks,
     uint32_t* __restrict__ block_offsets, uint32_t* __restrict__ block_table_offsets, uint32_t* __restrict__ status,
     int rows, int capacity, int max_blocks, int page_size, int max_positions) {
+    pdl_launch_dependents();
+    pdl_wait();
     __shared__ uint32_t warp_totals[kThreads / 32];
     __shared__ uint32_t carry;
     __shared__ uint32_t error;
@@ -194,6 +198,8 @@ __global__ void __launch_bounds__(kThreads) pack_tables_kernel(
     const uint32_t* __restrict__ block_table_offsets, const __nv_bfloat16* __restrict__ rope_table,
     uint32_t* __restrict__ block_tables, uint32_t* __restrict__ block_ids, __nv_bfloat16* __restrict__ cosine,
     __nv_bfloat16* __restrict__ sine, int max_blocks, int page_size, int max_positions) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int row = blockIdx.x;
     const uint32_t slot = state_slots[row];
     const uint32_t context = context_lengths[row];
@@ -232,9 +238,8 @@ extern "C" int qwc_page_table_apply(uint32_t* seq_tokens, uint32_t* seq_blocks, 
     if (count == 0) {
         return cudaSuccess;
     }
-    page_table_apply_kernel<<<(count + kThreads - 1) / kThreads, kThreads, 0, stream>>>(
+    return qwc::launch_chained(page_table_apply_kernel, dim3((count + kThreads - 1) / kThreads), dim3(kThreads), 0, stream, 
         seq_tokens, seq_blocks, edits, count, capacity, max_blocks);
-    return cudaGetLastError();
 }
 
 extern "C" int qwc_pack_decode_batch(const uint32_t* row_slots, const uint8_t* slot_active,
@@ -259,18 +264,16 @@ extern "C" int qwc_pack_decode_batch(const uint32_t* row_slots, const uint8_t* s
     if (seen_bytes > 40 * 1024) {
         return cudaErrorInvalidValue;
     }
-    pack_rows_kernel<<<1, kThreads, seen_bytes, stream>>>(
+    cudaError_t launched = qwc::launch_chained(pack_rows_kernel, dim3(1), dim3(kThreads), seen_bytes, stream, 
         row_slots, slot_active, seq_tokens, row_count, state_slots, positions, context_lengths, seq_blocks,
         physical_blocks, block_offsets, block_table_offsets, status, rows, capacity, max_blocks, page_size,
         max_positions > 0 ? max_positions : 0x7fffffff);
-    cudaError_t launched = cudaGetLastError();
     if (launched != cudaSuccess) {
         return launched;
     }
-    pack_tables_kernel<<<rows, kThreads, 0, stream>>>(
+    return qwc::launch_chained(pack_tables_kernel, dim3(rows), dim3(kThreads), 0, stream, 
         state_slots, positions, context_lengths, seq_blocks, block_table_offsets,
         static_cast<const __nv_bfloat16*>(rope_table), block_tables, block_ids,
         static_cast<__nv_bfloat16*>(cosine), static_cast<__nv_bfloat16*>(sine), max_blocks, page_size,
         max_positions > 0 ? max_positions : 0x7fffffff);
-    return cudaGetLastError();
 }

@@ -176,6 +176,25 @@ __device__ __forceinline__ void pdl_launch_dependents() {
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 }
 
+// Host side of the same: a launch that may begin before its predecessor in the stream has ended.
+// Every kernel launched this way calls pdl_wait() before it reads or writes anything that an
+// earlier kernel of the step touches (weights are never written during a step).
+template <typename... Params, typename... Args>
+cudaError_t launch_chained(void (*kernel)(Params...), dim3 grid, dim3 block, size_t shared_bytes, cudaStream_t stream,
+                           Args&&... args) {
+    cudaLaunchConfig_t config = {};
+    config.gridDim = grid;
+    config.blockDim = block;
+    config.dynamicSmemBytes = shared_bytes;
+    config.stream = stream;
+    cudaLaunchAttribute attribute[1];
+    attribute[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attribute[0].val.programmaticStreamSerializationAllowed = 1;
+    config.attrs = attribute;
+    config.numAttrs = 1;
+    return cudaLaunchKernelEx(&config, kernel, static_cast<Params>(args)...);
+}
+
 __device__ __forceinline__ void fence_proxy_async() {
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
 }

@@ -39,6 +39,8 @@ __global__ void __launch_bounds__(kThreads, 4) delta_decode_int8_kernel(
     const float* __restrict__ q, const float* __restrict__ k, const float* __restrict__ v,
     const float* __restrict__ alpha, const float* __restrict__ beta, const float* __restrict__ kq,
     float* __restrict__ out, int v_heads, int* status) {
+    pdl_launch_dependents();
+    pdl_wait();
     __shared__ __align__(128) uint8_t tile[kDim * kDim];
     __shared__ __align__(16) float row_scale[kDim];
     __shared__ float out_rows[kDim];
@@ -242,10 +244,9 @@ extern "C" int qwc_delta_decode_int8(void* state, float* state_scales, const voi
         return cudaErrorInvalidValue;
     }
     const dim3 grid(v_heads, batch, qwc::splits_for(batch, v_heads));
-    qwc::delta_decode_int8_kernel<<<grid, qwc::kThreads, 0, stream>>>(
+    return qwc::launch_chained(qwc::delta_decode_int8_kernel, dim3(grid), dim3(qwc::kThreads), 0, stream, 
         static_cast<int8_t*>(state), state_scales, static_cast<const uint32_t*>(state_slots),
         static_cast<const float*>(q), static_cast<const float*>(k), static_cast<const float*>(v),
         static_cast<const float*>(alpha), static_cast<const float*>(beta), static_cast<const float*>(kq),
         static_cast<float*>(out), v_heads, status);
-    return cudaGetLastError();
 }

@@ -163,6 +163,7 @@ __global__ void __launch_bounds__(kThreads, 1) paged_attention_packed_kernel(
     for (int i = threadIdx.x; i < kStages * kStageBytes / 16; i += kThreads) {
         reinterpret_cast<uint4*>(&sm.v[0][0])[i] = make_uint4(0, 0, 0, 0);
     }
+    pdl_wait();  // context lengths, tables, query and the cache rows of this step come from earlier kernels
     if (warp == 0) {
         long long total_units = 0;
         for (int r = lane; r < rows; r += 32) {
@@ -537,6 +538,7 @@ __global__ void __launch_bounds__(256) reduce_partitions_kernel(
     __nv_bfloat16* __restrict__ output, int rows, int partitions, int row_base, int gate_stride, int capacity_units,
     int plan_ctas) {
     pdl_launch_dependents();  // the output projection may start streaming its weights
+    pdl_wait();
     const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
     const int lane = threadIdx.x & 31;
     const int pairs = rows * kQueryHeads;
@@ -557,29 +559,55 @@ __global__ void __launch_bounds__(256) reduce_partitions_kernel(
     const int used = parts_of_row(
         units_of_context(context_lengths[row_base + warp / kQueryHeads], capacity_units), units_per_task);
     const float* stats = partial_stats + static_cast<size_t>(warp) * partitions * kPartialFloats;
+    // Lanes take the partials' statistics side by side (32 per round); the partial outputs are then
+    // read four at a time so that their latencies overlap.  The order of the additions is fixed.
     float maximum = -INFINITY;
-    for (int p = 0; p < used; ++p) {
-        if (stats[2 * p + 1] > 0.0f) {
-            maximum = fmaxf(maximum, stats[2 * p]);
+    for (int p = lane; p < used; p += 32) {
+        const float2 pair_stats = *reinterpret_cast<const float2*>(stats + 2 * p);
+        if (pair_stats.y > 0.0f) {
+            maximum = fmaxf(maximum, pair_stats.x);
         }
+    }
+#pragma unroll
+    for (int offset = 16; offset > 0; offset >>= 1) {
+        maximum = fmaxf(maximum, __shfl_xor_sync(0xffffffffu, maximum, offset));
     }
     float denominator = 0.0f;
     float acc[8] = {0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f};
-    for (int p = 0; p < used; ++p) {
-        const float sum = stats[2 * p + 1];
-        if (!(sum > 0.0f)) {
-            continue;
+    const __half* outs = partial_out + static_cast<size_t>(warp) * partitions * kHeadDim + 8 * lane;
+    for (int base = 0; base < used; base += 32) {
+        const int mine = base + lane;
+        float my_weight = 0.0f;
+        if (mine < used) {
+            const float2 pair_stats = *reinterpret_cast<const float2*>(stats + 2 * mine);
+            my_weight = pair_stats.y > 0.0f ? pair_stats.y * exp2f(pair_stats.x - maximum) : 0.0f;
         }
-        const float weight = sum * exp2f(stats[2 * p] - maximum);
-        denominator += weight;
-        const uint4 raw =
-            *reinterpret_cast<const uint4*>(partial_out + (static_cast<size_t>(warp) * partitions + p) * kHeadDim + 8 * lane);
-        const __half2* h = reinterpret_cast<const __half2*>(&raw);
+        const int count = min(32, used - base);
+        for (int first = 0; first < count; first += 4) {
+            uint4 raw[4];
+            float weight[4];
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            const float2 f = __half22float2(h[i]);
-            acc[2 * i] += weight * f.x;
-            acc[2 * i + 1] += weight * f.y;
+            for (int j = 0; j < 4; ++j) {
+                const int q = first + j;
+                weight[j] = __shfl_sync(0xffffffffu, my_weight, q & 31);
+                raw[j] = make_uint4(0, 0, 0, 0);
+                if (q < count) {
+                    raw[j] = *reinterpret_cast<const uint4*>(outs + static_cast<size_t>(base + q) * kHeadDim);
+                } else {
+                    weight[j] = 0.0f;
+                }
+            }
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                denominator += weight[j];
+                const __half2* h = reinterpret_cast<const __half2*>(&raw[j]);
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const float2 f = __half22float2(h[i]);
+                    acc[2 * i] += weight[j] * f.x;
+                    acc[2 * i + 1] += weight[j] * f.y;
+                }
+            }
         }
     }
     const float inverse = denominator > 0.0f ? 1.0f / denominator : 0.0f;
@@ -651,13 +679,12 @@ cudaError_t launch_attention(const void* query, const void* query_gate_projectio
     }
     const dim3 grid(sms);
     if (partitions == 1) {
-        paged_attention_packed_kernel<false><<<grid, kThreads, shared, stream>>>(
+        return qwc::launch_chained(paged_attention_packed_kernel<false>, dim3(grid), dim3(kThreads), shared, stream, 
             static_cast<const __nv_bfloat16*>(query), static_cast<const __nv_bfloat16*>(query_gate_projection),
             static_cast<const uint8_t*>(key_cache), static_cast<const uint8_t*>(value_cache),
             static_cast<const uint32_t*>(block_tables), static_cast<const uint32_t*>(context_lengths), key_scales,
             value_scales, static_cast<__nv_bfloat16*>(output), nullptr, nullptr, rows, max_blocks, row_base,
             page_size, gate_stride, 1, softmax_scale, status);
-        return cudaGetLastError();
     }
     const size_t partials = static_cast<size_t>(rows) * kQueryHeads * partitions;
     if (workspace == nullptr || workspace_bytes < partials * kPartialBytes) {
@@ -666,22 +693,20 @@ cudaError_t launch_attention(const void* query, const void* query_gate_projectio
     // partials is a multiple of 24, so the f16 block starts on a 16-byte boundary.
     float* partial_stats = static_cast<float*>(workspace);
     __half* partial_out = reinterpret_cast<__half*>(partial_stats + partials * kPartialFloats);
-    paged_attention_packed_kernel<true><<<grid, kThreads, shared, stream>>>(
+    const cudaError_t launched = qwc::launch_chained(paged_attention_packed_kernel<true>, dim3(grid), dim3(kThreads), shared, stream, 
         static_cast<const __nv_bfloat16*>(query), static_cast<const __nv_bfloat16*>(query_gate_projection),
         static_cast<const uint8_t*>(key_cache), static_cast<const uint8_t*>(value_cache),
         static_cast<const uint32_t*>(block_tables), static_cast<const uint32_t*>(context_lengths), key_scales,
         value_scales, static_cast<__nv_bfloat16*>(output), partial_stats, partial_out, rows, max_blocks, row_base,
         page_size, gate_stride, partitions, softmax_scale, status);
-    const cudaError_t launched = cudaGetLastError();
     if (launched != cudaSuccess) {
         return launched;
     }
     const int pairs = rows * kQueryHeads;
-    reduce_partitions_kernel<<<(pairs + 7) / 8, 256, 0, stream>>>(
+    return qwc::launch_chained(reduce_partitions_kernel, dim3((pairs + 7) / 8), dim3(256), 0, stream, 
         partial_stats, partial_out, static_cast<const __nv_bfloat16*>(query_gate_projection),
         static_cast<const uint32_t*>(context_lengths), static_cast<__nv_bfloat16*>(output), rows, partitions, row_base,
         gate_stride, max_blocks * (page_size / kUnitTokens), sms);
-    return cudaGetLastError();
 }
 
 // ---- built-in scratch for callers that cannot allocate ------------------------------------

@@ -50,6 +50,8 @@ __device__ __forceinline__ float block_sum(float value, float* scratch) {
 __global__ void embedding_gather_kernel(const uint8_t* __restrict__ table, const float* __restrict__ row_scales,
                                         const uint32_t* __restrict__ token_ids, __nv_bfloat16* __restrict__ output,
                                         int cols, int vocab) {
+    pdl_launch_dependents();
+    pdl_wait();
     const uint32_t token = token_ids[blockIdx.x];
     const size_t output_base = static_cast<size_t>(blockIdx.x) * cols;
     const bool valid = token < static_cast<uint32_t>(vocab);
@@ -71,6 +73,7 @@ __global__ void __launch_bounds__(kThreads) rmsnorm_bf16_kernel(const __nv_bfloa
                                                                 __nv_bfloat16* __restrict__ output, int hidden,
                                                                 float epsilon) {
     pdl_launch_dependents();  // the projection that follows may start streaming its weights
+    pdl_wait();
     __shared__ float scratch[kThreads / 32];
     const size_t base = static_cast<size_t>(blockIdx.x) * hidden;
     const int vectors = hidden / 8;
@@ -167,6 +170,8 @@ __global__ void __launch_bounds__(kDeltaHeadDim) delta_prepare_kernel(
     float* __restrict__ conv_state, const uint32_t* __restrict__ state_slots, float* __restrict__ query,
     float* __restrict__ key, float* __restrict__ value, float* __restrict__ alpha, float* __restrict__ beta,
     float* __restrict__ kq, int mixed_stride, int gate_stride, int v_heads) {
+    pdl_launch_dependents();
+    pdl_wait();
     __shared__ float scratch[kDeltaHeadDim / 32];
     const int head = blockIdx.x;
     const int batch = blockIdx.y;
@@ -222,6 +227,7 @@ __global__ void __launch_bounds__(kDeltaHeadDim) gated_rmsnorm_kernel(const floa
                                                                       __nv_bfloat16* __restrict__ output,
                                                                       float epsilon, int gate_stride, int heads) {
     pdl_launch_dependents();  // the projection that follows may start streaming its weights
+    pdl_wait();
     __shared__ float scratch[kDeltaHeadDim / 32];
     const int head = blockIdx.x;
     const int batch = blockIdx.y;
@@ -250,6 +256,8 @@ __global__ void __launch_bounds__(kHeadDim) prepare_attention_kernel(
     const float* __restrict__ value_scales, __nv_bfloat16* __restrict__ query, uint8_t* __restrict__ key_cache,
     uint8_t* __restrict__ value_cache, int page_size, int query_stride, int key_stride, int value_stride,
     float epsilon) {
+    pdl_launch_dependents();
+    pdl_wait();
     __shared__ float scratch[kHeadDim / 32];
     __shared__ __nv_bfloat16 normalized[kHeadDim];
     const int batch = blockIdx.y;
@@ -330,6 +338,8 @@ __device__ void reduce_candidate(float& value, uint32_t& index, float* shared_va
 __global__ void __launch_bounds__(kThreads) argmax_parts_kernel(const float* __restrict__ logits,
                                                                 float* __restrict__ partial_values,
                                                                 uint32_t* __restrict__ partial_indices, int vocab) {
+    pdl_launch_dependents();
+    pdl_wait();
     __shared__ float shared_values[kThreads / 32];
     __shared__ uint32_t shared_indices[kThreads / 32];
     const int batch = blockIdx.y;
@@ -354,6 +364,8 @@ __global__ void __launch_bounds__(kThreads) argmax_parts_kernel(const float* __r
 __global__ void __launch_bounds__(kThreads) argmax_reduce_kernel(const float* __restrict__ partial_values,
                                                                  const uint32_t* __restrict__ partial_indices,
                                                                  uint32_t* __restrict__ output, int parts) {
+    pdl_launch_dependents();
+    pdl_wait();
     __shared__ float shared_values[kThreads / 32];
     __shared__ uint32_t shared_indices[kThreads / 32];
     const int batch = blockIdx.x;
@@ -387,10 +399,9 @@ extern "C" int qwc_fp8_embedding_gather(const void* table, const void* row_scale
         cols <= 0 || vocab <= 0) {
         return cudaErrorInvalidValue;
     }
-    embedding_gather_kernel<<<batch, kThreads, 0, stream>>>(
+    return qwc::launch_chained(embedding_gather_kernel, dim3(batch), dim3(kThreads), 0, stream, 
         static_cast<const uint8_t*>(table), static_cast<const float*>(row_scales),
         static_cast<const uint32_t*>(token_ids), static_cast<__nv_bfloat16*>(output), cols, vocab);
-    return cudaGetLastError();
 }
 
 extern "C" int qwc_rmsnorm_bf16(const void* input, void* residual, const void* weight, void* output, int batch,
@@ -400,10 +411,9 @@ extern "C" int qwc_rmsnorm_bf16(const void* input, void* residual, const void* w
         epsilon <= 0.0f) {
         return cudaErrorInvalidValue;
     }
-    rmsnorm_bf16_kernel<<<batch, kThreads, 0, stream>>>(
+    return qwc::launch_chained(rmsnorm_bf16_kernel, dim3(batch), dim3(kThreads), 0, stream, 
         static_cast<const __nv_bfloat16*>(input), static_cast<__nv_bfloat16*>(residual),
         static_cast<const __nv_bfloat16*>(weight), static_cast<__nv_bfloat16*>(output), hidden, epsilon);
-    return cudaGetLastError();
 }
 
 extern "C" int qwc_delta_prepare_decode(const void* mixed_qkv, const void* a_projection, const void* b_projection,
@@ -421,14 +431,13 @@ extern "C" int qwc_delta_prepare_decode(const void* mixed_qkv, const void* a_pro
         return cudaErrorInvalidValue;
     }
     const dim3 grid(kDeltaKeyHeads, batch);
-    delta_prepare_kernel<<<grid, kDeltaHeadDim, 0, stream>>>(
+    return qwc::launch_chained(delta_prepare_kernel, dim3(grid), dim3(kDeltaHeadDim), 0, stream, 
         static_cast<const __nv_bfloat16*>(mixed_qkv), static_cast<const __nv_bfloat16*>(a_projection),
         static_cast<const __nv_bfloat16*>(b_projection), static_cast<const __nv_bfloat16*>(conv_weight),
         static_cast<const __nv_bfloat16*>(a_log), static_cast<const __nv_bfloat16*>(dt_bias),
         static_cast<float*>(conv_state), static_cast<const uint32_t*>(state_slots), static_cast<float*>(query),
         static_cast<float*>(key), static_cast<float*>(value), static_cast<float*>(alpha),
         static_cast<float*>(beta), static_cast<float*>(kq), mixed_stride, gate_stride, v_heads);
-    return cudaGetLastError();
 }
 
 extern "C" int qwc_delta_gated_rmsnorm(const float* input, const void* gate, const void* weight, void* output,
@@ -439,10 +448,9 @@ extern "C" int qwc_delta_gated_rmsnorm(const float* input, const void* gate, con
         return cudaErrorInvalidValue;
     }
     const dim3 grid(heads, batch);
-    gated_rmsnorm_kernel<<<grid, kDeltaHeadDim, 0, stream>>>(
+    return qwc::launch_chained(gated_rmsnorm_kernel, dim3(grid), dim3(kDeltaHeadDim), 0, stream, 
         input, static_cast<const __nv_bfloat16*>(gate), static_cast<const __nv_bfloat16*>(weight),
         static_cast<__nv_bfloat16*>(output), epsilon, gate_stride, heads);
-    return cudaGetLastError();
 }
 
 extern "C" int qwc_prepare_attention_decode_fp8_scaled(
@@ -460,7 +468,7 @@ extern "C" int qwc_prepare_attention_decode_fp8_scaled(
         return cudaErrorInvalidValue;
     }
     const dim3 grid(kQueryHeads + kKvHeads, batch);
-    prepare_attention_kernel<<<grid, kHeadDim, 0, stream>>>(
+    return qwc::launch_chained(prepare_attention_kernel, dim3(grid), dim3(kHeadDim), 0, stream, 
         static_cast<const __nv_bfloat16*>(query_gate_projection), static_cast<const __nv_bfloat16*>(key_projection),
         static_cast<const __nv_bfloat16*>(value_projection), static_cast<const __nv_bfloat16*>(query_norm_weight),
         static_cast<const __nv_bfloat16*>(key_norm_weight), static_cast<const __nv_bfloat16*>(cosine),
@@ -468,7 +476,6 @@ extern "C" int qwc_prepare_attention_decode_fp8_scaled(
         static_cast<const uint32_t*>(block_offsets), key_scales, value_scales, static_cast<__nv_bfloat16*>(query),
         static_cast<uint8_t*>(key_cache), static_cast<uint8_t*>(value_cache), page_size, query_stride, key_stride,
         value_stride, epsilon);
-    return cudaGetLastError();
 }
 
 extern "C" int qwc_prepare_attention_decode_fp8(const void* query_gate_projection, const void* key_projection,
@@ -509,11 +516,9 @@ extern "C" int qwc_argmax(const float* logits, float* partial_values, uint32_t* 
         return cudaErrorInvalidValue;
     }
     const dim3 grid(parts, batch);
-    argmax_parts_kernel<<<grid, kThreads, 0, stream>>>(logits, partial_values, partial_indices, vocab);
-    const cudaError_t launched = cudaGetLastError();
+    const cudaError_t launched = qwc::launch_chained(argmax_parts_kernel, dim3(grid), dim3(kThreads), 0, stream, logits, partial_values, partial_indices, vocab);
     if (launched != cudaSuccess) {
         return launched;
     }
-    argmax_reduce_kernel<<<batch, kThreads, 0, stream>>>(partial_values, partial_indices, output, parts);
-    return cudaGetLastError();
+    return qwc::launch_chained(argmax_reduce_kernel, dim3(batch), dim3(kThreads), 0, stream, partial_values, partial_indices, output, parts);
 }
