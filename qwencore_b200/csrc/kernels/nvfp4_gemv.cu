@@ -635,7 +635,9 @@ cudaError_t dispatch(const GemvParams& p, cudaStream_t stream) {
     if (MODE == kFp8Rows ? p.batch <= 8 : (p.batch <= 8 && !large)) {
         return launch<1, 1, MODE>(p, stream);
     }
-    if (MODE != kFp8Rows) {
+    // its stores are 16 bytes wide
+    const bool vector_stores = p.out_features % 8 == 0 && (reinterpret_cast<uintptr_t>(p.y) & 15) == 0;
+    if (MODE != kFp8Rows && vector_stores) {
         // Above eight rows the legacy tensor path cannot keep up with the weight stream.
         return launch_nvfp4_umma(p.packed[0], p.scales[0], p.packed[1], p.scales[1], p.x, p.y, p.out_features,
                                  p.in_features, p.batch, p.inverse_scale[0], p.inverse_scale[1],

@@ -96,6 +96,7 @@ struct Barriers {
     uint64_t x_full[kXStages];
     uint64_t x_free[kXStages];
     uint64_t d_ready;
+    uint64_t tmem_ready;
     uint32_t tmem_base;
     int failed;
 };
@@ -248,21 +249,33 @@ __global__ void __launch_bounds__(kThreads, 1)
             mbar_init(&bars.x_free[s], kMmaWarps);
         }
         mbar_init(&bars.d_ready, kMmaWarps);
+        mbar_init(&bars.tmem_ready, 1);
         bars.failed = status_is_set(p.status) ? 1 : 0;
         bars.tmem_base = 0;
         mbar_fence_init();
     }
     __syncthreads();
+    // Tensor memory is allocated while the producer already fetches weights and the converting warps
+    // activations; the warps that use it wait for the address below.
+    uint32_t tmem_base = 0;
     if (warp == kMmaWarp) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&bars.tmem_base)),
                      "r"(kTmemColumns)
                      : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+        __syncwarp();
+        if (lane == 0) {
+            mbar_arrive(&bars.tmem_ready);
+        }
     }
-    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-    __syncthreads();
-    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    const uint32_t tmem_base = bars.tmem_base;
+    bool tmem_ok = true;
+    if (warp < kFirstConvertWarp && warp != kProducerWarp) {
+        tmem_ok = wait_or_fail(&bars.tmem_ready, 0, &bars, p.status);
+        tmem_ok = __all_sync(0xffffffffu, tmem_ok);
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        tmem_base = *reinterpret_cast<volatile uint32_t*>(&bars.tmem_base);
+    }
 
     float result[32];
     bool have_result = false;
@@ -277,7 +290,7 @@ __global__ void __launch_bounds__(kThreads, 1)
         const int row_offset = local_row * kBoxRowBytes;
         const int row_swizzle = local_row & 7;
         const int scale_offset = (local_row & 31) * 16 + (local_row >> 5) * 4;
-        bool ok = true;
+        bool ok = tmem_ok;
         int previous_buf = -1;
         int previous_slot = -1;  // >= 0: the previous chunk was the last reader of that ring slot
         // Hands a finished chunk to the tensor-core warp and its ring slot back to the producer.
@@ -422,7 +435,7 @@ __global__ void __launch_bounds__(kThreads, 1)
         const uint64_t desc_stage = static_cast<uint64_t>(x_stage_bytes >> 4);
         const uint32_t a_tile = tmem_base + t * kTileColumns;
         const uint32_t d_tile = a_tile + kAccumulatorColumn;
-        bool ok = true;
+        bool ok = tmem_ok;
         int buf = 0, xs = 0;
         uint32_t a_parity = 0, x_parity = 0;
         for (int c = 0; c < total_chunks && ok; ++c) {
@@ -544,64 +557,69 @@ __global__ void __launch_bounds__(kThreads, 1)
     }
 
     // ---------------- split-K reduction, epilogue ----------------
+    // Every CTA of the cluster parks its accumulators in its own shared memory ([token][row], fp32;
+    // the weight ring is idle now).  Then the tokens are dealt out: CTA s sums, over all slices and in
+    // slice order, the tokens s, s + splits, ... and stores them, eight consecutive rows (16 bytes of
+    // bf16) per thread.  One CTA reading every peer for all tokens takes several microseconds.
     __syncthreads();
     const bool failed = *reinterpret_cast<volatile int*>(&bars.failed) != 0;
-    if (p.splits > 1) {
-        cg::cluster_group cluster = cg::this_cluster();
-        float* reduce = reinterpret_cast<float*>(smem);  // [32][256] floats: the weight ring is idle now
-        if (split != 0 && have_result) {
+    cg::cluster_group cluster = cg::this_cluster();
+    float* parked = reinterpret_cast<float*>(smem);  // [32][256]
+    constexpr int kParkedRows = kRowWarps * 32;
+    if (have_result) {
 #pragma unroll
-            for (int i = 0; i < 32; ++i) {
-                reduce[i * (kRowWarps * 32) + threadIdx.x] = result[i];
-            }
+        for (int i = 0; i < 32; ++i) {
+            parked[i * kParkedRows + threadIdx.x] = result[i];
         }
-        cluster.sync();
-        if (split == 0 && have_result) {
-            for (int r = 1; r < p.splits; ++r) {
-                const float* peer = cluster.map_shared_rank(reduce, r);
-#pragma unroll
-                for (int i = 0; i < 32; ++i) {
-                    result[i] += peer[i * (kRowWarps * 32) + threadIdx.x];
-                }
-            }
-        }
-        cluster.sync();
     }
-
-    if (!failed && have_result && split == 0) {
-        const int tile = warp >> 2;
-        const int local_row = (warp & 3) * 32 + lane;
-        const int row = (p.swiglu ? row_group * kTileRows : (row_group * kTiles + tile) * kTileRows) + local_row;
-        if (p.swiglu) {
-            // gate accumulators sit in tile 0, up in tile 1: exchange through shared memory
-            float* exchange = reinterpret_cast<float*>(smem) + 32 * kRowWarps * 32;  // [32][128]
-            if (tile == 1) {
-#pragma unroll
-                for (int i = 0; i < 32; ++i) {
-                    exchange[i * kTileRows + local_row] = result[i] * p.inverse_scale[1];
+    if (p.splits > 1) {
+        cluster.sync();
+    } else {
+        __syncthreads();
+    }
+    if (!failed && warp < kRowWarps) {
+        const int unit_shift = p.swiglu ? 4 : 5;  // 8-row units per token: 16 (128 outputs) or 32 (256)
+        const int row0 = p.swiglu ? row_group * kTileRows : row_group * kTiles * kTileRows;
+        const int owned = split < p.batch ? (p.batch - split + p.splits - 1) / p.splits : 0;
+        for (int u = threadIdx.x; u < (owned << unit_shift); u += kParkedRows) {
+            const int token = split + (u >> unit_shift) * p.splits;
+            const int r8 = (u & ((1 << unit_shift) - 1)) * 8;
+            float first[8] = {0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f};
+            float second[8] = {0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f};  // the up rows of a SwiGLU pair
+            for (int r = 0; r < p.splits; ++r) {
+                const float* peer = (p.splits > 1 ? cluster.map_shared_rank(parked, r) : parked) + token * kParkedRows + r8;
+                const float4 a = *reinterpret_cast<const float4*>(peer);
+                const float4 b = *reinterpret_cast<const float4*>(peer + 4);
+                first[0] += a.x; first[1] += a.y; first[2] += a.z; first[3] += a.w;
+                first[4] += b.x; first[5] += b.y; first[6] += b.z; first[7] += b.w;
+                if (p.swiglu) {
+                    const float4 c = *reinterpret_cast<const float4*>(peer + kTileRows);
+                    const float4 d = *reinterpret_cast<const float4*>(peer + kTileRows + 4);
+                    second[0] += c.x; second[1] += c.y; second[2] += c.z; second[3] += c.w;
+                    second[4] += d.x; second[5] += d.y; second[6] += d.z; second[7] += d.w;
                 }
             }
-            asm volatile("bar.sync 1, 256;" ::: "memory");  // the eight dequantising warps only
-            if (tile == 0 && row < p.out_features) {
+            const int row = row0 + r8;
+            if (row < p.out_features) {  // out_features is a multiple of 8: a unit is inside or outside
+                uint32_t packed[4];
 #pragma unroll
-                for (int token = 0; token < 32; ++token) {
-                    if (token < p.batch) {
-                        const float gate = result[token] * p.inverse_scale[0];
-                        const float up = exchange[token * kTileRows + local_row];
-                        const float silu = gate / (1.0f + __expf(-gate));
-                        p.y[static_cast<size_t>(token) * p.out_features + row] = __float2bfloat16(silu * up);
+                for (int i = 0; i < 4; ++i) {
+                    float lo = first[2 * i] * p.inverse_scale[0];
+                    float hi = first[2 * i + 1] * p.inverse_scale[0];
+                    if (p.swiglu) {
+                        lo = lo / (1.0f + __expf(-lo)) * (second[2 * i] * p.inverse_scale[1]);
+                        hi = hi / (1.0f + __expf(-hi)) * (second[2 * i + 1] * p.inverse_scale[1]);
                     }
+                    const __nv_bfloat162 pair = __floats2bfloat162_rn(lo, hi);
+                    packed[i] = *reinterpret_cast<const uint32_t*>(&pair);
                 }
-            }
-        } else if (row < p.out_features) {
-#pragma unroll
-            for (int token = 0; token < 32; ++token) {
-                if (token < p.batch) {
-                    p.y[static_cast<size_t>(token) * p.out_features + row] =
-                        __float2bfloat16(result[token] * p.inverse_scale[0]);
-                }
+                *reinterpret_cast<uint4*>(p.y + static_cast<size_t>(token) * p.out_features + row) =
+                    make_uint4(packed[0], packed[1], packed[2], packed[3]);
             }
         }
+    }
+    if (p.splits > 1) {
+        cluster.sync();  // nobody leaves while a peer may still read its shared memory
     }
 
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
