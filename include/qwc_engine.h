@@ -194,6 +194,16 @@ typedef struct qwc_phase_time {
 } qwc_phase_time;
 int qwc_engine_profile_step(qwc_engine* engine, int rows, qwc_phase_time* phases, int max_phases);
 
+/* Graph-timed cost of a subset of the step: captures a CUDA graph of only the phases whose label
+ * starts with `label_prefix` ("gemm.", "attn.decode", "delta.scan", "norm", ...; "" = the whole
+ * step), on the buffers the last real step left on the device, replays it `replays` times between
+ * two events and returns the mean milliseconds per replay and the phases it launched.  The eager
+ * timeline above includes host launch gaps; this does not.  The selected kernels run on stale
+ * activations, so the recurrent state and the KV pages they write are garbage afterwards: call it
+ * after the measurements that need them.  Needs one real step of `rows` rows beforehand. */
+int qwc_engine_time_phases(qwc_engine* engine, int rows, const char* label_prefix, int replays,
+                           float* milliseconds, int* launches);
+
 /*
  * One iteration of the serving worker loop (crates/qwc-engine/src/bin/serve.rs:806-1074,
  * decode part): scheduler.next_batch -> layout check -> table edits -> decode step ->

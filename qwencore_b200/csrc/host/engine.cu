@@ -225,6 +225,8 @@ struct qwc_engine {
 
     // timeline (eager mode only)
     bool profiling = false;
+    const char* phase_filter = nullptr;  // when set, only phases whose label starts with it are launched
+    int filtered_launches = 0;
     std::vector<Phase> marks;
 
     // latency mode
@@ -309,6 +311,18 @@ void mark(qwc_engine* e, const char* label) {
     e->marks.push_back({label, event});
 }
 
+// Opens a phase of the step: records its timeline mark and tells whether its kernels are to be
+// launched (always, unless a phase filter selects a subset for a graph-timed measurement).
+bool phase(qwc_engine* e, const char* label) {
+    mark(e, label);
+    if (e->phase_filter == nullptr) {
+        return true;
+    }
+    const bool selected = std::strncmp(label, e->phase_filter, std::strlen(e->phase_filter)) == 0;
+    e->filtered_launches += selected ? 1 : 0;
+    return selected;
+}
+
 // One projection; in latency mode the local slice lands at this rank's offset of the full
 // row and an all-gather completes it (batch 1 only, so the gathered layout is the row itself).
 int project(qwc_engine* e, const LinearW& w, const __nv_bfloat16* input, __nv_bfloat16* output, int batch) {
@@ -332,60 +346,72 @@ int decode_forward(qwc_engine* e, int batch) {
     uint32_t* tokens = e->in_dev + c.max_batch;
     const qwc_table_edit* edits = reinterpret_cast<const qwc_table_edit*>(e->in_dev + 2 * c.max_batch);
 
-    mark(e, "pack");
-    QWC_TRY(qwc_page_table_apply(e->seq_tokens, e->seq_blocks, edits, e->max_edits, c.state_slots, e->max_blocks, s));
-    QWC_TRY(qwc_pack_decode_batch(row_slots, nullptr, e->seq_tokens, e->seq_blocks, e->rope_table, c.max_context,
-                                  e->row_count, e->state_slots, e->positions, e->context_lengths, e->physical_blocks,
-                                  e->block_offsets, e->block_tables, e->block_table_offsets, nullptr, e->cosine,
-                                  e->sine, e->out_dev + c.max_batch, batch, c.state_slots, e->max_blocks,
-                                  c.kv_page_size, s));
-    mark(e, "embed");
-    QWC_TRY(qwc_fp8_embedding_gather(e->embed, e->embed_scales, tokens, e->residual, batch, c.hidden, c.vocab, s));
-    mark(e, "norm");
-    QWC_TRY(qwc_rmsnorm_bf16(e->residual, nullptr, e->layers[0].input_norm, e->normed, batch, c.hidden, kEps, s));
+    if (phase(e, "pack")) {
+        QWC_TRY(qwc_page_table_apply(e->seq_tokens, e->seq_blocks, edits, e->max_edits, c.state_slots, e->max_blocks, s));
+        QWC_TRY(qwc_pack_decode_batch(row_slots, nullptr, e->seq_tokens, e->seq_blocks, e->rope_table, c.max_context,
+                                      e->row_count, e->state_slots, e->positions, e->context_lengths, e->physical_blocks,
+                                      e->block_offsets, e->block_tables, e->block_table_offsets, nullptr, e->cosine,
+                                      e->sine, e->out_dev + c.max_batch, batch, c.state_slots, e->max_blocks,
+                                      c.kv_page_size, s));
+    }
+    if (phase(e, "embed")) {
+        QWC_TRY(qwc_fp8_embedding_gather(e->embed, e->embed_scales, tokens, e->residual, batch, c.hidden, c.vocab, s));
+    }
+    if (phase(e, "norm")) {
+        QWC_TRY(qwc_rmsnorm_bf16(e->residual, nullptr, e->layers[0].input_norm, e->normed, batch, c.hidden, kEps, s));
+    }
 
     for (size_t index = 0; index < e->layers.size(); ++index) {
         const Layer& layer = e->layers[index];
         if (!layer.full) {
-            mark(e, "gemm.la_in");
-            QWC_TRY(project(e, layer.in_proj, e->normed, e->mixer_in, batch));
-            mark(e, "delta.prepare");
-            QWC_TRY(qwc_delta_prepare_decode(e->mixer_in, e->mixer_in + e->a_offset, e->mixer_in + e->b_offset,
-                                             layer.conv_weight, layer.a_log, layer.dt_bias, layer.conv_state,
-                                             e->state_slots, e->dq, e->dk, e->dv, e->dalpha, e->dbeta, e->dkq,
-                                             c.state_slots, batch, e->mixer_width, e->mixer_width, s));
-            mark(e, "delta.scan");
-            QWC_TRY(qwc_delta_decode_int8(layer.state, layer.state_scales, e->state_slots, e->dq, e->dk, e->dv,
-                                          e->dalpha, e->dbeta, e->dkq, e->delta_out, c.state_slots, batch, s));
-            mark(e, "delta.norm");
-            QWC_TRY(qwc_delta_gated_rmsnorm(e->delta_out, e->mixer_in + e->z_offset, layer.out_norm, e->delta_normed,
-                                            batch, kEps, e->mixer_width, s));
-            mark(e, "gemm.la_out");
-            QWC_TRY(project(e, layer.la_out, e->delta_normed, e->mixer_out, batch));
+            if (phase(e, "gemm.la_in")) {
+                QWC_TRY(project(e, layer.in_proj, e->normed, e->mixer_in, batch));
+            }
+            if (phase(e, "delta.prepare")) {
+                QWC_TRY(qwc_delta_prepare_decode(e->mixer_in, e->mixer_in + e->a_offset, e->mixer_in + e->b_offset,
+                                                 layer.conv_weight, layer.a_log, layer.dt_bias, layer.conv_state,
+                                                 e->state_slots, e->dq, e->dk, e->dv, e->dalpha, e->dbeta, e->dkq,
+                                                 c.state_slots, batch, e->mixer_width, e->mixer_width, s));
+            }
+            if (phase(e, "delta.scan")) {
+                QWC_TRY(qwc_delta_decode_int8(layer.state, layer.state_scales, e->state_slots, e->dq, e->dk, e->dv,
+                                              e->dalpha, e->dbeta, e->dkq, e->delta_out, c.state_slots, batch, s));
+            }
+            if (phase(e, "delta.norm")) {
+                QWC_TRY(qwc_delta_gated_rmsnorm(e->delta_out, e->mixer_in + e->z_offset, layer.out_norm, e->delta_normed,
+                                                batch, kEps, e->mixer_width, s));
+            }
+            if (phase(e, "gemm.la_out")) {
+                QWC_TRY(project(e, layer.la_out, e->delta_normed, e->mixer_out, batch));
+            }
         } else {
-            mark(e, "gemm.attn_qkv");
-            QWC_TRY(project(e, layer.qkv, e->normed, e->qkv_buf, batch));
-            mark(e, "attn.prepare");
+            if (phase(e, "gemm.attn_qkv")) {
+                QWC_TRY(project(e, layer.qkv, e->normed, e->qkv_buf, batch));
+            }
             const int q_width = kQueryHeads * 2 * kHeadDim;
-            QWC_TRY(qwc_prepare_attention_decode_fp8_scaled(
-                e->qkv_buf, e->qkv_buf + q_width, e->qkv_buf + q_width + kKvHeads * kHeadDim, layer.q_norm,
-                layer.k_norm, e->cosine, e->sine, e->physical_blocks, e->block_offsets, layer.k_scale, layer.v_scale,
-                e->query, layer.k_cache, layer.v_cache, batch, c.kv_page_size, e->qkv_width, e->qkv_width,
-                e->qkv_width, kEps, s));
-            mark(e, "attn.decode");
-            // The output gate is the second half of each head of [q; gate], which sits at the
-            // front of the fused q|k|v row.
-            QWC_TRY(qwc_paged_attention_packed_fp8_scaled(
-                e->query, e->qkv_buf, layer.k_cache, layer.v_cache, e->block_tables, e->context_lengths,
-                layer.k_scale, layer.v_scale, e->attention_out, e->attention_workspace, e->attention_workspace_bytes,
-                batch, 0, e->max_blocks, c.kv_page_size, e->qkv_width, e->partitions, 1.0f / 16.0f, s));
-            mark(e, "gemm.attn_out");
-            QWC_TRY(project(e, layer.o, e->attention_out, e->mixer_out, batch));
+            if (phase(e, "attn.prepare")) {
+                QWC_TRY(qwc_prepare_attention_decode_fp8_scaled(
+                    e->qkv_buf, e->qkv_buf + q_width, e->qkv_buf + q_width + kKvHeads * kHeadDim, layer.q_norm,
+                    layer.k_norm, e->cosine, e->sine, e->physical_blocks, e->block_offsets, layer.k_scale, layer.v_scale,
+                    e->query, layer.k_cache, layer.v_cache, batch, c.kv_page_size, e->qkv_width, e->qkv_width,
+                    e->qkv_width, kEps, s));
+            }
+            if (phase(e, "attn.decode")) {
+                // The output gate is the second half of each head of [q | gate], which sits at the
+                // front of the fused q|k|v row.
+                QWC_TRY(qwc_paged_attention_packed_fp8_scaled(
+                    e->query, e->qkv_buf, layer.k_cache, layer.v_cache, e->block_tables, e->context_lengths,
+                    layer.k_scale, layer.v_scale, e->attention_out, e->attention_workspace, e->attention_workspace_bytes,
+                    batch, 0, e->max_blocks, c.kv_page_size, e->qkv_width, e->partitions, 1.0f / 16.0f, s));
+            }
+            if (phase(e, "gemm.attn_out")) {
+                QWC_TRY(project(e, layer.o, e->attention_out, e->mixer_out, batch));
+            }
         }
-        mark(e, "norm");
-        QWC_TRY(qwc_rmsnorm_bf16(e->mixer_out, e->residual, layer.post_norm, e->normed, batch, c.hidden, kEps, s));
-        mark(e, "gemm.mlp_gate_up");
-        {
+        if (phase(e, "norm")) {
+            QWC_TRY(qwc_rmsnorm_bf16(e->mixer_out, e->residual, layer.post_norm, e->normed, batch, c.hidden, kEps, s));
+        }
+        if (phase(e, "gemm.mlp_gate_up")) {
             __nv_bfloat16* target = e->mlp_hidden + static_cast<size_t>(c.split_rank) * layer.gate.out_features;
             QWC_TRY(qwc_nvfp4_swiglu_w4a16(layer.gate.packed, layer.gate.scales, layer.up.packed, layer.up.scales,
                                            e->normed, c.split_size > 1 ? target : e->mlp_hidden,
@@ -397,15 +423,16 @@ int decode_forward(qwc_engine* e, int batch) {
                 return cudaErrorUnknown;
             }
         }
-        mark(e, "gemm.mlp_down");
-        QWC_TRY(project(e, layer.down, e->mlp_hidden, e->mlp_out, batch));
-        mark(e, "norm");
+        if (phase(e, "gemm.mlp_down")) {
+            QWC_TRY(project(e, layer.down, e->mlp_hidden, e->mlp_out, batch));
+        }
         const __nv_bfloat16* next_norm = index + 1 < e->layers.size() ? e->layers[index + 1].input_norm : e->final_norm;
-        QWC_TRY(qwc_rmsnorm_bf16(e->mlp_out, e->residual, next_norm, e->normed, batch, c.hidden, kEps, s));
+        if (phase(e, "norm")) {
+            QWC_TRY(qwc_rmsnorm_bf16(e->mlp_out, e->residual, next_norm, e->normed, batch, c.hidden, kEps, s));
+        }
     }
 
-    mark(e, "lm_head");
-    {
+    if (phase(e, "lm_head")) {
         float* target = e->logits + static_cast<size_t>(c.split_rank) * e->vocab_local;
         QWC_TRY(qwc_fp8_lm_head_batched(e->lm_head, e->lm_head_scales, e->normed, c.split_size > 1 ? target : e->logits,
                                         batch, c.hidden, e->vocab_local, s));
@@ -415,10 +442,11 @@ int decode_forward(qwc_engine* e, int batch) {
             return cudaErrorUnknown;
         }
     }
-    mark(e, "sample");
-    QWC_TRY(qwc_argmax(e->logits, e->argmax_values, e->argmax_indices, e->out_dev, e->vocab_local * c.split_size, batch,
-                       kArgmaxParts, s));
-    mark(e, "end");
+    if (phase(e, "sample")) {
+        QWC_TRY(qwc_argmax(e->logits, e->argmax_values, e->argmax_indices, e->out_dev, e->vocab_local * c.split_size, batch,
+                           kArgmaxParts, s));
+    }
+    mark(e, "end");  // closes the last phase of the timeline
     return 0;
 }
 
@@ -977,6 +1005,55 @@ int qwc_engine_profile_step(qwc_engine* e, int rows, qwc_phase_time* phases, int
     }
     e->marks.clear();
     return status == 0 ? count : -status;
+}
+
+int qwc_engine_time_phases(qwc_engine* e, int rows, const char* label_prefix, int replays, float* milliseconds,
+                           int* launches) {
+    if (e == nullptr || rows <= 0 || rows > e->cfg.max_batch || label_prefix == nullptr || replays <= 0 ||
+        milliseconds == nullptr || !e->warmed[rows - 1]) {
+        return -1;
+    }
+    // A graph of only the selected phases, on the buffers the last real step left behind.
+    cudaGraph_t graph = nullptr;
+    cudaGraphExec_t exec = nullptr;
+    e->phase_filter = label_prefix;
+    e->filtered_launches = 0;
+    QWC_TRY(cudaStreamBeginCapture(e->stream, cudaStreamCaptureModeThreadLocal));
+    const int captured = decode_forward(e, rows);
+    const cudaError_t ended = cudaStreamEndCapture(e->stream, &graph);
+    e->phase_filter = nullptr;
+    if (launches != nullptr) {
+        *launches = e->filtered_launches;
+    }
+    if (captured != 0 || ended != cudaSuccess || e->filtered_launches == 0) {
+        if (graph != nullptr) {
+            cudaGraphDestroy(graph);
+        }
+        return captured != 0 ? captured : (ended != cudaSuccess ? static_cast<int>(ended) : -2);
+    }
+    const cudaError_t made = cudaGraphInstantiate(&exec, graph, 0);
+    cudaGraphDestroy(graph);
+    QWC_TRY(made);
+    cudaEvent_t begin, end;
+    cudaEventCreate(&begin);
+    cudaEventCreate(&end);
+    int status = 0;
+    for (int i = 0; i < 2 && status == 0; ++i) {
+        status = cudaGraphLaunch(exec, e->stream);
+    }
+    cudaEventRecord(begin, e->stream);
+    for (int i = 0; i < replays && status == 0; ++i) {
+        status = cudaGraphLaunch(exec, e->stream);
+    }
+    cudaEventRecord(end, e->stream);
+    const cudaError_t synced = cudaStreamSynchronize(e->stream);
+    float total = 0.0f;
+    cudaEventElapsedTime(&total, begin, end);
+    *milliseconds = total / static_cast<float>(replays);
+    cudaEventDestroy(begin);
+    cudaEventDestroy(end);
+    cudaGraphExecDestroy(exec);
+    return status != 0 ? status : static_cast<int>(synced);
 }
 
 int qwc_worker_step(qwc_engine* e, qwc_scheduler* scheduler, uint32_t eos_token, size_t* num_decoded,

@@ -99,6 +99,7 @@ ENGINE_SYMBOLS = {
     "qwc_engine_replay": (c_int, [P, c_int]),
     "qwc_engine_stream": (P, [P]),
     "qwc_engine_profile_step": (c_int, [P, c_int, POINTER(PhaseTime), c_int]),
+    "qwc_engine_time_phases": (c_int, [P, c_int, ctypes.c_char_p, c_int, POINTER(ctypes.c_float), POINTER(c_int)]),
     "qwc_worker_step": (c_int, [P, P, c_uint32, POINTER(c_size_t), P, c_size_t, POINTER(c_size_t)]),
 }
 for _name, (_restype, _argtypes) in ENGINE_SYMBOLS.items():
@@ -353,6 +354,16 @@ class Engine:
         if count < 0:
             raise abi.QwcError(-count, "qwc_engine_profile_step")
         return [(p.label.decode(), p.milliseconds, p.launches) for p in phases[:count]]
+
+    def time_phases(self, rows: int, label_prefix: str, replays: int = 5):
+        """Mean milliseconds per replay of a graph holding only the phases whose label starts with
+        `label_prefix`, and how many phases that is.  Leaves state and KV pages of the step garbage."""
+        milliseconds, launches = ctypes.c_float(), c_int()
+        code = lib.qwc_engine_time_phases(self._handle, rows, label_prefix.encode(), replays, byref(milliseconds),
+                                          byref(launches))
+        if code != 0:
+            raise abi.QwcError(code if code > 0 else -code, "qwc_engine_time_phases")
+        return milliseconds.value, launches.value
 
     def worker_step(self, scheduler: Scheduler, eos_token: int = 0xFFFFFFFF):
         decoded, count = c_size_t(), c_size_t()
