@@ -101,6 +101,49 @@ def contexts_for(rank: int) -> np.ndarray:
     return synth.log_uniform_contexts(rank, ROWS, CONTEXT_LOW, CONTEXT_HIGH)
 
 
+class RankGroup:
+    """The ranks of one launch: data-parallel replicas that only meet to line up and compare clocks.
+
+    One process per GPU under torchrun (backend "nccl"); the same class runs on CPU with "gloo" in the
+    tests.  There is no collective on the data path: a rank's 32 rows, its scheduler and its engine
+    are its own.  `value` of the whole job = rows of all ranks x steps / the slowest rank's time."""
+
+    def __init__(self, backend: str, local_device=None):
+        self.world = int(os.environ.get("WORLD_SIZE", "1"))
+        self.rank = int(os.environ.get("RANK", "0"))
+        self.local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+        self.backend = backend
+        self.device = local_device
+        self.dist = None
+        if self.world > 1:
+            import torch.distributed as dist
+
+            kwargs = {"device_id": local_device} if (backend == "nccl" and local_device is not None) else {}
+            dist.init_process_group(backend, **kwargs)
+            self.dist = dist
+
+    def barrier(self) -> None:
+        if self.dist is not None:
+            self.dist.barrier()
+
+    def max_over_ranks(self, value: float) -> float:
+        if self.dist is None:
+            return value
+        import torch
+
+        t = torch.tensor([value], dtype=torch.float64, device=self.device if self.backend == "nccl" else "cpu")
+        self.dist.all_reduce(t, op=self.dist.ReduceOp.MAX)
+        return float(t.item())
+
+    def whole_job_rate(self, units_per_rank: float, slowest_seconds: float) -> float:
+        return self.world * units_per_rank / slowest_seconds
+
+    def close(self) -> None:
+        if self.dist is not None:
+            self.dist.destroy_process_group()
+            self.dist = None
+
+
 def measured_peak_gbs():
     path = ROOT / "MEASURED_PEAKS.json"
     if path.exists():
@@ -231,17 +274,12 @@ def run_ours(args):
 
     from qwencore_b200 import engine as engine_module
 
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    rank = int(os.environ.get("RANK", "0"))
-    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device: the decode step has no CPU path")
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     torch.cuda.set_device(local_rank)
-    distributed = world > 1
-    if distributed:
-        import torch.distributed as dist
-
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    group = RankGroup("nccl", torch.device("cuda", local_rank))
+    world, rank, distributed = group.world, group.rank, group.world > 1
 
     contexts = contexts_for(rank)
     total_steps = args.steps + args.warmup + 8
@@ -262,16 +300,10 @@ def run_ours(args):
         engine.worker_step(scheduler)
 
     def barrier():
-        if distributed:
-            dist.barrier()
+        group.barrier()
         torch.cuda.synchronize()
 
-    def max_over_ranks(value: float) -> float:
-        if not distributed:
-            return value
-        t = torch.tensor([value], dtype=torch.float64, device="cuda")
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        return float(t.item())
+    max_over_ranks = group.max_over_ranks
 
     sampler = ClockSampler(local_rank)
     if rank == 0:
@@ -326,17 +358,16 @@ def run_ours(args):
 
     if rank != 0:
         engine.close()
-        if distributed:
-            dist.destroy_process_group()
+        group.close()
         return 0
 
     cpu_value, cpu_sample_text = cpu_tokens_per_second(os.cpu_count() or 1)
-    tokens = world * ROWS * args.steps
+    tokens = ROWS * args.steps  # per rank
     line = base_line(args, world)
     line.update({
-        "value": tokens / device_seconds,
+        "value": group.whole_job_rate(tokens, device_seconds),
         "ms_per_step": device_seconds / args.steps * 1e3,
-        "e2e": {"value": tokens / e2e_seconds, "unit": "tok/s", "ms_per_step": e2e_seconds / args.steps * 1e3,
+        "e2e": {"value": group.whole_job_rate(tokens, e2e_seconds), "unit": "tok/s", "ms_per_step": e2e_seconds / args.steps * 1e3,
                 "h2d_bytes_per_step": int((2 * ROWS + 4 * 2 * ROWS) * 4), "d2h_bytes_per_step": int((ROWS + 1) * 4),
                 "path": "qwc_worker_step: scheduler.next_batch, layout check, H2D of slots/tokens/edits, graph "
                         "replay, D2H of sampled tokens, scheduler.complete_batch"},
@@ -362,8 +393,7 @@ def run_ours(args):
     })
     print(json.dumps(line))
     engine.close()
-    if distributed:
-        dist.destroy_process_group()
+    group.close()
     return 0
 
 
