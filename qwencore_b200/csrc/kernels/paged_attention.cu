@@ -282,6 +282,24 @@ __global__ void __launch_bounds__(kThreads, 1) paged_attention_packed_kernel(
         const uint32_t v_base = smem_u32(&sm.v[0][0]);
         int n = 0;  // stages consumed so far
         bool ok = true;
+        // bf16 words of this lane's query fragments (head g of the task's group; rows 6, 7 are padding)
+        uint2 q_raw[16];
+        auto load_query = [&](const Task& next) {
+            const int head = next.kv_head * kGqaGroup + g;
+            const __nv_bfloat16* qp = query + (static_cast<size_t>(next.row) * kQueryHeads + head) * kHeadDim;
+#pragma unroll
+            for (int m = 0; m < 4; ++m) {
+                const int unit = 2 * t + (m & 1) + 8 * (m >> 1);
+#pragma unroll
+                for (int s = 0; s < 4; ++s) {
+                    q_raw[m * 4 + s] = g < kGqaGroup ? *reinterpret_cast<const uint2*>(qp + 16 * unit + 4 * s)
+                                                     : make_uint2(0u, 0u);
+                }
+            }
+        };
+        if (task_count > 0) {
+            load_query(sm.tasks[0]);
+        }
         for (int ti = 0; ti < task_count && ok; ++ti) {
             const Task task = sm.tasks[ti];
             const int row = task.row;
@@ -291,27 +309,15 @@ __global__ void __launch_bounds__(kThreads, 1) paged_attention_packed_kernel(
             // Query A fragments for the 16 k-steps.  K fragment reads take 16-byte bank group
             // u(t, m) = 2t + (m & 1) + 8 (m >> 1) of a token row in load m, so k-step (m, s)
             // contracts dims 16 u + 4 s .. + 3 for t = 0..3: Q uses the same permutation.
+            // The raw bf16 words were fetched while the previous task was computed.
             uint32_t qa[16][2];
-            {
-                const int head = kv_head * kGqaGroup + g;
-                const __nv_bfloat16* qp = query + (static_cast<size_t>(row) * kQueryHeads + head) * kHeadDim;
 #pragma unroll
-                for (int m = 0; m < 4; ++m) {
-                    const int unit = 2 * t + (m & 1) + 8 * (m >> 1);
-#pragma unroll
-                    for (int s = 0; s < 4; ++s) {
-                        if (g < kGqaGroup) {
-                            const uint2 raw = *reinterpret_cast<const uint2*>(qp + 16 * unit + 4 * s);
-                            qa[m * 4 + s][0] =
-                                pack_half2(__uint_as_float(raw.x << 16), __uint_as_float(raw.x & 0xffff0000u));
-                            qa[m * 4 + s][1] =
-                                pack_half2(__uint_as_float(raw.y << 16), __uint_as_float(raw.y & 0xffff0000u));
-                        } else {
-                            qa[m * 4 + s][0] = 0;
-                            qa[m * 4 + s][1] = 0;
-                        }
-                    }
-                }
+            for (int i = 0; i < 16; ++i) {
+                qa[i][0] = pack_half2(__uint_as_float(q_raw[i].x << 16), __uint_as_float(q_raw[i].x & 0xffff0000u));
+                qa[i][1] = pack_half2(__uint_as_float(q_raw[i].y << 16), __uint_as_float(q_raw[i].y & 0xffff0000u));
+            }
+            if (ti + 1 < task_count) {
+                load_query(sm.tasks[ti + 1]);  // in flight during this task
             }
             const float k_scale = key_scales ? key_scales[kv_head] : 1.0f;
             const float score_scale = softmax_scale * k_scale * kLog2e;
