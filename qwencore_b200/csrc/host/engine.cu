@@ -260,9 +260,11 @@ int gpu_alloc_t(qwc_engine* e, T** out, size_t count, bool zero = false) {
     return gpu_alloc(e, reinterpret_cast<void**>(out), count * sizeof(T), zero);
 }
 
-uint64_t tensor_seed(const qwc_engine* e, int layer, int tag) {
+// Replicated tensors (norms, conv, caches, state, embedding) are the same on every rank of a column
+// split; the split matrices hold different rows on every rank, so their seed takes the rank in.
+uint64_t tensor_seed(const qwc_engine* e, int layer, int tag, bool split_tensor = false) {
     return e->cfg.seed * 1000003ull + static_cast<uint64_t>(layer) * 131ull + static_cast<uint64_t>(tag) +
-           static_cast<uint64_t>(e->cfg.split_rank) * 7919ull * 65537ull;
+           (split_tensor ? static_cast<uint64_t>(e->cfg.split_rank) * 7919ull * 65537ull : 0ull);
 }
 
 void fill_bytes(qwc_engine* e, void* p, size_t n, uint64_t seed, int kind) {
@@ -290,8 +292,8 @@ int make_linear(qwc_engine* e, LinearW* w, int out_features, int in_features, in
     const size_t scale_bytes = scale_storage(w->out_features, in_features);
     QWC_TRY(gpu_alloc_t(e, &w->packed, packed_bytes));
     QWC_TRY(gpu_alloc_t(e, &w->scales, scale_bytes));
-    fill_bytes(e, w->packed, packed_bytes, tensor_seed(e, layer, tag), 0);
-    fill_bytes(e, w->scales, scale_bytes, tensor_seed(e, layer, tag + 1), 1);
+    fill_bytes(e, w->packed, packed_bytes, tensor_seed(e, layer, tag, true), 0);
+    fill_bytes(e, w->scales, scale_bytes, tensor_seed(e, layer, tag + 1, true), 1);
     return 0;
 }
 
@@ -652,8 +654,8 @@ int qwc_engine_create(const qwc_engine_config* config, qwc_engine** out) {
     if (status == 0) {
         fill_bytes(e, e->embed, table_bytes, tensor_seed(e, c.num_layers, 50), 2);
         fill_uniform(e, e->embed_scales, c.vocab, tensor_seed(e, c.num_layers, 51), 0.0001f, 0.0003f);
-        fill_bytes(e, e->lm_head, head_bytes, tensor_seed(e, c.num_layers, 52), 2);
-        fill_uniform(e, e->lm_head_scales, e->vocab_local, tensor_seed(e, c.num_layers, 53), 0.0001f, 0.0003f);
+        fill_bytes(e, e->lm_head, head_bytes, tensor_seed(e, c.num_layers, 52, true), 2);
+        fill_uniform(e, e->lm_head_scales, e->vocab_local, tensor_seed(e, c.num_layers, 53, true), 0.0001f, 0.0003f);
     }
 
     // ---- activations ----

@@ -162,7 +162,6 @@ __device__ __forceinline__ void bulk_wait_all() {
     asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
 }
 
-// Make generic-proxy shared-memory writes visible to the async proxy (bulk stores).
 // Programmatic dependent launch.  A kernel launched with the programmatic-serialization attribute
 // may start while its predecessor in the stream still runs; it must not touch anything the
 // predecessor writes before pdl_wait() returns (which is when the predecessor has completed and
@@ -195,6 +194,7 @@ cudaError_t launch_chained(void (*kernel)(Params...), dim3 grid, dim3 block, siz
     return cudaLaunchKernelEx(&config, kernel, static_cast<Params>(args)...);
 }
 
+// Make generic-proxy shared-memory writes visible to the async proxy (bulk stores, tensor-core reads).
 __device__ __forceinline__ void fence_proxy_async() {
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
 }

@@ -217,6 +217,8 @@ def test_decode_reports_packing_errors(cuda, engine_module):
 
 def test_phase_timeline_covers_every_phase(cuda, engine_module):
     """Timeline marks (crates/qwc-cuda/src/timeline.rs:17-77): one entry per phase label."""
+    from qwencore_b200 import abi
+
     engine = engine_module.Engine(small_config(engine_module, num_layers=4))
     try:
         cache = engine_module.CacheManager(6, 160, 16)
@@ -233,5 +235,15 @@ def test_phase_timeline_covers_every_phase(cuda, engine_module):
         traffic = engine.traffic(2, 83)
         assert traffic.gemv_launches_per_step == 4 * 2 + 3 * 2 + 2
         assert traffic.kv_bytes == 83 * 2 * 4 * 256
+        # graph-timed subsets of the step: the projections, one phase, everything, nothing
+        ms, launched = engine.time_phases(2, "gemm.", replays=3)
+        assert launched == traffic.gemv_launches_per_step and ms > 0
+        ms_scan, launched = engine.time_phases(2, "delta.scan", replays=3)
+        assert launched == 3 and 0 < ms_scan < ms * 10
+        ms_all, launched = engine.time_phases(2, "", replays=3)
+        assert launched == sum(count for _, count in phases.values()) and ms_all >= ms
+        with pytest.raises(abi.QwcError):
+            engine.time_phases(2, "no.such.phase")
+        assert abi.lib.qwc_device_status() == 0
     finally:
         engine.close()
