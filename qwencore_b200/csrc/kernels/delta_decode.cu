@@ -108,6 +108,13 @@ __global__ void __launch_bounds__(kThreads, 4) delta_decode_int8_kernel(
     const float bt = beta[static_cast<size_t>(b) * v_heads + h];
     const float kq_token = kq[static_cast<size_t>(b) * kDeltaKeyHeads + hk];
     const float* vp = v + (static_cast<size_t>(b) * v_heads + h) * kDim + row_begin;
+    // this lane's v element of every part, fetched before the first tile wait
+    float v_rows[kMaxParts];
+#pragma unroll
+    for (int part = 0; part < kMaxParts; ++part) {
+        const int row = part * kPartRows + (threadIdx.x >> 5) * 8 + ((threadIdx.x & 31) >> 2);
+        v_rows[part] = row < rows_here ? vp[row] : 0.0f;
+    }
 
     constexpr float kMagic = 12582912.0f;        // 1.5 * 2^23
     constexpr float kMagicBiased = 12583040.0f;  // kMagic + 128
@@ -126,7 +133,11 @@ __global__ void __launch_bounds__(kThreads, 4) delta_decode_int8_kernel(
         const uint4 c0 = *reinterpret_cast<const uint4*>(row_ptr);
         const uint4 c1 = *reinterpret_cast<const uint4*>(row_ptr + 64);
         const float scale = row_scale[local];
-        const float v_row = vp[local];
+        float v_row = v_rows[0];
+#pragma unroll
+        for (int i = 1; i < kMaxParts; ++i) {
+            v_row = part == i ? v_rows[i] : v_row;
+        }
 
         const uint32_t words[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
         float2 s[16];
