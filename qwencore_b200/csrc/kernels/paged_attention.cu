@@ -60,6 +60,7 @@ struct Task {
     int part;
     int unit_begin;
     int units;
+    int context;  // tokens of the row, cut at the block table's capacity
 };
 
 struct Smem {
@@ -218,8 +219,10 @@ __global__ void __launch_bounds__(kThreads, 1) paged_attention_packed_kernel(
                     ++row;
                 }
                 const int part = pair - sm.first_pair[row];
-                const int row_units = units_of_context(context_lengths[row_base + row], capacity_units);
+                const uint32_t row_context = context_lengths[row_base + row];
+                const int row_units = units_of_context(row_context, capacity_units);
                 Task task;
+                task.context = static_cast<int>(min(row_context, static_cast<uint32_t>(capacity_units) * kUnitTokens));
                 task.row = row_base + row;
                 task.kv_head = static_cast<int>(id % kKvHeads);
                 task.part = part;
@@ -248,20 +251,21 @@ __global__ void __launch_bounds__(kThreads, 1) paged_attention_packed_kernel(
             const int stages = (task.units + kStageUnits - 1) / kStageUnits;
             for (int st = 0; st < stages && ok; ++st, ++n) {
                 const int slot = n % kStages;
+                const int first = task.unit_begin + st * kStageUnits;
+                const int count = min(kStageUnits, task.units - st * kStageUnits);
+                // the page id is fetched before the wait for a free slot, which is the longer of the two
+                const uint32_t physical = lane < count ? table[(first + lane) / units_per_page] : 0u;
                 ok = mbar_wait_bounded(&sm.empty[slot], ((n / kStages) & 1) ^ 1, kStatusAttentionPageWait, status);
                 ok = __all_sync(0xffffffffu, ok) && *reinterpret_cast<volatile int*>(&sm.failed) == 0;
                 if (!ok) {
                     break;
                 }
-                const int first = task.unit_begin + st * kStageUnits;
-                const int count = min(kStageUnits, task.units - st * kStageUnits);
                 if (lane == 0) {
                     mbar_arrive_expect_tx(&sm.full[slot], static_cast<uint32_t>(count) * 2 * kUnitBytes);
                 }
                 __syncwarp();
                 if (lane < count) {
                     const int unit = first + lane;
-                    const uint32_t physical = table[unit / units_per_page];
                     const size_t offset = ((static_cast<size_t>(physical) * kKvHeads + task.kv_head) * page_size +
                                            static_cast<size_t>(unit % units_per_page) * kUnitTokens) *
                                           kHeadDim;
@@ -304,7 +308,7 @@ __global__ void __launch_bounds__(kThreads, 1) paged_attention_packed_kernel(
             const Task task = sm.tasks[ti];
             const int row = task.row;
             const int kv_head = task.kv_head;
-            const int context = min(static_cast<int>(min(context_lengths[row], 0x7fffffffu)), capacity_units * kUnitTokens);
+            const int context = task.context;
 
             // Query A fragments for the 16 k-steps.  K fragment reads take 16-byte bank group
             // u(t, m) = 2t + (m & 1) + 8 (m >> 1) of a token row in load m, so k-step (m, s)

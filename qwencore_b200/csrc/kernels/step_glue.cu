@@ -73,10 +73,20 @@ __global__ void __launch_bounds__(kThreads) rmsnorm_bf16_kernel(const __nv_bfloa
                                                                 __nv_bfloat16* __restrict__ output, int hidden,
                                                                 float epsilon) {
     pdl_launch_dependents();  // the projection that follows may start streaming its weights
-    pdl_wait();
     __shared__ float scratch[kThreads / 32];
     const size_t base = static_cast<size_t>(blockIdx.x) * hidden;
     const int vectors = hidden / 8;
+    // The norm weights are never written during a step: they are fetched while the kernel that
+    // produces the input is still running.
+    uint4 gains[kNormMaxPerThread];
+#pragma unroll
+    for (int i = 0; i < kNormMaxPerThread; ++i) {
+        const int vec = threadIdx.x + i * kThreads;
+        if (vec < vectors) {
+            gains[i] = *reinterpret_cast<const uint4*>(weight + 8 * vec);
+        }
+    }
+    pdl_wait();
     uint4 held[kNormMaxPerThread];
     float sum = 0.0f;
 #pragma unroll
@@ -114,8 +124,7 @@ __global__ void __launch_bounds__(kThreads) rmsnorm_bf16_kernel(const __nv_bfloa
     for (int i = 0; i < kNormMaxPerThread; ++i) {
         const int vec = threadIdx.x + i * kThreads;
         if (vec < vectors) {
-            const uint4 w4 = *reinterpret_cast<const uint4*>(weight + 8 * vec);
-            const uint32_t ww[4] = {w4.x, w4.y, w4.z, w4.w};
+            const uint32_t ww[4] = {gains[i].x, gains[i].y, gains[i].z, gains[i].w};
             const uint32_t xw[4] = {held[i].x, held[i].y, held[i].z, held[i].w};
             uint32_t out[4];
 #pragma unroll
@@ -145,23 +154,30 @@ __device__ __forceinline__ float softplusf_ref(float value) {
     return log1pf(__expf(value));
 }
 
-__device__ __forceinline__ float conv_update(const __nv_bfloat16* __restrict__ mixed_row,
-                                             const __nv_bfloat16* __restrict__ conv_weight,
-                                             float* __restrict__ conv_state, size_t slot_base, int channel) {
-    float* history = conv_state + (slot_base + channel) * 3;
-    const float current = __bfloat162float(mixed_row[channel]);
-    const __nv_bfloat16* weight = conv_weight + static_cast<size_t>(channel) * 4;
-    float convolved = __bfloat162float(weight[0]) * history[0];
-    convolved = fmaf(__bfloat162float(weight[1]), history[1], convolved);
-    convolved = fmaf(__bfloat162float(weight[2]), history[2], convolved);
-    convolved = fmaf(__bfloat162float(weight[3]), current, convolved);
-    const float h1 = history[1];
-    const float h2 = history[2];
-    history[0] = h1;
-    history[1] = h2;
-    history[2] = current;
+// One channel of the causal conv: the operands are fetched by load_* (all channels of a thread
+// first, so that their latencies overlap), then finished here.
+struct ConvOperands {
+    float history[3];
+    float current;
+    uint2 weight;  // four bf16 taps
+};
+
+__device__ __forceinline__ float conv_finish(const ConvOperands& in, float* __restrict__ history) {
+    const float w0 = __uint_as_float(in.weight.x << 16);
+    const float w1 = __uint_as_float(in.weight.x & 0xffff0000u);
+    const float w2 = __uint_as_float(in.weight.y << 16);
+    const float w3 = __uint_as_float(in.weight.y & 0xffff0000u);
+    float convolved = w0 * in.history[0];
+    convolved = fmaf(w1, in.history[1], convolved);
+    convolved = fmaf(w2, in.history[2], convolved);
+    convolved = fmaf(w3, in.current, convolved);
+    history[0] = in.history[1];
+    history[1] = in.history[2];
+    history[2] = in.current;
     return __bfloat162float(__float2bfloat16(convolved * sigmoidf_fast(convolved)));
 }
+
+constexpr int kMaxValueRatio = 3;  // value heads per key head: 32 / 16 or 48 / 16
 
 __global__ void __launch_bounds__(kDeltaHeadDim) delta_prepare_kernel(
     const __nv_bfloat16* __restrict__ mixed_qkv, const __nv_bfloat16* __restrict__ a_projection,
@@ -171,7 +187,6 @@ __global__ void __launch_bounds__(kDeltaHeadDim) delta_prepare_kernel(
     float* __restrict__ key, float* __restrict__ value, float* __restrict__ alpha, float* __restrict__ beta,
     float* __restrict__ kq, int mixed_stride, int gate_stride, int v_heads) {
     pdl_launch_dependents();
-    pdl_wait();
     __shared__ float scratch[kDeltaHeadDim / 32];
     const int head = blockIdx.x;
     const int batch = blockIdx.y;
@@ -179,18 +194,59 @@ __global__ void __launch_bounds__(kDeltaHeadDim) delta_prepare_kernel(
     const int ratio = v_heads / kDeltaKeyHeads;
     const int qk_elements = kDeltaKeyHeads * kDeltaHeadDim;
     const int channels = 2 * qk_elements + v_heads * kDeltaHeadDim;
+
+    // This thread's channels: q, k and one per value head that shares the key head.
+    int channel[2 + kMaxValueRatio];
+    channel[0] = head * kDeltaHeadDim + dimension;
+    channel[1] = qk_elements + head * kDeltaHeadDim + dimension;
+#pragma unroll
+    for (int r = 0; r < kMaxValueRatio; ++r) {
+        channel[2 + r] = 2 * qk_elements + (head * ratio + r) * kDeltaHeadDim + dimension;
+    }
+    // Conv taps and the gate constants are never written during a step: fetched before the wait.
+    ConvOperands operands[2 + kMaxValueRatio];
+#pragma unroll
+    for (int i = 0; i < 2 + kMaxValueRatio; ++i) {
+        if (i < 2 + ratio) {
+            operands[i].weight = *reinterpret_cast<const uint2*>(conv_weight + static_cast<size_t>(channel[i]) * 4);
+        }
+    }
+    float log_a = 0.0f, bias = 0.0f;
+    if (dimension < ratio) {
+        log_a = __bfloat162float(a_log[head * ratio + dimension]);
+        bias = __bfloat162float(dt_bias[head * ratio + dimension]);
+    }
+    pdl_wait();
     const uint32_t slot = state_slots[batch];
     const size_t slot_base = static_cast<size_t>(slot) * channels;
     const __nv_bfloat16* mixed_row = mixed_qkv + static_cast<size_t>(batch) * mixed_stride;
+    // every load of the step's data is issued before the first use
+#pragma unroll
+    for (int i = 0; i < 2 + kMaxValueRatio; ++i) {
+        if (i < 2 + ratio) {
+            const float* history = conv_state + (slot_base + channel[i]) * 3;
+            operands[i].history[0] = history[0];
+            operands[i].history[1] = history[1];
+            operands[i].history[2] = history[2];
+            operands[i].current = __bfloat162float(mixed_row[channel[i]]);
+        }
+    }
+    float projected_a = 0.0f, projected_b = 0.0f;
+    if (dimension < ratio) {
+        const size_t gate_read = static_cast<size_t>(batch) * gate_stride + head * ratio + dimension;
+        projected_a = __bfloat162float(a_projection[gate_read]);
+        projected_b = __bfloat162float(b_projection[gate_read]);
+    }
 
-    const float q = conv_update(mixed_row, conv_weight, conv_state, slot_base, head * kDeltaHeadDim + dimension);
-    const float k =
-        conv_update(mixed_row, conv_weight, conv_state, slot_base, qk_elements + head * kDeltaHeadDim + dimension);
-    for (int r = 0; r < ratio; ++r) {
-        const int value_head = head * ratio + r;
-        const float v = conv_update(mixed_row, conv_weight, conv_state, slot_base,
-                                    2 * qk_elements + value_head * kDeltaHeadDim + dimension);
-        value[(static_cast<size_t>(batch) * v_heads + value_head) * kDeltaHeadDim + dimension] = v;
+    const float q = conv_finish(operands[0], conv_state + (slot_base + channel[0]) * 3);
+    const float k = conv_finish(operands[1], conv_state + (slot_base + channel[1]) * 3);
+#pragma unroll
+    for (int r = 0; r < kMaxValueRatio; ++r) {
+        if (r < ratio) {
+            const int value_head = head * ratio + r;
+            const float v = conv_finish(operands[2 + r], conv_state + (slot_base + channel[2 + r]) * 3);
+            value[(static_cast<size_t>(batch) * v_heads + value_head) * kDeltaHeadDim + dimension] = v;
+        }
     }
 
     const float q_sum = block_sum(q * q, scratch);
@@ -208,12 +264,7 @@ __global__ void __launch_bounds__(kDeltaHeadDim) delta_prepare_kernel(
     }
     if (dimension < ratio) {
         const int value_head = head * ratio + dimension;
-        const size_t gate_read = static_cast<size_t>(batch) * gate_stride + value_head;
         const size_t gate_offset = static_cast<size_t>(batch) * v_heads + value_head;
-        const float projected_a = __bfloat162float(a_projection[gate_read]);
-        const float projected_b = __bfloat162float(b_projection[gate_read]);
-        const float log_a = __bfloat162float(a_log[value_head]);
-        const float bias = __bfloat162float(dt_bias[value_head]);
         const float log_decay = -__expf(log_a) * softplusf_ref(projected_a + bias);
         alpha[gate_offset] = __expf(log_decay);
         beta[gate_offset] = sigmoidf_fast(projected_b);
@@ -227,20 +278,20 @@ __global__ void __launch_bounds__(kDeltaHeadDim) gated_rmsnorm_kernel(const floa
                                                                       __nv_bfloat16* __restrict__ output,
                                                                       float epsilon, int gate_stride, int heads) {
     pdl_launch_dependents();  // the projection that follows may start streaming its weights
-    pdl_wait();
     __shared__ float scratch[kDeltaHeadDim / 32];
     const int head = blockIdx.x;
     const int batch = blockIdx.y;
     const int dimension = threadIdx.x;
+    const float gain = __bfloat162float(weight[dimension]);  // static: fetched before the wait
+    pdl_wait();
     const size_t offset = (static_cast<size_t>(batch) * heads + head) * kDeltaHeadDim + dimension;
     const size_t gate_offset = static_cast<size_t>(batch) * gate_stride + head * kDeltaHeadDim + dimension;
+    const float gate_value = __bfloat162float(gate[gate_offset]);  // issued with the input load, used last
     const float value = __bfloat162float(__float2bfloat16(input[offset]));
     const float sum = block_sum(value * value, scratch);
     const float inverse = rsqrtf(sum / static_cast<float>(kDeltaHeadDim) + epsilon);
     const __nv_bfloat16 normalized = __float2bfloat16(value * inverse);
-    const __nv_bfloat16 weighted =
-        __float2bfloat16(__bfloat162float(weight[dimension]) * __bfloat162float(normalized));
-    const float gate_value = __bfloat162float(gate[gate_offset]);
+    const __nv_bfloat16 weighted = __float2bfloat16(gain * __bfloat162float(normalized));
     const float silu = gate_value / (1.0f + __expf(-gate_value));
     output[offset] = __float2bfloat16(__bfloat162float(weighted) * silu);
 }
