@@ -635,9 +635,10 @@ cudaError_t dispatch(const GemvParams& p, cudaStream_t stream) {
     if (MODE == kFp8Rows ? p.batch <= 8 : (p.batch <= 8 && !large)) {
         return launch<1, 1, MODE>(p, stream);
     }
-    // its stores are 16 bytes wide
-    const bool vector_stores = p.out_features % 8 == 0 && (reinterpret_cast<uintptr_t>(p.y) & 15) == 0;
-    if (MODE != kFp8Rows && vector_stores) {
+    // its stores are 16 bytes wide and its activation fetch is a tiled TMA copy
+    const bool aligned = p.out_features % 8 == 0 && (reinterpret_cast<uintptr_t>(p.y) & 15) == 0 &&
+                         (reinterpret_cast<uintptr_t>(p.x) & 15) == 0;
+    if (MODE != kFp8Rows && aligned) {
         // Above eight rows the legacy tensor path cannot keep up with the weight stream.
         return launch_nvfp4_umma(p.packed[0], p.scales[0], p.packed[1], p.scales[1], p.x, p.y, p.out_features,
                                  p.in_features, p.batch, p.inverse_scale[0], p.inverse_scale[1],

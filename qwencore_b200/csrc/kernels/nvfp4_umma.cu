@@ -9,7 +9,7 @@
 // One CTA per SM works on two 128-row tiles (plain GEMV: 256 consecutive rows; SwiGLU: the gate
 // rows and the up rows of the same 128 outputs) and a K slice; K slices of one row group form a
 // thread-block cluster and are reduced through distributed shared memory.  K is walked in stages
-// of 256 elements (two 128-element chunks), each CTA starting at a different stage.
+// of 256 elements (two 128-element chunks).
 //
 //   warps 0-15  dequantise.  Thread = one weight row = one TMEM lane; warps 0-7 take the even
 //               chunks, warps 8-15 the odd ones.  A thread reads 64 bytes of its row per chunk
@@ -19,15 +19,15 @@
 //   warp 16     producer: per stage one tiled TMA copy per tile (a box of 128 rows x 128 bytes,
 //               128-byte swizzle, so that the row-per-thread reads above are free of bank
 //               conflicts) and one bulk copy of the swizzled scale tiles (contiguous over K for a
-//               128-row block), into a three-stage ring.  One instruction moves 16 KiB: a copy
+//               128-row block), into a four-stage ring.  One instruction moves 16 KiB: a copy
 //               per weight row is limited by the copy issue rate, not by HBM.
 //   warps 17-18 issue tcgen05.mma, one warp per tile: A from TMEM, B (activations, K-major core
 //               matrices) from shared memory, and tcgen05.commit to hand buffers back.  The
 //               instructions sit in an elect.sync region: issued from `lane == 0` they cost three
 //               times as many cycles each.
 //   warps 19-22 convert the activation rows bf16 -> f16 into the B layout; warp w owns operand
-//               stage w and every fourth chunk, and stages the bf16 rows with cp.async two of its
-//               chunks ahead.
+//               stage w and every fourth chunk, and fetches the bf16 rows of its next chunk with
+//               two tiled TMA copies as soon as it has read the current one.
 //
 // Every wait is bounded; a wait that gives up records a code in the status word, the CTA skips
 // its stores, frees its TMEM and returns.
@@ -50,9 +50,9 @@ constexpr int kTiles = 2;
 constexpr int kBoxBytes = kTileRows * kBoxRowBytes;       // 16 KiB, multiple of the 1 KiB swizzle period
 constexpr int kScaleStageBytes = kStageChunks * 2 * 512;  // scale tiles of 512 bytes per 128-row block and 64 K
 constexpr int kTileStageBytes = kBoxBytes + kScaleStageBytes;
-constexpr int kWeightStages = 3;
+constexpr int kWeightStages = 4;
 constexpr int kXStages = 4;
-constexpr int kRawBuffers = 2;  // bf16 chunks in flight per converting warp (cp.async), besides the one in work
+constexpr int kRawBuffers = 1;  // bf16 chunks in flight per converting warp (cp.async)
 constexpr int kABuffers = 3;
 constexpr int kRowWarps = 8;                     // one thread per weight row of the two tiles
 constexpr int kDequantSets = 2;                  // set s dequantises the chunks with index = s (mod 2)
@@ -97,6 +97,7 @@ struct Barriers {
     uint64_t x_free[kXStages];
     uint64_t d_ready;
     uint64_t tmem_ready;
+    uint64_t raw_full[kXStages];
     uint32_t tmem_base;
     int failed;
 };
@@ -195,7 +196,7 @@ __device__ __forceinline__ void tmem_load32(uint32_t taddr, float (&v)[32]) {
 
 __global__ void __launch_bounds__(kThreads, 1)
     nvfp4_umma_kernel(const __grid_constant__ CUtensorMap map0, const __grid_constant__ CUtensorMap map1,
-                      const UmmaParams p) {
+                      const __grid_constant__ CUtensorMap x_map, const UmmaParams p) {
     extern __shared__ unsigned char smem_raw[];
     __shared__ Barriers bars;
     // 128-byte-swizzled boxes need a 1 KiB-aligned shared address.
@@ -207,22 +208,19 @@ __global__ void __launch_bounds__(kThreads, 1)
     const int row_group = blockIdx.x / p.splits;
     const int split = blockIdx.x - row_group * p.splits;
     const int K = p.in_features;
-    // K is cut into stages of 256 elements; a slice is a whole number of stages.  Each CTA walks its
-    // slice from a different starting stage and wraps around: CTAs that all read the same activation
-    // chunk at the same moment queue on the few L2 slices that hold it.
+    // K is cut into stages of 256 elements; a slice is a whole number of stages.
     const int stages_in_k = K / (kChunkK * kStageChunks);
     const int s_begin = static_cast<int>(static_cast<long long>(stages_in_k) * split / p.splits);
     const int s_end = static_cast<int>(static_cast<long long>(stages_in_k) * (split + 1) / p.splits);
     const int num_wstages = s_end - s_begin;
     const int total_chunks = num_wstages * kStageChunks;
-    const int first_stage = num_wstages > 0 ? (row_group * 7 + split) % num_wstages : 0;
     const int group_blocks = K / 64;
     const int n_pad = p.n_pad;
     const int x_stage_bytes = n_pad * kChunkK * 2;
 
     unsigned char* weight_ring = smem;                                                   // [stage][tile][box | scales]
     unsigned char* x_ring = smem + kWeightStages * kTiles * kTileStageBytes;             // [xstage][...]
-    unsigned char* raw_ring = x_ring + kXStages * 32 * kChunkK * 2;                      // [warp][buffer][unit][16]
+    unsigned char* raw_ring = x_ring + kXStages * 32 * kChunkK * 2;                      // [warp][two boxes of 32 rows x 128 B, swizzled]
 
     // First row of each tile and the matrix it comes from.
     int tile_row0[kTiles];
@@ -250,6 +248,9 @@ __global__ void __launch_bounds__(kThreads, 1)
         }
         mbar_init(&bars.d_ready, kMmaWarps);
         mbar_init(&bars.tmem_ready, 1);
+        for (int s = 0; s < kXStages; ++s) {
+            mbar_init(&bars.raw_full[s], 1);
+        }
         bars.failed = status_is_set(p.status) ? 1 : 0;
         bars.tmem_base = 0;
         mbar_fence_init();
@@ -388,11 +389,9 @@ __global__ void __launch_bounds__(kThreads, 1)
     } else if (warp == kProducerWarp) {
         // ---------------- producer: weights and scales ----------------
         bool ok = true;
-        int k_stage = first_stage;
         for (int wstage = 0; wstage < num_wstages && ok; ++wstage) {
             const int slot = wstage % kWeightStages;
-            const int first = (s_begin + k_stage) * kStageChunks;  // first 128-element chunk of this stage
-            k_stage = k_stage + 1 == num_wstages ? 0 : k_stage + 1;
+            const int first = (s_begin + wstage) * kStageChunks;  // first 128-element chunk of this stage
             ok = wait_or_fail(&bars.w_empty[slot], ((wstage / kWeightStages) & 1) ^ 1, &bars, p.status);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) {
@@ -475,72 +474,58 @@ __global__ void __launch_bounds__(kThreads, 1)
         }
     } else {
         // ---------------- activation rows: bf16 -> f16, K-major core matrices ----------------
-        // Converting warp w owns operand stage w and the chunks w, w + 4, ...  Lane = activation row
-        // (two half-warps take the two halves of the K cores when only 16 rows are padded in).  The
-        // bf16 rows come global -> shared with cp.async, two chunks ahead of the one being converted,
-        // into staging that is private to the lane; then 16 bytes at a time: load, convert, store in
-        // the operand layout (K cores n_pad * 16 bytes apart, rows 16 bytes apart).
+        // Converting warp w owns operand stage w and the chunks w, w + 4, ...  The bf16 rows of a
+        // chunk come by two tiled TMA copies (boxes of 32 rows x 64 elements with the 128-byte
+        // swizzle; rows past the batch arrive as zeros) which the warp itself issues for its next
+        // chunk as soon as it has read the current one: no load instruction and no address
+        // arithmetic per element is spent on fetching.  Then lane = activation row (two half-warps
+        // take the two halves of the K cores when only 16 rows are padded in): load 16 bytes,
+        // convert, store in the operand layout (K cores n_pad * 16 bytes apart, rows 16 bytes apart).
         static_assert(kConvertWarps == kXStages, "one converting warp per operand stage");
+        static_assert(kRawBuffers == 1, "the staging slot is refilled after it has been read");
         const int w = warp - kFirstConvertWarp;
         const int token = lane & (n_pad - 1);
         const int half = n_pad == 16 ? lane >> 4 : 0;
         const int units = n_pad == 16 ? 8 : 16;          // 16-byte units per lane and chunk
-        const int source_step = n_pad == 16 ? 16 : 8;    // bf16 elements between a lane's units
-        const bool real = token < p.batch;
-        const __nv_bfloat16* source = p.x + (real ? static_cast<size_t>(token) * K + half * 8 : 0);
-        const uint32_t copy_bytes = real ? 16u : 0u;     // padding rows are zero-filled
-        const uint32_t staging = smem_u32(raw_ring) + w * kRawBuffers * (32 * kChunkK * 2) + lane * 16;
+        const int unit_step = n_pad == 16 ? 2 : 1;       // K cores between a lane's units
+        unsigned char* raw_slot = raw_ring + w * (32 * kChunkK * 2);
+        const uint32_t raw_row = smem_u32(raw_slot) + token * 128;
         unsigned char* stage = x_ring + w * x_stage_bytes + half * (n_pad * 16) + (token >> 3) * 128 + (token & 7) * 16;
-        // position of this warp's next chunk to fetch in the CTA's rotated walk over K
-        int fetch_stage = first_stage + w / kStageChunks;
-        fetch_stage -= fetch_stage >= num_wstages ? num_wstages : 0;
-        int fetch_chunk = w;
-        int fetch_buffer = 0;
-        auto fetch = [&]() {
-            if (fetch_chunk < total_chunks) {
-                const int k0 = ((s_begin + fetch_stage) * kStageChunks + (w % kStageChunks)) * kChunkK;
-                const __nv_bfloat16* from = source + (real ? k0 : 0);
-                const uint32_t to = staging + fetch_buffer * (32 * kChunkK * 2);
-#pragma unroll
-                for (int i = 0; i < 16; ++i) {
-                    if (i < units) {
-                        asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(to + i * 512),
-                                     "l"(from + (real ? i * source_step : 0)), "r"(copy_bytes)
-                                     : "memory");
-                    }
-                }
-                fetch_chunk += kConvertWarps;
-                fetch_stage += kConvertWarps / kStageChunks;
-                fetch_stage -= fetch_stage >= num_wstages ? num_wstages : 0;
-                fetch_buffer ^= 1;
+        auto fetch = [&](int c) {  // chunk c of this CTA's slice, c = w (mod 4)
+            if (c < total_chunks && elect_one()) {
+                const int k0 = (s_begin * kStageChunks + c) * kChunkK;
+                mbar_arrive_expect_tx(&bars.raw_full[w], 32 * kChunkK * 2);
+                tma_box_g2s(raw_slot, &x_map, k0, 0, &bars.raw_full[w]);
+                tma_box_g2s(raw_slot + 32 * 128, &x_map, k0 + 64, 0, &bars.raw_full[w]);
             }
-            asm volatile("cp.async.commit_group;" ::: "memory");
+            __syncwarp();
         };
-        static_assert(kConvertWarps % kStageChunks == 0 && kRawBuffers == 2, "fetch bookkeeping");
         bool ok = true;
         // Weights, scales and the whole pipeline above start before the kernel that produces the
         // activations has finished; only these loads wait for it.
         pdl_wait();
-        fetch();
-        fetch();
-        int buffer = 0;
-        uint32_t parity = 1;  // the first use of a stage finds it free
+        fetch(w);
+        uint32_t parity = 1;      // the first use of an operand stage finds it free
+        uint32_t raw_parity = 0;
         for (int c = w; c < total_chunks && ok; c += kConvertWarps) {
-            asm volatile("cp.async.wait_group 1;" ::: "memory");
-            ok = wait_or_fail(&bars.x_free[w], parity, &bars, p.status);
+            ok = wait_or_fail(&bars.raw_full[w], raw_parity, &bars, p.status);
+            if (ok) {
+                ok = wait_or_fail(&bars.x_free[w], parity, &bars, p.status);
+            }
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) {
                 break;
             }
             parity ^= 1;
-            const uint32_t from = staging + buffer * (32 * kChunkK * 2);
+            raw_parity ^= 1;
 #pragma unroll
             for (int i = 0; i < 16; ++i) {
                 if (i < units) {
+                    const int kcore = i * unit_step + half;  // 16-byte piece of the row's 256-byte chunk
                     uint4 raw;
                     asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];"
                                  : "=r"(raw.x), "=r"(raw.y), "=r"(raw.z), "=r"(raw.w)
-                                 : "r"(from + i * 512));
+                                 : "r"(raw_row + (kcore >> 3) * (32 * 128) + (((kcore & 7) ^ (token & 7)) << 4)));
                     *reinterpret_cast<uint4*>(stage + i * 512) = make_uint4(
                         bf16x2_to_f16x2(raw.x), bf16x2_to_f16x2(raw.y), bf16x2_to_f16x2(raw.z), bf16x2_to_f16x2(raw.w));
                 }
@@ -550,10 +535,8 @@ __global__ void __launch_bounds__(kThreads, 1)
             if (lane == 0) {
                 mbar_arrive(&bars.x_full[w]);
             }
-            buffer ^= 1;
-            fetch();  // refills the staging buffer just read
+            fetch(c + kConvertWarps);  // refills the staging slot just read
         }
-        asm volatile("cp.async.wait_group 0;" ::: "memory");
     }
 
     // ---------------- split-K reduction, epilogue ----------------
@@ -705,6 +688,23 @@ cudaError_t launch_nvfp4_umma(const void* packed0, const void* scales0, const vo
     if (encoded != cudaSuccess) {
         return encoded;
     }
+    // The activation rows as a [batch][K] bf16 matrix, fetched in boxes of 32 rows x 64 elements.
+    CUtensorMap x_map;
+    {
+        const EncodeTiled encode = tensor_map_encoder();
+        if (encode == nullptr) {
+            return cudaErrorNotSupported;
+        }
+        const cuuint64_t dims[2] = {static_cast<cuuint64_t>(in_features), static_cast<cuuint64_t>(batch)};
+        const cuuint64_t strides[1] = {static_cast<cuuint64_t>(in_features) * 2};
+        const cuuint32_t box[2] = {64, 32};
+        const cuuint32_t element_strides[2] = {1, 1};
+        if (encode(&x_map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(x), dims, strides, box,
+                   element_strides, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS) {
+            return cudaErrorInvalidValue;
+        }
+    }
     const int smem_bytes =
         kWeightStages * kTiles * kTileStageBytes + (kXStages + kConvertWarps * kRawBuffers) * 32 * kChunkK * 2 + 1024;
     static const cudaError_t opted =
@@ -775,7 +775,7 @@ cudaError_t launch_nvfp4_umma(const void* packed0, const void* scales0, const vo
     attribute[1].val.clusterDim.z = 1;
     config.attrs = attribute;
     config.numAttrs = splits > 1 ? 2 : 1;
-    return cudaLaunchKernelEx(&config, nvfp4_umma_kernel, map0, map1, p);
+    return cudaLaunchKernelEx(&config, nvfp4_umma_kernel, map0, map1, x_map, p);
 }
 
 }  // namespace qwc
