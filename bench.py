@@ -37,7 +37,7 @@ ROWS = 32
 CONTEXT_LOW, CONTEXT_HIGH = 128, 32768
 PAGE = 16
 METRIC = "decode_tokens_per_second"
-NCU_TRAFFIC_RATIO = 109.22 / 100.35  # profiles/nvfp4_umma_34816x5120_m32.md
+NCU_TRAFFIC_RATIO = 104.56 / 100.35  # profiles/nvfp4_umma_34816x5120_m32.md
 
 
 # ---- clocks ---------------------------------------------------------------------------------
@@ -375,7 +375,7 @@ def run_ours(args):
         "roofline": {"bound": "hbm", "kernel": "nvfp4_umma_kernel (all NVFP4 projections of the step)",
                      "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                      "peak_kind": f"of {peak_kind}",
-                     # DRAM read + write of one captured launch (ncu, 34816 x 5120, 32 rows) is 1.09 x its
+                     # DRAM read + write of one captured launch (ncu, 34816 x 5120, 32 rows) is 1.04 x its
                      # algorithmic bytes; every launch streams its matrix once, so traffic scales with it
                      "traffic": bytes_per_launch * NCU_TRAFFIC_RATIO,
                      "bytes_per_launch": bytes_per_launch, "us_per_launch": seconds_per_launch * 1e6,
