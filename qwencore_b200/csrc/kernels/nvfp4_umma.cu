@@ -60,7 +60,7 @@ constexpr int kDequantWarps = kRowWarps * kDequantSets;
 constexpr int kProducerWarp = kDequantWarps;
 constexpr int kMmaWarp = kDequantWarps + 1;
 static_assert(kDequantSets == kStageChunks, "each dequantising warp reads one chunk of every stage");
-constexpr int kConvertWarps = 4;
+constexpr int kConvertWarps = 8;               // two per operand stage: each converts half of a chunk's units
 constexpr int kMmaWarps = 2;  // one issuing warp per tile
 constexpr int kFirstConvertWarp = kMmaWarp + kMmaWarps;
 constexpr int kThreads = (kDequantWarps + 1 + kMmaWarps + kConvertWarps) * 32;
@@ -243,7 +243,7 @@ __global__ void __launch_bounds__(kThreads, 1)
             }
         }
         for (int s = 0; s < kXStages; ++s) {
-            mbar_init(&bars.x_full[s], 1);
+            mbar_init(&bars.x_full[s], kConvertWarps / kXStages);
             mbar_init(&bars.x_free[s], kMmaWarps);
         }
         mbar_init(&bars.d_ready, kMmaWarps);
@@ -481,18 +481,19 @@ __global__ void __launch_bounds__(kThreads, 1)
         // arithmetic per element is spent on fetching.  Then lane = activation row (two half-warps
         // take the two halves of the K cores when only 16 rows are padded in): load 16 bytes,
         // convert, store in the operand layout (K cores n_pad * 16 bytes apart, rows 16 bytes apart).
-        static_assert(kConvertWarps == kXStages, "one converting warp per operand stage");
+        static_assert(kConvertWarps == 2 * kXStages, "two converting warps per operand stage");
         static_assert(kRawBuffers == 1, "the staging slot is refilled after it has been read");
-        const int w = warp - kFirstConvertWarp;
+        const int w = (warp - kFirstConvertWarp) % kXStages;   // operand stage and staging slot
+        const int part = (warp - kFirstConvertWarp) / kXStages;  // which half of the units this warp converts
         const int token = lane & (n_pad - 1);
         const int half = n_pad == 16 ? lane >> 4 : 0;
-        const int units = n_pad == 16 ? 8 : 16;          // 16-byte units per lane and chunk
+        const int units = n_pad == 16 ? 8 : 16;          // 16-byte units per lane and chunk, both warps together
         const int unit_step = n_pad == 16 ? 2 : 1;       // K cores between a lane's units
         unsigned char* raw_slot = raw_ring + w * (32 * kChunkK * 2);
         const uint32_t raw_row = smem_u32(raw_slot) + token * 128;
         unsigned char* stage = x_ring + w * x_stage_bytes + half * (n_pad * 16) + (token >> 3) * 128 + (token & 7) * 16;
-        auto fetch = [&](int c) {  // chunk c of this CTA's slice, c = w (mod 4)
-            if (c < total_chunks && elect_one()) {
+        auto fetch = [&](int c) {  // chunk c of this CTA's slice, c = w (mod 4); issued by the part-0 warp
+            if (part == 0 && c < total_chunks && elect_one()) {
                 const int k0 = (s_begin * kStageChunks + c) * kChunkK;
                 mbar_arrive_expect_tx(&bars.raw_full[w], 32 * kChunkK * 2);
                 tma_box_g2s(raw_slot, &x_map, k0, 0, &bars.raw_full[w]);
@@ -507,7 +508,7 @@ __global__ void __launch_bounds__(kThreads, 1)
         fetch(w);
         uint32_t parity = 1;      // the first use of an operand stage finds it free
         uint32_t raw_parity = 0;
-        for (int c = w; c < total_chunks && ok; c += kConvertWarps) {
+        for (int c = w; c < total_chunks && ok; c += kXStages) {
             ok = wait_or_fail(&bars.raw_full[w], raw_parity, &bars, p.status);
             if (ok) {
                 ok = wait_or_fail(&bars.x_free[w], parity, &bars, p.status);
@@ -516,10 +517,9 @@ __global__ void __launch_bounds__(kThreads, 1)
             if (!ok) {
                 break;
             }
-            parity ^= 1;
-            raw_parity ^= 1;
 #pragma unroll
-            for (int i = 0; i < 16; ++i) {
+            for (int j = 0; j < 8; ++j) {
+                const int i = 2 * j + part;  // the two warps of a stage take alternate units
                 if (i < units) {
                     const int kcore = i * unit_step + half;  // 16-byte piece of the row's 256-byte chunk
                     uint4 raw;
@@ -535,7 +535,18 @@ __global__ void __launch_bounds__(kThreads, 1)
             if (lane == 0) {
                 mbar_arrive(&bars.x_full[w]);
             }
-            fetch(c + kConvertWarps);  // refills the staging slot just read
+            if (part == 0 && c + kXStages < total_chunks) {
+                // the staging slot may be refilled once both warps have read it: that is when the
+                // operand stage's barrier completes its phase
+                ok = wait_or_fail(&bars.x_full[w], parity ^ 1, &bars, p.status);
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) {
+                    break;
+                }
+            }
+            parity ^= 1;
+            raw_parity ^= 1;
+            fetch(c + kXStages);
         }
     }
 
@@ -706,7 +717,7 @@ cudaError_t launch_nvfp4_umma(const void* packed0, const void* scales0, const vo
         }
     }
     const int smem_bytes =
-        kWeightStages * kTiles * kTileStageBytes + (kXStages + kConvertWarps * kRawBuffers) * 32 * kChunkK * 2 + 1024;
+        kWeightStages * kTiles * kTileStageBytes + (kXStages + kXStages * kRawBuffers) * 32 * kChunkK * 2 + 1024;
     static const cudaError_t opted =
         cudaFuncSetAttribute(nvfp4_umma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
     if (opted != cudaSuccess) {
