@@ -540,21 +540,24 @@ __global__ void __launch_bounds__(kThreads, 1) paged_attention_packed_kernel(
     }
 }
 
-// Log-sum-exp merge of the partitions, output gate, bf16 store: one warp per
-// (row, head), eight dims per lane (as cuda/paged_attention.cu:1736-1823).
-__global__ void __launch_bounds__(256) reduce_partitions_kernel(
+// Log-sum-exp merge of the partitions, output gate, bf16 store (as cuda/paged_attention.cu:1736-1823).
+// One CTA of four warps per (row, head): the longest row of a ragged batch has dozens of partials,
+// and a single warp walking them is a chain of dependent memory round trips.  Warp w takes the
+// partials w, w + 4, ... (eight dims per lane), the four sums meet in shared memory in warp order.
+constexpr int kMergeWarps = 4;
+
+__global__ void __launch_bounds__(kMergeWarps * 32) reduce_partitions_kernel(
     const float* __restrict__ partial_stats, const __half* __restrict__ partial_out,
     const __nv_bfloat16* __restrict__ query_gate_projection, const uint32_t* __restrict__ context_lengths,
     __nv_bfloat16* __restrict__ output, int rows, int partitions, int row_base, int gate_stride, int capacity_units,
     int plan_ctas) {
     pdl_launch_dependents();  // the output projection may start streaming its weights
     pdl_wait();
-    const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    __shared__ float sums[kMergeWarps][kHeadDim];
+    __shared__ float denominators[kMergeWarps];
+    const int pair = blockIdx.x;  // (row, head)
+    const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
-    const int pairs = rows * kQueryHeads;
-    if (warp >= pairs) {
-        return;
-    }
     // The same plan as the attention kernel made: this row has `used` partials, the rest of its
     // slots were never written.
     long long total_units = 0;
@@ -567,10 +570,9 @@ __global__ void __launch_bounds__(256) reduce_partitions_kernel(
     }
     const int units_per_task = plan_units_per_task(total_units, capacity_units, partitions, plan_ctas);
     const int used = parts_of_row(
-        units_of_context(context_lengths[row_base + warp / kQueryHeads], capacity_units), units_per_task);
-    const float* stats = partial_stats + static_cast<size_t>(warp) * partitions * kPartialFloats;
-    // Lanes take the partials' statistics side by side (32 per round); the partial outputs are then
-    // read four at a time so that their latencies overlap.  The order of the additions is fixed.
+        units_of_context(context_lengths[row_base + pair / kQueryHeads], capacity_units), units_per_task);
+    const float* stats = partial_stats + static_cast<size_t>(pair) * partitions * kPartialFloats;
+    // every warp finds the maximum over all partials (lanes side by side) ...
     float maximum = -INFINITY;
     for (int p = lane; p < used; p += 32) {
         const float2 pair_stats = *reinterpret_cast<const float2*>(stats + 2 * p);
@@ -582,47 +584,63 @@ __global__ void __launch_bounds__(256) reduce_partitions_kernel(
     for (int offset = 16; offset > 0; offset >>= 1) {
         maximum = fmaxf(maximum, __shfl_xor_sync(0xffffffffu, maximum, offset));
     }
+    // ... and sums its own quarter of them, four outputs in flight at a time
     float denominator = 0.0f;
     float acc[8] = {0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f};
-    const __half* outs = partial_out + static_cast<size_t>(warp) * partitions * kHeadDim + 8 * lane;
-    for (int base = 0; base < used; base += 32) {
-        const int mine = base + lane;
-        float my_weight = 0.0f;
-        if (mine < used) {
-            const float2 pair_stats = *reinterpret_cast<const float2*>(stats + 2 * mine);
-            my_weight = pair_stats.y > 0.0f ? pair_stats.y * exp2f(pair_stats.x - maximum) : 0.0f;
-        }
-        const int count = min(32, used - base);
-        for (int first = 0; first < count; first += 4) {
-            uint4 raw[4];
-            float weight[4];
+    const __half* outs = partial_out + static_cast<size_t>(pair) * partitions * kHeadDim + 8 * lane;
+    for (int first = warp; first < used; first += 4 * kMergeWarps) {
+        uint4 raw[4];
+        float weight[4];
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                const int q = first + j;
-                weight[j] = __shfl_sync(0xffffffffu, my_weight, q & 31);
-                raw[j] = make_uint4(0, 0, 0, 0);
-                if (q < count) {
-                    raw[j] = *reinterpret_cast<const uint4*>(outs + static_cast<size_t>(base + q) * kHeadDim);
-                } else {
-                    weight[j] = 0.0f;
-                }
+        for (int j = 0; j < 4; ++j) {
+            const int p = first + j * kMergeWarps;
+            weight[j] = 0.0f;
+            raw[j] = make_uint4(0, 0, 0, 0);
+            if (p < used) {
+                const float2 pair_stats = *reinterpret_cast<const float2*>(stats + 2 * p);
+                weight[j] = pair_stats.y > 0.0f ? pair_stats.y * exp2f(pair_stats.x - maximum) : 0.0f;
+                raw[j] = *reinterpret_cast<const uint4*>(outs + static_cast<size_t>(p) * kHeadDim);
             }
+        }
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                denominator += weight[j];
-                const __half2* h = reinterpret_cast<const __half2*>(&raw[j]);
+        for (int j = 0; j < 4; ++j) {
+            denominator += weight[j];
+            const __half2* h = reinterpret_cast<const __half2*>(&raw[j]);
 #pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    const float2 f = __half22float2(h[i]);
-                    acc[2 * i] += weight[j] * f.x;
-                    acc[2 * i + 1] += weight[j] * f.y;
-                }
+            for (int i = 0; i < 4; ++i) {
+                const float2 f = __half22float2(h[i]);
+                acc[2 * i] += weight[j] * f.x;
+                acc[2 * i + 1] += weight[j] * f.y;
             }
         }
     }
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        sums[warp][8 * lane + i] = acc[i];
+    }
+    if (lane == 0) {
+        denominators[warp] = denominator;
+    }
+    __syncthreads();
+    if (warp != 0) {
+        return;
+    }
+    denominator = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        acc[i] = 0.0f;
+    }
+#pragma unroll
+    for (int w = 0; w < kMergeWarps; ++w) {
+        denominator += denominators[w];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            acc[i] += sums[w][8 * lane + i];
+        }
+    }
     const float inverse = denominator > 0.0f ? 1.0f / denominator : 0.0f;
-    const int row = row_base + warp / kQueryHeads;
-    const int head = warp % kQueryHeads;
+    const int row = row_base + pair / kQueryHeads;
+    const int head = pair % kQueryHeads;
     float gates[8] = {1.0f, 1.0f, 1.0f, 1.0f, 1.0f, 1.0f, 1.0f, 1.0f};
     if (query_gate_projection != nullptr) {
         const uint4 graw = *reinterpret_cast<const uint4*>(
@@ -713,7 +731,7 @@ cudaError_t launch_attention(const void* query, const void* query_gate_projectio
         return launched;
     }
     const int pairs = rows * kQueryHeads;
-    return qwc::launch_chained(reduce_partitions_kernel, dim3((pairs + 7) / 8), dim3(256), 0, stream, 
+    return qwc::launch_chained(reduce_partitions_kernel, dim3(pairs), dim3(kMergeWarps * 32), 0, stream, 
         partial_stats, partial_out, static_cast<const __nv_bfloat16*>(query_gate_projection),
         static_cast<const uint32_t*>(context_lengths), static_cast<__nv_bfloat16*>(output), rows, partitions, row_base,
         gate_stride, max_blocks * (page_size / kUnitTokens), sms);
