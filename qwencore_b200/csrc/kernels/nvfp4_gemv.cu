@@ -41,10 +41,12 @@ namespace cg = cooperative_groups;
 
 namespace qwc {
 
-// tcgen05 path for 9..32 rows (nvfp4_umma.cu).
+// tcgen05 paths (nvfp4_umma.cu): NVFP4 projections, and the e4m3 vocabulary head.
 cudaError_t launch_nvfp4_umma(const void* packed0, const void* scales0, const void* packed1, const void* scales1,
                               const void* x, void* y, int out_features, int in_features, int batch, float inverse0,
                               float inverse1, bool swiglu, cudaStream_t stream);
+cudaError_t launch_fp8_umma(const void* weights, const float* row_scales, const void* x, float* logits,
+                            int out_features, int in_features, int batch, cudaStream_t stream);
 
 namespace {
 
@@ -632,12 +634,18 @@ cudaError_t dispatch(const GemvParams& p, cudaStream_t stream) {
     // longer start-up (TMEM allocation, first TMA round trip, cluster reduction): it takes over
     // above eight rows, and below that for matrices of 30 MB and more.
     const bool large = static_cast<long long>(p.out_features) * p.in_features >= 60ll * 1000 * 1000;
-    if (MODE == kFp8Rows ? p.batch <= 8 : (p.batch <= 8 && !large)) {
-        return launch<1, 1, MODE>(p, stream);
-    }
     // its stores are 16 bytes wide and its activation fetch is a tiled TMA copy
     const bool aligned = p.out_features % 8 == 0 && (reinterpret_cast<uintptr_t>(p.y) & 15) == 0 &&
-                         (reinterpret_cast<uintptr_t>(p.x) & 15) == 0;
+                         (reinterpret_cast<uintptr_t>(p.x) & 15) == 0 &&
+                         (MODE != kFp8Rows || ((reinterpret_cast<uintptr_t>(p.y_f32) & 15) == 0 &&
+                                               (reinterpret_cast<uintptr_t>(p.row_scales) & 15) == 0));
+    if (p.batch <= 8 && !(large && aligned)) {
+        return launch<1, 1, MODE>(p, stream);
+    }
+    if (MODE == kFp8Rows && aligned) {
+        return launch_fp8_umma(p.packed[0], p.row_scales, p.x, p.y_f32, p.out_features, p.in_features, p.batch,
+                               stream);
+    }
     if (MODE != kFp8Rows && aligned) {
         // Above eight rows the legacy tensor path cannot keep up with the weight stream.
         return launch_nvfp4_umma(p.packed[0], p.scales[0], p.packed[1], p.scales[1], p.x, p.y, p.out_features,

@@ -1,4 +1,5 @@
-// NVFP4 W4A16 skinny GEMM for 9..32 activation rows on the 5th-generation tensor cores.
+// NVFP4 W4A16 skinny GEMM for up to 32 activation rows on the 5th-generation tensor cores, and the
+// FP8 vocabulary head through the same pipeline.
 //
 // Same contract as nvfp4_gemv.cu (crates/qwc-cuda/cuda/nvfp4.cu:489-537, :585-643); this file
 // serves the batches where the legacy mma.sync path runs out of tensor throughput: a profile of
@@ -25,9 +26,14 @@
 //               matrices) from shared memory, and tcgen05.commit to hand buffers back.  The
 //               instructions sit in an elect.sync region: issued from `lane == 0` they cost three
 //               times as many cycles each.
-//   warps 19-22 convert the activation rows bf16 -> f16 into the B layout; warp w owns operand
-//               stage w and every fourth chunk, and fetches the bf16 rows of its next chunk with
-//               two tiled TMA copies as soon as it has read the current one.
+//   warps 19-26 convert the activation rows bf16 -> f16 into the B layout; two warps share operand
+//               stage w and every fourth chunk, and the first of them fetches the bf16 rows of the
+//               next chunk with two tiled TMA copies as soon as both have read the current one.
+//
+// Vocabulary-head mode (crates/qwc-cuda/cuda/vocab_fp8.cu:255: e4m3 bytes [vocab][hidden], one fp32
+// scale per row, fp32 logits): a stage is one 128-element chunk (the same 128-byte box), there are
+// no block scales, each dequantising set reads every other stage, and the row scale multiplies the
+// accumulator in the epilogue.
 //
 // Every wait is bounded; a wait that gives up records a code in the status word, the CTA skips
 // its stores, frees its TMEM and returns.
@@ -85,6 +91,11 @@ struct UmmaParams {
     int row_groups;  // 128-row (swiglu) or 256-row groups
     int splits;
     int* status;
+    // FP8 rows (the vocabulary head): e4m3 weights, one byte per element, no block scales; a stage
+    // then holds one 128-element chunk per row instead of two; fp32 output times a per-row scale.
+    int fp8;
+    const float* row_scales;
+    float* y_f32;
 };
 
 
@@ -209,11 +220,12 @@ __global__ void __launch_bounds__(kThreads, 1)
     const int split = blockIdx.x - row_group * p.splits;
     const int K = p.in_features;
     // K is cut into stages of 256 elements; a slice is a whole number of stages.
-    const int stages_in_k = K / (kChunkK * kStageChunks);
+    const int stage_chunks = p.fp8 ? 1 : kStageChunks;  // 128 bytes per row and stage either way
+    const int stages_in_k = K / (kChunkK * stage_chunks);
     const int s_begin = static_cast<int>(static_cast<long long>(stages_in_k) * split / p.splits);
     const int s_end = static_cast<int>(static_cast<long long>(stages_in_k) * (split + 1) / p.splits);
     const int num_wstages = s_end - s_begin;
-    const int total_chunks = num_wstages * kStageChunks;
+    const int total_chunks = num_wstages * stage_chunks;
     const int group_blocks = K / 64;
     const int n_pad = p.n_pad;
     const int x_stage_bytes = n_pad * kChunkK * 2;
@@ -234,7 +246,7 @@ __global__ void __launch_bounds__(kThreads, 1)
     if (threadIdx.x == 0) {
         for (int s = 0; s < kWeightStages; ++s) {
             mbar_init(&bars.w_full[s], 1);
-            mbar_init(&bars.w_empty[s], kDequantWarps);
+            mbar_init(&bars.w_empty[s], p.fp8 ? kRowWarps : kDequantWarps);  // warps that read a stage
         }
         for (int t = 0; t < kTiles; ++t) {
             for (int b = 0; b < kABuffers; ++b) {
@@ -311,7 +323,7 @@ __global__ void __launch_bounds__(kThreads, 1)
             }
         };
         for (int c = set; c < total_chunks && ok; c += kDequantSets) {
-            const int wstage = c / kStageChunks;
+            const int wstage = p.fp8 ? c : c / kStageChunks;
             const int slot = wstage % kWeightStages;
             const int q = set;
             ok = wait_or_fail(&bars.w_full[slot], (wstage / kWeightStages) & 1, &bars, p.status);
@@ -321,6 +333,35 @@ __global__ void __launch_bounds__(kThreads, 1)
             }
             const unsigned char* stage = weight_ring + (slot * kTiles + tile) * kTileStageBytes;
             const unsigned char* row = stage + row_offset;
+            const int buf = c % kABuffers;
+            if (p.fp8) {
+                // 128 e4m3 bytes of this row: one conversion per pair, no block scale (the per-row
+                // scale is applied to the accumulator in the epilogue)
+                uint4 bytes[8];
+#pragma unroll
+                for (int piece = 0; piece < 8; ++piece) {
+                    bytes[piece] = *reinterpret_cast<const uint4*>(row + ((piece ^ row_swizzle) << 4));
+                }
+                ok = wait_or_fail(&bars.a_free[tile][buf], ((c / kABuffers) & 1) ^ 1, &bars, p.status);
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) {
+                    break;
+                }
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll
+                for (int part = 0; part < 4; ++part) {
+                    uint32_t out[16];
+#pragma unroll
+                    for (int piece = 0; piece < 2; ++piece) {
+                        const uint4 raw = bytes[2 * part + piece];
+                        cvt_e4m3x4_to_f16x2(raw.x, out[8 * piece + 0], out[8 * piece + 1]);
+                        cvt_e4m3x4_to_f16x2(raw.y, out[8 * piece + 2], out[8 * piece + 3]);
+                        cvt_e4m3x4_to_f16x2(raw.z, out[8 * piece + 4], out[8 * piece + 5]);
+                        cvt_e4m3x4_to_f16x2(raw.w, out[8 * piece + 6], out[8 * piece + 7]);
+                    }
+                    tmem_store16(lane_address + buf * 64 + part * 16, out);
+                }
+            } else {
             const unsigned char* scale_tiles = stage + kBoxBytes + q * 1024 + scale_offset;
             uint4 raw[4];
 #pragma unroll
@@ -330,7 +371,6 @@ __global__ void __launch_bounds__(kThreads, 1)
             // 8 block scales of this chunk: two words of four e4m3 (cuda/nvfp4.cu:33-39 layout)
             const uint32_t scale_word0 = *reinterpret_cast<const uint32_t*>(scale_tiles);
             const uint32_t scale_word1 = *reinterpret_cast<const uint32_t*>(scale_tiles + 512);
-            const int buf = c % kABuffers;
             ok = wait_or_fail(&bars.a_free[tile][buf], ((c / kABuffers) & 1) ^ 1, &bars, p.status);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) {
@@ -362,6 +402,7 @@ __global__ void __launch_bounds__(kThreads, 1)
                     }
                 }
                 tmem_store16(lane_address + buf * 64 + part * 16, out);
+            }
             }
             previous_buf = buf;
             previous_slot = slot;  // this warp reads one chunk per stage
@@ -408,12 +449,18 @@ __global__ void __launch_bounds__(kThreads, 1)
                 for (int t = 0; t < kTiles; ++t) {
                     scale_tiles_present += tile_row0[t] < p.out_features ? 1 : 0;
                 }
+                if (p.fp8) {
+                    scale_tiles_present = 0;  // one float per row, applied in the epilogue
+                }
                 mbar_arrive_expect_tx(&bars.w_full[slot], kTiles * kBoxBytes + scale_tiles_present * n * 1024);
+                // Byte offset of the stage within a row: 64 bytes per 128 four-bit elements, or one
+                // 128-byte box per 128 e4m3 elements.
+                const int byte0 = p.fp8 ? (s_begin + wstage) * 128 : first * 64;
 #pragma unroll
                 for (int t = 0; t < kTiles; ++t) {
                     unsigned char* stage = weight_ring + (slot * kTiles + t) * kTileStageBytes;
-                    tma_box_g2s(stage, t == 1 ? &map1 : &map0, first * 64, tile_row0[t], &bars.w_full[slot]);
-                    if (tile_row0[t] < p.out_features) {
+                    tma_box_g2s(stage, t == 1 ? &map1 : &map0, byte0, tile_row0[t], &bars.w_full[slot]);
+                    if (!p.fp8 && tile_row0[t] < p.out_features) {
                         bulk_g2s(stage + kBoxBytes,
                                  tile_scales[t] + (static_cast<size_t>(tile_row0[t] >> 7) * group_blocks + 2 * first) * 512,
                                  n * 1024, &bars.w_full[slot]);
@@ -494,7 +541,7 @@ __global__ void __launch_bounds__(kThreads, 1)
         unsigned char* stage = x_ring + w * x_stage_bytes + half * (n_pad * 16) + (token >> 3) * 128 + (token & 7) * 16;
         auto fetch = [&](int c) {  // chunk c of this CTA's slice, c = w (mod 4); issued by the part-0 warp
             if (part == 0 && c < total_chunks && elect_one()) {
-                const int k0 = (s_begin * kStageChunks + c) * kChunkK;
+                const int k0 = (s_begin * stage_chunks + c) * kChunkK;
                 mbar_arrive_expect_tx(&bars.raw_full[w], 32 * kChunkK * 2);
                 tma_box_g2s(raw_slot, &x_map, k0, 0, &bars.raw_full[w]);
                 tma_box_g2s(raw_slot + 32 * 128, &x_map, k0 + 64, 0, &bars.raw_full[w]);
@@ -594,7 +641,16 @@ __global__ void __launch_bounds__(kThreads, 1)
                 }
             }
             const int row = row0 + r8;
-            if (row < p.out_features) {  // out_features is a multiple of 8: a unit is inside or outside
+            if (row < p.out_features && p.fp8) {
+                // vocabulary head: fp32 logits, one scale per weight row
+                const float4 s_lo = *reinterpret_cast<const float4*>(p.row_scales + row);
+                const float4 s_hi = *reinterpret_cast<const float4*>(p.row_scales + row + 4);
+                float* out = p.y_f32 + static_cast<size_t>(token) * p.out_features + row;
+                *reinterpret_cast<float4*>(out) =
+                    make_float4(first[0] * s_lo.x, first[1] * s_lo.y, first[2] * s_lo.z, first[3] * s_lo.w);
+                *reinterpret_cast<float4*>(out + 4) =
+                    make_float4(first[4] * s_hi.x, first[5] * s_hi.y, first[6] * s_hi.z, first[7] * s_hi.w);
+            } else if (row < p.out_features) {  // out_features is a multiple of 8: a unit is inside or outside
                 uint32_t packed[4];
 #pragma unroll
                 for (int i = 0; i < 4; ++i) {
@@ -641,14 +697,14 @@ EncodeTiled tensor_map_encoder() {
     return encoder;
 }
 
-// Packed nibbles as a [rows][K / 2] byte matrix, fetched in boxes of 128 rows x 128 bytes.
-cudaError_t encode_weight_map(CUtensorMap* map, const void* packed, int out_features, int in_features) {
+// Weight bytes as a [rows][row_bytes] matrix, fetched in boxes of 128 rows x 128 bytes.
+cudaError_t encode_weight_map(CUtensorMap* map, const void* packed, int out_features, int row_bytes) {
     const EncodeTiled encode = tensor_map_encoder();
     if (encode == nullptr) {
         return cudaErrorNotSupported;
     }
-    const cuuint64_t dims[2] = {static_cast<cuuint64_t>(in_features / 2), static_cast<cuuint64_t>(out_features)};
-    const cuuint64_t strides[1] = {static_cast<cuuint64_t>(in_features / 2)};
+    const cuuint64_t dims[2] = {static_cast<cuuint64_t>(row_bytes), static_cast<cuuint64_t>(out_features)};
+    const cuuint64_t strides[1] = {static_cast<cuuint64_t>(row_bytes)};
     const cuuint32_t box[2] = {kBoxRowBytes, kTileRows};
     const cuuint32_t element_strides[2] = {1, 1};
     const CUresult result =
@@ -672,18 +728,12 @@ int sm_count_umma() {
 }  // namespace
 
 
-cudaError_t launch_nvfp4_umma(const void* packed0, const void* scales0, const void* packed1, const void* scales1,
-                              const void* x, void* y, int out_features, int in_features, int batch, float inverse0,
-                              float inverse1, bool swiglu, cudaStream_t stream) {
-    UmmaParams p = {};
-    p.packed[0] = static_cast<const uint8_t*>(packed0);
-    p.scales[0] = static_cast<const uint8_t*>(scales0);
-    p.packed[1] = static_cast<const uint8_t*>(swiglu ? packed1 : packed0);
-    p.scales[1] = static_cast<const uint8_t*>(swiglu ? scales1 : scales0);
+namespace {
+
+// Fills the launch-dependent fields of p (its operand pointers and mode are the caller's) and launches.
+cudaError_t launch_umma(UmmaParams p, const void* x, int out_features, int in_features, int batch, bool swiglu,
+                        cudaStream_t stream) {
     p.x = static_cast<const __nv_bfloat16*>(x);
-    p.y = static_cast<__nv_bfloat16*>(y);
-    p.inverse_scale[0] = inverse0;
-    p.inverse_scale[1] = inverse1;
     p.out_features = out_features;
     p.in_features = in_features;
     p.batch = batch;
@@ -691,10 +741,12 @@ cudaError_t launch_nvfp4_umma(const void* packed0, const void* scales0, const vo
     p.swiglu = swiglu ? 1 : 0;
     const int rows_per_group = swiglu ? kTileRows : kTiles * kTileRows;
     p.row_groups = (out_features + rows_per_group - 1) / rows_per_group;
+    // bytes of one weight row: two elements per byte, or one e4m3 byte each
+    const int row_bytes = p.fp8 ? in_features : in_features / 2;
     CUtensorMap map0, map1;
-    cudaError_t encoded = encode_weight_map(&map0, p.packed[0], out_features, in_features);
+    cudaError_t encoded = encode_weight_map(&map0, p.packed[0], out_features, row_bytes);
     if (encoded == cudaSuccess) {
-        encoded = encode_weight_map(&map1, p.packed[1], out_features, in_features);
+        encoded = encode_weight_map(&map1, p.packed[1], out_features, row_bytes);
     }
     if (encoded != cudaSuccess) {
         return encoded;
@@ -753,11 +805,12 @@ cudaError_t launch_nvfp4_umma(const void* packed0, const void* scales0, const vo
         return r;
     }();
     const int chunks = in_features / kChunkK;
+    const int stage_chunks = p.fp8 ? 1 : kStageChunks;
     int splits = 1;
     double best_cost = 1e30;
     for (int size = 1; size <= 8; ++size) {
         const int clusters = size == 1 ? sm_count_umma() : residency.clusters[size];
-        if (clusters <= 0 || (size > 1 && chunks / size < 2 * kStageChunks)) {
+        if (clusters <= 0 || (size > 1 && chunks / size < 2 * stage_chunks)) {
             continue;
         }
         const int waves = (p.row_groups + clusters - 1) / clusters;
@@ -787,6 +840,36 @@ cudaError_t launch_nvfp4_umma(const void* packed0, const void* scales0, const vo
     config.attrs = attribute;
     config.numAttrs = splits > 1 ? 2 : 1;
     return cudaLaunchKernelEx(&config, nvfp4_umma_kernel, map0, map1, x_map, p);
+}
+
+}  // namespace
+
+cudaError_t launch_nvfp4_umma(const void* packed0, const void* scales0, const void* packed1, const void* scales1,
+                              const void* x, void* y, int out_features, int in_features, int batch, float inverse0,
+                              float inverse1, bool swiglu, cudaStream_t stream) {
+    UmmaParams p = {};
+    p.packed[0] = static_cast<const uint8_t*>(packed0);
+    p.scales[0] = static_cast<const uint8_t*>(scales0);
+    p.packed[1] = static_cast<const uint8_t*>(swiglu ? packed1 : packed0);
+    p.scales[1] = static_cast<const uint8_t*>(swiglu ? scales1 : scales0);
+    p.y = static_cast<__nv_bfloat16*>(y);
+    p.inverse_scale[0] = inverse0;
+    p.inverse_scale[1] = inverse1;
+    return launch_umma(p, x, out_features, in_features, batch, swiglu, stream);
+}
+
+// The vocabulary head through the same pipeline: e4m3 weight bytes [vocab][hidden], one fp32 scale per
+// row, fp32 logits [batch][vocab].  hidden a multiple of 128, vocab of 8, logits 16-byte aligned.
+cudaError_t launch_fp8_umma(const void* weights, const float* row_scales, const void* x, float* logits,
+                            int out_features, int in_features, int batch, cudaStream_t stream) {
+    UmmaParams p = {};
+    p.packed[0] = p.packed[1] = static_cast<const uint8_t*>(weights);
+    p.scales[0] = p.scales[1] = nullptr;
+    p.fp8 = 1;
+    p.row_scales = row_scales;
+    p.y_f32 = logits;
+    p.inverse_scale[0] = p.inverse_scale[1] = 1.0f;
+    return launch_umma(p, x, out_features, in_features, batch, false, stream);
 }
 
 }  // namespace qwc

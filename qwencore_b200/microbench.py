@@ -186,9 +186,31 @@ def contexts_for(kind: str, rows: int, low: int, high: int):
     raise SystemExit(f"unknown context distribution {kind}")
 
 
+def lm_head(vocab: int, hidden: int, rows: int, plain: int = 0) -> dict:
+    """The FP8 vocabulary head: e4m3 weight bytes, one fp32 scale per row, fp32 logits."""
+    generator = torch.Generator(device="cuda")
+    generator.manual_seed(0)
+    copies = max(2, -(-2 * L2_BYTES // (vocab * hidden))) if not plain else 2
+    tables = [torch.randint(0x20, 0x48, (vocab, hidden), dtype=torch.uint8, device="cuda", generator=generator)
+              for _ in range(copies)]
+    scales = torch.full((vocab,), 0.01, dtype=torch.float32, device="cuda")
+    x = _dev(synth.normal_bf16(0, "x", (rows, hidden)))
+    logits = torch.zeros((rows, vocab), dtype=torch.float32, device="cuda")
+    counter = [0]
+
+    def launch():
+        index = counter[0] % copies
+        counter[0] += 1
+        ops.fp8_lm_head(tables[index], scales, x, logits, rows, hidden, vocab)
+
+    microseconds = time_launches(launch, 4 * copies, plain)
+    nbytes = vocab * hidden + vocab * 4 + rows * hidden * 2 + rows * vocab * 4
+    return report(f"lm_head V={vocab} K={hidden} M={rows}", microseconds, nbytes)
+
+
 def main(argv=None) -> None:
     parser = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
-    parser.add_argument("kernel", choices=["gemv", "swiglu", "delta", "attention", "all"])
+    parser.add_argument("kernel", choices=["gemv", "swiglu", "lm_head", "delta", "attention", "all"])
     parser.add_argument("args", nargs="*")
     parser.add_argument("--partitions", type=int, default=0)
     parser.add_argument("--page", type=int, default=16)
@@ -201,6 +223,8 @@ def main(argv=None) -> None:
     if options.kernel in ("gemv", "swiglu"):
         n, k, m = (int(v) for v in values[:3])
         projection(n, k, m, swiglu=options.kernel == "swiglu", plain=options.plain)
+    elif options.kernel == "lm_head":
+        lm_head(int(values[0]), int(values[1]), int(values[2]), plain=options.plain)
     elif options.kernel == "delta":
         delta(int(values[0]), int(values[1]), plain=options.plain)
     elif options.kernel == "attention":
@@ -216,6 +240,8 @@ def main(argv=None) -> None:
             projection(12352, 5120, rows)
             projection(14336, 5120, rows)
             projection(5120, 6144, rows)
+        for rows in (1, 8, 32):
+            lm_head(151936, 5120, rows)
         for heads in (48, 32):
             delta(32, heads)
             delta(1, heads)

@@ -383,10 +383,14 @@ def test_fp8_embedding_gather_is_bit_exact(cuda, ops):
     assert not host(out)[3:].any()
 
 
-@pytest.mark.parametrize("batch", [1, 8, 32])
-def test_fp8_lm_head_and_argmax(cuda, ops, batch):
+# 5003: not a multiple of the row tile nor of the 16-byte store (the mma.sync kernel at every batch size);
+# 5000: stores aligned, a ragged last tile (above eight rows the tcgen05 kernel); 12000: a table large
+# enough that the tcgen05 kernel takes every batch size.
+@pytest.mark.parametrize("batch,vocab", [(1, 5003), (8, 5003), (32, 5003), (8, 5000), (9, 5000), (16, 5000),
+                                         (17, 5000), (32, 5000), (32, 4096), (1, 12000), (5, 12000)])
+def test_fp8_lm_head_and_argmax(cuda, ops, batch, vocab):
     torch = cuda
-    vocab, hidden = 5003, 5120  # vocabulary not a multiple of the row tile
+    hidden = 5120
     rows = synth.normal_bf16(8, "head", (vocab, hidden), std=0.02)
     weights, scales = oracle.fp8_quantize_rows(rows, vocab, hidden)
     x = synth.normal_bf16(8, f"h{batch}", (batch, hidden))
