@@ -29,6 +29,7 @@ constexpr int kStatusOk = 0;
 constexpr int kStatusAttentionPageWait = 0x101;
 constexpr int kStatusDeltaTileWait = 0x102;
 constexpr int kStatusGemvWait = 0x103;
+constexpr int kStatusAttentionPlanOverflow = 0x104;  // a CTA's task list would not hold its share
 
 // Process-wide shape selection (see qwc_configure in the C ABI).
 struct Shape {

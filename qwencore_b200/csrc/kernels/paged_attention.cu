@@ -9,11 +9,12 @@
 // The op reads every K and V byte of the row's context once and nothing else of size,
 // so it is HBM-bound.  Layout for sm_100a:
 //   * a persistent grid of one CTA per SM.  The rows of a ragged batch differ in context by
-//     orders of magnitude, so the work is cut on the device into tasks of equal size: a task
-//     is (row, kv head, span of units_per_task 16-token units), units_per_task chosen from
-//     the sum of the rows' contexts so that every CTA gets about six tasks, and CTA c takes
-//     tasks c, c + grid, ...  The launch shape depends only on the SM count, so the step
-//     stays capturable in a CUDA graph whatever the contexts are;
+//     orders of magnitude, so the work is cut on the device into equal shares: the 16-token
+//     units of all (row, kv head) pairs are laid end to end, CTA c owns positions
+//     [c share, (c + 1) share) of that line, and a task is the piece of one pair inside one
+//     CTA's share (its partial is merged by the second kernel).  Every CTA streams the same
+//     number of bytes whatever the contexts are, and the launch shape depends only on the SM
+//     count, so the step stays capturable in a CUDA graph;
 //   * inside a CTA one producer warp and eight consumer warps.  KV moves in 4 KiB units (16
 //     tokens x 256 B of one kv head: a whole 16-token page, or a quarter of a 64-token page)
 //     by bulk-async copies (TMA 1-D) into a 3-stage ring of 8 units (128 tokens, 64 KiB of
@@ -50,8 +51,9 @@ constexpr int kStageBytes = kStageUnits * kUnitPitch;    // per K or V
 constexpr int kPartialFloats = 2;
 constexpr size_t kPartialBytes = 2 * sizeof(float) + kHeadDim * sizeof(__half);  // 520
 constexpr float kLog2e = 1.4426950408889634f;
-constexpr int kTasksPerCta = 6;       // target when the task size is chosen
 constexpr int kMaxCtaTasks = 64;      // list capacity; the plan keeps a CTA far below it
+constexpr int kPlanMinPadding = 8;    // units a task costs beyond its tokens (query load, epilogue, merge)
+constexpr int kPlanPaddingDivisor = 24;  // padding = share / this at least: bounds the tasks of one CTA
 constexpr int kPlanRows = 256;        // rows whose prefix fits the shared-memory table
 
 struct Task {
@@ -71,10 +73,9 @@ struct Smem {
     float warp_sum[kConsumerWarps][8];
     uint64_t full[kStages];
     uint64_t empty[kStages];
-    int first_pair[kPlanRows + 1];  // prefix sum of the rows' task counts (per kv head)
+    int first_unit[kPlanRows + 1];  // prefix sum of the rows' units (a row without context counts one)
     Task tasks[kMaxCtaTasks];
     int task_count;
-    int units_per_task;
     int issued;                     // stages the producer has put in flight
     int consumed;                   // stages the consumers have finished
     int failed;
@@ -107,21 +108,42 @@ __device__ __forceinline__ void consumer_sync() {
     asm volatile("bar.sync 1, %0;" ::"n"(kConsumerThreads) : "memory");
 }
 
-// 16-token units per task.  Both kernels evaluate this from the same inputs.
-//   * at most `partitions` tasks per row: the workspace has that many partial slots;
-//   * about kTasksPerCta tasks per CTA, so that the CTAs finish together;
-//   * whole stages, so that only the last stage of a row is partly filled.
-__device__ __forceinline__ int plan_units_per_task(long long total_units, int capacity_units, int partitions,
-                                                   int ctas) {
-    if (partitions <= 1) {
-        return capacity_units > 0 ? capacity_units : 1;
-    }
-    const long long by_capacity = (capacity_units + partitions - 1) / partitions;
-    const long long by_balance = (total_units * kKvHeads + static_cast<long long>(ctas) * kTasksPerCta - 1) /
-                                 (static_cast<long long>(ctas) * kTasksPerCta);
-    long long units = by_capacity > by_balance ? by_capacity : by_balance;
-    units = (units + kStageUnits - 1) / kStageUnits * kStageUnits;
-    return static_cast<int>(units < kStageUnits ? kStageUnits : units);
+// The split plan.  Both kernels evaluate it from the same inputs.
+//
+// The (row, kv head) pairs are laid end to end, row-major, on a line of units; a pair takes
+// max(units, 1) + padding positions (the padding stands for what a task costs beyond its tokens).
+// Every CTA owns `share` consecutive positions and works on the tokens that fall inside: all CTAs
+// stream the same amount, whatever the rows' lengths.  The piece of a pair inside CTA c is partial
+// number c - (first CTA that touches the pair); a pair without context is one empty piece.
+//   * padding >= share / kPlanPaddingDivisor, so that a CTA never holds more than
+//     kPlanPaddingDivisor + pairs / CTAs + 2 tasks;
+//   * share >= capacity / (partitions - 1): a row never has more pieces than the workspace has slots;
+//   * share is a whole number of stages.
+struct SplitPlan {
+    long long share;
+    int padding;
+};
+
+__device__ __forceinline__ SplitPlan make_split_plan(long long total_row_units, int rows, int capacity_units,
+                                                     int partitions, int ctas) {
+    const long long by_capacity = partitions > 1 ? (capacity_units + partitions - 2) / (partitions - 1) : 0;
+    long long share = (total_row_units * kKvHeads + ctas - 1) / ctas;
+    share = share > by_capacity ? share : by_capacity;
+    const long long padding_wanted = (share + kPlanPaddingDivisor - 1) / kPlanPaddingDivisor;
+    SplitPlan plan;
+    plan.padding = static_cast<int>(padding_wanted > kPlanMinPadding ? padding_wanted : kPlanMinPadding);
+    const long long line = (total_row_units + static_cast<long long>(rows) * plan.padding) * kKvHeads;
+    share = (line + ctas - 1) / ctas;
+    share = share > by_capacity ? share : by_capacity;
+    plan.share = (share + kStageUnits - 1) / kStageUnits * kStageUnits;
+    return plan;
+}
+
+// first position of pair (row, kv head); units_before = units of the rows before it
+__device__ __forceinline__ long long pair_position(const SplitPlan& plan, int row, int kv_head, long long units_before,
+                                                   int row_units) {
+    return (units_before + static_cast<long long>(row) * plan.padding) * kKvHeads +
+           static_cast<long long>(kv_head) * (row_units + plan.padding);
 }
 
 // A context longer than the block table can describe is cut at the table's capacity.
@@ -130,10 +152,8 @@ __device__ __forceinline__ int units_of_context(uint32_t context, int capacity_u
     return static_cast<int>(units < static_cast<uint32_t>(capacity_units) ? units : capacity_units);
 }
 
-// Tasks of one row per kv head; a row without context still gets one (it stores zeros).
-__device__ __forceinline__ int parts_of_row(int units, int units_per_task) {
-    return units <= 0 ? 1 : (units + units_per_task - 1) / units_per_task;
-}
+// Units a row occupies on the plan's line: a row without context still gets one task (it stores zeros).
+__device__ __forceinline__ int plan_units(int units) { return units > 0 ? units : 1; }
 
 template <bool kSplit>
 __global__ void __launch_bounds__(kThreads, 1) paged_attention_packed_kernel(
@@ -166,37 +186,7 @@ __global__ void __launch_bounds__(kThreads, 1) paged_attention_packed_kernel(
     }
     pdl_wait();  // context lengths, tables, query and the cache rows of this step come from earlier kernels
     if (warp == 0) {
-        long long total_units = 0;
-        for (int r = lane; r < rows; r += 32) {
-            total_units += units_of_context(context_lengths[row_base + r], capacity_units);
-        }
-#pragma unroll
-        for (int offset = 16; offset > 0; offset >>= 1) {
-            total_units += __shfl_xor_sync(0xffffffffu, total_units, offset);
-        }
-        const int units_per_task = plan_units_per_task(total_units, capacity_units, kSplit ? partitions : 1, gridDim.x);
-        // prefix of the rows' task counts: a warp scan per 32 rows
-        int carry = 0;
-        for (int base = 0; base < rows; base += 32) {
-            const int r = base + lane;
-            const int mine =
-                r < rows ? parts_of_row(units_of_context(context_lengths[row_base + r], capacity_units), units_per_task) : 0;
-            int inclusive = mine;
-#pragma unroll
-            for (int offset = 1; offset < 32; offset <<= 1) {
-                const int other = __shfl_up_sync(0xffffffffu, inclusive, offset);
-                if (lane >= offset) {
-                    inclusive += other;
-                }
-            }
-            if (r < rows) {
-                sm.first_pair[r] = carry + inclusive - mine;
-            }
-            carry += __shfl_sync(0xffffffffu, inclusive, 31);
-        }
         if (lane == 0) {
-            sm.first_pair[rows] = carry;
-            sm.units_per_task = units_per_task;
             sm.failed = 0;
             sm.issued = 0;
             for (int s = 0; s < kStages; ++s) {
@@ -205,34 +195,105 @@ __global__ void __launch_bounds__(kThreads, 1) paged_attention_packed_kernel(
             }
             mbar_fence_init();
         }
-        __syncwarp();
-        // task ids of this CTA: c, c + grid, ...; id = pair * kKvHeads + kv head
-        const int total_tasks = carry * kKvHeads;
         int count = 0;
-        for (int base = 0; base < kMaxCtaTasks; base += 32) {
-            const int index = base + lane;
-            const long long id = static_cast<long long>(blockIdx.x) + static_cast<long long>(index) * gridDim.x;
-            if (id < total_tasks) {
-                const int pair = static_cast<int>(id / kKvHeads);
-                int row = 0;
-                while (row + 1 < rows && sm.first_pair[row + 1] <= pair) {
-                    ++row;
+        if (!kSplit) {
+            // whole (row, kv head) pairs, dealt round: c, c + grid, ...
+            for (int index = lane; index < kMaxCtaTasks; index += 32) {
+                const long long id = static_cast<long long>(blockIdx.x) + static_cast<long long>(index) * gridDim.x;
+                if (id < static_cast<long long>(rows) * kKvHeads) {
+                    const int row = static_cast<int>(id / kKvHeads);
+                    const uint32_t row_context = context_lengths[row_base + row];
+                    Task task;
+                    task.context = static_cast<int>(min(row_context, static_cast<uint32_t>(capacity_units) * kUnitTokens));
+                    task.row = row_base + row;
+                    task.kv_head = static_cast<int>(id % kKvHeads);
+                    task.part = 0;
+                    task.unit_begin = 0;
+                    task.units = units_of_context(row_context, capacity_units);
+                    sm.tasks[index] = task;
+                    ++count;
                 }
-                const int part = pair - sm.first_pair[row];
-                const uint32_t row_context = context_lengths[row_base + row];
-                const int row_units = units_of_context(row_context, capacity_units);
-                Task task;
-                task.context = static_cast<int>(min(row_context, static_cast<uint32_t>(capacity_units) * kUnitTokens));
-                task.row = row_base + row;
-                task.kv_head = static_cast<int>(id % kKvHeads);
-                task.part = part;
-                task.unit_begin = part * units_per_task;
-                task.units = max(0, min(units_per_task, row_units - task.unit_begin));
-                sm.tasks[index] = task;
-                ++count;
+            }
+            count = __reduce_add_sync(0xffffffffu, count);
+        } else {
+            // prefix of the rows' units: a warp scan per 32 rows
+            int carry = 0;
+            for (int base = 0; base < rows; base += 32) {
+                const int r = base + lane;
+                const int mine = r < rows ? plan_units(units_of_context(context_lengths[row_base + r], capacity_units)) : 0;
+                int inclusive = mine;
+#pragma unroll
+                for (int offset = 1; offset < 32; offset <<= 1) {
+                    const int other = __shfl_up_sync(0xffffffffu, inclusive, offset);
+                    if (lane >= offset) {
+                        inclusive += other;
+                    }
+                }
+                if (r < rows) {
+                    sm.first_unit[r] = carry + inclusive - mine;
+                }
+                carry += __shfl_sync(0xffffffffu, inclusive, 31);
+            }
+            if (lane == 0) {
+                sm.first_unit[rows] = carry;
+            }
+            __syncwarp();
+            const SplitPlan plan = make_split_plan(carry, rows, capacity_units, partitions, gridDim.x);
+            const long long low = static_cast<long long>(blockIdx.x) * plan.share;
+            const long long high = low + plan.share;
+            // the pieces of this CTA, in (row, kv head) order: 32 rows at a time, a lane per row
+            for (int base = 0; base < rows; base += 32) {
+                const int r = base + lane;
+                Task mine[kKvHeads];
+                int found = 0;
+                if (r < rows) {
+                    const uint32_t row_context = context_lengths[row_base + r];
+                    const int row_units = units_of_context(row_context, capacity_units);
+                    const int occupied = plan_units(row_units);
+#pragma unroll
+                    for (int kv = 0; kv < kKvHeads; ++kv) {
+                        const long long start = pair_position(plan, r, kv, sm.first_unit[r], occupied);
+                        if (start < high && start + occupied > low) {
+                            const long long begin = low > start ? low - start : 0;
+                            const long long end = high - start < occupied ? high - start : occupied;
+                            Task task;
+                            task.context =
+                                static_cast<int>(min(row_context, static_cast<uint32_t>(capacity_units) * kUnitTokens));
+                            task.row = row_base + r;
+                            task.kv_head = kv;
+                            task.part = static_cast<int>(blockIdx.x - start / plan.share);
+                            task.unit_begin = static_cast<int>(begin);
+                            task.units = max(0, min(static_cast<int>(end), row_units) - static_cast<int>(begin));
+                            mine[found++] = task;
+                        }
+                    }
+                }
+                int before = found;  // exclusive prefix over the lanes
+#pragma unroll
+                for (int offset = 1; offset < 32; offset <<= 1) {
+                    const int other = __shfl_up_sync(0xffffffffu, before, offset);
+                    if (lane >= offset) {
+                        before += other;
+                    }
+                }
+                const int all = __shfl_sync(0xffffffffu, before, 31);
+                before -= found;
+#pragma unroll
+                for (int i = 0; i < kKvHeads; ++i) {
+                    if (i < found && count + before + i < kMaxCtaTasks) {
+                        sm.tasks[count + before + i] = mine[i];
+                    }
+                }
+                count += all;
+            }
+            if (count > kMaxCtaTasks) {
+                // cannot happen while the launcher's check of rows against the SM count holds
+                if (lane == 0) {
+                    atomicCAS(status, 0, kStatusAttentionPlanOverflow);
+                }
+                count = 0;
             }
         }
-        count = __reduce_add_sync(0xffffffffu, count);
         if (lane == 0) {
             sm.task_count = count;
         }
@@ -558,19 +619,24 @@ __global__ void __launch_bounds__(kMergeWarps * 32) reduce_partitions_kernel(
     const int pair = blockIdx.x;  // (row, head)
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
-    // The same plan as the attention kernel made: this row has `used` partials, the rest of its
+    // The same plan as the attention kernel made: this pair has `used` partials, the rest of its
     // slots were never written.
-    long long total_units = 0;
+    const int plan_row = pair / kQueryHeads;
+    long long total_units = 0, units_before = 0;
     for (int r = lane; r < rows; r += 32) {
-        total_units += units_of_context(context_lengths[row_base + r], capacity_units);
+        const int units = plan_units(units_of_context(context_lengths[row_base + r], capacity_units));
+        total_units += units;
+        units_before += r < plan_row ? units : 0;
     }
 #pragma unroll
     for (int offset = 16; offset > 0; offset >>= 1) {
         total_units += __shfl_xor_sync(0xffffffffu, total_units, offset);
+        units_before += __shfl_xor_sync(0xffffffffu, units_before, offset);
     }
-    const int units_per_task = plan_units_per_task(total_units, capacity_units, partitions, plan_ctas);
-    const int used = parts_of_row(
-        units_of_context(context_lengths[row_base + pair / kQueryHeads], capacity_units), units_per_task);
+    const SplitPlan plan = make_split_plan(total_units, rows, capacity_units, partitions, plan_ctas);
+    const int occupied = plan_units(units_of_context(context_lengths[row_base + plan_row], capacity_units));
+    const long long start = pair_position(plan, plan_row, (pair % kQueryHeads) / kGqaGroup, units_before, occupied);
+    const int used = static_cast<int>((start + occupied - 1) / plan.share - start / plan.share) + 1;
     const float* stats = partial_stats + static_cast<size_t>(pair) * partitions * kPartialFloats;
     // every warp finds the maximum over all partials (lanes side by side) ...
     float maximum = -INFINITY;
@@ -696,13 +762,14 @@ cudaError_t launch_attention(const void* query, const void* query_gate_projectio
         return opted_split;
     }
     // One CTA per SM, whatever the batch: the task list is cut on the device.  A CTA's list holds
-    // kMaxCtaTasks entries; the plan gives it kTasksPerCta + 1 plus one per row and kv head.
+    // kMaxCtaTasks entries; the plan gives it at most kPlanPaddingDivisor + 2 plus one per row and
+    // kv head and CTA (undivided rows: one per row and kv head and CTA).
     int device = 0, sms = 0;
     if (cudaGetDevice(&device) != cudaSuccess ||
         cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || sms <= 0) {
         return cudaErrorInvalidDevice;
     }
-    if ((rows * kKvHeads + sms - 1) / sms + kTasksPerCta + 2 > kMaxCtaTasks) {
+    if ((rows * kKvHeads + sms - 1) / sms + kPlanPaddingDivisor + 2 > kMaxCtaTasks) {
         return cudaErrorInvalidValue;
     }
     const dim3 grid(sms);
