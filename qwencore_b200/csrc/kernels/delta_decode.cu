@@ -34,7 +34,7 @@ constexpr int kMaxParts = kDim / kPartRows;
 
 __device__ __forceinline__ float2 f2(float a, float b) { return make_float2(a, b); }
 
-__global__ void __launch_bounds__(kThreads, 4) delta_decode_int8_kernel(
+__global__ void __launch_bounds__(kThreads, 7) delta_decode_int8_kernel(
     int8_t* __restrict__ state, float* __restrict__ state_scales, const uint32_t* __restrict__ state_slots,
     const float* __restrict__ q, const float* __restrict__ k, const float* __restrict__ v,
     const float* __restrict__ alpha, const float* __restrict__ beta, const float* __restrict__ kq,
@@ -44,6 +44,7 @@ __global__ void __launch_bounds__(kThreads, 4) delta_decode_int8_kernel(
     __shared__ __align__(128) uint8_t tile[kDim * kDim];
     __shared__ __align__(16) float row_scale[kDim];
     __shared__ float out_rows[kDim];
+    __shared__ __align__(16) float v_rows[kDim];
     __shared__ uint64_t bars[kMaxParts];
     __shared__ int failed;
 
@@ -73,48 +74,37 @@ __global__ void __launch_bounds__(kThreads, 4) delta_decode_int8_kernel(
     if (threadIdx.x == 0) {
         for (int part = 0; part < parts; ++part) {
             const uint32_t bytes = part_rows * kDim;
-            mbar_arrive_expect_tx(&bars[part], bytes + (part == 0 ? rows_here * 4 : 0));
+            mbar_arrive_expect_tx(&bars[part], bytes + (part == 0 ? rows_here * 8 : 0));
             bulk_g2s(tile + part * kPartRows * kDim, S + part * kPartRows * kDim, bytes, &bars[part]);
             if (part == 0) {
                 bulk_g2s(row_scale, scales, rows_here * 4, &bars[0]);
+                bulk_g2s(v_rows, v + (static_cast<size_t>(b) * v_heads + h) * kDim + row_begin, rows_here * 4, &bars[0]);
             }
         }
     }
 
     const int lane = threadIdx.x & 31;
     const int warp = threadIdx.x >> 5;
-    const int sub = lane & 3;        // which quarter of the row this lane owns
-    const int row_in_warp = lane >> 2;
+    const int sub = lane & 7;        // which eighth of the row this lane owns: columns [16 sub, 16 sub + 16)
+    const int row_in_warp = lane >> 3;
 
-    // Columns of this lane: [16 sub, 16 sub + 16) and [64 + 16 sub, 64 + 16 sub + 16).
-    float2 kk[16], qq[16];
+    float2 kk[8], qq[8];
     {
-        const float* kp = k + (static_cast<size_t>(b) * kDeltaKeyHeads + hk) * kDim;
-        const float* qp = q + (static_cast<size_t>(b) * kDeltaKeyHeads + hk) * kDim;
+        const float* kp = k + (static_cast<size_t>(b) * kDeltaKeyHeads + hk) * kDim + 16 * sub;
+        const float* qp = q + (static_cast<size_t>(b) * kDeltaKeyHeads + hk) * kDim + 16 * sub;
 #pragma unroll
-        for (int half = 0; half < 2; ++half) {
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-                const float4 kv = *reinterpret_cast<const float4*>(kp + 64 * half + 16 * sub + 4 * i);
-                const float4 qv = *reinterpret_cast<const float4*>(qp + 64 * half + 16 * sub + 4 * i);
-                kk[half * 8 + 2 * i] = f2(kv.x, kv.y);
-                kk[half * 8 + 2 * i + 1] = f2(kv.z, kv.w);
-                qq[half * 8 + 2 * i] = f2(qv.x, qv.y);
-                qq[half * 8 + 2 * i + 1] = f2(qv.z, qv.w);
-            }
+        for (int i = 0; i < 4; ++i) {
+            const float4 kv = *reinterpret_cast<const float4*>(kp + 4 * i);
+            const float4 qv = *reinterpret_cast<const float4*>(qp + 4 * i);
+            kk[2 * i] = f2(kv.x, kv.y);
+            kk[2 * i + 1] = f2(kv.z, kv.w);
+            qq[2 * i] = f2(qv.x, qv.y);
+            qq[2 * i + 1] = f2(qv.z, qv.w);
         }
     }
     const float a = alpha[static_cast<size_t>(b) * v_heads + h];
     const float bt = beta[static_cast<size_t>(b) * v_heads + h];
     const float kq_token = kq[static_cast<size_t>(b) * kDeltaKeyHeads + hk];
-    const float* vp = v + (static_cast<size_t>(b) * v_heads + h) * kDim + row_begin;
-    // this lane's v element of every part, fetched before the first tile wait
-    float v_rows[kMaxParts];
-#pragma unroll
-    for (int part = 0; part < kMaxParts; ++part) {
-        const int row = part * kPartRows + (threadIdx.x >> 5) * 8 + ((threadIdx.x & 31) >> 2);
-        v_rows[part] = row < rows_here ? vp[row] : 0.0f;
-    }
 
     constexpr float kMagic = 12582912.0f;        // 1.5 * 2^23
     constexpr float kMagicBiased = 12583040.0f;  // kMagic + 128
@@ -125,77 +115,77 @@ __global__ void __launch_bounds__(kThreads, 4) delta_decode_int8_kernel(
             failed = 1;
             break;
         }
-        const int local = part * kPartRows + warp * 8 + row_in_warp;
         if (warp * 8 >= part_rows) {
             continue;  // whole warp beyond the split's rows
         }
-        uint8_t* row_ptr = tile + local * kDim + 16 * sub;
-        const uint4 c0 = *reinterpret_cast<const uint4*>(row_ptr);
-        const uint4 c1 = *reinterpret_cast<const uint4*>(row_ptr + 64);
-        const float scale = row_scale[local];
-        float v_row = v_rows[0];
 #pragma unroll
-        for (int i = 1; i < kMaxParts; ++i) {
-            v_row = part == i ? v_rows[i] : v_row;
-        }
+        for (int pass = 0; pass < 2; ++pass) {
+            const int local = part * kPartRows + warp * 8 + pass * 4 + row_in_warp;
+            uint8_t* row_ptr = tile + local * kDim + 16 * sub;
+            const uint4 codes = *reinterpret_cast<const uint4*>(row_ptr);
+            const float scale = row_scale[local];
+            const float v_row = v_rows[local];
 
-        const uint32_t words[8] = {c0.x, c0.y, c0.z, c0.w, c1.x, c1.y, c1.z, c1.w};
-        float2 s[16];
-        const float2 bias = f2(-kMagicBiased, -kMagicBiased);
-        const float2 scale2 = f2(scale, scale);
-        float2 u2 = f2(0.0f, 0.0f), w2 = f2(0.0f, 0.0f);
+            const uint32_t words[4] = {codes.x, codes.y, codes.z, codes.w};
+            float2 s[8];
+            const float2 bias = f2(-kMagicBiased, -kMagicBiased);
+            const float2 scale2 = f2(scale, scale);
+            float2 u2 = f2(0.0f, 0.0f), w2 = f2(0.0f, 0.0f);
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
-            const uint32_t x = words[i] ^ 0x80808080u;
-            const float2 lo = f2(__uint_as_float(__byte_perm(x, 0x4B400000u, 0x7650)),
-                                 __uint_as_float(__byte_perm(x, 0x4B400000u, 0x7651)));
-            const float2 hi = f2(__uint_as_float(__byte_perm(x, 0x4B400000u, 0x7652)),
-                                 __uint_as_float(__byte_perm(x, 0x4B400000u, 0x7653)));
-            s[2 * i] = __fmul2_rn(__fadd2_rn(lo, bias), scale2);
-            s[2 * i + 1] = __fmul2_rn(__fadd2_rn(hi, bias), scale2);
-            u2 = __ffma2_rn(s[2 * i], kk[2 * i], u2);
-            w2 = __ffma2_rn(s[2 * i], qq[2 * i], w2);
-            u2 = __ffma2_rn(s[2 * i + 1], kk[2 * i + 1], u2);
-            w2 = __ffma2_rn(s[2 * i + 1], qq[2 * i + 1], w2);
-        }
-        float u = u2.x + u2.y;
-        float w = w2.x + w2.y;
-        u += __shfl_xor_sync(0xffffffffu, u, 1);
-        w += __shfl_xor_sync(0xffffffffu, w, 1);
-        u += __shfl_xor_sync(0xffffffffu, u, 2);
-        w += __shfl_xor_sync(0xffffffffu, w, 2);
-
-        const float c = bt * (v_row - a * u);
-        const float contribution = a * w + c * kq_token;
-
-        const float2 a2 = f2(a, a);
-        const float2 cc = f2(c, c);
-        float peak = 0.0f;
+            for (int i = 0; i < 4; ++i) {
+                const uint32_t x = words[i] ^ 0x80808080u;
+                const float2 lo = f2(__uint_as_float(__byte_perm(x, 0x4B400000u, 0x7650)),
+                                     __uint_as_float(__byte_perm(x, 0x4B400000u, 0x7651)));
+                const float2 hi = f2(__uint_as_float(__byte_perm(x, 0x4B400000u, 0x7652)),
+                                     __uint_as_float(__byte_perm(x, 0x4B400000u, 0x7653)));
+                s[2 * i] = __fmul2_rn(__fadd2_rn(lo, bias), scale2);
+                s[2 * i + 1] = __fmul2_rn(__fadd2_rn(hi, bias), scale2);
+                u2 = __ffma2_rn(s[2 * i], kk[2 * i], u2);
+                w2 = __ffma2_rn(s[2 * i], qq[2 * i], w2);
+                u2 = __ffma2_rn(s[2 * i + 1], kk[2 * i + 1], u2);
+                w2 = __ffma2_rn(s[2 * i + 1], qq[2 * i + 1], w2);
+            }
+            float u = u2.x + u2.y;
+            float w = w2.x + w2.y;
 #pragma unroll
-        for (int i = 0; i < 16; ++i) {
-            s[i] = __ffma2_rn(cc, kk[i], __fmul2_rn(a2, s[i]));
-            peak = fmaxf(peak, fmaxf(fabsf(s[i].x), fabsf(s[i].y)));
-        }
-        peak = fmaxf(peak, __shfl_xor_sync(0xffffffffu, peak, 1));
-        peak = fmaxf(peak, __shfl_xor_sync(0xffffffffu, peak, 2));
+            for (int offset = 1; offset < 8; offset <<= 1) {
+                u += __shfl_xor_sync(0xffffffffu, u, offset);
+                w += __shfl_xor_sync(0xffffffffu, w, offset);
+            }
 
-        const float inverse = peak == 0.0f ? 0.0f : __fdiv_rn(127.0f, peak);
-        const float2 inverse2 = f2(inverse, inverse);
-        const float2 magic2 = f2(kMagic, kMagic);
-        uint32_t packed[8];
+            const float c = bt * (v_row - a * u);
+            const float contribution = a * w + c * kq_token;
+
+            const float2 a2 = f2(a, a);
+            const float2 cc = f2(c, c);
+            float peak = 0.0f;
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
-            const float2 y0 = __fadd2_rn(__fmul2_rn(s[2 * i], inverse2), magic2);
-            const float2 y1 = __fadd2_rn(__fmul2_rn(s[2 * i + 1], inverse2), magic2);
-            const uint32_t lo = __byte_perm(__float_as_uint(y0.x), __float_as_uint(y0.y), 0x0040);
-            const uint32_t hi = __byte_perm(__float_as_uint(y1.x), __float_as_uint(y1.y), 0x0040);
-            packed[i] = __byte_perm(lo, hi, 0x5410);
-        }
-        *reinterpret_cast<uint4*>(row_ptr) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
-        *reinterpret_cast<uint4*>(row_ptr + 64) = make_uint4(packed[4], packed[5], packed[6], packed[7]);
-        if (sub == 0) {
-            row_scale[local] = __fmul_rn(peak, 1.0f / 127.0f);
-            out_rows[local] = contribution;
+            for (int i = 0; i < 8; ++i) {
+                s[i] = __ffma2_rn(cc, kk[i], __fmul2_rn(a2, s[i]));
+                peak = fmaxf(peak, fmaxf(fabsf(s[i].x), fabsf(s[i].y)));
+            }
+#pragma unroll
+            for (int offset = 1; offset < 8; offset <<= 1) {
+                peak = fmaxf(peak, __shfl_xor_sync(0xffffffffu, peak, offset));
+            }
+
+            const float inverse = peak == 0.0f ? 0.0f : __fdiv_rn(127.0f, peak);
+            const float2 inverse2 = f2(inverse, inverse);
+            const float2 magic2 = f2(kMagic, kMagic);
+            uint32_t packed[4];
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+                const float2 y0 = __fadd2_rn(__fmul2_rn(s[2 * i], inverse2), magic2);
+                const float2 y1 = __fadd2_rn(__fmul2_rn(s[2 * i + 1], inverse2), magic2);
+                const uint32_t lo = __byte_perm(__float_as_uint(y0.x), __float_as_uint(y0.y), 0x0040);
+                const uint32_t hi = __byte_perm(__float_as_uint(y1.x), __float_as_uint(y1.y), 0x0040);
+                packed[i] = __byte_perm(lo, hi, 0x5410);
+            }
+            *reinterpret_cast<uint4*>(row_ptr) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+            if (sub == 0) {
+                row_scale[local] = __fmul_rn(peak, 1.0f / 127.0f);
+                out_rows[local] = contribution;
+            }
         }
     }
 

@@ -52,7 +52,7 @@ constexpr int kPartialFloats = 2;
 constexpr size_t kPartialBytes = 2 * sizeof(float) + kHeadDim * sizeof(__half);  // 520
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr int kMaxCtaTasks = 64;      // list capacity; the plan keeps a CTA far below it
-constexpr int kPlanMinPadding = 8;    // units a task costs beyond its tokens (query load, epilogue, merge)
+constexpr int kPlanMinPadding = 16;   // units a task costs beyond its tokens (query load, epilogue, merge)
 constexpr int kPlanPaddingDivisor = 24;  // padding = share / this at least: bounds the tasks of one CTA
 constexpr int kPlanRows = 256;        // rows whose prefix fits the shared-memory table
 
