@@ -12,9 +12,13 @@
 //     memory by bulk-async copies (TMA 1-D) in 4 KiB quarters, each signalling its own
 //     mbarrier, so the first rows are processed while the rest are in flight, and the
 //     requantised tile leaves by one bulk store;
-//   * four CTAs are resident per SM (64 KiB of state in flight per SM);
-//   * four lanes share a row (32 codes each), so the three per-row reductions cost two
-//     shuffle steps; k and q stay in registers for all rows of the tile;
+//   * eight lanes share a row (16 codes each: one 16-byte shared-memory access per lane and
+//     row), so the three per-row reductions cost three shuffle steps; the lane's 16 elements
+//     of k and q stay in registers for all rows of the tile.  That keeps the kernel at 72
+//     registers, so seven CTAs are resident per SM (112 KiB of state in flight per SM): the
+//     kernel is bound by dependent-instruction latency, and the warps of more resident CTAs
+//     are what hides it (four lanes per row, 121 registers and four CTAs per SM ran 9 %
+//     slower);
 //   * the elementwise fp32 work uses the packed f32x2 pipe, and both int8 <-> fp32
 //     conversions are bit tricks on the 2^23 binade (exact, round-to-nearest-even),
 //     which keeps the instruction count under what the memory stream allows.
