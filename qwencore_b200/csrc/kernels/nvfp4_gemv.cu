@@ -637,6 +637,8 @@ cudaError_t dispatch(const GemvParams& p, cudaStream_t stream) {
     // its stores are 16 bytes wide and its activation fetch is a tiled TMA copy
     const bool aligned = p.out_features % 8 == 0 && (reinterpret_cast<uintptr_t>(p.y) & 15) == 0 &&
                          (reinterpret_cast<uintptr_t>(p.x) & 15) == 0 &&
+                         ((reinterpret_cast<uintptr_t>(p.packed[0]) | reinterpret_cast<uintptr_t>(p.packed[1]) |
+                           reinterpret_cast<uintptr_t>(p.scales[0]) | reinterpret_cast<uintptr_t>(p.scales[1])) & 15) == 0 &&
                          (MODE != kFp8Rows || ((reinterpret_cast<uintptr_t>(p.y_f32) & 15) == 0 &&
                                                (reinterpret_cast<uintptr_t>(p.row_scales) & 15) == 0));
     if (p.batch <= 8 && !(large && aligned)) {
