@@ -77,6 +77,22 @@ int qwc_nvfp4_swiglu_w4a16(const void* gate_packed, const void* gate_scales, con
                            int out_features, int in_features, int batch, float gate_global_scale,
                            float up_global_scale, qwc_stream stream);
 
+/*
+ * Additive (no reference counterpart).  Names the weights of the projection that the calling
+ * thread's stream will run AFTER the next qwc_nvfp4_w4a16 / qwc_nvfp4_swiglu_w4a16 /
+ * qwc_fp8_lm_head* call it makes: that launch then asks L2 for the first stages of the named
+ * matrix once its own last bytes are on their way, so HBM keeps streaming across the kernel
+ * boundary.  kind: 0 = NVFP4 matrix (packed0, scales0), 1 = SwiGLU pair (packed0/scales0 = gate,
+ * packed1/scales1 = up), 2 = e4m3 rows of the vocabulary head (packed0 = table; no scales).
+ * Pure hint: host-side only (no launch, no sync, capture-legal), good for one launch of this
+ * thread, ignored when that launch does not take the tcgen05 path; wrong or stale hints cost
+ * bandwidth, never correctness (prefetches do not fault on valid device memory and write nothing).
+ * The pointers must be device memory of the shapes given, 16-byte aligned.
+ * Returns cudaErrorInvalidValue for a null matrix, non-positive or misaligned shapes, or an unknown kind.
+ */
+int qwc_nvfp4_prefetch_next(const void* packed0, const void* scales0, const void* packed1,
+                            const void* scales1, int out_features, int in_features, int kind);
+
 /* ------------------------------------------------------------------ */
 /* Packed paged FP8 attention                                           */
 /* ------------------------------------------------------------------ */

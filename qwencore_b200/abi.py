@@ -44,6 +44,7 @@ KERNEL_SYMBOLS = {
     "qwc_device_status_reset": (c_int, []),
     "qwc_nvfp4_w4a16": (c_int, [P, P, P, P, c_int, c_int, c_int, c_float, P]),
     "qwc_nvfp4_swiglu_w4a16": (c_int, [P, P, P, P, P, P, c_int, c_int, c_int, c_float, c_float, P]),
+    "qwc_nvfp4_prefetch_next": (c_int, [P, P, P, P, c_int, c_int, c_int]),
     "qwc_paged_attention_packed_fp8": (c_int, [P, P, P, P, P, P, P, P, c_size_t, c_int, c_int, c_int, c_int,
                                                c_int, c_float, P]),
     "qwc_paged_attention_packed_fp8_scaled": (c_int, [P, P, P, P, P, P, P, P, P, P, c_size_t, c_int, c_int,

@@ -325,6 +325,22 @@ bool phase(qwc_engine* e, const char* label) {
     return selected;
 }
 
+// Names the projection after the one about to be launched (qwc_nvfp4_prefetch_next): its first
+// stages are asked of L2 while the launch drains.  Only where the two are a few small kernels apart:
+// an attention pass in between would push the lines out of L2 again.
+void hint_next(const qwc_engine* e, const LinearW& next) {
+    if (e->cfg.split_size == 1) {
+        (void)qwc_nvfp4_prefetch_next(next.packed, next.scales, nullptr, nullptr, next.out_features, next.in_features, 0);
+    }
+}
+
+void hint_next_pair(const qwc_engine* e, const LinearW& gate, const LinearW& up) {
+    if (e->cfg.split_size == 1) {
+        (void)qwc_nvfp4_prefetch_next(gate.packed, gate.scales, up.packed, up.scales, gate.out_features,
+                                      gate.in_features, 1);
+    }
+}
+
 // One projection; in latency mode the local slice lands at this rank's offset of the full
 // row and an all-gather completes it (batch 1 only, so the gathered layout is the row itself).
 int project(qwc_engine* e, const LinearW& w, const __nv_bfloat16* input, __nv_bfloat16* output, int batch) {
@@ -367,6 +383,7 @@ int decode_forward(qwc_engine* e, int batch) {
         const Layer& layer = e->layers[index];
         if (!layer.full) {
             if (phase(e, "gemm.la_in")) {
+                hint_next(e, layer.la_out);
                 QWC_TRY(project(e, layer.in_proj, e->normed, e->mixer_in, batch));
             }
             if (phase(e, "delta.prepare")) {
@@ -384,6 +401,7 @@ int decode_forward(qwc_engine* e, int batch) {
                                                 batch, kEps, e->mixer_width, s));
             }
             if (phase(e, "gemm.la_out")) {
+                hint_next_pair(e, layer.gate, layer.up);
                 QWC_TRY(project(e, layer.la_out, e->delta_normed, e->mixer_out, batch));
             }
         } else {
@@ -407,6 +425,7 @@ int decode_forward(qwc_engine* e, int batch) {
                     batch, 0, e->max_blocks, c.kv_page_size, e->qkv_width, e->partitions, 1.0f / 16.0f, s));
             }
             if (phase(e, "gemm.attn_out")) {
+                hint_next_pair(e, layer.gate, layer.up);
                 QWC_TRY(project(e, layer.o, e->attention_out, e->mixer_out, batch));
             }
         }
@@ -415,6 +434,7 @@ int decode_forward(qwc_engine* e, int batch) {
         }
         if (phase(e, "gemm.mlp_gate_up")) {
             __nv_bfloat16* target = e->mlp_hidden + static_cast<size_t>(c.split_rank) * layer.gate.out_features;
+            hint_next(e, layer.down);
             QWC_TRY(qwc_nvfp4_swiglu_w4a16(layer.gate.packed, layer.gate.scales, layer.up.packed, layer.up.scales,
                                            e->normed, c.split_size > 1 ? target : e->mlp_hidden,
                                            layer.gate.out_features, layer.gate.in_features, batch,
@@ -426,6 +446,12 @@ int decode_forward(qwc_engine* e, int batch) {
             }
         }
         if (phase(e, "gemm.mlp_down")) {
+            if (index + 1 < e->layers.size()) {
+                const Layer& following = e->layers[index + 1];
+                hint_next(e, following.full ? following.qkv : following.in_proj);
+            } else if (c.split_size == 1) {
+                (void)qwc_nvfp4_prefetch_next(e->lm_head, nullptr, nullptr, nullptr, e->vocab_local, c.hidden, 2);
+            }
             QWC_TRY(project(e, layer.down, e->mlp_hidden, e->mlp_out, batch));
         }
         const __nv_bfloat16* next_norm = index + 1 < e->layers.size() ? e->layers[index + 1].input_norm : e->final_norm;

@@ -31,6 +31,18 @@ constexpr int kStatusDeltaTileWait = 0x102;
 constexpr int kStatusGemvWait = 0x103;
 constexpr int kStatusAttentionPlanOverflow = 0x104;  // a CTA's task list would not hold its share
 
+// What a caller said about the projection its stream runs after the next one it launches
+// (qwc_nvfp4_prefetch_next): kept per host thread, taken (and cleared) by the next projection launch.
+struct NextProjection {
+    const void* packed[2];  // matrix, or gate and up matrices
+    const void* scales[2];
+    int out_features;
+    int in_features;
+    int kind;  // 0 NVFP4, 1 NVFP4 SwiGLU pair, 2 e4m3 rows
+};
+void set_next_projection(const NextProjection& next);
+NextProjection take_next_projection();
+
 // Process-wide shape selection (see qwc_configure in the C ABI).
 struct Shape {
     int delta_value_heads;

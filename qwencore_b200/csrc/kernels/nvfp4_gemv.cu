@@ -626,6 +626,20 @@ cudaError_t launch(const GemvParams& base, cudaStream_t stream) {
     return cudaLaunchKernelEx(&config, nvfp4_gemv_kernel<NT, MT, MODE>, p);
 }
 
+thread_local NextProjection g_next_projection = {};
+
+}  // namespace
+
+void set_next_projection(const NextProjection& next) { g_next_projection = next; }
+
+NextProjection take_next_projection() {
+    const NextProjection taken = g_next_projection;
+    g_next_projection = NextProjection{};
+    return taken;
+}
+
+namespace {
+
 template <int MODE>
 cudaError_t dispatch(const GemvParams& p, cudaStream_t stream) {
     const int wide_tiles = ((p.out_features + 127) / 128) * 4;
@@ -642,6 +656,7 @@ cudaError_t dispatch(const GemvParams& p, cudaStream_t stream) {
                          (MODE != kFp8Rows || ((reinterpret_cast<uintptr_t>(p.y_f32) & 15) == 0 &&
                                                (reinterpret_cast<uintptr_t>(p.row_scales) & 15) == 0));
     if (p.batch <= 8 && !(large && aligned)) {
+        (void)take_next_projection();  // only the tcgen05 kernel acts on the hint; it is good for one launch
         return launch<1, 1, MODE>(p, stream);
     }
     if (MODE == kFp8Rows && aligned) {
@@ -654,6 +669,7 @@ cudaError_t dispatch(const GemvParams& p, cudaStream_t stream) {
                                  p.in_features, p.batch, p.inverse_scale[0], p.inverse_scale[1],
                                  MODE == kNvfp4Swiglu, stream);
     }
+    (void)take_next_projection();
     if (p.batch <= 16) {
         return wide ? launch<2, 2, MODE>(p, stream) : launch<2, 1, MODE>(p, stream);
     }
@@ -682,6 +698,29 @@ namespace {
 
 }  // namespace
 }  // namespace qwc
+
+extern "C" int qwc_nvfp4_prefetch_next(const void* packed0, const void* scales0, const void* packed1,
+                                       const void* scales1, int out_features, int in_features, int kind) {
+    const bool pair = kind == 1;
+    const bool rows = kind == 2;
+    if (kind < 0 || kind > 2 || packed0 == nullptr || (!rows && scales0 == nullptr) ||
+        (pair && (packed1 == nullptr || scales1 == nullptr)) || out_features <= 0 || in_features <= 0 ||
+        in_features % 256 != 0 ||
+        ((reinterpret_cast<uintptr_t>(packed0) | reinterpret_cast<uintptr_t>(scales0) |
+          reinterpret_cast<uintptr_t>(packed1) | reinterpret_cast<uintptr_t>(scales1)) & 15) != 0) {
+        return cudaErrorInvalidValue;
+    }
+    qwc::NextProjection next = {};
+    next.packed[0] = packed0;
+    next.packed[1] = pair ? packed1 : packed0;
+    next.scales[0] = rows ? packed0 : scales0;
+    next.scales[1] = pair ? scales1 : next.scales[0];
+    next.out_features = out_features;
+    next.in_features = in_features;
+    next.kind = kind;
+    qwc::set_next_projection(next);
+    return cudaSuccess;
+}
 
 extern "C" int qwc_nvfp4_w4a16(const void* packed, const void* scales, const void* input, void* output,
                                int out_features, int in_features, int batch, float weight_global_scale,

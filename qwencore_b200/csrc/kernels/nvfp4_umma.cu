@@ -35,6 +35,11 @@
 // no block scales, each dequantising set reads every other stage, and the row scale multiplies the
 // accumulator in the epilogue.
 //
+// When the caller has named the projection that follows (qwc_nvfp4_prefetch_next), the producer's
+// last act is to ask L2 for the first stages of that launch's CTAs (tiled TMA prefetches without a
+// shared-memory destination), so that HBM keeps streaming while this launch works off its ring and
+// the next launch finds its first boxes in L2.
+//
 // Every wait is bounded; a wait that gives up records a code in the status word, the CTA skips
 // its stores, frees its TMEM and returns.
 
@@ -96,6 +101,20 @@ struct UmmaParams {
     int fp8;
     const float* row_scales;
     float* y_f32;
+    // The projection that this stream runs next, when the caller has named it: every CTA asks L2 for
+    // the first stages of some of that launch's CTAs once its own last stage is on its way, so that
+    // HBM keeps streaming while this launch drains its ring and the next one starts.
+    struct Next {
+        int valid;
+        int swiglu;
+        int nvfp4;  // block scales to fetch as well
+        int out_features;
+        int ctas;       // row groups x splits of that launch
+        int splits;
+        int stages_in_k;
+        int group_blocks;
+        const uint8_t* scales[2];
+    } next;
 };
 
 
@@ -177,6 +196,19 @@ __device__ __forceinline__ void tma_box_g2s(void* smem_dst, const CUtensorMap* m
         : "memory");
 }
 
+// The same box, but only brought into L2 (no shared-memory destination, nothing to wait for).
+__device__ __forceinline__ void tma_box_prefetch_l2(const CUtensorMap* map, int x, int y) {
+    asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];" ::"l"(
+                     reinterpret_cast<uint64_t>(map)),
+                 "r"(x), "r"(y)
+                 : "memory");
+}
+
+// Contiguous bytes into L2; address 16-byte aligned, size a multiple of 16.
+__device__ __forceinline__ void bulk_prefetch_l2(const void* global, uint32_t bytes) {
+    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(global), "r"(bytes) : "memory");
+}
+
 __device__ __forceinline__ void tmem_store16(uint32_t taddr, const uint32_t (&r)[16]) {
     asm volatile(
         "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};" ::"r"(
@@ -207,7 +239,8 @@ __device__ __forceinline__ void tmem_load32(uint32_t taddr, float (&v)[32]) {
 
 __global__ void __launch_bounds__(kThreads, 1)
     nvfp4_umma_kernel(const __grid_constant__ CUtensorMap map0, const __grid_constant__ CUtensorMap map1,
-                      const __grid_constant__ CUtensorMap x_map, const UmmaParams p) {
+                      const __grid_constant__ CUtensorMap x_map, const __grid_constant__ CUtensorMap next_map0,
+                      const __grid_constant__ CUtensorMap next_map1, const UmmaParams p) {
     extern __shared__ unsigned char smem_raw[];
     __shared__ Barriers bars;
     // 128-byte-swizzled boxes need a 1 KiB-aligned shared address.
@@ -469,6 +502,32 @@ __global__ void __launch_bounds__(kThreads, 1)
             }
             __syncwarp();
         }
+        if (ok && p.next.valid && elect_one()) {
+            for (int cta = blockIdx.x; cta < p.next.ctas; cta += gridDim.x) {
+                const int group = cta / p.next.splits;
+                const int slice = cta - group * p.next.splits;
+                const int first_stage =
+                    static_cast<int>(static_cast<long long>(p.next.stages_in_k) * slice / p.next.splits);
+                const int end_stage =
+                    static_cast<int>(static_cast<long long>(p.next.stages_in_k) * (slice + 1) / p.next.splits);
+                const int stages = min(kWeightStages, end_stage - first_stage);
+#pragma unroll
+                for (int t = 0; t < kTiles; ++t) {
+                    const int row0 = p.next.swiglu ? group * kTileRows : (group * kTiles + t) * kTileRows;
+                    if (row0 >= p.next.out_features) {
+                        continue;
+                    }
+                    for (int st = 0; st < stages; ++st) {
+                        tma_box_prefetch_l2(t == 1 ? &next_map1 : &next_map0, (first_stage + st) * kBoxRowBytes, row0);
+                        if (p.next.nvfp4) {
+                            bulk_prefetch_l2(p.next.scales[t] + (static_cast<size_t>(row0 >> 7) * p.next.group_blocks +
+                                                                 2 * kStageChunks * (first_stage + st)) * 512,
+                                             kStageChunks * 1024);
+                        }
+                    }
+                }
+            }
+        }
     } else if (warp < kFirstConvertWarp) {
         // ---------------- tensor-core issue ----------------
         // One warp per tile.  The whole warp waits; only the instructions themselves sit in the
@@ -622,22 +681,51 @@ __global__ void __launch_bounds__(kThreads, 1)
         const int unit_shift = p.swiglu ? 4 : 5;  // 8-row units per token: 16 (128 outputs) or 32 (256)
         const int row0 = p.swiglu ? row_group * kTileRows : row_group * kTiles * kTileRows;
         const int owned = split < p.batch ? (p.batch - split + p.splits - 1) / p.splits : 0;
+        const auto slice_base = [&](int r) -> const float* {
+            return p.splits > 1 ? cluster.map_shared_rank(parked, r) : parked;
+        };
         for (int u = threadIdx.x; u < (owned << unit_shift); u += kParkedRows) {
             const int token = split + (u >> unit_shift) * p.splits;
             const int r8 = (u & ((1 << unit_shift) - 1)) * 8;
             float first[8] = {0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f};
             float second[8] = {0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f};  // the up rows of a SwiGLU pair
-            for (int r = 0; r < p.splits; ++r) {
-                const float* peer = (p.splits > 1 ? cluster.map_shared_rank(parked, r) : parked) + token * kParkedRows + r8;
-                const float4 a = *reinterpret_cast<const float4*>(peer);
-                const float4 b = *reinterpret_cast<const float4*>(peer + 4);
-                first[0] += a.x; first[1] += a.y; first[2] += a.z; first[3] += a.w;
-                first[4] += b.x; first[5] += b.y; first[6] += b.z; first[7] += b.w;
+            // A load from a peer's shared memory is a round trip through the cluster network: the loads
+            // of four slices are issued together and only then summed (in slice order, as before), so a
+            // six-way split waits for two round trips instead of six.
+            const int offset = token * kParkedRows + r8;
+            for (int base = 0; base < p.splits; base += 4) {
+                float4 a[4], b[4];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    if (base + j < p.splits) {
+                        const float* peer = slice_base(base + j) + offset;
+                        a[j] = *reinterpret_cast<const float4*>(peer);
+                        b[j] = *reinterpret_cast<const float4*>(peer + 4);
+                    }
+                }
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    if (base + j < p.splits) {
+                        first[0] += a[j].x; first[1] += a[j].y; first[2] += a[j].z; first[3] += a[j].w;
+                        first[4] += b[j].x; first[5] += b[j].y; first[6] += b[j].z; first[7] += b[j].w;
+                    }
+                }
                 if (p.swiglu) {
-                    const float4 c = *reinterpret_cast<const float4*>(peer + kTileRows);
-                    const float4 d = *reinterpret_cast<const float4*>(peer + kTileRows + 4);
-                    second[0] += c.x; second[1] += c.y; second[2] += c.z; second[3] += c.w;
-                    second[4] += d.x; second[5] += d.y; second[6] += d.z; second[7] += d.w;
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        if (base + j < p.splits) {
+                            const float* peer = slice_base(base + j) + offset + kTileRows;
+                            a[j] = *reinterpret_cast<const float4*>(peer);
+                            b[j] = *reinterpret_cast<const float4*>(peer + 4);
+                        }
+                    }
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        if (base + j < p.splits) {
+                            second[0] += a[j].x; second[1] += a[j].y; second[2] += a[j].z; second[3] += a[j].w;
+                            second[4] += b[j].x; second[5] += b[j].y; second[6] += b[j].z; second[7] += b[j].w;
+                        }
+                    }
                 }
             }
             const int row = row0 + r8;
@@ -804,23 +892,53 @@ cudaError_t launch_umma(UmmaParams p, const void* x, int out_features, int in_fe
         }
         return r;
     }();
-    const int chunks = in_features / kChunkK;
-    const int stage_chunks = p.fp8 ? 1 : kStageChunks;
-    int splits = 1;
-    double best_cost = 1e30;
-    for (int size = 1; size <= 8; ++size) {
-        const int clusters = size == 1 ? sm_count_umma() : residency.clusters[size];
-        if (clusters <= 0 || (size > 1 && chunks / size < 2 * stage_chunks)) {
-            continue;
+    const auto plan_splits = [&](int row_groups, int features_in, bool fp8) {
+        const int chunks = features_in / kChunkK;
+        const int stage_chunks = fp8 ? 1 : kStageChunks;
+        int best = 1;
+        double best_cost = 1e30;
+        for (int size = 1; size <= 8; ++size) {
+            const int clusters = size == 1 ? sm_count_umma() : residency.clusters[size];
+            if (clusters <= 0 || (size > 1 && chunks / size < 2 * stage_chunks)) {
+                continue;
+            }
+            const int waves = (row_groups + clusters - 1) / clusters;
+            const double cost = waves * (static_cast<double>((chunks + size - 1) / size) + 6.0) + 1.5 * (size - 1);
+            if (cost < best_cost) {
+                best_cost = cost;
+                best = size;
+            }
         }
-        const int waves = (p.row_groups + clusters - 1) / clusters;
-        const double cost = waves * (static_cast<double>((chunks + size - 1) / size) + 6.0) + 1.5 * (size - 1);
-        if (cost < best_cost) {
-            best_cost = cost;
-            splits = size;
+        return best;
+    };
+    const int splits = plan_splits(p.row_groups, in_features, p.fp8 != 0);
+    p.splits = splits;
+    // The caller's hint about the projection that follows (one use): its plan is made the way its own
+    // launch will make it, so that this launch's CTAs ask for the boxes that launch starts with.
+    CUtensorMap next_map0 = map0, next_map1 = map1;
+    p.next.valid = 0;
+    const NextProjection hint = take_next_projection();
+    if (hint.packed[0] != nullptr && hint.out_features > 0 && hint.in_features > 0) {
+        const bool next_fp8 = hint.kind == 2;
+        const bool next_swiglu = hint.kind == 1;
+        const int next_row_bytes = next_fp8 ? hint.in_features : hint.in_features / 2;
+        const int next_rows_per_group = next_swiglu ? kTileRows : kTiles * kTileRows;
+        const int next_groups = (hint.out_features + next_rows_per_group - 1) / next_rows_per_group;
+        if (encode_weight_map(&next_map0, hint.packed[0], hint.out_features, next_row_bytes) == cudaSuccess &&
+            encode_weight_map(&next_map1, hint.packed[next_swiglu ? 1 : 0], hint.out_features, next_row_bytes) ==
+                cudaSuccess) {
+            p.next.valid = 1;
+            p.next.swiglu = next_swiglu ? 1 : 0;
+            p.next.nvfp4 = next_fp8 ? 0 : 1;
+            p.next.out_features = hint.out_features;
+            p.next.splits = plan_splits(next_groups, hint.in_features, next_fp8);
+            p.next.ctas = next_groups * p.next.splits;
+            p.next.stages_in_k = hint.in_features / (kChunkK * (next_fp8 ? 1 : kStageChunks));
+            p.next.group_blocks = hint.in_features / 64;
+            p.next.scales[0] = static_cast<const uint8_t*>(hint.scales[0]);
+            p.next.scales[1] = static_cast<const uint8_t*>(hint.scales[next_swiglu ? 1 : 0]);
         }
     }
-    p.splits = splits;
     p.status = status_ptr();
     if (p.status == nullptr) {
         return cudaErrorInvalidValue;
@@ -839,7 +957,7 @@ cudaError_t launch_umma(UmmaParams p, const void* x, int out_features, int in_fe
     attribute[1].val.clusterDim.z = 1;
     config.attrs = attribute;
     config.numAttrs = splits > 1 ? 2 : 1;
-    return cudaLaunchKernelEx(&config, nvfp4_umma_kernel, map0, map1, x_map, p);
+    return cudaLaunchKernelEx(&config, nvfp4_umma_kernel, map0, map1, x_map, next_map0, next_map1, p);
 }
 
 }  // namespace

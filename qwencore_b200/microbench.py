@@ -83,7 +83,8 @@ def report(label: str, microseconds: float, nbytes: int) -> dict:
     return {"label": label, "us": microseconds, "gbs": gbs, "frac": gbs / peak}
 
 
-def projection(out_features: int, in_features: int, rows: int, swiglu: bool = False, plain: int = 0) -> dict:
+def projection(out_features: int, in_features: int, rows: int, swiglu: bool = False, plain: int = 0,
+               hint: bool = False) -> dict:
     matrix_bytes = out_features * in_features // 2 + ops.block_scale_storage_len(out_features, in_features)
     per_launch = matrix_bytes * (2 if swiglu else 1)
     copies = max(2, -(-2 * L2_BYTES // per_launch)) if not plain else 2
@@ -103,6 +104,13 @@ def projection(out_features: int, in_features: int, rows: int, swiglu: bool = Fa
     def launch():
         index = counter[0] % copies
         counter[0] += 1
+        if hint:
+            # the launch after this one reads the next copy
+            after = (index + 1) % copies
+            if swiglu:
+                ops.prefetch_next(linears[2 * after], linears[2 * after + 1])
+            else:
+                ops.prefetch_next(linears[after])
         if swiglu:
             ops.swiglu_w4a16(linears[2 * index], linears[2 * index + 1], x, y, rows)
         else:
@@ -111,7 +119,7 @@ def projection(out_features: int, in_features: int, rows: int, swiglu: bool = Fa
     microseconds = time_launches(launch, 4 * copies, plain)
     nbytes = (out_features * in_features // 2 + out_features * in_features // 16) * (2 if swiglu else 1)
     nbytes += rows * in_features * 2 + rows * out_features * 2
-    name = "swiglu" if swiglu else "gemv"
+    name = ("swiglu" if swiglu else "gemv") + (" +hint" if hint else "")
     return report(f"{name} N={out_features} K={in_features} M={rows}", microseconds, nbytes)
 
 
@@ -214,6 +222,8 @@ def main(argv=None) -> None:
     parser.add_argument("args", nargs="*")
     parser.add_argument("--partitions", type=int, default=0)
     parser.add_argument("--page", type=int, default=16)
+    parser.add_argument("--hint", action="store_true",
+                        help="name the next launch's weights to each projection (qwc_nvfp4_prefetch_next)")
     parser.add_argument("--plain", type=int, default=0, help="issue this many eager launches and exit (for a profiler)")
     options = parser.parse_args(argv)
     if not torch.cuda.is_available():
@@ -222,7 +232,7 @@ def main(argv=None) -> None:
     values = options.args
     if options.kernel in ("gemv", "swiglu"):
         n, k, m = (int(v) for v in values[:3])
-        projection(n, k, m, swiglu=options.kernel == "swiglu", plain=options.plain)
+        projection(n, k, m, swiglu=options.kernel == "swiglu", plain=options.plain, hint=options.hint)
     elif options.kernel == "lm_head":
         lm_head(int(values[0]), int(values[1]), int(values[2]), plain=options.plain)
     elif options.kernel == "delta":

@@ -81,6 +81,18 @@ def swiglu_w4a16(gate: Linear, up: Linear, x: torch.Tensor, out: torch.Tensor, b
               "qwc_nvfp4_swiglu_w4a16")
 
 
+def prefetch_next(first: Linear, second: Linear | None = None) -> None:
+    """Names the projection that follows the next one launched from this thread (a hint for L2):
+    one matrix, or the gate and up matrices of a SwiGLU pair."""
+    if second is None:
+        abi.check(abi.lib.qwc_nvfp4_prefetch_next(_p(first.packed), _p(first.scales), None, None, first.out_features,
+                                                  first.in_features, 0), "qwc_nvfp4_prefetch_next")
+    else:
+        abi.check(abi.lib.qwc_nvfp4_prefetch_next(_p(first.packed), _p(first.scales), _p(second.packed),
+                                                  _p(second.scales), first.out_features, first.in_features, 1),
+                  "qwc_nvfp4_prefetch_next")
+
+
 def packed_workspace_bytes(rows: int, partitions: int) -> int:
     return int(abi.lib.qwc_paged_attention_packed_workspace_bytes(rows, partitions))
 

@@ -127,6 +127,44 @@ def test_w4a16_model_shapes_within_rms_bound(cuda, ops, out_features, in_feature
         assert_rms_close(got, oracle.bf16_round(want), f"gemv {out_features}x{in_features} b{batch}")
 
 
+def test_prefetch_next_hint_changes_no_result_and_rejects_bad_arguments(cuda, ops):
+    """qwc_nvfp4_prefetch_next only moves lines into L2: a hinted launch stores the same bytes."""
+    torch = cuda
+    from qwencore_b200 import abi
+    N, K, batch = 5120, 6144, 32
+    packed, scales, swizzled = synth.nvfp4_matrix(3, "hinted", N, K)
+    other_p, _, other_sw = synth.nvfp4_matrix(3, "after", 12352, 5120)
+    up_p, _, up_sw = synth.nvfp4_matrix(3, "after_up", 12352, 5120)
+    x = dev(torch, synth.normal_bf16(3, "x", (batch, K)))
+    linear = ops.Linear(dev(torch, packed), dev(torch, swizzled), 1.0, N, K)
+    after = ops.Linear(dev(torch, other_p), dev(torch, other_sw), 1.0, 12352, 5120)
+    after_up = ops.Linear(dev(torch, up_p), dev(torch, up_sw), 1.0, 12352, 5120)
+    plain = bf16_out(torch, batch, N)
+    linear.forward_w4a16(x, plain, batch)
+    for second in (None, after_up):
+        hinted = bf16_out(torch, batch, N)
+        ops.prefetch_next(after, second)
+        linear.forward_w4a16(x, hinted, batch)
+        torch.cuda.synchronize()
+        assert np.array_equal(host(hinted), host(plain))
+    table = torch.zeros((4096, 5120), dtype=torch.uint8, device="cuda")
+    assert abi.lib.qwc_nvfp4_prefetch_next(table.data_ptr(), None, None, None, 4096, 5120, 2) == 0
+    hinted = bf16_out(torch, batch, N)
+    linear.forward_w4a16(x, hinted, batch)
+    torch.cuda.synchronize()
+    assert np.array_equal(host(hinted), host(plain))
+    invalid = 1  # cudaErrorInvalidValue
+    good = (after.packed.data_ptr(), after.scales.data_ptr())
+    assert abi.lib.qwc_nvfp4_prefetch_next(None, good[1], None, None, 12352, 5120, 0) == invalid
+    assert abi.lib.qwc_nvfp4_prefetch_next(good[0], None, None, None, 12352, 5120, 0) == invalid
+    assert abi.lib.qwc_nvfp4_prefetch_next(good[0], good[1], None, None, 12352, 5120, 1) == invalid
+    assert abi.lib.qwc_nvfp4_prefetch_next(good[0], good[1], None, None, 12352, 5000, 0) == invalid
+    assert abi.lib.qwc_nvfp4_prefetch_next(good[0], good[1], None, None, 0, 5120, 0) == invalid
+    assert abi.lib.qwc_nvfp4_prefetch_next(good[0], good[1], None, None, 12352, 5120, 3) == invalid
+    assert abi.lib.qwc_nvfp4_prefetch_next(good[0] + 8, good[1], None, None, 12352, 5120, 0) == invalid
+    assert abi.lib.qwc_device_status() == 0
+
+
 @pytest.mark.parametrize("batch", [1, 6, 13, 32])
 def test_swiglu_w4a16_mlp_shape(cuda, ops, batch):
     torch = cuda
