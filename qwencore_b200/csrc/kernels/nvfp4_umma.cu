@@ -276,11 +276,53 @@ __global__ void __launch_bounds__(kThreads, 1)
         tile_scales[t] = p.scales[t];  // the launcher repeats matrix 0 when there is no second one
     }
 
-    if (threadIdx.x == 0) {
+    // One stage of the weight ring: a box per tile and the tiles' block scales (issued by one thread).
+    auto issue_stage = [&](int wstage) {
+        const int slot = wstage % kWeightStages;
+        const int first = (s_begin + wstage) * kStageChunks;  // first 128-element chunk of this stage
+        constexpr int n = kStageChunks;
+        // A box is always delivered whole (rows or bytes outside the matrix arrive as zeros)
+        // and the scale storage is padded to whole 128-row blocks; a tile that starts past
+        // the matrix has no scale block at all and keeps whatever the slot held (its rows
+        // are never stored).
+        int scale_tiles_present = 0;
+#pragma unroll
+        for (int t = 0; t < kTiles; ++t) {
+            scale_tiles_present += tile_row0[t] < p.out_features ? 1 : 0;
+        }
+        if (p.fp8) {
+            scale_tiles_present = 0;  // one float per row, applied in the epilogue
+        }
+        mbar_arrive_expect_tx(&bars.w_full[slot], kTiles * kBoxBytes + scale_tiles_present * n * 1024);
+        // Byte offset of the stage within a row: 64 bytes per 128 four-bit elements, or one
+        // 128-byte box per 128 e4m3 elements.
+        const int byte0 = p.fp8 ? (s_begin + wstage) * 128 : first * 64;
+#pragma unroll
+        for (int t = 0; t < kTiles; ++t) {
+            unsigned char* stage = weight_ring + (slot * kTiles + t) * kTileStageBytes;
+            tma_box_g2s(stage, t == 1 ? &map1 : &map0, byte0, tile_row0[t], &bars.w_full[slot]);
+            if (!p.fp8 && tile_row0[t] < p.out_features) {
+                bulk_g2s(stage + kBoxBytes,
+                         tile_scales[t] + (static_cast<size_t>(tile_row0[t] >> 7) * group_blocks + 2 * first) * 512,
+                         n * 1024, &bars.w_full[slot]);
+            }
+        }
+    };
+    // The first trip round the weight ring does not wait for the rest of the CTA: the producer's
+    // thread sets up the ring's own barriers and asks for the first stages before the CTA-wide barrier
+    // (weights are never written during a step, so nothing has to be waited for either).
+    const int early_stages = num_wstages < kWeightStages ? num_wstages : kWeightStages;
+    if (threadIdx.x == kProducerWarp * 32) {
         for (int s = 0; s < kWeightStages; ++s) {
             mbar_init(&bars.w_full[s], 1);
             mbar_init(&bars.w_empty[s], p.fp8 ? kRowWarps : kDequantWarps);  // warps that read a stage
         }
+        mbar_fence_init();
+        for (int wstage = 0; wstage < early_stages; ++wstage) {
+            issue_stage(wstage);
+        }
+    }
+    if (threadIdx.x == 0) {
         for (int t = 0; t < kTiles; ++t) {
             for (int b = 0; b < kABuffers; ++b) {
                 mbar_init(&bars.a_ready[t][b], 4);
@@ -463,42 +505,15 @@ __global__ void __launch_bounds__(kThreads, 1)
     } else if (warp == kProducerWarp) {
         // ---------------- producer: weights and scales ----------------
         bool ok = true;
-        for (int wstage = 0; wstage < num_wstages && ok; ++wstage) {
+        for (int wstage = early_stages; wstage < num_wstages && ok; ++wstage) {
             const int slot = wstage % kWeightStages;
-            const int first = (s_begin + wstage) * kStageChunks;  // first 128-element chunk of this stage
             ok = wait_or_fail(&bars.w_empty[slot], ((wstage / kWeightStages) & 1) ^ 1, &bars, p.status);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) {
                 break;
             }
             if (elect_one()) {
-                constexpr int n = kStageChunks;
-                // A box is always delivered whole (rows or bytes outside the matrix arrive as zeros)
-                // and the scale storage is padded to whole 128-row blocks; a tile that starts past
-                // the matrix has no scale block at all and keeps whatever the slot held (its rows
-                // are never stored).
-                int scale_tiles_present = 0;
-#pragma unroll
-                for (int t = 0; t < kTiles; ++t) {
-                    scale_tiles_present += tile_row0[t] < p.out_features ? 1 : 0;
-                }
-                if (p.fp8) {
-                    scale_tiles_present = 0;  // one float per row, applied in the epilogue
-                }
-                mbar_arrive_expect_tx(&bars.w_full[slot], kTiles * kBoxBytes + scale_tiles_present * n * 1024);
-                // Byte offset of the stage within a row: 64 bytes per 128 four-bit elements, or one
-                // 128-byte box per 128 e4m3 elements.
-                const int byte0 = p.fp8 ? (s_begin + wstage) * 128 : first * 64;
-#pragma unroll
-                for (int t = 0; t < kTiles; ++t) {
-                    unsigned char* stage = weight_ring + (slot * kTiles + t) * kTileStageBytes;
-                    tma_box_g2s(stage, t == 1 ? &map1 : &map0, byte0, tile_row0[t], &bars.w_full[slot]);
-                    if (!p.fp8 && tile_row0[t] < p.out_features) {
-                        bulk_g2s(stage + kBoxBytes,
-                                 tile_scales[t] + (static_cast<size_t>(tile_row0[t] >> 7) * group_blocks + 2 * first) * 512,
-                                 n * 1024, &bars.w_full[slot]);
-                    }
-                }
+                issue_stage(wstage);
             }
             __syncwarp();
         }
