@@ -775,6 +775,16 @@ __global__ void __launch_bounds__(kThreads, 1)
         cluster.sync();  // nobody leaves while a peer may still read its shared memory
     }
 
+    // A CTA that gave up must not return while the stages it asked for before the barrier are still
+    // landing in its shared memory: their thread waits for them, with a limit of 0.2 ms per ring slot
+    // (a stage that was consumed has completed its first phase long ago and the wait falls through).
+    if (failed && threadIdx.x == kProducerWarp * 32) {
+        for (int slot = 0; slot < kWeightStages; ++slot) {
+            const long long start = clock64();
+            while (!mbar_try_wait(&bars.w_full[slot], 0) && clock64() - start < 400000ll) {
+            }
+        }
+    }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
     if (warp == kMmaWarp) {
