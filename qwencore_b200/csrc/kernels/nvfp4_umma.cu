@@ -692,14 +692,17 @@ __global__ void __launch_bounds__(kThreads, 1)
     } else {
         __syncthreads();
     }
-    if (!failed && warp < kRowWarps) {
+    // Every warp of the CTA takes part: the loop is a chain of dependent instructions per unit (and a
+    // division and an exponential per output for SwiGLU), so the more units run side by side the
+    // sooner the CTA leaves.
+    if (!failed) {
         const int unit_shift = p.swiglu ? 4 : 5;  // 8-row units per token: 16 (128 outputs) or 32 (256)
         const int row0 = p.swiglu ? row_group * kTileRows : row_group * kTiles * kTileRows;
         const int owned = split < p.batch ? (p.batch - split + p.splits - 1) / p.splits : 0;
         const auto slice_base = [&](int r) -> const float* {
             return p.splits > 1 ? cluster.map_shared_rank(parked, r) : parked;
         };
-        for (int u = threadIdx.x; u < (owned << unit_shift); u += kParkedRows) {
+        for (int u = threadIdx.x; u < (owned << unit_shift); u += kThreads) {
             const int token = split + (u >> unit_shift) * p.splits;
             const int r8 = (u & ((1 << unit_shift) - 1)) * 8;
             float first[8] = {0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f};
