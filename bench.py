@@ -37,7 +37,7 @@ ROWS = 32
 CONTEXT_LOW, CONTEXT_HIGH = 128, 32768
 PAGE = 16
 METRIC = "decode_tokens_per_second"
-NCU_TRAFFIC_RATIO = 104.56 / 100.35  # profiles/nvfp4_umma_34816x5120_m32.md
+NCU_TRAFFIC_RATIO = 104.83 / 100.35  # profiles/nvfp4_umma_34816x5120_m32.md
 
 
 # ---- clocks ---------------------------------------------------------------------------------
