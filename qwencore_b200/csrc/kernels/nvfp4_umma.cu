@@ -237,6 +237,8 @@ __device__ __forceinline__ void tmem_load32(uint32_t taddr, float (&v)[32]) {
     }
 }
 
+// kFp8: the vocabulary-head mode as its own instantiation, so that neither carries the other's code.
+template <bool kFp8>
 __global__ void __launch_bounds__(kThreads, 1)
     nvfp4_umma_kernel(const __grid_constant__ CUtensorMap map0, const __grid_constant__ CUtensorMap map1,
                       const __grid_constant__ CUtensorMap x_map, const __grid_constant__ CUtensorMap next_map0,
@@ -253,7 +255,7 @@ __global__ void __launch_bounds__(kThreads, 1)
     const int split = blockIdx.x - row_group * p.splits;
     const int K = p.in_features;
     // K is cut into stages of 256 elements; a slice is a whole number of stages.
-    const int stage_chunks = p.fp8 ? 1 : kStageChunks;  // 128 bytes per row and stage either way
+    const int stage_chunks = kFp8 ? 1 : kStageChunks;  // 128 bytes per row and stage either way
     const int stages_in_k = K / (kChunkK * stage_chunks);
     const int s_begin = static_cast<int>(static_cast<long long>(stages_in_k) * split / p.splits);
     const int s_end = static_cast<int>(static_cast<long long>(stages_in_k) * (split + 1) / p.splits);
@@ -290,18 +292,18 @@ __global__ void __launch_bounds__(kThreads, 1)
         for (int t = 0; t < kTiles; ++t) {
             scale_tiles_present += tile_row0[t] < p.out_features ? 1 : 0;
         }
-        if (p.fp8) {
+        if (kFp8) {
             scale_tiles_present = 0;  // one float per row, applied in the epilogue
         }
         mbar_arrive_expect_tx(&bars.w_full[slot], kTiles * kBoxBytes + scale_tiles_present * n * 1024);
         // Byte offset of the stage within a row: 64 bytes per 128 four-bit elements, or one
         // 128-byte box per 128 e4m3 elements.
-        const int byte0 = p.fp8 ? (s_begin + wstage) * 128 : first * 64;
+        const int byte0 = kFp8 ? (s_begin + wstage) * 128 : first * 64;
 #pragma unroll
         for (int t = 0; t < kTiles; ++t) {
             unsigned char* stage = weight_ring + (slot * kTiles + t) * kTileStageBytes;
             tma_box_g2s(stage, t == 1 ? &map1 : &map0, byte0, tile_row0[t], &bars.w_full[slot]);
-            if (!p.fp8 && tile_row0[t] < p.out_features) {
+            if (!kFp8 && tile_row0[t] < p.out_features) {
                 bulk_g2s(stage + kBoxBytes,
                          tile_scales[t] + (static_cast<size_t>(tile_row0[t] >> 7) * group_blocks + 2 * first) * 512,
                          n * 1024, &bars.w_full[slot]);
@@ -315,7 +317,7 @@ __global__ void __launch_bounds__(kThreads, 1)
     if (threadIdx.x == kProducerWarp * 32) {
         for (int s = 0; s < kWeightStages; ++s) {
             mbar_init(&bars.w_full[s], 1);
-            mbar_init(&bars.w_empty[s], p.fp8 ? kRowWarps : kDequantWarps);  // warps that read a stage
+            mbar_init(&bars.w_empty[s], kFp8 ? kRowWarps : kDequantWarps);  // warps that read a stage
         }
         mbar_fence_init();
         for (int wstage = 0; wstage < early_stages; ++wstage) {
@@ -398,7 +400,7 @@ __global__ void __launch_bounds__(kThreads, 1)
             }
         };
         for (int c = set; c < total_chunks && ok; c += kDequantSets) {
-            const int wstage = p.fp8 ? c : c / kStageChunks;
+            const int wstage = kFp8 ? c : c / kStageChunks;
             const int slot = wstage % kWeightStages;
             const int q = set;
             ok = wait_or_fail(&bars.w_full[slot], (wstage / kWeightStages) & 1, &bars, p.status);
@@ -409,7 +411,7 @@ __global__ void __launch_bounds__(kThreads, 1)
             const unsigned char* stage = weight_ring + (slot * kTiles + tile) * kTileStageBytes;
             const unsigned char* row = stage + row_offset;
             const int buf = c % kABuffers;
-            if (p.fp8) {
+            if (kFp8) {
                 // 128 e4m3 bytes of this row: one conversion per pair, no block scale (the per-row
                 // scale is applied to the accumulator in the epilogue)
                 uint4 bytes[8];
@@ -747,7 +749,7 @@ __global__ void __launch_bounds__(kThreads, 1)
                 }
             }
             const int row = row0 + r8;
-            if (row < p.out_features && p.fp8) {
+            if (row < p.out_features && kFp8) {
                 // vocabulary head: fp32 logits, one scale per weight row
                 const float4 s_lo = *reinterpret_cast<const float4*>(p.row_scales + row);
                 const float4 s_hi = *reinterpret_cast<const float4*>(p.row_scales + row + 4);
@@ -886,8 +888,13 @@ cudaError_t launch_umma(UmmaParams p, const void* x, int out_features, int in_fe
     }
     const int smem_bytes =
         kWeightStages * kTiles * kTileStageBytes + (kXStages + kXStages * kRawBuffers) * 32 * kChunkK * 2 + 1024;
-    static const cudaError_t opted =
-        cudaFuncSetAttribute(nvfp4_umma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
+    static const cudaError_t opted = [smem_bytes]() {
+        const cudaError_t first =
+            cudaFuncSetAttribute(nvfp4_umma_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
+        return first != cudaSuccess
+                   ? first
+                   : cudaFuncSetAttribute(nvfp4_umma_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
+    }();
     if (opted != cudaSuccess) {
         return opted;
     }
@@ -912,7 +919,7 @@ cudaError_t launch_umma(UmmaParams p, const void* x, int out_features, int in_fe
             probe.attrs = attribute;
             probe.numAttrs = 1;
             int clusters = 0;
-            if (cudaOccupancyMaxActiveClusters(&clusters, nvfp4_umma_kernel, &probe) != cudaSuccess) {
+            if (cudaOccupancyMaxActiveClusters(&clusters, nvfp4_umma_kernel<false>, &probe) != cudaSuccess) {
                 clusters = 0;
                 (void)cudaGetLastError();
             }
@@ -985,7 +992,8 @@ cudaError_t launch_umma(UmmaParams p, const void* x, int out_features, int in_fe
     attribute[1].val.clusterDim.z = 1;
     config.attrs = attribute;
     config.numAttrs = splits > 1 ? 2 : 1;
-    return cudaLaunchKernelEx(&config, nvfp4_umma_kernel, map0, map1, x_map, next_map0, next_map1, p);
+    return p.fp8 ? cudaLaunchKernelEx(&config, nvfp4_umma_kernel<true>, map0, map1, x_map, next_map0, next_map1, p)
+                 : cudaLaunchKernelEx(&config, nvfp4_umma_kernel<false>, map0, map1, x_map, next_map0, next_map1, p);
 }
 
 }  // namespace
