@@ -237,8 +237,10 @@ __device__ __forceinline__ void tmem_load32(uint32_t taddr, float (&v)[32]) {
     }
 }
 
-// kFp8: the vocabulary-head mode as its own instantiation, so that neither carries the other's code.
-template <bool kFp8>
+// The mode (vocabulary head, SwiGLU pair) and the padded batch are template parameters: every
+// instantiation carries only its own code, which the instruction caches of an SM with five kinds of
+// warps per scheduler repay.
+template <bool kFp8, bool kSwiglu, int kPad>
 __global__ void __launch_bounds__(kThreads, 1)
     nvfp4_umma_kernel(const __grid_constant__ CUtensorMap map0, const __grid_constant__ CUtensorMap map1,
                       const __grid_constant__ CUtensorMap x_map, const __grid_constant__ CUtensorMap next_map0,
@@ -262,7 +264,7 @@ __global__ void __launch_bounds__(kThreads, 1)
     const int num_wstages = s_end - s_begin;
     const int total_chunks = num_wstages * stage_chunks;
     const int group_blocks = K / 64;
-    const int n_pad = p.n_pad;
+    constexpr int n_pad = kPad;  // activation rows padded to 16 or 32
     const int x_stage_bytes = n_pad * kChunkK * 2;
 
     unsigned char* weight_ring = smem;                                                   // [stage][tile][box | scales]
@@ -274,7 +276,7 @@ __global__ void __launch_bounds__(kThreads, 1)
     const uint8_t* tile_scales[kTiles];
 #pragma unroll
     for (int t = 0; t < kTiles; ++t) {
-        tile_row0[t] = p.swiglu ? row_group * kTileRows : (row_group * kTiles + t) * kTileRows;
+        tile_row0[t] = kSwiglu ? row_group * kTileRows : (row_group * kTiles + t) * kTileRows;
         tile_scales[t] = p.scales[t];  // the launcher repeats matrix 0 when there is no second one
     }
 
@@ -698,8 +700,8 @@ __global__ void __launch_bounds__(kThreads, 1)
     // division and an exponential per output for SwiGLU), so the more units run side by side the
     // sooner the CTA leaves.
     if (!failed) {
-        const int unit_shift = p.swiglu ? 4 : 5;  // 8-row units per token: 16 (128 outputs) or 32 (256)
-        const int row0 = p.swiglu ? row_group * kTileRows : row_group * kTiles * kTileRows;
+        const int unit_shift = kSwiglu ? 4 : 5;  // 8-row units per token: 16 (128 outputs) or 32 (256)
+        const int row0 = kSwiglu ? row_group * kTileRows : row_group * kTiles * kTileRows;
         const int owned = split < p.batch ? (p.batch - split + p.splits - 1) / p.splits : 0;
         const auto slice_base = [&](int r) -> const float* {
             return p.splits > 1 ? cluster.map_shared_rank(parked, r) : parked;
@@ -730,7 +732,7 @@ __global__ void __launch_bounds__(kThreads, 1)
                         first[4] += b[j].x; first[5] += b[j].y; first[6] += b[j].z; first[7] += b[j].w;
                     }
                 }
-                if (p.swiglu) {
+                if (kSwiglu) {
 #pragma unroll
                     for (int j = 0; j < 4; ++j) {
                         if (base + j < p.splits) {
@@ -764,7 +766,7 @@ __global__ void __launch_bounds__(kThreads, 1)
                 for (int i = 0; i < 4; ++i) {
                     float lo = first[2 * i] * p.inverse_scale[0];
                     float hi = first[2 * i + 1] * p.inverse_scale[0];
-                    if (p.swiglu) {
+                    if (kSwiglu) {
                         lo = lo / (1.0f + __expf(-lo)) * (second[2 * i] * p.inverse_scale[1]);
                         hi = hi / (1.0f + __expf(-hi)) * (second[2 * i + 1] * p.inverse_scale[1]);
                     }
@@ -888,12 +890,20 @@ cudaError_t launch_umma(UmmaParams p, const void* x, int out_features, int in_fe
     }
     const int smem_bytes =
         kWeightStages * kTiles * kTileStageBytes + (kXStages + kXStages * kRawBuffers) * 32 * kChunkK * 2 + 1024;
+    using Kernel = void (*)(const CUtensorMap, const CUtensorMap, const CUtensorMap, const CUtensorMap,
+                            const CUtensorMap, const UmmaParams);
+    static const Kernel kernels[6] = {nvfp4_umma_kernel<false, false, 16>, nvfp4_umma_kernel<false, false, 32>,
+                                      nvfp4_umma_kernel<false, true, 16>,  nvfp4_umma_kernel<false, true, 32>,
+                                      nvfp4_umma_kernel<true, false, 16>,  nvfp4_umma_kernel<true, false, 32>};
     static const cudaError_t opted = [smem_bytes]() {
-        const cudaError_t first =
-            cudaFuncSetAttribute(nvfp4_umma_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
-        return first != cudaSuccess
-                   ? first
-                   : cudaFuncSetAttribute(nvfp4_umma_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
+        for (const Kernel kernel : kernels) {
+            const cudaError_t error =
+                cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
+            if (error != cudaSuccess) {
+                return error;
+            }
+        }
+        return cudaSuccess;
     }();
     if (opted != cudaSuccess) {
         return opted;
@@ -919,7 +929,7 @@ cudaError_t launch_umma(UmmaParams p, const void* x, int out_features, int in_fe
             probe.attrs = attribute;
             probe.numAttrs = 1;
             int clusters = 0;
-            if (cudaOccupancyMaxActiveClusters(&clusters, nvfp4_umma_kernel<false>, &probe) != cudaSuccess) {
+            if (cudaOccupancyMaxActiveClusters(&clusters, kernels[1], &probe) != cudaSuccess) {
                 clusters = 0;
                 (void)cudaGetLastError();
             }
@@ -992,8 +1002,8 @@ cudaError_t launch_umma(UmmaParams p, const void* x, int out_features, int in_fe
     attribute[1].val.clusterDim.z = 1;
     config.attrs = attribute;
     config.numAttrs = splits > 1 ? 2 : 1;
-    return p.fp8 ? cudaLaunchKernelEx(&config, nvfp4_umma_kernel<true>, map0, map1, x_map, next_map0, next_map1, p)
-                 : cudaLaunchKernelEx(&config, nvfp4_umma_kernel<false>, map0, map1, x_map, next_map0, next_map1, p);
+    const Kernel kernel = kernels[(p.fp8 ? 4 : (p.swiglu ? 2 : 0)) + (p.n_pad == 32 ? 1 : 0)];
+    return cudaLaunchKernelEx(&config, kernel, map0, map1, x_map, next_map0, next_map1, p);
 }
 
 }  // namespace
