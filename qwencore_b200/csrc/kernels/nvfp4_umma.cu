@@ -237,10 +237,10 @@ __device__ __forceinline__ void tmem_load32(uint32_t taddr, float (&v)[32]) {
     }
 }
 
-// The mode (vocabulary head, SwiGLU pair) and the padded batch are template parameters: every
+// The mode (vocabulary head, SwiGLU pair), the padded batch and whether K is split are template parameters: every
 // instantiation carries only its own code, which the instruction caches of an SM with five kinds of
 // warps per scheduler repay.
-template <bool kFp8, bool kSwiglu, int kPad>
+template <bool kFp8, bool kSwiglu, int kPad, bool kSplit>
 __global__ void __launch_bounds__(kThreads, 1)
     nvfp4_umma_kernel(const __grid_constant__ CUtensorMap map0, const __grid_constant__ CUtensorMap map1,
                       const __grid_constant__ CUtensorMap x_map, const __grid_constant__ CUtensorMap next_map0,
@@ -253,14 +253,16 @@ __global__ void __launch_bounds__(kThreads, 1)
     pdl_launch_dependents();
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
-    const int row_group = blockIdx.x / p.splits;
-    const int split = blockIdx.x - row_group * p.splits;
+    const int splits = kSplit ? p.splits : 1;  // K slices of a row group = CTAs of the cluster
+    const int row_group = blockIdx.x / splits;
+    const int split = blockIdx.x - row_group * splits;
     const int K = p.in_features;
     // K is cut into stages of 256 elements; a slice is a whole number of stages.
     const int stage_chunks = kFp8 ? 1 : kStageChunks;  // 128 bytes per row and stage either way
     const int stages_in_k = K / (kChunkK * stage_chunks);
-    const int s_begin = static_cast<int>(static_cast<long long>(stages_in_k) * split / p.splits);
-    const int s_end = static_cast<int>(static_cast<long long>(stages_in_k) * (split + 1) / p.splits);
+    // stages_in_k * 8 fits 32 bits for every K an int can hold
+    const int s_begin = stages_in_k * split / splits;
+    const int s_end = stages_in_k * (split + 1) / splits;
     const int num_wstages = s_end - s_begin;
     const int total_chunks = num_wstages * stage_chunks;
     const int group_blocks = K / 64;
@@ -691,7 +693,7 @@ __global__ void __launch_bounds__(kThreads, 1)
             parked[i * kParkedRows + threadIdx.x] = result[i];
         }
     }
-    if (p.splits > 1) {
+    if (kSplit) {
         cluster.sync();
     } else {
         __syncthreads();
@@ -702,12 +704,12 @@ __global__ void __launch_bounds__(kThreads, 1)
     if (!failed) {
         const int unit_shift = kSwiglu ? 4 : 5;  // 8-row units per token: 16 (128 outputs) or 32 (256)
         const int row0 = kSwiglu ? row_group * kTileRows : row_group * kTiles * kTileRows;
-        const int owned = split < p.batch ? (p.batch - split + p.splits - 1) / p.splits : 0;
+        const int owned = split < p.batch ? (p.batch - split + splits - 1) / splits : 0;
         const auto slice_base = [&](int r) -> const float* {
-            return p.splits > 1 ? cluster.map_shared_rank(parked, r) : parked;
+            return kSplit ? cluster.map_shared_rank(parked, r) : parked;
         };
         for (int u = threadIdx.x; u < (owned << unit_shift); u += kThreads) {
-            const int token = split + (u >> unit_shift) * p.splits;
+            const int token = split + (u >> unit_shift) * splits;
             const int r8 = (u & ((1 << unit_shift) - 1)) * 8;
             float first[8] = {0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f};
             float second[8] = {0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f};  // the up rows of a SwiGLU pair
@@ -715,11 +717,11 @@ __global__ void __launch_bounds__(kThreads, 1)
             // of four slices are issued together and only then summed (in slice order, as before), so a
             // six-way split waits for two round trips instead of six.
             const int offset = token * kParkedRows + r8;
-            for (int base = 0; base < p.splits; base += 4) {
+            for (int base = 0; base < splits; base += 4) {
                 float4 a[4], b[4];
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
-                    if (base + j < p.splits) {
+                    if (base + j < splits) {
                         const float* peer = slice_base(base + j) + offset;
                         a[j] = *reinterpret_cast<const float4*>(peer);
                         b[j] = *reinterpret_cast<const float4*>(peer + 4);
@@ -727,7 +729,7 @@ __global__ void __launch_bounds__(kThreads, 1)
                 }
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
-                    if (base + j < p.splits) {
+                    if (base + j < splits) {
                         first[0] += a[j].x; first[1] += a[j].y; first[2] += a[j].z; first[3] += a[j].w;
                         first[4] += b[j].x; first[5] += b[j].y; first[6] += b[j].z; first[7] += b[j].w;
                     }
@@ -735,7 +737,7 @@ __global__ void __launch_bounds__(kThreads, 1)
                 if (kSwiglu) {
 #pragma unroll
                     for (int j = 0; j < 4; ++j) {
-                        if (base + j < p.splits) {
+                        if (base + j < splits) {
                             const float* peer = slice_base(base + j) + offset + kTileRows;
                             a[j] = *reinterpret_cast<const float4*>(peer);
                             b[j] = *reinterpret_cast<const float4*>(peer + 4);
@@ -743,7 +745,7 @@ __global__ void __launch_bounds__(kThreads, 1)
                     }
 #pragma unroll
                     for (int j = 0; j < 4; ++j) {
-                        if (base + j < p.splits) {
+                        if (base + j < splits) {
                             second[0] += a[j].x; second[1] += a[j].y; second[2] += a[j].z; second[3] += a[j].w;
                             second[4] += b[j].x; second[5] += b[j].y; second[6] += b[j].z; second[7] += b[j].w;
                         }
@@ -778,7 +780,7 @@ __global__ void __launch_bounds__(kThreads, 1)
             }
         }
     }
-    if (p.splits > 1) {
+    if (kSplit) {
         cluster.sync();  // nobody leaves while a peer may still read its shared memory
     }
 
@@ -892,9 +894,13 @@ cudaError_t launch_umma(UmmaParams p, const void* x, int out_features, int in_fe
         kWeightStages * kTiles * kTileStageBytes + (kXStages + kXStages * kRawBuffers) * 32 * kChunkK * 2 + 1024;
     using Kernel = void (*)(const CUtensorMap, const CUtensorMap, const CUtensorMap, const CUtensorMap,
                             const CUtensorMap, const UmmaParams);
-    static const Kernel kernels[6] = {nvfp4_umma_kernel<false, false, 16>, nvfp4_umma_kernel<false, false, 32>,
-                                      nvfp4_umma_kernel<false, true, 16>,  nvfp4_umma_kernel<false, true, 32>,
-                                      nvfp4_umma_kernel<true, false, 16>,  nvfp4_umma_kernel<true, false, 32>};
+    static const Kernel kernels[12] = {
+        nvfp4_umma_kernel<false, false, 16, false>, nvfp4_umma_kernel<false, false, 32, false>,
+        nvfp4_umma_kernel<false, true, 16, false>,  nvfp4_umma_kernel<false, true, 32, false>,
+        nvfp4_umma_kernel<true, false, 16, false>,  nvfp4_umma_kernel<true, false, 32, false>,
+        nvfp4_umma_kernel<false, false, 16, true>,  nvfp4_umma_kernel<false, false, 32, true>,
+        nvfp4_umma_kernel<false, true, 16, true>,   nvfp4_umma_kernel<false, true, 32, true>,
+        nvfp4_umma_kernel<true, false, 16, true>,   nvfp4_umma_kernel<true, false, 32, true>};
     static const cudaError_t opted = [smem_bytes]() {
         for (const Kernel kernel : kernels) {
             const cudaError_t error =
@@ -929,7 +935,7 @@ cudaError_t launch_umma(UmmaParams p, const void* x, int out_features, int in_fe
             probe.attrs = attribute;
             probe.numAttrs = 1;
             int clusters = 0;
-            if (cudaOccupancyMaxActiveClusters(&clusters, kernels[1], &probe) != cudaSuccess) {
+            if (cudaOccupancyMaxActiveClusters(&clusters, kernels[7], &probe) != cudaSuccess) {
                 clusters = 0;
                 (void)cudaGetLastError();
             }
@@ -1002,7 +1008,7 @@ cudaError_t launch_umma(UmmaParams p, const void* x, int out_features, int in_fe
     attribute[1].val.clusterDim.z = 1;
     config.attrs = attribute;
     config.numAttrs = splits > 1 ? 2 : 1;
-    const Kernel kernel = kernels[(p.fp8 ? 4 : (p.swiglu ? 2 : 0)) + (p.n_pad == 32 ? 1 : 0)];
+    const Kernel kernel = kernels[(splits > 1 ? 6 : 0) + (p.fp8 ? 4 : (p.swiglu ? 2 : 0)) + (p.n_pad == 32 ? 1 : 0)];
     return cudaLaunchKernelEx(&config, kernel, map0, map1, x_map, next_map0, next_map1, p);
 }
 
