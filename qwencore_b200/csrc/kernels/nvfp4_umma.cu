@@ -132,10 +132,9 @@ struct Barriers {
     int failed;
 };
 
-__device__ __forceinline__ bool wait_or_fail(uint64_t* bar, uint32_t parity, Barriers* b, int* status) {
-    if (mbar_try_wait(bar, parity)) {
-        return true;
-    }
+// The polling loop is kept out of line: it is inlined at no call site, so the roles' main loops stay
+// short for the instruction caches; a wait that is already satisfied costs one test.
+__device__ __noinline__ bool wait_or_fail_slow(uint64_t* bar, uint32_t parity, Barriers* b, int* status) {
     const long long start = clock64();
     for (;;) {
 #pragma unroll 1
@@ -154,6 +153,13 @@ __device__ __forceinline__ bool wait_or_fail(uint64_t* bar, uint32_t parity, Bar
     atomicCAS(status, 0, kStatusGemvWait);
     *reinterpret_cast<volatile int*>(&b->failed) = 1;
     return false;
+}
+
+__device__ __forceinline__ bool wait_or_fail(uint64_t* bar, uint32_t parity, Barriers* b, int* status) {
+    if (mbar_try_wait(bar, parity)) {
+        return true;
+    }
+    return wait_or_fail_slow(bar, parity, b, status);
 }
 
 // True in exactly one lane of a converged warp.  The compiler keeps the operands of what that lane
