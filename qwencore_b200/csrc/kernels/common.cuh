@@ -126,8 +126,9 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 // records `code` in the status word and returns false; callers then skip the data and
 // exit cleanly.  Kernels that wait also return at once when the status word is already
 // set, so one failed wait cannot serialise into a long stall over the whole grid.
-__device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity, int code,
-                                                  int* status) {
+// The polling loop stays out of line so that the loops that wait stay short for the instruction caches;
+// a wait that is already satisfied costs one test.
+static __device__ __noinline__ bool mbar_wait_bounded_slow(uint64_t* bar, uint32_t parity, int code, int* status) {
     const long long start = clock64();
     for (;;) {
 #pragma unroll 1
@@ -142,6 +143,13 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity
     }
     atomicCAS(status, 0, code);
     return false;
+}
+
+__device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity, int code, int* status) {
+    if (mbar_try_wait(bar, parity)) {
+        return true;
+    }
+    return mbar_wait_bounded_slow(bar, parity, code, status);
 }
 
 __device__ __forceinline__ bool status_is_set(const int* status) {
