@@ -10,7 +10,11 @@ the device-to-host read of the sampled tokens.  `roofline` is the NVFP4 projecti
 algorithmic bytes per launch over its event-timed duration (a CUDA graph of all projection
 launches of one step, replayed on the engine's stream), against the measured HBM copy rate of this
 pool.  `cpu_baseline` / `--impl reference` time the scalar CPU port of the
-reference's own `reference` modules on the host cores, on a bounded sample of the same step.
+reference's own `reference` modules on the host cores, on a bounded sample of the same step: four
+layers (three DeltaNet, one full attention) at c=32 with the benchmark's contexts, times 16, plus
+the vocabulary head timed on an eighth of its rows.  `c1` is the same engine at one row (context
+2048), the other half of the metric; with N > 1 `latency_mode` adds the column-split step at batch 1
+over all N GPUs.
 
 With N > 1 (launched by torchrun) every rank owns a full replica and a disjoint slice of the
 batch - no collective on the data path - so `value` is the sum over ranks (weak scaling).
@@ -37,7 +41,10 @@ ROWS = 32
 CONTEXT_LOW, CONTEXT_HIGH = 128, 32768
 PAGE = 16
 METRIC = "decode_tokens_per_second"
-NCU_TRAFFIC_RATIO = 104.83 / 100.35  # profiles/nvfp4_umma_34816x5120_m32.md
+C1_CONTEXT = 2048
+# DRAM read + write of one captured projection launch (ncu, 34816 x 5120 at 32 rows) over its
+# algorithmic bytes; every launch streams its matrix once, so the traffic scales with the matrix.
+NCU_TRAFFIC_RATIO = 104.83 / 100.35
 
 
 # ---- clocks ---------------------------------------------------------------------------------
@@ -135,6 +142,18 @@ class RankGroup:
         self.dist.all_reduce(t, op=self.dist.ReduceOp.MAX)
         return float(t.item())
 
+    def gather(self, values) -> list:
+        """Every rank's list of floats, in rank order."""
+        if self.dist is None:
+            return [list(values)]
+        import torch
+
+        mine = torch.tensor(list(values), dtype=torch.float64,
+                            device=self.device if self.backend == "nccl" else "cpu")
+        everyone = [torch.zeros_like(mine) for _ in range(self.world)]
+        self.dist.all_gather(everyone, mine)
+        return [t.tolist() for t in everyone]
+
     def whole_job_rate(self, units_per_rank: float, slowest_seconds: float) -> float:
         return self.world * units_per_rank / slowest_seconds
 
@@ -154,51 +173,56 @@ def measured_peak_gbs():
     return 6650.0, "fallback"
 
 
-def step_macs(contexts, hidden=5120, intermediate=17408, vocab=151936, v_heads=32, layers=64, interval=4):
-    """Multiply-accumulates of one step: what the scalar CPU path has to do."""
-    rows = len(contexts)
-    full = layers // interval
-    linear = layers - full
-    mixer = 2 * 2048 + 2 * v_heads * 128 + 2 * v_heads
-    mlp = 3 * intermediate * hidden
-    per_row = layers * mlp + linear * (mixer * hidden + hidden * v_heads * 128) + \
-        full * (14336 * hidden + hidden * 6144) + vocab * hidden
-    attention = full * 2 * 24 * 256 * float(np.sum(contexts))
-    delta = linear * rows * v_heads * 128 * 128 * 4
-    return rows * per_row + attention + delta, rows * mlp
+CPU_SAMPLE_LAYERS = 4
+CPU_HEAD_FRACTION = 8
 
 
-def cpu_sample(threads: int, repeats: int = 1):
-    """Times the oracle on one MLP block (gate/up SwiGLU + down) for the 32-row batch.
+class CpuStep:
+    """The CPU port on a bounded sample of the benchmark's step: `CPU_SAMPLE_LAYERS` layers (3 DeltaNet +
+    1 full attention, the model's pattern) at c=32 with the benchmark's contexts, extrapolated linearly
+    to 64 layers, plus the vocabulary head and argmax timed on 1/8 of the rows."""
 
-    Returns (seconds per sample, sample MACs, description)."""
-    from oracle import oracle
-    from qwencore_b200 import synth
+    def __init__(self, threads: int):
+        from oracle import oracle, step
 
-    hidden, intermediate = 5120, 17408
-    oracle.set_num_threads(threads)
-    gate = synth.nvfp4_matrix(0, "bench.gate", intermediate, hidden)
-    up = synth.nvfp4_matrix(0, "bench.up", intermediate, hidden)
-    down = synth.nvfp4_matrix(0, "bench.down", hidden, intermediate)
-    x = synth.normal_bf16(0, "bench.x", (ROWS, hidden))
-    best = float("inf")
-    for _ in range(repeats):
+        self.oracle, self.step = oracle, step
+        self.threads = threads
+        oracle.set_num_threads(threads)
+        self.head_rows = 151936 // CPU_HEAD_FRACTION
+        self.model = step.SyntheticModel(contexts_for(0), num_layers=CPU_SAMPLE_LAYERS, head_rows=self.head_rows)
+        self.head_seconds = None
+
+    def layers_seconds(self) -> float:
         start = time.perf_counter()
-        g = oracle.gemv_w4a16(gate[0], gate[1], 1.0, x, intermediate, hidden, ROWS)
-        u = oracle.gemv_w4a16(up[0], up[1], 1.0, x, intermediate, hidden, ROWS)
-        h = oracle.bf16_from_f32(oracle.swiglu_combine(g, u))
-        oracle.gemv_w4a16(down[0], down[1], 1.0, h, hidden, intermediate, ROWS)
-        best = min(best, time.perf_counter() - start)
-    return best, ROWS * 3 * intermediate * hidden, "one MLP block (NVFP4 gate/up SwiGLU + down) at c=32"
+        _, _, self.normed = self.step.decode_step(self.model, self.model.layout, self.model.tokens, head=False)
+        return time.perf_counter() - start
+
+    def head_seconds_full(self) -> float:
+        model, oracle = self.model, self.oracle
+        start = time.perf_counter()
+        logits = oracle.fp8_lm_head(model.lm_head, model.lm_head_scales, self.normed, ROWS, model.cfg.hidden,
+                                    self.head_rows)
+        oracle.argmax(logits, self.head_rows, ROWS)
+        return (time.perf_counter() - start) * CPU_HEAD_FRACTION
+
+    def step_seconds(self):
+        """(seconds of one whole step, seconds of the layer sample, seconds of the head)."""
+        layers = self.layers_seconds()
+        if self.head_seconds is None:
+            self.head_seconds = self.head_seconds_full()
+        return layers * (64 / CPU_SAMPLE_LAYERS) + self.head_seconds, layers, self.head_seconds
+
+    def describe(self, layers: float, head: float, runs: int = 1) -> str:
+        return (f"{CPU_SAMPLE_LAYERS} layers (3 DeltaNet + 1 full attention) of the step at c=32, contexts log-uniform "
+                f"[{CONTEXT_LOW}, {CONTEXT_HIGH}]: {layers:.2f} s on {self.threads} threads"
+                f"{'' if runs == 1 else f' (mean of {runs} runs)'}, x{64 // CPU_SAMPLE_LAYERS} for 64 layers; "
+                f"vocabulary head + argmax on 1/{CPU_HEAD_FRACTION} of the rows, x{CPU_HEAD_FRACTION}: {head:.2f} s")
 
 
-def cpu_tokens_per_second(threads: int, repeats: int = 1):
-    seconds, sample_macs, what = cpu_sample(threads, repeats)
-    total_macs, _ = step_macs(contexts_for(0))
-    step_seconds = seconds * total_macs / sample_macs
-    sample = (f"{what}: {seconds:.2f} s on {threads} threads; scaled by multiply-accumulate count to the whole "
-              f"step (x{total_macs / sample_macs:.1f})")
-    return ROWS / step_seconds, sample
+def cpu_tokens_per_second(threads: int):
+    sample = CpuStep(threads)
+    seconds, layers, head = sample.step_seconds()
+    return ROWS / seconds, sample.describe(layers, head)
 
 
 def base_line(args, n_gpus):
@@ -230,36 +254,31 @@ def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return 0
-    from oracle import oracle
-
     threads = os.cpu_count() or 1
-    oracle.set_num_threads(threads)
+    sample = CpuStep(threads)
     for _ in range(min(args.warmup, 1)):
-        cpu_sample(threads)
-    samples = []
+        sample.step_seconds()
+    steps, layer_samples = [], []
+    head = 0.0
     start = time.perf_counter()
-    what = ""
-    sample_macs = 1
     for _ in range(args.steps):
-        seconds, sample_macs, what = cpu_sample(threads)
-        samples.append(seconds)
+        seconds, layers, head = sample.step_seconds()
+        steps.append(seconds)
+        layer_samples.append(layers)
         if time.perf_counter() - start > 150:  # bounded: the whole run must end within minutes
             break
-    total_macs, _ = step_macs(contexts_for(0))
-    seconds = float(np.mean(samples))
-    step_seconds = seconds * total_macs / sample_macs
+    step_seconds = float(np.mean(steps))
     value = ROWS / step_seconds
     line = base_line(args, args.gpus)
     line.update({
         "impl": "reference",
         "value": value,
-        "steps": len(samples),
+        "steps": len(steps),
         "ms_per_step": step_seconds * 1e3,
         "config": {**line["config"], "parallelism": "host cores of rank 0"},
         "cpu_baseline": {"value": value, "unit": "tok/s", "cores": threads, "kind": "port",
-                         "sample": f"{what}: mean {seconds:.2f} s over {len(samples)} runs; scaled by "
-                                   f"multiply-accumulate count to the whole step (x{total_macs / sample_macs:.1f}); "
-                                   "the reference's CPU path is Rust and cannot be built here, this is its C port"},
+                         "sample": sample.describe(float(np.mean(layer_samples)), head, len(steps)) +
+                                   "; the reference's CPU path is Rust and cannot be built here, this is its C port"},
         "e2e": {"value": value, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     })
@@ -268,6 +287,80 @@ def run_reference(args):
 
 
 # ---- our arm ------------------------------------------------------------------------------------
+
+def time_worker_steps(engine, scheduler, group, stream, steps, rows):
+    """Wall-clock seconds of `steps` worker-loop steps (host inputs, copies inside), max over ranks."""
+    import torch
+
+    group.barrier()
+    torch.cuda.synchronize()
+    wall = time.perf_counter()
+    for _ in range(steps):
+        decoded, _ = engine.worker_step(scheduler)
+        assert decoded == rows
+    group.barrier()
+    torch.cuda.synchronize()
+    return time.perf_counter() - wall
+
+
+def time_replays(engine, group, stream, steps, rows):
+    """Device seconds of `steps` graph replays with the inputs resident (CUDA events on the engine's stream)."""
+    import torch
+
+    for _ in range(3):
+        engine.replay(rows)
+    group.barrier()
+    torch.cuda.synchronize()
+    begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    begin.record(stream)
+    for _ in range(steps):
+        engine.replay(rows)
+    end.record(stream)
+    group.barrier()
+    torch.cuda.synchronize()
+    return begin.elapsed_time(end) * 1e-3
+
+
+def run_latency_mode(args, group, local_rank, single_gpu_ms):
+    """Batch 1 with every projection column-split over all ranks of the launch (one sequence, context
+    2048): milliseconds per step, max over ranks, and the ranks' sampled tokens compared."""
+    import torch
+
+    from qwencore_b200 import engine as engine_module
+
+    world, rank = group.world, group.rank
+    steps = max(args.steps, 20)
+    blocks = (C1_CONTEXT + steps + args.warmup + 64) // PAGE + 8
+    config = engine_module.default_config(max_batch=1, max_context=C1_CONTEXT + 1024, kv_pool_blocks=blocks,
+                                          state_slots=2, seed=3, split_rank=rank, split_size=world)
+    engine = engine_module.Engine(config)
+    unique = [engine_module.nccl_unique_id() if rank == 0 else None]
+    group.dist.broadcast_object_list(unique, src=0, device=torch.device("cuda", local_rank))
+    engine.init_split(unique[0])
+    cache = engine_module.CacheManager(2, blocks, PAGE)
+    cache.admit(1, C1_CONTEXT)
+    engine.apply_edits(cache.drain_edits())
+    token = np.array([17], dtype=np.uint32)
+    slot = np.array([cache.sequence(1)["state_slot"]], dtype=np.uint32)
+    produced = []
+    for _ in range(max(args.warmup, 3) + 1):  # eager, capture, replays
+        cache.append_token(1)
+        token = engine.decode(slot, token, cache.drain_edits())
+        produced.append(float(token[0]))
+    stream = torch.cuda.ExternalStream(engine.stream)
+    seconds = group.max_over_ranks(time_replays(engine, group, stream, steps, 1))
+    tokens_of_ranks = group.gather(produced)
+    traffic = engine.traffic(1, float(C1_CONTEXT))
+    engine.close()
+    ms = seconds / steps * 1e3
+    return {"ms_per_step": ms, "tok_s": 1e3 / ms, "vs_1gpu": single_gpu_ms / ms, "gpus": world,
+            "exchanges_per_step": int(traffic.gemv_launches_per_step + 1),
+            "weight_bytes_per_rank": traffic.weight_bytes,
+            "preflight": {"ranks_agree_on_tokens": all(t == tokens_of_ranks[0] for t in tokens_of_ranks),
+                          "steps_compared": len(produced)},
+            "workload": f"batch 1, context {C1_CONTEXT}, 64 layers, every projection and the vocabulary head "
+                        f"column-split {world} ways"}
+
 
 def run_ours(args):
     import torch
@@ -279,7 +372,7 @@ def run_ours(args):
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     torch.cuda.set_device(local_rank)
     group = RankGroup("nccl", torch.device("cuda", local_rank))
-    world, rank, distributed = group.world, group.rank, group.world > 1
+    world, rank = group.world, group.rank
 
     contexts = contexts_for(rank)
     total_steps = args.steps + args.warmup + 8
@@ -299,38 +392,15 @@ def run_ours(args):
     for _ in range(max(args.warmup, 3)):  # captures the graph, then replays
         engine.worker_step(scheduler)
 
-    def barrier():
-        group.barrier()
-        torch.cuda.synchronize()
-
-    max_over_ranks = group.max_over_ranks
-
     sampler = ClockSampler(local_rank)
     if rank == 0:
         sampler.start()
 
-    # ---- end to end: host inputs, copies inside the timed region ----
-    barrier()
-    begin, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    wall = time.perf_counter()
-    begin.record(stream)
-    for _ in range(args.steps):
-        rows, _ = engine.worker_step(scheduler)
-        assert rows == ROWS
-    end.record(stream)
-    barrier()
-    e2e_seconds = max_over_ranks(time.perf_counter() - wall)
-
-    # ---- device only: inputs resident, graph replays ----
-    for _ in range(3):
-        engine.replay(ROWS)
-    barrier()
-    begin.record(stream)
-    for _ in range(args.steps):
-        engine.replay(ROWS)
-    end.record(stream)
-    barrier()
-    device_seconds = max_over_ranks(begin.elapsed_time(end) * 1e-3)
+    # ---- c = 32: end to end (host inputs, copies inside the timed region), then device only ----
+    e2e_mine = time_worker_steps(engine, scheduler, group, stream, args.steps, ROWS)
+    e2e_seconds = group.max_over_ranks(e2e_mine)
+    device_mine = time_replays(engine, group, stream, args.steps, ROWS)
+    device_seconds = group.max_over_ranks(device_mine)
 
     clocks = sampler.stop() if rank == 0 else None
 
@@ -340,7 +410,10 @@ def run_ours(args):
     graph_phases = {}
     for prefix in ("gemm.", "attn.decode", "attn.prepare", "delta.scan", "delta.prepare", "delta.norm", "norm",
                    "lm_head", "sample", "pack", "embed"):
-        ms, launched = engine.time_phases(ROWS, prefix, replays=5)
+        try:
+            ms, launched = engine.time_phases(ROWS, prefix, replays=5)
+        except Exception:  # a phase that this build folds into another launches nothing
+            continue
         graph_phases[prefix.rstrip(".")] = {"ms": round(ms, 4), "launches": launched}
     gemv_ms, gemv_launches = graph_phases["gemm"]["ms"], graph_phases["gemm"]["launches"]
     phases = {}
@@ -356,8 +429,33 @@ def run_ours(args):
     achieved = bytes_per_launch / seconds_per_launch / 1e9
     step_bytes = traffic.weight_bytes + traffic.state_bytes + traffic.kv_bytes
 
+    # ---- c = 1: the same engine, one row of context 2048 (the other half of the metric) ----
+    c1_steps = max(args.steps, 20)
+    single = engine_module.Scheduler(ROWS, 1 << 22, ROWS + 1, blocks_needed, PAGE)
+    single.submit(1, C1_CONTEXT, c1_steps + args.warmup + 24)
+    decoded = 0
+    while decoded == 0:
+        decoded, _ = engine.worker_step(single)
+    for _ in range(max(args.warmup, 3)):
+        engine.worker_step(single)
+    c1_e2e = group.max_over_ranks(time_worker_steps(engine, single, group, stream, c1_steps, 1))
+    c1_device = group.max_over_ranks(time_replays(engine, group, stream, c1_steps, 1))
+    c1_gemm_ms, c1_gemm_launches = engine.time_phases(1, "gemm.", replays=5)
+    c1_traffic = engine.traffic(1, float(C1_CONTEXT))
+    c1_bytes = c1_traffic.weight_bytes + c1_traffic.state_bytes + c1_traffic.kv_bytes
+
+    per_rank = group.gather([device_mine / args.steps * 1e3, e2e_mine / args.steps * 1e3, traffic.kv_bytes,
+                             float(np.sum(contexts))])
+    engine.close()
+
+    latency = None
+    if world > 1:
+        try:
+            latency = run_latency_mode(args, group, local_rank, c1_device / c1_steps * 1e3)
+        except Exception as error:  # the throughput line must still be printed
+            latency = {"error": f"{type(error).__name__}: {error}"}
+
     if rank != 0:
-        engine.close()
         group.close()
         return 0
 
@@ -368,16 +466,17 @@ def run_ours(args):
         "value": group.whole_job_rate(tokens, device_seconds),
         "ms_per_step": device_seconds / args.steps * 1e3,
         "e2e": {"value": group.whole_job_rate(tokens, e2e_seconds), "unit": "tok/s", "ms_per_step": e2e_seconds / args.steps * 1e3,
-                "h2d_bytes_per_step": int((2 * ROWS + 4 * 2 * ROWS) * 4), "d2h_bytes_per_step": int((ROWS + 1) * 4),
+                "h2d_bytes_per_step": int((2 * ROWS + 4 * 2 * ROWS) * 4), "d2h_bytes_per_step": int((ROWS + 2) * 4),
                 "path": "qwc_worker_step: scheduler.next_batch, layout check, H2D of slots/tokens/edits, graph "
-                        "replay, D2H of sampled tokens, scheduler.complete_batch"},
+                        "replay, D2H of sampled tokens and status words, scheduler.complete_batch"},
         "gpu_launches": int(traffic.kernel_launches_per_step * args.steps),
-        "roofline": {"bound": "hbm", "kernel": "nvfp4_umma_kernel (all NVFP4 projections of the step)",
+        "roofline": {"bound": "hbm", "kernel": "NVFP4 projection kernel (all NVFP4 projections of the step)",
                      "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                      "peak_kind": f"of {peak_kind}",
-                     # DRAM read + write of one captured launch (ncu, 34816 x 5120, 32 rows) is 1.04 x its
-                     # algorithmic bytes; every launch streams its matrix once, so traffic scales with it
                      "traffic": bytes_per_launch * NCU_TRAFFIC_RATIO,
+                     "traffic_source": "ncu dram__bytes_read.sum + dram__bytes_write.sum of one captured launch "
+                                       "(34816 x 5120 at 32 rows) over its algorithmic bytes, applied to the "
+                                       "average projection launch of the step",
                      "bytes_per_launch": bytes_per_launch, "us_per_launch": seconds_per_launch * 1e6,
                      "launches_timed": gemv_launches},
         "step_roofline": {"bytes_per_step": step_bytes, "weights": traffic.weight_bytes,
@@ -385,14 +484,26 @@ def run_ours(args):
                           "achieved_gbs": step_bytes / (device_seconds / args.steps) / 1e9,
                           "frac_of_measured_peak": step_bytes / (device_seconds / args.steps) / 1e9 / peak,
                           "frac_of_8tbs": step_bytes / (device_seconds / args.steps) / 8e12},
+        "c1": {"workload": f"one row, context {C1_CONTEXT}, same engine and graph path",
+               "value": group.whole_job_rate(c1_steps, c1_device), "unit": "tok/s",
+               "ms_per_step": c1_device / c1_steps * 1e3,
+               "e2e": {"value": group.whole_job_rate(c1_steps, c1_e2e), "unit": "tok/s",
+                       "ms_per_step": c1_e2e / c1_steps * 1e3},
+               "bytes_per_step": c1_bytes,
+               "frac_of_measured_peak": c1_bytes / (c1_device / c1_steps) / 1e9 / peak,
+               "frac_of_8tbs": c1_bytes / (c1_device / c1_steps) / 8e12,
+               "projections_ms": round(c1_gemm_ms, 4), "projection_launches": c1_gemm_launches},
+        "per_rank": [{"rank": i, "ms_per_step": round(v[0], 4), "e2e_ms_per_step": round(v[1], 4), "kv_bytes": v[2],
+                      "context_tokens": v[3]} for i, v in enumerate(per_rank)],
         "phases_graph_ms_per_step": graph_phases,
         "phases_eager_ms_per_step": {label: round(total[0], 4) for label, total in sorted(phases.items())},
         "cpu_baseline": {"value": cpu_value, "unit": "tok/s", "cores": os.cpu_count() or 1, "kind": "port",
                          "sample": cpu_sample_text},
         "clocks": clocks,
     })
+    if latency is not None:
+        line["latency_mode"] = latency
     print(json.dumps(line))
-    engine.close()
     group.close()
     return 0
 

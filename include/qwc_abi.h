@@ -51,6 +51,13 @@ void qwc_get_shape(qwc_shape* shape);
  * (see qwc_device_status_reset).  Host call; synchronises the device. */
 int qwc_device_status(void);
 int qwc_device_status_reset(void);
+/* Host-side fault injection: stores `code` in the status word as a bounded wait that gave up
+ * would (every kernel that waits then returns at once and skips its stores).  Synchronises. */
+int qwc_device_status_set(int code);
+/* Copies the status word to `destination` (device memory, 4 bytes) in stream order: no sync,
+ * capture-legal.  A step that ends with this copy lets its caller read the word together with
+ * the step's results instead of synchronising for it. */
+int qwc_device_status_copy(void* destination, qwc_stream stream);
 
 /* ------------------------------------------------------------------ */
 /* NVFP4 W4A16 projections                                              */
@@ -87,7 +94,9 @@ int qwc_nvfp4_swiglu_w4a16(const void* gate_packed, const void* gate_scales, con
  * Pure hint: host-side only (no launch, no sync, capture-legal), good for one launch of this
  * thread, ignored when that launch does not take the tcgen05 path; wrong or stale hints cost
  * bandwidth, never correctness (prefetches do not fault on valid device memory and write nothing).
- * The pointers must be device memory of the shapes given, 16-byte aligned.
+ * The pointers must be device memory of the shapes given, 16-byte aligned, and must stay mapped
+ * until the projection call that consumes the hint has run on the device (a call that is refused
+ * for bad arguments consumes the hint without launching anything).
  * Returns cudaErrorInvalidValue for a null matrix, non-positive or misaligned shapes, or an unknown kind.
  */
 int qwc_nvfp4_prefetch_next(const void* packed0, const void* scales0, const void* packed1,

@@ -147,6 +147,12 @@ int qwc_engine_init_split(qwc_engine* engine, const void* unique_id_128);
  * caches back.  Layer-indexed names take the layer number; others ignore it.  Returns 0 or 1. */
 int qwc_engine_tensor(qwc_engine* engine, const char* name, int layer, void** device_ptr, size_t* bytes);
 
+/* Test aid: with `enable` != 0 every later step also copies, per layer, the mixer's output
+ * projection and the residual stream after the MLP into the tensor "trace"
+ * (bf16 [num_layers][2][max_batch][hidden]); 0 turns it off again.  Captured graphs are dropped
+ * either way (the next step of each batch size is captured anew). */
+int qwc_engine_trace_layers(qwc_engine* engine, int enable);
+
 /* Synchronous copies of a named tensor to / from host memory (`bytes` must equal its size). */
 int qwc_engine_read(qwc_engine* engine, const char* name, int layer, void* host, size_t bytes);
 int qwc_engine_write(qwc_engine* engine, const char* name, int layer, const void* host, size_t bytes);
@@ -173,7 +179,10 @@ int qwc_engine_apply_edits(qwc_engine* engine, const qwc_table_edit* edits, size
  * greedy tokens back into sampled u32[rows].  Synchronous.  Mirrors
  * Executor::execute_layout for a pure-decode layout (executor.rs:878-905,947-951).
  * Returns a cudaError_t; a packing error (status word of qwc_pack_decode_batch) is returned
- * as 0x1000 + status.
+ * as 0x1000 + status, and a bounded device-side wait that gave up or a state slot beyond the
+ * pool (the sticky word of qwc_device_status, which the step copies back with its tokens) as
+ * 0x4000 + status: such a step has skipped stores and its tokens must not be committed
+ * (qwc_worker_step rolls the batch back).
  */
 int qwc_engine_decode(qwc_engine* engine, const uint32_t* row_slots, const uint32_t* tokens,
                       const qwc_table_edit* edits, size_t num_edits, int rows, uint32_t* sampled);

@@ -42,6 +42,8 @@ KERNEL_SYMBOLS = {
     "qwc_get_shape": (None, [POINTER(Shape)]),
     "qwc_device_status": (c_int, []),
     "qwc_device_status_reset": (c_int, []),
+    "qwc_device_status_set": (c_int, [c_int]),
+    "qwc_device_status_copy": (c_int, [P, P]),
     "qwc_nvfp4_w4a16": (c_int, [P, P, P, P, c_int, c_int, c_int, c_float, P]),
     "qwc_nvfp4_swiglu_w4a16": (c_int, [P, P, P, P, P, P, c_int, c_int, c_int, c_float, c_float, P]),
     "qwc_nvfp4_prefetch_next": (c_int, [P, P, P, P, c_int, c_int, c_int]),

@@ -213,7 +213,7 @@ struct qwc_engine {
     uint32_t *block_offsets = nullptr, *block_tables = nullptr, *block_table_offsets = nullptr, *row_count = nullptr;
     __nv_bfloat16 *cosine = nullptr, *sine = nullptr;
 
-    // step inputs / outputs: [row_slots | tokens | edits] and [sampled | pack status]
+    // step inputs / outputs: [row_slots | tokens | edits] and [sampled | pack status | wait status]
     uint32_t* in_host = nullptr;
     uint32_t* in_dev = nullptr;
     uint32_t* out_host = nullptr;
@@ -228,6 +228,9 @@ struct qwc_engine {
     const char* phase_filter = nullptr;  // when set, only phases whose label starts with it are launched
     int filtered_launches = 0;
     std::vector<Phase> marks;
+
+    // per-layer trace (parity tests): [layer][mixer_out | residual after the MLP][max_batch * hidden] bf16
+    __nv_bfloat16* trace = nullptr;
 
     // latency mode
     void* comm = nullptr;
@@ -429,6 +432,11 @@ int decode_forward(qwc_engine* e, int batch) {
                 QWC_TRY(project(e, layer.o, e->attention_out, e->mixer_out, batch));
             }
         }
+        const size_t trace_row = static_cast<size_t>(c.max_batch) * c.hidden;
+        if (e->trace != nullptr && e->phase_filter == nullptr) {
+            QWC_TRY(cudaMemcpyAsync(e->trace + (2 * index) * trace_row, e->mixer_out, trace_row * 2,
+                                    cudaMemcpyDeviceToDevice, s));
+        }
         if (phase(e, "norm")) {
             QWC_TRY(qwc_rmsnorm_bf16(e->mixer_out, e->residual, layer.post_norm, e->normed, batch, c.hidden, kEps, s));
         }
@@ -458,6 +466,10 @@ int decode_forward(qwc_engine* e, int batch) {
         if (phase(e, "norm")) {
             QWC_TRY(qwc_rmsnorm_bf16(e->mlp_out, e->residual, next_norm, e->normed, batch, c.hidden, kEps, s));
         }
+        if (e->trace != nullptr && e->phase_filter == nullptr) {
+            QWC_TRY(cudaMemcpyAsync(e->trace + (2 * index + 1) * trace_row, e->residual, trace_row * 2,
+                                    cudaMemcpyDeviceToDevice, s));
+        }
     }
 
     if (phase(e, "lm_head")) {
@@ -473,6 +485,11 @@ int decode_forward(qwc_engine* e, int batch) {
     if (phase(e, "sample")) {
         QWC_TRY(qwc_argmax(e->logits, e->argmax_values, e->argmax_indices, e->out_dev, e->vocab_local * c.split_size, batch,
                            kArgmaxParts, s));
+    }
+    // The sticky status word of the bounded waits rides back with the sampled tokens: a step in
+    // which a wait gave up has skipped stores, and its tokens must not be committed.
+    if (e->phase_filter == nullptr) {
+        QWC_TRY(qwc_device_status_copy(e->out_dev + c.max_batch + 1, s));
     }
     mark(e, "end");  // closes the last phase of the timeline
     return 0;
@@ -771,10 +788,10 @@ int qwc_engine_create(const qwc_engine_config* config, qwc_engine** out) {
         status = cudaMallocHost(reinterpret_cast<void**>(&e->in_host), e->in_words * sizeof(uint32_t));
     }
     if (status == 0) {
-        status = cudaMallocHost(reinterpret_cast<void**>(&e->out_host), (mb + 1) * sizeof(uint32_t));
+        status = cudaMallocHost(reinterpret_cast<void**>(&e->out_host), (mb + 2) * sizeof(uint32_t));
     }
     QWC_STEP(gpu_alloc_t(e, &e->in_dev, e->in_words, true));
-    QWC_STEP(gpu_alloc_t(e, &e->out_dev, mb + 1, true));
+    QWC_STEP(gpu_alloc_t(e, &e->out_dev, mb + 2, true));
 #undef QWC_STEP
     if (status == 0) {
         status = cudaStreamSynchronize(e->stream);
@@ -852,6 +869,7 @@ int qwc_engine_tensor(qwc_engine* e, const char* name, int layer, void** device_
     if (n == "block_tables") return set(e->block_tables, mb * e->max_blocks * 4);
     if (n == "context_lengths") return set(e->context_lengths, mb * 4);
     if (n == "rope_table") return set(e->rope_table, static_cast<size_t>(c.max_context) * 2 * kRopeDim * 2);
+    if (n == "trace") return set(e->trace, static_cast<size_t>(c.num_layers) * 2 * mb * c.hidden * 2);
     if (layer < 0 || layer >= c.num_layers) {
         return 1;
     }
@@ -891,6 +909,28 @@ int qwc_engine_tensor(qwc_engine* e, const char* name, int layer, void** device_
         if (n == "v_cache") return set(l.v_cache, cache_bytes);
     }
     return 1;
+}
+
+int qwc_engine_trace_layers(qwc_engine* e, int enable) {
+    if (e == nullptr) {
+        return cudaErrorInvalidValue;
+    }
+    QWC_TRY(cudaStreamSynchronize(e->stream));
+    // The copies are part of the step's launch sequence: graphs captured without them are dropped.
+    for (cudaGraphExec_t& exec : e->graphs) {
+        if (exec != nullptr) {
+            cudaGraphExecDestroy(exec);
+            exec = nullptr;
+        }
+    }
+    if (enable != 0 && e->trace == nullptr) {
+        const size_t count = static_cast<size_t>(e->cfg.num_layers) * 2 * e->cfg.max_batch * e->cfg.hidden;
+        QWC_TRY(gpu_alloc_t(e, &e->trace, count, true));
+        QWC_TRY(cudaStreamSynchronize(e->stream));
+    } else if (enable == 0) {
+        e->trace = nullptr;  // the buffer stays with the engine's allocations until it is destroyed
+    }
+    return 0;
 }
 
 int qwc_engine_read(qwc_engine* e, const char* name, int layer, void* host, size_t bytes) {
@@ -968,12 +1008,16 @@ int qwc_engine_decode(qwc_engine* e, const uint32_t* row_slots, const uint32_t* 
     }
     QWC_TRY(upload_inputs(e, row_slots, tokens, edits, num_edits, rows));
     QWC_TRY(launch_decode(e, rows));
-    QWC_TRY(cudaMemcpyAsync(e->out_host, e->out_dev, (e->cfg.max_batch + 1) * sizeof(uint32_t), cudaMemcpyDeviceToHost,
+    QWC_TRY(cudaMemcpyAsync(e->out_host, e->out_dev, (e->cfg.max_batch + 2) * sizeof(uint32_t), cudaMemcpyDeviceToHost,
                             e->stream));
     QWC_TRY(cudaStreamSynchronize(e->stream));
     std::memcpy(sampled, e->out_host, sizeof(uint32_t) * rows);
     const uint32_t pack_status = e->out_host[e->cfg.max_batch];
-    return pack_status == 0 ? 0 : 0x1000 + static_cast<int>(pack_status);
+    const uint32_t wait_status = e->out_host[e->cfg.max_batch + 1];
+    if (pack_status != 0) {
+        return 0x1000 + static_cast<int>(pack_status);
+    }
+    return wait_status == 0 ? 0 : 0x4000 + static_cast<int>(wait_status);
 }
 
 int qwc_engine_replay(qwc_engine* e, int rows) {

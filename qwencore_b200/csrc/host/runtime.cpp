@@ -2,6 +2,7 @@
 #include "runtime.h"
 
 #include <algorithm>
+#include <unordered_map>
 #include <limits>
 #include <unordered_set>
 
@@ -156,9 +157,31 @@ const Sequence* CacheManager::sequence(SeqId id) const {
     return it == seqs_.end() ? nullptr : &it->second;
 }
 
+// The device applies one drain with a thread per edit and no order between them, so a drain
+// never carries two edits of the same word: the last one wins here, at the place of the first.
+// (A released slot goes straight to the next admission, and a rollback follows an append, so
+// "tokens = 0" and "tokens = prompt" for one slot do meet in one drain.)
 std::vector<TableEdit> CacheManager::drain_edits() {
     std::vector<TableEdit> out;
-    out.swap(edits_);
+    out.reserve(edits_.size());
+    std::unordered_map<uint64_t, size_t> place;  // (slot, kind, index) -> position in `out`
+    for (const TableEdit& edit : edits_) {
+        if (edit.kind == 2) {
+            // a relative edit cannot be merged with an absolute one; the host emits none
+            out.push_back(edit);
+            continue;
+        }
+        const uint64_t key = (static_cast<uint64_t>(edit.slot) << 33) | (static_cast<uint64_t>(edit.kind & 1u) << 32) |
+                             (edit.kind == 0 ? edit.index : 0u);
+        const auto found = place.find(key);
+        if (found == place.end()) {
+            place.emplace(key, out.size());
+            out.push_back(edit);
+        } else {
+            out[found->second] = edit;
+        }
+    }
+    edits_.clear();
     return out;
 }
 

@@ -7,7 +7,34 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <mutex>
+
 namespace qwc {
+
+// Lazy launcher set-up (shared-memory opt-in of a kernel, residency probes) belongs to a device, not
+// to the process: a kernel attribute set with one device current says nothing about another.
+// `slots` is the caller's table, one entry per device; `setup` runs once per device, with that
+// device current, and its result is returned on every later call from that device.
+constexpr int kMaxDevices = 64;
+template <typename T>
+struct PerDevice {
+    bool done[kMaxDevices] = {};
+    T value[kMaxDevices] = {};
+    std::mutex lock;
+    template <typename Setup>
+    T* get(Setup&& setup) {
+        int device = 0;
+        if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= kMaxDevices) {
+            return nullptr;
+        }
+        std::lock_guard<std::mutex> guard(lock);
+        if (!done[device]) {
+            value[device] = setup();
+            done[device] = true;
+        }
+        return &value[device];
+    }
+};
 
 // Row caps shared by the launchers; garbage-argument guards, not structure
 // (mirrors crates/qwc-cuda/cuda/limits.cuh).
@@ -30,6 +57,8 @@ constexpr int kStatusAttentionPageWait = 0x101;
 constexpr int kStatusDeltaTileWait = 0x102;
 constexpr int kStatusGemvWait = 0x103;
 constexpr int kStatusAttentionPlanOverflow = 0x104;  // a CTA's task list would not hold its share
+constexpr int kStatusStateSlotRange = 0x105;         // a row named a DeltaNet state slot beyond the pool
+constexpr int kStatusPeerWait = 0x106;               // a peer rank's slice of an activation row did not arrive
 
 // What a caller said about the projection its stream runs after the next one it launches
 // (qwc_nvfp4_prefetch_next): kept per host thread, taken (and cleared) by the next projection launch.

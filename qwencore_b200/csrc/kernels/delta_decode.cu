@@ -42,7 +42,7 @@ __global__ void __launch_bounds__(kThreads, 7) delta_decode_int8_kernel(
     int8_t* __restrict__ state, float* __restrict__ state_scales, const uint32_t* __restrict__ state_slots,
     const float* __restrict__ q, const float* __restrict__ k, const float* __restrict__ v,
     const float* __restrict__ alpha, const float* __restrict__ beta, const float* __restrict__ kq,
-    float* __restrict__ out, int v_heads, int* status) {
+    float* __restrict__ out, int v_heads, int state_capacity, int* status) {
     pdl_launch_dependents();
     pdl_wait();
     __shared__ __align__(128) uint8_t tile[kDim * kDim];
@@ -60,6 +60,14 @@ __global__ void __launch_bounds__(kThreads, 7) delta_decode_int8_kernel(
     const int rows_here = kDim / gridDim.z;
     const int row_begin = blockIdx.z * rows_here;
     const int slot = state_slots == nullptr ? b : static_cast<int>(state_slots[b]);
+    if (static_cast<uint32_t>(slot) >= static_cast<uint32_t>(state_capacity)) {
+        // a slot beyond the pool: nothing of this row is read or written, the host learns of it
+        // through the status word (the whole CTA takes this branch: the slot is per row)
+        if (threadIdx.x == 0) {
+            atomicCAS(status, 0, kStatusStateSlotRange);
+        }
+        return;
+    }
     const int hk = h / (v_heads / kDeltaKeyHeads);
     const int parts = (rows_here + kPartRows - 1) / kPartRows;
     const int part_rows = rows_here < kPartRows ? rows_here : kPartRows;
@@ -114,7 +122,9 @@ __global__ void __launch_bounds__(kThreads, 7) delta_decode_int8_kernel(
     constexpr float kMagicBiased = 12583040.0f;  // kMagic + 128
 
     for (int part = 0; part < parts; ++part) {
-        const bool arrived = mbar_wait_bounded(&bars[part], 0, kStatusDeltaTileWait, status);
+        // a warp leaves as a whole: the row reductions below are full-warp shuffles
+        const bool arrived =
+            __all_sync(0xffffffffu, mbar_wait_bounded(&bars[part], 0, kStatusDeltaTileWait, status));
         if (!arrived) {
             failed = 1;
             break;
@@ -196,6 +206,13 @@ __global__ void __launch_bounds__(kThreads, 7) delta_decode_int8_kernel(
     fence_proxy_async();
     __syncthreads();
     if (failed) {
+        // The copies that were asked for may still be landing in this CTA's shared memory: their
+        // thread waits for each of them (bounded) before the CTA gives the memory back.
+        if (threadIdx.x == 0) {
+            for (int part = 0; part < parts; ++part) {
+                mbar_wait_bounded(&bars[part], 0, kStatusDeltaTileWait, status);
+            }
+        }
         return;
     }
     if (threadIdx.x == 0) {
@@ -253,5 +270,5 @@ extern "C" int qwc_delta_decode_int8(void* state, float* state_scales, const voi
         static_cast<int8_t*>(state), state_scales, static_cast<const uint32_t*>(state_slots),
         static_cast<const float*>(q), static_cast<const float*>(k), static_cast<const float*>(v),
         static_cast<const float*>(alpha), static_cast<const float*>(beta), static_cast<const float*>(kq),
-        static_cast<float*>(out), v_heads, status);
+        static_cast<float*>(out), v_heads, state_capacity, status);
 }

@@ -563,16 +563,23 @@ cudaError_t launch(const GemvParams& base, cudaStream_t stream) {
     GemvParams p = base;
     const int row_blocks = (p.out_features + 127) / 128;
     p.num_tiles = row_blocks * ((SWIGLU || MT == 1) ? 8 : 4);
-    static const cudaError_t opted = cudaFuncSetAttribute(
-        nvfp4_gemv_kernel<NT, MT, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemLimit);
-    if (opted != cudaSuccess) {
-        return opted;
+    static PerDevice<cudaError_t> opted_per_device;
+    const cudaError_t* opted = opted_per_device.get([]() {
+        return cudaFuncSetAttribute(nvfp4_gemv_kernel<NT, MT, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                    kSmemLimit);
+    });
+    if (opted == nullptr) {
+        return cudaErrorInvalidDevice;
+    }
+    if (*opted != cudaSuccess) {
+        return *opted;
     }
     // Resident clusters of 1, 2, 4 and 8 full-size CTAs, asked of the driver once.
     struct Residency {
         int clusters[4];
     };
-    static const Residency residency = []() {
+    static PerDevice<Residency> residency_per_device;
+    const Residency* residency_found = residency_per_device.get([]() {
         Residency r = {};
         for (int index = 0; index < 4; ++index) {
             cudaLaunchConfig_t probe = {};
@@ -594,7 +601,11 @@ cudaError_t launch(const GemvParams& base, cudaStream_t stream) {
             r.clusters[index] = clusters;
         }
         return r;
-    }();
+    });
+    if (residency_found == nullptr) {
+        return cudaErrorInvalidDevice;
+    }
+    const Residency& residency = *residency_found;
     const Plan plan =
         choose_plan(p.num_tiles, p.in_features / kChunk, sm_count(), C::kMaxTiles, residency.clusters);
     p.tiles_per_cta = plan.tiles_per_cta;
@@ -728,6 +739,7 @@ extern "C" int qwc_nvfp4_w4a16(const void* packed, const void* scales, const voi
     if (packed == nullptr || scales == nullptr || input == nullptr || output == nullptr || out_features <= 0 ||
         in_features <= 0 || in_features % 256 != 0 || batch <= 0 || batch > qwc::kMaxBatch ||
         !(weight_global_scale > 0.0f)) {
+        (void)qwc::take_next_projection();  // a hint is good for one call, also for one that is refused
         return cudaErrorInvalidValue;
     }
     qwc::GemvParams p = {};
@@ -753,6 +765,7 @@ extern "C" int qwc_nvfp4_swiglu_w4a16(const void* gate_packed, const void* gate_
         input == nullptr || output == nullptr || out_features <= 0 || in_features <= 0 ||
         in_features % 256 != 0 || batch <= 0 || batch > qwc::kMaxBatch || !(gate_global_scale > 0.0f) ||
         !(up_global_scale > 0.0f)) {
+        (void)qwc::take_next_projection();
         return cudaErrorInvalidValue;
     }
     qwc::GemvParams p = {};

@@ -907,7 +907,8 @@ cudaError_t launch_umma(UmmaParams p, const void* x, int out_features, int in_fe
         nvfp4_umma_kernel<false, false, 16, true>,  nvfp4_umma_kernel<false, false, 32, true>,
         nvfp4_umma_kernel<false, true, 16, true>,   nvfp4_umma_kernel<false, true, 32, true>,
         nvfp4_umma_kernel<true, false, 16, true>,   nvfp4_umma_kernel<true, false, 32, true>};
-    static const cudaError_t opted = [smem_bytes]() {
+    static PerDevice<cudaError_t> opted_per_device;
+    const cudaError_t* opted_found = opted_per_device.get([smem_bytes]() {
         for (const Kernel kernel : kernels) {
             const cudaError_t error =
                 cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes);
@@ -916,9 +917,12 @@ cudaError_t launch_umma(UmmaParams p, const void* x, int out_features, int in_fe
             }
         }
         return cudaSuccess;
-    }();
-    if (opted != cudaSuccess) {
-        return opted;
+    });
+    if (opted_found == nullptr) {
+        return cudaErrorInvalidDevice;
+    }
+    if (*opted_found != cudaSuccess) {
+        return *opted_found;
     }
     // K split: the slices of a row group form a cluster, and a cluster must sit inside one GPC, so
     // the number of clusters resident at once is asked of the driver per cluster size.  The cost of
@@ -926,7 +930,8 @@ cudaError_t launch_umma(UmmaParams p, const void* x, int out_features, int in_fe
     struct Residency {
         int clusters[9];
     };
-    static const Residency residency = [smem_bytes]() {
+    static PerDevice<Residency> residency_per_device;
+    const Residency* residency_found = residency_per_device.get([smem_bytes]() {
         Residency r = {};
         for (int size = 1; size <= 8; ++size) {
             cudaLaunchConfig_t probe = {};
@@ -948,7 +953,11 @@ cudaError_t launch_umma(UmmaParams p, const void* x, int out_features, int in_fe
             r.clusters[size] = clusters;
         }
         return r;
-    }();
+    });
+    if (residency_found == nullptr) {
+        return cudaErrorInvalidDevice;
+    }
+    const Residency& residency = *residency_found;
     const auto plan_splits = [&](int row_groups, int features_in, bool fp8) {
         const int chunks = features_in / kChunkK;
         const int stage_chunks = fp8 ? 1 : kStageChunks;

@@ -78,7 +78,9 @@ struct Smem {
     int task_count;
     int issued;                     // stages the producer has put in flight
     int consumed;                   // stages the consumers have finished
-    int failed;
+    int failed;                     // a consumer's wait gave up
+    int producer_failed;            // the producer's wait gave up (written by the producer only)
+    int leave[2];                   // what one consumer thread saw of the two flags before the barrier of stage n & 1
 };
 
 __device__ __forceinline__ uint32_t pack_half2(float lo, float hi) {
@@ -188,6 +190,10 @@ __global__ void __launch_bounds__(kThreads, 1) paged_attention_packed_kernel(
     if (warp == 0) {
         if (lane == 0) {
             sm.failed = 0;
+            sm.producer_failed = 0;
+            sm.leave[0] = 0;
+            sm.leave[1] = 0;
+            sm.consumed = 0;
             sm.issued = 0;
             for (int s = 0; s < kStages; ++s) {
                 mbar_init(&sm.full[s], 1);
@@ -317,7 +323,10 @@ __global__ void __launch_bounds__(kThreads, 1) paged_attention_packed_kernel(
                 // the page id is fetched before the wait for a free slot, which is the longer of the two
                 const uint32_t physical = lane < count ? table[(first + lane) / units_per_page] : 0u;
                 ok = mbar_wait_bounded(&sm.empty[slot], ((n / kStages) & 1) ^ 1, kStatusAttentionPageWait, status);
-                ok = __all_sync(0xffffffffu, ok) && *reinterpret_cast<volatile int*>(&sm.failed) == 0;
+                // one lane reads the consumers' flag for the whole warp: the decision to leave is uniform
+                const int consumers_left =
+                    __shfl_sync(0xffffffffu, *reinterpret_cast<volatile int*>(&sm.failed), 0);
+                ok = __all_sync(0xffffffffu, ok) && consumers_left == 0;
                 if (!ok) {
                     break;
                 }
@@ -340,7 +349,7 @@ __global__ void __launch_bounds__(kThreads, 1) paged_attention_packed_kernel(
             }
         }
         if (!ok && lane == 0) {
-            *reinterpret_cast<volatile int*>(&sm.failed) = 1;
+            *reinterpret_cast<volatile int*>(&sm.producer_failed) = 1;
         }
     } else {
         // ---------------- consumers ---------------------------------------------------------
@@ -458,10 +467,19 @@ __global__ void __launch_bounds__(kThreads, 1) paged_attention_packed_kernel(
                 if (t == 0) {
                     sm.warp_max[warp][g] = local_max;
                 }
+                // The flags can change at any moment (the producer raises its own asynchronously), so a
+                // consumer that read them for itself after the barrier could leave while another stays and
+                // waits at the next barrier for ever.  One thread samples them before the barrier into the
+                // word of this stage; every consumer acts on that word only.  A failure that thread 0 has
+                // not seen yet is acted on one stage later.
+                if (threadIdx.x == 0) {
+                    sm.leave[n & 1] = *reinterpret_cast<volatile int*>(&sm.failed) |
+                                      *reinterpret_cast<volatile int*>(&sm.producer_failed);
+                }
                 consumer_sync();
-                ok = *reinterpret_cast<volatile int*>(&sm.failed) == 0;
+                ok = *reinterpret_cast<volatile int*>(&sm.leave[n & 1]) == 0;
                 if (!ok) {
-                    break;  // every consumer reads the flag after the same barrier and leaves together
+                    break;  // the same word for every consumer: they leave together
                 }
 
                 float new_max = running_max;
@@ -594,7 +612,7 @@ __global__ void __launch_bounds__(kThreads, 1) paged_attention_packed_kernel(
     __syncthreads();
     // After a failed wait the CTA must not return while copies it issued are still landing:
     // one thread waits (bounded) for the stages that were put in flight and never consumed.
-    if (threadIdx.x == 0 && sm.failed != 0) {
+    if (threadIdx.x == 0 && (sm.failed | sm.producer_failed) != 0) {
         for (int i = sm.consumed; i < sm.issued; ++i) {
             mbar_wait_bounded(&sm.full[i % kStages], (i / kStages) & 1, kStatusAttentionPageWait, status);
         }
@@ -751,15 +769,22 @@ cudaError_t launch_attention(const void* query, const void* query_gate_projectio
         return cudaErrorInvalidValue;
     }
     const size_t shared = sizeof(Smem);
-    static const cudaError_t opted_direct = cudaFuncSetAttribute(
-        paged_attention_packed_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(shared));
-    static const cudaError_t opted_split = cudaFuncSetAttribute(
-        paged_attention_packed_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(shared));
-    if (opted_direct != cudaSuccess) {
-        return opted_direct;
+    static PerDevice<cudaError_t> opted_per_device;
+    const cudaError_t* opted = opted_per_device.get([shared]() {
+        const cudaError_t direct =
+            cudaFuncSetAttribute(paged_attention_packed_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 static_cast<int>(shared));
+        if (direct != cudaSuccess) {
+            return direct;
+        }
+        return cudaFuncSetAttribute(paged_attention_packed_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                    static_cast<int>(shared));
+    });
+    if (opted == nullptr) {
+        return cudaErrorInvalidDevice;
     }
-    if (opted_split != cudaSuccess) {
-        return opted_split;
+    if (*opted != cudaSuccess) {
+        return *opted;
     }
     // One CTA per SM, whatever the batch: the task list is cut on the device.  A CTA's list holds
     // kMaxCtaTasks entries; the plan gives it at most kPlanPaddingDivisor + 2 plus one per row and

@@ -12,7 +12,7 @@ Shape g_shape = {48, 64};
 
 __device__ int g_status_word = 0;
 
-constexpr int kMaxDevices = 64;
+
 int* g_status_ptrs[kMaxDevices] = {};
 
 }  // namespace
@@ -71,4 +71,20 @@ extern "C" int qwc_device_status_reset(void) {
         return cudaErrorInvalidValue;
     }
     return cudaMemset(word, 0, sizeof(int));
+}
+
+extern "C" int qwc_device_status_set(int code) {
+    int* word = qwc::status_ptr();
+    if (word == nullptr) {
+        return cudaErrorInvalidValue;
+    }
+    return cudaMemcpy(word, &code, sizeof(int), cudaMemcpyHostToDevice);
+}
+
+extern "C" int qwc_device_status_copy(void* destination, qwc_stream stream) {
+    int* word = qwc::status_ptr();
+    if (word == nullptr || destination == nullptr) {
+        return cudaErrorInvalidValue;
+    }
+    return cudaMemcpyAsync(destination, word, sizeof(int), cudaMemcpyDeviceToDevice, static_cast<cudaStream_t>(stream));
 }

@@ -185,7 +185,7 @@ __global__ void __launch_bounds__(kDeltaHeadDim) delta_prepare_kernel(
     const __nv_bfloat16* __restrict__ a_log, const __nv_bfloat16* __restrict__ dt_bias,
     float* __restrict__ conv_state, const uint32_t* __restrict__ state_slots, float* __restrict__ query,
     float* __restrict__ key, float* __restrict__ value, float* __restrict__ alpha, float* __restrict__ beta,
-    float* __restrict__ kq, int mixed_stride, int gate_stride, int v_heads) {
+    float* __restrict__ kq, int mixed_stride, int gate_stride, int v_heads, int state_capacity, int* status) {
     pdl_launch_dependents();
     __shared__ float scratch[kDeltaHeadDim / 32];
     const int head = blockIdx.x;
@@ -218,6 +218,14 @@ __global__ void __launch_bounds__(kDeltaHeadDim) delta_prepare_kernel(
     }
     pdl_wait();
     const uint32_t slot = state_slots[batch];
+    if (slot >= static_cast<uint32_t>(state_capacity)) {
+        // a slot beyond the pool: the row's conv history is neither read nor written; the host
+        // learns of it through the status word (uniform over the CTA: the slot is per row)
+        if (threadIdx.x == 0) {
+            atomicCAS(status, 0, kStatusStateSlotRange);
+        }
+        return;
+    }
     const size_t slot_base = static_cast<size_t>(slot) * channels;
     const __nv_bfloat16* mixed_row = mixed_qkv + static_cast<size_t>(batch) * mixed_stride;
     // every load of the step's data is issued before the first use
@@ -481,6 +489,10 @@ extern "C" int qwc_delta_prepare_decode(const void* mixed_qkv, const void* a_pro
         mixed_stride < channels || gate_stride < v_heads) {
         return cudaErrorInvalidValue;
     }
+    int* status = qwc::status_ptr();
+    if (status == nullptr) {
+        return cudaErrorInvalidValue;
+    }
     const dim3 grid(kDeltaKeyHeads, batch);
     return qwc::launch_chained(delta_prepare_kernel, dim3(grid), dim3(kDeltaHeadDim), 0, stream, 
         static_cast<const __nv_bfloat16*>(mixed_qkv), static_cast<const __nv_bfloat16*>(a_projection),
@@ -488,7 +500,8 @@ extern "C" int qwc_delta_prepare_decode(const void* mixed_qkv, const void* a_pro
         static_cast<const __nv_bfloat16*>(a_log), static_cast<const __nv_bfloat16*>(dt_bias),
         static_cast<float*>(conv_state), static_cast<const uint32_t*>(state_slots), static_cast<float*>(query),
         static_cast<float*>(key), static_cast<float*>(value), static_cast<float*>(alpha),
-        static_cast<float*>(beta), static_cast<float*>(kq), mixed_stride, gate_stride, v_heads);
+        static_cast<float*>(beta), static_cast<float*>(kq), mixed_stride, gate_stride, v_heads, state_capacity,
+        status);
 }
 
 extern "C" int qwc_delta_gated_rmsnorm(const float* input, const void* gate, const void* weight, void* output,
@@ -549,6 +562,7 @@ extern "C" int qwc_fp8_lm_head_batched(const void* weights, const void* row_scal
                                        void* logits, int batch, int hidden_size, int vocab, cudaStream_t stream) {
     if (weights == nullptr || row_scales == nullptr || hidden == nullptr || logits == nullptr || batch <= 0 ||
         batch > kMaxLogitsRows || hidden_size <= 0 || hidden_size % 256 != 0 || vocab <= 0) {
+        (void)take_next_projection();  // a hint is good for one call, also for one that is refused
         return cudaErrorInvalidValue;
     }
     return launch_fp8_rows(weights, static_cast<const float*>(row_scales), hidden, static_cast<float*>(logits),

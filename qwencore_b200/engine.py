@@ -91,6 +91,7 @@ ENGINE_SYMBOLS = {
     "qwc_engine_nccl_unique_id": (c_int, [P]),
     "qwc_engine_init_split": (c_int, [P, P]),
     "qwc_engine_tensor": (c_int, [P, c_char_p, c_int, POINTER(P), POINTER(c_size_t)]),
+    "qwc_engine_trace_layers": (c_int, [P, c_int]),
     "qwc_engine_read": (c_int, [P, c_char_p, c_int, P, c_size_t]),
     "qwc_engine_write": (c_int, [P, c_char_p, c_int, P, c_size_t]),
     "qwc_engine_traffic": (None, [P, c_int, c_double, POINTER(StepTraffic)]),
@@ -320,6 +321,10 @@ class Engine:
         values = np.ascontiguousarray(values)
         abi.check(lib.qwc_engine_write(self._handle, name.encode(), layer, values.ctypes.data_as(P), values.nbytes),
                   "qwc_engine_write")
+
+    def trace_layers(self, enable: bool = True) -> None:
+        """Per-layer copies of the mixer output and the residual stream into the tensor "trace" (tests)."""
+        abi.check(lib.qwc_engine_trace_layers(self._handle, 1 if enable else 0), "qwc_engine_trace_layers")
 
     def traffic(self, rows: int, context_tokens: float) -> StepTraffic:
         out = StepTraffic()

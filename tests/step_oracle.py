@@ -1,13 +1,10 @@
-"""CPU oracle of the whole decode step, composed from the per-op oracle functions in the
-order of crates/qwc-engine/src/executor.rs:997-1112 with every inter-kernel rounding point
-(bf16 activations between kernels, e4m3 KV pages, int8 state).  Test infrastructure only."""
+"""The engine's weights and caches copied to the host, for the CPU oracle of the whole step
+(oracle/step.py).  Test infrastructure only."""
 
 import numpy as np
 
 from oracle import oracle
-from qwencore_b200 import synth
-
-KEY_HEADS, DIM, Q_HEADS, KV_HEADS, HEAD_DIM = 16, 128, 24, 4, 256
+from oracle.step import DIM, HEAD_DIM, KEY_HEADS, KV_HEADS, Q_HEADS, decode_step, model_dimensions, project  # noqa: F401
 
 
 class HostModel:
@@ -15,15 +12,7 @@ class HostModel:
 
     def __init__(self, engine):
         c = engine.config
-        self.cfg = c
-        self.v_heads = c.delta_value_heads
-        self.channels = 2 * KEY_HEADS * DIM + self.v_heads * DIM
-        self.z_offset = self.channels
-        self.a_offset = self.z_offset + self.v_heads * DIM
-        self.b_offset = self.a_offset + self.v_heads
-        self.mixer_width = self.b_offset + self.v_heads
-        self.qkv_width = Q_HEADS * 2 * HEAD_DIM + 2 * KV_HEADS * HEAD_DIM
-        self.max_blocks = (c.max_context + c.kv_page_size - 1) // c.kv_page_size
+        model_dimensions(self, c)
         self.layers = []
         for i in range(c.num_layers):
             full = (i + 1) % c.full_attention_interval == 0
@@ -64,56 +53,3 @@ class HostModel:
         self.embed_scales = engine.read("embed_scales", 0, np.float32)
         self.lm_head = engine.read("lm_head").reshape(c.vocab, c.hidden)
         self.lm_head_scales = engine.read("lm_head_scales", 0, np.float32)
-
-
-def project(weight, x_bits, batch):
-    packed, scales, n, k = weight
-    return oracle.bf16_from_f32(oracle.gemv_w4a16(packed, scales, 1.0, x_bits, n, k, batch))
-
-
-def decode_step(model: HostModel, layout, tokens):
-    """One step on the host copies (updated in place).  `layout` is oracle.layout_decode output.
-    Returns (logits f32[batch, vocab], argmax u32[batch])."""
-    c = model.cfg
-    batch = len(tokens)
-    slots = layout["state_slots"]
-    cosine, sine = oracle.rope_rows(layout["positions"])
-    residual = oracle.fp8_embedding_gather(model.embed, model.embed_scales, tokens, c.hidden, c.vocab)
-    normed = oracle.rmsnorm_bf16(residual, None, model.layers[0]["input_norm"], batch, c.hidden)
-    for index, layer in enumerate(model.layers):
-        if not layer["full"]:
-            mixed = project(layer["in_proj"], normed, batch)
-            base = mixed.ctypes.data
-            q, k, v, alpha, beta, kq = oracle.delta_prepare_decode(
-                mixed, base + 2 * model.a_offset, base + 2 * model.b_offset, layer["conv_weight"], layer["a_log"],
-                layer["dt_bias"], layer["conv_state"], slots, batch, model.mixer_width, model.mixer_width, KEY_HEADS,
-                model.v_heads)
-            out = oracle.delta_decode_int8(layer["state"], layer["state_scales"], slots, q, k, v, alpha, beta, kq,
-                                           batch, model.v_heads)
-            gated = oracle.delta_gated_rmsnorm(out, base + 2 * model.z_offset, layer["out_norm"], batch,
-                                               model.v_heads, model.mixer_width)
-            mixer_out = project(layer["la_out"], gated.reshape(batch, -1), batch)
-        else:
-            qkv = project(layer["qkv"], normed, batch)
-            q_width = Q_HEADS * 2 * HEAD_DIM
-            query_gate = np.ascontiguousarray(qkv[:, :q_width])
-            key_proj = np.ascontiguousarray(qkv[:, q_width:q_width + KV_HEADS * HEAD_DIM])
-            value_proj = np.ascontiguousarray(qkv[:, q_width + KV_HEADS * HEAD_DIM:])
-            query = oracle.prepare_attention_decode_fp8(
-                query_gate, key_proj, value_proj, layer["q_norm"], layer["k_norm"], cosine, sine,
-                layout["physical_blocks"], layout["block_offsets"], layer["k_cache"], layer["v_cache"], batch,
-                c.kv_page_size, k_scale=layer["k_scale"], v_scale=layer["v_scale"])
-            attended = oracle.paged_attention_fp8(
-                query, query_gate, layer["k_cache"], layer["v_cache"], layout["block_tables"],
-                layout["context_lengths"], model.max_blocks, batch, page_size=c.kv_page_size,
-                k_scale=layer["k_scale"], v_scale=layer["v_scale"])
-            mixer_out = project(layer["o"], oracle.bf16_from_f32(attended).reshape(batch, -1), batch)
-        normed = oracle.rmsnorm_bf16(mixer_out, residual, layer["post_norm"], batch, c.hidden)
-        gate = oracle.gemv_w4a16(layer["gate"][0], layer["gate"][1], 1.0, normed, c.intermediate, c.hidden, batch)
-        up = oracle.gemv_w4a16(layer["up"][0], layer["up"][1], 1.0, normed, c.intermediate, c.hidden, batch)
-        hidden = oracle.bf16_from_f32(oracle.swiglu_combine(gate, up))
-        mlp_out = project(layer["down"], hidden, batch)
-        next_norm = model.layers[index + 1]["input_norm"] if index + 1 < len(model.layers) else model.final_norm
-        normed = oracle.rmsnorm_bf16(mlp_out, residual, next_norm, batch, c.hidden)
-    logits = oracle.fp8_lm_head(model.lm_head, model.lm_head_scales, normed, batch, c.hidden, c.vocab)
-    return logits, oracle.argmax(logits, c.vocab, batch), normed

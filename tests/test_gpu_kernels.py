@@ -382,6 +382,32 @@ def test_delta_zero_rows_store_zero_scale(cuda, ops):
     assert not state.any() and not scales.any() and not out.any()
 
 
+def test_delta_slot_beyond_the_pool_is_skipped_and_reported(cuda, ops):
+    """A row that names a state slot past the pool touches no memory: the kernel skips the row and
+    the sticky status word tells the host (nothing faults; the access never happens)."""
+    from qwencore_b200 import abi
+
+    batch, v_heads = 3, 32
+    case = synth.delta_case(6, batch, v_heads, capacity=4)
+    slots = case["slots"].copy()
+    bad_row = 1
+    slots[bad_row] = 4  # capacity is 4: slots 0..3 exist
+    case = dict(case, slots=slots)
+    assert abi.lib.qwc_device_status() == 0
+    try:
+        state, scales, out = run_delta(cuda, ops, case, batch, v_heads)
+        assert abi.lib.qwc_device_status() == 0x105
+        # the pool is as it was wherever the rows in range did not write, and the bad row wrote nothing
+        touched = {int(s) for i, s in enumerate(slots) if i != bad_row}
+        for slot in range(case["capacity"]):
+            if slot not in touched:
+                assert np.array_equal(state[slot], case["state"][slot])
+        assert not out[bad_row].any()
+    finally:
+        assert abi.lib.qwc_device_status_reset() == 0
+    assert abi.lib.qwc_device_status() == 0
+
+
 # ---------------------------------------------------------------------------------------
 # Step glue
 # ---------------------------------------------------------------------------------------

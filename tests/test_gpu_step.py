@@ -215,6 +215,38 @@ def test_decode_reports_packing_errors(cuda, engine_module):
         engine.close()
 
 
+def test_step_returns_the_device_status_word_and_the_worker_rolls_back(cuda, engine_module):
+    """A bounded wait that gave up leaves a code in the sticky status word and kernels skip their
+    stores: the step must say so instead of returning tokens (injected on the host: the word is
+    set as a failed wait would set it, nothing on the device faults or hangs)."""
+    from qwencore_b200 import abi
+
+    engine = engine_module.Engine(small_config(engine_module, num_layers=4, max_batch=3, state_slots=3))
+    try:
+        scheduler = engine_module.Scheduler(3, 64, 3, 160, 16)
+        scheduler.submit(1, 20, 8)
+        scheduler.submit(2, 33, 8)
+        rows = 0
+        while rows == 0:
+            rows, _ = engine.worker_step(scheduler)
+        assert rows == 2
+        remaining = scheduler.remaining_tokens(1)
+        assert abi.lib.qwc_device_status_set(0x103) == 0
+        try:
+            with pytest.raises(abi.QwcError) as error:
+                engine.worker_step(scheduler)
+            assert error.value.code == 0x4000 + 0x103
+        finally:
+            assert abi.lib.qwc_device_status_reset() == 0
+        # the batch was rolled back: nothing was committed, the next step decodes the same rows
+        assert scheduler.remaining_tokens(1) == remaining
+        rows, _ = engine.worker_step(scheduler)
+        assert rows == 2 and scheduler.remaining_tokens(1) == remaining - 1
+        assert abi.lib.qwc_device_status() == 0
+    finally:
+        engine.close()
+
+
 def test_phase_timeline_covers_every_phase(cuda, engine_module):
     """Timeline marks (crates/qwc-cuda/src/timeline.rs:17-77): one entry per phase label."""
     from qwencore_b200 import abi

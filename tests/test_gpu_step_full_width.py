@@ -1,0 +1,105 @@
+"""The benchmarked configuration itself under the CPU oracle: the widths bench.py times (hidden 5120,
+SwiGLU 17408, vocabulary 151 936, 32 value heads, page 16), a batch of 32 rows with the benchmark's
+log-uniform contexts in [128, 32768], and four layers (three DeltaNet, one full attention) so that
+the scalar oracle finishes in seconds.  One eager and one replayed step; per layer the mixer output
+and the residual stream, at the end the full logits and the greedy tokens.
+
+(crates/qwc-engine/src/executor.rs:997-1112 is the step the oracle restates.)"""
+
+import numpy as np
+import pytest
+
+from oracle import oracle
+from qwencore_b200 import synth
+
+pytestmark = pytest.mark.gpu
+
+ROWS = 32
+PAGE = 16
+LAYERS = 4
+
+
+def relative_errors(got_bits, want_bits):
+    """(max abs error, rms error) of two bf16 tensors, both divided by the RMS of the oracle's."""
+    got = synth.bf16_value(got_bits).astype(np.float64)
+    want = synth.bf16_value(want_bits).astype(np.float64)
+    rms = np.sqrt(np.mean(want ** 2))
+    return np.max(np.abs(got - want)) / rms, np.sqrt(np.mean((got - want) ** 2)) / rms
+
+
+def test_benchmark_width_step_matches_oracle_layer_by_layer(cuda, built_library, capsys):
+    from qwencore_b200 import abi, engine as engine_module
+    from step_oracle import HostModel, decode_step
+    from test_gpu_step import host_layout
+
+    before = abi.get_shape()
+    contexts = synth.log_uniform_contexts(0, ROWS, 128, 32768)
+    steps = 2
+    blocks = int(np.sum((contexts + steps + PAGE - 1) // PAGE)) + 8
+    config = engine_module.default_config(num_layers=LAYERS, max_batch=ROWS, max_context=32768 + 64,
+                                          kv_pool_blocks=blocks, state_slots=ROWS + 1, seed=11)
+    assert config.vocab == 151936 and config.hidden == 5120 and config.intermediate == 17408
+    engine = engine_module.Engine(config)
+    try:
+        engine.trace_layers(True)
+        cache = engine_module.CacheManager(config.state_slots, config.kv_pool_blocks, PAGE)
+        ids = []
+        for i, context in enumerate(contexts):
+            cache.admit(100 + i, int(context))
+            ids.append(100 + i)
+        engine.apply_edits(cache.drain_edits())
+        model = HostModel(engine)
+        rng = np.random.default_rng(3)
+        order = [ids[i] for i in rng.permutation(ROWS)]  # batch order differs from slot order
+        tokens = rng.integers(0, config.vocab, ROWS).astype(np.uint32)
+        report = []
+        for step in range(steps):  # step 0 runs eagerly, step 1 replays the captured graph
+            for seq in order:
+                cache.append_token(seq)
+            edits = cache.drain_edits()
+            layout = host_layout(cache, order, PAGE, config.state_slots, model.max_blocks)
+            assert layout["status"] == 0
+            sampled = engine.decode(layout["state_slots"], tokens, edits)
+            want_trace = []
+            want_logits, want_tokens, _ = decode_step(model, layout, tokens, trace=want_trace)
+            got_trace = engine.read("trace", 0, np.uint16).reshape(LAYERS, 2, ROWS, config.hidden)
+
+            # per layer: the mixer's output projection and the residual stream after the MLP.  A bf16
+            # output cannot sit closer to the oracle than its own grid (2^-8 relative), and from the
+            # second layer on every input carries the previous layers' grid-level differences: the
+            # bound is on the RMS of the error, the worst element is reported and held to 10 %.
+            for layer in range(LAYERS):
+                for which, name in ((0, "mixer_out"), (1, "residual")):
+                    worst, rms_error = relative_errors(got_trace[layer, which], want_trace[layer][which])
+                    report.append(f"step {step} layer {layer} {name}: max|err|/rms {worst:.4f}, rms err/rms "
+                                  f"{rms_error:.5f}")
+                    assert rms_error <= 2e-2, report[-1]
+                    assert worst <= 1e-1, report[-1]
+
+            got_logits = engine.read("logits", 0, np.float32).reshape(ROWS, config.vocab)
+            assert np.isfinite(got_logits).all()
+            rms = np.sqrt(np.mean(want_logits.astype(np.float64) ** 2))
+            worst = np.max(np.abs(got_logits - want_logits))
+            rms_error = np.sqrt(np.mean((got_logits - want_logits).astype(np.float64) ** 2))
+            assert rms_error <= 2e-2 * rms, f"step {step}: logits rms err {rms_error} vs rms {rms}"
+            assert worst <= 1e-1 * rms, f"step {step}: logits err {worst} vs rms {rms}"
+            # greedy tokens: every one of the 32 rows is compared.  The argmax itself is exact on the
+            # GPU's logits; it equals the oracle's token wherever the oracle's top-2 gap exceeds what
+            # the logits may differ by, and the number of such rows is reported.
+            assert np.array_equal(sampled, oracle.argmax(got_logits, config.vocab, ROWS))
+            ordered = np.sort(want_logits, axis=1)
+            gap = ordered[:, -1] - ordered[:, -2]
+            clear = gap > 4 * worst
+            agree = sampled == want_tokens
+            report.append(f"step {step} logits: max|err|/rms {worst / rms:.4f}, rms err/rms {rms_error / rms:.5f}; "
+                          f"tokens equal on {int(agree.sum())} of {ROWS} rows, {int(clear.sum())} rows with a clear "
+                          f"top-2 gap")
+            assert np.array_equal(sampled[clear], want_tokens[clear]), report[-1]
+            assert clear.sum() >= ROWS // 4, "the inputs must exercise the token comparison: " + report[-1]
+            tokens = want_tokens.copy()
+        assert abi.lib.qwc_device_status() == 0
+        with capsys.disabled():
+            print("\n" + "\n".join(report))
+    finally:
+        engine.close()
+        abi.configure(*before)

@@ -363,3 +363,21 @@ def test_host_layout_agrees_with_the_oracle_statement(built_library):
     assert want["context_lengths"].tolist() == layout["context_lens"]
     assert want["block_table_offsets"].tolist() == layout["block_table_offsets"]
     assert want["block_ids"].tolist() == layout["block_ids"]
+
+
+def test_a_drain_carries_one_edit_per_table_word(built_library):
+    """The device applies a drain with one thread per edit and no order among them, so the host
+    keeps only the last edit of a word: a slot that is released and admitted again within one drain
+    (the state pool hands the newest free slot out first) sends one token count, not two."""
+    m = CacheManager(2, 8, 16)
+    m.admit(1, 20)
+    m.drain_edits()
+    m.release(1)
+    m.admit(2, 40)  # takes the slot that was just released
+    edits = m.drain_edits().tolist()
+    words = [(slot, kind, index if kind == 0 else 0) for slot, index, _, kind in edits]
+    assert len(words) == len(set(words))
+    assert [0, 0, 40, 1] in edits and [0, 0, 0, 1] not in edits
+    m.append_token(2)
+    m.rollback_token(2)
+    assert m.drain_edits().tolist() == [[0, 0, 40, 1]]
