@@ -102,6 +102,46 @@ int qwc_nvfp4_swiglu_w4a16(const void* gate_packed, const void* gate_scales, con
 int qwc_nvfp4_prefetch_next(const void* packed0, const void* scales0, const void* packed1,
                             const void* scales1, int out_features, int in_features, int kind);
 
+/*
+ * Additive (no reference counterpart): the same projections on STAGED activations, for a caller
+ * that chains them (the decode executor).  "Staged" is f16 in the layout the tensor core reads its
+ * B operand in: [features / 8][rows padded to 16 (batch <= 16) or 32][8], so that a 128-element
+ * chunk of every row is one contiguous block (qwc_staged_activation_bytes gives the size;
+ * qwc_stage_activations converts bf16 rows; values are the bf16 values, |x| > 65504 saturates).
+ * The kernels that produce activations can store this layout directly (the `_staged` variants of
+ * the RMSNorm, gated RMSNorm and attention entry points below, and `staged_output` here), so no
+ * projection converts its input.  The work of a launch is cut into equal shares for every SM; tiles
+ * whose K range is split between CTAs are summed through `workspace` (qwc_streamk_workspace_bytes()
+ * bytes of device memory, 16-byte aligned, cleared once with qwc_streamk_workspace_init and then
+ * left to the library; launches that overlap on the device must not share one).  Sums are taken in
+ * a fixed order: results are bit-reproducible.  `output` (bf16 [batch][out]) and `staged_output`
+ * (the same values staged for a following projection) may each be NULL, not both.
+ * out_features % 8 == 0, in_features % 256 == 0, batch 1..32, all pointers 16-byte aligned.
+ * A launch in which a bounded wait gave up (qwc_device_status) leaves the workspace dirty: clear it
+ * again before the next use.  qwc_nvfp4_prefetch_next applies to these calls as well.
+ */
+size_t qwc_streamk_workspace_bytes(void);
+int qwc_streamk_workspace_init(void* workspace, qwc_stream stream);
+size_t qwc_staged_activation_bytes(int batch, int features);
+int qwc_stage_activations(const void* input, void* staged, int batch, int in_features, qwc_stream stream);
+int qwc_nvfp4_w4a16_staged(const void* packed, const void* scales, const void* staged_input, void* output,
+                           void* staged_output, int out_features, int in_features, int batch,
+                           float weight_global_scale, void* workspace, qwc_stream stream);
+int qwc_nvfp4_swiglu_w4a16_staged(const void* gate_packed, const void* gate_scales, const void* up_packed,
+                                  const void* up_scales, const void* staged_input, void* output,
+                                  void* staged_output, int out_features, int in_features, int batch,
+                                  float gate_global_scale, float up_global_scale, void* workspace,
+                                  qwc_stream stream);
+/*
+ * The FP8 vocabulary head (see qwc_fp8_lm_head_batched) on staged activations, with greedy sampling
+ * folded in: `logits` (f32 [batch][vocab]) may be NULL when only the tokens are wanted, `sampled`
+ * (u32 [batch], argmax with ties to the smaller index, cuda/sampling.cu:11-14) may be NULL when only
+ * the logits are.  With `sampled`, `status_out` (u32, may be NULL) receives the device status word.
+ */
+int qwc_fp8_lm_head_staged(const void* weights, const void* row_scales, const void* staged_input, void* logits,
+                           void* sampled, void* status_out, int batch, int hidden_size, int vocab,
+                           void* workspace, qwc_stream stream);
+
 /* ------------------------------------------------------------------ */
 /* Packed paged FP8 attention                                           */
 /* ------------------------------------------------------------------ */

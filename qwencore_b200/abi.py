@@ -47,6 +47,13 @@ KERNEL_SYMBOLS = {
     "qwc_nvfp4_w4a16": (c_int, [P, P, P, P, c_int, c_int, c_int, c_float, P]),
     "qwc_nvfp4_swiglu_w4a16": (c_int, [P, P, P, P, P, P, c_int, c_int, c_int, c_float, c_float, P]),
     "qwc_nvfp4_prefetch_next": (c_int, [P, P, P, P, c_int, c_int, c_int]),
+    "qwc_streamk_workspace_bytes": (c_size_t, []),
+    "qwc_streamk_workspace_init": (c_int, [P, P]),
+    "qwc_staged_activation_bytes": (c_size_t, [c_int, c_int]),
+    "qwc_stage_activations": (c_int, [P, P, c_int, c_int, P]),
+    "qwc_nvfp4_w4a16_staged": (c_int, [P, P, P, P, P, c_int, c_int, c_int, c_float, P, P]),
+    "qwc_nvfp4_swiglu_w4a16_staged": (c_int, [P, P, P, P, P, P, P, c_int, c_int, c_int, c_float, c_float, P, P]),
+    "qwc_fp8_lm_head_staged": (c_int, [P, P, P, P, P, P, c_int, c_int, c_int, P, P]),
     "qwc_paged_attention_packed_fp8": (c_int, [P, P, P, P, P, P, P, P, c_size_t, c_int, c_int, c_int, c_int,
                                                c_int, c_float, P]),
     "qwc_paged_attention_packed_fp8_scaled": (c_int, [P, P, P, P, P, P, P, P, P, P, c_size_t, c_int, c_int,

@@ -44,9 +44,8 @@
 // its stores, frees its TMEM and returns.
 
 #include <cooperative_groups.h>
-#include <cuda.h>
 
-#include "common.cuh"
+#include "tcgen05.cuh"
 
 namespace cg = cooperative_groups;
 
@@ -160,87 +159,6 @@ __device__ __forceinline__ bool wait_or_fail(uint64_t* bar, uint32_t parity, Bar
         return true;
     }
     return wait_or_fail_slow(bar, parity, b, status);
-}
-
-// True in exactly one lane of a converged warp.  The compiler keeps the operands of what that lane
-// issues in uniform registers; `lane == 0` instead costs a register move per operand per instruction.
-__device__ __forceinline__ bool elect_one() {
-    uint32_t elected;
-    asm volatile("{\n.reg .pred p;\nelect.sync _|p, 0xffffffff;\nselp.u32 %0, 1, 0, p;\n}\n" : "=r"(elected));
-    return elected != 0;
-}
-
-__device__ __forceinline__ uint64_t smem_descriptor(uint32_t address, uint32_t leading_bytes, uint32_t stride_bytes) {
-    // K-major, no swizzle: start address, leading (K) and stride (N) byte offsets in 16-byte units, version 1.
-    const uint64_t lo = ((address >> 4) & 0x3FFFu) | (static_cast<uint64_t>((leading_bytes >> 4) & 0x3FFFu) << 16);
-    const uint64_t hi = ((stride_bytes >> 4) & 0x3FFFu) | (1u << 14);
-    return lo | (hi << 32);
-}
-
-__device__ __forceinline__ void umma_f16(uint32_t d_tmem, uint32_t a_tmem, uint64_t b_desc, uint32_t idesc,
-                                         uint32_t accumulate) {
-    asm volatile(
-        "{\n"
-        ".reg .pred p;\n"
-        "setp.ne.b32 p, %4, 0;\n"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n"
-        "}\n" ::"r"(d_tmem),
-        "r"(a_tmem), "l"(b_desc), "r"(idesc), "r"(accumulate)
-        : "memory");
-}
-
-__device__ __forceinline__ void umma_commit(uint64_t* bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
-                 : "memory");
-}
-
-__device__ __forceinline__ void tma_box_g2s(void* smem_dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
-    asm volatile(
-        "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(
-            smem_u32(smem_dst)),
-        "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(smem_u32(bar))
-        : "memory");
-}
-
-// The same box, but only brought into L2 (no shared-memory destination, nothing to wait for).
-__device__ __forceinline__ void tma_box_prefetch_l2(const CUtensorMap* map, int x, int y) {
-    asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global.tile [%0, {%1, %2}];" ::"l"(
-                     reinterpret_cast<uint64_t>(map)),
-                 "r"(x), "r"(y)
-                 : "memory");
-}
-
-// Contiguous bytes into L2; address 16-byte aligned, size a multiple of 16.
-__device__ __forceinline__ void bulk_prefetch_l2(const void* global, uint32_t bytes) {
-    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(global), "r"(bytes) : "memory");
-}
-
-__device__ __forceinline__ void tmem_store16(uint32_t taddr, const uint32_t (&r)[16]) {
-    asm volatile(
-        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};" ::"r"(
-            taddr),
-        "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
-        "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
-        : "memory");
-}
-
-__device__ __forceinline__ void tmem_load32(uint32_t taddr, float (&v)[32]) {
-    uint32_t r[32];
-    asm volatile(
-        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,"
-        "%29,%30,%31}, [%32];"
-        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
-          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
-          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-        : "r"(taddr)
-        : "memory");
-    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#pragma unroll
-    for (int i = 0; i < 32; ++i) {
-        v[i] = __uint_as_float(r[i]);
-    }
 }
 
 // The mode (vocabulary head, SwiGLU pair), the padded batch and whether K is split are template parameters: every
@@ -805,41 +723,6 @@ __global__ void __launch_bounds__(kThreads, 1)
     if (warp == kMmaWarp) {
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(kTmemColumns) : "memory");
     }
-}
-
-using EncodeTiled = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                 const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                 CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-// The driver's tensor-map encoder, looked up through the runtime so that libcuda is not a link dependency.
-EncodeTiled tensor_map_encoder() {
-    static const EncodeTiled encoder = []() -> EncodeTiled {
-        void* entry = nullptr;
-        cudaDriverEntryPointQueryResult found = cudaDriverEntryPointSymbolNotFound;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &entry, cudaEnableDefault, &found) != cudaSuccess ||
-            found != cudaDriverEntryPointSuccess) {
-            return nullptr;
-        }
-        return reinterpret_cast<EncodeTiled>(entry);
-    }();
-    return encoder;
-}
-
-// Weight bytes as a [rows][row_bytes] matrix, fetched in boxes of 128 rows x 128 bytes.
-cudaError_t encode_weight_map(CUtensorMap* map, const void* packed, int out_features, int row_bytes) {
-    const EncodeTiled encode = tensor_map_encoder();
-    if (encode == nullptr) {
-        return cudaErrorNotSupported;
-    }
-    const cuuint64_t dims[2] = {static_cast<cuuint64_t>(row_bytes), static_cast<cuuint64_t>(out_features)};
-    const cuuint64_t strides[1] = {static_cast<cuuint64_t>(row_bytes)};
-    const cuuint32_t box[2] = {kBoxRowBytes, kTileRows};
-    const cuuint32_t element_strides[2] = {1, 1};
-    const CUresult result =
-        encode(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(packed), dims, strides, box, element_strides,
-               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    return result == CUDA_SUCCESS ? cudaSuccess : cudaErrorInvalidValue;
 }
 
 int sm_count_umma() {

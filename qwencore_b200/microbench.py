@@ -84,7 +84,7 @@ def report(label: str, microseconds: float, nbytes: int) -> dict:
 
 
 def projection(out_features: int, in_features: int, rows: int, swiglu: bool = False, plain: int = 0,
-               hint: bool = False) -> dict:
+               hint: bool = False, staged: bool = False) -> dict:
     matrix_bytes = out_features * in_features // 2 + ops.block_scale_storage_len(out_features, in_features)
     per_launch = matrix_bytes * (2 if swiglu else 1)
     copies = max(2, -(-2 * L2_BYTES // per_launch)) if not plain else 2
@@ -100,6 +100,10 @@ def projection(out_features: int, in_features: int, rows: int, swiglu: bool = Fa
     x = _dev(synth.normal_bf16(0, "x", (rows, in_features)))
     y = torch.zeros((rows, out_features), dtype=torch.uint16, device="cuda")
     counter = [0]
+    if staged:  # the equal-share kernel: activations already in the tensor core's operand layout
+        staged_x = ops.new_staged(rows, in_features)
+        ops.stage_activations(x, staged_x, rows, in_features)
+        workspace = ops.new_streamk_workspace()
 
     def launch():
         index = counter[0] % copies
@@ -111,7 +115,11 @@ def projection(out_features: int, in_features: int, rows: int, swiglu: bool = Fa
                 ops.prefetch_next(linears[2 * after], linears[2 * after + 1])
             else:
                 ops.prefetch_next(linears[after])
-        if swiglu:
+        if staged and swiglu:
+            ops.swiglu_w4a16_staged(linears[2 * index], linears[2 * index + 1], staged_x, y, None, rows, workspace)
+        elif staged:
+            ops.w4a16_staged(linears[index], staged_x, y, None, rows, workspace)
+        elif swiglu:
             ops.swiglu_w4a16(linears[2 * index], linears[2 * index + 1], x, y, rows)
         else:
             linears[index].forward_w4a16(x, y, rows)
@@ -119,7 +127,7 @@ def projection(out_features: int, in_features: int, rows: int, swiglu: bool = Fa
     microseconds = time_launches(launch, 4 * copies, plain)
     nbytes = (out_features * in_features // 2 + out_features * in_features // 16) * (2 if swiglu else 1)
     nbytes += rows * in_features * 2 + rows * out_features * 2
-    name = ("swiglu" if swiglu else "gemv") + (" +hint" if hint else "")
+    name = ("swiglu" if swiglu else "gemv") + (" staged" if staged else "") + (" +hint" if hint else "")
     return report(f"{name} N={out_features} K={in_features} M={rows}", microseconds, nbytes)
 
 
@@ -194,8 +202,9 @@ def contexts_for(kind: str, rows: int, low: int, high: int):
     raise SystemExit(f"unknown context distribution {kind}")
 
 
-def lm_head(vocab: int, hidden: int, rows: int, plain: int = 0) -> dict:
-    """The FP8 vocabulary head: e4m3 weight bytes, one fp32 scale per row, fp32 logits."""
+def lm_head(vocab: int, hidden: int, rows: int, plain: int = 0, staged: bool = False) -> dict:
+    """The FP8 vocabulary head: e4m3 weight bytes, one fp32 scale per row, fp32 logits (staged: the
+    equal-share kernel with greedy sampling folded in, no logits written)."""
     generator = torch.Generator(device="cuda")
     generator.manual_seed(0)
     copies = max(2, -(-2 * L2_BYTES // (vocab * hidden))) if not plain else 2
@@ -205,26 +214,36 @@ def lm_head(vocab: int, hidden: int, rows: int, plain: int = 0) -> dict:
     x = _dev(synth.normal_bf16(0, "x", (rows, hidden)))
     logits = torch.zeros((rows, vocab), dtype=torch.float32, device="cuda")
     counter = [0]
+    if staged:
+        staged_x = ops.new_staged(rows, hidden)
+        ops.stage_activations(x, staged_x, rows, hidden)
+        workspace = ops.new_streamk_workspace()
+        tokens = torch.zeros(rows, dtype=torch.int32, device="cuda")
 
     def launch():
         index = counter[0] % copies
         counter[0] += 1
-        ops.fp8_lm_head(tables[index], scales, x, logits, rows, hidden, vocab)
+        if staged:
+            ops.fp8_lm_head_staged(tables[index], scales, staged_x, None, tokens, None, rows, hidden, vocab, workspace)
+        else:
+            ops.fp8_lm_head(tables[index], scales, x, logits, rows, hidden, vocab)
 
     microseconds = time_launches(launch, 4 * copies, plain)
-    nbytes = vocab * hidden + vocab * 4 + rows * hidden * 2 + rows * vocab * 4
-    return report(f"lm_head V={vocab} K={hidden} M={rows}", microseconds, nbytes)
+    nbytes = vocab * hidden + vocab * 4 + rows * hidden * 2 + (0 if staged else rows * vocab * 4)
+    return report(f"lm_head{' staged+sample' if staged else ''} V={vocab} K={hidden} M={rows}", microseconds, nbytes)
 
 
 def main(argv=None) -> None:
     parser = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
-    parser.add_argument("kernel", choices=["gemv", "swiglu", "lm_head", "delta", "attention", "all"])
+    parser.add_argument("kernel", choices=["gemv", "swiglu", "lm_head", "delta", "attention", "projections", "all"])
     parser.add_argument("args", nargs="*")
     parser.add_argument("--partitions", type=int, default=0)
     parser.add_argument("--page", type=int, default=16)
     parser.add_argument("--hint", action="store_true",
                         help="name the next launch's weights to each projection (qwc_nvfp4_prefetch_next)")
     parser.add_argument("--plain", type=int, default=0, help="issue this many eager launches and exit (for a profiler)")
+    parser.add_argument("--staged", action="store_true",
+                        help="projections and the head through the equal-share kernel on staged activations")
     options = parser.parse_args(argv)
     if not torch.cuda.is_available():
         raise SystemExit("a CUDA device is required")
@@ -232,9 +251,20 @@ def main(argv=None) -> None:
     values = options.args
     if options.kernel in ("gemv", "swiglu"):
         n, k, m = (int(v) for v in values[:3])
-        projection(n, k, m, swiglu=options.kernel == "swiglu", plain=options.plain, hint=options.hint)
+        projection(n, k, m, swiglu=options.kernel == "swiglu", plain=options.plain, hint=options.hint,
+                   staged=options.staged)
     elif options.kernel == "lm_head":
-        lm_head(int(values[0]), int(values[1]), int(values[2]), plain=options.plain)
+        lm_head(int(values[0]), int(values[1]), int(values[2]), plain=options.plain, staged=options.staged)
+    elif options.kernel == "projections":
+        for rows in (1, 8, 32):
+            projection(34816, 5120, rows, staged=options.staged, hint=options.hint)
+            projection(17408, 5120, rows, swiglu=True, staged=options.staged, hint=options.hint)
+            projection(5120, 17408, rows, staged=options.staged, hint=options.hint)
+            projection(12352, 5120, rows, staged=options.staged, hint=options.hint)
+            projection(5120, 4096, rows, staged=options.staged, hint=options.hint)
+            projection(14336, 5120, rows, staged=options.staged, hint=options.hint)
+            projection(5120, 6144, rows, staged=options.staged, hint=options.hint)
+            lm_head(151936, 5120, rows, staged=options.staged)
     elif options.kernel == "delta":
         delta(int(values[0]), int(values[1]), plain=options.plain)
     elif options.kernel == "attention":

