@@ -90,7 +90,8 @@ int qwc_nvfp4_swiglu_w4a16(const void* gate_packed, const void* gate_scales, con
  * qwc_fp8_lm_head* call it makes: that launch then asks L2 for the first stages of the named
  * matrix once its own last bytes are on their way, so HBM keeps streaming across the kernel
  * boundary.  kind: 0 = NVFP4 matrix (packed0, scales0), 1 = SwiGLU pair (packed0/scales0 = gate,
- * packed1/scales1 = up), 2 = e4m3 rows of the vocabulary head (packed0 = table; no scales).
+ * packed1/scales1 = up), 2 = e4m3 rows of the vocabulary head (packed0 = table; no scales),
+ * 3 = an NVFP4 matrix that will run through qwc_nvfp4_w4a16_split.
  * Pure hint: host-side only (no launch, no sync, capture-legal), good for one launch of this
  * thread, ignored when that launch does not take the tcgen05 path; wrong or stale hints cost
  * bandwidth, never correctness (prefetches do not fault on valid device memory and write nothing).
@@ -133,6 +134,38 @@ int qwc_nvfp4_swiglu_w4a16_staged(const void* gate_packed, const void* gate_scal
                                   float gate_global_scale, float up_global_scale, void* workspace,
                                   qwc_stream stream);
 /*
+ * Additive: a projection whose output feeds a residual RMSNorm and has too few rows for the SMs
+ * (5120 outputs = 20 tile pairs on 148 SMs) runs as a regular K split and leaves the sum to the norm:
+ * qwc_nvfp4_w4a16_split stores fp32 partial rows [qwc_nvfp4_split_count(out, in)][batch][out]
+ * (unscaled: the global scale is applied after the sum) and ends with plain stores, no reduction
+ * between CTAs; qwc_rmsnorm_bf16_split_staged sums the slices in slice order (bit-reproducible),
+ * rounds the sum / weight_global_scale to bf16 as the projection would have (and stores those rows
+ * in `projection_output`, bf16 [batch][hidden], when it is not NULL), and continues as
+ * qwc_rmsnorm_bf16_staged on those values.  hidden <= 10240.
+ */
+int qwc_nvfp4_split_count(int out_features, int in_features);
+int qwc_nvfp4_w4a16_split(const void* packed, const void* scales, const void* staged_input, float* partial_sums,
+                          int out_features, int in_features, int batch, qwc_stream stream);
+int qwc_rmsnorm_bf16_split_staged(const float* partial_sums, int splits, float weight_global_scale,
+                                  void* projection_output, void* residual, const void* weight, void* output,
+                                  void* staged_output, int batch, int hidden, float epsilon, qwc_stream stream);
+
+/* Consumers of a K-split projection other than the residual norm: the DeltaNet prepare step and the
+ * gated RMSNorm on a split mixer in-projection (same arithmetic as qwc_delta_prepare_decode and
+ * qwc_delta_gated_rmsnorm_staged; a, b and the gate z are columns a_column, b_column, gate_column of
+ * the in-projection's rows of `width` outputs), and the plain sum to bf16 rows [batch][width]. */
+int qwc_delta_prepare_decode_split(const float* partial_sums, int slices, int width, float weight_global_scale,
+                                   int a_column, int b_column, const void* conv_weight, const void* a_log,
+                                   const void* dt_bias, void* conv_state, const void* state_slots, void* query,
+                                   void* key, void* value, void* alpha, void* beta, void* kq, int state_capacity,
+                                   int batch, qwc_stream stream);
+int qwc_delta_gated_rmsnorm_split(const float* input, const float* partial_sums, int slices, int width,
+                                  float weight_global_scale, int gate_column, const void* weight, void* output,
+                                  void* staged_output, int batch, float epsilon, qwc_stream stream);
+int qwc_nvfp4_sum_slices(const float* partial_sums, int slices, float weight_global_scale, void* rows, int batch,
+                         int width, qwc_stream stream);
+
+/*
  * The FP8 vocabulary head (see qwc_fp8_lm_head_batched) on staged activations, with greedy sampling
  * folded in: `logits` (f32 [batch][vocab]) may be NULL when only the tokens are wanted, `sampled`
  * (u32 [batch], argmax with ties to the smaller index, cuda/sampling.cu:11-14) may be NULL when only
@@ -141,6 +174,25 @@ int qwc_nvfp4_swiglu_w4a16_staged(const void* gate_packed, const void* gate_scal
 int qwc_fp8_lm_head_staged(const void* weights, const void* row_scales, const void* staged_input, void* logits,
                            void* sampled, void* status_out, int batch, int hidden_size, int vocab,
                            void* workspace, qwc_stream stream);
+
+/*
+ * Additive: the producers of activations with a staged output beside (or instead of) their bf16
+ * rows.  Same arguments and arithmetic as qwc_rmsnorm_bf16, qwc_delta_gated_rmsnorm and
+ * qwc_paged_attention_packed_fp8_scaled below; `output` and `staged_output` may each be NULL, not
+ * both; with a staged output the batch (row_base + rows for attention) is at most 32.
+ */
+int qwc_rmsnorm_bf16_staged(const void* input, void* residual, const void* weight, void* output,
+                            void* staged_output, int batch, int hidden, float epsilon, qwc_stream stream);
+int qwc_delta_gated_rmsnorm_staged(const float* input, const void* gate, const void* weight, void* output,
+                                   void* staged_output, int batch, float epsilon, int gate_stride,
+                                   qwc_stream stream);
+int qwc_paged_attention_packed_fp8_staged(const void* query, const void* query_gate_projection,
+                                          const void* key_cache, const void* value_cache,
+                                          const void* block_tables, const void* context_lengths,
+                                          const float* key_scales, const float* value_scales, void* output,
+                                          void* staged_output, void* workspace, size_t workspace_bytes, int rows,
+                                          int row_base, int max_blocks, int page_size, int gate_stride,
+                                          int partitions, float softmax_scale, qwc_stream stream);
 
 /* ------------------------------------------------------------------ */
 /* Packed paged FP8 attention                                           */

@@ -127,6 +127,7 @@ typedef struct qwc_engine_config {
     int split_size;              /* ... of this many; 1 = off.  Needs max_batch == 1. */
     int use_graph;               /* 1: replay a captured graph per batch size (default path) */
     int attention_partitions;    /* 0 = choose from max_batch and max_context */
+    int write_logits;            /* 1: the vocabulary head also stores fp32 logits (tensor "logits"); 0: tokens only */
 } qwc_engine_config;
 
 /* Fills `config` with the synthetic 27B-shaped model of the benchmark. */

@@ -54,6 +54,16 @@ KERNEL_SYMBOLS = {
     "qwc_nvfp4_w4a16_staged": (c_int, [P, P, P, P, P, c_int, c_int, c_int, c_float, P, P]),
     "qwc_nvfp4_swiglu_w4a16_staged": (c_int, [P, P, P, P, P, P, P, c_int, c_int, c_int, c_float, c_float, P, P]),
     "qwc_fp8_lm_head_staged": (c_int, [P, P, P, P, P, P, c_int, c_int, c_int, P, P]),
+    "qwc_rmsnorm_bf16_staged": (c_int, [P, P, P, P, P, c_int, c_int, c_float, P]),
+    "qwc_nvfp4_split_count": (c_int, [c_int, c_int]),
+    "qwc_delta_prepare_decode_split": (c_int, [P, c_int, c_int, c_float, c_int, c_int] + [P] * 11 + [c_int, c_int, P]),
+    "qwc_delta_gated_rmsnorm_split": (c_int, [P, P, c_int, c_int, c_float, c_int, P, P, P, c_int, c_float, P]),
+    "qwc_nvfp4_sum_slices": (c_int, [P, c_int, c_float, P, c_int, c_int, P]),
+    "qwc_nvfp4_w4a16_split": (c_int, [P, P, P, P, c_int, c_int, c_int, P]),
+    "qwc_rmsnorm_bf16_split_staged": (c_int, [P, c_int, c_float, P, P, P, P, P, c_int, c_int, c_float, P]),
+    "qwc_delta_gated_rmsnorm_staged": (c_int, [P, P, P, P, P, c_int, c_float, c_int, P]),
+    "qwc_paged_attention_packed_fp8_staged": (c_int, [P, P, P, P, P, P, P, P, P, P, P, c_size_t, c_int, c_int,
+                                                      c_int, c_int, c_int, c_int, c_float, P]),
     "qwc_paged_attention_packed_fp8": (c_int, [P, P, P, P, P, P, P, P, c_size_t, c_int, c_int, c_int, c_int,
                                                c_int, c_float, P]),
     "qwc_paged_attention_packed_fp8_scaled": (c_int, [P, P, P, P, P, P, P, P, P, P, c_size_t, c_int, c_int,

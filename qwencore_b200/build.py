@@ -20,7 +20,11 @@ CSRC = PACKAGE_DIR / "csrc"
 BUILD_DIR = PACKAGE_DIR / "_build"
 LIBRARY = PACKAGE_DIR / "libqwc_b200.so"
 
+# QWC_NVCC_DEFINES="-DQWC_STREAMK_TRACE" builds the projection kernel with its CTA timeline
+EXTRA_DEFINES = os.environ.get("QWC_NVCC_DEFINES", "").split()
+
 NVCC_FLAGS = [
+    *EXTRA_DEFINES,
     "-gencode",
     "arch=compute_100a,code=sm_100a",
     "-std=c++17",

@@ -200,6 +200,12 @@ struct qwc_engine {
     __nv_bfloat16 *residual = nullptr, *normed = nullptr, *mixer_in = nullptr, *qkv_buf = nullptr, *query = nullptr;
     __nv_bfloat16 *attention_out = nullptr, *delta_normed = nullptr, *mixer_out = nullptr, *mlp_hidden = nullptr;
     __nv_bfloat16* mlp_out = nullptr;
+    // activations staged for the projection that reads them (f16, tensor-core operand layout)
+    void *normed_staged = nullptr, *delta_normed_staged = nullptr, *attention_out_staged = nullptr;
+    void* mlp_hidden_staged = nullptr;
+    void* streamk_workspace = nullptr;
+    float* split_sums = nullptr;  // fp32 partial rows of a K-split projection: [slice][batch][hidden]
+    float* split_sums_wide = nullptr;  // ... of the mixer in-projection or q|k|v: [slice][batch][width]
     float *dq = nullptr, *dk = nullptr, *dv = nullptr, *dalpha = nullptr, *dbeta = nullptr, *dkq = nullptr;
     float *delta_out = nullptr, *logits = nullptr, *argmax_values = nullptr;
     uint32_t* argmax_indices = nullptr;
@@ -337,6 +343,13 @@ void hint_next(const qwc_engine* e, const LinearW& next) {
     }
 }
 
+// ... a projection that will run as a regular K split (its CTAs start elsewhere in the matrix)
+void hint_next_split(const qwc_engine* e, const LinearW& next) {
+    if (e->cfg.split_size == 1) {
+        (void)qwc_nvfp4_prefetch_next(next.packed, next.scales, nullptr, nullptr, next.out_features, next.in_features, 3);
+    }
+}
+
 void hint_next_pair(const qwc_engine* e, const LinearW& gate, const LinearW& up) {
     if (e->cfg.split_size == 1) {
         (void)qwc_nvfp4_prefetch_next(gate.packed, gate.scales, up.packed, up.scales, gate.out_features,
@@ -360,6 +373,25 @@ int project(qwc_engine* e, const LinearW& w, const __nv_bfloat16* input, __nv_bf
     return 0;
 }
 
+// A projection to the hidden width (mixer output, MLP down) followed by the residual RMSNorm: too few
+// row tiles for the SMs, so it runs as a regular K split whose slices the norm sums (one GPU only).
+int project_and_norm(qwc_engine* e, const LinearW& w, const void* staged_input, __nv_bfloat16* projection_rows,
+                     const __nv_bfloat16* norm_weight, int batch, const char* gemm_label) {
+    const qwc_engine_config& c = e->cfg;
+    if (phase(e, gemm_label)) {
+        QWC_TRY(qwc_nvfp4_w4a16_split(w.packed, w.scales, staged_input, e->split_sums, w.out_features, w.in_features,
+                                      batch, e->stream));
+    }
+    if (phase(e, "norm")) {
+        // the projection's own bf16 rows reach memory only for a caller that traces the layers
+        QWC_TRY(qwc_rmsnorm_bf16_split_staged(e->split_sums, qwc_nvfp4_split_count(w.out_features, w.in_features),
+                                              w.global_scale, e->trace != nullptr ? projection_rows : nullptr,
+                                              e->residual, norm_weight, nullptr, e->normed_staged, batch, c.hidden,
+                                              kEps, e->stream));
+    }
+    return 0;
+}
+
 int decode_forward(qwc_engine* e, int batch) {
     const qwc_engine_config& c = e->cfg;
     cudaStream_t s = e->stream;
@@ -378,18 +410,31 @@ int decode_forward(qwc_engine* e, int batch) {
     if (phase(e, "embed")) {
         QWC_TRY(qwc_fp8_embedding_gather(e->embed, e->embed_scales, tokens, e->residual, batch, c.hidden, c.vocab, s));
     }
+    const bool staged = c.split_size == 1;  // one GPU: every projection reads staged activations
     if (phase(e, "norm")) {
-        QWC_TRY(qwc_rmsnorm_bf16(e->residual, nullptr, e->layers[0].input_norm, e->normed, batch, c.hidden, kEps, s));
+        QWC_TRY(qwc_rmsnorm_bf16_staged(e->residual, nullptr, e->layers[0].input_norm, staged ? nullptr : e->normed,
+                                        staged ? e->normed_staged : nullptr, batch, c.hidden, kEps, s));
     }
 
     for (size_t index = 0; index < e->layers.size(); ++index) {
         const Layer& layer = e->layers[index];
         if (!layer.full) {
+            const int in_slices = qwc_nvfp4_split_count(layer.in_proj.out_features, layer.in_proj.in_features);
             if (phase(e, "gemm.la_in")) {
-                hint_next(e, layer.la_out);
-                QWC_TRY(project(e, layer.in_proj, e->normed, e->mixer_in, batch));
+                hint_next_split(e, layer.la_out);
+                // one GPU: a regular K split whose slices the prepare step and the gated norm sum
+                QWC_TRY(staged ? qwc_nvfp4_w4a16_split(layer.in_proj.packed, layer.in_proj.scales, e->normed_staged,
+                                                       e->split_sums_wide, layer.in_proj.out_features,
+                                                       layer.in_proj.in_features, batch, s)
+                               : project(e, layer.in_proj, e->normed, e->mixer_in, batch));
             }
-            if (phase(e, "delta.prepare")) {
+            if (staged && phase(e, "delta.prepare")) {
+                QWC_TRY(qwc_delta_prepare_decode_split(e->split_sums_wide, in_slices, e->mixer_width,
+                                                       layer.in_proj.global_scale, e->a_offset, e->b_offset,
+                                                       layer.conv_weight, layer.a_log, layer.dt_bias, layer.conv_state,
+                                                       e->state_slots, e->dq, e->dk, e->dv, e->dalpha, e->dbeta,
+                                                       e->dkq, c.state_slots, batch, s));
+            } else if (phase(e, "delta.prepare")) {
                 QWC_TRY(qwc_delta_prepare_decode(e->mixer_in, e->mixer_in + e->a_offset, e->mixer_in + e->b_offset,
                                                  layer.conv_weight, layer.a_log, layer.dt_bias, layer.conv_state,
                                                  e->state_slots, e->dq, e->dk, e->dv, e->dalpha, e->dbeta, e->dkq,
@@ -399,16 +444,29 @@ int decode_forward(qwc_engine* e, int batch) {
                 QWC_TRY(qwc_delta_decode_int8(layer.state, layer.state_scales, e->state_slots, e->dq, e->dk, e->dv,
                                               e->dalpha, e->dbeta, e->dkq, e->delta_out, c.state_slots, batch, s));
             }
-            if (phase(e, "delta.norm")) {
+            if (staged && phase(e, "delta.norm")) {
+                QWC_TRY(qwc_delta_gated_rmsnorm_split(e->delta_out, e->split_sums_wide, in_slices, e->mixer_width,
+                                                      layer.in_proj.global_scale, e->z_offset, layer.out_norm, nullptr,
+                                                      e->delta_normed_staged, batch, kEps, s));
+            } else if (phase(e, "delta.norm")) {
                 QWC_TRY(qwc_delta_gated_rmsnorm(e->delta_out, e->mixer_in + e->z_offset, layer.out_norm, e->delta_normed,
                                                 batch, kEps, e->mixer_width, s));
             }
-            if (phase(e, "gemm.la_out")) {
+            if (staged) {
                 hint_next_pair(e, layer.gate, layer.up);
+                QWC_TRY(project_and_norm(e, layer.la_out, e->delta_normed_staged, e->mixer_out, layer.post_norm, batch,
+                                         "gemm.la_out"));
+            } else if (phase(e, "gemm.la_out")) {
                 QWC_TRY(project(e, layer.la_out, e->delta_normed, e->mixer_out, batch));
             }
         } else {
-            if (phase(e, "gemm.attn_qkv")) {
+            if (staged && phase(e, "gemm.attn_qkv")) {
+                QWC_TRY(qwc_nvfp4_w4a16_split(layer.qkv.packed, layer.qkv.scales, e->normed_staged, e->split_sums_wide,
+                                              layer.qkv.out_features, layer.qkv.in_features, batch, s));
+                QWC_TRY(qwc_nvfp4_sum_slices(e->split_sums_wide,
+                                             qwc_nvfp4_split_count(layer.qkv.out_features, layer.qkv.in_features),
+                                             layer.qkv.global_scale, e->qkv_buf, batch, e->qkv_width, s));
+            } else if (phase(e, "gemm.attn_qkv")) {
                 QWC_TRY(project(e, layer.qkv, e->normed, e->qkv_buf, batch));
             }
             const int q_width = kQueryHeads * 2 * kHeadDim;
@@ -422,13 +480,17 @@ int decode_forward(qwc_engine* e, int batch) {
             if (phase(e, "attn.decode")) {
                 // The output gate is the second half of each head of [q | gate], which sits at the
                 // front of the fused q|k|v row.
-                QWC_TRY(qwc_paged_attention_packed_fp8_scaled(
+                QWC_TRY(qwc_paged_attention_packed_fp8_staged(
                     e->query, e->qkv_buf, layer.k_cache, layer.v_cache, e->block_tables, e->context_lengths,
-                    layer.k_scale, layer.v_scale, e->attention_out, e->attention_workspace, e->attention_workspace_bytes,
+                    layer.k_scale, layer.v_scale, staged ? nullptr : e->attention_out,
+                    staged ? e->attention_out_staged : nullptr, e->attention_workspace, e->attention_workspace_bytes,
                     batch, 0, e->max_blocks, c.kv_page_size, e->qkv_width, e->partitions, 1.0f / 16.0f, s));
             }
-            if (phase(e, "gemm.attn_out")) {
+            if (staged) {
                 hint_next_pair(e, layer.gate, layer.up);
+                QWC_TRY(project_and_norm(e, layer.o, e->attention_out_staged, e->mixer_out, layer.post_norm, batch,
+                                         "gemm.attn_out"));
+            } else if (phase(e, "gemm.attn_out")) {
                 QWC_TRY(project(e, layer.o, e->attention_out, e->mixer_out, batch));
             }
         }
@@ -437,12 +499,18 @@ int decode_forward(qwc_engine* e, int batch) {
             QWC_TRY(cudaMemcpyAsync(e->trace + (2 * index) * trace_row, e->mixer_out, trace_row * 2,
                                     cudaMemcpyDeviceToDevice, s));
         }
-        if (phase(e, "norm")) {
+        if (!staged && phase(e, "norm")) {
             QWC_TRY(qwc_rmsnorm_bf16(e->mixer_out, e->residual, layer.post_norm, e->normed, batch, c.hidden, kEps, s));
         }
-        if (phase(e, "gemm.mlp_gate_up")) {
+        if (phase(e, "gemm.mlp_gate_up") && staged) {
+            hint_next_split(e, layer.down);
+            QWC_TRY(qwc_nvfp4_swiglu_w4a16_staged(layer.gate.packed, layer.gate.scales, layer.up.packed,
+                                                  layer.up.scales, e->normed_staged, nullptr, e->mlp_hidden_staged,
+                                                  layer.gate.out_features, layer.gate.in_features, batch,
+                                                  layer.gate.global_scale, layer.up.global_scale,
+                                                  e->streamk_workspace, s));
+        } else if (phase(e, "gemm.mlp_gate_up")) {
             __nv_bfloat16* target = e->mlp_hidden + static_cast<size_t>(c.split_rank) * layer.gate.out_features;
-            hint_next(e, layer.down);
             QWC_TRY(qwc_nvfp4_swiglu_w4a16(layer.gate.packed, layer.gate.scales, layer.up.packed, layer.up.scales,
                                            e->normed, c.split_size > 1 ? target : e->mlp_hidden,
                                            layer.gate.out_features, layer.gate.in_features, batch,
@@ -453,18 +521,22 @@ int decode_forward(qwc_engine* e, int batch) {
                 return cudaErrorUnknown;
             }
         }
-        if (phase(e, "gemm.mlp_down")) {
+        const __nv_bfloat16* next_norm = index + 1 < e->layers.size() ? e->layers[index + 1].input_norm : e->final_norm;
+        if (staged) {
             if (index + 1 < e->layers.size()) {
                 const Layer& following = e->layers[index + 1];
                 hint_next(e, following.full ? following.qkv : following.in_proj);
-            } else if (c.split_size == 1) {
+            } else {
                 (void)qwc_nvfp4_prefetch_next(e->lm_head, nullptr, nullptr, nullptr, e->vocab_local, c.hidden, 2);
             }
-            QWC_TRY(project(e, layer.down, e->mlp_hidden, e->mlp_out, batch));
-        }
-        const __nv_bfloat16* next_norm = index + 1 < e->layers.size() ? e->layers[index + 1].input_norm : e->final_norm;
-        if (phase(e, "norm")) {
-            QWC_TRY(qwc_rmsnorm_bf16(e->mlp_out, e->residual, next_norm, e->normed, batch, c.hidden, kEps, s));
+            QWC_TRY(project_and_norm(e, layer.down, e->mlp_hidden_staged, e->mlp_out, next_norm, batch, "gemm.mlp_down"));
+        } else {
+            if (phase(e, "gemm.mlp_down")) {
+                QWC_TRY(project(e, layer.down, e->mlp_hidden, e->mlp_out, batch));
+            }
+            if (phase(e, "norm")) {
+                QWC_TRY(qwc_rmsnorm_bf16(e->mlp_out, e->residual, next_norm, e->normed, batch, c.hidden, kEps, s));
+            }
         }
         if (e->trace != nullptr && e->phase_filter == nullptr) {
             QWC_TRY(cudaMemcpyAsync(e->trace + (2 * index + 1) * trace_row, e->residual, trace_row * 2,
@@ -472,6 +544,19 @@ int decode_forward(qwc_engine* e, int batch) {
         }
     }
 
+    if (staged) {
+        // One launch streams the vocabulary and keeps the best token of every row; a small second one
+        // picks the winners and stores the device status word beside them.  Logits reach memory only
+        // for a caller who asked for them.
+        if (phase(e, "lm_head")) {
+            QWC_TRY(qwc_fp8_lm_head_staged(e->lm_head, e->lm_head_scales, e->normed_staged,
+                                           c.write_logits ? e->logits : nullptr, e->out_dev,
+                                           e->out_dev + c.max_batch + 1, batch, c.hidden, e->vocab_local,
+                                           e->streamk_workspace, s));
+        }
+        mark(e, "end");
+        return 0;
+    }
     if (phase(e, "lm_head")) {
         float* target = e->logits + static_cast<size_t>(c.split_rank) * e->vocab_local;
         QWC_TRY(qwc_fp8_lm_head_batched(e->lm_head, e->lm_head_scales, e->normed, c.split_size > 1 ? target : e->logits,
@@ -570,6 +655,7 @@ void qwc_engine_default_config(qwc_engine_config* config) {
     config->split_size = 1;
     config->use_graph = 1;
     config->attention_partitions = 0;
+    config->write_logits = 0;
 }
 
 int qwc_engine_nccl_unique_id(void* unique_id_128) {
@@ -712,6 +798,19 @@ int qwc_engine_create(const qwc_engine_config* config, qwc_engine** out) {
     QWC_STEP(gpu_alloc_t(e, &e->mixer_out, static_cast<size_t>(mb) * c.hidden, true));
     QWC_STEP(gpu_alloc_t(e, &e->mlp_hidden, static_cast<size_t>(mb) * c.intermediate, true));
     QWC_STEP(gpu_alloc_t(e, &e->mlp_out, static_cast<size_t>(mb) * c.hidden, true));
+    {
+        // staged copies are sized for 32 padded rows, whatever the batch
+        int widest = c.hidden > c.intermediate ? c.hidden : c.intermediate;
+        (void)widest;
+        QWC_STEP(gpu_alloc(e, &e->normed_staged, static_cast<size_t>(c.hidden) * 32 * 2, true));
+        QWC_STEP(gpu_alloc(e, &e->delta_normed_staged, static_cast<size_t>(e->v_heads) * kDeltaDim * 32 * 2, true));
+        QWC_STEP(gpu_alloc(e, &e->attention_out_staged, static_cast<size_t>(kQueryHeads) * kHeadDim * 32 * 2, true));
+        QWC_STEP(gpu_alloc(e, &e->mlp_hidden_staged, static_cast<size_t>(c.intermediate) * 32 * 2, true));
+        QWC_STEP(gpu_alloc(e, &e->streamk_workspace, qwc_streamk_workspace_bytes(), true));
+        QWC_STEP(gpu_alloc_t(e, &e->split_sums, static_cast<size_t>(16) * 32 * c.hidden, true));
+        const int wide = e->mixer_width > e->qkv_width ? e->mixer_width : e->qkv_width;
+        QWC_STEP(gpu_alloc_t(e, &e->split_sums_wide, static_cast<size_t>(16) * 32 * wide, true));
+    }
     QWC_STEP(gpu_alloc_t(e, &e->dq, static_cast<size_t>(mb) * kDeltaKeyHeads * kDeltaDim, true));
     QWC_STEP(gpu_alloc_t(e, &e->dk, static_cast<size_t>(mb) * kDeltaKeyHeads * kDeltaDim, true));
     QWC_STEP(gpu_alloc_t(e, &e->dv, static_cast<size_t>(mb) * e->v_heads * kDeltaDim, true));
@@ -955,7 +1054,9 @@ int qwc_engine_write(qwc_engine* e, const char* name, int layer, const void* hos
 
 void qwc_engine_traffic(const qwc_engine* e, int rows, double context_tokens, qwc_step_traffic* out) {
     std::memset(out, 0, sizeof(*out));
-    int gemv = 0, kernels = 3 /*table edits + pack*/ + 1 /*embed*/ + 1 /*norm*/ + 1 /*lm_head*/ + 2 /*argmax*/;
+    // one GPU: the head samples in its own epilogue and one small kernel picks the winners
+    int gemv = 0, kernels = 3 /*table edits + pack*/ + 1 /*embed*/ + 1 /*norm*/ + 1 /*lm_head*/ +
+                            (e->cfg.split_size == 1 ? 1 : 2) /*sampling*/;
     double gemv_bytes = 0.0;
     for (const Layer& l : e->layers) {
         gemv_bytes += static_cast<double>(l.gate.weight_bytes() + l.up.weight_bytes() + l.down.weight_bytes());
@@ -970,7 +1071,7 @@ void qwc_engine_traffic(const qwc_engine* e, int rows, double context_tokens, qw
         } else {
             gemv_bytes += static_cast<double>(l.qkv.weight_bytes() + l.o.weight_bytes());
             gemv += 2;
-            kernels += 2 + 2 + (e->partitions > 1 ? 1 : 0);
+            kernels += 2 + 2 + (e->partitions > 1 ? 1 : 0) + (e->cfg.split_size == 1 ? 1 : 0 /*slice sum*/);
             out->kv_bytes += context_tokens * 2.0 * kKvHeads * kHeadDim;
         }
     }

@@ -16,8 +16,12 @@
 //     same number of bytes whatever the matrix shape is.  A share crosses pair boundaries, so a CTA
 //     works through a list of segments; a segment that does not cover all of K leaves an fp32 partial
 //     tile in a workspace in global memory (L2-resident) and takes a ticket; whoever takes the last
-//     ticket of a tile sums the partials in segment order (bit-reproducible) and stores the result.
-//     Nobody waits for anybody: there is no cluster and no barrier between CTAs.
+//     ticket of a tile sums the partials in a fixed order (bit-reproducible) and stores the result.
+//     Nobody waits for anybody: there is no cluster and no barrier between CTAs.  The piece a CTA
+//     ends its share with is the first piece of its pair, and the other pieces are usually long
+//     finished by then: while the main loop still runs, the (idle) epilogue warps look at the
+//     ticket, and if everybody else has arrived they fetch the sum of the other pieces into shared
+//     memory, so that the end of the launch is one TMEM read, one addition and the stores.
 //   * A drain that does not stop the stream.  Accumulators are double-buffered in tensor memory and
 //     eight epilogue warps read them, so the dequantising warps and the tensor core go on with the
 //     next segment while the previous one is scaled, combined (SwiGLU) and stored.
@@ -55,7 +59,7 @@ constexpr int kBoxBytes = kTileRows * kBoxRowBytes;       // 16 KiB, multiple of
 constexpr int kScaleStageBytes = kStageChunks * 2 * 512;  // scale blocks of 512 bytes per 128 rows and 64 K
 constexpr int kTileStageBytes = kBoxBytes + kScaleStageBytes;
 constexpr int kWeightStages = 4;
-constexpr int kXStages = 6;                   // activation chunks in flight
+constexpr int kXStages = 5;                   // activation chunks in flight
 constexpr int kXStageBytes = 32 * kChunkK * 2;  // a chunk of 32 rows; 16 rows use half of it
 constexpr int kABuffers = 3;
 constexpr int kRowWarps = 8;                  // one thread per weight row of the two tiles
@@ -75,7 +79,10 @@ constexpr int kAccumulatorBuffers = 2;
 constexpr int kTileColumns = kAccumulatorColumn + 32 * kAccumulatorBuffers;
 static_assert(kTiles * kTileColumns <= kTmemColumns, "tensor memory budget");
 static_assert(kTileStageBytes % 1024 == 0, "swizzled boxes start on 1 KiB boundaries");
-constexpr int kSmemBytes = kWeightStages * kTiles * kTileStageBytes + kXStages * kXStageBytes + 1024;
+constexpr int kStashWarpFloats = kTiles * 16 * 32;  // what an epilogue warp holds of a tile pair: 4 KiB
+constexpr int kStashBytes = 8 * kStashWarpFloats * 4;
+constexpr int kSmemBytes =
+    kWeightStages * kTiles * kTileStageBytes + kXStages * kXStageBytes + kStashBytes + 1024;
 
 // Workspace in global memory: partial tiles, then tickets, then the vocabulary head's candidates.
 constexpr int kMaxCtas = 160;
@@ -104,6 +111,12 @@ struct StreamKParams {
     int units;        // pair_tiles * stages_in_k
     float* partials;
     int* tickets;
+    // Regular K split: CTA = pair * splits + slice, no tickets.  With more than one slice every CTA
+    // stores its fp32 partial rows [slice][batch][N] in split_out and the consumer sums them; with one
+    // slice (a CTA per tile pair: matrices with about as many pairs as SMs) the CTA finishes its pair
+    // itself.  0 splits: equal shares with tickets.
+    int splits;
+    float* split_out;
     float* candidate_values;     // vocabulary head with sampling: [32][kCandidateSlots]
     uint32_t* candidate_indices;
     int* status;
@@ -116,11 +129,34 @@ struct StreamKParams {
         int out_features;
         int ctas;
         int units;
+        int splits;  // 0: equal shares
         int stages_in_k;
         int group_blocks;
         const uint8_t* scales[2];
     } next;
 };
+
+// Optional timeline of every CTA of the last launch (compile with -DQWC_STREAMK_TRACE): nanosecond
+// stamps of the global timer at the events named in trace_names(), read back with qwc_streamk_trace.
+#ifdef QWC_STREAMK_TRACE
+constexpr int kTraceSlots = 32;
+__device__ unsigned long long g_trace[kMaxCtas * kTraceSlots];
+__device__ __forceinline__ void trace_stamp(int slot) {
+    unsigned long long now;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(now)::"memory");
+    g_trace[blockIdx.x * kTraceSlots + slot] = now;
+}
+#define QWC_TRACE(slot) trace_stamp(slot)
+#define QWC_TRACE_LANE0(slot) \
+    do {                      \
+        if (lane == 0) {      \
+            trace_stamp(slot); \
+        }                     \
+    } while (0)
+#else
+#define QWC_TRACE(slot)
+#define QWC_TRACE_LANE0(slot)
+#endif
 
 struct Barriers {
     uint64_t w_full[kWeightStages];
@@ -166,6 +202,21 @@ __device__ __forceinline__ bool sk_wait(uint64_t* bar, uint32_t parity, Barriers
     return sk_wait_slow(bar, parity, b, status);
 }
 
+// One look at a barrier phase, without the hardware's own wait that try_wait includes.
+__device__ __forceinline__ bool mbar_test(uint64_t* bar, uint32_t parity) {
+    uint32_t done;
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+        "selp.u32 %0, 1, 0, p;\n"
+        "}\n"
+        : "=r"(done)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return done != 0;
+}
+
 // First unit of CTA `cta` when `units` units are shared by `ctas` CTAs.
 __device__ __forceinline__ int share_begin(int units, int cta, int ctas) {
     return static_cast<int>(static_cast<long long>(units) * cta / ctas);
@@ -176,11 +227,82 @@ __device__ __forceinline__ int share_owner(int units, int unit, int ctas) {
     return static_cast<int>(((static_cast<long long>(unit) + 1) * ctas - 1) / units);
 }
 
+// A ticket is taken with release (the partial stored before it is visible to whoever sees the count)
+// and acquire (the one who takes the last ticket sees every partial stored before the others).
+__device__ __forceinline__ int ticket_take(int* ticket) {
+    int taken;
+    asm volatile("atom.acq_rel.gpu.global.add.s32 %0, [%1], 1;" : "=r"(taken) : "l"(ticket) : "memory");
+    return taken;
+}
+
+__device__ __forceinline__ int ticket_look(const int* ticket) {
+    int count;
+    asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(count) : "l"(ticket) : "memory");
+    return count;
+}
+
 __device__ __forceinline__ bool better_candidate(float value, uint32_t index, float best, uint32_t best_index) {
     return value > best || (value == best && index < best_index);
 }
 
-template <bool kFp8, bool kSwiglu, int kPad>
+// Where the partial of CTA `owner` for tile pair `pair` lies, for epilogue warp `e` (see the kernel:
+// slot 0 when the owner's share starts with that piece, slot 1 when it ends with it).
+__device__ __forceinline__ const float* piece_of(const float* partials, int units, int ctas, int S, int pair,
+                                                 int owner, int e) {
+    const int slot = share_begin(units, owner, ctas) >= pair * S ? 0 : 1;
+    return partials + (static_cast<size_t>(owner * 2 + slot) * kEpilogueWarps + e) * kPartialWarpFloats;
+}
+
+// Sums `count` pieces of a tile pair into this warp's stash (shared memory), in the fixed order
+// first + 1, first + 2, .., last, first (the first piece comes last because its owner is the one who
+// usually finishes the sum, with that piece still on chip).  The piece of CTA `own` (-1: none) is
+// taken from the stash itself, where it already lies, the others from the workspace; kPieces x kWidth
+// loads are in flight at a time: the sum costs L2 round trips, not bandwidth.
+template <int kCols, int kPieces, int kWidth>
+__device__ __forceinline__ void sum_pieces_to_stash(const float* partials, int units, int ctas, int S, int pair,
+                                                    int first_cta, int last_cta, int count, int own, int e,
+                                                    int lane, float* stash) {
+    const int pieces = last_cta - first_cta + 1;
+#pragma unroll 1
+    for (int base = 0; base < 2 * kCols; base += kWidth) {
+        float total[kWidth];
+#pragma unroll
+        for (int i = 0; i < kWidth; ++i) {
+            total[i] = 0.0f;
+        }
+#pragma unroll 1
+        for (int q0 = 0; q0 < count; q0 += kPieces) {
+            float piece[kPieces][kWidth];
+#pragma unroll
+            for (int j = 0; j < kPieces; ++j) {
+                // a batch that reaches past the last piece reads the last piece again and adds nothing
+                const int q = min(q0 + j, count - 1);
+                const int owner = q < pieces - 1 ? first_cta + 1 + q : first_cta;
+                const float* theirs = piece_of(partials, units, ctas, S, pair, owner, e) + lane;
+#pragma unroll
+                for (int i = 0; i < kWidth; ++i) {
+                    const int flat = base + i;  // tile * kCols + column
+                    piece[j][i] = owner == own ? stash[flat * 32 + lane]
+                                               : __ldcg(theirs + ((flat / kCols) * 16 + flat % kCols) * 32);
+                }
+            }
+#pragma unroll
+            for (int j = 0; j < kPieces; ++j) {
+                const bool valid = q0 + j < count;
+#pragma unroll
+                for (int i = 0; i < kWidth; ++i) {
+                    total[i] += valid ? piece[j][i] : 0.0f;
+                }
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < kWidth; ++i) {
+            stash[(base + i) * 32 + lane] = total[i];
+        }
+    }
+}
+
+template <bool kFp8, bool kSwiglu, int kPad, bool kSplitOut>
 __global__ void __launch_bounds__(kThreads, 1)
     nvfp4_streamk_kernel(const __grid_constant__ CUtensorMap map0, const __grid_constant__ CUtensorMap map1,
                          const __grid_constant__ CUtensorMap next_map0, const __grid_constant__ CUtensorMap next_map1,
@@ -193,12 +315,23 @@ __global__ void __launch_bounds__(kThreads, 1)
     pdl_launch_dependents();
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
+    if (threadIdx.x == 0) {
+        QWC_TRACE(0);  // entry
+    }
     const int cta = blockIdx.x;
     const int ctas = gridDim.x;
     const int S = p.stages_in_k;
     constexpr int stage_chunks = kFp8 ? 1 : kStageChunks;  // 128 bytes per row and stage either way
-    const int u_begin = share_begin(p.units, cta, ctas);
-    const int u_end = share_begin(p.units, cta + 1, ctas);
+    int u_begin, u_end;
+    if (kSplitOut) {
+        const int pair = cta / p.splits;
+        const int slice = cta - pair * p.splits;
+        u_begin = pair * S + S * slice / p.splits;
+        u_end = pair * S + S * (slice + 1) / p.splits;
+    } else {
+        u_begin = share_begin(p.units, cta, ctas);
+        u_end = share_begin(p.units, cta + 1, ctas);
+    }
     const int num_units = u_end - u_begin;
     const int total_chunks = num_units * stage_chunks;
     const int pair_first = u_begin / S;
@@ -208,6 +341,7 @@ __global__ void __launch_bounds__(kThreads, 1)
 
     unsigned char* weight_ring = smem;                                       // [stage][tile][box | scales]
     unsigned char* x_ring = smem + kWeightStages * kTiles * kTileStageBytes;  // [chunk][K core][row][8] f16
+    float* stash_base = reinterpret_cast<float*>(x_ring + kXStages * kXStageBytes);  // [epilogue warp][4 KiB]
 
     // One stage of the weight ring: a box per tile and the tiles' block scales (issued by one thread).
     auto issue_stage = [&](int index, int pair, int stage) {
@@ -274,6 +408,9 @@ __global__ void __launch_bounds__(kThreads, 1)
         mbar_fence_init();
     }
     __syncthreads();
+    if (threadIdx.x == 0) {
+        QWC_TRACE(1);  // barriers set up
+    }
     // Tensor memory is allocated while the producer already fetches weights; the warps that use it
     // wait for the address below.
     uint32_t tmem_base = 0;
@@ -314,6 +451,9 @@ __global__ void __launch_bounds__(kThreads, 1)
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) {
                 break;
+            }
+            if (warp == 0 && c == 0) {
+                QWC_TRACE_LANE0(2);  // first weights landed
             }
             const unsigned char* stage = weight_ring + (slot * kTiles + tile) * kTileStageBytes;
             const unsigned char* row = stage + row_offset;
@@ -398,6 +538,9 @@ __global__ void __launch_bounds__(kThreads, 1)
                 mbar_arrive(&bars.w_empty[slot]);  // this warp reads one chunk per stage
             }
         }
+        if (warp == 0) {
+            QWC_TRACE_LANE0(6);  // last chunk dequantised
+        }
     } else if (warp == kProducerWarp) {
         // ---------------- producer: weights and scales ----------------
         bool ok = true;
@@ -422,11 +565,20 @@ __global__ void __launch_bounds__(kThreads, 1)
                 ++pair;
             }
         }
+        QWC_TRACE_LANE0(7);  // last stage requested
         if (ok && p.next.valid && elect_one()) {
             // the first stages of the shares of the launch that follows, dealt over this launch's CTAs
             for (int other = cta; other < p.next.ctas; other += ctas) {
-                const int first = share_begin(p.next.units, other, p.next.ctas);
-                const int end = share_begin(p.next.units, other + 1, p.next.ctas);
+                int first, end;
+                if (p.next.splits > 0) {
+                    const int its_pair = other / p.next.splits;
+                    const int its_slice = other - its_pair * p.next.splits;
+                    first = its_pair * p.next.stages_in_k + p.next.stages_in_k * its_slice / p.next.splits;
+                    end = its_pair * p.next.stages_in_k + p.next.stages_in_k * (its_slice + 1) / p.next.splits;
+                } else {
+                    first = share_begin(p.next.units, other, p.next.ctas);
+                    end = share_begin(p.next.units, other + 1, p.next.ctas);
+                }
                 const int count = min(kWeightStages, end - first);
                 int next_pair = first / p.next.stages_in_k;
                 int next_stage = first - next_pair * p.next.stages_in_k;
@@ -479,12 +631,18 @@ __global__ void __launch_bounds__(kThreads, 1)
             if (ok) {
                 ok = sk_wait(&bars.x_full[xs], x_parity, &bars, p.status);
             }
+            if (t == 0 && c == 0) {
+                QWC_TRACE_LANE0(3);  // first activations landed
+            }
             if (ok) {
                 ok = sk_wait(&bars.a_ready[t][buf], a_parity, &bars, p.status);
             }
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) {
                 break;
+            }
+            if (t == 0 && c == 0) {
+                QWC_TRACE_LANE0(4);  // first MMA
             }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             if (elect_one()) {
@@ -516,11 +674,15 @@ __global__ void __launch_bounds__(kThreads, 1)
             }
             segment += last ? 1 : 0;
         }
+        if (t == 0) {
+            QWC_TRACE_LANE0(5);  // last MMA issued
+        }
     } else if (warp == kXWarp) {
         // ---------------- activation chunks ----------------
         // Everything above starts before the kernel that produces the activations has finished; these
         // loads (and the epilogue's stores) wait for it.
         pdl_wait();
+        QWC_TRACE_LANE0(22);  // the previous kernel has finished
         bool ok = true;
         int stage = stage_first;
         for (int c = 0; c < total_chunks && ok; ++c) {
@@ -548,6 +710,8 @@ __global__ void __launch_bounds__(kThreads, 1)
     } else {
         // ---------------- epilogue ----------------
         // Warp e: output rows 32 (e % 4) .. + 31 of both tiles, activation rows (e / 4) * kPad / 2 .. .
+        // Everything goes through the warp's 4 KiB stash in shared memory ([tile * kCols + column][lane]),
+        // eight columns at a time, so that no step holds more than a few registers.
         constexpr int kCols = kPad / 2;  // accumulator columns per tile and warp
         const int e = warp - kFirstEpilogueWarp;
         const int quarter = e & 3;
@@ -557,22 +721,78 @@ __global__ void __launch_bounds__(kThreads, 1)
         float best_value = -INFINITY;      // lane i: best logit of activation row first_token + i
         uint32_t best_index = UINT32_MAX;
         const bool sampling = kFp8 && p.candidate_values != nullptr;
+        float* stash = stash_base + e * kStashWarpFloats + lane;
         pdl_wait();
+        if (e == 0) {
+            QWC_TRACE_LANE0(23);
+        }
         bool ok = tmem_ok;
 
-        // Scales a finished tile pair, combines (SwiGLU), rounds and stores.  v[t * kCols + i]: tile t,
-        // activation row first_token + i, this lane's output row.
-        auto finalize = [&](int pair, const float (&v)[2 * kCols]) {
-            if (kSwiglu) {
-                const int row = pair * kTileRows + quarter * 32 + lane;
-                if (row < p.out_features) {
+        // Scales the finished tile pair in the stash, combines (SwiGLU), rounds and stores.
+        auto finalize = [&](int pair) {
+#pragma unroll 1
+            for (int c0 = 0; c0 < kCols; c0 += 8) {
+                float v0[8], v1[8];
 #pragma unroll
-                    for (int i = 0; i < kCols; ++i) {
-                        const int token = first_token + i;
-                        if (token < p.batch) {
-                            const float gate = v[i] * p.inverse_scale[0];
-                            const float up = v[kCols + i] * p.inverse_scale[1];
-                            const __nv_bfloat16 rounded = __float2bfloat16(gate / (1.0f + __expf(-gate)) * up);
+                for (int i = 0; i < 8; ++i) {
+                    v0[i] = stash[(c0 + i) * 32];
+                    v1[i] = stash[(kCols + c0 + i) * 32];
+                }
+                if (kSwiglu) {
+                    const int row = pair * kTileRows + quarter * 32 + lane;
+                    if (row < p.out_features) {
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) {
+                            const int token = first_token + c0 + i;
+                            if (token < p.batch) {
+                                const float gate = v0[i] * p.inverse_scale[0];
+                                const float up = v1[i] * p.inverse_scale[1];
+                                const __nv_bfloat16 rounded = __float2bfloat16(gate / (1.0f + __expf(-gate)) * up);
+                                if (p.y != nullptr) {
+                                    p.y[static_cast<size_t>(token) * p.out_features + row] = rounded;
+                                }
+                                if (p.y_staged != nullptr) {
+                                    p.y_staged[(static_cast<size_t>(row >> 3) * kPad + token) * 8 + (row & 7)] =
+                                        __float2half_rn(fminf(fmaxf(__bfloat162float(rounded), -65504.0f), 65504.0f));
+                                }
+                            }
+                        }
+                    }
+                    continue;
+                }
+#pragma unroll
+                for (int t = 0; t < kTiles; ++t) {
+                    const int row = (pair * kTiles + t) * kTileRows + quarter * 32 + lane;
+                    const bool inside = row < p.out_features;
+                    const float row_scale = kFp8 ? (inside ? p.row_scales[row] : 0.0f) : p.inverse_scale[0];
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        const int token = first_token + c0 + i;
+                        const float value = (t == 0 ? v0[i] : v1[i]) * row_scale;
+                        if (kFp8) {
+                            if (inside && token < p.batch && p.y_f32 != nullptr) {
+                                p.y_f32[static_cast<size_t>(token) * p.out_features + row] = value;
+                            }
+                            if (sampling) {
+                                // best of this warp's 32 rows for this activation row; lane c0 + i keeps it
+                                float candidate = inside ? value : -INFINITY;
+                                uint32_t index = inside ? static_cast<uint32_t>(row) : UINT32_MAX;
+#pragma unroll
+                                for (int offset = 16; offset > 0; offset >>= 1) {
+                                    const float other = __shfl_xor_sync(0xffffffffu, candidate, offset);
+                                    const uint32_t other_index = __shfl_xor_sync(0xffffffffu, index, offset);
+                                    if (better_candidate(other, other_index, candidate, index)) {
+                                        candidate = other;
+                                        index = other_index;
+                                    }
+                                }
+                                if (lane == c0 + i && better_candidate(candidate, index, best_value, best_index)) {
+                                    best_value = candidate;
+                                    best_index = index;
+                                }
+                            }
+                        } else if (inside && token < p.batch) {
+                            const __nv_bfloat16 rounded = __float2bfloat16(value);
                             if (p.y != nullptr) {
                                 p.y[static_cast<size_t>(token) * p.out_features + row] = rounded;
                             }
@@ -583,53 +803,18 @@ __global__ void __launch_bounds__(kThreads, 1)
                         }
                     }
                 }
-                return;
-            }
-#pragma unroll
-            for (int t = 0; t < kTiles; ++t) {
-                const int row = (pair * kTiles + t) * kTileRows + quarter * 32 + lane;
-                const bool inside = row < p.out_features;
-                const float row_scale = kFp8 ? (inside ? p.row_scales[row] : 0.0f) : p.inverse_scale[0];
-#pragma unroll
-                for (int i = 0; i < kCols; ++i) {
-                    const int token = first_token + i;
-                    const float value = v[t * kCols + i] * row_scale;
-                    if (kFp8) {
-                        if (inside && token < p.batch && p.y_f32 != nullptr) {
-                            p.y_f32[static_cast<size_t>(token) * p.out_features + row] = value;
-                        }
-                        if (sampling) {
-                            // best of this warp's 32 rows for this activation row; lane i keeps it
-                            float candidate = inside ? value : -INFINITY;
-                            uint32_t index = inside ? static_cast<uint32_t>(row) : UINT32_MAX;
-#pragma unroll
-                            for (int offset = 16; offset > 0; offset >>= 1) {
-                                const float other = __shfl_xor_sync(0xffffffffu, candidate, offset);
-                                const uint32_t other_index = __shfl_xor_sync(0xffffffffu, index, offset);
-                                if (better_candidate(other, other_index, candidate, index)) {
-                                    candidate = other;
-                                    index = other_index;
-                                }
-                            }
-                            if (lane == i && better_candidate(candidate, index, best_value, best_index)) {
-                                best_value = candidate;
-                                best_index = index;
-                            }
-                        }
-                    } else if (inside && token < p.batch) {
-                        const __nv_bfloat16 rounded = __float2bfloat16(value);
-                        if (p.y != nullptr) {
-                            p.y[static_cast<size_t>(token) * p.out_features + row] = rounded;
-                        }
-                        if (p.y_staged != nullptr) {
-                            p.y_staged[(static_cast<size_t>(row >> 3) * kPad + token) * 8 + (row & 7)] =
-                                __float2half_rn(fminf(fmaxf(__bfloat162float(rounded), -65504.0f), 65504.0f));
-                        }
-                    }
-                }
             }
         };
-
+        // `count` pieces in the fixed order; `own`: this CTA when its piece lies in the stash, else -1
+        const auto sum_to_stash = [&](int pair, int first_cta, int last_cta, int count, int own) {
+            if (count <= 2) {
+                sum_pieces_to_stash<kCols, 2, kCols>(p.partials, p.units, ctas, S, pair, first_cta, last_cta, count, own,
+                                                     e, lane, stash - lane);
+            } else {
+                sum_pieces_to_stash<kCols, 4, 8>(p.partials, p.units, ctas, S, pair, first_cta, last_cta, count, own, e,
+                                                 lane, stash - lane);
+            }
+        };
         int u = u_begin;
         int segment = 0;
         while (u < u_end && ok) {
@@ -637,27 +822,57 @@ __global__ void __launch_bounds__(kThreads, 1)
             const int s0 = u - pair * S;
             const int s1 = min(S, s0 + (u_end - u));
             const int acc = segment & 1;
+            const bool whole = !kSplitOut && s0 == 0 && s1 == S;
+            const bool ticketed = !kSplitOut && !whole;
+            const int first_cta = ticketed ? share_owner(p.units, pair * S, ctas) : cta;
+            const int last_cta = ticketed ? share_owner(p.units, pair * S + S - 1, ctas) : cta;
+            int* ticket = p.tickets + pair * kEpilogueWarps + e;
+            // The first piece of a pair is what its CTA ends its share with, so it usually arrives last:
+            // its owner looks at the ticket while it waits for its own accumulators (the epilogue warps
+            // have nothing else to do), and once all the others are in, it parks their sum in the stash.
+            // The end of the launch is then one TMEM read, one addition and the stores.
+            const bool may_look = ticketed && s0 == 0 && u + (s1 - s0) == u_end;
+            bool parked = false;
+            if (may_look) {
+                const long long start = clock64();
+                while (!mbar_test(&bars.d_ready[acc], (segment >> 1) & 1)) {
+                    int count = 0;
+                    if (lane == 0) {
+                        count = ticket_look(ticket);  // an L2 round trip: this loop polls gently
+                    }
+                    count = __shfl_sync(0xffffffffu, count, 0);
+                    if (count == last_cta - first_cta) {
+                        sum_to_stash(pair, first_cta, last_cta, count, -1);
+                        parked = true;
+                        break;
+                    }
+                    if (clock64() - start > 40000000ll || *reinterpret_cast<volatile int*>(&bars.failed) != 0) {
+                        break;  // the bounded wait below gives the verdict
+                    }
+                }
+            }
             ok = sk_wait(&bars.d_ready[acc], (segment >> 1) & 1, &bars, p.status);
             ok = __all_sync(0xffffffffu, ok);
             if (!ok) {
                 break;
             }
+            if (e == 0 && segment < 4) {
+                QWC_TRACE_LANE0(8 + 3 * segment);  // accumulators of the segment complete
+            }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            float v[2 * kCols];
-            {
-                uint32_t r0[kCols], r1[kCols];
-                if constexpr (kCols == 16) {
-                    tmem_load16_issue(lane_address + acc * 32, reinterpret_cast<uint32_t(&)[16]>(r0));
-                    tmem_load16_issue(lane_address + kTileColumns + acc * 32, reinterpret_cast<uint32_t(&)[16]>(r1));
-                } else {
-                    tmem_load8_issue(lane_address + acc * 32, reinterpret_cast<uint32_t(&)[8]>(r0));
-                    tmem_load8_issue(lane_address + kTileColumns + acc * 32, reinterpret_cast<uint32_t(&)[8]>(r1));
-                }
-                tmem_load_wait();
+            // tensor memory -> stash (added to the parked sum of the other pieces when there is one)
 #pragma unroll
-                for (int i = 0; i < kCols; ++i) {
-                    v[i] = __uint_as_float(r0[i]);
-                    v[kCols + i] = __uint_as_float(r1[i]);
+            for (int t = 0; t < kTiles; ++t) {
+#pragma unroll
+                for (int c0 = 0; c0 < kCols; c0 += 8) {
+                    uint32_t r[8];
+                    tmem_load8_issue(lane_address + t * kTileColumns + acc * 32 + c0, r);
+                    tmem_load_wait();
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        float* slot = stash + (t * kCols + c0 + i) * 32;
+                        *slot = parked ? *slot + __uint_as_float(r[i]) : __uint_as_float(r[i]);
+                    }
                 }
             }
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -665,56 +880,72 @@ __global__ void __launch_bounds__(kThreads, 1)
             if (lane == 0) {
                 mbar_arrive(&bars.d_free[acc]);
             }
-            if (s0 == 0 && s1 == S) {
-                finalize(pair, v);
-            } else {
+            if (e == 0 && segment < 4) {
+                QWC_TRACE_LANE0(9 + 3 * segment);  // accumulators read
+            }
+            bool complete = whole || parked;
+            if (kSplitOut && p.split_out == nullptr) {
+                complete = true;  // one CTA per tile pair: nothing to sum
+            } else if (kSplitOut) {
+                // the consumer sums the slices: fp32 rows [slice][batch][N], this lane's two rows
+                const int slice = cta - pair * p.splits;
+#pragma unroll
+                for (int t = 0; t < kTiles; ++t) {
+                    const int row = (pair * kTiles + t) * kTileRows + quarter * 32 + lane;
+                    if (row < p.out_features) {
+#pragma unroll
+                        for (int i = 0; i < kCols; ++i) {
+                            const int token = first_token + i;
+                            if (token < p.batch) {
+                                p.split_out[(static_cast<size_t>(slice) * p.batch + token) * p.out_features + row] =
+                                    stash[(t * kCols + i) * 32];
+                            }
+                        }
+                    }
+                }
+            } else if (parked) {
+                if (lane == 0) {
+                    *ticket = 0;  // everybody else arrived long ago: the tickets go back
+                }
+            } else if (!whole) {
                 // A piece of the pair's K range: the partial goes to this CTA's slot (0: the share starts
                 // with it, 1: the share ends with it), then a ticket.  Tickets are per (pair, epilogue
                 // warp): a warp never has to wait for the other warps of its CTA.
                 const int slot = u == u_begin ? 0 : 1;
-                float* mine = p.partials + (static_cast<size_t>(cta * 2 + slot) * kEpilogueWarps + e) * kPartialWarpFloats;
+                float* mine = p.partials + (static_cast<size_t>(cta * 2 + slot) * kEpilogueWarps + e) * kPartialWarpFloats + lane;
 #pragma unroll
                 for (int i = 0; i < kCols; ++i) {
-                    mine[i * 32 + lane] = v[i];
-                    mine[(16 + i) * 32 + lane] = v[kCols + i];
+                    mine[i * 32] = stash[i * 32];
+                    mine[(16 + i) * 32] = stash[(kCols + i) * 32];
                 }
-                __threadfence();
-                __syncwarp();
-                int* ticket = p.tickets + pair * kEpilogueWarps + e;
+                __syncwarp();  // every lane's stores are ordered before the ticket that lane 0 takes
                 int taken = 0;
                 if (lane == 0) {
-                    taken = atomicAdd(ticket, 1);
+                    taken = ticket_take(ticket);
                 }
                 taken = __shfl_sync(0xffffffffu, taken, 0);
-                const int first_cta = share_owner(p.units, pair * S, ctas);
-                const int last_cta = share_owner(p.units, pair * S + S - 1, ctas);
                 if (taken == last_cta - first_cta) {
-                    // the last piece to arrive: sum all pieces in K order, whoever arrived when
+                    // the last piece to arrive sums all of them, in the fixed order
                     if (lane == 0) {
                         *ticket = 0;  // ready for the next launch
                     }
-                    __threadfence();
-#pragma unroll
-                    for (int i = 0; i < 2 * kCols; ++i) {
-                        v[i] = 0.0f;
-                    }
-                    for (int other = first_cta; other <= last_cta; ++other) {
-                        const int other_slot = share_begin(p.units, other, ctas) >= pair * S ? 0 : 1;
-                        const float* theirs =
-                            p.partials + (static_cast<size_t>(other * 2 + other_slot) * kEpilogueWarps + e) * kPartialWarpFloats;
-                        float piece[2 * kCols];
-#pragma unroll
-                        for (int i = 0; i < kCols; ++i) {
-                            piece[i] = __ldcg(theirs + i * 32 + lane);
-                            piece[kCols + i] = __ldcg(theirs + (16 + i) * 32 + lane);
-                        }
-#pragma unroll
-                        for (int i = 0; i < 2 * kCols; ++i) {
-                            v[i] += piece[i];
-                        }
-                    }
-                    finalize(pair, v);
+                    sum_to_stash(pair, first_cta, last_cta, last_cta - first_cta + 1, cta);
+                    complete = true;
                 }
+            }
+            if (complete) {
+                __syncwarp();
+                finalize(pair);
+            }
+            if (e == 0 && segment < 4) {
+                QWC_TRACE_LANE0(10 + 3 * segment);  // segment stored (partial or final)
+#ifdef QWC_STREAMK_TRACE
+                if (lane == 0) {
+                    g_trace[blockIdx.x * kTraceSlots + 24 + segment] =
+                        (whole ? 1 : 0) | (parked ? 2 : 0) | (complete ? 4 : 0) | ((last_cta - first_cta + 1) << 8) |
+                        (static_cast<unsigned long long>(s1 - s0) << 16);
+                }
+#endif
             }
             u += s1 - s0;
             ++segment;
@@ -731,6 +962,9 @@ __global__ void __launch_bounds__(kThreads, 1)
     // (a stage that was consumed has completed its first phase long ago and the wait falls through).
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
+    if (threadIdx.x == 0) {
+        QWC_TRACE(21);  // every role done
+    }
     const bool failed = *reinterpret_cast<volatile int*>(&bars.failed) != 0;
     if (failed && threadIdx.x == kProducerWarp * 32) {
         for (int slot = 0; slot < early_stages; ++slot) {
@@ -840,16 +1074,36 @@ struct LaunchShape {
     int stages_in_k;
     int units;
     int ctas;
+    int splits;  // of the regular K split whose sum is left to the consumer; 0: equal shares with tickets
 };
 
-LaunchShape shape_of(int out_features, int in_features, bool swiglu, bool fp8) {
+// Tile pairs that nearly fill the SMs once are not cut at all: one CTA per pair.
+bool prefers_whole_pairs(int pair_tiles, int ctas) { return pair_tiles <= ctas && pair_tiles * 20 >= ctas * 17; }
+
+LaunchShape shape_of(int out_features, int in_features, bool swiglu, bool fp8, bool split_out = false) {
     LaunchShape shape;
     const int rows_per_pair = swiglu ? kTileRows : kTiles * kTileRows;
     shape.pair_tiles = (out_features + rows_per_pair - 1) / rows_per_pair;
     shape.stages_in_k = in_features / (fp8 ? kChunkK : kChunkK * kStageChunks);
     shape.units = shape.pair_tiles * shape.stages_in_k;
+    shape.splits = 0;
     const int sms = sm_count_streamk();
     shape.ctas = sms < kMaxCtas ? sms : kMaxCtas;
+    if (!split_out && !fp8 && prefers_whole_pairs(shape.pair_tiles, shape.ctas)) {
+        shape.splits = 1;
+        shape.ctas = shape.pair_tiles;
+        return shape;
+    }
+    if (split_out) {
+        // as many K slices per tile pair as fill the SMs once; a slice holds at least one stage
+        int splits = shape.ctas / shape.pair_tiles;
+        splits = splits < 1 ? 1 : splits;
+        splits = splits > shape.stages_in_k ? shape.stages_in_k : splits;
+        splits = splits > 16 ? 16 : splits;
+        shape.splits = splits;
+        shape.ctas = shape.pair_tiles * splits;
+        return shape;
+    }
     if (shape.ctas > shape.units) {
         shape.ctas = shape.units;
     }
@@ -858,17 +1112,19 @@ LaunchShape shape_of(int out_features, int in_features, bool swiglu, bool fp8) {
 
 cudaError_t launch_streamk(StreamKParams p, const void* packed0, const void* packed1, bool swiglu, bool fp8,
                            void* workspace, cudaStream_t stream) {
-    const LaunchShape shape = shape_of(p.out_features, p.in_features, swiglu, fp8);
-    if (shape.pair_tiles > kMaxPairTiles || shape.units <= 0) {
+    const bool split_out = p.split_out != nullptr;
+    const LaunchShape shape = shape_of(p.out_features, p.in_features, swiglu, fp8, split_out);
+    if (shape.pair_tiles > kMaxPairTiles || shape.units <= 0 || shape.ctas > 4 * kMaxCtas) {
         (void)take_next_projection();
         return cudaErrorInvalidValue;
     }
     p.pair_tiles = shape.pair_tiles;
     p.stages_in_k = shape.stages_in_k;
     p.units = shape.units;
+    p.splits = shape.splits;
     unsigned char* base = static_cast<unsigned char*>(workspace);
     p.partials = reinterpret_cast<float*>(base);
-    p.tickets = reinterpret_cast<int*>(base + kPartialBytes);
+    p.tickets = shape.splits > 0 ? nullptr : reinterpret_cast<int*>(base + kPartialBytes);
     const int row_bytes = fp8 ? p.in_features : p.in_features / 2;
     CUtensorMap map0, map1;
     cudaError_t encoded = encode_weight_map(&map0, packed0, p.out_features, row_bytes);
@@ -881,10 +1137,12 @@ cudaError_t launch_streamk(StreamKParams p, const void* packed0, const void* pac
     }
     using Kernel = void (*)(const CUtensorMap, const CUtensorMap, const CUtensorMap, const CUtensorMap,
                             const StreamKParams);
-    static const Kernel kernels[6] = {
-        nvfp4_streamk_kernel<false, false, 16>, nvfp4_streamk_kernel<false, false, 32>,
-        nvfp4_streamk_kernel<false, true, 16>,  nvfp4_streamk_kernel<false, true, 32>,
-        nvfp4_streamk_kernel<true, false, 16>,  nvfp4_streamk_kernel<true, false, 32>};
+    static const Kernel kernels[10] = {
+        nvfp4_streamk_kernel<false, false, 16, false>, nvfp4_streamk_kernel<false, false, 32, false>,
+        nvfp4_streamk_kernel<false, true, 16, false>,  nvfp4_streamk_kernel<false, true, 32, false>,
+        nvfp4_streamk_kernel<true, false, 16, false>,  nvfp4_streamk_kernel<true, false, 32, false>,
+        nvfp4_streamk_kernel<false, false, 16, true>,  nvfp4_streamk_kernel<false, false, 32, true>,
+        nvfp4_streamk_kernel<false, true, 16, true>,   nvfp4_streamk_kernel<false, true, 32, true>};
     static PerDevice<cudaError_t> opted_per_device;
     const cudaError_t* opted = opted_per_device.get([]() {
         for (const Kernel kernel : kernels) {
@@ -908,7 +1166,8 @@ cudaError_t launch_streamk(StreamKParams p, const void* packed0, const void* pac
         const bool next_fp8 = hint.kind == 2;
         const bool next_swiglu = hint.kind == 1;
         const int next_row_bytes = next_fp8 ? hint.in_features : hint.in_features / 2;
-        const LaunchShape next = shape_of(hint.out_features, hint.in_features, next_swiglu, next_fp8);
+        // kind 3: an NVFP4 matrix that will run as a regular K split (qwc_nvfp4_w4a16_split)
+        const LaunchShape next = shape_of(hint.out_features, hint.in_features, next_swiglu, next_fp8, hint.kind == 3);
         if (next.units > 0 &&
             encode_weight_map(&next_map0, hint.packed[0], hint.out_features, next_row_bytes) == cudaSuccess &&
             encode_weight_map(&next_map1, hint.packed[next_swiglu ? 1 : 0], hint.out_features, next_row_bytes) ==
@@ -919,6 +1178,7 @@ cudaError_t launch_streamk(StreamKParams p, const void* packed0, const void* pac
             p.next.out_features = hint.out_features;
             p.next.ctas = next.ctas;
             p.next.units = next.units;
+            p.next.splits = next.splits;
             p.next.stages_in_k = next.stages_in_k;
             p.next.group_blocks = hint.in_features / 64;
             p.next.scales[0] = static_cast<const uint8_t*>(hint.scales[0]);
@@ -930,7 +1190,9 @@ cudaError_t launch_streamk(StreamKParams p, const void* packed0, const void* pac
         return cudaErrorInvalidValue;
     }
     const int n_pad = p.batch <= 16 ? 16 : 32;
-    const Kernel kernel = kernels[(fp8 ? 4 : (swiglu ? 2 : 0)) + (n_pad == 32 ? 1 : 0)];
+    const bool regular = shape.splits > 0;  // no tickets: slices for the consumer, or whole pairs
+    const Kernel kernel =
+        kernels[(regular ? (swiglu ? 8 : 6) : (fp8 ? 4 : (swiglu ? 2 : 0))) + (n_pad == 32 ? 1 : 0)];
     cudaLaunchConfig_t config = {};
     config.gridDim = dim3(shape.ctas);
     config.blockDim = dim3(kThreads);
@@ -952,6 +1214,23 @@ bool aligned16(const void* pointer) { return (reinterpret_cast<uintptr_t>(pointe
 using namespace qwc;
 
 extern "C" size_t qwc_streamk_workspace_bytes(void) { return kWorkspaceBytes; }
+
+// Timeline of the last launch: kMaxCtas x 32 nanosecond stamps (see QWC_STREAMK_TRACE above); returns the
+// number of 64-bit words copied, 0 when the library was built without the trace.
+extern "C" int qwc_streamk_trace(unsigned long long* host, int capacity_words) {
+#ifdef QWC_STREAMK_TRACE
+    const int words = kMaxCtas * kTraceSlots;
+    if (host == nullptr || capacity_words < words ||
+        cudaMemcpyFromSymbol(host, g_trace, sizeof(unsigned long long) * words) != cudaSuccess) {
+        return -1;
+    }
+    return words;
+#else
+    (void)host;
+    (void)capacity_words;
+    return 0;
+#endif
+}
 
 extern "C" int qwc_streamk_workspace_init(void* workspace, cudaStream_t stream) {
     if (workspace == nullptr || !aligned16(workspace)) {
@@ -999,6 +1278,33 @@ extern "C" int qwc_nvfp4_w4a16_staged(const void* packed, const void* scales, co
     p.in_features = in_features;
     p.batch = batch;
     return launch_streamk(p, packed, packed, false, false, workspace, stream);
+}
+
+extern "C" int qwc_nvfp4_split_count(int out_features, int in_features) {
+    if (out_features <= 0 || in_features <= 0 || in_features % 256 != 0) {
+        return 0;
+    }
+    return shape_of(out_features, in_features, false, false, true).splits;
+}
+
+extern "C" int qwc_nvfp4_w4a16_split(const void* packed, const void* scales, const void* staged_input,
+                                     float* partial_sums, int out_features, int in_features, int batch,
+                                     cudaStream_t stream) {
+    if (packed == nullptr || scales == nullptr || staged_input == nullptr || partial_sums == nullptr ||
+        out_features <= 0 || in_features <= 0 || in_features % 256 != 0 || batch <= 0 || batch > 32 ||
+        !aligned16(packed) || !aligned16(scales) || !aligned16(staged_input)) {
+        (void)take_next_projection();
+        return cudaErrorInvalidValue;
+    }
+    StreamKParams p = {};
+    p.scales[0] = p.scales[1] = static_cast<const uint8_t*>(scales);
+    p.x = static_cast<const __half*>(staged_input);
+    p.inverse_scale[0] = p.inverse_scale[1] = 1.0f;
+    p.out_features = out_features;
+    p.in_features = in_features;
+    p.batch = batch;
+    p.split_out = partial_sums;
+    return launch_streamk(p, packed, packed, false, false, nullptr, stream);
 }
 
 extern "C" int qwc_nvfp4_swiglu_w4a16_staged(const void* gate_packed, const void* gate_scales, const void* up_packed,

@@ -163,9 +163,9 @@ __global__ void __launch_bounds__(kThreads, 1) paged_attention_packed_kernel(
     const uint8_t* __restrict__ key_cache, const uint8_t* __restrict__ value_cache,
     const uint32_t* __restrict__ block_tables, const uint32_t* __restrict__ context_lengths,
     const float* __restrict__ key_scales, const float* __restrict__ value_scales,
-    __nv_bfloat16* __restrict__ output, float* __restrict__ partial_stats, __half* __restrict__ partial_out,
-    int rows, int max_blocks, int row_base, int page_size, int gate_stride, int partitions, float softmax_scale,
-    int* status) {
+    __nv_bfloat16* __restrict__ output, __half* __restrict__ staged_output, int padded_rows,
+    float* __restrict__ partial_stats, __half* __restrict__ partial_out, int rows, int max_blocks, int row_base,
+    int page_size, int gate_stride, int partitions, float softmax_scale, int* status) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
     Smem& sm = *reinterpret_cast<Smem*>(smem_raw);
 
@@ -600,7 +600,17 @@ __global__ void __launch_bounds__(kThreads, 1) paged_attention_packed_kernel(
                         uint2 packed;
                         packed.x = *reinterpret_cast<uint32_t*>(&lo);
                         packed.y = *reinterpret_cast<uint32_t*>(&hi);
-                        *reinterpret_cast<uint2*>(op + d) = packed;
+                        if (output != nullptr) {
+                            *reinterpret_cast<uint2*>(op + d) = packed;
+                        }
+                        if (staged_output != nullptr) {
+                            // the same values as f16 in the operand layout of the output projection
+                            const int feature = head * kHeadDim + d;
+                            *reinterpret_cast<uint2*>(staged_output +
+                                                      (static_cast<size_t>(feature >> 3) * padded_rows + row) * 8 +
+                                                      (feature & 7)) =
+                                make_uint2(bf16x2_to_f16x2(packed.x), bf16x2_to_f16x2(packed.y));
+                        }
                     }
                 }
             }
@@ -628,8 +638,8 @@ constexpr int kMergeWarps = 4;
 __global__ void __launch_bounds__(kMergeWarps * 32) reduce_partitions_kernel(
     const float* __restrict__ partial_stats, const __half* __restrict__ partial_out,
     const __nv_bfloat16* __restrict__ query_gate_projection, const uint32_t* __restrict__ context_lengths,
-    __nv_bfloat16* __restrict__ output, int rows, int partitions, int row_base, int gate_stride, int capacity_units,
-    int plan_ctas) {
+    __nv_bfloat16* __restrict__ output, __half* __restrict__ staged_output, int padded_rows, int rows, int partitions,
+    int row_base, int gate_stride, int capacity_units, int plan_ctas) {
     pdl_launch_dependents();  // the output projection may start streaming its weights
     pdl_wait();
     __shared__ float sums[kMergeWarps][kHeadDim];
@@ -743,15 +753,26 @@ __global__ void __launch_bounds__(kMergeWarps * 32) reduce_partitions_kernel(
                                                   acc[2 * i + 1] * inverse * gates[2 * i + 1]);
         packed[i] = *reinterpret_cast<uint32_t*>(&v);
     }
-    *reinterpret_cast<uint4*>(output + (static_cast<size_t>(row) * kQueryHeads + head) * kHeadDim + 8 * lane) =
-        make_uint4(packed[0], packed[1], packed[2], packed[3]);
+    if (output != nullptr) {
+        *reinterpret_cast<uint4*>(output + (static_cast<size_t>(row) * kQueryHeads + head) * kHeadDim + 8 * lane) =
+            make_uint4(packed[0], packed[1], packed[2], packed[3]);
+    }
+    if (staged_output != nullptr) {
+        // the same values as f16 in the operand layout of the output projection: this lane's eight
+        // dims are one K core
+        const int core = head * (kHeadDim / 8) + lane;
+        *reinterpret_cast<uint4*>(staged_output + (static_cast<size_t>(core) * padded_rows + row) * 8) =
+            make_uint4(bf16x2_to_f16x2(packed[0]), bf16x2_to_f16x2(packed[1]), bf16x2_to_f16x2(packed[2]),
+                       bf16x2_to_f16x2(packed[3]));
+    }
 }
 
 cudaError_t launch_attention(const void* query, const void* query_gate_projection, const void* key_cache,
                              const void* value_cache, const void* block_tables, const void* context_lengths,
                              const float* key_scales, const float* value_scales, void* output, void* workspace,
                              size_t workspace_bytes, int rows, int row_base, int max_blocks, int page_size,
-                             int gate_stride, int partitions, float softmax_scale, cudaStream_t stream) {
+                             int gate_stride, int partitions, float softmax_scale, cudaStream_t stream,
+                             void* staged_output = nullptr) {
     if (gate_stride == 0) {
         gate_stride = kQueryHeads * 2 * kHeadDim;
     }
@@ -759,7 +780,8 @@ cudaError_t launch_attention(const void* query, const void* query_gate_projectio
         return cudaErrorInvalidValue;
     }
     if (query == nullptr || key_cache == nullptr || value_cache == nullptr || block_tables == nullptr ||
-        context_lengths == nullptr || output == nullptr || rows <= 0 || rows > kPlanRows || row_base < 0 ||
+        context_lengths == nullptr || (output == nullptr && staged_output == nullptr) ||
+        (staged_output != nullptr && row_base + rows > 32) || rows <= 0 || rows > kPlanRows || row_base < 0 ||
         max_blocks <= 0 || partitions <= 0 || partitions > 65535 || !isfinite(softmax_scale) ||
         softmax_scale <= 0.0f || (page_size != 16 && page_size != 64)) {
         return cudaErrorInvalidValue;
@@ -798,13 +820,14 @@ cudaError_t launch_attention(const void* query, const void* query_gate_projectio
         return cudaErrorInvalidValue;
     }
     const dim3 grid(sms);
+    const int padded_rows = row_base + rows <= 16 ? 16 : 32;  // of the staged output
     if (partitions == 1) {
         return qwc::launch_chained(paged_attention_packed_kernel<false>, dim3(grid), dim3(kThreads), shared, stream, 
             static_cast<const __nv_bfloat16*>(query), static_cast<const __nv_bfloat16*>(query_gate_projection),
             static_cast<const uint8_t*>(key_cache), static_cast<const uint8_t*>(value_cache),
             static_cast<const uint32_t*>(block_tables), static_cast<const uint32_t*>(context_lengths), key_scales,
-            value_scales, static_cast<__nv_bfloat16*>(output), nullptr, nullptr, rows, max_blocks, row_base,
-            page_size, gate_stride, 1, softmax_scale, status);
+            value_scales, static_cast<__nv_bfloat16*>(output), static_cast<__half*>(staged_output), padded_rows,
+            nullptr, nullptr, rows, max_blocks, row_base, page_size, gate_stride, 1, softmax_scale, status);
     }
     const size_t partials = static_cast<size_t>(rows) * kQueryHeads * partitions;
     if (workspace == nullptr || workspace_bytes < partials * kPartialBytes) {
@@ -817,16 +840,17 @@ cudaError_t launch_attention(const void* query, const void* query_gate_projectio
         static_cast<const __nv_bfloat16*>(query), static_cast<const __nv_bfloat16*>(query_gate_projection),
         static_cast<const uint8_t*>(key_cache), static_cast<const uint8_t*>(value_cache),
         static_cast<const uint32_t*>(block_tables), static_cast<const uint32_t*>(context_lengths), key_scales,
-        value_scales, static_cast<__nv_bfloat16*>(output), partial_stats, partial_out, rows, max_blocks, row_base,
-        page_size, gate_stride, partitions, softmax_scale, status);
+        value_scales, static_cast<__nv_bfloat16*>(output), nullptr, padded_rows, partial_stats, partial_out, rows,
+        max_blocks, row_base, page_size, gate_stride, partitions, softmax_scale, status);
     if (launched != cudaSuccess) {
         return launched;
     }
     const int pairs = rows * kQueryHeads;
     return qwc::launch_chained(reduce_partitions_kernel, dim3(pairs), dim3(kMergeWarps * 32), 0, stream, 
         partial_stats, partial_out, static_cast<const __nv_bfloat16*>(query_gate_projection),
-        static_cast<const uint32_t*>(context_lengths), static_cast<__nv_bfloat16*>(output), rows, partitions, row_base,
-        gate_stride, max_blocks * (page_size / kUnitTokens), sms);
+        static_cast<const uint32_t*>(context_lengths), static_cast<__nv_bfloat16*>(output),
+        static_cast<__half*>(staged_output), padded_rows, rows, partitions, row_base, gate_stride,
+        max_blocks * (page_size / kUnitTokens), sms);
 }
 
 // ---- built-in scratch for callers that cannot allocate ------------------------------------
@@ -908,6 +932,20 @@ extern "C" int qwc_paged_attention_packed_fp8_scaled(const void* query, const vo
                                  context_lengths, key_scales, value_scales, output, workspace, workspace_bytes,
                                  rows, row_base, max_blocks, page_size, gate_stride, partitions, softmax_scale,
                                  stream);
+}
+
+extern "C" int qwc_paged_attention_packed_fp8_staged(const void* query, const void* query_gate_projection,
+                                                     const void* key_cache, const void* value_cache,
+                                                     const void* block_tables, const void* context_lengths,
+                                                     const float* key_scales, const float* value_scales,
+                                                     void* output, void* staged_output, void* workspace,
+                                                     size_t workspace_bytes, int rows, int row_base, int max_blocks,
+                                                     int page_size, int gate_stride, int partitions,
+                                                     float softmax_scale, cudaStream_t stream) {
+    return qwc::launch_attention(query, query_gate_projection, key_cache, value_cache, block_tables,
+                                 context_lengths, key_scales, value_scales, output, workspace, workspace_bytes,
+                                 rows, row_base, max_blocks, page_size, gate_stride, partitions, softmax_scale,
+                                 stream, staged_output);
 }
 
 extern "C" int qwc_paged_attention_packed_fp8_noalloc(const void* query, const void* query_gate_projection,

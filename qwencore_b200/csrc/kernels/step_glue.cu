@@ -30,7 +30,7 @@ __device__ __forceinline__ uint8_t to_fp8(float value) {
 __device__ __forceinline__ float sigmoidf_fast(float x) { return 1.0f / (1.0f + __expf(-x)); }
 
 // Sum over the CTA; every thread receives the total.  `scratch` holds one float per warp.
-__device__ __forceinline__ float block_sum(float value, float* scratch) {
+__device__ __forceinline__ float block_sum(float value, float* scratch) {  // scratch: blockDim.x / 32 floats
     value = warp_sum(value);
     const int lane = threadIdx.x & 31;
     const int warp = threadIdx.x >> 5;
@@ -70,8 +70,9 @@ constexpr int kNormMaxPerThread = 10;  // 8 * 256 * 10 = 20480 columns at most
 __global__ void __launch_bounds__(kThreads) rmsnorm_bf16_kernel(const __nv_bfloat16* __restrict__ input,
                                                                 __nv_bfloat16* __restrict__ residual,
                                                                 const __nv_bfloat16* __restrict__ weight,
-                                                                __nv_bfloat16* __restrict__ output, int hidden,
-                                                                float epsilon) {
+                                                                __nv_bfloat16* __restrict__ output,
+                                                                __half* __restrict__ staged, int padded_rows,
+                                                                int hidden, float epsilon) {
     pdl_launch_dependents();  // the projection that follows may start streaming its weights
     __shared__ float scratch[kThreads / 32];
     const size_t base = static_cast<size_t>(blockIdx.x) * hidden;
@@ -135,8 +136,163 @@ __global__ void __launch_bounds__(kThreads) rmsnorm_bf16_kernel(const __nv_bfloa
                 __nv_bfloat162 rounded = __floats2bfloat162_rn(lo, hi);
                 out[j] = *reinterpret_cast<uint32_t*>(&rounded);
             }
-            *reinterpret_cast<uint4*>(output + base + 8 * vec) = make_uint4(out[0], out[1], out[2], out[3]);
+            if (output != nullptr) {
+                *reinterpret_cast<uint4*>(output + base + 8 * vec) = make_uint4(out[0], out[1], out[2], out[3]);
+            }
+            if (staged != nullptr) {
+                // the same bf16 values as f16, where the projection that follows reads its operand:
+                // [hidden / 8][padded rows][8]
+                *reinterpret_cast<uint4*>(staged + (static_cast<size_t>(vec) * padded_rows + blockIdx.x) * 8) =
+                    make_uint4(bf16x2_to_f16x2(out[0]), bf16x2_to_f16x2(out[1]), bf16x2_to_f16x2(out[2]),
+                               bf16x2_to_f16x2(out[3]));
+            }
         }
+    }
+}
+
+// ---- residual RMSNorm that also finishes a K-split projection ------------------------
+// The projection before a residual RMSNorm (mixer output, MLP down: 5120 outputs, too few row tiles
+// for the SMs) runs as a regular K split and leaves fp32 partial rows [slice][batch][hidden]; summing
+// them here costs this kernel nothing it would not wait for anyway (one round trip for its input),
+// and the projection ends with plain stores instead of a reduction between CTAs.  The arithmetic is
+// the unsplit one: x = bf16(sum * scale) is the projection's bf16 output (cuda/nvfp4.cu:209-220),
+// then cuda/rmsnorm.cu:85-149 on x.  Slices are summed in slice order: bit-reproducible.
+constexpr int kSplitNormThreads = 640;
+constexpr int kSplitNormMaxItems = 4;  // float4 items per thread: hidden <= 4 * 4 * 640
+
+__global__ void __launch_bounds__(kSplitNormThreads) rmsnorm_split_kernel(
+    const float* __restrict__ partial_sums, int splits, float scale, __nv_bfloat16* __restrict__ projection,
+    __nv_bfloat16* __restrict__ residual, const __nv_bfloat16* __restrict__ weight,
+    __nv_bfloat16* __restrict__ output, __half* __restrict__ staged, int padded_rows, int hidden, int batch,
+    float epsilon) {
+    pdl_launch_dependents();
+    __shared__ float scratch[kSplitNormThreads / 32];
+    const int token = blockIdx.x;
+    const int items = hidden / 4;
+    uint2 gains[kSplitNormMaxItems];
+#pragma unroll
+    for (int i = 0; i < kSplitNormMaxItems; ++i) {
+        const int item = threadIdx.x + i * kSplitNormThreads;
+        if (item < items) {
+            gains[i] = *reinterpret_cast<const uint2*>(weight + 4 * item);  // static: fetched before the wait
+        }
+    }
+    pdl_wait();
+    const size_t slice_stride = static_cast<size_t>(batch) * hidden;
+    const float* mine = partial_sums + static_cast<size_t>(token) * hidden;
+    float held[kSplitNormMaxItems][4];
+    float sum = 0.0f;
+#pragma unroll
+    for (int i = 0; i < kSplitNormMaxItems; ++i) {
+        const int item = threadIdx.x + i * kSplitNormThreads;
+        if (item < items) {
+            float4 total = __ldcg(reinterpret_cast<const float4*>(mine + 4 * item));
+            uint2 res = make_uint2(0u, 0u);
+            if (residual != nullptr) {
+                res = *reinterpret_cast<const uint2*>(residual + static_cast<size_t>(token) * hidden + 4 * item);
+            }
+            for (int slice = 1; slice < splits; ++slice) {
+                const float4 more = __ldcg(reinterpret_cast<const float4*>(mine + slice * slice_stride + 4 * item));
+                total.x += more.x;
+                total.y += more.y;
+                total.z += more.z;
+                total.w += more.w;
+            }
+            // the projection's own output rounding, then the residual sum's
+            float x[4] = {__bfloat162float(__float2bfloat16(total.x * scale)),
+                          __bfloat162float(__float2bfloat16(total.y * scale)),
+                          __bfloat162float(__float2bfloat16(total.z * scale)),
+                          __bfloat162float(__float2bfloat16(total.w * scale))};
+            if (projection != nullptr) {  // a caller that also wants the projection's own bf16 rows
+                __nv_bfloat162 lo = __floats2bfloat162_rn(x[0], x[1]);
+                __nv_bfloat162 hi = __floats2bfloat162_rn(x[2], x[3]);
+                *reinterpret_cast<uint2*>(projection + static_cast<size_t>(token) * hidden + 4 * item) =
+                    make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
+            }
+            if (residual != nullptr) {
+                const float r[4] = {__uint_as_float(res.x << 16), __uint_as_float(res.x & 0xffff0000u),
+                                    __uint_as_float(res.y << 16), __uint_as_float(res.y & 0xffff0000u)};
+                __nv_bfloat162 lo = __floats2bfloat162_rn(x[0] + r[0], x[1] + r[1]);
+                __nv_bfloat162 hi = __floats2bfloat162_rn(x[2] + r[2], x[3] + r[3]);
+                const uint2 stored = make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
+                *reinterpret_cast<uint2*>(residual + static_cast<size_t>(token) * hidden + 4 * item) = stored;
+                x[0] = __uint_as_float(stored.x << 16);
+                x[1] = __uint_as_float(stored.x & 0xffff0000u);
+                x[2] = __uint_as_float(stored.y << 16);
+                x[3] = __uint_as_float(stored.y & 0xffff0000u);
+            }
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                held[i][j] = x[j];
+                sum = fmaf(x[j], x[j], sum);
+            }
+        }
+    }
+    const float total = block_sum(sum, scratch);
+    const float inverse = rsqrtf(total / static_cast<float>(hidden) + epsilon);
+#pragma unroll
+    for (int i = 0; i < kSplitNormMaxItems; ++i) {
+        const int item = threadIdx.x + i * kSplitNormThreads;
+        if (item < items) {
+            const float g[4] = {__uint_as_float(gains[i].x << 16), __uint_as_float(gains[i].x & 0xffff0000u),
+                                __uint_as_float(gains[i].y << 16), __uint_as_float(gains[i].y & 0xffff0000u)};
+            __nv_bfloat162 lo = __floats2bfloat162_rn(held[i][0] * inverse * (1.0f + g[0]),
+                                                      held[i][1] * inverse * (1.0f + g[1]));
+            __nv_bfloat162 hi = __floats2bfloat162_rn(held[i][2] * inverse * (1.0f + g[2]),
+                                                      held[i][3] * inverse * (1.0f + g[3]));
+            const uint2 out = make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
+            if (output != nullptr) {
+                *reinterpret_cast<uint2*>(output + static_cast<size_t>(token) * hidden + 4 * item) = out;
+            }
+            if (staged != nullptr) {
+                // half of a K core: [hidden / 8][padded rows][8]
+                *reinterpret_cast<uint2*>(staged + (static_cast<size_t>(item >> 1) * padded_rows + token) * 8 +
+                                          (item & 1) * 4) = make_uint2(bf16x2_to_f16x2(out.x), bf16x2_to_f16x2(out.y));
+            }
+        }
+    }
+}
+
+// One output of a projection that ran as a regular K split (qwc_nvfp4_w4a16_split): the slices summed in
+// slice order, scaled and rounded to bf16 as the projection's own epilogue would have done.
+struct SplitSource {
+    const float* sums;  // [slices][batch][width] fp32, or null: the consumer reads bf16 rows instead
+    int slices;
+    int batch;
+    int width;
+    float scale;
+};
+
+__device__ __forceinline__ float split_value(const SplitSource& source, int row, int column) {
+    const size_t stride = static_cast<size_t>(source.batch) * source.width;
+    const float* at = source.sums + static_cast<size_t>(row) * source.width + column;
+    float total = __ldcg(at);
+    for (int slice = 1; slice < source.slices; ++slice) {
+        total += __ldcg(at + slice * stride);
+    }
+    return __bfloat162float(__float2bfloat16(total * source.scale));
+}
+
+// fp32 slices -> the projection's bf16 rows, for consumers that read rows: four outputs per thread.
+__global__ void __launch_bounds__(kThreads) sum_slices_kernel(const SplitSource source, __nv_bfloat16* __restrict__ rows) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const size_t quads = static_cast<size_t>(source.batch) * source.width / 4;
+    const size_t stride = static_cast<size_t>(source.batch) * source.width;
+    for (size_t quad = static_cast<size_t>(blockIdx.x) * kThreads + threadIdx.x; quad < quads;
+         quad += static_cast<size_t>(gridDim.x) * kThreads) {
+        float4 total = __ldcg(reinterpret_cast<const float4*>(source.sums + 4 * quad));
+        for (int slice = 1; slice < source.slices; ++slice) {
+            const float4 more = __ldcg(reinterpret_cast<const float4*>(source.sums + slice * stride + 4 * quad));
+            total.x += more.x;
+            total.y += more.y;
+            total.z += more.z;
+            total.w += more.w;
+        }
+        __nv_bfloat162 lo = __floats2bfloat162_rn(total.x * source.scale, total.y * source.scale);
+        __nv_bfloat162 hi = __floats2bfloat162_rn(total.z * source.scale, total.w * source.scale);
+        *reinterpret_cast<uint2*>(rows + 4 * quad) =
+            make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
     }
 }
 
@@ -185,7 +341,8 @@ __global__ void __launch_bounds__(kDeltaHeadDim) delta_prepare_kernel(
     const __nv_bfloat16* __restrict__ a_log, const __nv_bfloat16* __restrict__ dt_bias,
     float* __restrict__ conv_state, const uint32_t* __restrict__ state_slots, float* __restrict__ query,
     float* __restrict__ key, float* __restrict__ value, float* __restrict__ alpha, float* __restrict__ beta,
-    float* __restrict__ kq, int mixed_stride, int gate_stride, int v_heads, int state_capacity, int* status) {
+    float* __restrict__ kq, int mixed_stride, int gate_stride, int v_heads, int state_capacity, int* status,
+    const SplitSource split, int a_column, int b_column) {
     pdl_launch_dependents();
     __shared__ float scratch[kDeltaHeadDim / 32];
     const int head = blockIdx.x;
@@ -236,14 +393,20 @@ __global__ void __launch_bounds__(kDeltaHeadDim) delta_prepare_kernel(
             operands[i].history[0] = history[0];
             operands[i].history[1] = history[1];
             operands[i].history[2] = history[2];
-            operands[i].current = __bfloat162float(mixed_row[channel[i]]);
+            operands[i].current = split.sums != nullptr ? split_value(split, batch, channel[i])
+                                                        : __bfloat162float(mixed_row[channel[i]]);
         }
     }
     float projected_a = 0.0f, projected_b = 0.0f;
     if (dimension < ratio) {
         const size_t gate_read = static_cast<size_t>(batch) * gate_stride + head * ratio + dimension;
-        projected_a = __bfloat162float(a_projection[gate_read]);
-        projected_b = __bfloat162float(b_projection[gate_read]);
+        if (split.sums != nullptr) {
+            projected_a = split_value(split, batch, a_column + head * ratio + dimension);
+            projected_b = split_value(split, batch, b_column + head * ratio + dimension);
+        } else {
+            projected_a = __bfloat162float(a_projection[gate_read]);
+            projected_b = __bfloat162float(b_projection[gate_read]);
+        }
     }
 
     const float q = conv_finish(operands[0], conv_state + (slot_base + channel[0]) * 3);
@@ -284,7 +447,9 @@ __global__ void __launch_bounds__(kDeltaHeadDim) gated_rmsnorm_kernel(const floa
                                                                       const __nv_bfloat16* __restrict__ gate,
                                                                       const __nv_bfloat16* __restrict__ weight,
                                                                       __nv_bfloat16* __restrict__ output,
-                                                                      float epsilon, int gate_stride, int heads) {
+                                                                      __half* __restrict__ staged, int padded_rows,
+                                                                      float epsilon, int gate_stride, int heads,
+                                                                      const SplitSource split, int gate_column) {
     pdl_launch_dependents();  // the projection that follows may start streaming its weights
     __shared__ float scratch[kDeltaHeadDim / 32];
     const int head = blockIdx.x;
@@ -294,14 +459,25 @@ __global__ void __launch_bounds__(kDeltaHeadDim) gated_rmsnorm_kernel(const floa
     pdl_wait();
     const size_t offset = (static_cast<size_t>(batch) * heads + head) * kDeltaHeadDim + dimension;
     const size_t gate_offset = static_cast<size_t>(batch) * gate_stride + head * kDeltaHeadDim + dimension;
-    const float gate_value = __bfloat162float(gate[gate_offset]);  // issued with the input load, used last
+    // issued with the input load, used last
+    const float gate_value = split.sums != nullptr
+                                 ? split_value(split, batch, gate_column + head * kDeltaHeadDim + dimension)
+                                 : __bfloat162float(gate[gate_offset]);
     const float value = __bfloat162float(__float2bfloat16(input[offset]));
     const float sum = block_sum(value * value, scratch);
     const float inverse = rsqrtf(sum / static_cast<float>(kDeltaHeadDim) + epsilon);
     const __nv_bfloat16 normalized = __float2bfloat16(value * inverse);
     const __nv_bfloat16 weighted = __float2bfloat16(gain * __bfloat162float(normalized));
     const float silu = gate_value / (1.0f + __expf(-gate_value));
-    output[offset] = __float2bfloat16(__bfloat162float(weighted) * silu);
+    const __nv_bfloat16 result = __float2bfloat16(__bfloat162float(weighted) * silu);
+    if (output != nullptr) {
+        output[offset] = result;
+    }
+    if (staged != nullptr) {
+        const int feature = head * kDeltaHeadDim + dimension;
+        staged[(static_cast<size_t>(feature >> 3) * padded_rows + batch) * 8 + (feature & 7)] =
+            __float2half_rn(fminf(fmaxf(__bfloat162float(result), -65504.0f), 65504.0f));
+    }
 }
 
 // ---- QK-norm + partial RoPE + FP8 page write (cuda/attention_prepare.cu:52-143) -----
@@ -463,16 +639,51 @@ extern "C" int qwc_fp8_embedding_gather(const void* table, const void* row_scale
         static_cast<const uint32_t*>(token_ids), static_cast<__nv_bfloat16*>(output), cols, vocab);
 }
 
-extern "C" int qwc_rmsnorm_bf16(const void* input, void* residual, const void* weight, void* output, int batch,
-                                int hidden, float epsilon, cudaStream_t stream) {
-    if (input == nullptr || weight == nullptr || output == nullptr || batch <= 0 || batch > kMaxStepRows ||
-        hidden <= 0 || hidden % 256 != 0 || hidden > 8 * kThreads * kNormMaxPerThread || !isfinite(epsilon) ||
-        epsilon <= 0.0f) {
+extern "C" int qwc_rmsnorm_bf16_staged(const void* input, void* residual, const void* weight, void* output,
+                                       void* staged_output, int batch, int hidden, float epsilon,
+                                       cudaStream_t stream) {
+    if (input == nullptr || weight == nullptr || (output == nullptr && staged_output == nullptr) || batch <= 0 ||
+        batch > kMaxStepRows || (staged_output != nullptr && batch > 32) || hidden <= 0 || hidden % 256 != 0 ||
+        hidden > 8 * kThreads * kNormMaxPerThread || !isfinite(epsilon) || epsilon <= 0.0f) {
         return cudaErrorInvalidValue;
     }
-    return qwc::launch_chained(rmsnorm_bf16_kernel, dim3(batch), dim3(kThreads), 0, stream, 
+    return qwc::launch_chained(rmsnorm_bf16_kernel, dim3(batch), dim3(kThreads), 0, stream,
         static_cast<const __nv_bfloat16*>(input), static_cast<__nv_bfloat16*>(residual),
-        static_cast<const __nv_bfloat16*>(weight), static_cast<__nv_bfloat16*>(output), hidden, epsilon);
+        static_cast<const __nv_bfloat16*>(weight), static_cast<__nv_bfloat16*>(output),
+        static_cast<__half*>(staged_output), batch <= 16 ? 16 : 32, hidden, epsilon);
+}
+
+extern "C" int qwc_rmsnorm_bf16_split_staged(const float* partial_sums, int splits, float weight_global_scale,
+                                             void* projection_output, void* residual, const void* weight,
+                                             void* output, void* staged_output, int batch, int hidden,
+                                             float epsilon, cudaStream_t stream) {
+    if (partial_sums == nullptr || splits <= 0 || splits > 64 || !(weight_global_scale > 0.0f) || weight == nullptr ||
+        (output == nullptr && staged_output == nullptr) || batch <= 0 || batch > 32 || hidden <= 0 ||
+        hidden % 256 != 0 || hidden > 4 * kSplitNormThreads * kSplitNormMaxItems || !isfinite(epsilon) ||
+        epsilon <= 0.0f || (reinterpret_cast<uintptr_t>(partial_sums) & 15) != 0) {
+        return cudaErrorInvalidValue;
+    }
+    return qwc::launch_chained(rmsnorm_split_kernel, dim3(batch), dim3(kSplitNormThreads), 0, stream, partial_sums,
+                               splits, 1.0f / weight_global_scale, static_cast<__nv_bfloat16*>(projection_output),
+                               static_cast<__nv_bfloat16*>(residual),
+                               static_cast<const __nv_bfloat16*>(weight), static_cast<__nv_bfloat16*>(output),
+                               static_cast<__half*>(staged_output), batch <= 16 ? 16 : 32, hidden, batch, epsilon);
+}
+
+extern "C" int qwc_rmsnorm_bf16(const void* input, void* residual, const void* weight, void* output, int batch,
+                                int hidden, float epsilon, cudaStream_t stream) {
+    if (output == nullptr) {
+        return cudaErrorInvalidValue;
+    }
+    return qwc_rmsnorm_bf16_staged(input, residual, weight, output, nullptr, batch, hidden, epsilon, stream);
+}
+
+namespace {
+int launch_delta_prepare(const void* mixed_qkv, const void* a_projection, const void* b_projection,
+                         const void* conv_weight, const void* a_log, const void* dt_bias, void* conv_state,
+                         const void* state_slots, void* query, void* key, void* value, void* alpha, void* beta,
+                         void* kq, int state_capacity, int batch, int mixed_stride, int gate_stride,
+                         const qwc::SplitSource& split, int a_column, int b_column, cudaStream_t stream);
 }
 
 extern "C" int qwc_delta_prepare_decode(const void* mixed_qkv, const void* a_projection, const void* b_projection,
@@ -480,6 +691,41 @@ extern "C" int qwc_delta_prepare_decode(const void* mixed_qkv, const void* a_pro
                                         void* conv_state, const void* state_slots, void* query, void* key,
                                         void* value, void* alpha, void* beta, void* kq, int state_capacity,
                                         int batch, int mixed_stride, int gate_stride, cudaStream_t stream) {
+    if (mixed_qkv == nullptr || a_projection == nullptr || b_projection == nullptr) {
+        return cudaErrorInvalidValue;
+    }
+    return launch_delta_prepare(mixed_qkv, a_projection, b_projection, conv_weight, a_log, dt_bias, conv_state,
+                                state_slots, query, key, value, alpha, beta, kq, state_capacity, batch, mixed_stride,
+                                gate_stride, qwc::SplitSource{}, 0, 0, stream);
+}
+
+// The same on a mixer in-projection that ran as a regular K split: fp32 slices
+// [slices][batch][width] instead of bf16 rows; a and b are columns of the same rows.
+extern "C" int qwc_delta_prepare_decode_split(const float* partial_sums, int slices, int width,
+                                              float weight_global_scale, int a_column, int b_column,
+                                              const void* conv_weight, const void* a_log, const void* dt_bias,
+                                              void* conv_state, const void* state_slots, void* query, void* key,
+                                              void* value, void* alpha, void* beta, void* kq, int state_capacity,
+                                              int batch, cudaStream_t stream) {
+    const int v_heads = current_shape().delta_value_heads;
+    const int channels = 2 * kDeltaKeyHeads * kDeltaHeadDim + v_heads * kDeltaHeadDim;
+    if (partial_sums == nullptr || slices <= 0 || slices > 64 || width < channels || a_column < channels ||
+        b_column < channels || a_column + v_heads > width || b_column + v_heads > width ||
+        !(weight_global_scale > 0.0f)) {
+        return cudaErrorInvalidValue;
+    }
+    const qwc::SplitSource split = {partial_sums, slices, batch, width, 1.0f / weight_global_scale};
+    return launch_delta_prepare(partial_sums, partial_sums, partial_sums, conv_weight, a_log, dt_bias, conv_state,
+                                state_slots, query, key, value, alpha, beta, kq, state_capacity, batch, width, width,
+                                split, a_column, b_column, stream);
+}
+
+namespace {
+int launch_delta_prepare(const void* mixed_qkv, const void* a_projection, const void* b_projection,
+                         const void* conv_weight, const void* a_log, const void* dt_bias, void* conv_state,
+                         const void* state_slots, void* query, void* key, void* value, void* alpha, void* beta,
+                         void* kq, int state_capacity, int batch, int mixed_stride, int gate_stride,
+                         const qwc::SplitSource& split, int a_column, int b_column, cudaStream_t stream) {
     const int v_heads = current_shape().delta_value_heads;
     const int channels = 2 * kDeltaKeyHeads * kDeltaHeadDim + v_heads * kDeltaHeadDim;
     if (mixed_qkv == nullptr || a_projection == nullptr || b_projection == nullptr || conv_weight == nullptr ||
@@ -501,20 +747,66 @@ extern "C" int qwc_delta_prepare_decode(const void* mixed_qkv, const void* a_pro
         static_cast<float*>(conv_state), static_cast<const uint32_t*>(state_slots), static_cast<float*>(query),
         static_cast<float*>(key), static_cast<float*>(value), static_cast<float*>(alpha),
         static_cast<float*>(beta), static_cast<float*>(kq), mixed_stride, gate_stride, v_heads, state_capacity,
-        status);
+        status, split, a_column, b_column);
+}
+}  // namespace
+
+extern "C" int qwc_delta_gated_rmsnorm_staged(const float* input, const void* gate, const void* weight, void* output,
+                                              void* staged_output, int batch, float epsilon, int gate_stride,
+                                              cudaStream_t stream) {
+    const int heads = current_shape().delta_value_heads;
+    if (input == nullptr || gate == nullptr || weight == nullptr || (output == nullptr && staged_output == nullptr) ||
+        batch <= 0 || batch > kMaxStepRows || (staged_output != nullptr && batch > 32) || !isfinite(epsilon) ||
+        epsilon <= 0.0f || gate_stride < heads * kDeltaHeadDim) {
+        return cudaErrorInvalidValue;
+    }
+    const dim3 grid(heads, batch);
+    return qwc::launch_chained(gated_rmsnorm_kernel, dim3(grid), dim3(kDeltaHeadDim), 0, stream,
+        input, static_cast<const __nv_bfloat16*>(gate), static_cast<const __nv_bfloat16*>(weight),
+        static_cast<__nv_bfloat16*>(output), static_cast<__half*>(staged_output), batch <= 16 ? 16 : 32, epsilon,
+        gate_stride, heads, SplitSource{}, 0);
+}
+
+// The same with the gate rows taken from a K-split in-projection (column `gate_column` of its rows).
+extern "C" int qwc_delta_gated_rmsnorm_split(const float* input, const float* partial_sums, int slices, int width,
+                                             float weight_global_scale, int gate_column, const void* weight,
+                                             void* output, void* staged_output, int batch, float epsilon,
+                                             cudaStream_t stream) {
+    const int heads = current_shape().delta_value_heads;
+    if (input == nullptr || partial_sums == nullptr || slices <= 0 || slices > 64 || gate_column < 0 ||
+        gate_column + heads * kDeltaHeadDim > width || !(weight_global_scale > 0.0f) || weight == nullptr ||
+        (output == nullptr && staged_output == nullptr) || batch <= 0 || batch > 32 || !isfinite(epsilon) ||
+        epsilon <= 0.0f) {
+        return cudaErrorInvalidValue;
+    }
+    const SplitSource split = {partial_sums, slices, batch, width, 1.0f / weight_global_scale};
+    const dim3 grid(heads, batch);
+    return qwc::launch_chained(gated_rmsnorm_kernel, dim3(grid), dim3(kDeltaHeadDim), 0, stream,
+        input, static_cast<const __nv_bfloat16*>(nullptr), static_cast<const __nv_bfloat16*>(weight),
+        static_cast<__nv_bfloat16*>(output), static_cast<__half*>(staged_output), batch <= 16 ? 16 : 32, epsilon,
+        width, heads, split, gate_column);
+}
+
+// fp32 slices of a K-split projection -> its bf16 rows [batch][width] (for consumers that read rows).
+extern "C" int qwc_nvfp4_sum_slices(const float* partial_sums, int slices, float weight_global_scale, void* rows,
+                                    int batch, int width, cudaStream_t stream) {
+    if (partial_sums == nullptr || slices <= 0 || slices > 64 || !(weight_global_scale > 0.0f) || rows == nullptr ||
+        batch <= 0 || batch > 32 || width <= 0 || width % 4 != 0 ||
+        (reinterpret_cast<uintptr_t>(partial_sums) & 15) != 0 || (reinterpret_cast<uintptr_t>(rows) & 7) != 0) {
+        return cudaErrorInvalidValue;
+    }
+    const SplitSource split = {partial_sums, slices, batch, width, 1.0f / weight_global_scale};
+    const int blocks = static_cast<int>((static_cast<size_t>(batch) * width / 4 + kThreads - 1) / kThreads);
+    return qwc::launch_chained(sum_slices_kernel, dim3(blocks < 592 ? blocks : 592), dim3(kThreads), 0, stream, split,
+                               static_cast<__nv_bfloat16*>(rows));
 }
 
 extern "C" int qwc_delta_gated_rmsnorm(const float* input, const void* gate, const void* weight, void* output,
                                        int batch, float epsilon, int gate_stride, cudaStream_t stream) {
-    const int heads = current_shape().delta_value_heads;
-    if (input == nullptr || gate == nullptr || weight == nullptr || output == nullptr || batch <= 0 ||
-        batch > kMaxStepRows || !isfinite(epsilon) || epsilon <= 0.0f || gate_stride < heads * kDeltaHeadDim) {
+    if (output == nullptr) {
         return cudaErrorInvalidValue;
     }
-    const dim3 grid(heads, batch);
-    return qwc::launch_chained(gated_rmsnorm_kernel, dim3(grid), dim3(kDeltaHeadDim), 0, stream, 
-        input, static_cast<const __nv_bfloat16*>(gate), static_cast<const __nv_bfloat16*>(weight),
-        static_cast<__nv_bfloat16*>(output), epsilon, gate_stride, heads);
+    return qwc_delta_gated_rmsnorm_staged(input, gate, weight, output, nullptr, batch, epsilon, gate_stride, stream);
 }
 
 extern "C" int qwc_prepare_attention_decode_fp8_scaled(

@@ -45,7 +45,7 @@ class EngineConfig(ctypes.Structure):
                 ("intermediate", c_int), ("vocab", c_int), ("delta_value_heads", c_int), ("kv_page_size", c_int),
                 ("max_batch", c_int), ("max_context", c_int), ("kv_pool_blocks", c_int), ("state_slots", c_int),
                 ("seed", ctypes.c_ulonglong), ("split_rank", c_int), ("split_size", c_int), ("use_graph", c_int),
-                ("attention_partitions", c_int)]
+                ("attention_partitions", c_int), ("write_logits", c_int)]
 
 
 class StepTraffic(ctypes.Structure):

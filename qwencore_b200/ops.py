@@ -137,6 +137,27 @@ def fp8_lm_head_staged(weights, row_scales, staged_x, logits, sampled, status_ou
               "qwc_fp8_lm_head_staged")
 
 
+def split_count(linear: Linear) -> int:
+    return int(abi.lib.qwc_nvfp4_split_count(linear.out_features, linear.in_features))
+
+
+def w4a16_split(linear: Linear, staged_x, partial_sums, batch: int) -> None:
+    """fp32 partial rows [split_count][batch][out] of a regular K split; the consumer sums them."""
+    assert partial_sums.dtype == torch.float32
+    assert partial_sums.numel() >= split_count(linear) * batch * linear.out_features
+    abi.check(abi.lib.qwc_nvfp4_w4a16_split(_p(linear.packed), _p(linear.scales), _p(staged_x), _p(partial_sums),
+                                            linear.out_features, linear.in_features, batch, _stream()),
+              "qwc_nvfp4_w4a16_split")
+
+
+def rmsnorm_split_staged(partial_sums, splits: int, weight_global_scale: float, projection_out, residual, weight,
+                         out, staged_out, batch: int, hidden: int, epsilon: float = 1e-6) -> None:
+    abi.check(abi.lib.qwc_rmsnorm_bf16_split_staged(_p(partial_sums), splits, weight_global_scale,
+                                                    _p(projection_out), _p(residual), _p(weight), _p(out),
+                                                    _p(staged_out), batch, hidden, epsilon, _stream()),
+              "qwc_rmsnorm_bf16_split_staged")
+
+
 def prefetch_next(first: Linear, second: Linear | None = None) -> None:
     """Names the projection that follows the next one launched from this thread (a hint for L2):
     one matrix, or the gate and up matrices of a SwiGLU pair."""

@@ -23,7 +23,7 @@ def engine_module(cuda, built_library):
 
 def small_config(engine_module, **overrides):
     values = dict(num_layers=4, vocab=8192, max_batch=4, max_context=512, kv_pool_blocks=160, state_slots=6,
-                  seed=7, use_graph=1)
+                  seed=7, use_graph=1, write_logits=1)
     values.update(overrides)
     return engine_module.default_config(**values)
 
@@ -261,7 +261,7 @@ def test_phase_timeline_covers_every_phase(cuda, engine_module):
         phases = dict((label, (ms, launches)) for label, ms, launches in engine.profile_step(2))
         for label in ("pack", "embed", "norm", "gemm.la_in", "delta.prepare", "delta.scan", "delta.norm",
                       "gemm.la_out", "gemm.attn_qkv", "attn.prepare", "attn.decode", "gemm.attn_out",
-                      "gemm.mlp_gate_up", "gemm.mlp_down", "lm_head", "sample"):
+                      "gemm.mlp_gate_up", "gemm.mlp_down", "lm_head"):  # sampling is part of the head
             assert label in phases, label
         assert phases["gemm.mlp_down"][1] == 4 and phases["delta.scan"][1] == 3 and phases["attn.decode"][1] == 1
         traffic = engine.traffic(2, 83)

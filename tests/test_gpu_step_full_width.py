@@ -37,7 +37,7 @@ def test_benchmark_width_step_matches_oracle_layer_by_layer(cuda, built_library,
     steps = 2
     blocks = int(np.sum((contexts + steps + PAGE - 1) // PAGE)) + 8
     config = engine_module.default_config(num_layers=LAYERS, max_batch=ROWS, max_context=32768 + 64,
-                                          kv_pool_blocks=blocks, state_slots=ROWS + 1, seed=11)
+                                          kv_pool_blocks=blocks, state_slots=ROWS + 1, seed=11, write_logits=1)
     assert config.vocab == 151936 and config.hidden == 5120 and config.intermediate == 17408
     engine = engine_module.Engine(config)
     try:

@@ -31,6 +31,13 @@ def workspace(cuda, ops):
     return ops.new_streamk_workspace()
 
 
+def assert_staged_holds(staged_values, bf16_values, what):
+    """The staged copy is the bf16 value converted to f16: identical where f16 has the bits (|v| >= 2^-14,
+    saturated at 65504), rounded to the f16 subnormal grid (2^-24) below that."""
+    want = np.clip(np.asarray(bf16_values, dtype=np.float32), -65504.0, 65504.0).astype(np.float16)
+    assert np.array_equal(np.asarray(staged_values).view(np.uint16), want.view(np.uint16)), what
+
+
 def staged_input(torch, ops, x_bits, batch, features):
     staged = ops.new_staged(batch, features)
     ops.stage_activations(dev(torch, x_bits), staged, batch, features)
@@ -82,7 +89,7 @@ def test_staged_w4a16_matches_cpu_for_all_supported_batches(cuda, ops, workspace
         tolerance = 0.035 + np.abs(want) * 0.012  # tests/nvfp4.rs:68
         assert np.all(np.abs(got - want) <= tolerance), f"batch {batch}"
         # the staged copy holds the same bf16 values, as f16
-        assert np.array_equal(got_staged.astype(np.float32), got), f"staged output, batch {batch}"
+        assert_staged_holds(got_staged, got, f"staged output, batch {batch}")
 
         want_up = oracle.gemv_w4a16(up_packed, scales, 4.0, x, OUT, IN, batch)
         want_fused = oracle.swiglu_combine(want, want_up)
@@ -94,7 +101,7 @@ def test_staged_w4a16_matches_cpu_for_all_supported_batches(cuda, ops, workspace
         got_fused = synth.bf16_value(host(fused))
         tolerance = 0.075 + np.abs(want_fused) * 0.025  # tests/nvfp4.rs:103
         assert np.all(np.abs(got_fused - want_fused) <= tolerance), f"fused batch {batch}"
-        assert np.array_equal(host(ops.unstage(fused_staged, batch, OUT)).astype(np.float32), got_fused)
+        assert_staged_holds(host(ops.unstage(fused_staged, batch, OUT)), got_fused, f"fused staged, batch {batch}")
 
 
 # (out, in, batches, what the shape exercises on 148 SMs)
@@ -121,7 +128,7 @@ def test_staged_w4a16_model_shapes_within_rms_bound(cuda, ops, workspace, out_fe
                                              in_features, batch)
         got = synth.bf16_value(got_bits)
         assert_rms_close(got, oracle.bf16_round(want), f"staged gemv {out_features}x{in_features} b{batch}")
-        assert np.array_equal(got_staged.astype(np.float32), np.clip(got, -65504, 65504))
+        assert_staged_holds(got_staged, got, f"staged output {out_features}x{in_features} b{batch}")
 
 
 def test_staged_w4a16_is_bit_reproducible_and_agrees_with_the_bf16_entry(cuda, ops, workspace):
@@ -252,3 +259,116 @@ def test_staged_entries_reject_bad_arguments(cuda, ops, workspace):
     assert abi.lib.qwc_staged_activation_bytes(17, 256) == 256 // 8 * 32 * 8 * 2
     assert abi.lib.qwc_staged_activation_bytes(33, 256) == 0
     torch.cuda.synchronize()
+
+
+# ---------------------------------------------------------------------------------------
+# Regular K split with the sum left to the consumer
+# ---------------------------------------------------------------------------------------
+
+def run_split(torch, ops, packed, swizzled, x_bits, out_features, in_features, batch):
+    linear = ops.Linear(dev(torch, packed), dev(torch, swizzled), 1.0, out_features, in_features)
+    slices = ops.split_count(linear)
+    sums = torch.zeros((slices, batch, out_features), dtype=torch.float32, device="cuda")
+    ops.w4a16_split(linear, staged_input(torch, ops, x_bits, batch, in_features), sums, batch)
+    return linear, slices, sums
+
+
+@pytest.mark.parametrize("out_features,in_features,batch", [(5120, 4096, 32), (5120, 17408, 7), (5120, 6144, 1)])
+def test_split_projection_finished_by_the_residual_norm(cuda, ops, out_features, in_features, batch):
+    """Mixer output / MLP down: fp32 slices, summed by the residual RMSNorm (cuda/rmsnorm.cu:85-149 on the
+    projection's bf16 values, cuda/nvfp4.cu:209-220)."""
+    torch = cuda
+    packed, scales, swizzled = synth.nvfp4_matrix(5, f"split{in_features}", out_features, in_features)
+    x = synth.normal_bf16(5, "split.x", (batch, in_features))
+    residual = synth.normal_bf16(5, "split.res", (batch, out_features), std=20.0)
+    weight = synth.normal_bf16(5, "split.w", (out_features,), std=0.02)
+    global_scale = 4.0
+    want_rows = oracle.bf16_from_f32(oracle.gemv_w4a16(packed, scales, global_scale, x, out_features, in_features, batch))
+    want_residual = residual.copy()
+    want_normed = oracle.rmsnorm_bf16(want_rows, want_residual, weight, batch, out_features)
+
+    linear, slices, sums = run_split(torch, ops, packed, swizzled, x, out_features, in_features, batch)
+    assert slices >= 2
+    rows = bf16_out(torch, batch, out_features)
+    res_dev = dev(torch, residual)
+    normed = bf16_out(torch, batch, out_features)
+    staged = ops.new_staged(batch, out_features)
+    ops.rmsnorm_split_staged(sums, slices, global_scale, rows, res_dev, dev(torch, weight), normed, staged, batch,
+                             out_features)
+    torch.cuda.synchronize()
+    got_rows = synth.bf16_value(host(rows))
+    assert_rms_close(got_rows, synth.bf16_value(want_rows), "split projection rows")
+    assert_rms_close(synth.bf16_value(host(res_dev)), synth.bf16_value(want_residual), "residual after the split sum")
+    assert_rms_close(synth.bf16_value(host(normed)), synth.bf16_value(want_normed), "norm after the split sum")
+    assert_staged_holds(host(ops.unstage(staged, batch, out_features)), synth.bf16_value(host(normed)), "staged norm")
+    # given its own projection rows the norm is the unsplit kernel bit for bit
+    again_res = dev(torch, residual)
+    again = bf16_out(torch, batch, out_features)
+    ops.rmsnorm_bf16(rows, again_res, dev(torch, weight), again, batch, out_features)
+    torch.cuda.synchronize()
+    assert np.array_equal(host(again_res), host(res_dev)) and np.array_equal(host(again), host(normed))
+    # the slices are bit-reproducible
+    _, _, sums_again = run_split(torch, ops, packed, swizzled, x, out_features, in_features, batch)
+    torch.cuda.synchronize()
+    assert torch.equal(sums, sums_again)
+
+
+def test_split_slices_summed_to_rows_and_by_the_deltanet_consumers(cuda, ops):
+    """The mixer in-projection as a K split: the plain sum to bf16 rows against the oracle, and the
+    DeltaNet prepare step and gated RMSNorm reading the slices give the bits they give on those rows."""
+    from qwencore_b200 import abi
+
+    torch = cuda
+    v_heads, batch, hidden = 32, 9, 5120
+    before = abi.get_shape()
+    abi.configure(v_heads, 16)
+    try:
+        channels = 2 * 16 * 128 + v_heads * 128
+        z_offset, a_offset = channels, channels + v_heads * 128
+        b_offset = a_offset + v_heads
+        width = b_offset + v_heads  # 12352
+        packed, scales, swizzled = synth.nvfp4_matrix(6, "inproj", width, hidden)
+        x = synth.normal_bf16(6, "inproj.x", (batch, hidden), std=0.05)
+        linear, slices, sums = run_split(torch, ops, packed, swizzled, x, width, hidden, batch)
+        assert slices == 3
+        rows = bf16_out(torch, batch, width)
+        abi.check(abi.lib.qwc_nvfp4_sum_slices(sums.data_ptr(), slices, 1.0, rows.data_ptr(), batch, width,
+                                               torch.cuda.current_stream().cuda_stream), "qwc_nvfp4_sum_slices")
+        torch.cuda.synchronize()
+        want = oracle.gemv_w4a16(packed, scales, 1.0, x, width, hidden, batch)
+        assert_rms_close(synth.bf16_value(host(rows)), oracle.bf16_round(want), "summed in-projection rows")
+
+        capacity = batch + 2
+        slots = dev(torch, np.random.default_rng(0).permutation(capacity)[:batch].astype(np.uint32))
+        conv_weight = dev(torch, synth.normal_bf16(6, "conv", (channels * 4,), std=0.3))
+        a_log = dev(torch, synth.normal_bf16(6, "alog", (v_heads,), std=0.5))
+        dt_bias = dev(torch, synth.normal_bf16(6, "dt", (v_heads,), std=0.5))
+        conv_init = np.random.default_rng(1).uniform(-1, 1, (capacity, channels, 3)).astype(np.float32)
+        out_norm = dev(torch, synth.normal_bf16(6, "onorm", (128,), std=0.05))
+        delta_out = dev(torch, np.random.default_rng(2).standard_normal((batch, v_heads, 128)).astype(np.float32))
+        stream = torch.cuda.current_stream().cuda_stream
+        results = []
+        for split in (False, True):
+            conv_state = dev(torch, conv_init)
+            outs = [torch.zeros(n, dtype=torch.float32, device="cuda")
+                    for n in (batch * 2048, batch * 2048, batch * v_heads * 128, batch * v_heads, batch * v_heads,
+                              batch * 16)]
+            normed = bf16_out(torch, batch, v_heads * 128)
+            if split:
+                abi.check(abi.lib.qwc_delta_prepare_decode_split(
+                    sums.data_ptr(), slices, width, 1.0, a_offset, b_offset, conv_weight.data_ptr(), a_log.data_ptr(),
+                    dt_bias.data_ptr(), conv_state.data_ptr(), slots.data_ptr(), *[o.data_ptr() for o in outs],
+                    capacity, batch, stream), "qwc_delta_prepare_decode_split")
+                abi.check(abi.lib.qwc_delta_gated_rmsnorm_split(
+                    delta_out.data_ptr(), sums.data_ptr(), slices, width, 1.0, z_offset, out_norm.data_ptr(),
+                    normed.data_ptr(), None, batch, 1e-6, stream), "qwc_delta_gated_rmsnorm_split")
+            else:
+                ops.delta_prepare_decode(rows, a_offset, b_offset, conv_weight, a_log, dt_bias, conv_state, slots,
+                                         *outs, capacity, batch, width)
+                ops.delta_gated_rmsnorm(delta_out, rows, z_offset, out_norm, normed, batch, width)
+            torch.cuda.synchronize()
+            results.append([host(conv_state)] + [host(o) for o in outs] + [host(normed)])
+        for on_rows, on_slices in zip(*results):
+            assert np.array_equal(on_rows.view(np.uint8), on_slices.view(np.uint8))
+    finally:
+        abi.configure(*before)
