@@ -79,7 +79,8 @@ constexpr int kAccumulatorBuffers = 2;
 constexpr int kTileColumns = kAccumulatorColumn + 32 * kAccumulatorBuffers;
 static_assert(kTiles * kTileColumns <= kTmemColumns, "tensor memory budget");
 static_assert(kTileStageBytes % 1024 == 0, "swizzled boxes start on 1 KiB boundaries");
-constexpr int kStashWarpFloats = kTiles * 16 * 32;  // what an epilogue warp holds of a tile pair: 4 KiB
+constexpr int kStashPitch = 33;  // floats per column of a warp's stash: a lane reads a whole column without bank conflicts
+constexpr int kStashWarpFloats = kTiles * 16 * kStashPitch + 64;  // a tile pair's accumulators, and 64 row scales
 constexpr int kStashBytes = 8 * kStashWarpFloats * 4;
 constexpr int kSmemBytes =
     kWeightStages * kTiles * kTileStageBytes + kXStages * kXStageBytes + kStashBytes + 1024;
@@ -158,6 +159,10 @@ __device__ __forceinline__ void trace_stamp(int slot) {
 #define QWC_TRACE_LANE0(slot)
 #endif
 
+// Where the stores of the epilogue's rehearsal go (see the kernel): a line per lane of every epilogue
+// warp, so that the rehearsals of different warps do not queue for the same line; nobody reads it.
+__device__ float g_rehearsal_sink[kMaxCtas * kEpilogueWarps * 32];
+
 struct Barriers {
     uint64_t w_full[kWeightStages];
     uint64_t w_empty[kWeightStages];
@@ -235,11 +240,15 @@ __device__ __forceinline__ int ticket_take(int* ticket) {
     return taken;
 }
 
+// A look that orders nothing (polled in a loop: an acquire per look would be a fence per look) ...
 __device__ __forceinline__ int ticket_look(const int* ticket) {
     int count;
-    asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(count) : "l"(ticket) : "memory");
+    asm volatile("ld.relaxed.gpu.global.s32 %0, [%1];" : "=r"(count) : "l"(ticket) : "memory");
     return count;
 }
+
+// ... and the acquire that follows the look that found everybody in.
+__device__ __forceinline__ void ticket_acquire() { asm volatile("fence.acq_rel.gpu;" ::: "memory"); }
 
 __device__ __forceinline__ bool better_candidate(float value, uint32_t index, float best, uint32_t best_index) {
     return value > best || (value == best && index < best_index);
@@ -282,7 +291,7 @@ __device__ __forceinline__ void sum_pieces_to_stash(const float* partials, int u
 #pragma unroll
                 for (int i = 0; i < kWidth; ++i) {
                     const int flat = base + i;  // tile * kCols + column
-                    piece[j][i] = owner == own ? stash[flat * 32 + lane]
+                    piece[j][i] = owner == own ? stash[flat * kStashPitch + lane]
                                                : __ldcg(theirs + ((flat / kCols) * 16 + flat % kCols) * 32);
                 }
             }
@@ -297,7 +306,7 @@ __device__ __forceinline__ void sum_pieces_to_stash(const float* partials, int u
         }
 #pragma unroll
         for (int i = 0; i < kWidth; ++i) {
-            stash[(base + i) * 32 + lane] = total[i];
+            stash[(base + i) * kStashPitch + lane] = total[i];
         }
     }
 }
@@ -722,37 +731,48 @@ __global__ void __launch_bounds__(kThreads, 1)
         uint32_t best_index = UINT32_MAX;
         const bool sampling = kFp8 && p.candidate_values != nullptr;
         float* stash = stash_base + e * kStashWarpFloats + lane;
-        pdl_wait();
-        if (e == 0) {
-            QWC_TRACE_LANE0(23);
-        }
         bool ok = tmem_ok;
 
-        // Scales the finished tile pair in the stash, combines (SwiGLU), rounds and stores.
-        auto finalize = [&](int pair) {
+        // Scales the finished tile pair in the stash, combines (SwiGLU), rounds and stores the activation
+        // rows below `batch`.  batch == 0 is the rehearsal (below): every instruction runs, for every
+        // row, but the stores go to a sink and nothing is sampled.
+        auto finalize = [&](int pair, int batch) {
+            const bool rehearsal = batch == 0;
+            const int rows_stored = rehearsal ? kPad : batch;
+            float* const sink = g_rehearsal_sink + (cta * kEpilogueWarps + e) * 32;
+            __nv_bfloat16* const y = rehearsal ? reinterpret_cast<__nv_bfloat16*>(sink) : p.y;
+            __half* const y_staged = rehearsal ? reinterpret_cast<__half*>(sink) : p.y_staged;
+            float* const y_f32 = rehearsal ? sink : p.y_f32;
+            const size_t row_pitch = rehearsal ? 0 : static_cast<size_t>(p.out_features);
+            const size_t staged_pitch = rehearsal ? 0 : static_cast<size_t>(kPad) * 8;
 #pragma unroll 1
             for (int c0 = 0; c0 < kCols; c0 += 8) {
                 float v0[8], v1[8];
 #pragma unroll
                 for (int i = 0; i < 8; ++i) {
-                    v0[i] = stash[(c0 + i) * 32];
-                    v1[i] = stash[(kCols + c0 + i) * 32];
+                    v0[i] = stash[(c0 + i) * kStashPitch];
+                    v1[i] = stash[(kCols + c0 + i) * kStashPitch];
                 }
                 if (kSwiglu) {
                     const int row = pair * kTileRows + quarter * 32 + lane;
                     if (row < p.out_features) {
+                        const size_t column = rehearsal ? lane : row;
 #pragma unroll
                         for (int i = 0; i < 8; ++i) {
                             const int token = first_token + c0 + i;
-                            if (token < p.batch) {
+                            if (token < rows_stored) {
                                 const float gate = v0[i] * p.inverse_scale[0];
                                 const float up = v1[i] * p.inverse_scale[1];
-                                const __nv_bfloat16 rounded = __float2bfloat16(gate / (1.0f + __expf(-gate)) * up);
+                                // (the fast division: an IEEE one leaves the fast path for every gate below
+                                // -88, where the exponential is infinite, and costs microseconds at the very
+                                // end of the launch; the two differ by two units in the last place of fp32)
+                                const __nv_bfloat16 rounded =
+                                    __float2bfloat16(__fdividef(gate, 1.0f + __expf(-gate)) * up);
                                 if (p.y != nullptr) {
-                                    p.y[static_cast<size_t>(token) * p.out_features + row] = rounded;
+                                    y[token * row_pitch + column] = rounded;
                                 }
                                 if (p.y_staged != nullptr) {
-                                    p.y_staged[(static_cast<size_t>(row >> 3) * kPad + token) * 8 + (row & 7)] =
+                                    y_staged[(column >> 3) * staged_pitch + token * 8 + (column & 7)] =
                                         __float2half_rn(fminf(fmaxf(__bfloat162float(rounded), -65504.0f), 65504.0f));
                                 }
                             }
@@ -764,40 +784,23 @@ __global__ void __launch_bounds__(kThreads, 1)
                 for (int t = 0; t < kTiles; ++t) {
                     const int row = (pair * kTiles + t) * kTileRows + quarter * 32 + lane;
                     const bool inside = row < p.out_features;
+                    const size_t column = rehearsal ? lane : row;
                     const float row_scale = kFp8 ? (inside ? p.row_scales[row] : 0.0f) : p.inverse_scale[0];
 #pragma unroll
                     for (int i = 0; i < 8; ++i) {
                         const int token = first_token + c0 + i;
                         const float value = (t == 0 ? v0[i] : v1[i]) * row_scale;
                         if (kFp8) {
-                            if (inside && token < p.batch && p.y_f32 != nullptr) {
-                                p.y_f32[static_cast<size_t>(token) * p.out_features + row] = value;
+                            if (inside && token < rows_stored && p.y_f32 != nullptr) {
+                                y_f32[token * row_pitch + column] = value;
                             }
-                            if (sampling) {
-                                // best of this warp's 32 rows for this activation row; lane c0 + i keeps it
-                                float candidate = inside ? value : -INFINITY;
-                                uint32_t index = inside ? static_cast<uint32_t>(row) : UINT32_MAX;
-#pragma unroll
-                                for (int offset = 16; offset > 0; offset >>= 1) {
-                                    const float other = __shfl_xor_sync(0xffffffffu, candidate, offset);
-                                    const uint32_t other_index = __shfl_xor_sync(0xffffffffu, index, offset);
-                                    if (better_candidate(other, other_index, candidate, index)) {
-                                        candidate = other;
-                                        index = other_index;
-                                    }
-                                }
-                                if (lane == c0 + i && better_candidate(candidate, index, best_value, best_index)) {
-                                    best_value = candidate;
-                                    best_index = index;
-                                }
-                            }
-                        } else if (inside && token < p.batch) {
+                        } else if (inside && token < rows_stored) {
                             const __nv_bfloat16 rounded = __float2bfloat16(value);
                             if (p.y != nullptr) {
-                                p.y[static_cast<size_t>(token) * p.out_features + row] = rounded;
+                                y[token * row_pitch + column] = rounded;
                             }
                             if (p.y_staged != nullptr) {
-                                p.y_staged[(static_cast<size_t>(row >> 3) * kPad + token) * 8 + (row & 7)] =
+                                y_staged[(column >> 3) * staged_pitch + token * 8 + (column & 7)] =
                                     __float2half_rn(fminf(fmaxf(__bfloat162float(rounded), -65504.0f), 65504.0f));
                             }
                         }
@@ -805,6 +808,78 @@ __global__ void __launch_bounds__(kThreads, 1)
                 }
             }
         };
+        // Greedy sampling without logits: the best (logit, row) of the tile pair in the stash for every
+        // activation row this warp holds.  A lane takes one column of the stash (lanes below kCols: tile 0,
+        // the next kCols lanes: tile 1) and walks down its 32 rows - no exchange between lanes but the
+        // row scales, which every lane fetches for its own row and leaves in shared memory.
+        auto sample_pair = [&](int pair, bool rehearsal) {
+            float* scales = stash - lane + kTiles * 16 * kStashPitch;  // [tile][row of this quarter]
+#pragma unroll
+            for (int t = 0; t < kTiles; ++t) {
+                const int row = (pair * kTiles + t) * kTileRows + quarter * 32 + lane;
+                // a row past the vocabulary can never win: its logit is -inf whatever the accumulator holds
+                scales[t * 32 + lane] = row < p.out_features ? p.row_scales[row] : NAN;
+            }
+            __syncwarp();
+            const int t = lane / kCols;
+            float candidate = -INFINITY;
+            uint32_t index = UINT32_MAX;
+            if (t < kTiles) {
+                const float* column = stash - lane + lane * kStashPitch;  // (t * kCols + lane % kCols) == lane
+                const uint32_t row0 = static_cast<uint32_t>((pair * kTiles + t) * kTileRows + quarter * 32);
+#pragma unroll 8
+                for (int r = 0; r < 32; ++r) {
+                    const float scale = scales[t * 32 + r];
+                    const float value = scale == scale ? column[r] * scale : -INFINITY;
+                    if (value > candidate) {  // rows ascend: a later equal value never replaces an earlier one
+                        candidate = value;
+                        index = row0 + r;
+                    }
+                }
+            }
+            // the two tiles' winners of a column meet in the lane that keeps the column's running best
+            const float other = __shfl_down_sync(0xffffffffu, candidate, kCols);
+            const uint32_t other_index = __shfl_down_sync(0xffffffffu, index, kCols);
+            if (better_candidate(other, other_index, candidate, index)) {
+                candidate = other;
+                index = other_index;
+            }
+            if (!rehearsal && lane < kCols && better_candidate(candidate, index, best_value, best_index)) {
+                best_value = candidate;
+                best_index = index;
+            }
+            __syncwarp();
+        };
+        // A slice of a regular K split: fp32 rows [slice][batch][N] for the consumer to sum, this lane's two
+        // rows (batch == 0: the rehearsal, as above).
+        auto store_slice = [&](int pair, int batch) {
+            const bool rehearsal = batch == 0;
+            const int slice = kSplitOut ? cta - pair * p.splits : 0;
+            const int rows_stored = rehearsal ? kPad : batch;
+            float* const out = rehearsal ? g_rehearsal_sink + (cta * kEpilogueWarps + e) * 32
+                                         : p.split_out + static_cast<size_t>(slice) * p.batch * p.out_features;
+            const size_t row_pitch = rehearsal ? 0 : static_cast<size_t>(p.out_features);
+#pragma unroll
+            for (int t = 0; t < kTiles; ++t) {
+                const int row = (pair * kTiles + t) * kTileRows + quarter * 32 + lane;
+                if (row < p.out_features) {
+                    const size_t column = rehearsal ? lane : row;
+#pragma unroll
+                    for (int i = 0; i < kCols; ++i) {
+                        const int token = first_token + i;
+                        if (token < rows_stored) {
+                            out[token * row_pitch + column] = stash[(t * kCols + i) * kStashPitch];
+                        }
+                    }
+                }
+            }
+        };
+        // Rehearsal.  What this warp runs at the very end of the launch - after the last MMA, with every
+        // SM waiting for it - it has not run before, so its instructions would come from L2 one cache
+        // line at a time.  It has nothing to do until the first accumulators are complete: it walks
+        // through the same code once now, its stores aimed at a sink, and finds it in the instruction cache
+        // later (measured on the K-split in-projection: accumulators read -> slice stored 1.6 -> 0.6 us).
+        // (It is the first pass of the segment loop below, so that it is the same code, not a copy.)
         // `count` pieces in the fixed order; `own`: this CTA when its piece lies in the stash, else -1
         const auto sum_to_stash = [&](int pair, int first_cta, int last_cta, int count, int own) {
             if (count <= 2) {
@@ -816,8 +891,9 @@ __global__ void __launch_bounds__(kThreads, 1)
             }
         };
         int u = u_begin;
-        int segment = 0;
-        while (u < u_end && ok) {
+        int segment = -1;  // -1: the rehearsal
+        while (segment < 0 || (u < u_end && ok)) {
+            const bool rehearsal = segment < 0;
             const int pair = u / S;
             const int s0 = u - pair * S;
             const int s1 = min(S, s0 + (u_end - u));
@@ -827,121 +903,135 @@ __global__ void __launch_bounds__(kThreads, 1)
             const int first_cta = ticketed ? share_owner(p.units, pair * S, ctas) : cta;
             const int last_cta = ticketed ? share_owner(p.units, pair * S + S - 1, ctas) : cta;
             int* ticket = p.tickets + pair * kEpilogueWarps + e;
-            // The first piece of a pair is what its CTA ends its share with, so it usually arrives last:
-            // its owner looks at the ticket while it waits for its own accumulators (the epilogue warps
-            // have nothing else to do), and once all the others are in, it parks their sum in the stash.
-            // The end of the launch is then one TMEM read, one addition and the stores.
-            const bool may_look = ticketed && s0 == 0 && u + (s1 - s0) == u_end;
+            int limit = p.batch;       // activation rows that are stored
+            bool complete = false;     // the pair is finished here: scale, combine, store
+            bool slice = false;        // the segment is a slice for the consumer to sum
             bool parked = false;
-            if (may_look) {
-                const long long start = clock64();
-                while (!mbar_test(&bars.d_ready[acc], (segment >> 1) & 1)) {
-                    int count = 0;
-                    if (lane == 0) {
-                        count = ticket_look(ticket);  // an L2 round trip: this loop polls gently
-                    }
-                    count = __shfl_sync(0xffffffffu, count, 0);
-                    if (count == last_cta - first_cta) {
-                        sum_to_stash(pair, first_cta, last_cta, count, -1);
-                        parked = true;
-                        break;
-                    }
-                    if (clock64() - start > 40000000ll || *reinterpret_cast<volatile int*>(&bars.failed) != 0) {
-                        break;  // the bounded wait below gives the verdict
-                    }
-                }
-            }
-            ok = sk_wait(&bars.d_ready[acc], (segment >> 1) & 1, &bars, p.status);
-            ok = __all_sync(0xffffffffu, ok);
-            if (!ok) {
-                break;
-            }
-            if (e == 0 && segment < 4) {
-                QWC_TRACE_LANE0(8 + 3 * segment);  // accumulators of the segment complete
-            }
-            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            // tensor memory -> stash (added to the parked sum of the other pieces when there is one)
-#pragma unroll
-            for (int t = 0; t < kTiles; ++t) {
-#pragma unroll
-                for (int c0 = 0; c0 < kCols; c0 += 8) {
-                    uint32_t r[8];
-                    tmem_load8_issue(lane_address + t * kTileColumns + acc * 32 + c0, r);
-                    tmem_load_wait();
-#pragma unroll
-                    for (int i = 0; i < 8; ++i) {
-                        float* slot = stash + (t * kCols + c0 + i) * 32;
-                        *slot = parked ? *slot + __uint_as_float(r[i]) : __uint_as_float(r[i]);
+            if (rehearsal) {
+                limit = 0;  // the stores go to a sink
+                asm volatile("" : "+r"(limit));  // opaque: one copy of the code below serves both passes
+                slice = kSplitOut && p.split_out != nullptr;
+                complete = !slice;
+            } else {
+                // The first piece of a pair is what its CTA ends its share with, so it usually arrives
+                // last: its owner looks at the ticket while it waits for its own accumulators (the epilogue
+                // warps have nothing else to do), and once all the others are in, it parks their sum in
+                // the stash.  The end of the launch is then one TMEM read, one addition and the stores.
+                const bool may_look = ticketed && s0 == 0 && u + (s1 - s0) == u_end;
+                if (may_look) {
+                    const long long start = clock64();
+                    while (!mbar_test(&bars.d_ready[acc], (segment >> 1) & 1)) {
+                        int count = 0;
+                        if (lane == 0) {
+                            count = ticket_look(ticket);  // an L2 round trip
+                        }
+                        count = __shfl_sync(0xffffffffu, count, 0);
+                        if (count == last_cta - first_cta) {
+                            ticket_acquire();
+                            __syncwarp();
+                            sum_to_stash(pair, first_cta, last_cta, count, -1);
+                            parked = true;
+                            break;
+                        }
+                        if (clock64() - start > 40000000ll || *reinterpret_cast<volatile int*>(&bars.failed) != 0) {
+                            break;  // the bounded wait below gives the verdict
+                        }
+                        __nanosleep(400);  // the look is not urgent and must not crowd the memory pipeline
                     }
                 }
-            }
-            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-            __syncwarp();
-            if (lane == 0) {
-                mbar_arrive(&bars.d_free[acc]);
-            }
-            if (e == 0 && segment < 4) {
-                QWC_TRACE_LANE0(9 + 3 * segment);  // accumulators read
-            }
-            bool complete = whole || parked;
-            if (kSplitOut && p.split_out == nullptr) {
-                complete = true;  // one CTA per tile pair: nothing to sum
-            } else if (kSplitOut) {
-                // the consumer sums the slices: fp32 rows [slice][batch][N], this lane's two rows
-                const int slice = cta - pair * p.splits;
+                ok = sk_wait(&bars.d_ready[acc], (segment >> 1) & 1, &bars, p.status);
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) {
+                    break;
+                }
+                if (e == 0) {
+                    QWC_TRACE_LANE0(8 + 3 * min(segment, 3));  // accumulators of the segment complete
+                }
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                // tensor memory -> stash (added to the parked sum of the other pieces when there is one)
 #pragma unroll
                 for (int t = 0; t < kTiles; ++t) {
-                    const int row = (pair * kTiles + t) * kTileRows + quarter * 32 + lane;
-                    if (row < p.out_features) {
 #pragma unroll
-                        for (int i = 0; i < kCols; ++i) {
-                            const int token = first_token + i;
-                            if (token < p.batch) {
-                                p.split_out[(static_cast<size_t>(slice) * p.batch + token) * p.out_features + row] =
-                                    stash[(t * kCols + i) * 32];
-                            }
+                    for (int c0 = 0; c0 < kCols; c0 += 8) {
+                        uint32_t r[8];
+                        tmem_load8_issue(lane_address + t * kTileColumns + acc * 32 + c0, r);
+                        tmem_load_wait();
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) {
+                            float* slot = stash + (t * kCols + c0 + i) * kStashPitch;
+                            *slot = parked ? *slot + __uint_as_float(r[i]) : __uint_as_float(r[i]);
                         }
                     }
                 }
-            } else if (parked) {
+                asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+                __syncwarp();
                 if (lane == 0) {
-                    *ticket = 0;  // everybody else arrived long ago: the tickets go back
+                    mbar_arrive(&bars.d_free[acc]);
                 }
-            } else if (!whole) {
-                // A piece of the pair's K range: the partial goes to this CTA's slot (0: the share starts
-                // with it, 1: the share ends with it), then a ticket.  Tickets are per (pair, epilogue
-                // warp): a warp never has to wait for the other warps of its CTA.
-                const int slot = u == u_begin ? 0 : 1;
-                float* mine = p.partials + (static_cast<size_t>(cta * 2 + slot) * kEpilogueWarps + e) * kPartialWarpFloats + lane;
-#pragma unroll
-                for (int i = 0; i < kCols; ++i) {
-                    mine[i * 32] = stash[i * 32];
-                    mine[(16 + i) * 32] = stash[(kCols + i) * 32];
+                if (e == 0) {
+                    QWC_TRACE_LANE0(9 + 3 * min(segment, 3));  // accumulators read
                 }
-                __syncwarp();  // every lane's stores are ordered before the ticket that lane 0 takes
-                int taken = 0;
-                if (lane == 0) {
-                    taken = ticket_take(ticket);
-                }
-                taken = __shfl_sync(0xffffffffu, taken, 0);
-                if (taken == last_cta - first_cta) {
-                    // the last piece to arrive sums all of them, in the fixed order
+                complete = whole || parked;
+                if (kSplitOut) {
+                    slice = p.split_out != nullptr;
+                    complete = !slice;  // one CTA per tile pair: nothing to sum
+                } else if (parked) {
                     if (lane == 0) {
-                        *ticket = 0;  // ready for the next launch
+                        *ticket = 0;  // everybody else arrived long ago: the tickets go back
                     }
-                    sum_to_stash(pair, first_cta, last_cta, last_cta - first_cta + 1, cta);
-                    complete = true;
+                } else if (!whole) {
+                    // A piece of the pair's K range: the partial goes to this CTA's slot (0: the share
+                    // starts with it, 1: the share ends with it), then a ticket.  Tickets are per (pair,
+                    // epilogue warp): a warp never has to wait for the other warps of its CTA.
+                    const int slot = u == u_begin ? 0 : 1;
+                    float* mine =
+                        p.partials + (static_cast<size_t>(cta * 2 + slot) * kEpilogueWarps + e) * kPartialWarpFloats + lane;
+#pragma unroll
+                    for (int i = 0; i < kCols; ++i) {
+                        mine[i * 32] = stash[i * kStashPitch];
+                        mine[(16 + i) * 32] = stash[(kCols + i) * kStashPitch];
+                    }
+                    __syncwarp();  // every lane's stores are ordered before the ticket that lane 0 takes
+                    int taken = 0;
+                    if (lane == 0) {
+                        taken = ticket_take(ticket);
+                    }
+                    taken = __shfl_sync(0xffffffffu, taken, 0);
+                    if (taken == last_cta - first_cta) {
+                        // the last piece to arrive sums all of them, in the fixed order
+                        if (lane == 0) {
+                            *ticket = 0;  // ready for the next launch
+                        }
+                        sum_to_stash(pair, first_cta, last_cta, last_cta - first_cta + 1, cta);
+                        complete = true;
+                    }
                 }
+            }
+            if (slice) {
+                store_slice(pair, limit);
             }
             if (complete) {
                 __syncwarp();
-                finalize(pair);
+                if (sampling) {
+                    sample_pair(pair, rehearsal);
+                }
+                if (!sampling || p.y_f32 != nullptr) {
+                    finalize(pair, limit);
+                }
             }
-            if (e == 0 && segment < 4) {
-                QWC_TRACE_LANE0(10 + 3 * segment);  // segment stored (partial or final)
+            if (rehearsal) {
+                pdl_wait();  // from here on the warp touches what earlier kernels wrote and read
+                if (e == 0) {
+                    QWC_TRACE_LANE0(23);
+                }
+                segment = 0;
+                continue;
+            }
+            if (e == 0) {
+                QWC_TRACE_LANE0(10 + 3 * min(segment, 3));  // segment stored (partial or final); the fourth slot: the last
 #ifdef QWC_STREAMK_TRACE
                 if (lane == 0) {
-                    g_trace[blockIdx.x * kTraceSlots + 24 + segment] =
+                    g_trace[blockIdx.x * kTraceSlots + 24 + min(segment, 3)] =
                         (whole ? 1 : 0) | (parked ? 2 : 0) | (complete ? 4 : 0) | ((last_cta - first_cta + 1) << 8) |
                         (static_cast<unsigned long long>(s1 - s0) << 16);
                 }

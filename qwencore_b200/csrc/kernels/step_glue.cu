@@ -186,17 +186,28 @@ __global__ void __launch_bounds__(kSplitNormThreads) rmsnorm_split_kernel(
     for (int i = 0; i < kSplitNormMaxItems; ++i) {
         const int item = threadIdx.x + i * kSplitNormThreads;
         if (item < items) {
-            float4 total = __ldcg(reinterpret_cast<const float4*>(mine + 4 * item));
             uint2 res = make_uint2(0u, 0u);
             if (residual != nullptr) {
                 res = *reinterpret_cast<const uint2*>(residual + static_cast<size_t>(token) * hidden + 4 * item);
             }
-            for (int slice = 1; slice < splits; ++slice) {
-                const float4 more = __ldcg(reinterpret_cast<const float4*>(mine + slice * slice_stride + 4 * item));
-                total.x += more.x;
-                total.y += more.y;
-                total.z += more.z;
-                total.w += more.w;
+            // eight slices in flight at a time: the sum costs one round trip, not one per slice
+            float4 total = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            for (int first = 0; first < splits; first += 8) {
+                float4 part[8];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    part[j] = __ldcg(reinterpret_cast<const float4*>(mine + min(first + j, splits - 1) * slice_stride +
+                                                                     4 * item));
+                }
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    if (first + j < splits) {
+                        total.x += part[j].x;
+                        total.y += part[j].y;
+                        total.z += part[j].z;
+                        total.w += part[j].w;
+                    }
+                }
             }
             // the projection's own output rounding, then the residual sum's
             float x[4] = {__bfloat162float(__float2bfloat16(total.x * scale)),
@@ -263,12 +274,22 @@ struct SplitSource {
     float scale;
 };
 
+// (The loads of up to four slices are issued together: one round trip, not one per slice.  A slice
+// past the last one reads the last one again and adds nothing.)
 __device__ __forceinline__ float split_value(const SplitSource& source, int row, int column) {
     const size_t stride = static_cast<size_t>(source.batch) * source.width;
     const float* at = source.sums + static_cast<size_t>(row) * source.width + column;
-    float total = __ldcg(at);
-    for (int slice = 1; slice < source.slices; ++slice) {
-        total += __ldcg(at + slice * stride);
+    float total = 0.0f;
+    for (int first = 0; first < source.slices; first += 4) {
+        float part[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            part[j] = __ldcg(at + min(first + j, source.slices - 1) * stride);
+        }
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            total += first + j < source.slices ? part[j] : 0.0f;
+        }
     }
     return __bfloat162float(__float2bfloat16(total * source.scale));
 }
@@ -281,13 +302,22 @@ __global__ void __launch_bounds__(kThreads) sum_slices_kernel(const SplitSource 
     const size_t stride = static_cast<size_t>(source.batch) * source.width;
     for (size_t quad = static_cast<size_t>(blockIdx.x) * kThreads + threadIdx.x; quad < quads;
          quad += static_cast<size_t>(gridDim.x) * kThreads) {
-        float4 total = __ldcg(reinterpret_cast<const float4*>(source.sums + 4 * quad));
-        for (int slice = 1; slice < source.slices; ++slice) {
-            const float4 more = __ldcg(reinterpret_cast<const float4*>(source.sums + slice * stride + 4 * quad));
-            total.x += more.x;
-            total.y += more.y;
-            total.z += more.z;
-            total.w += more.w;
+        float4 total = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        for (int first = 0; first < source.slices; first += 4) {
+            float4 part[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                part[j] = __ldcg(reinterpret_cast<const float4*>(source.sums + min(first + j, source.slices - 1) * stride +
+                                                                 4 * quad));
+            }
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const bool keep = first + j < source.slices;
+                total.x += keep ? part[j].x : 0.0f;
+                total.y += keep ? part[j].y : 0.0f;
+                total.z += keep ? part[j].z : 0.0f;
+                total.w += keep ? part[j].w : 0.0f;
+            }
         }
         __nv_bfloat162 lo = __floats2bfloat162_rn(total.x * source.scale, total.y * source.scale);
         __nv_bfloat162 hi = __floats2bfloat162_rn(total.z * source.scale, total.w * source.scale);

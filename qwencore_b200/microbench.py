@@ -84,7 +84,7 @@ def report(label: str, microseconds: float, nbytes: int) -> dict:
 
 
 def projection(out_features: int, in_features: int, rows: int, swiglu: bool = False, plain: int = 0,
-               hint: bool = False, staged: bool = False) -> dict:
+               hint: bool = False, staged: bool = False, split: bool = False) -> dict:
     matrix_bytes = out_features * in_features // 2 + ops.block_scale_storage_len(out_features, in_features)
     per_launch = matrix_bytes * (2 if swiglu else 1)
     copies = max(2, -(-2 * L2_BYTES // per_launch)) if not plain else 2
@@ -104,6 +104,8 @@ def projection(out_features: int, in_features: int, rows: int, swiglu: bool = Fa
         staged_x = ops.new_staged(rows, in_features)
         ops.stage_activations(x, staged_x, rows, in_features)
         workspace = ops.new_streamk_workspace()
+    if split:  # regular K split: fp32 slices for the consumer to sum
+        sums = torch.zeros((16, rows, out_features), dtype=torch.float32, device="cuda")
 
     def launch():
         index = counter[0] % copies
@@ -115,7 +117,9 @@ def projection(out_features: int, in_features: int, rows: int, swiglu: bool = Fa
                 ops.prefetch_next(linears[2 * after], linears[2 * after + 1])
             else:
                 ops.prefetch_next(linears[after])
-        if staged and swiglu:
+        if split:
+            ops.w4a16_split(linears[index], staged_x, sums, rows)
+        elif staged and swiglu:
             ops.swiglu_w4a16_staged(linears[2 * index], linears[2 * index + 1], staged_x, y, None, rows, workspace)
         elif staged:
             ops.w4a16_staged(linears[index], staged_x, y, None, rows, workspace)
@@ -127,7 +131,8 @@ def projection(out_features: int, in_features: int, rows: int, swiglu: bool = Fa
     microseconds = time_launches(launch, 4 * copies, plain)
     nbytes = (out_features * in_features // 2 + out_features * in_features // 16) * (2 if swiglu else 1)
     nbytes += rows * in_features * 2 + rows * out_features * 2
-    name = ("swiglu" if swiglu else "gemv") + (" staged" if staged else "") + (" +hint" if hint else "")
+    name = ("swiglu" if swiglu else "gemv") + (" split" if split else " staged" if staged else "") + \
+        (" +hint" if hint else "")
     return report(f"{name} N={out_features} K={in_features} M={rows}", microseconds, nbytes)
 
 
@@ -235,7 +240,7 @@ def lm_head(vocab: int, hidden: int, rows: int, plain: int = 0, staged: bool = F
 
 def main(argv=None) -> None:
     parser = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
-    parser.add_argument("kernel", choices=["gemv", "swiglu", "lm_head", "delta", "attention", "projections", "all"])
+    parser.add_argument("kernel", choices=["gemv", "swiglu", "lm_head", "delta", "attention", "projections", "step-projections", "all"])
     parser.add_argument("args", nargs="*")
     parser.add_argument("--partitions", type=int, default=0)
     parser.add_argument("--page", type=int, default=16)
@@ -255,6 +260,16 @@ def main(argv=None) -> None:
                    staged=options.staged)
     elif options.kernel == "lm_head":
         lm_head(int(values[0]), int(values[1]), int(values[2]), plain=options.plain, staged=options.staged)
+    elif options.kernel == "step-projections":
+        # every projection as the decode step runs it on one GPU
+        for rows in (1, 32):
+            projection(12352, 5120, rows, staged=True, split=True)
+            projection(5120, 4096, rows, staged=True, split=True)
+            projection(14336, 5120, rows, staged=True, split=True)
+            projection(5120, 6144, rows, staged=True, split=True)
+            projection(17408, 5120, rows, swiglu=True, staged=True)
+            projection(5120, 17408, rows, staged=True, split=True)
+            lm_head(151936, 5120, rows, staged=True)
     elif options.kernel == "projections":
         for rows in (1, 8, 32):
             projection(34816, 5120, rows, staged=options.staged, hint=options.hint)

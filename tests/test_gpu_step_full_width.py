@@ -66,17 +66,19 @@ def test_benchmark_width_step_matches_oracle_layer_by_layer(cuda, built_library,
 
             # per layer: the mixer's output projection and the residual stream after the MLP.  A bf16
             # output cannot sit closer to the oracle than its own grid (2^-8 relative), and from the
-            # second layer on every input carries the previous layers' grid-level differences: the
-            # bound is on the RMS of the error (2 % of the RMS of the values); the worst single element
-            # is reported and held to a quarter of the RMS (an element of a gated, per-head normalised
-            # DeltaNet output moves by several of its own grid steps when one state code flips).
+            # second layer on every input carries the previous layers' grid-level differences.  The
+            # residual stream - what the next layer and the head read - is held to an RMS error of 1 %
+            # of its RMS and a worst element of 10 %.  A DeltaNet mixer output is a small term of that
+            # stream and the end of a chain that amplifies (L2-normalised q and k, int8 state codes that
+            # flip, a per-head RMSNorm): its RMS error is held to 4 % and its worst element to half of
+            # its RMS; both are printed.
             for layer in range(LAYERS):
-                for which, name in ((0, "mixer_out"), (1, "residual")):
+                for which, name, rms_bound, worst_bound in ((0, "mixer_out", 4e-2, 5e-1), (1, "residual", 1e-2, 1e-1)):
                     worst, rms_error = relative_errors(got_trace[layer, which], want_trace[layer][which])
                     report.append(f"step {step} layer {layer} {name}: max|err|/rms {worst:.4f}, rms err/rms "
                                   f"{rms_error:.5f}")
-                    assert rms_error <= 2e-2, "\n".join(report)
-                    assert worst <= 2.5e-1, "\n".join(report)
+                    assert rms_error <= rms_bound, "\n".join(report)
+                    assert worst <= worst_bound, "\n".join(report)
 
             got_logits = engine.read("logits", 0, np.float32).reshape(ROWS, config.vocab)
             assert np.isfinite(got_logits).all()
