@@ -164,6 +164,19 @@ int qwc_delta_gated_rmsnorm_split(const float* input, const float* partial_sums,
                                   void* staged_output, int batch, float epsilon, qwc_stream stream);
 int qwc_nvfp4_sum_slices(const float* partial_sums, int slices, float weight_global_scale, void* rows, int batch,
                          int width, qwc_stream stream);
+/* The recurrent update in the step's own form: as qwc_delta_decode_int8, but the state slots and the
+ * state tiles are fetched before the kernel waits for its predecessor on the stream (so neither may be
+ * written by the kernels just before it: in a decode step they are not), and - when every head is one
+ * CTA, which qwc_delta_decode_fuses_norm(batch) tells - the gated RMSNorm (qwc_delta_gated_rmsnorm*)
+ * runs in the same CTA: `staged_output` (not NULL) receives its result staged for the output
+ * projection and `out` is left alone.  The gate z is column `gate_column` of the in-projection's rows
+ * of `width` outputs, given as K-split slices (gate_sums, slices, gate_global_scale) or bf16 rows. */
+int qwc_delta_decode_fuses_norm(int batch);
+int qwc_delta_decode_int8_step(void* state, float* state_scales, const void* state_slots, const void* q,
+                               const void* k, const void* v, const void* alpha, const void* beta, const void* kq,
+                               void* out, int state_capacity, int batch, const float* gate_sums, int slices,
+                               float gate_global_scale, const void* gate_rows, int width, int gate_column,
+                               const void* norm_weight, float epsilon, void* staged_output, qwc_stream stream);
 
 /*
  * The FP8 vocabulary head (see qwc_fp8_lm_head_batched) on staged activations, with greedy sampling

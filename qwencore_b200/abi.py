@@ -59,6 +59,9 @@ KERNEL_SYMBOLS = {
     "qwc_delta_prepare_decode_split": (c_int, [P, c_int, c_int, c_float, c_int, c_int] + [P] * 11 + [c_int, c_int, P]),
     "qwc_delta_gated_rmsnorm_split": (c_int, [P, P, c_int, c_int, c_float, c_int, P, P, P, c_int, c_float, P]),
     "qwc_nvfp4_sum_slices": (c_int, [P, c_int, c_float, P, c_int, c_int, P]),
+    "qwc_delta_decode_fuses_norm": (c_int, [c_int]),
+    "qwc_delta_decode_int8_step": (c_int, [P] * 10 + [c_int, c_int, P, c_int, c_float, P, c_int, c_int, P, c_float,
+                                           P, P]),
     "qwc_nvfp4_w4a16_split": (c_int, [P, P, P, P, c_int, c_int, c_int, P]),
     "qwc_rmsnorm_bf16_split_staged": (c_int, [P, c_int, c_float, P, P, P, P, P, c_int, c_int, c_float, P]),
     "qwc_delta_gated_rmsnorm_staged": (c_int, [P, P, P, P, P, c_int, c_float, c_int, P]),

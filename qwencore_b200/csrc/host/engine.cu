@@ -440,11 +440,21 @@ int decode_forward(qwc_engine* e, int batch) {
                                                  e->state_slots, e->dq, e->dk, e->dv, e->dalpha, e->dbeta, e->dkq,
                                                  c.state_slots, batch, e->mixer_width, e->mixer_width, s));
             }
-            if (phase(e, "delta.scan")) {
+            const bool fused_norm = staged && qwc_delta_decode_fuses_norm(batch) != 0;
+            if (staged && phase(e, "delta.scan")) {
+                // slots and state tiles fetched while the prepare step runs; with one CTA per head the
+                // gated norm rides in the same CTA and the staged result goes straight to the out projection
+                QWC_TRY(qwc_delta_decode_int8_step(layer.state, layer.state_scales, e->state_slots, e->dq, e->dk, e->dv,
+                                                   e->dalpha, e->dbeta, e->dkq, e->delta_out, c.state_slots, batch,
+                                                   e->split_sums_wide, in_slices, layer.in_proj.global_scale, nullptr,
+                                                   e->mixer_width, e->z_offset, layer.out_norm, kEps,
+                                                   fused_norm ? e->delta_normed_staged : nullptr, s));
+            } else if (phase(e, "delta.scan")) {
                 QWC_TRY(qwc_delta_decode_int8(layer.state, layer.state_scales, e->state_slots, e->dq, e->dk, e->dv,
                                               e->dalpha, e->dbeta, e->dkq, e->delta_out, c.state_slots, batch, s));
             }
-            if (staged && phase(e, "delta.norm")) {
+            if (fused_norm) {
+            } else if (staged && phase(e, "delta.norm")) {
                 QWC_TRY(qwc_delta_gated_rmsnorm_split(e->delta_out, e->split_sums_wide, in_slices, e->mixer_width,
                                                       layer.in_proj.global_scale, e->z_offset, layer.out_norm, nullptr,
                                                       e->delta_normed_staged, batch, kEps, s));
@@ -1065,7 +1075,7 @@ void qwc_engine_traffic(const qwc_engine* e, int rows, double context_tokens, qw
         if (!l.full) {
             gemv_bytes += static_cast<double>(l.in_proj.weight_bytes() + l.la_out.weight_bytes());
             gemv += 2;
-            kernels += 2 + 3;
+            kernels += 2 + 3 - (e->cfg.split_size == 1 && qwc_delta_decode_fuses_norm(rows) ? 1 : 0);
             // int8 state and fp32 row scales, read and written (delta_net.rs traffic_bytes analogue)
             out->state_bytes += 2.0 * rows * e->v_heads * (kDeltaDim * kDeltaDim + kDeltaDim * 4.0);
         } else {

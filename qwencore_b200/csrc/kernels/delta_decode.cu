@@ -38,13 +38,36 @@ constexpr int kMaxParts = kDim / kPartRows;
 
 __device__ __forceinline__ float2 f2(float a, float b) { return make_float2(a, b); }
 
+// What the fused output stage needs (the gated RMSNorm of cuda/delta_output.cu:20-64 on this CTA's head,
+// staged for the output projection); `staged == nullptr`: no fusion, `out` is written instead.
+struct GatedNorm {
+    const __nv_bfloat16* weight;  // [128]
+    const float* gate_sums;       // the in-projection's K-split slices [slices][batch][width], or null
+    const __nv_bfloat16* gate_rows;  // ... or its bf16 rows with `gate_stride` elements per row
+    int slices;
+    int batch;
+    int width;
+    int gate_column;  // of z within a row
+    float gate_scale;
+    float epsilon;
+    __half* staged;   // [heads * 128 / 8][padded rows][8]
+    int padded_rows;
+};
+
+// `kEarly`: the rows' state slots were fixed when the step was packed and a layer's state is written by
+// nobody but this kernel, so the slot lookup and the copies of the state tile are issued before the
+// wait for the preceding kernel (which produces q, k, v and the gates).  Callers outside a step, who
+// may have written slots or state just before on the same stream, get the conservative order.
+template <bool kEarly>
 __global__ void __launch_bounds__(kThreads, 7) delta_decode_int8_kernel(
     int8_t* __restrict__ state, float* __restrict__ state_scales, const uint32_t* __restrict__ state_slots,
     const float* __restrict__ q, const float* __restrict__ k, const float* __restrict__ v,
     const float* __restrict__ alpha, const float* __restrict__ beta, const float* __restrict__ kq,
-    float* __restrict__ out, int v_heads, int state_capacity, int* status) {
+    float* __restrict__ out, int v_heads, int state_capacity, int* status, const GatedNorm norm) {
     pdl_launch_dependents();
-    pdl_wait();
+    if (!kEarly) {
+        pdl_wait();
+    }
     __shared__ __align__(128) uint8_t tile[kDim * kDim];
     __shared__ __align__(16) float row_scale[kDim];
     __shared__ float out_rows[kDim];
@@ -86,14 +109,20 @@ __global__ void __launch_bounds__(kThreads, 7) delta_decode_int8_kernel(
     if (threadIdx.x == 0) {
         for (int part = 0; part < parts; ++part) {
             const uint32_t bytes = part_rows * kDim;
-            mbar_arrive_expect_tx(&bars[part], bytes + (part == 0 ? rows_here * 8 : 0));
+            mbar_arrive_expect_tx(&bars[part], bytes + (part == 0 ? rows_here * 4 : 0));
             bulk_g2s(tile + part * kPartRows * kDim, S + part * kPartRows * kDim, bytes, &bars[part]);
             if (part == 0) {
                 bulk_g2s(row_scale, scales, rows_here * 4, &bars[0]);
-                bulk_g2s(v_rows, v + (static_cast<size_t>(b) * v_heads + h) * kDim + row_begin, rows_here * 4, &bars[0]);
             }
         }
     }
+    if (kEarly) {
+        pdl_wait();  // q, k, v and the gates come from the preceding kernel
+    }
+    for (int i = threadIdx.x; i < rows_here; i += kThreads) {
+        v_rows[i] = v[(static_cast<size_t>(b) * v_heads + h) * kDim + row_begin + i];
+    }
+    __syncthreads();
 
     const int lane = threadIdx.x & 31;
     const int warp = threadIdx.x >> 5;
@@ -220,9 +249,56 @@ __global__ void __launch_bounds__(kThreads, 7) delta_decode_int8_kernel(
         bulk_s2g(scales, row_scale, rows_here * 4);
         bulk_commit();
     }
-    float* op = out + (static_cast<size_t>(b) * v_heads + h) * kDim + row_begin;
-    for (int i = threadIdx.x; i < rows_here; i += kThreads) {
-        op[i] = out_rows[i];
+    if (norm.staged != nullptr) {
+        // The whole head is here (the launcher fuses only unsplit heads): gated RMSNorm and the staged
+        // store, thread = dimension.  Rounding points as cuda/delta_output.cu:38-64.
+        __shared__ float warp_sums[kThreads / 32];
+        const int dimension = threadIdx.x;
+        const int column = norm.gate_column + h * kDim + dimension;
+        float gate_value;
+        if (norm.gate_sums != nullptr) {
+            const size_t stride = static_cast<size_t>(norm.batch) * norm.width;
+            const float* at = norm.gate_sums + static_cast<size_t>(b) * norm.width + column;
+            float total = 0.0f;
+            for (int first = 0; first < norm.slices; first += 4) {
+                float part[4];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    part[j] = __ldcg(at + min(first + j, norm.slices - 1) * stride);
+                }
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    total += first + j < norm.slices ? part[j] : 0.0f;
+                }
+            }
+            gate_value = __bfloat162float(__float2bfloat16(total * norm.gate_scale));
+        } else {
+            gate_value = __bfloat162float(norm.gate_rows[static_cast<size_t>(b) * norm.width + column]);
+        }
+        const float gain = __bfloat162float(norm.weight[dimension]);
+        const float value = __bfloat162float(__float2bfloat16(out_rows[dimension]));
+        float sum = warp_sum(value * value);
+        if ((threadIdx.x & 31) == 0) {
+            warp_sums[threadIdx.x >> 5] = sum;
+        }
+        __syncthreads();
+        sum = 0.0f;
+        for (int w = 0; w < kThreads / 32; ++w) {
+            sum += warp_sums[w];
+        }
+        const float inverse = rsqrtf(sum / static_cast<float>(kDim) + norm.epsilon);
+        const __nv_bfloat16 normalized = __float2bfloat16(value * inverse);
+        const __nv_bfloat16 weighted = __float2bfloat16(gain * __bfloat162float(normalized));
+        const float silu = gate_value / (1.0f + __expf(-gate_value));
+        const __nv_bfloat16 result = __float2bfloat16(__bfloat162float(weighted) * silu);
+        const int feature = h * kDim + dimension;
+        norm.staged[(static_cast<size_t>(feature >> 3) * norm.padded_rows + b) * 8 + (feature & 7)] =
+            __float2half_rn(fminf(fmaxf(__bfloat162float(result), -65504.0f), 65504.0f));
+    } else {
+        float* op = out + (static_cast<size_t>(b) * v_heads + h) * kDim + row_begin;
+        for (int i = threadIdx.x; i < rows_here; i += kThreads) {
+            op[i] = out_rows[i];
+        }
     }
     if (threadIdx.x == 0) {
         bulk_wait_all_read();
@@ -266,9 +342,65 @@ extern "C" int qwc_delta_decode_int8(void* state, float* state_scales, const voi
         return cudaErrorInvalidValue;
     }
     const dim3 grid(v_heads, batch, qwc::splits_for(batch, v_heads));
-    return qwc::launch_chained(qwc::delta_decode_int8_kernel, dim3(grid), dim3(qwc::kThreads), 0, stream, 
+    return qwc::launch_chained(qwc::delta_decode_int8_kernel<false>, dim3(grid), dim3(qwc::kThreads), 0, stream,
         static_cast<int8_t*>(state), state_scales, static_cast<const uint32_t*>(state_slots),
         static_cast<const float*>(q), static_cast<const float*>(k), static_cast<const float*>(v),
         static_cast<const float*>(alpha), static_cast<const float*>(beta), static_cast<const float*>(kq),
-        static_cast<float*>(out), v_heads, state_capacity, status);
+        static_cast<float*>(out), v_heads, state_capacity, status, qwc::GatedNorm{});
+}
+
+// The step's form of the same update (additive; the decode executor's own): the state slots and the
+// state tiles are fetched while the preceding kernel still runs (see kEarly above), and when every head
+// is one CTA (qwc_delta_decode_fuses_norm) the gated RMSNorm of qwc_delta_gated_rmsnorm_split /
+// _staged runs in the same CTA and the result is stored staged for the output projection; `out` is
+// then not written.  gate: either the in-projection's K-split slices (gate_sums, slices, scale) or its
+// bf16 rows (gate_rows), `width` elements per row, z at column `gate_column`.
+extern "C" int qwc_delta_decode_fuses_norm(int batch) {
+    const int v_heads = qwc::current_shape().delta_value_heads;
+    return batch > 0 && batch <= 32 && qwc::splits_for(batch, v_heads) == 1 ? 1 : 0;
+}
+
+extern "C" int qwc_delta_decode_int8_step(void* state, float* state_scales, const void* state_slots, const void* q,
+                                          const void* k, const void* v, const void* alpha, const void* beta,
+                                          const void* kq, void* out, int state_capacity, int batch,
+                                          const float* gate_sums, int slices, float gate_global_scale,
+                                          const void* gate_rows, int width, int gate_column,
+                                          const void* norm_weight, float epsilon, void* staged_output,
+                                          cudaStream_t stream) {
+    if (state == nullptr || state_scales == nullptr || state_slots == nullptr || q == nullptr || k == nullptr ||
+        v == nullptr || alpha == nullptr || beta == nullptr || kq == nullptr || out == nullptr ||
+        state_capacity < batch || batch <= 0 || batch > qwc::kMaxDecodeBatch) {
+        return cudaErrorInvalidValue;
+    }
+    const int v_heads = qwc::current_shape().delta_value_heads;
+    int* status = qwc::status_ptr();
+    if (status == nullptr) {
+        return cudaErrorInvalidValue;
+    }
+    const int splits = qwc::splits_for(batch, v_heads);
+    qwc::GatedNorm norm = {};
+    if (staged_output != nullptr) {
+        if (splits != 1 || batch > 32 || norm_weight == nullptr || (gate_sums == nullptr && gate_rows == nullptr) ||
+            (gate_sums != nullptr && (slices <= 0 || slices > 64 || !(gate_global_scale > 0.0f))) ||
+            gate_column < 0 || gate_column + v_heads * qwc::kDim > width || !isfinite(epsilon) || epsilon <= 0.0f) {
+            return cudaErrorInvalidValue;
+        }
+        norm.weight = static_cast<const __nv_bfloat16*>(norm_weight);
+        norm.gate_sums = gate_sums;
+        norm.gate_rows = static_cast<const __nv_bfloat16*>(gate_rows);
+        norm.slices = slices;
+        norm.batch = batch;
+        norm.width = width;
+        norm.gate_column = gate_column;
+        norm.gate_scale = gate_sums != nullptr ? 1.0f / gate_global_scale : 1.0f;
+        norm.epsilon = epsilon;
+        norm.staged = static_cast<__half*>(staged_output);
+        norm.padded_rows = batch <= 16 ? 16 : 32;
+    }
+    const dim3 grid(v_heads, batch, splits);
+    return qwc::launch_chained(qwc::delta_decode_int8_kernel<true>, dim3(grid), dim3(qwc::kThreads), 0, stream,
+        static_cast<int8_t*>(state), state_scales, static_cast<const uint32_t*>(state_slots),
+        static_cast<const float*>(q), static_cast<const float*>(k), static_cast<const float*>(v),
+        static_cast<const float*>(alpha), static_cast<const float*>(beta), static_cast<const float*>(kq),
+        static_cast<float*>(out), v_heads, state_capacity, status, norm);
 }

@@ -372,7 +372,7 @@ __global__ void __launch_bounds__(kDeltaHeadDim) delta_prepare_kernel(
     float* __restrict__ conv_state, const uint32_t* __restrict__ state_slots, float* __restrict__ query,
     float* __restrict__ key, float* __restrict__ value, float* __restrict__ alpha, float* __restrict__ beta,
     float* __restrict__ kq, int mixed_stride, int gate_stride, int v_heads, int state_capacity, int* status,
-    const SplitSource split, int a_column, int b_column) {
+    const SplitSource split, int a_column, int b_column, bool early) {
     pdl_launch_dependents();
     __shared__ float scratch[kDeltaHeadDim / 32];
     const int head = blockIdx.x;
@@ -403,7 +403,11 @@ __global__ void __launch_bounds__(kDeltaHeadDim) delta_prepare_kernel(
         log_a = __bfloat162float(a_log[head * ratio + dimension]);
         bias = __bfloat162float(dt_bias[head * ratio + dimension]);
     }
-    pdl_wait();
+    // `early` (the step's own form): the rows' slots were fixed when the step was packed and a layer's conv
+    // history is written by nobody but this kernel, so both are fetched while the in-projection still runs.
+    if (!early) {
+        pdl_wait();
+    }
     const uint32_t slot = state_slots[batch];
     if (slot >= static_cast<uint32_t>(state_capacity)) {
         // a slot beyond the pool: the row's conv history is neither read nor written; the host
@@ -423,6 +427,14 @@ __global__ void __launch_bounds__(kDeltaHeadDim) delta_prepare_kernel(
             operands[i].history[0] = history[0];
             operands[i].history[1] = history[1];
             operands[i].history[2] = history[2];
+        }
+    }
+    if (early) {
+        pdl_wait();  // the in-projection's outputs
+    }
+#pragma unroll
+    for (int i = 0; i < 2 + kMaxValueRatio; ++i) {
+        if (i < 2 + ratio) {
             operands[i].current = split.sums != nullptr ? split_value(split, batch, channel[i])
                                                         : __bfloat162float(mixed_row[channel[i]]);
         }
@@ -713,7 +725,7 @@ int launch_delta_prepare(const void* mixed_qkv, const void* a_projection, const 
                          const void* conv_weight, const void* a_log, const void* dt_bias, void* conv_state,
                          const void* state_slots, void* query, void* key, void* value, void* alpha, void* beta,
                          void* kq, int state_capacity, int batch, int mixed_stride, int gate_stride,
-                         const qwc::SplitSource& split, int a_column, int b_column, cudaStream_t stream);
+                         const qwc::SplitSource& split, int a_column, int b_column, bool early, cudaStream_t stream);
 }
 
 extern "C" int qwc_delta_prepare_decode(const void* mixed_qkv, const void* a_projection, const void* b_projection,
@@ -726,11 +738,14 @@ extern "C" int qwc_delta_prepare_decode(const void* mixed_qkv, const void* a_pro
     }
     return launch_delta_prepare(mixed_qkv, a_projection, b_projection, conv_weight, a_log, dt_bias, conv_state,
                                 state_slots, query, key, value, alpha, beta, kq, state_capacity, batch, mixed_stride,
-                                gate_stride, qwc::SplitSource{}, 0, 0, stream);
+                                gate_stride, qwc::SplitSource{}, 0, 0, false, stream);
 }
 
 // The same on a mixer in-projection that ran as a regular K split: fp32 slices
-// [slices][batch][width] instead of bf16 rows; a and b are columns of the same rows.
+// [slices][batch][width] instead of bf16 rows; a and b are columns of the same rows.  This is the
+// step's own form: it reads state_slots and conv_state before it waits for the preceding kernel, so
+// neither may be written by the kernels that run just before it on the stream (in a decode step the
+// slots are packed at the start and a layer's conv history belongs to this kernel).
 extern "C" int qwc_delta_prepare_decode_split(const float* partial_sums, int slices, int width,
                                               float weight_global_scale, int a_column, int b_column,
                                               const void* conv_weight, const void* a_log, const void* dt_bias,
@@ -747,7 +762,7 @@ extern "C" int qwc_delta_prepare_decode_split(const float* partial_sums, int sli
     const qwc::SplitSource split = {partial_sums, slices, batch, width, 1.0f / weight_global_scale};
     return launch_delta_prepare(partial_sums, partial_sums, partial_sums, conv_weight, a_log, dt_bias, conv_state,
                                 state_slots, query, key, value, alpha, beta, kq, state_capacity, batch, width, width,
-                                split, a_column, b_column, stream);
+                                split, a_column, b_column, true, stream);
 }
 
 namespace {
@@ -755,7 +770,7 @@ int launch_delta_prepare(const void* mixed_qkv, const void* a_projection, const 
                          const void* conv_weight, const void* a_log, const void* dt_bias, void* conv_state,
                          const void* state_slots, void* query, void* key, void* value, void* alpha, void* beta,
                          void* kq, int state_capacity, int batch, int mixed_stride, int gate_stride,
-                         const qwc::SplitSource& split, int a_column, int b_column, cudaStream_t stream) {
+                         const qwc::SplitSource& split, int a_column, int b_column, bool early, cudaStream_t stream) {
     const int v_heads = current_shape().delta_value_heads;
     const int channels = 2 * kDeltaKeyHeads * kDeltaHeadDim + v_heads * kDeltaHeadDim;
     if (mixed_qkv == nullptr || a_projection == nullptr || b_projection == nullptr || conv_weight == nullptr ||
@@ -777,7 +792,7 @@ int launch_delta_prepare(const void* mixed_qkv, const void* a_projection, const 
         static_cast<float*>(conv_state), static_cast<const uint32_t*>(state_slots), static_cast<float*>(query),
         static_cast<float*>(key), static_cast<float*>(value), static_cast<float*>(alpha),
         static_cast<float*>(beta), static_cast<float*>(kq), mixed_stride, gate_stride, v_heads, state_capacity,
-        status, split, a_column, b_column);
+        status, split, a_column, b_column, early);
 }
 }  // namespace
 

@@ -372,3 +372,72 @@ def test_split_slices_summed_to_rows_and_by_the_deltanet_consumers(cuda, ops):
             assert np.array_equal(on_rows.view(np.uint8), on_slices.view(np.uint8))
     finally:
         abi.configure(*before)
+
+
+def test_delta_step_form_with_fused_gated_norm_is_the_two_kernels_bit_for_bit(cuda, ops):
+    """qwc_delta_decode_int8_step: the recurrent update that fetches slots and state tiles before the
+    wait for its predecessor and, with one CTA per head, runs the gated RMSNorm in the same CTA.  It
+    must leave the state, the scales and the staged output of qwc_delta_decode_int8 followed by
+    qwc_delta_gated_rmsnorm_staged, bit for bit (crates/qwc-cuda/cuda/delta_net.cu:177-256,
+    cuda/delta_output.cu:20-64)."""
+    from qwencore_b200 import abi
+
+    torch = cuda
+    v_heads, batch = 32, 32
+    before = abi.get_shape()
+    abi.configure(v_heads, 16)
+    try:
+        assert abi.lib.qwc_delta_decode_fuses_norm(batch) == 1 and abi.lib.qwc_delta_decode_fuses_norm(1) == 0
+        case = synth.delta_case(9, batch, v_heads)
+        width = v_heads * 128 + 64
+        gate_rows = synth.normal_bf16(9, "z", (batch, width))
+        out_norm = dev(torch, synth.normal_bf16(9, "onorm", (128,), std=0.05))
+        stream = torch.cuda.current_stream().cuda_stream
+        inputs = [dev(torch, case[name]) for name in ("slots", "q", "k", "v", "alpha", "beta", "kq")]
+        gate_dev = dev(torch, gate_rows)
+
+        state_a, scales_a = dev(torch, case["state"]), dev(torch, case["scales"])
+        out_a = torch.zeros((batch, v_heads, 128), dtype=torch.float32, device="cuda")
+        ops.delta_decode_slots_packed(state_a, scales_a, *inputs, out_a, case["capacity"], batch)
+        staged_a = ops.new_staged(batch, v_heads * 128)
+        abi.check(abi.lib.qwc_delta_gated_rmsnorm_staged(out_a.data_ptr(), gate_dev.data_ptr() + 2 * 64,
+                                                         out_norm.data_ptr(), None, staged_a.data_ptr(), batch, 1e-6,
+                                                         width, stream), "qwc_delta_gated_rmsnorm_staged")
+
+        state_b, scales_b = dev(torch, case["state"]), dev(torch, case["scales"])
+        out_b = torch.full((batch, v_heads, 128), 7.0, dtype=torch.float32, device="cuda")
+        staged_b = ops.new_staged(batch, v_heads * 128)
+        abi.check(abi.lib.qwc_delta_decode_int8_step(
+            state_b.data_ptr(), scales_b.data_ptr(), *[t.data_ptr() for t in inputs], out_b.data_ptr(),
+            case["capacity"], batch, None, 0, 1.0, gate_dev.data_ptr(), width, 64, out_norm.data_ptr(), 1e-6,
+            staged_b.data_ptr(), stream), "qwc_delta_decode_int8_step")
+        torch.cuda.synchronize()
+        assert torch.equal(state_a, state_b) and torch.equal(scales_a, scales_b)
+        assert torch.equal(staged_a.view(torch.int16), staged_b.view(torch.int16))
+        assert bool((out_b == 7.0).all()), "the fused form leaves `out` alone"
+
+        # without the fusion (and for a batch whose heads are split over CTAs) it is the plain update
+        one = synth.delta_case(10, 1, v_heads)
+        one_inputs = [dev(torch, one[name]) for name in ("slots", "q", "k", "v", "alpha", "beta", "kq")]
+        results = []
+        for step_form in (False, True):
+            state, scales = dev(torch, one["state"]), dev(torch, one["scales"])
+            out = torch.zeros((1, v_heads, 128), dtype=torch.float32, device="cuda")
+            if step_form:
+                abi.check(abi.lib.qwc_delta_decode_int8_step(
+                    state.data_ptr(), scales.data_ptr(), *[t.data_ptr() for t in one_inputs], out.data_ptr(),
+                    one["capacity"], 1, None, 0, 1.0, None, 0, 0, None, 1e-6, None, stream),
+                    "qwc_delta_decode_int8_step")
+            else:
+                ops.delta_decode_slots_packed(state, scales, *one_inputs, out, one["capacity"], 1)
+            torch.cuda.synchronize()
+            results.append((host(state), host(scales), host(out)))
+        for a, b in zip(*results):
+            assert np.array_equal(a.view(np.uint8), b.view(np.uint8))
+        staged = ops.new_staged(1, v_heads * 128)
+        assert abi.lib.qwc_delta_decode_int8_step(
+            state.data_ptr(), scales.data_ptr(), *[t.data_ptr() for t in one_inputs], out.data_ptr(), one["capacity"],
+            1, None, 0, 1.0, gate_dev.data_ptr(), width, 64, out_norm.data_ptr(), 1e-6, staged.data_ptr(),
+            stream) == abi.CUDA_ERROR_INVALID_VALUE
+    finally:
+        abi.configure(*before)
