@@ -23,6 +23,7 @@ batch - no collective on the data path - so `value` is the sum over ranks (weak 
 from __future__ import annotations
 
 import argparse
+import ctypes
 import json
 import os
 import subprocess
@@ -321,9 +322,9 @@ def time_replays(engine, group, stream, steps, rows):
     return begin.elapsed_time(end) * 1e-3
 
 
-def run_latency_mode(args, group, local_rank, single_gpu_ms):
-    """Batch 1 with every projection column-split over all ranks of the launch (one sequence, context
-    2048): milliseconds per step, max over ranks, and the ranks' sampled tokens compared."""
+def time_latency_engine(args, group, local_rank, fused):
+    """One latency-mode engine (fused peer stores, or the library all-gather): ms per step as the max
+    over ranks, every rank's tokens of the warm-up steps, and the traffic model."""
     import torch
 
     from qwencore_b200 import engine as engine_module
@@ -332,30 +333,81 @@ def run_latency_mode(args, group, local_rank, single_gpu_ms):
     steps = max(args.steps, 20)
     blocks = (C1_CONTEXT + steps + args.warmup + 64) // PAGE + 8
     config = engine_module.default_config(max_batch=1, max_context=C1_CONTEXT + 1024, kv_pool_blocks=blocks,
-                                          state_slots=2, seed=3, split_rank=rank, split_size=world)
+                                          state_slots=2, seed=3, split_rank=rank, split_size=world,
+                                          exchange=1 if fused else 0)
     engine = engine_module.Engine(config)
-    unique = [engine_module.nccl_unique_id() if rank == 0 else None]
-    group.dist.broadcast_object_list(unique, src=0, device=torch.device("cuda", local_rank))
-    engine.init_split(unique[0])
+    if fused:
+        engine_module.connect_exchange(engine)
+    else:
+        unique = [engine_module.nccl_unique_id() if rank == 0 else None]
+        group.dist.broadcast_object_list(unique, src=0, device=torch.device("cuda", local_rank))
+        engine.init_split(unique[0])
     cache = engine_module.CacheManager(2, blocks, PAGE)
     cache.admit(1, C1_CONTEXT)
     engine.apply_edits(cache.drain_edits())
     token = np.array([17], dtype=np.uint32)
     slot = np.array([cache.sequence(1)["state_slot"]], dtype=np.uint32)
     produced = []
-    for _ in range(max(args.warmup, 3) + 1):  # eager, capture, replays
+    for index in range(max(args.warmup, 3) + 1):  # eager, capture, replays
         cache.append_token(1)
-        token = engine.decode(slot, token, cache.drain_edits())
+        group.barrier()  # the ranks step together (a consumer waits a second for its peers' words)
+        try:
+            token = engine.decode(slot, token, cache.drain_edits())
+        except Exception as error:
+            detail = (ctypes.c_uint32 * 2)()
+            engine_module.lib.qwc_device_status_detail(detail)
+            engine_module.lib.qwc_device_status_reset()
+            raise RuntimeError(f"{'fused' if fused else 'library'} engine, warm-up step {index}, rank {rank}: {error}; "
+                               f"tag waited for {detail[0]:#x}, found {detail[1]:#x}") from error
         produced.append(float(token[0]))
     stream = torch.cuda.ExternalStream(engine.stream)
     seconds = group.max_over_ranks(time_replays(engine, group, stream, steps, 1))
     tokens_of_ranks = group.gather(produced)
     traffic = engine.traffic(1, float(C1_CONTEXT))
+    # where the step's time goes: one more step launched eagerly with an event between phases (every
+    # rank takes it - the ranks step together); no overlap between kernels, so an upper bound per phase
+    group.barrier()
+    phases = {}
+    for label, ms, launches in engine.profile_step(1):
+        phases[label] = {"ms": round(ms, 4), "launches": launches}
+    status = engine_module.lib.qwc_device_status()
+    # ... and each phase's kernels alone, as a graph replayed back to back (no waits: the words of the
+    # last whole step still carry the current tag; the values are stale, which is why this comes last)
+    graph_phases = {}
+    if fused:
+        group.barrier()
+        for prefix in ("gemm.", "norm", "delta.prepare", "delta.scan", "delta.norm", "attn.", "mlp.combine", "lm_head"):
+            try:
+                phase_ms, launched = engine.time_phases(1, prefix, replays=5)
+            except Exception:
+                continue
+            graph_phases[prefix.rstrip(".")] = {"ms": round(phase_ms, 4), "launches": launched}
+        group.barrier()
     engine.close()
-    ms = seconds / steps * 1e3
+    return seconds / steps * 1e3, produced, tokens_of_ranks, traffic, status, {"eager": phases, "graph": graph_phases}
+
+
+def run_latency_mode(args, group, local_rank, single_gpu_ms):
+    """Batch 1 with every projection column-split over all ranks of the launch (one sequence, context
+    2048): milliseconds per step, max over ranks, and the ranks' sampled tokens compared.  The headline
+    is the fused form (projections store their partial sums into the peers' memory, consumers sum
+    them); the same split with an ncclAllGather after every projection is timed beside it."""
+    world = group.world
+    ms, produced, tokens_of_ranks, traffic, status, phases = time_latency_engine(args, group, local_rank, True)
+    library_ms, _, library_tokens, _, _, _ = time_latency_engine(args, group, local_rank, False)
     return {"ms_per_step": ms, "tok_s": 1e3 / ms, "vs_1gpu": single_gpu_ms / ms, "gpus": world,
+            "exchange": "partial sums stored into every rank's memory by the projection's epilogue (8-byte "
+                        "tagged words over NVLink), summed by the consuming kernel after a bounded wait; no "
+                        "library collective in the step",
             "exchanges_per_step": int(traffic.gemv_launches_per_step + 1),
+            "kernel_launches_per_step": int(traffic.kernel_launches_per_step),
             "weight_bytes_per_rank": traffic.weight_bytes,
+            "device_status": int(status),
+            "phases_eager_ms_per_step": phases["eager"],
+            "phases_graph_ms_per_step": phases["graph"],
+            "library_collective": {"ms_per_step": library_ms, "vs_1gpu": single_gpu_ms / library_ms,
+                                   "what": "same split, ncclAllGather after every projection",
+                                   "ranks_agree_on_tokens": all(t == library_tokens[0] for t in library_tokens)},
             "preflight": {"ranks_agree_on_tokens": all(t == tokens_of_ranks[0] for t in tokens_of_ranks),
                           "steps_compared": len(produced)},
             "workload": f"batch 1, context {C1_CONTEXT}, 64 layers, every projection and the vocabulary head "

@@ -20,6 +20,8 @@
 #include <stddef.h>
 #include <stdint.h>
 
+#include "qwc_exchange.h"
+
 #ifdef __cplusplus
 extern "C" {
 #endif
@@ -51,6 +53,9 @@ void qwc_get_shape(qwc_shape* shape);
  * (see qwc_device_status_reset).  Host call; synchronises the device. */
 int qwc_device_status(void);
 int qwc_device_status_reset(void);
+/* After code 0x106 (a wait for a peer's words gave up): the tag the first such wait looked for and the
+ * tag it found instead (epoch << 10 | exchange number; 0 = never written).  Host-side, synchronising. */
+int qwc_device_status_detail(uint32_t* expected_and_found);
 /* Host-side fault injection: stores `code` in the status word as a bounded wait that gave up
  * would (every kernel that waits then returns at once and skips its stores).  Synchronises. */
 int qwc_device_status_set(int code);
@@ -187,6 +192,59 @@ int qwc_delta_decode_int8_step(void* state, float* state_scales, const void* sta
 int qwc_fp8_lm_head_staged(const void* weights, const void* row_scales, const void* staged_input, void* logits,
                            void* sampled, void* status_out, int batch, int hidden_size, int vocab,
                            void* workspace, qwc_stream stream);
+
+/*
+ * Additive: latency mode.  The weight rows of every projection are split over the ranks of one node
+ * and a single sequence is decoded (batch 1).  Where the reference gathers each projection's output
+ * with ncclAllGather, these entry points fuse the exchange into the kernels on both sides of it:
+ *
+ *  - qwc_nvfp4_w4a16_exchange / qwc_nvfp4_swiglu_w4a16_exchange run this rank's rows as a regular K
+ *    split and store every partial sum into EVERY rank's copy of the row
+ *    ([qwc_nvfp4_exchange_slices(...)][row->width] words of 8 bytes at row->offset of each block):
+ *    columns rank * out_features .. of the row; for the SwiGLU pair the row is [gate | up], each half
+ *    ranks * out_features wide, unscaled and uncombined;
+ *  - the consumers (qwc_rmsnorm_bf16_exchanged, qwc_delta_prepare_decode_exchanged,
+ *    qwc_delta_gated_rmsnorm_exchanged, qwc_nvfp4_sum_exchanged, qwc_swiglu_combine_exchanged) sum
+ *    the slices in slice order, exactly as their one-GPU forms do, after a bounded wait for the words
+ *    of this step (status code 0x106 in the device status word when a peer's words do not come; the
+ *    step's tokens must then be discarded);
+ *  - qwc_fp8_lm_head_exchange scans this rank's vocabulary rows and hands every rank its best
+ *    candidates; the token stored in `sampled` is the same on all ranks (ties to the smaller index;
+ *    `sampled` NULL: the candidates are stored and no token is picked; `logits`, f32 [vocab_local], may
+ *    be NULL and receives this rank's columns only).
+ *
+ * All ranks must issue the same sequence of steps (qwc_exchange_advance first in each) with the same
+ * instance numbers.  Every rank of a row must use the same slice count, which holds when they call
+ * with the same shapes.  One activation row only.
+ */
+int qwc_exchange_advance(void* epoch, qwc_stream stream);
+size_t qwc_exchange_row_bytes(int width);
+size_t qwc_exchange_candidate_bytes(int ranks);
+int qwc_nvfp4_exchange_slices(int out_features, int in_features, int swiglu);
+int qwc_nvfp4_w4a16_exchange(const void* packed, const void* scales, const void* staged_input,
+                             const qwc_exchange_row* row, int out_features, int in_features, qwc_stream stream);
+int qwc_nvfp4_swiglu_w4a16_exchange(const void* gate_packed, const void* gate_scales, const void* up_packed,
+                                    const void* up_scales, const void* staged_input, const qwc_exchange_row* row,
+                                    int out_features, int in_features, qwc_stream stream);
+int qwc_rmsnorm_bf16_exchanged(const qwc_exchange_row* row, int slices, float weight_global_scale,
+                               void* projection_output, void* residual, const void* weight, void* output,
+                               void* staged_output, int hidden, float epsilon, qwc_stream stream);
+int qwc_delta_prepare_decode_exchanged(const qwc_exchange_row* row, int slices, float weight_global_scale,
+                                       int a_column, int b_column, const void* conv_weight, const void* a_log,
+                                       const void* dt_bias, void* conv_state, const void* state_slots,
+                                       void* query, void* key, void* value, void* alpha, void* beta, void* kq,
+                                       int state_capacity, qwc_stream stream);
+int qwc_delta_gated_rmsnorm_exchanged(const float* input, const qwc_exchange_row* row, int slices,
+                                      float weight_global_scale, int gate_column, const void* weight,
+                                      void* output, void* staged_output, float epsilon, qwc_stream stream);
+int qwc_nvfp4_sum_exchanged(const qwc_exchange_row* row, int slices, float weight_global_scale, void* rows,
+                            qwc_stream stream);
+int qwc_swiglu_combine_exchanged(const qwc_exchange_row* row, int slices, float gate_global_scale,
+                                 float up_global_scale, void* output, void* staged_output, int intermediate,
+                                 qwc_stream stream);
+int qwc_fp8_lm_head_exchange(const void* weights, const void* row_scales, const void* staged_input,
+                             void* logits, const qwc_exchange_row* candidates, void* sampled, void* status_out,
+                             int hidden_size, int vocab_local, void* workspace, qwc_stream stream);
 
 /*
  * Additive: the producers of activations with a staged output beside (or instead of) their bf16

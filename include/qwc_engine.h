@@ -128,6 +128,11 @@ typedef struct qwc_engine_config {
     int use_graph;               /* 1: replay a captured graph per batch size (default path) */
     int attention_partitions;    /* 0 = choose from max_batch and max_context */
     int write_logits;            /* 1: the vocabulary head also stores fp32 logits (tensor "logits"); 0: tokens only */
+    int exchange;                /* latency mode: 0 = every projection's output gathered by ncclAllGather
+                                    (qwc_engine_init_split), 1 = fused: projections store their partial sums
+                                    into every rank's memory and the consumers sum them
+                                    (qwc_engine_exchange_handle / qwc_engine_open_peers).  Needs max_batch == 1;
+                                    with split_size 1 the rank exchanges with itself (tests). */
 } qwc_engine_config;
 
 /* Fills `config` with the synthetic 27B-shaped model of the benchmark. */
@@ -143,6 +148,15 @@ void qwc_engine_destroy(qwc_engine* engine);
  * Returns 0, or a negative code when libnccl cannot be loaded / initialised. */
 int qwc_engine_nccl_unique_id(void* unique_id_128);
 int qwc_engine_init_split(qwc_engine* engine, const void* unique_id_128);
+
+/* Fused latency mode (config.exchange = 1): every rank exports the 64-byte inter-process handle of
+ * its exchange block, the caller distributes them (any host channel), and every rank maps the
+ * others' blocks with `handles` = split_size handles in rank order (its own entry is ignored).  The
+ * ranks must be processes on one node whose GPUs have peer access.  Until the peers are open a step
+ * returns cudaErrorNotReady.  In this mode the step uses no library collective; every rank stores the
+ * same sampled token; "logits" holds this rank's vocab / split_size columns only. */
+int qwc_engine_exchange_handle(qwc_engine* engine, void* handle_64);
+int qwc_engine_open_peers(qwc_engine* engine, const void* handles, int count);
 
 /* Device pointer and size of a named resident tensor, for tests that read weights and
  * caches back.  Layer-indexed names take the layer number; others ignore it.  Returns 0 or 1. */

@@ -35,6 +35,14 @@ class TableEdit(ctypes.Structure):
                 ("kind", ctypes.c_uint32)]
 
 
+class ExchangeRow(ctypes.Structure):
+    """qwc_exchange_row (include/qwc_exchange.h): one activation row that the ranks of latency mode hand
+    one another; pass ctypes.byref(row)."""
+
+    _fields_ = [("blocks", c_void_p * 8), ("ranks", c_int), ("rank", c_int), ("epoch", c_void_p),
+                ("instance", ctypes.c_uint32), ("offset", ctypes.c_uint64), ("width", c_int), ("flags", ctypes.c_uint32)]
+
+
 # name -> (restype, argtypes); every symbol declared in include/qwc_abi.h
 P = c_void_p
 KERNEL_SYMBOLS = {
@@ -42,6 +50,7 @@ KERNEL_SYMBOLS = {
     "qwc_get_shape": (None, [POINTER(Shape)]),
     "qwc_device_status": (c_int, []),
     "qwc_device_status_reset": (c_int, []),
+    "qwc_device_status_detail": (c_int, [P]),
     "qwc_device_status_set": (c_int, [c_int]),
     "qwc_device_status_copy": (c_int, [P, P]),
     "qwc_nvfp4_w4a16": (c_int, [P, P, P, P, c_int, c_int, c_int, c_float, P]),
@@ -56,6 +65,19 @@ KERNEL_SYMBOLS = {
     "qwc_fp8_lm_head_staged": (c_int, [P, P, P, P, P, P, c_int, c_int, c_int, P, P]),
     "qwc_rmsnorm_bf16_staged": (c_int, [P, P, P, P, P, c_int, c_int, c_float, P]),
     "qwc_nvfp4_split_count": (c_int, [c_int, c_int]),
+    # latency mode: rows exchanged between ranks (P: a qwc_exchange_row*)
+    "qwc_exchange_advance": (c_int, [P, P]),
+    "qwc_exchange_row_bytes": (c_size_t, [c_int]),
+    "qwc_exchange_candidate_bytes": (c_size_t, [c_int]),
+    "qwc_nvfp4_exchange_slices": (c_int, [c_int, c_int, c_int]),
+    "qwc_nvfp4_w4a16_exchange": (c_int, [P, P, P, P, c_int, c_int, P]),
+    "qwc_nvfp4_swiglu_w4a16_exchange": (c_int, [P, P, P, P, P, P, c_int, c_int, P]),
+    "qwc_rmsnorm_bf16_exchanged": (c_int, [P, c_int, c_float, P, P, P, P, P, c_int, c_float, P]),
+    "qwc_delta_prepare_decode_exchanged": (c_int, [P, c_int, c_float, c_int, c_int] + [P] * 11 + [c_int, P]),
+    "qwc_delta_gated_rmsnorm_exchanged": (c_int, [P, P, c_int, c_float, c_int, P, P, P, c_float, P]),
+    "qwc_nvfp4_sum_exchanged": (c_int, [P, c_int, c_float, P, P]),
+    "qwc_swiglu_combine_exchanged": (c_int, [P, c_int, c_float, c_float, P, P, c_int, P]),
+    "qwc_fp8_lm_head_exchange": (c_int, [P, P, P, P, P, P, P, c_int, c_int, P, P]),
     "qwc_delta_prepare_decode_split": (c_int, [P, c_int, c_int, c_float, c_int, c_int] + [P] * 11 + [c_int, c_int, P]),
     "qwc_delta_gated_rmsnorm_split": (c_int, [P, P, c_int, c_int, c_float, c_int, P, P, P, c_int, c_float, P]),
     "qwc_nvfp4_sum_slices": (c_int, [P, c_int, c_float, P, c_int, c_int, P]),

@@ -239,7 +239,16 @@ struct qwc_engine {
     __nv_bfloat16* trace = nullptr;
 
     // latency mode
-    void* comm = nullptr;
+    void* comm = nullptr;  // NCCL all-gather form
+    // fused form: the block that the ranks' projections store their slices into, and everybody's block
+    // as this device addresses it
+    unsigned char* exchange_block = nullptr;
+    size_t exchange_bytes = 0;
+    void* exchange_blocks[QWC_MAX_PEERS] = {};
+    std::vector<void*> opened_peers;
+    bool peers_ready = false;
+    uint32_t* epoch = nullptr;
+    size_t row_wide = 0, row_hidden[2] = {0, 0}, row_swiglu = 0, row_candidates = 0;  // offsets in the block
 
     // worker loop state
     std::vector<uint32_t> last_token;  // per state slot
@@ -392,9 +401,176 @@ int project_and_norm(qwc_engine* e, const LinearW& w, const void* staged_input, 
     return 0;
 }
 
+// ---- latency mode, fused form ---------------------------------------------------------------
+// One sequence; every projection computes this rank's rows and stores its K-split slices into every
+// rank's exchange block, and the kernel that consumes the row sums them after a bounded wait for the
+// tagged words (kernels/exchange.cuh).  Everything between projections (norms, the DeltaNet update, the
+// attention pass) runs replicated on every rank: at one row it is small next to the weights.
+qwc_exchange_row exchange_row(const qwc_engine* e, size_t offset, uint32_t instance, int width) {
+    qwc_exchange_row row = {};
+    for (int r = 0; r < e->cfg.split_size; ++r) {
+        row.blocks[r] = e->exchange_blocks[r];
+    }
+    row.ranks = e->cfg.split_size;
+    row.rank = e->cfg.split_rank;
+    row.epoch = e->epoch;
+    row.instance = instance;
+    row.offset = offset;
+    row.width = width;
+    // a graph of selected phases only (timing): its consumers run on whatever the last whole step left
+    row.flags = e->phase_filter != nullptr ? QWC_EXCHANGE_ANY_TAG : 0u;
+    return row;
+}
+
+int decode_forward_exchange(qwc_engine* e) {
+    const qwc_engine_config& c = e->cfg;
+    cudaStream_t s = e->stream;
+    if (!e->peers_ready) {
+        return cudaErrorNotReady;  // the peers' blocks are not mapped yet
+    }
+    // A graph of selected phases only (qwc_engine_time_phases) does not advance the epoch and its consumers
+    // take the words that are there whatever their tag (exchange_row): nothing waits.
+    uint32_t* row_slots = e->in_dev;
+    uint32_t* tokens = e->in_dev + c.max_batch;
+    const qwc_table_edit* edits = reinterpret_cast<const qwc_table_edit*>(e->in_dev + 2 * c.max_batch);
+    const int batch = 1;
+    uint32_t instance = 0;
+
+    if (e->phase_filter == nullptr) {
+        QWC_TRY(qwc_exchange_advance(e->epoch, s));
+    }
+    if (phase(e, "pack")) {
+        QWC_TRY(qwc_page_table_apply(e->seq_tokens, e->seq_blocks, edits, e->max_edits, c.state_slots, e->max_blocks, s));
+        QWC_TRY(qwc_pack_decode_batch(row_slots, nullptr, e->seq_tokens, e->seq_blocks, e->rope_table, c.max_context,
+                                      e->row_count, e->state_slots, e->positions, e->context_lengths, e->physical_blocks,
+                                      e->block_offsets, e->block_tables, e->block_table_offsets, nullptr, e->cosine,
+                                      e->sine, e->out_dev + c.max_batch, batch, c.state_slots, e->max_blocks,
+                                      c.kv_page_size, s));
+    }
+    if (phase(e, "embed")) {
+        QWC_TRY(qwc_fp8_embedding_gather(e->embed, e->embed_scales, tokens, e->residual, batch, c.hidden, c.vocab, s));
+    }
+    if (phase(e, "norm")) {
+        QWC_TRY(qwc_rmsnorm_bf16_staged(e->residual, nullptr, e->layers[0].input_norm, nullptr, e->normed_staged,
+                                        batch, c.hidden, kEps, s));
+    }
+
+    // a projection to the hidden width, then the residual norm that sums what all ranks stored
+    const auto finish_with_norm = [&](const LinearW& w, const void* staged_input, int which,
+                                      __nv_bfloat16* projection_rows, const __nv_bfloat16* norm_weight,
+                                      const char* label) -> int {
+        const qwc_exchange_row row = exchange_row(e, e->row_hidden[which], instance++, c.hidden);
+        if (phase(e, label)) {
+            QWC_TRY(qwc_nvfp4_w4a16_exchange(w.packed, w.scales, staged_input, &row, w.out_features, w.in_features, s));
+        }
+        if (phase(e, "norm")) {
+            QWC_TRY(qwc_rmsnorm_bf16_exchanged(&row, qwc_nvfp4_exchange_slices(w.out_features, w.in_features, 0),
+                                               w.global_scale, e->trace != nullptr ? projection_rows : nullptr,
+                                               e->residual, norm_weight, nullptr, e->normed_staged, c.hidden, kEps, s));
+        }
+        return 0;
+    };
+
+    for (size_t index = 0; index < e->layers.size(); ++index) {
+        const Layer& layer = e->layers[index];
+        if (!layer.full) {
+            const LinearW& in = layer.in_proj;
+            const qwc_exchange_row row = exchange_row(e, e->row_wide, instance++, e->mixer_width);
+            const int slices = qwc_nvfp4_exchange_slices(in.out_features, in.in_features, 0);
+            if (phase(e, "gemm.la_in")) {
+                QWC_TRY(qwc_nvfp4_w4a16_exchange(in.packed, in.scales, e->normed_staged, &row, in.out_features,
+                                                 in.in_features, s));
+            }
+            if (phase(e, "delta.prepare")) {
+                QWC_TRY(qwc_delta_prepare_decode_exchanged(&row, slices, in.global_scale, e->a_offset, e->b_offset,
+                                                           layer.conv_weight, layer.a_log, layer.dt_bias,
+                                                           layer.conv_state, e->state_slots, e->dq, e->dk, e->dv,
+                                                           e->dalpha, e->dbeta, e->dkq, c.state_slots, s));
+            }
+            if (phase(e, "delta.scan")) {
+                QWC_TRY(qwc_delta_decode_int8_step(layer.state, layer.state_scales, e->state_slots, e->dq, e->dk, e->dv,
+                                                   e->dalpha, e->dbeta, e->dkq, e->delta_out, c.state_slots, batch,
+                                                   nullptr, 0, 1.0f, nullptr, e->mixer_width, e->z_offset, layer.out_norm,
+                                                   kEps, nullptr, s));
+            }
+            if (phase(e, "delta.norm")) {
+                QWC_TRY(qwc_delta_gated_rmsnorm_exchanged(e->delta_out, &row, slices, in.global_scale, e->z_offset,
+                                                          layer.out_norm, nullptr, e->delta_normed_staged, kEps, s));
+            }
+            QWC_TRY(finish_with_norm(layer.la_out, e->delta_normed_staged, 0, e->mixer_out, layer.post_norm,
+                                     "gemm.la_out"));
+        } else {
+            const LinearW& qkv = layer.qkv;
+            const qwc_exchange_row row = exchange_row(e, e->row_wide, instance++, e->qkv_width);
+            if (phase(e, "gemm.attn_qkv")) {
+                QWC_TRY(qwc_nvfp4_w4a16_exchange(qkv.packed, qkv.scales, e->normed_staged, &row, qkv.out_features,
+                                                 qkv.in_features, s));
+                QWC_TRY(qwc_nvfp4_sum_exchanged(&row, qwc_nvfp4_exchange_slices(qkv.out_features, qkv.in_features, 0),
+                                                qkv.global_scale, e->qkv_buf, s));
+            }
+            const int q_width = kQueryHeads * 2 * kHeadDim;
+            if (phase(e, "attn.prepare")) {
+                QWC_TRY(qwc_prepare_attention_decode_fp8_scaled(
+                    e->qkv_buf, e->qkv_buf + q_width, e->qkv_buf + q_width + kKvHeads * kHeadDim, layer.q_norm,
+                    layer.k_norm, e->cosine, e->sine, e->physical_blocks, e->block_offsets, layer.k_scale, layer.v_scale,
+                    e->query, layer.k_cache, layer.v_cache, batch, c.kv_page_size, e->qkv_width, e->qkv_width,
+                    e->qkv_width, kEps, s));
+            }
+            if (phase(e, "attn.decode")) {
+                QWC_TRY(qwc_paged_attention_packed_fp8_staged(
+                    e->query, e->qkv_buf, layer.k_cache, layer.v_cache, e->block_tables, e->context_lengths, layer.k_scale,
+                    layer.v_scale, nullptr, e->attention_out_staged, e->attention_workspace, e->attention_workspace_bytes,
+                    batch, 0, e->max_blocks, c.kv_page_size, e->qkv_width, e->partitions, 1.0f / 16.0f, s));
+            }
+            QWC_TRY(finish_with_norm(layer.o, e->attention_out_staged, 0, e->mixer_out, layer.post_norm,
+                                     "gemm.attn_out"));
+        }
+        const size_t trace_row = static_cast<size_t>(c.max_batch) * c.hidden;
+        if (e->trace != nullptr && e->phase_filter == nullptr) {
+            QWC_TRY(cudaMemcpyAsync(e->trace + (2 * index) * trace_row, e->mixer_out, trace_row * 2,
+                                    cudaMemcpyDeviceToDevice, s));
+        }
+        {
+            const qwc_exchange_row row = exchange_row(e, e->row_swiglu, instance++, 2 * c.intermediate);
+            if (phase(e, "gemm.mlp_gate_up")) {
+                QWC_TRY(qwc_nvfp4_swiglu_w4a16_exchange(layer.gate.packed, layer.gate.scales, layer.up.packed,
+                                                        layer.up.scales, e->normed_staged, &row, layer.gate.out_features,
+                                                        layer.gate.in_features, s));
+            }
+            if (phase(e, "mlp.combine")) {
+                QWC_TRY(qwc_swiglu_combine_exchanged(
+                    &row, qwc_nvfp4_exchange_slices(layer.gate.out_features, layer.gate.in_features, 1),
+                    layer.gate.global_scale, layer.up.global_scale, nullptr, e->mlp_hidden_staged, c.intermediate, s));
+            }
+        }
+        const __nv_bfloat16* next_norm = index + 1 < e->layers.size() ? e->layers[index + 1].input_norm : e->final_norm;
+        QWC_TRY(finish_with_norm(layer.down, e->mlp_hidden_staged, 1, e->mlp_out, next_norm, "gemm.mlp_down"));
+        if (e->trace != nullptr && e->phase_filter == nullptr) {
+            QWC_TRY(cudaMemcpyAsync(e->trace + (2 * index + 1) * trace_row, e->residual, trace_row * 2,
+                                    cudaMemcpyDeviceToDevice, s));
+        }
+    }
+    if (instance >= QWC_EXCHANGE_MAX_INSTANCES) {
+        return cudaErrorInvalidValue;
+    }
+    // every rank scans its rows of the vocabulary and hands the others its best candidates
+    const qwc_exchange_row candidates = exchange_row(e, e->row_candidates, instance++, 4);
+    if (phase(e, "lm_head")) {
+        QWC_TRY(qwc_fp8_lm_head_exchange(e->lm_head, e->lm_head_scales, e->normed_staged,
+                                         c.write_logits ? e->logits : nullptr, &candidates, e->out_dev,
+                                         e->out_dev + c.max_batch + 1, c.hidden, e->vocab_local, e->streamk_workspace,
+                                         s));
+    }
+    mark(e, "end");
+    return 0;
+}
+
 int decode_forward(qwc_engine* e, int batch) {
     const qwc_engine_config& c = e->cfg;
     cudaStream_t s = e->stream;
+    if (c.exchange != 0) {
+        return decode_forward_exchange(e);
+    }
     uint32_t* row_slots = e->in_dev;
     uint32_t* tokens = e->in_dev + c.max_batch;
     const qwc_table_edit* edits = reinterpret_cast<const qwc_table_edit*>(e->in_dev + 2 * c.max_batch);
@@ -666,6 +842,7 @@ void qwc_engine_default_config(qwc_engine_config* config) {
     config->use_graph = 1;
     config->attention_partitions = 0;
     config->write_logits = 0;
+    config->exchange = 0;
 }
 
 int qwc_engine_nccl_unique_id(void* unique_id_128) {
@@ -692,12 +869,48 @@ int qwc_engine_init_split(qwc_engine* e, const void* unique_id_128) {
     return init(&e->comm, e->cfg.split_size, id, e->cfg.split_rank) == 0 ? 0 : -2;
 }
 
+// The fused latency mode's set-up: every rank exports the inter-process handle of its exchange block,
+// the caller distributes the handles (any host-side channel), and every rank maps the others' blocks.
+// After that the step needs no library collective at all.
+int qwc_engine_exchange_handle(qwc_engine* e, void* handle_64) {
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "the handle travels as 64 bytes");
+    if (e == nullptr || handle_64 == nullptr || e->exchange_block == nullptr) {
+        return cudaErrorInvalidValue;
+    }
+    cudaIpcMemHandle_t handle;
+    QWC_TRY(cudaIpcGetMemHandle(&handle, e->exchange_block));
+    std::memcpy(handle_64, &handle, sizeof(handle));
+    return 0;
+}
+
+int qwc_engine_open_peers(qwc_engine* e, const void* handles, int count) {
+    if (e == nullptr || handles == nullptr || e->exchange_block == nullptr || count != e->cfg.split_size ||
+        e->peers_ready) {
+        return cudaErrorInvalidValue;
+    }
+    const unsigned char* bytes = static_cast<const unsigned char*>(handles);
+    for (int r = 0; r < count; ++r) {
+        if (r == e->cfg.split_rank) {
+            continue;
+        }
+        cudaIpcMemHandle_t handle;
+        std::memcpy(&handle, bytes + static_cast<size_t>(r) * sizeof(handle), sizeof(handle));
+        void* mapped = nullptr;
+        QWC_TRY(cudaIpcOpenMemHandle(&mapped, handle, cudaIpcMemLazyEnablePeerAccess));
+        e->opened_peers.push_back(mapped);
+        e->exchange_blocks[r] = mapped;
+    }
+    e->peers_ready = true;
+    return 0;
+}
+
 int qwc_engine_create(const qwc_engine_config* config, qwc_engine** out) {
     if (config == nullptr || out == nullptr || config->num_layers <= 0 || config->full_attention_interval <= 0 ||
         config->hidden <= 0 || config->hidden % 256 != 0 || config->intermediate % 256 != 0 || config->vocab <= 0 ||
         config->max_batch <= 0 || config->max_batch > 32 || config->max_context <= 0 || config->kv_pool_blocks <= 0 ||
         config->state_slots < config->max_batch || config->split_size < 1 || config->split_rank < 0 ||
-        config->split_rank >= config->split_size || (config->split_size > 1 && config->max_batch != 1)) {
+        config->split_rank >= config->split_size || (config->split_size > 1 && config->max_batch != 1) ||
+        config->split_size > QWC_MAX_PEERS || (config->exchange != 0 && config->max_batch != 1)) {
         return cudaErrorInvalidValue;
     }
     qwc_shape shape = {config->delta_value_heads, config->kv_page_size};
@@ -820,6 +1033,26 @@ int qwc_engine_create(const qwc_engine_config* config, qwc_engine** out) {
         QWC_STEP(gpu_alloc_t(e, &e->split_sums, static_cast<size_t>(16) * 32 * c.hidden, true));
         const int wide = e->mixer_width > e->qkv_width ? e->mixer_width : e->qkv_width;
         QWC_STEP(gpu_alloc_t(e, &e->split_sums_wide, static_cast<size_t>(16) * 32 * wide, true));
+        if (c.exchange != 0) {
+            // one allocation, so that one inter-process handle covers every row: [wide | hidden A |
+            // hidden B | gate and up | candidates].  Consecutive exchanges of a step never share a row.
+            size_t at = 0;
+            e->row_wide = at;
+            at += qwc_exchange_row_bytes(wide);
+            e->row_hidden[0] = at;
+            at += qwc_exchange_row_bytes(c.hidden);
+            e->row_hidden[1] = at;
+            at += qwc_exchange_row_bytes(c.hidden);
+            e->row_swiglu = at;
+            at += qwc_exchange_row_bytes(2 * c.intermediate);
+            e->row_candidates = at;
+            at += qwc_exchange_candidate_bytes(c.split_size);
+            e->exchange_bytes = at;
+            QWC_STEP(gpu_alloc_t(e, &e->exchange_block, at, true));
+            QWC_STEP(gpu_alloc_t(e, &e->epoch, 4, true));
+            e->exchange_blocks[c.split_rank] = e->exchange_block;
+            e->peers_ready = c.split_size == 1;  // a single rank exchanges with itself
+        }
     }
     QWC_STEP(gpu_alloc_t(e, &e->dq, static_cast<size_t>(mb) * kDeltaKeyHeads * kDeltaDim, true));
     QWC_STEP(gpu_alloc_t(e, &e->dk, static_cast<size_t>(mb) * kDeltaKeyHeads * kDeltaDim, true));
@@ -929,6 +1162,9 @@ void qwc_engine_destroy(qwc_engine* e) {
     }
     if (e->comm != nullptr && nccl_api().comm_destroy != nullptr) {
         nccl_api().comm_destroy(e->comm);
+    }
+    for (void* peer : e->opened_peers) {
+        cudaIpcCloseMemHandle(peer);
     }
     for (void* p : e->allocations) {
         cudaFree(p);
@@ -1083,6 +1319,14 @@ void qwc_engine_traffic(const qwc_engine* e, int rows, double context_tokens, qw
             gemv += 2;
             kernels += 2 + 2 + (e->partitions > 1 ? 1 : 0) + (e->cfg.split_size == 1 ? 1 : 0 /*slice sum*/);
             out->kv_bytes += context_tokens * 2.0 * kKvHeads * kHeadDim;
+        }
+    }
+    if (e->cfg.exchange != 0) {
+        // fused latency mode: epoch, edits + pack, embed, norm, head, sampling; per layer the SwiGLU pair,
+        // its combine, down and its norm, and six kernels of the mixer (one more when attention merges)
+        kernels = 1 + 3 + 1 + 1 + 1 + 1;
+        for (const Layer& l : e->layers) {
+            kernels += 4 + 6 + (l.full && e->partitions > 1 ? 1 : 0);
         }
     }
     const double head = static_cast<double>(e->vocab_local) * e->cfg.hidden + e->vocab_local * 4.0;

@@ -45,6 +45,7 @@
 // stores, frees its TMEM and returns.  A launch that ends that way leaves tickets taken: the
 // workspace must be cleared (qwc_streamk_workspace_init) before it is used again.
 
+#include "exchange.cuh"
 #include "tcgen05.cuh"
 
 namespace qwc {
@@ -118,6 +119,10 @@ struct StreamKParams {
     // itself.  0 splits: equal shares with tickets.
     int splits;
     float* split_out;
+    // Latency mode (one activation row, weight rows split over ranks): the slices go to every rank's
+    // exchange block as tagged words instead (exchange.cuh); split_out is null then.
+    ExchangeTarget exchange;
+    uint32_t index_offset;  // vocabulary head in latency mode: this rank's first row in the whole vocabulary
     float* candidate_values;     // vocabulary head with sampling: [32][kCandidateSlots]
     uint32_t* candidate_indices;
     int* status;
@@ -855,6 +860,34 @@ __global__ void __launch_bounds__(kThreads, 1)
         auto store_slice = [&](int pair, int batch) {
             const bool rehearsal = batch == 0;
             const int slice = kSplitOut ? cta - pair * p.splits : 0;
+            if (p.exchange.ranks > 0) {
+                // one activation row (the first column of the warps that hold the first rows); every
+                // rank's copy of the slice array gets the value, its own included
+                if (first_token != 0) {
+                    return;
+                }
+                const uint32_t tag = rehearsal ? 0u : exchange_tag(p.exchange.epoch, p.exchange.instance);
+                uint2* const sink = reinterpret_cast<uint2*>(g_rehearsal_sink + (cta * kEpilogueWarps + e) * 32);
+#pragma unroll
+                for (int t = 0; t < kTiles; ++t) {
+                    const int row = kSwiglu ? pair * kTileRows + quarter * 32 + lane
+                                            : (pair * kTiles + t) * kTileRows + quarter * 32 + lane;
+                    if (row < p.out_features) {
+                        // SwiGLU pair: the row is [gate | up], each half holding all ranks' columns
+                        const size_t element = rehearsal ? static_cast<size_t>(lane >> 1)
+                                                         : static_cast<size_t>(slice) * p.exchange.width +
+                                                               (kSwiglu ? t * (p.exchange.width / 2) : 0) +
+                                                               p.exchange.first_column + row;
+                        const float value = stash[(t * kCols) * kStashPitch];
+                        for (int r = 0; r < p.exchange.ranks; ++r) {
+                            uint2* const block =
+                                rehearsal ? sink : reinterpret_cast<uint2*>(p.exchange.blocks[r] + p.exchange.offset);
+                            store_tagged(block + element, value, tag);
+                        }
+                    }
+                }
+                return;
+            }
             const int rows_stored = rehearsal ? kPad : batch;
             float* const out = rehearsal ? g_rehearsal_sink + (cta * kEpilogueWarps + e) * 32
                                          : p.split_out + static_cast<size_t>(slice) * p.batch * p.out_features;
@@ -910,7 +943,7 @@ __global__ void __launch_bounds__(kThreads, 1)
             if (rehearsal) {
                 limit = 0;  // the stores go to a sink
                 asm volatile("" : "+r"(limit));  // opaque: one copy of the code below serves both passes
-                slice = kSplitOut && p.split_out != nullptr;
+                slice = kSplitOut && (p.split_out != nullptr || p.exchange.ranks > 0);
                 complete = !slice;
             } else {
                 // The first piece of a pair is what its CTA ends its share with, so it usually arrives
@@ -973,7 +1006,7 @@ __global__ void __launch_bounds__(kThreads, 1)
                 }
                 complete = whole || parked;
                 if (kSplitOut) {
-                    slice = p.split_out != nullptr;
+                    slice = p.split_out != nullptr || p.exchange.ranks > 0;
                     complete = !slice;  // one CTA per tile pair: nothing to sum
                 } else if (parked) {
                     if (lane == 0) {
@@ -1040,7 +1073,20 @@ __global__ void __launch_bounds__(kThreads, 1)
             u += s1 - s0;
             ++segment;
         }
-        if (sampling && ok && lane < kCols && first_token + lane < 32) {
+        if (sampling && ok && p.exchange.ranks > 0) {
+            // latency mode: the one row's candidate of this warp goes to every rank, as two tagged words
+            // (value, then the row's number in the whole vocabulary)
+            if (first_token == 0 && lane == 0) {
+                const uint32_t tag = exchange_tag(p.exchange.epoch, p.exchange.instance);
+                const size_t element = static_cast<size_t>(p.exchange.first_column + cta * 4 + quarter) * 2;
+                const uint32_t index = best_index == UINT32_MAX ? UINT32_MAX : best_index + p.index_offset;
+                for (int r = 0; r < p.exchange.ranks; ++r) {
+                    uint2* const block = reinterpret_cast<uint2*>(p.exchange.blocks[r] + p.exchange.offset);
+                    store_tagged(block + element, best_value, tag);
+                    store_tagged(block + element + 1, __uint_as_float(index), tag);
+                }
+            }
+        } else if (sampling && ok && lane < kCols && first_token + lane < 32) {
             const size_t slot = static_cast<size_t>(first_token + lane) * kCandidateSlots + cta * 4 + quarter;
             p.candidate_values[slot] = best_value;
             p.candidate_indices[slot] = best_index;
@@ -1128,6 +1174,61 @@ __global__ void __launch_bounds__(kSampleThreads) sample_candidates_kernel(const
     }
 }
 
+// Latency mode: the same choice over the candidates that all ranks stored into this rank's block (two
+// tagged words each: value, vocabulary row), after a bounded wait for this step's words.  Every rank
+// sees the same candidates in the same places and stores the same token.
+__global__ void __launch_bounds__(kSampleThreads) sample_exchanged_kernel(const TaggedRow candidates, int slots,
+                                                                          uint32_t* __restrict__ output,
+                                                                          uint32_t* __restrict__ status_out) {
+    pdl_launch_dependents();
+    pdl_wait();
+    __shared__ float shared_values[kSampleThreads / 32];
+    __shared__ uint32_t shared_indices[kSampleThreads / 32];
+    const uint32_t tag = exchange_tag(candidates.epoch, candidates.instance);
+    float best = -INFINITY;
+    uint32_t best_index = UINT32_MAX;
+    for (int i = threadIdx.x; i < slots; i += kSampleThreads) {
+        const uint4 pair = load_tagged_pair(candidates.words + 2 * i);
+        const float value = ((pair.y ^ tag) & candidates.tag_mask) == 0
+                                ? __uint_as_float(pair.x)
+                                : await_tagged(candidates.words + 2 * i, tag, candidates.status);
+        const uint32_t index =
+            ((pair.w ^ tag) & candidates.tag_mask) == 0
+                ? pair.z
+                : __float_as_uint(await_tagged(candidates.words + 2 * i + 1, tag, candidates.status));
+        if (better_candidate(value, index, best, best_index)) {
+            best = value;
+            best_index = index;
+        }
+    }
+#pragma unroll
+    for (int offset = 16; offset > 0; offset >>= 1) {
+        const float other = __shfl_xor_sync(0xffffffffu, best, offset);
+        const uint32_t other_index = __shfl_xor_sync(0xffffffffu, best_index, offset);
+        if (better_candidate(other, other_index, best, best_index)) {
+            best = other;
+            best_index = other_index;
+        }
+    }
+    if ((threadIdx.x & 31) == 0) {
+        shared_values[threadIdx.x >> 5] = best;
+        shared_indices[threadIdx.x >> 5] = best_index;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        for (int w = 1; w < kSampleThreads / 32; ++w) {
+            if (better_candidate(shared_values[w], shared_indices[w], best, best_index)) {
+                best = shared_values[w];
+                best_index = shared_indices[w];
+            }
+        }
+        output[0] = best_index;
+        if (status_out != nullptr) {
+            *status_out = static_cast<uint32_t>(*reinterpret_cast<const volatile int*>(candidates.status));
+        }
+    }
+}
+
 // bf16 rows -> the staged f16 operand layout [K / 8][n_pad][8]; one thread per 8 elements.
 __global__ void __launch_bounds__(256) stage_activations_kernel(const __nv_bfloat16* __restrict__ x,
                                                                 __half* __restrict__ staged, int batch, int in_features,
@@ -1170,6 +1271,10 @@ struct LaunchShape {
 // Tile pairs that nearly fill the SMs once are not cut at all: one CTA per pair.
 bool prefers_whole_pairs(int pair_tiles, int ctas) { return pair_tiles <= ctas && pair_tiles * 20 >= ctas * 17; }
 
+// What a consumer can have in flight per output at once: more slices would cost it a second round trip.
+constexpr int kMaxKSlices = 8;
+static_assert(kMaxKSlices == kExchangeMaxSlices, "exchange rows are sized for this many slices");
+
 LaunchShape shape_of(int out_features, int in_features, bool swiglu, bool fp8, bool split_out = false) {
     LaunchShape shape;
     const int rows_per_pair = swiglu ? kTileRows : kTiles * kTileRows;
@@ -1189,7 +1294,7 @@ LaunchShape shape_of(int out_features, int in_features, bool swiglu, bool fp8, b
         int splits = shape.ctas / shape.pair_tiles;
         splits = splits < 1 ? 1 : splits;
         splits = splits > shape.stages_in_k ? shape.stages_in_k : splits;
-        splits = splits > 16 ? 16 : splits;
+        splits = splits > kMaxKSlices ? kMaxKSlices : splits;
         shape.splits = splits;
         shape.ctas = shape.pair_tiles * splits;
         return shape;
@@ -1202,7 +1307,7 @@ LaunchShape shape_of(int out_features, int in_features, bool swiglu, bool fp8, b
 
 cudaError_t launch_streamk(StreamKParams p, const void* packed0, const void* packed1, bool swiglu, bool fp8,
                            void* workspace, cudaStream_t stream) {
-    const bool split_out = p.split_out != nullptr;
+    const bool split_out = p.split_out != nullptr || (p.exchange.ranks > 0 && !fp8);
     const LaunchShape shape = shape_of(p.out_features, p.in_features, swiglu, fp8, split_out);
     if (shape.pair_tiles > kMaxPairTiles || shape.units <= 0 || shape.ctas > 4 * kMaxCtas) {
         (void)take_next_projection();
@@ -1463,4 +1568,99 @@ extern "C" int qwc_fp8_lm_head_staged(const void* weights, const void* row_scale
     return launch_chained(sample_candidates_kernel, dim3(batch), dim3(kSampleThreads), 0, stream, candidate_values,
                           candidate_indices, static_cast<uint32_t*>(sampled), shape.ctas * 4,
                           static_cast<const int*>(status), static_cast<uint32_t*>(status_out));
+}
+
+// ---- latency mode: projections that hand their slices to every rank (exchange.cuh) ----------------
+
+extern "C" int qwc_nvfp4_exchange_slices(int out_features, int in_features, int swiglu) {
+    if (out_features <= 0 || in_features <= 0 || in_features % 256 != 0) {
+        return 0;
+    }
+    return shape_of(out_features, in_features, swiglu != 0, false, true).splits;
+}
+
+extern "C" size_t qwc_exchange_candidate_bytes(int ranks) {
+    if (ranks < 1 || ranks > kMaxPeers) {
+        return 0;
+    }
+    return static_cast<size_t>(ranks) * kMaxCtas * 4 * 2 * sizeof(uint2);
+}
+
+extern "C" int qwc_nvfp4_w4a16_exchange(const void* packed, const void* scales, const void* staged_input,
+                                        const qwc_exchange_row* row, int out_features, int in_features,
+                                        cudaStream_t stream) {
+    if (packed == nullptr || scales == nullptr || staged_input == nullptr || !valid_exchange_row(row) ||
+        out_features <= 0 || in_features <= 0 || in_features % 256 != 0 || row->width != row->ranks * out_features ||
+        !aligned16(packed) || !aligned16(scales) || !aligned16(staged_input)) {
+        (void)take_next_projection();
+        return cudaErrorInvalidValue;
+    }
+    StreamKParams p = {};
+    p.scales[0] = p.scales[1] = static_cast<const uint8_t*>(scales);
+    p.x = static_cast<const __half*>(staged_input);
+    p.inverse_scale[0] = p.inverse_scale[1] = 1.0f;
+    p.out_features = out_features;
+    p.in_features = in_features;
+    p.batch = 1;
+    p.exchange = exchange_target(*row, row->rank * out_features);
+    return launch_streamk(p, packed, packed, false, false, nullptr, stream);
+}
+
+extern "C" int qwc_nvfp4_swiglu_w4a16_exchange(const void* gate_packed, const void* gate_scales, const void* up_packed,
+                                               const void* up_scales, const void* staged_input,
+                                               const qwc_exchange_row* row, int out_features, int in_features,
+                                               cudaStream_t stream) {
+    if (gate_packed == nullptr || gate_scales == nullptr || up_packed == nullptr || up_scales == nullptr ||
+        staged_input == nullptr || !valid_exchange_row(row) || out_features <= 0 || in_features <= 0 ||
+        in_features % 256 != 0 || row->width != 2 * row->ranks * out_features || !aligned16(gate_packed) ||
+        !aligned16(gate_scales) || !aligned16(up_packed) || !aligned16(up_scales) || !aligned16(staged_input)) {
+        (void)take_next_projection();
+        return cudaErrorInvalidValue;
+    }
+    StreamKParams p = {};
+    p.scales[0] = static_cast<const uint8_t*>(gate_scales);
+    p.scales[1] = static_cast<const uint8_t*>(up_scales);
+    p.x = static_cast<const __half*>(staged_input);
+    p.inverse_scale[0] = p.inverse_scale[1] = 1.0f;
+    p.out_features = out_features;
+    p.in_features = in_features;
+    p.batch = 1;
+    p.exchange = exchange_target(*row, row->rank * out_features);
+    return launch_streamk(p, gate_packed, up_packed, true, false, nullptr, stream);
+}
+
+extern "C" int qwc_fp8_lm_head_exchange(const void* weights, const void* row_scales, const void* staged_input,
+                                        void* logits, const qwc_exchange_row* candidates, void* sampled,
+                                        void* status_out,
+                                        int hidden_size, int vocab_local, void* workspace, cudaStream_t stream) {
+    int* status = status_ptr();
+    if (weights == nullptr || row_scales == nullptr || staged_input == nullptr || !valid_exchange_row(candidates) ||
+        workspace == nullptr || hidden_size <= 0 || hidden_size % 256 != 0 || vocab_local <= 0 ||
+        !aligned16(weights) || !aligned16(staged_input) || !aligned16(workspace) || status == nullptr) {
+        (void)take_next_projection();
+        return cudaErrorInvalidValue;
+    }
+    const LaunchShape shape = shape_of(vocab_local, hidden_size, false, true);
+    const int slots_per_rank = shape.ctas * 4;
+    StreamKParams p = {};
+    p.scales[0] = p.scales[1] = nullptr;
+    p.x = static_cast<const __half*>(staged_input);
+    p.y_f32 = static_cast<float*>(logits);  // this rank's columns only, or null
+    p.row_scales = static_cast<const float*>(row_scales);
+    p.inverse_scale[0] = p.inverse_scale[1] = 1.0f;
+    p.out_features = vocab_local;
+    p.in_features = hidden_size;
+    p.batch = 1;
+    unsigned char* base = static_cast<unsigned char*>(workspace);
+    p.candidate_values = reinterpret_cast<float*>(base + kPartialBytes + kTicketBytes);  // marks the sampling form
+    p.candidate_indices = reinterpret_cast<uint32_t*>(p.candidate_values + 32 * kCandidateSlots);
+    p.exchange = exchange_target(*candidates, candidates->rank * slots_per_rank);
+    p.index_offset = static_cast<uint32_t>(candidates->rank) * static_cast<uint32_t>(vocab_local);
+    const cudaError_t launched = launch_streamk(p, weights, weights, false, true, workspace, stream);
+    if (launched != cudaSuccess || sampled == nullptr) {
+        return launched;  // sampled == NULL: the candidates only (another launch picks the token)
+    }
+    return launch_chained(sample_exchanged_kernel, dim3(1), dim3(kSampleThreads), 0, stream,
+                          tagged_row(*candidates, 1, status), candidates->ranks * slots_per_rank,
+                          static_cast<uint32_t*>(sampled), static_cast<uint32_t*>(status_out));
 }

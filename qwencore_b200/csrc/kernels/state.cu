@@ -10,7 +10,8 @@ namespace {
 // Defaults reproduce the reference constants (cuda/delta_net.cu:36, cuda/paged_attention.cu:21).
 Shape g_shape = {48, 64};
 
-__device__ int g_status_word = 0;
+// [0] the sticky status word; [2], [3] what the first failed wait for a peer looked for and found (tags)
+__device__ int g_status_word[4] = {0, 0, 0, 0};
 
 
 int* g_status_ptrs[kMaxDevices] = {};
@@ -70,7 +71,15 @@ extern "C" int qwc_device_status_reset(void) {
     if (word == nullptr) {
         return cudaErrorInvalidValue;
     }
-    return cudaMemset(word, 0, sizeof(int));
+    return cudaMemset(word, 0, 4 * sizeof(int));
+}
+
+extern "C" int qwc_device_status_detail(uint32_t* expected_and_found) {
+    int* word = qwc::status_ptr();
+    if (word == nullptr || expected_and_found == nullptr) {
+        return cudaErrorInvalidValue;
+    }
+    return cudaMemcpy(expected_and_found, word + 2, 2 * sizeof(int), cudaMemcpyDeviceToHost);
 }
 
 extern "C" int qwc_device_status_set(int code) {

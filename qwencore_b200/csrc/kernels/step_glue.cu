@@ -5,7 +5,10 @@
 //
 // Rounding points follow the reference kernels exactly (file:line at each launcher).
 
+#include <cooperative_groups.h>
+
 #include "common.cuh"
+#include "exchange.cuh"
 
 namespace qwc {
 
@@ -150,6 +153,51 @@ __global__ void __launch_bounds__(kThreads) rmsnorm_bf16_kernel(const __nv_bfloa
     }
 }
 
+// One output of a projection that ran as a regular K split (qwc_nvfp4_w4a16_split): the slices summed in
+// slice order, scaled and rounded to bf16 as the projection's own epilogue would have done.  In latency
+// mode the slices are tagged words that the ranks stored into one another's memory (exchange.cuh): one
+// activation row, and a read that may have to wait for a peer.
+struct SplitSource {
+    const float* sums;  // [slices][batch][width] fp32, or null: the consumer reads bf16 rows instead
+    int slices;
+    int batch;
+    int width;
+    float scale;
+    TaggedRow tagged;  // words != null: the exchanged form (sums is null then)
+};
+
+__device__ __forceinline__ bool has_slices(const SplitSource& source) {
+    return source.sums != nullptr || source.tagged.words != nullptr;
+}
+
+// The tag that this step's words of an exchanged row carry (read once, after the wait for the preceding kernel).
+__device__ __forceinline__ uint32_t split_tag(const SplitSource& source) {
+    return source.tagged.words != nullptr ? exchange_tag(source.tagged.epoch, source.tagged.instance) : 0u;
+}
+
+// (The loads of up to four slices are issued together: one round trip, not one per slice.  A slice
+// past the last one reads the last one again and adds nothing.)
+__device__ __forceinline__ float split_value(const SplitSource& source, uint32_t tag, int row, int column) {
+    if (source.tagged.words != nullptr) {
+        return __bfloat162float(__float2bfloat16(tagged_sum(source.tagged, tag, column) * source.scale));
+    }
+    const size_t stride = static_cast<size_t>(source.batch) * source.width;
+    const float* at = source.sums + static_cast<size_t>(row) * source.width + column;
+    float total = 0.0f;
+    for (int first = 0; first < source.slices; first += 4) {
+        float part[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            part[j] = __ldcg(at + min(first + j, source.slices - 1) * stride);
+        }
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            total += first + j < source.slices ? part[j] : 0.0f;
+        }
+    }
+    return __bfloat162float(__float2bfloat16(total * source.scale));
+}
+
 // ---- residual RMSNorm that also finishes a K-split projection ------------------------
 // The projection before a residual RMSNorm (mixer output, MLP down: 5120 outputs, too few row tiles
 // for the SMs) runs as a regular K split and leaves fp32 partial rows [slice][batch][hidden]; summing
@@ -160,11 +208,12 @@ __global__ void __launch_bounds__(kThreads) rmsnorm_bf16_kernel(const __nv_bfloa
 constexpr int kSplitNormThreads = 640;
 constexpr int kSplitNormMaxItems = 4;  // float4 items per thread: hidden <= 4 * 4 * 640
 
+template <bool kExchanged>  // the slices are another rank's tagged words (latency mode, one row)
 __global__ void __launch_bounds__(kSplitNormThreads) rmsnorm_split_kernel(
     const float* __restrict__ partial_sums, int splits, float scale, __nv_bfloat16* __restrict__ projection,
     __nv_bfloat16* __restrict__ residual, const __nv_bfloat16* __restrict__ weight,
     __nv_bfloat16* __restrict__ output, __half* __restrict__ staged, int padded_rows, int hidden, int batch,
-    float epsilon) {
+    float epsilon, const TaggedRow exchanged) {
     pdl_launch_dependents();
     __shared__ float scratch[kSplitNormThreads / 32];
     const int token = blockIdx.x;
@@ -178,6 +227,7 @@ __global__ void __launch_bounds__(kSplitNormThreads) rmsnorm_split_kernel(
         }
     }
     pdl_wait();
+    const uint32_t tag = kExchanged ? exchange_tag(exchanged.epoch, exchanged.instance) : 0u;
     const size_t slice_stride = static_cast<size_t>(batch) * hidden;
     const float* mine = partial_sums + static_cast<size_t>(token) * hidden;
     float held[kSplitNormMaxItems][4];
@@ -192,7 +242,10 @@ __global__ void __launch_bounds__(kSplitNormThreads) rmsnorm_split_kernel(
             }
             // eight slices in flight at a time: the sum costs one round trip, not one per slice
             float4 total = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-            for (int first = 0; first < splits; first += 8) {
+            if (kExchanged) {  // latency mode: the ranks' tagged slices of the one row
+                total = tagged_sum4(exchanged, tag, 4 * item);
+            }
+            for (int first = 0; !kExchanged && first < splits; first += 8) {
                 float4 part[8];
 #pragma unroll
                 for (int j = 0; j < 8; ++j) {
@@ -264,46 +317,159 @@ __global__ void __launch_bounds__(kSplitNormThreads) rmsnorm_split_kernel(
     }
 }
 
-// One output of a projection that ran as a regular K split (qwc_nvfp4_w4a16_split): the slices summed in
-// slice order, scaled and rounded to bf16 as the projection's own epilogue would have done.
-struct SplitSource {
-    const float* sums;  // [slices][batch][width] fp32, or null: the consumer reads bf16 rows instead
-    int slices;
-    int batch;
-    int width;
-    float scale;
-};
+// ---- the same for ONE row, spread over a cluster ---------------------------------------
+// With a single activation row the kernel above is one CTA pulling every slice of the row through
+// one SM (8 slices x 5120 x 8 bytes in latency mode: several microseconds of L2 bandwidth of one SM,
+// several times what the arithmetic takes).  Here the row is divided over a cluster of eight CTAs,
+// each summing and normalising hidden / 8 columns (one item of four columns per thread, every slice
+// of it in flight at once); the only thing they share is the sum of squares: each CTA stores its
+// partial into every CTA's shared memory, one cluster barrier, and all add the eight partials in rank
+// order.  Same arithmetic as above except for the order in which the squares are added.
+constexpr int kRowNormCtas = 8;
 
-// (The loads of up to four slices are issued together: one round trip, not one per slice.  A slice
-// past the last one reads the last one again and adds nothing.)
-__device__ __forceinline__ float split_value(const SplitSource& source, int row, int column) {
-    const size_t stride = static_cast<size_t>(source.batch) * source.width;
-    const float* at = source.sums + static_cast<size_t>(row) * source.width + column;
-    float total = 0.0f;
-    for (int first = 0; first < source.slices; first += 4) {
-        float part[4];
+template <bool kExchanged>
+__global__ void __cluster_dims__(kRowNormCtas, 1, 1) __launch_bounds__(256)
+    rmsnorm_row_cluster_kernel(const float* __restrict__ partial_sums, int splits, float scale,
+                               __nv_bfloat16* __restrict__ projection, __nv_bfloat16* __restrict__ residual,
+                               const __nv_bfloat16* __restrict__ weight, __nv_bfloat16* __restrict__ output,
+                               __half* __restrict__ staged, int hidden, float epsilon, const TaggedRow exchanged) {
+    pdl_launch_dependents();
+    namespace cg = cooperative_groups;
+    cg::cluster_group cluster = cg::this_cluster();
+    __shared__ float scratch[256 / 32];
+    __shared__ float partials[kRowNormCtas];
+    const int rank = static_cast<int>(cluster.block_rank());
+    const int items_per_cta = hidden / (4 * kRowNormCtas);
+    const bool active = static_cast<int>(threadIdx.x) < items_per_cta;
+    const int item = rank * items_per_cta + threadIdx.x;
+    uint2 gains = make_uint2(0u, 0u);
+    if (active) {
+        gains = *reinterpret_cast<const uint2*>(weight + 4 * item);  // static: fetched before the wait
+    }
+    pdl_wait();
+    float x[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+    float sum = 0.0f;
+    if (active) {
+        uint2 res = make_uint2(0u, 0u);
+        if (residual != nullptr) {
+            res = *reinterpret_cast<const uint2*>(residual + 4 * item);
+        }
+        float4 total = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        if (kExchanged) {
+            total = tagged_sum4(exchanged, exchange_tag(exchanged.epoch, exchanged.instance), 4 * item);
+        } else {
+            for (int first = 0; first < splits; first += 8) {
+                float4 part[8];
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            part[j] = __ldcg(at + min(first + j, source.slices - 1) * stride);
+                for (int j = 0; j < 8; ++j) {
+                    part[j] = __ldcg(reinterpret_cast<const float4*>(
+                        partial_sums + static_cast<size_t>(min(first + j, splits - 1)) * hidden + 4 * item));
+                }
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    if (first + j < splits) {
+                        total.x += part[j].x;
+                        total.y += part[j].y;
+                        total.z += part[j].z;
+                        total.w += part[j].w;
+                    }
+                }
+            }
+        }
+        x[0] = __bfloat162float(__float2bfloat16(total.x * scale));
+        x[1] = __bfloat162float(__float2bfloat16(total.y * scale));
+        x[2] = __bfloat162float(__float2bfloat16(total.z * scale));
+        x[3] = __bfloat162float(__float2bfloat16(total.w * scale));
+        if (projection != nullptr) {
+            __nv_bfloat162 lo = __floats2bfloat162_rn(x[0], x[1]);
+            __nv_bfloat162 hi = __floats2bfloat162_rn(x[2], x[3]);
+            *reinterpret_cast<uint2*>(projection + 4 * item) =
+                make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
+        }
+        if (residual != nullptr) {
+            const float r[4] = {__uint_as_float(res.x << 16), __uint_as_float(res.x & 0xffff0000u),
+                                __uint_as_float(res.y << 16), __uint_as_float(res.y & 0xffff0000u)};
+            __nv_bfloat162 lo = __floats2bfloat162_rn(x[0] + r[0], x[1] + r[1]);
+            __nv_bfloat162 hi = __floats2bfloat162_rn(x[2] + r[2], x[3] + r[3]);
+            const uint2 stored = make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
+            *reinterpret_cast<uint2*>(residual + 4 * item) = stored;
+            x[0] = __uint_as_float(stored.x << 16);
+            x[1] = __uint_as_float(stored.x & 0xffff0000u);
+            x[2] = __uint_as_float(stored.y << 16);
+            x[3] = __uint_as_float(stored.y & 0xffff0000u);
         }
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
-            total += first + j < source.slices ? part[j] : 0.0f;
+            sum = fmaf(x[j], x[j], sum);
         }
     }
-    return __bfloat162float(__float2bfloat16(total * source.scale));
+    const float mine = block_sum(sum, scratch);
+    if (threadIdx.x < kRowNormCtas) {
+        *cluster.map_shared_rank(&partials[rank], threadIdx.x) = mine;  // into CTA threadIdx.x's copy
+    }
+    cluster.sync();
+    float total = 0.0f;
+#pragma unroll
+    for (int r = 0; r < kRowNormCtas; ++r) {
+        total += partials[r];
+    }
+    const float inverse = rsqrtf(total / static_cast<float>(hidden) + epsilon);
+    if (active) {
+        const float g[4] = {__uint_as_float(gains.x << 16), __uint_as_float(gains.x & 0xffff0000u),
+                            __uint_as_float(gains.y << 16), __uint_as_float(gains.y & 0xffff0000u)};
+        __nv_bfloat162 lo = __floats2bfloat162_rn(x[0] * inverse * (1.0f + g[0]), x[1] * inverse * (1.0f + g[1]));
+        __nv_bfloat162 hi = __floats2bfloat162_rn(x[2] * inverse * (1.0f + g[2]), x[3] * inverse * (1.0f + g[3]));
+        const uint2 out = make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
+        if (output != nullptr) {
+            *reinterpret_cast<uint2*>(output + 4 * item) = out;
+        }
+        if (staged != nullptr) {  // one row of [hidden / 8][16][8]
+            *reinterpret_cast<uint2*>(staged + static_cast<size_t>(item >> 1) * 16 * 8 + (item & 1) * 4) =
+                make_uint2(bf16x2_to_f16x2(out.x), bf16x2_to_f16x2(out.y));
+        }
+    }
 }
+
+// hidden a multiple of 256 and at most 8192: hidden / 32 threads per CTA (rounded up to warps)
+template <bool kExchanged>
+cudaError_t launch_row_norm(const float* partial_sums, int splits, float scale, void* projection, void* residual,
+                            const void* weight, void* output, void* staged, int hidden, float epsilon,
+                            const TaggedRow& exchanged, cudaStream_t stream) {
+    cudaLaunchConfig_t config = {};
+    config.gridDim = dim3(kRowNormCtas);
+    config.blockDim = dim3(((hidden / (4 * kRowNormCtas)) + 31) / 32 * 32);
+    config.stream = stream;
+    cudaLaunchAttribute attributes[2];
+    attributes[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attributes[0].val.programmaticStreamSerializationAllowed = 1;
+    attributes[1].id = cudaLaunchAttributeClusterDimension;
+    attributes[1].val.clusterDim.x = kRowNormCtas;
+    attributes[1].val.clusterDim.y = 1;
+    attributes[1].val.clusterDim.z = 1;
+    config.attrs = attributes;
+    config.numAttrs = 2;
+    return cudaLaunchKernelEx(&config, rmsnorm_row_cluster_kernel<kExchanged>, partial_sums, splits, scale,
+                              static_cast<__nv_bfloat16*>(projection), static_cast<__nv_bfloat16*>(residual),
+                              static_cast<const __nv_bfloat16*>(weight), static_cast<__nv_bfloat16*>(output),
+                              static_cast<__half*>(staged), hidden, epsilon, exchanged);
+}
+
+bool row_norm_fits(int hidden) { return hidden % 256 == 0 && hidden <= 8192; }
 
 // fp32 slices -> the projection's bf16 rows, for consumers that read rows: four outputs per thread.
 __global__ void __launch_bounds__(kThreads) sum_slices_kernel(const SplitSource source, __nv_bfloat16* __restrict__ rows) {
     pdl_launch_dependents();
     pdl_wait();
+    const uint32_t tag = split_tag(source);
     const size_t quads = static_cast<size_t>(source.batch) * source.width / 4;
     const size_t stride = static_cast<size_t>(source.batch) * source.width;
     for (size_t quad = static_cast<size_t>(blockIdx.x) * kThreads + threadIdx.x; quad < quads;
          quad += static_cast<size_t>(gridDim.x) * kThreads) {
         float4 total = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-        for (int first = 0; first < source.slices; first += 4) {
+        if (source.tagged.words != nullptr) {
+            total = tagged_sum4(source.tagged, tag, static_cast<int>(4 * quad));
+        }
+        for (int first = 0; source.tagged.words == nullptr && first < source.slices; first += 4) {
             float4 part[4];
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
@@ -324,6 +490,49 @@ __global__ void __launch_bounds__(kThreads) sum_slices_kernel(const SplitSource 
         *reinterpret_cast<uint2*>(rows + 4 * quad) =
             make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
     }
+}
+
+// ---- latency mode: the SwiGLU pair finished on the consumer side ----------------------
+// The gate and up projections of a rank's columns ran as one K-split launch whose slices every rank
+// received ([slice][gate | up] tagged words); this sums them and applies the epilogue of the fused
+// one-GPU kernel (gate and up scaled in fp32, silu(gate) * up rounded once to bf16,
+// cuda/nvfp4.cu:292-318), four outputs per thread, into the staged operand of the down projection.
+__global__ void __launch_bounds__(kThreads) swiglu_combine_kernel(const TaggedRow row, float gate_scale, float up_scale,
+                                                                  __nv_bfloat16* __restrict__ output,
+                                                                  __half* __restrict__ staged, int intermediate) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const uint32_t tag = exchange_tag(row.epoch, row.instance);
+    const int quad = blockIdx.x * kThreads + threadIdx.x;
+    if (4 * quad >= intermediate) {
+        return;
+    }
+    const float4 gate = tagged_sum4(row, tag, 4 * quad);
+    const float4 up = tagged_sum4(row, tag, intermediate + 4 * quad);
+    const float g[4] = {gate.x * gate_scale, gate.y * gate_scale, gate.z * gate_scale, gate.w * gate_scale};
+    const float u[4] = {up.x * up_scale, up.y * up_scale, up.z * up_scale, up.w * up_scale};
+    __nv_bfloat16 rounded[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        rounded[i] = __float2bfloat16(__fdividef(g[i], 1.0f + __expf(-g[i])) * u[i]);
+    }
+    __nv_bfloat162 lo = __halves2bfloat162(rounded[0], rounded[1]);
+    __nv_bfloat162 hi = __halves2bfloat162(rounded[2], rounded[3]);
+    const uint2 out = make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
+    if (output != nullptr) {
+        *reinterpret_cast<uint2*>(output + 4 * quad) = out;
+    }
+    if (staged != nullptr) {  // one row of [intermediate / 8][16][8]
+        *reinterpret_cast<uint2*>(staged + static_cast<size_t>(quad >> 1) * 16 * 8 + (quad & 1) * 4) =
+            make_uint2(bf16x2_to_f16x2(out.x), bf16x2_to_f16x2(out.y));
+    }
+}
+
+// The first kernel of a latency-mode step: a new epoch, hence new tags for every exchange of the step.
+__global__ void exchange_advance_kernel(uint32_t* epoch) {
+    pdl_launch_dependents();
+    pdl_wait();
+    *epoch = *epoch + 1u;
 }
 
 // ---- DeltaNet prepare (cuda/delta_prepare.cu:44-86,168-245), one launch -------------
@@ -432,19 +641,40 @@ __global__ void __launch_bounds__(kDeltaHeadDim) delta_prepare_kernel(
     if (early) {
         pdl_wait();  // the in-projection's outputs
     }
+    const uint32_t tag = split_tag(split);
+    float projected_a = 0.0f, projected_b = 0.0f;
+    if (split.tagged.words != nullptr) {
+        // latency mode: every word this thread needs is asked for at once (channels, a and b; a thread
+        // without an a / b of its own asks for column 0 and drops it)
+        constexpr int kValues = 2 + kMaxValueRatio + 2;
+        int columns[kValues];
+        float sums[kValues];
+#pragma unroll
+        for (int i = 0; i < 2 + kMaxValueRatio; ++i) {
+            columns[i] = i < 2 + ratio ? channel[i] : 0;
+        }
+        columns[kValues - 2] = dimension < ratio ? a_column + head * ratio + dimension : 0;
+        columns[kValues - 1] = dimension < ratio ? b_column + head * ratio + dimension : 0;
+        tagged_sums<kValues>(split.tagged, tag, columns, sums);
+#pragma unroll
+        for (int i = 0; i < 2 + kMaxValueRatio; ++i) {
+            operands[i].current = __bfloat162float(__float2bfloat16(sums[i] * split.scale));
+        }
+        projected_a = __bfloat162float(__float2bfloat16(sums[kValues - 2] * split.scale));
+        projected_b = __bfloat162float(__float2bfloat16(sums[kValues - 1] * split.scale));
+    }
 #pragma unroll
     for (int i = 0; i < 2 + kMaxValueRatio; ++i) {
-        if (i < 2 + ratio) {
-            operands[i].current = split.sums != nullptr ? split_value(split, batch, channel[i])
-                                                        : __bfloat162float(mixed_row[channel[i]]);
+        if (i < 2 + ratio && split.tagged.words == nullptr) {
+            operands[i].current = has_slices(split) ? split_value(split, tag, batch, channel[i])
+                                                    : __bfloat162float(mixed_row[channel[i]]);
         }
     }
-    float projected_a = 0.0f, projected_b = 0.0f;
-    if (dimension < ratio) {
+    if (dimension < ratio && split.tagged.words == nullptr) {
         const size_t gate_read = static_cast<size_t>(batch) * gate_stride + head * ratio + dimension;
-        if (split.sums != nullptr) {
-            projected_a = split_value(split, batch, a_column + head * ratio + dimension);
-            projected_b = split_value(split, batch, b_column + head * ratio + dimension);
+        if (has_slices(split)) {
+            projected_a = split_value(split, tag, batch, a_column + head * ratio + dimension);
+            projected_b = split_value(split, tag, batch, b_column + head * ratio + dimension);
         } else {
             projected_a = __bfloat162float(a_projection[gate_read]);
             projected_b = __bfloat162float(b_projection[gate_read]);
@@ -502,9 +732,9 @@ __global__ void __launch_bounds__(kDeltaHeadDim) gated_rmsnorm_kernel(const floa
     const size_t offset = (static_cast<size_t>(batch) * heads + head) * kDeltaHeadDim + dimension;
     const size_t gate_offset = static_cast<size_t>(batch) * gate_stride + head * kDeltaHeadDim + dimension;
     // issued with the input load, used last
-    const float gate_value = split.sums != nullptr
-                                 ? split_value(split, batch, gate_column + head * kDeltaHeadDim + dimension)
-                                 : __bfloat162float(gate[gate_offset]);
+    const float gate_value = has_slices(split) ? split_value(split, split_tag(split), batch,
+                                                             gate_column + head * kDeltaHeadDim + dimension)
+                                               : __bfloat162float(gate[gate_offset]);
     const float value = __bfloat162float(__float2bfloat16(input[offset]));
     const float sum = block_sum(value * value, scratch);
     const float inverse = rsqrtf(sum / static_cast<float>(kDeltaHeadDim) + epsilon);
@@ -705,11 +935,16 @@ extern "C" int qwc_rmsnorm_bf16_split_staged(const float* partial_sums, int spli
         epsilon <= 0.0f || (reinterpret_cast<uintptr_t>(partial_sums) & 15) != 0) {
         return cudaErrorInvalidValue;
     }
-    return qwc::launch_chained(rmsnorm_split_kernel, dim3(batch), dim3(kSplitNormThreads), 0, stream, partial_sums,
+    if (batch == 1 && row_norm_fits(hidden) && splits <= 64) {
+        return launch_row_norm<false>(partial_sums, splits, 1.0f / weight_global_scale, projection_output, residual,
+                                      weight, output, staged_output, hidden, epsilon, TaggedRow{}, stream);
+    }
+    return qwc::launch_chained(rmsnorm_split_kernel<false>, dim3(batch), dim3(kSplitNormThreads), 0, stream, partial_sums,
                                splits, 1.0f / weight_global_scale, static_cast<__nv_bfloat16*>(projection_output),
                                static_cast<__nv_bfloat16*>(residual),
                                static_cast<const __nv_bfloat16*>(weight), static_cast<__nv_bfloat16*>(output),
-                               static_cast<__half*>(staged_output), batch <= 16 ? 16 : 32, hidden, batch, epsilon);
+                               static_cast<__half*>(staged_output), batch <= 16 ? 16 : 32, hidden, batch, epsilon,
+                               TaggedRow{});
 }
 
 extern "C" int qwc_rmsnorm_bf16(const void* input, void* residual, const void* weight, void* output, int batch,
@@ -844,6 +1079,120 @@ extern "C" int qwc_nvfp4_sum_slices(const float* partial_sums, int slices, float
     const int blocks = static_cast<int>((static_cast<size_t>(batch) * width / 4 + kThreads - 1) / kThreads);
     return qwc::launch_chained(sum_slices_kernel, dim3(blocks < 592 ? blocks : 592), dim3(kThreads), 0, stream, split,
                                static_cast<__nv_bfloat16*>(rows));
+}
+
+// ---- latency mode: consumers of exchanged rows (exchange.cuh) --------------------------
+extern "C" int qwc_exchange_advance(void* epoch, cudaStream_t stream) {
+    if (epoch == nullptr || (reinterpret_cast<uintptr_t>(epoch) & 3) != 0) {
+        return cudaErrorInvalidValue;
+    }
+    return qwc::launch_chained(exchange_advance_kernel, dim3(1), dim3(1), 0, stream, static_cast<uint32_t*>(epoch));
+}
+
+extern "C" size_t qwc_exchange_row_bytes(int width) {
+    if (width <= 0 || width % 4 != 0) {
+        return 0;
+    }
+    return static_cast<size_t>(kExchangeMaxSlices) * width * sizeof(uint2);
+}
+
+namespace {
+bool valid_slices(int slices) { return slices > 0 && slices <= kExchangeMaxSlices; }
+}  // namespace
+
+extern "C" int qwc_rmsnorm_bf16_exchanged(const qwc_exchange_row* row, int slices, float weight_global_scale,
+                                          void* projection_output, void* residual, const void* weight,
+                                          void* output, void* staged_output, int hidden, float epsilon,
+                                          cudaStream_t stream) {
+    int* status = qwc::status_ptr();
+    if (!valid_exchange_row(row) || !valid_slices(slices) || row->width != hidden || !(weight_global_scale > 0.0f) ||
+        weight == nullptr || (output == nullptr && staged_output == nullptr) || hidden <= 0 || hidden % 256 != 0 ||
+        hidden > 4 * kSplitNormThreads * kSplitNormMaxItems || !isfinite(epsilon) || epsilon <= 0.0f ||
+        status == nullptr) {
+        return cudaErrorInvalidValue;
+    }
+    if (row_norm_fits(hidden)) {
+        return launch_row_norm<true>(nullptr, slices, 1.0f / weight_global_scale, projection_output, residual, weight,
+                                     output, staged_output, hidden, epsilon, tagged_row(*row, slices, status), stream);
+    }
+    return qwc::launch_chained(rmsnorm_split_kernel<true>, dim3(1), dim3(kSplitNormThreads), 0, stream,
+                               static_cast<const float*>(nullptr), slices, 1.0f / weight_global_scale,
+                               static_cast<__nv_bfloat16*>(projection_output), static_cast<__nv_bfloat16*>(residual),
+                               static_cast<const __nv_bfloat16*>(weight), static_cast<__nv_bfloat16*>(output),
+                               static_cast<__half*>(staged_output), 16, hidden, 1, epsilon,
+                               tagged_row(*row, slices, status));
+}
+
+extern "C" int qwc_delta_prepare_decode_exchanged(const qwc_exchange_row* row, int slices, float weight_global_scale,
+                                                  int a_column, int b_column, const void* conv_weight,
+                                                  const void* a_log, const void* dt_bias, void* conv_state,
+                                                  const void* state_slots, void* query, void* key, void* value,
+                                                  void* alpha, void* beta, void* kq, int state_capacity,
+                                                  cudaStream_t stream) {
+    const int v_heads = current_shape().delta_value_heads;
+    const int channels = 2 * kDeltaKeyHeads * kDeltaHeadDim + v_heads * kDeltaHeadDim;
+    int* status = qwc::status_ptr();
+    if (!valid_exchange_row(row) || !valid_slices(slices) || row->width < channels || a_column < channels ||
+        b_column < channels || a_column + v_heads > row->width || b_column + v_heads > row->width ||
+        !(weight_global_scale > 0.0f) || status == nullptr) {
+        return cudaErrorInvalidValue;
+    }
+    qwc::SplitSource split = {nullptr, slices, 1, row->width, 1.0f / weight_global_scale};
+    split.tagged = tagged_row(*row, slices, status);
+    return launch_delta_prepare(row, row, row, conv_weight, a_log, dt_bias, conv_state, state_slots, query, key,
+                                value, alpha, beta, kq, state_capacity, 1, row->width, row->width, split, a_column,
+                                b_column, true, stream);
+}
+
+extern "C" int qwc_delta_gated_rmsnorm_exchanged(const float* input, const qwc_exchange_row* row, int slices,
+                                                 float weight_global_scale, int gate_column, const void* weight,
+                                                 void* output, void* staged_output, float epsilon,
+                                                 cudaStream_t stream) {
+    const int heads = current_shape().delta_value_heads;
+    int* status = qwc::status_ptr();
+    if (input == nullptr || !valid_exchange_row(row) || !valid_slices(slices) || gate_column < 0 ||
+        gate_column + heads * kDeltaHeadDim > row->width || !(weight_global_scale > 0.0f) || weight == nullptr ||
+        (output == nullptr && staged_output == nullptr) || !isfinite(epsilon) || epsilon <= 0.0f ||
+        status == nullptr) {
+        return cudaErrorInvalidValue;
+    }
+    SplitSource split = {nullptr, slices, 1, row->width, 1.0f / weight_global_scale};
+    split.tagged = tagged_row(*row, slices, status);
+    const dim3 grid(heads, 1);
+    return qwc::launch_chained(gated_rmsnorm_kernel, dim3(grid), dim3(kDeltaHeadDim), 0, stream, input,
+                               static_cast<const __nv_bfloat16*>(nullptr), static_cast<const __nv_bfloat16*>(weight),
+                               static_cast<__nv_bfloat16*>(output), static_cast<__half*>(staged_output), 16, epsilon,
+                               row->width, heads, split, gate_column);
+}
+
+extern "C" int qwc_nvfp4_sum_exchanged(const qwc_exchange_row* row, int slices, float weight_global_scale,
+                                       void* rows, cudaStream_t stream) {
+    int* status = qwc::status_ptr();
+    if (!valid_exchange_row(row) || !valid_slices(slices) || !(weight_global_scale > 0.0f) || rows == nullptr ||
+        (reinterpret_cast<uintptr_t>(rows) & 7) != 0 || status == nullptr) {
+        return cudaErrorInvalidValue;
+    }
+    SplitSource split = {nullptr, slices, 1, row->width, 1.0f / weight_global_scale};
+    split.tagged = tagged_row(*row, slices, status);
+    const int blocks = (row->width / 4 + kThreads - 1) / kThreads;
+    return qwc::launch_chained(sum_slices_kernel, dim3(blocks), dim3(kThreads), 0, stream, split,
+                               static_cast<__nv_bfloat16*>(rows));
+}
+
+extern "C" int qwc_swiglu_combine_exchanged(const qwc_exchange_row* row, int slices, float gate_global_scale,
+                                            float up_global_scale, void* output, void* staged_output,
+                                            int intermediate, cudaStream_t stream) {
+    int* status = qwc::status_ptr();
+    if (!valid_exchange_row(row) || !valid_slices(slices) || intermediate <= 0 || intermediate % 8 != 0 ||
+        row->width != 2 * intermediate || !(gate_global_scale > 0.0f) || !(up_global_scale > 0.0f) ||
+        (output == nullptr && staged_output == nullptr) || (reinterpret_cast<uintptr_t>(output) & 7) != 0 ||
+        (reinterpret_cast<uintptr_t>(staged_output) & 15) != 0 || status == nullptr) {
+        return cudaErrorInvalidValue;
+    }
+    const int blocks = (intermediate / 4 + kThreads - 1) / kThreads;
+    return qwc::launch_chained(swiglu_combine_kernel, dim3(blocks), dim3(kThreads), 0, stream,
+                               tagged_row(*row, slices, status), 1.0f / gate_global_scale, 1.0f / up_global_scale,
+                               static_cast<__nv_bfloat16*>(output), static_cast<__half*>(staged_output), intermediate);
 }
 
 extern "C" int qwc_delta_gated_rmsnorm(const float* input, const void* gate, const void* weight, void* output,

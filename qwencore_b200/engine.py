@@ -45,7 +45,7 @@ class EngineConfig(ctypes.Structure):
                 ("intermediate", c_int), ("vocab", c_int), ("delta_value_heads", c_int), ("kv_page_size", c_int),
                 ("max_batch", c_int), ("max_context", c_int), ("kv_pool_blocks", c_int), ("state_slots", c_int),
                 ("seed", ctypes.c_ulonglong), ("split_rank", c_int), ("split_size", c_int), ("use_graph", c_int),
-                ("attention_partitions", c_int), ("write_logits", c_int)]
+                ("attention_partitions", c_int), ("write_logits", c_int), ("exchange", c_int)]
 
 
 class StepTraffic(ctypes.Structure):
@@ -90,6 +90,8 @@ ENGINE_SYMBOLS = {
     "qwc_engine_destroy": (None, [P]),
     "qwc_engine_nccl_unique_id": (c_int, [P]),
     "qwc_engine_init_split": (c_int, [P, P]),
+    "qwc_engine_exchange_handle": (c_int, [P, P]),
+    "qwc_engine_open_peers": (c_int, [P, P, c_int]),
     "qwc_engine_tensor": (c_int, [P, c_char_p, c_int, POINTER(P), POINTER(c_size_t)]),
     "qwc_engine_trace_layers": (c_int, [P, c_int]),
     "qwc_engine_read": (c_int, [P, c_char_p, c_int, P, c_size_t]),
@@ -385,6 +387,37 @@ class Engine:
         code = lib.qwc_engine_init_split(self._handle, buffer)
         if code != 0:
             raise abi.QwcError(code, "qwc_engine_init_split")
+
+
+    def exchange_handle(self) -> bytes:
+        """The 64-byte inter-process handle of this rank's exchange block (fused latency mode)."""
+        buffer = ctypes.create_string_buffer(64)
+        code = lib.qwc_engine_exchange_handle(self._handle, buffer)
+        if code != 0:
+            raise abi.QwcError(code, "qwc_engine_exchange_handle")
+        return buffer.raw
+
+    def open_peers(self, handles) -> None:
+        """Maps the other ranks' exchange blocks; `handles`: every rank's exchange_handle(), in rank order."""
+        joined = b"".join(handles)
+        buffer = ctypes.create_string_buffer(joined, len(joined))
+        code = lib.qwc_engine_open_peers(self._handle, buffer, len(handles))
+        if code != 0:
+            raise abi.QwcError(code, "qwc_engine_open_peers")
+
+
+def connect_exchange(engine, group=None) -> None:
+    """Fused latency mode, set-up over torch.distributed (any backend; gloo is enough): every rank
+    contributes the handle of its exchange block and maps the others', in rank order."""
+    import torch.distributed as dist
+
+    world = dist.get_world_size(group)
+    handles = [None] * world
+    dist.all_gather_object(handles, engine.exchange_handle(), group=group)
+    if any(not isinstance(h, bytes) or len(h) != 64 for h in handles):
+        raise ValueError("every rank must contribute a 64-byte handle")
+    engine.open_peers(handles)
+    dist.barrier(group)  # nobody steps before everybody has mapped everybody
 
 
 def nccl_unique_id() -> bytes:

@@ -1,7 +1,9 @@
 """One rank of the column-split (latency mode) engine test: run by tests/test_gpu_split.py, one
-process per GPU.  Every rank holds N / G rows of every projection and of the vocabulary head; an
-in-graph all-gather completes each output row.  Rank 0 rebuilds the whole model on the host from
-all ranks' slices, runs the CPU oracle step on it and compares."""
+process per GPU.  Every rank holds N / G rows of every projection and of the vocabulary head.  With
+QWC_SPLIT_EXCHANGE=1 the ranks store their partial sums into one another's memory and the consumers
+sum them (the fused form); with 0 an in-graph ncclAllGather completes each output row.  Rank 0
+rebuilds the whole model on the host from all ranks' slices, runs the CPU oracle step on it and
+compares."""
 
 import os
 import sys
@@ -50,12 +52,17 @@ def main():
     rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
     torch.cuda.set_device(int(os.environ["LOCAL_RANK"]))
     dist.init_process_group("gloo")
+    fused = os.environ.get("QWC_SPLIT_EXCHANGE", "1") == "1"
     config = E.default_config(num_layers=4, vocab=8192, max_batch=1, max_context=512, kv_pool_blocks=64,
-                              state_slots=2, seed=11, use_graph=1, split_rank=rank, split_size=world)
+                              state_slots=2, seed=11, use_graph=1, split_rank=rank, split_size=world,
+                              write_logits=1, exchange=1 if fused else 0)
     engine = E.Engine(config)
-    unique = [E.nccl_unique_id() if rank == 0 else None]
-    dist.broadcast_object_list(unique, src=0)
-    engine.init_split(unique[0])
+    if fused:
+        E.connect_exchange(engine)
+    else:
+        unique = [E.nccl_unique_id() if rank == 0 else None]
+        dist.broadcast_object_list(unique, src=0)
+        engine.init_split(unique[0])
 
     # every rank's slices of the split tensors, gathered on rank 0
     c = config
@@ -87,15 +94,24 @@ def main():
         cache.append_token(100)
         edits = cache.drain_edits()
         layout = host_layout(cache, [100], 16, 2, (c.max_context + 15) // 16)
+        dist.barrier()  # the ranks step together: a consumer waits a second for its peers, not for the oracle
         sampled = engine.decode(layout["state_slots"], tokens, edits)
         logits = engine.read("logits", 0, np.float32).reshape(c.max_batch, c.vocab)[:1]
+        if fused:
+            logits = logits[:, : c.vocab // world]  # this rank's columns; only the candidates travel
         everyone = [None] * world if rank == 0 else None
         dist.gather_object((sampled.tolist(), logits.tobytes()), everyone, dst=0)
         if rank == 0:
-            # the gathered logits are the same bytes on every rank
-            for other in everyone[1:]:
-                if other != everyone[0]:
-                    failures.append(f"step {step}: ranks disagree")
+            if fused:
+                # every rank picked the same token from everybody's candidates
+                if any(other[0] != everyone[0][0] for other in everyone[1:]):
+                    failures.append(f"step {step}: ranks disagree on the token")
+                logits = np.concatenate([np.frombuffer(other[1], np.float32) for other in everyone]).reshape(1, c.vocab)
+            else:
+                # the gathered logits are the same bytes on every rank
+                for other in everyone[1:]:
+                    if other != everyone[0]:
+                        failures.append(f"step {step}: ranks disagree")
             want_logits, want_tokens, _ = decode_step(model, layout, tokens)
             rms = np.sqrt(np.mean(want_logits.astype(np.float64) ** 2))
             rms_err = np.sqrt(np.mean((logits - want_logits).astype(np.float64) ** 2))

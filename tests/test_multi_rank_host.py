@@ -70,3 +70,41 @@ def test_workload_slice_is_a_function_of_the_rank():
 
     assert bench.contexts_for(3).tolist() == bench.contexts_for(3).tolist()
     assert bench.contexts_for(3).tolist() != bench.contexts_for(4).tolist()
+
+
+# Latency mode's set-up: every rank contributes the handle of its exchange block and receives
+# everybody's in rank order (the device part - mapping the blocks - is the engine's and needs GPUs).
+EXCHANGE_WORKER = r"""
+import json, os, sys
+sys.path.insert(0, os.environ["QWC_ROOT"])
+import torch.distributed as dist
+from qwencore_b200 import engine as E
+
+class FakeEngine:
+    def __init__(self, rank):
+        self.rank, self.opened = rank, None
+    def exchange_handle(self):
+        return bytes([self.rank]) * 64
+    def open_peers(self, handles):
+        self.opened = handles
+
+dist.init_process_group("gloo")
+fake = FakeEngine(dist.get_rank())
+E.connect_exchange(fake)
+print(json.dumps({"rank": fake.rank, "first_bytes": [h[0] for h in fake.opened], "sizes": [len(h) for h in fake.opened]}))
+dist.destroy_process_group()
+"""
+
+
+def test_exchange_handles_arrive_in_rank_order_on_every_rank():
+    processes = []
+    for rank in range(2):
+        env = dict(os.environ, WORLD_SIZE="2", RANK=str(rank), LOCAL_RANK=str(rank), MASTER_ADDR="127.0.0.1",
+                   MASTER_PORT="29643", QWC_ROOT=str(ROOT))
+        processes.append(subprocess.Popen([sys.executable, "-c", EXCHANGE_WORKER], env=env, stdout=subprocess.PIPE,
+                                          stderr=subprocess.PIPE, text=True))
+    for process in processes:
+        out, err = process.communicate(timeout=240)
+        assert process.returncode == 0, err[-2000:]
+        result = json.loads(out.strip().splitlines()[-1])
+        assert result["first_bytes"] == [0, 1] and result["sizes"] == [64, 64]
