@@ -418,8 +418,10 @@ int qwc_fp8_lm_head_batched(const void* weights, const void* row_scales, const v
 int qwc_fp8_max_logits_batch(void);    /* crates/qwc-cuda/src/ffi.rs:142 */
 int qwc_fp8_max_batched_logits(void);  /* crates/qwc-cuda/src/ffi.rs:144 */
 
-/* Two-stage greedy argmax, ties -> lower index.
- * Replaces crates/qwc-cuda/src/ffi.rs:625-634 (cuda/sampling.cu:94-118). */
+/* Greedy argmax, ties -> lower index, NaN never wins.
+ * Replaces crates/qwc-cuda/src/ffi.rs:625-634 (cuda/sampling.cu:94-118) behind its signature.  The
+ * reference runs two launches through the caller's partial arrays; here one launch (a cluster of
+ * eight CTAs per row) does it and partial_values / partial_indices / parts are checked but unused. */
 int qwc_argmax(const float* logits, float* partial_values, uint32_t* partial_indices,
                uint32_t* output, int vocab, int batch, int parts, qwc_stream stream);
 

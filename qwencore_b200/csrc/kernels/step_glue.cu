@@ -177,8 +177,9 @@ __device__ __forceinline__ uint32_t split_tag(const SplitSource& source) {
 
 // (The loads of up to four slices are issued together: one round trip, not one per slice.  A slice
 // past the last one reads the last one again and adds nothing.)
+template <bool kExchanged>
 __device__ __forceinline__ float split_value(const SplitSource& source, uint32_t tag, int row, int column) {
-    if (source.tagged.words != nullptr) {
+    if (kExchanged) {
         return __bfloat162float(__float2bfloat16(tagged_sum(source.tagged, tag, column) * source.scale));
     }
     const size_t stride = static_cast<size_t>(source.batch) * source.width;
@@ -317,14 +318,17 @@ __global__ void __launch_bounds__(kSplitNormThreads) rmsnorm_split_kernel(
     }
 }
 
-// ---- the same for ONE row, spread over a cluster ---------------------------------------
-// With a single activation row the kernel above is one CTA pulling every slice of the row through
-// one SM (8 slices x 5120 x 8 bytes in latency mode: several microseconds of L2 bandwidth of one SM,
-// several times what the arithmetic takes).  Here the row is divided over a cluster of eight CTAs,
-// each summing and normalising hidden / 8 columns (one item of four columns per thread, every slice
-// of it in flight at once); the only thing they share is the sum of squares: each CTA stores its
-// partial into every CTA's shared memory, one cluster barrier, and all add the eight partials in rank
-// order.  Same arithmetic as above except for the order in which the squares are added.
+// ---- the same with every row spread over a cluster -------------------------------------
+// The kernel above is one CTA per row pulling every slice of the row through one SM (in latency mode
+// 8 slices x 5120 x 8 bytes: several microseconds of one SM's L2 bandwidth, several times what the
+// arithmetic takes), and its 640-thread CTAs do not fit on an SM beside a CTA of the projection
+// kernel, so the projection that follows cannot start (and fetch its weights) on those SMs until the
+// norm is over.  Here a row is divided over a cluster of eight CTAs, each summing and normalising
+// hidden / 8 columns (one item of four columns per thread, every slice of it in flight at once, about
+// 5 K registers per CTA: resident beside a projection CTA); the only thing they share is the sum of
+// squares: each CTA stores its partial into every CTA's shared memory, one cluster barrier, and all
+// add the eight partials in rank order.  Same arithmetic as above except for the order in which the
+// squares are added.
 constexpr int kRowNormCtas = 8;
 
 template <bool kExchanged>
@@ -332,13 +336,16 @@ __global__ void __cluster_dims__(kRowNormCtas, 1, 1) __launch_bounds__(256)
     rmsnorm_row_cluster_kernel(const float* __restrict__ partial_sums, int splits, float scale,
                                __nv_bfloat16* __restrict__ projection, __nv_bfloat16* __restrict__ residual,
                                const __nv_bfloat16* __restrict__ weight, __nv_bfloat16* __restrict__ output,
-                               __half* __restrict__ staged, int hidden, float epsilon, const TaggedRow exchanged) {
+                               __half* __restrict__ staged, int padded_rows, int hidden, int batch, float epsilon,
+                               const TaggedRow exchanged) {
     pdl_launch_dependents();
     namespace cg = cooperative_groups;
     cg::cluster_group cluster = cg::this_cluster();
     __shared__ float scratch[256 / 32];
     __shared__ float partials[kRowNormCtas];
     const int rank = static_cast<int>(cluster.block_rank());
+    const int token = blockIdx.y;
+    const size_t row_base = static_cast<size_t>(token) * hidden;
     const int items_per_cta = hidden / (4 * kRowNormCtas);
     const bool active = static_cast<int>(threadIdx.x) < items_per_cta;
     const int item = rank * items_per_cta + threadIdx.x;
@@ -352,7 +359,7 @@ __global__ void __cluster_dims__(kRowNormCtas, 1, 1) __launch_bounds__(256)
     if (active) {
         uint2 res = make_uint2(0u, 0u);
         if (residual != nullptr) {
-            res = *reinterpret_cast<const uint2*>(residual + 4 * item);
+            res = *reinterpret_cast<const uint2*>(residual + row_base + 4 * item);
         }
         float4 total = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
         if (kExchanged) {
@@ -363,7 +370,8 @@ __global__ void __cluster_dims__(kRowNormCtas, 1, 1) __launch_bounds__(256)
 #pragma unroll
                 for (int j = 0; j < 8; ++j) {
                     part[j] = __ldcg(reinterpret_cast<const float4*>(
-                        partial_sums + static_cast<size_t>(min(first + j, splits - 1)) * hidden + 4 * item));
+                        partial_sums + (static_cast<size_t>(min(first + j, splits - 1)) * batch + token) * hidden +
+                        4 * item));
                 }
 #pragma unroll
                 for (int j = 0; j < 8; ++j) {
@@ -383,7 +391,7 @@ __global__ void __cluster_dims__(kRowNormCtas, 1, 1) __launch_bounds__(256)
         if (projection != nullptr) {
             __nv_bfloat162 lo = __floats2bfloat162_rn(x[0], x[1]);
             __nv_bfloat162 hi = __floats2bfloat162_rn(x[2], x[3]);
-            *reinterpret_cast<uint2*>(projection + 4 * item) =
+            *reinterpret_cast<uint2*>(projection + row_base + 4 * item) =
                 make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
         }
         if (residual != nullptr) {
@@ -392,7 +400,7 @@ __global__ void __cluster_dims__(kRowNormCtas, 1, 1) __launch_bounds__(256)
             __nv_bfloat162 lo = __floats2bfloat162_rn(x[0] + r[0], x[1] + r[1]);
             __nv_bfloat162 hi = __floats2bfloat162_rn(x[2] + r[2], x[3] + r[3]);
             const uint2 stored = make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
-            *reinterpret_cast<uint2*>(residual + 4 * item) = stored;
+            *reinterpret_cast<uint2*>(residual + row_base + 4 * item) = stored;
             x[0] = __uint_as_float(stored.x << 16);
             x[1] = __uint_as_float(stored.x & 0xffff0000u);
             x[2] = __uint_as_float(stored.y << 16);
@@ -421,10 +429,11 @@ __global__ void __cluster_dims__(kRowNormCtas, 1, 1) __launch_bounds__(256)
         __nv_bfloat162 hi = __floats2bfloat162_rn(x[2] * inverse * (1.0f + g[2]), x[3] * inverse * (1.0f + g[3]));
         const uint2 out = make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
         if (output != nullptr) {
-            *reinterpret_cast<uint2*>(output + 4 * item) = out;
+            *reinterpret_cast<uint2*>(output + row_base + 4 * item) = out;
         }
-        if (staged != nullptr) {  // one row of [hidden / 8][16][8]
-            *reinterpret_cast<uint2*>(staged + static_cast<size_t>(item >> 1) * 16 * 8 + (item & 1) * 4) =
+        if (staged != nullptr) {  // half of a K core: [hidden / 8][padded rows][8]
+            *reinterpret_cast<uint2*>(staged + (static_cast<size_t>(item >> 1) * padded_rows + token) * 8 +
+                                      (item & 1) * 4) =
                 make_uint2(bf16x2_to_f16x2(out.x), bf16x2_to_f16x2(out.y));
         }
     }
@@ -433,10 +442,10 @@ __global__ void __cluster_dims__(kRowNormCtas, 1, 1) __launch_bounds__(256)
 // hidden a multiple of 256 and at most 8192: hidden / 32 threads per CTA (rounded up to warps)
 template <bool kExchanged>
 cudaError_t launch_row_norm(const float* partial_sums, int splits, float scale, void* projection, void* residual,
-                            const void* weight, void* output, void* staged, int hidden, float epsilon,
+                            const void* weight, void* output, void* staged, int batch, int hidden, float epsilon,
                             const TaggedRow& exchanged, cudaStream_t stream) {
     cudaLaunchConfig_t config = {};
-    config.gridDim = dim3(kRowNormCtas);
+    config.gridDim = dim3(kRowNormCtas, batch);
     config.blockDim = dim3(((hidden / (4 * kRowNormCtas)) + 31) / 32 * 32);
     config.stream = stream;
     cudaLaunchAttribute attributes[2];
@@ -451,12 +460,13 @@ cudaError_t launch_row_norm(const float* partial_sums, int splits, float scale, 
     return cudaLaunchKernelEx(&config, rmsnorm_row_cluster_kernel<kExchanged>, partial_sums, splits, scale,
                               static_cast<__nv_bfloat16*>(projection), static_cast<__nv_bfloat16*>(residual),
                               static_cast<const __nv_bfloat16*>(weight), static_cast<__nv_bfloat16*>(output),
-                              static_cast<__half*>(staged), hidden, epsilon, exchanged);
+                              static_cast<__half*>(staged), batch <= 16 ? 16 : 32, hidden, batch, epsilon, exchanged);
 }
 
 bool row_norm_fits(int hidden) { return hidden % 256 == 0 && hidden <= 8192; }
 
 // fp32 slices -> the projection's bf16 rows, for consumers that read rows: four outputs per thread.
+template <bool kExchanged>
 __global__ void __launch_bounds__(kThreads) sum_slices_kernel(const SplitSource source, __nv_bfloat16* __restrict__ rows) {
     pdl_launch_dependents();
     pdl_wait();
@@ -466,10 +476,10 @@ __global__ void __launch_bounds__(kThreads) sum_slices_kernel(const SplitSource 
     for (size_t quad = static_cast<size_t>(blockIdx.x) * kThreads + threadIdx.x; quad < quads;
          quad += static_cast<size_t>(gridDim.x) * kThreads) {
         float4 total = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
-        if (source.tagged.words != nullptr) {
+        if (kExchanged) {
             total = tagged_sum4(source.tagged, tag, static_cast<int>(4 * quad));
         }
-        for (int first = 0; source.tagged.words == nullptr && first < source.slices; first += 4) {
+        for (int first = 0; !kExchanged && first < source.slices; first += 4) {
             float4 part[4];
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
@@ -574,6 +584,7 @@ __device__ __forceinline__ float conv_finish(const ConvOperands& in, float* __re
 
 constexpr int kMaxValueRatio = 3;  // value heads per key head: 32 / 16 or 48 / 16
 
+template <bool kExchanged>  // the split source is an exchanged row of tagged words (latency mode)
 __global__ void __launch_bounds__(kDeltaHeadDim) delta_prepare_kernel(
     const __nv_bfloat16* __restrict__ mixed_qkv, const __nv_bfloat16* __restrict__ a_projection,
     const __nv_bfloat16* __restrict__ b_projection, const __nv_bfloat16* __restrict__ conv_weight,
@@ -643,7 +654,7 @@ __global__ void __launch_bounds__(kDeltaHeadDim) delta_prepare_kernel(
     }
     const uint32_t tag = split_tag(split);
     float projected_a = 0.0f, projected_b = 0.0f;
-    if (split.tagged.words != nullptr) {
+    if (kExchanged) {
         // latency mode: every word this thread needs is asked for at once (channels, a and b; a thread
         // without an a / b of its own asks for column 0 and drops it)
         constexpr int kValues = 2 + kMaxValueRatio + 2;
@@ -665,16 +676,16 @@ __global__ void __launch_bounds__(kDeltaHeadDim) delta_prepare_kernel(
     }
 #pragma unroll
     for (int i = 0; i < 2 + kMaxValueRatio; ++i) {
-        if (i < 2 + ratio && split.tagged.words == nullptr) {
-            operands[i].current = has_slices(split) ? split_value(split, tag, batch, channel[i])
+        if (i < 2 + ratio && !kExchanged) {
+            operands[i].current = split.sums != nullptr ? split_value<false>(split, tag, batch, channel[i])
                                                     : __bfloat162float(mixed_row[channel[i]]);
         }
     }
-    if (dimension < ratio && split.tagged.words == nullptr) {
+    if (dimension < ratio && !kExchanged) {
         const size_t gate_read = static_cast<size_t>(batch) * gate_stride + head * ratio + dimension;
-        if (has_slices(split)) {
-            projected_a = split_value(split, tag, batch, a_column + head * ratio + dimension);
-            projected_b = split_value(split, tag, batch, b_column + head * ratio + dimension);
+        if (split.sums != nullptr) {
+            projected_a = split_value<false>(split, tag, batch, a_column + head * ratio + dimension);
+            projected_b = split_value<false>(split, tag, batch, b_column + head * ratio + dimension);
         } else {
             projected_a = __bfloat162float(a_projection[gate_read]);
             projected_b = __bfloat162float(b_projection[gate_read]);
@@ -715,6 +726,7 @@ __global__ void __launch_bounds__(kDeltaHeadDim) delta_prepare_kernel(
 }
 
 // ---- gated RMSNorm over value heads (cuda/delta_output.cu:20-64) --------------------
+template <bool kExchanged>
 __global__ void __launch_bounds__(kDeltaHeadDim) gated_rmsnorm_kernel(const float* __restrict__ input,
                                                                       const __nv_bfloat16* __restrict__ gate,
                                                                       const __nv_bfloat16* __restrict__ weight,
@@ -732,7 +744,7 @@ __global__ void __launch_bounds__(kDeltaHeadDim) gated_rmsnorm_kernel(const floa
     const size_t offset = (static_cast<size_t>(batch) * heads + head) * kDeltaHeadDim + dimension;
     const size_t gate_offset = static_cast<size_t>(batch) * gate_stride + head * kDeltaHeadDim + dimension;
     // issued with the input load, used last
-    const float gate_value = has_slices(split) ? split_value(split, split_tag(split), batch,
+    const float gate_value = has_slices(split) ? split_value<kExchanged>(split, split_tag(split), batch,
                                                              gate_column + head * kDeltaHeadDim + dimension)
                                                : __bfloat162float(gate[gate_offset]);
     const float value = __bfloat162float(__float2bfloat16(input[offset]));
@@ -805,91 +817,75 @@ __global__ void __launch_bounds__(kHeadDim) prepare_attention_kernel(
     value_cache[cache_base + dimension] = to_fp8(v * v_inverse);
 }
 
-// ---- greedy argmax (cuda/sampling.cu:11-92) -------------------------------------------
-__device__ __forceinline__ bool better(float value, uint32_t index, float best, uint32_t best_index) {
-    return value > best || (value == best && index < best_index);
+// ---- greedy argmax over fp32 logits -------------------------------------------------------
+// Behind the ABI of cuda/sampling.cu:39-92 (largest logit, ties to the smaller index, NaN never wins,
+// UINT32_MAX for a row without a comparable value), in one launch: a cluster of eight CTAs per row,
+// each scanning an eighth of the row with 16-byte loads; a candidate is one 64-bit key - the logit's
+// bits made monotonic in the high word, the complemented index in the low word - so that "better" is an
+// integer maximum; the eight CTA winners meet in the first CTA's shared memory (one cluster barrier).
+// The caller's partial arrays of the two-launch form are not needed.
+constexpr int kArgmaxCtas = 8;
+
+__device__ __forceinline__ unsigned long long argmax_key(float value, uint32_t index) {
+    const uint32_t raw = __float_as_uint(value);
+    const uint32_t bits = raw == 0x80000000u ? 0u : raw;  // -0 equals +0: the index decides between them
+    const uint32_t ordered = (bits & 0x80000000u) != 0 ? ~bits : bits | 0x80000000u;  // ascending with the value
+    return value != value ? 0ull : (static_cast<unsigned long long>(ordered) << 32) | (0xffffffffu - index);
 }
 
-__device__ void reduce_candidate(float& value, uint32_t& index, float* shared_values, uint32_t* shared_indices) {
-#pragma unroll
-    for (int off = 16; off > 0; off >>= 1) {
-        const float other = __shfl_xor_sync(0xffffffffu, value, off);
-        const uint32_t other_index = __shfl_xor_sync(0xffffffffu, index, off);
-        if (better(other, other_index, value, index)) {
-            value = other;
-            index = other_index;
-        }
-    }
-    const int lane = threadIdx.x & 31;
-    const int warp = threadIdx.x >> 5;
-    if (lane == 0) {
-        shared_values[warp] = value;
-        shared_indices[warp] = index;
-    }
-    __syncthreads();
-    if (warp == 0) {
-        value = lane < (blockDim.x >> 5) ? shared_values[lane] : -INFINITY;
-        index = lane < (blockDim.x >> 5) ? shared_indices[lane] : UINT32_MAX;
-#pragma unroll
-        for (int off = 16; off > 0; off >>= 1) {
-            const float other = __shfl_xor_sync(0xffffffffu, value, off);
-            const uint32_t other_index = __shfl_xor_sync(0xffffffffu, index, off);
-            if (better(other, other_index, value, index)) {
-                value = other;
-                index = other_index;
+__global__ void __cluster_dims__(kArgmaxCtas, 1, 1) __launch_bounds__(kThreads)
+    argmax_cluster_kernel(const float* __restrict__ logits, uint32_t* __restrict__ output, int vocab) {
+    pdl_launch_dependents();
+    namespace cg = cooperative_groups;
+    cg::cluster_group cluster = cg::this_cluster();
+    __shared__ unsigned long long warp_keys[kThreads / 32];
+    __shared__ unsigned long long cta_keys[kArgmaxCtas];
+    pdl_wait();
+    const int row_index = blockIdx.y;
+    const int rank = static_cast<int>(cluster.block_rank());
+    const float* row = logits + static_cast<size_t>(row_index) * vocab;
+    const int span = ((vocab + kArgmaxCtas - 1) / kArgmaxCtas + 3) & ~3;
+    const int begin = rank * span;
+    const int end = min(vocab, begin + span);
+    unsigned long long best = 0ull;
+    if ((reinterpret_cast<uintptr_t>(row) & 15) == 0) {
+        for (int column = begin + 4 * threadIdx.x; column < end; column += 4 * kThreads) {
+            if (column + 4 <= end) {
+                const float4 v = __ldcs(reinterpret_cast<const float4*>(row + column));
+                best = max(best, max(max(argmax_key(v.x, column), argmax_key(v.y, column + 1)),
+                                     max(argmax_key(v.z, column + 2), argmax_key(v.w, column + 3))));
+            } else {
+                for (int c = column; c < end; ++c) {
+                    best = max(best, argmax_key(row[c], c));
+                }
             }
         }
-    }
-}
-
-__global__ void __launch_bounds__(kThreads) argmax_parts_kernel(const float* __restrict__ logits,
-                                                                float* __restrict__ partial_values,
-                                                                uint32_t* __restrict__ partial_indices, int vocab) {
-    pdl_launch_dependents();
-    pdl_wait();
-    __shared__ float shared_values[kThreads / 32];
-    __shared__ uint32_t shared_indices[kThreads / 32];
-    const int batch = blockIdx.y;
-    const float* row = logits + static_cast<size_t>(batch) * vocab;
-    float best = -INFINITY;
-    uint32_t best_index = UINT32_MAX;
-    for (int column = blockIdx.x * kThreads + threadIdx.x; column < vocab; column += gridDim.x * kThreads) {
-        const float value = row[column];
-        if (better(value, static_cast<uint32_t>(column), best, best_index)) {
-            best = value;
-            best_index = static_cast<uint32_t>(column);
+    } else {
+        for (int column = begin + threadIdx.x; column < end; column += kThreads) {
+            best = max(best, argmax_key(row[column], column));
         }
     }
-    reduce_candidate(best, best_index, shared_values, shared_indices);
-    if (threadIdx.x == 0) {
-        const size_t offset = static_cast<size_t>(batch) * gridDim.x + blockIdx.x;
-        partial_values[offset] = best;
-        partial_indices[offset] = best_index;
+#pragma unroll
+    for (int offset = 16; offset > 0; offset >>= 1) {
+        best = max(best, __shfl_xor_sync(0xffffffffu, best, offset));
     }
-}
-
-__global__ void __launch_bounds__(kThreads) argmax_reduce_kernel(const float* __restrict__ partial_values,
-                                                                 const uint32_t* __restrict__ partial_indices,
-                                                                 uint32_t* __restrict__ output, int parts) {
-    pdl_launch_dependents();
-    pdl_wait();
-    __shared__ float shared_values[kThreads / 32];
-    __shared__ uint32_t shared_indices[kThreads / 32];
-    const int batch = blockIdx.x;
-    float best = -INFINITY;
-    uint32_t best_index = UINT32_MAX;
-    for (int part = threadIdx.x; part < parts; part += kThreads) {
-        const size_t offset = static_cast<size_t>(batch) * parts + part;
-        const float value = partial_values[offset];
-        const uint32_t index = partial_indices[offset];
-        if (better(value, index, best, best_index)) {
-            best = value;
-            best_index = index;
+    if ((threadIdx.x & 31) == 0) {
+        warp_keys[threadIdx.x >> 5] = best;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        for (int w = 1; w < kThreads / 32; ++w) {
+            best = max(best, warp_keys[w]);
         }
+        *cluster.map_shared_rank(&cta_keys[rank], 0) = best;
     }
-    reduce_candidate(best, best_index, shared_values, shared_indices);
-    if (threadIdx.x == 0) {
-        output[batch] = best_index;
+    cluster.sync();
+    if (rank == 0 && threadIdx.x == 0) {
+        unsigned long long winner = 0ull;
+        for (int r = 0; r < kArgmaxCtas; ++r) {
+            winner = max(winner, cta_keys[r]);
+        }
+        output[row_index] = 0xffffffffu - static_cast<uint32_t>(winner & 0xffffffffull);
     }
 }
 
@@ -935,9 +931,9 @@ extern "C" int qwc_rmsnorm_bf16_split_staged(const float* partial_sums, int spli
         epsilon <= 0.0f || (reinterpret_cast<uintptr_t>(partial_sums) & 15) != 0) {
         return cudaErrorInvalidValue;
     }
-    if (batch == 1 && row_norm_fits(hidden) && splits <= 64) {
+    if (batch == 1 && row_norm_fits(hidden)) {  // one row: spread over a cluster (several rows fill the SMs as they are)
         return launch_row_norm<false>(partial_sums, splits, 1.0f / weight_global_scale, projection_output, residual,
-                                      weight, output, staged_output, hidden, epsilon, TaggedRow{}, stream);
+                                      weight, output, staged_output, batch, hidden, epsilon, TaggedRow{}, stream);
     }
     return qwc::launch_chained(rmsnorm_split_kernel<false>, dim3(batch), dim3(kSplitNormThreads), 0, stream, partial_sums,
                                splits, 1.0f / weight_global_scale, static_cast<__nv_bfloat16*>(projection_output),
@@ -1020,7 +1016,8 @@ int launch_delta_prepare(const void* mixed_qkv, const void* a_projection, const 
         return cudaErrorInvalidValue;
     }
     const dim3 grid(kDeltaKeyHeads, batch);
-    return qwc::launch_chained(delta_prepare_kernel, dim3(grid), dim3(kDeltaHeadDim), 0, stream, 
+    return qwc::launch_chained(split.tagged.words != nullptr ? delta_prepare_kernel<true> : delta_prepare_kernel<false>,
+                               dim3(grid), dim3(kDeltaHeadDim), 0, stream,
         static_cast<const __nv_bfloat16*>(mixed_qkv), static_cast<const __nv_bfloat16*>(a_projection),
         static_cast<const __nv_bfloat16*>(b_projection), static_cast<const __nv_bfloat16*>(conv_weight),
         static_cast<const __nv_bfloat16*>(a_log), static_cast<const __nv_bfloat16*>(dt_bias),
@@ -1041,7 +1038,7 @@ extern "C" int qwc_delta_gated_rmsnorm_staged(const float* input, const void* ga
         return cudaErrorInvalidValue;
     }
     const dim3 grid(heads, batch);
-    return qwc::launch_chained(gated_rmsnorm_kernel, dim3(grid), dim3(kDeltaHeadDim), 0, stream,
+    return qwc::launch_chained(gated_rmsnorm_kernel<false>, dim3(grid), dim3(kDeltaHeadDim), 0, stream,
         input, static_cast<const __nv_bfloat16*>(gate), static_cast<const __nv_bfloat16*>(weight),
         static_cast<__nv_bfloat16*>(output), static_cast<__half*>(staged_output), batch <= 16 ? 16 : 32, epsilon,
         gate_stride, heads, SplitSource{}, 0);
@@ -1061,7 +1058,7 @@ extern "C" int qwc_delta_gated_rmsnorm_split(const float* input, const float* pa
     }
     const SplitSource split = {partial_sums, slices, batch, width, 1.0f / weight_global_scale};
     const dim3 grid(heads, batch);
-    return qwc::launch_chained(gated_rmsnorm_kernel, dim3(grid), dim3(kDeltaHeadDim), 0, stream,
+    return qwc::launch_chained(gated_rmsnorm_kernel<false>, dim3(grid), dim3(kDeltaHeadDim), 0, stream,
         input, static_cast<const __nv_bfloat16*>(nullptr), static_cast<const __nv_bfloat16*>(weight),
         static_cast<__nv_bfloat16*>(output), static_cast<__half*>(staged_output), batch <= 16 ? 16 : 32, epsilon,
         width, heads, split, gate_column);
@@ -1077,7 +1074,7 @@ extern "C" int qwc_nvfp4_sum_slices(const float* partial_sums, int slices, float
     }
     const SplitSource split = {partial_sums, slices, batch, width, 1.0f / weight_global_scale};
     const int blocks = static_cast<int>((static_cast<size_t>(batch) * width / 4 + kThreads - 1) / kThreads);
-    return qwc::launch_chained(sum_slices_kernel, dim3(blocks < 592 ? blocks : 592), dim3(kThreads), 0, stream, split,
+    return qwc::launch_chained(sum_slices_kernel<false>, dim3(blocks < 592 ? blocks : 592), dim3(kThreads), 0, stream, split,
                                static_cast<__nv_bfloat16*>(rows));
 }
 
@@ -1113,7 +1110,8 @@ extern "C" int qwc_rmsnorm_bf16_exchanged(const qwc_exchange_row* row, int slice
     }
     if (row_norm_fits(hidden)) {
         return launch_row_norm<true>(nullptr, slices, 1.0f / weight_global_scale, projection_output, residual, weight,
-                                     output, staged_output, hidden, epsilon, tagged_row(*row, slices, status), stream);
+                                     output, staged_output, 1, hidden, epsilon, tagged_row(*row, slices, status),
+                                     stream);
     }
     return qwc::launch_chained(rmsnorm_split_kernel<true>, dim3(1), dim3(kSplitNormThreads), 0, stream,
                                static_cast<const float*>(nullptr), slices, 1.0f / weight_global_scale,
@@ -1159,7 +1157,7 @@ extern "C" int qwc_delta_gated_rmsnorm_exchanged(const float* input, const qwc_e
     SplitSource split = {nullptr, slices, 1, row->width, 1.0f / weight_global_scale};
     split.tagged = tagged_row(*row, slices, status);
     const dim3 grid(heads, 1);
-    return qwc::launch_chained(gated_rmsnorm_kernel, dim3(grid), dim3(kDeltaHeadDim), 0, stream, input,
+    return qwc::launch_chained(gated_rmsnorm_kernel<true>, dim3(grid), dim3(kDeltaHeadDim), 0, stream, input,
                                static_cast<const __nv_bfloat16*>(nullptr), static_cast<const __nv_bfloat16*>(weight),
                                static_cast<__nv_bfloat16*>(output), static_cast<__half*>(staged_output), 16, epsilon,
                                row->width, heads, split, gate_column);
@@ -1175,7 +1173,7 @@ extern "C" int qwc_nvfp4_sum_exchanged(const qwc_exchange_row* row, int slices, 
     SplitSource split = {nullptr, slices, 1, row->width, 1.0f / weight_global_scale};
     split.tagged = tagged_row(*row, slices, status);
     const int blocks = (row->width / 4 + kThreads - 1) / kThreads;
-    return qwc::launch_chained(sum_slices_kernel, dim3(blocks), dim3(kThreads), 0, stream, split,
+    return qwc::launch_chained(sum_slices_kernel<true>, dim3(blocks), dim3(kThreads), 0, stream, split,
                                static_cast<__nv_bfloat16*>(rows));
 }
 
@@ -1262,14 +1260,24 @@ extern "C" int qwc_fp8_lm_head(const void* weights, const void* row_scales, cons
 
 extern "C" int qwc_argmax(const float* logits, float* partial_values, uint32_t* partial_indices, uint32_t* output,
                           int vocab, int batch, int parts, cudaStream_t stream) {
+    // partial_values / partial_indices / parts belong to the two-launch form of the reference's signature:
+    // checked as that form would, not used.
     if (logits == nullptr || partial_values == nullptr || partial_indices == nullptr || output == nullptr ||
         vocab <= 0 || batch <= 0 || batch > kMaxDecodeBatch || parts <= 0 || parts > kThreads) {
         return cudaErrorInvalidValue;
     }
-    const dim3 grid(parts, batch);
-    const cudaError_t launched = qwc::launch_chained(argmax_parts_kernel, dim3(grid), dim3(kThreads), 0, stream, logits, partial_values, partial_indices, vocab);
-    if (launched != cudaSuccess) {
-        return launched;
-    }
-    return qwc::launch_chained(argmax_reduce_kernel, dim3(batch), dim3(kThreads), 0, stream, partial_values, partial_indices, output, parts);
+    cudaLaunchConfig_t config = {};
+    config.gridDim = dim3(kArgmaxCtas, batch);
+    config.blockDim = dim3(kThreads);
+    config.stream = stream;
+    cudaLaunchAttribute attributes[2];
+    attributes[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attributes[0].val.programmaticStreamSerializationAllowed = 1;
+    attributes[1].id = cudaLaunchAttributeClusterDimension;
+    attributes[1].val.clusterDim.x = kArgmaxCtas;
+    attributes[1].val.clusterDim.y = 1;
+    attributes[1].val.clusterDim.z = 1;
+    config.attrs = attributes;
+    config.numAttrs = 2;
+    return cudaLaunchKernelEx(&config, argmax_cluster_kernel, logits, output, vocab);
 }

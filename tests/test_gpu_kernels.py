@@ -480,17 +480,27 @@ def test_argmax_ties_go_to_lower_index(cuda, ops):
     """crates/qwc-cuda/tests/sampling.rs:19-27"""
     torch = cuda
     vocab = 151936
-    logits = np.full((3, vocab), -2.0, dtype=np.float32)
+    logits = np.full((7, vocab), -2.0, dtype=np.float32)
     logits[0, [150000, 77, 9000]] = 5.0
     logits[1, vocab - 1] = 1.0
     logits[2, :] = 0.25
+    # what `value > best || (value == best && index < best_index)` does with the special values
+    # (cuda/sampling.cu:11-14): a NaN never wins, -inf is an ordinary smallest value, -0 equals +0
+    logits[3, :] = np.nan
+    logits[4, :] = -np.inf
+    logits[4, 5] = np.nan
+    logits[5, :] = -np.inf
+    logits[5, [70000, 120001]] = -3.0e38
+    logits[6, :] = -1.0
+    logits[6, 9] = 0.0
+    logits[6, 4] = -0.0
     parts = 256
-    pv = torch.zeros(3 * parts, dtype=torch.float32, device="cuda")
-    pi = u32_out(torch, 3 * parts)
-    tokens = u32_out(torch, 3)
-    ops.argmax(dev(torch, logits), pv, pi, tokens, vocab, 3, parts)
+    pv = torch.zeros(7 * parts, dtype=torch.float32, device="cuda")
+    pi = u32_out(torch, 7 * parts)
+    tokens = u32_out(torch, 7)
+    ops.argmax(dev(torch, logits), pv, pi, tokens, vocab, 7, parts)
     torch.cuda.synchronize()
-    assert host(tokens).tolist() == [77, vocab - 1, 0]
+    assert host(tokens).tolist() == [77, vocab - 1, 0, 0xFFFFFFFF, 0, 70000, 4]
 
 
 @pytest.mark.parametrize("v_heads", [32, 48])
