@@ -322,8 +322,12 @@ def time_replays(engine, group, stream, steps, rows):
     return begin.elapsed_time(end) * 1e-3
 
 
+def traffic_launches(engine):
+    return engine.traffic(1, float(C1_CONTEXT)).gemv_launches_per_step
+
+
 def time_latency_engine(args, group, local_rank, fused):
-    """One latency-mode engine (fused peer stores, or the library all-gather): ms per step as the max
+    """One latency-mode engine (fused peer loads, or the library all-gather): ms per step as the max
     over ranks, every rank's tokens of the warm-up steps, and the traffic model."""
     import torch
 
@@ -362,6 +366,26 @@ def time_latency_engine(args, group, local_rank, fused):
         produced.append(float(token[0]))
     stream = torch.cuda.ExternalStream(engine.stream)
     seconds = group.max_over_ranks(time_replays(engine, group, stream, steps, 1))
+    waits = None
+    if fused:
+        # After the timed region, three more steps with the wait bookkeeping on: per exchange of the step,
+        # the longest a consumer thread of this rank waited for a peer's word.  The bookkeeping is an atomic
+        # per late word and lengthens the waits it measures, so these are upper bounds and never timed.
+        engine_module.profile_waits(engine, True)
+        for _ in range(3):
+            cache.append_token(1)
+            group.barrier()
+            token = engine.decode(slot, token, cache.drain_edits())
+        nanoseconds = engine_module.exchange_waits(engine).astype(np.float64)
+        engine_module.profile_waits(engine, False)
+        count = int(traffic_launches(engine)) + 1
+        waits = {"bookkeeping": "on for these three steps only; perturbs what it measures (upper bounds)",
+                 "sum_of_longest_us": round(float(nanoseconds.sum()) / 1e3, 1),
+                 "over_5us": int((nanoseconds > 5e3).sum()),
+                 "mean_us_by_exchange_of_a_layer": [round(float(np.mean(nanoseconds[i:count - 1:4])) / 1e3, 1)
+                                                    for i in range(4)]}
+        sums = group.gather([waits["sum_of_longest_us"]])
+        waits["sum_of_longest_us_per_rank"] = [s[0] for s in sums]
     tokens_of_ranks = group.gather(produced)
     traffic = engine.traffic(1, float(C1_CONTEXT))
     # where the step's time goes: one more step launched eagerly with an event between phases (every
@@ -384,20 +408,22 @@ def time_latency_engine(args, group, local_rank, fused):
             graph_phases[prefix.rstrip(".")] = {"ms": round(phase_ms, 4), "launches": launched}
         group.barrier()
     engine.close()
-    return seconds / steps * 1e3, produced, tokens_of_ranks, traffic, status, {"eager": phases, "graph": graph_phases}
+    return (seconds / steps * 1e3, produced, tokens_of_ranks, traffic, status,
+            {"eager": phases, "graph": graph_phases, "waits": waits})
 
 
 def run_latency_mode(args, group, local_rank, single_gpu_ms):
     """Batch 1 with every projection column-split over all ranks of the launch (one sequence, context
     2048): milliseconds per step, max over ranks, and the ranks' sampled tokens compared.  The headline
-    is the fused form (projections store their partial sums into the peers' memory, consumers sum
-    them); the same split with an ncclAllGather after every projection is timed beside it."""
+    is the fused form (every projection leaves its partial sums in its rank's block, the consumers read
+    each column from its owner over NVLink); the same split with an ncclAllGather after every
+    projection is timed beside it."""
     world = group.world
     ms, produced, tokens_of_ranks, traffic, status, phases = time_latency_engine(args, group, local_rank, True)
     library_ms, _, library_tokens, _, _, _ = time_latency_engine(args, group, local_rank, False)
     return {"ms_per_step": ms, "tok_s": 1e3 / ms, "vs_1gpu": single_gpu_ms / ms, "gpus": world,
-            "exchange": "partial sums stored into every rank's memory by the projection's epilogue (8-byte "
-                        "tagged words over NVLink), summed by the consuming kernel after a bounded wait; no "
+            "exchange": "partial sums kept by the rank that computed them as 8-byte tagged words; the consuming "
+                        "kernel reads every column from its owner over NVLink and sums after a bounded wait; no "
                         "library collective in the step",
             "exchanges_per_step": int(traffic.gemv_launches_per_step + 1),
             "kernel_launches_per_step": int(traffic.kernel_launches_per_step),
@@ -405,6 +431,7 @@ def run_latency_mode(args, group, local_rank, single_gpu_ms):
             "device_status": int(status),
             "phases_eager_ms_per_step": phases["eager"],
             "phases_graph_ms_per_step": phases["graph"],
+            "waits_for_peers": phases["waits"],
             "library_collective": {"ms_per_step": library_ms, "vs_1gpu": single_gpu_ms / library_ms,
                                    "what": "same split, ncclAllGather after every projection",
                                    "ranks_agree_on_tokens": all(t == library_tokens[0] for t in library_tokens)},

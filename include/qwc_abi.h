@@ -205,13 +205,13 @@ int qwc_fp8_lm_head_staged(const void* weights, const void* row_scales, const vo
  *    ranks * out_features wide, unscaled and uncombined;
  *  - the consumers (qwc_rmsnorm_bf16_exchanged, qwc_delta_prepare_decode_exchanged,
  *    qwc_delta_gated_rmsnorm_exchanged, qwc_nvfp4_sum_exchanged, qwc_swiglu_combine_exchanged) sum
- *    the slices in slice order, exactly as their one-GPU forms do, after a bounded wait for the words
- *    of this step (status code 0x106 in the device status word when a peer's words do not come; the
- *    step's tokens must then be discarded);
+ *    the slices of their own rank's copy in slice order, exactly as their one-GPU forms do, after a
+ *    bounded wait for the words of this step (status code 0x106 in the device status word when a
+ *    peer's words do not come; the step's tokens must then be discarded);
  *  - qwc_fp8_lm_head_exchange scans this rank's vocabulary rows and hands every rank its best
  *    candidates; the token stored in `sampled` is the same on all ranks (ties to the smaller index;
- *    `sampled` NULL: the candidates are stored and no token is picked; `logits`, f32 [vocab_local], may
- *    be NULL and receives this rank's columns only).
+ *    `sampled` NULL: the candidates are stored and no token is picked; `logits`, f32 [vocab_local],
+ *    may be NULL and receives this rank's columns only).
  *
  * All ranks must issue the same sequence of steps (qwc_exchange_advance first in each) with the same
  * instance numbers.  Every rank of a row must use the same slice count, which holds when they call

@@ -157,6 +157,13 @@ int qwc_engine_init_split(qwc_engine* engine, const void* unique_id_128);
  * same sampled token; "logits" holds this rank's vocab / split_size columns only. */
 int qwc_engine_exchange_handle(qwc_engine* engine, void* handle_64);
 int qwc_engine_open_peers(qwc_engine* engine, const void* handles, int count);
+/* Measurement aid of the fused latency mode: for each exchange of the step (in step order; 1024
+ * entries) the longest time, in nanoseconds, that a consumer thread of this rank has waited for a
+ * peer's word since the last call; reads and clears (synchronises the engine's stream). */
+int qwc_engine_exchange_waits(qwc_engine* engine, unsigned long long* nanoseconds, int capacity);
+/* Turns that bookkeeping on or off (off by default: it costs an atomic per word that was waited for,
+ * enough to lengthen the waits; never on in a timed run).  Captured graphs are dropped and rebuilt. */
+int qwc_engine_profile_waits(qwc_engine* engine, int enable);
 
 /* Device pointer and size of a named resident tensor, for tests that read weights and
  * caches back.  Layer-indexed names take the layer number; others ignore it.  Returns 0 or 1. */

@@ -34,6 +34,11 @@ typedef struct qwc_exchange_row {
     int width;                   /* elements of the full row (all ranks' columns), a multiple of 4 */
     uint32_t flags;              /* QWC_EXCHANGE_ANY_TAG: consumers take whatever words are there (for timing a
                                     consumer alone on the words of an earlier step; never in a real step) */
+    void* wait_profile;          /* NULL, or device u64[QWC_EXCHANGE_MAX_INSTANCES]: entry [instance] is raised to the
+                                    longest time, in nanoseconds, that a consumer thread has waited for a word of
+                                    this exchange (the caller zeroes it).  A measurement aid that costs an atomic
+                                    per late word and so lengthens the waits several times over: never in a
+                                    timed run */
 } qwc_exchange_row;
 
 #define QWC_EXCHANGE_ANY_TAG 1u

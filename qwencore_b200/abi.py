@@ -40,7 +40,7 @@ class ExchangeRow(ctypes.Structure):
     one another; pass ctypes.byref(row)."""
 
     _fields_ = [("blocks", c_void_p * 8), ("ranks", c_int), ("rank", c_int), ("epoch", c_void_p),
-                ("instance", ctypes.c_uint32), ("offset", ctypes.c_uint64), ("width", c_int), ("flags", ctypes.c_uint32)]
+                ("instance", ctypes.c_uint32), ("offset", ctypes.c_uint64), ("width", c_int), ("flags", ctypes.c_uint32), ("wait_profile", c_void_p)]
 
 
 # name -> (restype, argtypes); every symbol declared in include/qwc_abi.h

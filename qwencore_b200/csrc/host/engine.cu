@@ -248,6 +248,9 @@ struct qwc_engine {
     std::vector<void*> opened_peers;
     bool peers_ready = false;
     uint32_t* epoch = nullptr;
+    unsigned long long* wait_profile = nullptr;  // [exchange of the step]: longest wait for a peer's word, ns
+    bool profile_waits = false;  // off by default: the bookkeeping itself (atomics on one word per exchange) is
+                                 // slow enough to lengthen the waits it measures
     size_t row_wide = 0, row_hidden[2] = {0, 0}, row_swiglu = 0, row_candidates = 0;  // offsets in the block
 
     // worker loop state
@@ -419,6 +422,7 @@ qwc_exchange_row exchange_row(const qwc_engine* e, size_t offset, uint32_t insta
     row.width = width;
     // a graph of selected phases only (timing): its consumers run on whatever the last whole step left
     row.flags = e->phase_filter != nullptr ? QWC_EXCHANGE_ANY_TAG : 0u;
+    row.wait_profile = e->profile_waits ? e->wait_profile : nullptr;
     return row;
 }
 
@@ -883,6 +887,32 @@ int qwc_engine_exchange_handle(qwc_engine* e, void* handle_64) {
     return 0;
 }
 
+int qwc_engine_profile_waits(qwc_engine* e, int enable) {
+    if (e == nullptr || e->wait_profile == nullptr) {
+        return cudaErrorInvalidValue;
+    }
+    QWC_TRY(cudaStreamSynchronize(e->stream));
+    e->profile_waits = enable != 0;
+    // the row descriptions are baked into captured graphs: drop them
+    for (cudaGraphExec_t& exec : e->graphs) {
+        if (exec != nullptr) {
+            cudaGraphExecDestroy(exec);
+            exec = nullptr;
+        }
+    }
+    return cudaMemset(e->wait_profile, 0, sizeof(unsigned long long) * QWC_EXCHANGE_MAX_INSTANCES);
+}
+
+int qwc_engine_exchange_waits(qwc_engine* e, unsigned long long* nanoseconds, int capacity) {
+    if (e == nullptr || nanoseconds == nullptr || e->wait_profile == nullptr || capacity < QWC_EXCHANGE_MAX_INSTANCES) {
+        return cudaErrorInvalidValue;
+    }
+    QWC_TRY(cudaStreamSynchronize(e->stream));
+    QWC_TRY(cudaMemcpy(nanoseconds, e->wait_profile, sizeof(unsigned long long) * QWC_EXCHANGE_MAX_INSTANCES,
+                       cudaMemcpyDeviceToHost));
+    return cudaMemset(e->wait_profile, 0, sizeof(unsigned long long) * QWC_EXCHANGE_MAX_INSTANCES);
+}
+
 int qwc_engine_open_peers(qwc_engine* e, const void* handles, int count) {
     if (e == nullptr || handles == nullptr || e->exchange_block == nullptr || count != e->cfg.split_size ||
         e->peers_ready) {
@@ -1050,6 +1080,7 @@ int qwc_engine_create(const qwc_engine_config* config, qwc_engine** out) {
             e->exchange_bytes = at;
             QWC_STEP(gpu_alloc_t(e, &e->exchange_block, at, true));
             QWC_STEP(gpu_alloc_t(e, &e->epoch, 4, true));
+            QWC_STEP(gpu_alloc_t(e, &e->wait_profile, QWC_EXCHANGE_MAX_INSTANCES, true));
             e->exchange_blocks[c.split_rank] = e->exchange_block;
             e->peers_ready = c.split_size == 1;  // a single rank exchanges with itself
         }

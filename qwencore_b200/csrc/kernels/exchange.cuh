@@ -1,19 +1,29 @@
 // Latency mode: the rows that ranks hand one another inside a decode step.
 //
-// A projection whose weight rows are split over G ranks leaves, on every rank, fp32 partial rows for
-// its own columns ([slice][width], one row: latency mode is batch 1).  Instead of finishing them
-// locally and gathering the result with a collective, the projection's epilogue stores each partial
-// value straight into every rank's copy of the slice array - its own by a local store, the others'
-// by a store through the peer mapping of their exchange block - and the kernels that consume the row
-// (the residual norm, the DeltaNet prepare step, ...) sum slices exactly as they do on one GPU.
+// A projection whose weight rows are split over G ranks leaves, on every rank, fp32 partial sums for
+// its own columns of the output row ([slice][width], one row: latency mode is batch 1).  Instead of
+// finishing them locally and gathering the result with a collective, the projection's epilogue stores
+// each partial sum straight into every rank's copy of the slice array - its own by a local store, the
+// others' through the peer mapping of their exchange block - and the kernels that consume the row
+// (the residual norm, the DeltaNet prepare step, ...) sum the slices of their own copy exactly as they
+// do on one GPU.
 //
-// There is no flag and no fence: every element travels as one aligned 8-byte word {fp32 bits, tag}, and
-// an 8-byte store is a single access, so a reader that sees the tag sees the value.  The tag names the
-// step and the exchange within it (epoch << 10 | instance; the epoch is a device word that the first
-// kernel of every step advances, equal on all ranks because they run the same steps); whatever an
-// earlier use of the buffer left there carries another tag.  A consumer polls the words it needs until
-// their tags match, with an iteration limit: when it gives up it stores kStatusPeerWait in the sticky
-// status word, uses zero, and every later wait of the step gives up at once.
+// There is no flag and no fence: every element travels as one aligned 8-byte word {fp32 bits, tag},
+// written by one store, so a reader that sees the tag sees the value.  The tag names the step and the
+// exchange within it (epoch << 10 | instance; the epoch is a device word that the first kernel of
+// every step advances, equal on all ranks because they run the same steps); whatever an earlier use
+// of the buffer left there carries another tag.  A consumer polls the words it needs until their tags
+// match, for at most a second: when it gives up it stores kStatusPeerWait in the sticky status word,
+// uses zero, and every later wait of the step gives up at once.
+//
+// Measured alternatives (two B200s, 64 layers, ms per step; the form above: 4.45): consumers that
+// read each column from its owner's block over NVLink instead (stores stay local): 12.7 - a polling
+// load of a peer's memory takes a link round trip and was slow to see new values; a system-scope
+// fence per storing warp after the stores: 7.0 - the fence costs 4 - 10 us at the end of every
+// projection and buys nothing, the stores arrive without it.  (Neither a rotated order of
+// destinations per rank nor a longer back-off between polls changed the step time on four GPUs.)  A per-exchange wait profile (an atomic
+// maximum per word that was waited for) is available for diagnosis but lengthens the waits it
+// measures by an order of magnitude; it is off unless asked for.
 //
 // A buffer may be written for exchange i + 2 or later while a peer still reads exchange i from it: a
 // rank launches the producer of exchange i + 1 only after its consumers of exchange i have completed,
@@ -40,18 +50,17 @@ static_assert((1 << kExchangeTagBits) == QWC_EXCHANGE_MAX_INSTANCES, "the tag ho
 constexpr unsigned long long kExchangeWaitNs = 1000000000ull;  // a consumer waits a second for a peer's words
 constexpr int kExchangeSpinLimit = 1 << 24;  // ... and never more than this many polls, whatever the timer says
 
-// Producer side: where the partial rows go.
+// Producer side: where the partial sums go.
 struct ExchangeTarget {
-    unsigned char* blocks[kMaxPeers];  // every rank's exchange block as this device addresses it; [rank] is its own
-    int ranks;                         // 0: no exchange
-    const uint32_t* epoch;             // device word, advanced once per step
-    uint32_t instance;                 // of this exchange within the step
-    unsigned long long offset;         // of the slice array inside every block, bytes
-    int width;                         // elements of a full row (all ranks' columns)
-    int first_column;                  // where this rank's columns start
+    uint2* copies[kMaxPeers];  // the row [slices][width] in every rank's block as this device addresses it
+    int ranks;                 // 0: no exchange
+    const uint32_t* epoch;     // device word, advanced once per step
+    uint32_t instance;         // of this exchange within the step
+    int width;                 // elements of a full row (all ranks' columns)
+    int first_column;          // where this rank's columns start
 };
 
-// Consumer side: one row as [slices][width] tagged words.
+// Consumer side: this rank's copy of the row, [slices][width] tagged words.
 struct TaggedRow {
     const uint2* words;  // null: not an exchanged row
     int slices;
@@ -60,6 +69,7 @@ struct TaggedRow {
     uint32_t instance;
     int* status;
     uint32_t tag_mask;  // all ones; zero when any tag is accepted (QWC_EXCHANGE_ANY_TAG)
+    unsigned long long* wait_profile;  // null, or [instance]: the longest wait seen, ns
 };
 
 __device__ __forceinline__ uint32_t exchange_tag(const uint32_t* epoch, uint32_t instance) {
@@ -89,12 +99,18 @@ __device__ __forceinline__ uint4 load_tagged_pair(const uint2* at) {  // two nei
 // The slow path of a read: poll one word until its tag matches, for at most kExchangeWaitNs.  Gives up
 // at once when the status word already holds a code (an earlier wait of this step failed: the row
 // will not come).
-static __device__ __noinline__ float await_tagged(const uint2* at, uint32_t tag, int* status) {
+static __device__ __noinline__ float await_tagged(const uint2* at, uint32_t tag, int* status,
+                                                  unsigned long long* wait_profile) {
     unsigned long long start;
     asm volatile("mov.u64 %0, %globaltimer;" : "=l"(start)::"memory");
     for (int spin = 0; spin < kExchangeSpinLimit; ++spin) {
         const uint2 word = load_tagged(at);
         if (word.y == tag) {
+            if (wait_profile != nullptr) {
+                unsigned long long now;
+                asm volatile("mov.u64 %0, %globaltimer;" : "=l"(now)::"memory");
+                atomicMax(wait_profile + (tag & (QWC_EXCHANGE_MAX_INSTANCES - 1)), now - start);
+            }
             return __uint_as_float(word.x);
         }
         if ((spin & 63) == 0) {
@@ -119,9 +135,11 @@ static __device__ __noinline__ float await_tagged(const uint2* at, uint32_t tag,
 template <int kValues>
 __device__ __forceinline__ void tagged_sums(const TaggedRow& row, uint32_t tag, const int (&columns)[kValues],
                                             float (&totals)[kValues]) {
+    const uint2* at[kValues];
 #pragma unroll
     for (int v = 0; v < kValues; ++v) {
         totals[v] = 0.0f;
+        at[v] = row.words + columns[v];
     }
     for (int first = 0; first < row.slices; first += 8) {
         uint2 part[kValues][8];
@@ -129,8 +147,7 @@ __device__ __forceinline__ void tagged_sums(const TaggedRow& row, uint32_t tag, 
         for (int v = 0; v < kValues; ++v) {
 #pragma unroll
             for (int j = 0; j < 8; ++j) {
-                part[v][j] =
-                    load_tagged(row.words + static_cast<size_t>(min(first + j, row.slices - 1)) * row.width + columns[v]);
+                part[v][j] = load_tagged(at[v] + static_cast<size_t>(min(first + j, row.slices - 1)) * row.width);
             }
         }
 #pragma unroll
@@ -140,8 +157,8 @@ __device__ __forceinline__ void tagged_sums(const TaggedRow& row, uint32_t tag, 
                 if (first + j < row.slices) {
                     totals[v] += ((part[v][j].y ^ tag) & row.tag_mask) == 0
                                      ? __uint_as_float(part[v][j].x)
-                                     : await_tagged(row.words + static_cast<size_t>(first + j) * row.width + columns[v],
-                                                    tag, row.status);
+                                     : await_tagged(at[v] + static_cast<size_t>(first + j) * row.width, tag, row.status,
+                                                    row.wait_profile);
                 }
             }
         }
@@ -175,8 +192,9 @@ __device__ __forceinline__ float4 tagged_sum4(const TaggedRow& row, uint32_t tag
                 const uint32_t tags[4] = {part[j][0].y, part[j][0].w, part[j][1].y, part[j][1].w};
 #pragma unroll
                 for (int c = 0; c < 4; ++c) {
-                    total[c] += ((tags[c] ^ tag) & row.tag_mask) == 0 ? __uint_as_float(bits[c])
-                                                                      : await_tagged(from + c, tag, row.status);
+                    total[c] += ((tags[c] ^ tag) & row.tag_mask) == 0
+                                    ? __uint_as_float(bits[c])
+                                    : await_tagged(from + c, tag, row.status, row.wait_profile);
                 }
             }
         }
@@ -203,12 +221,11 @@ inline bool valid_exchange_row(const qwc_exchange_row* row) {
 inline ExchangeTarget exchange_target(const qwc_exchange_row& row, int first_column) {
     ExchangeTarget target = {};
     for (int r = 0; r < row.ranks; ++r) {
-        target.blocks[r] = static_cast<unsigned char*>(row.blocks[r]);
+        target.copies[r] = reinterpret_cast<uint2*>(static_cast<unsigned char*>(row.blocks[r]) + row.offset);
     }
     target.ranks = row.ranks;
     target.epoch = static_cast<const uint32_t*>(row.epoch);
     target.instance = row.instance;
-    target.offset = row.offset;
     target.width = row.width;
     target.first_column = first_column;
     return target;
@@ -223,6 +240,7 @@ inline TaggedRow tagged_row(const qwc_exchange_row& row, int slices, int* status
     tagged.instance = row.instance;
     tagged.status = status;
     tagged.tag_mask = (row.flags & QWC_EXCHANGE_ANY_TAG) != 0 ? 0u : 0xffffffffu;
+    tagged.wait_profile = static_cast<unsigned long long*>(row.wait_profile);
     return tagged;
 }
 

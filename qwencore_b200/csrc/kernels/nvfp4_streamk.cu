@@ -121,7 +121,7 @@ struct StreamKParams {
     float* split_out;
     // Latency mode (one activation row, weight rows split over ranks): the slices go to every rank's
     // exchange block as tagged words instead (exchange.cuh); split_out is null then.
-    ExchangeTarget exchange;
+    ExchangeTarget exchange;  // ranks == 0: not in latency mode
     uint32_t index_offset;  // vocabulary head in latency mode: this rank's first row in the whole vocabulary
     float* candidate_values;     // vocabulary head with sampling: [32][kCandidateSlots]
     uint32_t* candidate_indices;
@@ -861,8 +861,9 @@ __global__ void __launch_bounds__(kThreads, 1)
             const bool rehearsal = batch == 0;
             const int slice = kSplitOut ? cta - pair * p.splits : 0;
             if (p.exchange.ranks > 0) {
-                // one activation row (the first column of the warps that hold the first rows); every
-                // rank's copy of the slice array gets the value, its own included
+                // Latency mode, one activation row (the first column of the warps that hold the first
+                // rows): this rank's columns of the row go to every rank's copy of the slice array, its
+                // own included, as tagged words (exchange.cuh).
                 if (first_token != 0) {
                     return;
                 }
@@ -874,15 +875,12 @@ __global__ void __launch_bounds__(kThreads, 1)
                                             : (pair * kTiles + t) * kTileRows + quarter * 32 + lane;
                     if (row < p.out_features) {
                         // SwiGLU pair: the row is [gate | up], each half holding all ranks' columns
-                        const size_t element = rehearsal ? static_cast<size_t>(lane >> 1)
-                                                         : static_cast<size_t>(slice) * p.exchange.width +
-                                                               (kSwiglu ? t * (p.exchange.width / 2) : 0) +
-                                                               p.exchange.first_column + row;
+                        const size_t element = static_cast<size_t>(slice) * p.exchange.width +
+                                               (kSwiglu ? t * (p.exchange.width / 2) : 0) + p.exchange.first_column +
+                                               row;
                         const float value = stash[(t * kCols) * kStashPitch];
                         for (int r = 0; r < p.exchange.ranks; ++r) {
-                            uint2* const block =
-                                rehearsal ? sink : reinterpret_cast<uint2*>(p.exchange.blocks[r] + p.exchange.offset);
-                            store_tagged(block + element, value, tag);
+                            store_tagged(rehearsal ? sink + (lane >> 1) : p.exchange.copies[r] + element, value, tag);
                         }
                     }
                 }
@@ -1081,9 +1079,8 @@ __global__ void __launch_bounds__(kThreads, 1)
                 const size_t element = static_cast<size_t>(p.exchange.first_column + cta * 4 + quarter) * 2;
                 const uint32_t index = best_index == UINT32_MAX ? UINT32_MAX : best_index + p.index_offset;
                 for (int r = 0; r < p.exchange.ranks; ++r) {
-                    uint2* const block = reinterpret_cast<uint2*>(p.exchange.blocks[r] + p.exchange.offset);
-                    store_tagged(block + element, best_value, tag);
-                    store_tagged(block + element + 1, __uint_as_float(index), tag);
+                    store_tagged(p.exchange.copies[r] + element, best_value, tag);
+                    store_tagged(p.exchange.copies[r] + element + 1, __uint_as_float(index), tag);
                 }
             }
         } else if (sampling && ok && lane < kCols && first_token + lane < 32) {
@@ -1188,14 +1185,15 @@ __global__ void __launch_bounds__(kSampleThreads) sample_exchanged_kernel(const 
     float best = -INFINITY;
     uint32_t best_index = UINT32_MAX;
     for (int i = threadIdx.x; i < slots; i += kSampleThreads) {
-        const uint4 pair = load_tagged_pair(candidates.words + 2 * i);
+        const uint2* at = candidates.words + 2 * i;
+        const uint4 pair = load_tagged_pair(at);
         const float value = ((pair.y ^ tag) & candidates.tag_mask) == 0
                                 ? __uint_as_float(pair.x)
-                                : await_tagged(candidates.words + 2 * i, tag, candidates.status);
+                                : await_tagged(at, tag, candidates.status, candidates.wait_profile);
         const uint32_t index =
             ((pair.w ^ tag) & candidates.tag_mask) == 0
                 ? pair.z
-                : __float_as_uint(await_tagged(candidates.words + 2 * i + 1, tag, candidates.status));
+                : __float_as_uint(await_tagged(at + 1, tag, candidates.status, candidates.wait_profile));
         if (better_candidate(value, index, best, best_index)) {
             best = value;
             best_index = index;
@@ -1590,8 +1588,8 @@ extern "C" int qwc_nvfp4_w4a16_exchange(const void* packed, const void* scales, 
                                         const qwc_exchange_row* row, int out_features, int in_features,
                                         cudaStream_t stream) {
     if (packed == nullptr || scales == nullptr || staged_input == nullptr || !valid_exchange_row(row) ||
-        out_features <= 0 || in_features <= 0 || in_features % 256 != 0 || row->width != row->ranks * out_features ||
-        !aligned16(packed) || !aligned16(scales) || !aligned16(staged_input)) {
+        out_features <= 0 || out_features % 8 != 0 || in_features <= 0 || in_features % 256 != 0 ||
+        row->width != row->ranks * out_features || !aligned16(packed) || !aligned16(scales) || !aligned16(staged_input)) {
         (void)take_next_projection();
         return cudaErrorInvalidValue;
     }
@@ -1611,8 +1609,8 @@ extern "C" int qwc_nvfp4_swiglu_w4a16_exchange(const void* gate_packed, const vo
                                                const qwc_exchange_row* row, int out_features, int in_features,
                                                cudaStream_t stream) {
     if (gate_packed == nullptr || gate_scales == nullptr || up_packed == nullptr || up_scales == nullptr ||
-        staged_input == nullptr || !valid_exchange_row(row) || out_features <= 0 || in_features <= 0 ||
-        in_features % 256 != 0 || row->width != 2 * row->ranks * out_features || !aligned16(gate_packed) ||
+        staged_input == nullptr || !valid_exchange_row(row) || out_features <= 0 || out_features % 8 != 0 ||
+        in_features <= 0 || in_features % 256 != 0 || row->width != 2 * row->ranks * out_features || !aligned16(gate_packed) ||
         !aligned16(gate_scales) || !aligned16(up_packed) || !aligned16(up_scales) || !aligned16(staged_input)) {
         (void)take_next_projection();
         return cudaErrorInvalidValue;

@@ -1108,17 +1108,17 @@ extern "C" int qwc_rmsnorm_bf16_exchanged(const qwc_exchange_row* row, int slice
         status == nullptr) {
         return cudaErrorInvalidValue;
     }
+    const TaggedRow tagged = tagged_row(*row, slices, status);
     if (row_norm_fits(hidden)) {
         return launch_row_norm<true>(nullptr, slices, 1.0f / weight_global_scale, projection_output, residual, weight,
-                                     output, staged_output, 1, hidden, epsilon, tagged_row(*row, slices, status),
-                                     stream);
+                                     output, staged_output, 1, hidden, epsilon, tagged, stream);
     }
     return qwc::launch_chained(rmsnorm_split_kernel<true>, dim3(1), dim3(kSplitNormThreads), 0, stream,
                                static_cast<const float*>(nullptr), slices, 1.0f / weight_global_scale,
                                static_cast<__nv_bfloat16*>(projection_output), static_cast<__nv_bfloat16*>(residual),
                                static_cast<const __nv_bfloat16*>(weight), static_cast<__nv_bfloat16*>(output),
                                static_cast<__half*>(staged_output), 16, hidden, 1, epsilon,
-                               tagged_row(*row, slices, status));
+                               tagged);
 }
 
 extern "C" int qwc_delta_prepare_decode_exchanged(const qwc_exchange_row* row, int slices, float weight_global_scale,
@@ -1187,9 +1187,10 @@ extern "C" int qwc_swiglu_combine_exchanged(const qwc_exchange_row* row, int sli
         (reinterpret_cast<uintptr_t>(staged_output) & 15) != 0 || status == nullptr) {
         return cudaErrorInvalidValue;
     }
+    const TaggedRow tagged = tagged_row(*row, slices, status);
     const int blocks = (intermediate / 4 + kThreads - 1) / kThreads;
-    return qwc::launch_chained(swiglu_combine_kernel, dim3(blocks), dim3(kThreads), 0, stream,
-                               tagged_row(*row, slices, status), 1.0f / gate_global_scale, 1.0f / up_global_scale,
+    return qwc::launch_chained(swiglu_combine_kernel, dim3(blocks), dim3(kThreads), 0, stream, tagged,
+                               1.0f / gate_global_scale, 1.0f / up_global_scale,
                                static_cast<__nv_bfloat16*>(output), static_cast<__half*>(staged_output), intermediate);
 }
 

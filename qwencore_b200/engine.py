@@ -92,6 +92,8 @@ ENGINE_SYMBOLS = {
     "qwc_engine_init_split": (c_int, [P, P]),
     "qwc_engine_exchange_handle": (c_int, [P, P]),
     "qwc_engine_open_peers": (c_int, [P, P, c_int]),
+    "qwc_engine_exchange_waits": (c_int, [P, P, c_int]),
+    "qwc_engine_profile_waits": (c_int, [P, c_int]),
     "qwc_engine_tensor": (c_int, [P, c_char_p, c_int, POINTER(P), POINTER(c_size_t)]),
     "qwc_engine_trace_layers": (c_int, [P, c_int]),
     "qwc_engine_read": (c_int, [P, c_char_p, c_int, P, c_size_t]),
@@ -404,6 +406,22 @@ class Engine:
         code = lib.qwc_engine_open_peers(self._handle, buffer, len(handles))
         if code != 0:
             raise abi.QwcError(code, "qwc_engine_open_peers")
+
+
+def profile_waits(engine, enable: bool) -> None:
+    """Turns the per-exchange wait bookkeeping on or off (drops the captured graphs)."""
+    code = lib.qwc_engine_profile_waits(engine._handle, 1 if enable else 0)
+    if code != 0:
+        raise abi.QwcError(code, "qwc_engine_profile_waits")
+
+
+def exchange_waits(engine) -> np.ndarray:
+    """Per exchange of the step: the longest wait (ns) of a consumer thread for a peer's word since the last call."""
+    waits = np.zeros(1024, dtype=np.uint64)
+    code = lib.qwc_engine_exchange_waits(engine._handle, waits.ctypes.data_as(P), 1024)
+    if code != 0:
+        raise abi.QwcError(code, "qwc_engine_exchange_waits")
+    return waits
 
 
 def connect_exchange(engine, group=None) -> None:
