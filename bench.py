@@ -45,7 +45,7 @@ METRIC = "decode_tokens_per_second"
 C1_CONTEXT = 2048
 # DRAM read + write of one captured projection launch (ncu, 34816 x 5120 at 32 rows) over its
 # algorithmic bytes; every launch streams its matrix once, so the traffic scales with the matrix.
-NCU_TRAFFIC_RATIO = 104.83 / 100.35
+NCU_TRAFFIC_RATIO = 104.49 / 100.35
 
 
 # ---- clocks ---------------------------------------------------------------------------------

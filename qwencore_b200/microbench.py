@@ -140,7 +140,8 @@ def delta(batch: int, value_heads: int, plain: int = 0) -> dict:
     abi.configure(value_heads, abi.get_shape()[1])
     capacity = batch + 1
     state_bytes = capacity * value_heads * 128 * 128
-    layers = max(2, -(-2 * L2_BYTES // state_bytes)) if not plain else 2
+    # (for a profiler: four layers, 140 MB at 32 x 32 heads - more than L2 holds, so that the DRAM counters count)
+    layers = max(2, -(-2 * L2_BYTES // state_bytes)) if not plain else 4
     states = [torch.randint(-127, 128, (capacity, value_heads, 128, 128), dtype=torch.int8, device="cuda")
               for _ in range(layers)]
     scales = [torch.rand((capacity, value_heads, 128), device="cuda") * 0.01 for _ in range(layers)]
@@ -249,6 +250,8 @@ def main(argv=None) -> None:
     parser.add_argument("--plain", type=int, default=0, help="issue this many eager launches and exit (for a profiler)")
     parser.add_argument("--staged", action="store_true",
                         help="projections and the head through the equal-share kernel on staged activations")
+    parser.add_argument("--split", action="store_true",
+                        help="with --staged: the regular K split whose sum is left to the consumer")
     options = parser.parse_args(argv)
     if not torch.cuda.is_available():
         raise SystemExit("a CUDA device is required")
@@ -257,7 +260,7 @@ def main(argv=None) -> None:
     if options.kernel in ("gemv", "swiglu"):
         n, k, m = (int(v) for v in values[:3])
         projection(n, k, m, swiglu=options.kernel == "swiglu", plain=options.plain, hint=options.hint,
-                   staged=options.staged)
+                   staged=options.staged, split=options.split)
     elif options.kernel == "lm_head":
         lm_head(int(values[0]), int(values[1]), int(values[2]), plain=options.plain, staged=options.staged)
     elif options.kernel == "step-projections":
