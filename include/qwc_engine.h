@@ -80,6 +80,14 @@ int qwc_scheduler_next_batch(qwc_scheduler* scheduler, uint32_t* decode_ids, siz
                              qwc_prefill_chunk* prefill, size_t* num_prefill);
 int qwc_scheduler_complete_batch(qwc_scheduler* scheduler, const uint32_t* stopped, size_t num_stopped,
                                  qwc_completion* completed, size_t max_completed, size_t* num_completed);
+/* The same for steps in which decode sequences may have produced more than one token
+ * (Scheduler::complete_batch_multi, crates/qwc-runtime/src/scheduler.rs:392-500): `produced_tokens[i]`
+ * tokens for sequence `produced_ids[i]`; sequences not named count one; zero tokens -> Invariant, a
+ * sequence that is not in the batch's decode list -> InvalidStopped. */
+int qwc_scheduler_complete_batch_multi(qwc_scheduler* scheduler, const uint32_t* stopped, size_t num_stopped,
+                                       const uint32_t* produced_ids, const uint32_t* produced_tokens,
+                                       size_t num_produced, qwc_completion* completed, size_t max_completed,
+                                       size_t* num_completed);
 int qwc_scheduler_abort_batch(qwc_scheduler* scheduler);
 /* *removed receives 1 when the request existed. */
 int qwc_scheduler_cancel(qwc_scheduler* scheduler, uint32_t id, int* removed);

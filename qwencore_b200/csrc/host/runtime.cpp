@@ -336,9 +336,26 @@ SchedulerError Scheduler::next_batch(Batch* out, bool* has_batch) {
 }
 
 SchedulerError Scheduler::complete_batch(const std::vector<SeqId>& stopped, std::vector<Completion>* completed) {
+    return complete_batch_multi(stopped, {}, completed);
+}
+
+// The same, for steps in which a decode sequence may have produced more than one token (speculative
+// verification accepts 1 .. k + 1): sequences missing from `produced` count one token
+// (crates/qwc-runtime/src/scheduler.rs:392-500).
+SchedulerError Scheduler::complete_batch_multi(const std::vector<SeqId>& stopped,
+                                               const std::vector<std::pair<SeqId, size_t>>& produced,
+                                               std::vector<Completion>* completed) {
     completed->clear();
     if (!in_flight_) {
         return SchedulerError::NoBatchInFlight;
+    }
+    for (const auto& entry : produced) {
+        if (entry.second == 0) {
+            return SchedulerError::Invariant;
+        }
+        if (std::find(in_flight_->decode.begin(), in_flight_->decode.end(), entry.first) == in_flight_->decode.end()) {
+            return SchedulerError::InvalidStopped;
+        }
     }
     std::unordered_set<SeqId> stopped_set;
     for (SeqId id : stopped) {
@@ -371,7 +388,14 @@ SchedulerError Scheduler::complete_batch(const std::vector<SeqId>& stopped, std:
             return SchedulerError::Invariant;
         }
         ActiveRequest& active = it->second;
-        active.generated = std::min(active.generated + 1, active.request.max_new_tokens);
+        size_t tokens = 1;
+        for (const auto& entry : produced) {
+            if (entry.first == id) {
+                tokens = entry.second;
+                break;  // the first entry of a sequence counts, as in the reference's `find`
+            }
+        }
+        active.generated = std::min(active.generated + tokens, active.request.max_new_tokens);
         const bool was_stopped = stopped_set.count(id) != 0;
         if (was_stopped || active.generated >= active.request.max_new_tokens) {
             completed->push_back({id, active.generated, was_stopped ? FinishReason::Stopped : FinishReason::Length});

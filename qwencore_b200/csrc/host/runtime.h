@@ -11,6 +11,7 @@
 #include <deque>
 #include <optional>
 #include <unordered_map>
+#include <utility>
 #include <vector>
 
 namespace qwc {
@@ -172,6 +173,9 @@ public:
     // Returns None with *has_batch == false when there is nothing to run.
     SchedulerError next_batch(Batch* batch, bool* has_batch);
     SchedulerError complete_batch(const std::vector<SeqId>& stopped, std::vector<Completion>* completed);
+    SchedulerError complete_batch_multi(const std::vector<SeqId>& stopped,
+                                        const std::vector<std::pair<SeqId, size_t>>& produced,
+                                        std::vector<Completion>* completed);
     SchedulerError abort_batch();
     SchedulerError cancel(SeqId id, bool* removed);
     std::optional<size_t> remaining_tokens(SeqId id) const;

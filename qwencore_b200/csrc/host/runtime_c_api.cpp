@@ -129,6 +129,25 @@ int qwc_scheduler_complete_batch(qwc_scheduler* scheduler, const uint32_t* stopp
     return static_cast<int>(error);
 }
 
+int qwc_scheduler_complete_batch_multi(qwc_scheduler* scheduler, const uint32_t* stopped, size_t num_stopped,
+                                       const uint32_t* produced_ids, const uint32_t* produced_tokens,
+                                       size_t num_produced, qwc_completion* completed, size_t max_completed,
+                                       size_t* num_completed) {
+    std::vector<SeqId> stopped_ids(stopped, stopped + num_stopped);
+    std::vector<std::pair<SeqId, size_t>> produced;
+    for (size_t i = 0; i < num_produced; ++i) {
+        produced.emplace_back(produced_ids[i], static_cast<size_t>(produced_tokens[i]));
+    }
+    std::vector<Completion> done;
+    const SchedulerError error = scheduler->scheduler.complete_batch_multi(stopped_ids, produced, &done);
+    *num_completed = done.size();
+    for (size_t i = 0; i < done.size() && i < max_completed; ++i) {
+        completed[i] = {done[i].id, static_cast<uint32_t>(done[i].generated_tokens),
+                        static_cast<uint32_t>(done[i].reason)};
+    }
+    return static_cast<int>(error);
+}
+
 int qwc_scheduler_abort_batch(qwc_scheduler* scheduler) { return static_cast<int>(scheduler->scheduler.abort_batch()); }
 
 int qwc_scheduler_cancel(qwc_scheduler* scheduler, uint32_t id, int* removed) {

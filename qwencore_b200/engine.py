@@ -77,6 +77,7 @@ ENGINE_SYMBOLS = {
     "qwc_scheduler_submit": (c_int, [P, c_uint32, c_size_t, c_size_t]),
     "qwc_scheduler_next_batch": (c_int, [P, P, POINTER(c_size_t), P, POINTER(c_size_t)]),
     "qwc_scheduler_complete_batch": (c_int, [P, P, c_size_t, P, c_size_t, POINTER(c_size_t)]),
+    "qwc_scheduler_complete_batch_multi": (c_int, [P, P, c_size_t, P, P, c_size_t, P, c_size_t, POINTER(c_size_t)]),
     "qwc_scheduler_abort_batch": (c_int, [P]),
     "qwc_scheduler_cancel": (c_int, [P, c_uint32, POINTER(c_int)]),
     "qwc_scheduler_remaining_tokens": (c_longlong, [P, c_uint32]),
@@ -222,6 +223,20 @@ class Scheduler:
         count = c_size_t()
         code = lib.qwc_scheduler_complete_batch(self._handle, stopped.ctypes.data_as(P), stopped.size, done,
                                                 self.max_num_seqs, byref(count))
+        if code != 0:
+            raise RuntimeError_("SchedulerError", code, SCHEDULER_ERROR)
+        return [(c.id, c.generated_tokens, "Stopped" if c.reason else "Length") for c in done[:count.value]]
+
+    def complete_batch_multi(self, stopped=(), produced=()):
+        """`produced`: (sequence, tokens) pairs for sequences that produced more than one token."""
+        stopped = _u32(list(stopped))
+        ids = _u32([p[0] for p in produced])
+        tokens = _u32([p[1] for p in produced])
+        done = (Completion * self.max_num_seqs)()
+        count = c_size_t()
+        code = lib.qwc_scheduler_complete_batch_multi(self._handle, stopped.ctypes.data_as(P), stopped.size,
+                                                      ids.ctypes.data_as(P), tokens.ctypes.data_as(P), ids.size, done,
+                                                      self.max_num_seqs, byref(count))
         if code != 0:
             raise RuntimeError_("SchedulerError", code, SCHEDULER_ERROR)
         return [(c.id, c.generated_tokens, "Stopped" if c.reason else "Length") for c in done[:count.value]]

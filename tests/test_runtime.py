@@ -281,6 +281,30 @@ def test_complete_batch_validates_stopped_ids(built_library):
     assert s.remaining_tokens(1) == 4 and s.remaining_tokens(2) is None
 
 
+def test_complete_batch_multi_counts_the_tokens_a_sequence_produced(built_library):
+    # scheduler.rs:392-500 (the reference has no test of its own for this; the cases follow its doc comment
+    # and its checks at :407-414 and :468-472)
+    s = scheduler(2, 10, 2, 64)
+    with rejected("NoBatchInFlight"):
+        s.complete_batch_multi([], [(1, 2)])
+    s.submit(1, 4, 7)
+    s.submit(2, 4, 3)
+    s.next_batch()
+    s.complete_batch()
+    assert sorted(s.next_batch()["decode"]) == [1, 2]
+    with rejected("Invariant"):
+        s.complete_batch_multi([], [(1, 0)])           # a step produces at least one token
+    with rejected("InvalidStopped"):
+        s.complete_batch_multi([], [(9, 2)])           # not a decode sequence of this batch
+    assert s.complete_batch_multi([], [(1, 3)]) == []  # sequence 2 is not named: one token
+    assert s.remaining_tokens(1) == 4 and s.remaining_tokens(2) == 2
+    s.next_batch()
+    # more tokens than the request has left: capped at its length; the first entry of a sequence counts
+    done = s.complete_batch_multi([], [(1, 9), (2, 2), (2, 1)])
+    assert sorted(done) == [(1, 7, "Length"), (2, 3, "Length")]
+    assert s.active() == 0 and s.cache.states_in_use() == 0
+
+
 def test_decode_rows_take_priority_over_admission(built_library):
     # scheduler.rs:301-323: decode fills the batch first; a full batch admits nobody
     s = scheduler(4, 100, 2, 64)
