@@ -415,6 +415,12 @@ int qwc_fp8_lm_head(const void* weights, const void* row_scales, const void* hid
                     int batch, int hidden_size, int vocab, qwc_stream stream);
 int qwc_fp8_lm_head_batched(const void* weights, const void* row_scales, const void* hidden,
                             void* logits, int batch, int hidden_size, int vocab, qwc_stream stream);
+/* bf16 rows [rows][cols] -> e4m3 rows with one fp32 scale per row (scale = max|x| / 448, 1 for a zero
+ * row), written at rows first_row .. of `output` and `row_scales`: the weight loader's conversion of
+ * the vocabulary tables, chunk by chunk.  Replaces crates/qwc-cuda/src/ffi.rs:60-68
+ * (cuda/vocab_fp8.cu:681-700). */
+int qwc_fp8_quantize_rows(const void* input, void* output, void* row_scales, int rows, int cols,
+                          int first_row, qwc_stream stream);
 int qwc_fp8_max_logits_batch(void);    /* crates/qwc-cuda/src/ffi.rs:142 */
 int qwc_fp8_max_batched_logits(void);  /* crates/qwc-cuda/src/ffi.rs:144 */
 

@@ -184,6 +184,11 @@ int qwc_engine_tensor(qwc_engine* engine, const char* name, int layer, void** de
 int qwc_engine_trace_layers(qwc_engine* engine, int enable);
 
 /* Synchronous copies of a named tensor to / from host memory (`bytes` must equal its size). */
+/* The fp32 global divisor of an NVFP4 matrix ("gate", "up", "down", "in_proj", "la_out", "qkv", "o"):
+ * synthetic weights carry 1; a weight loader sets the checkpoint's weight_global_scale
+ * (crates/qwc-engine/src/weights.rs:470-476).  Setting it drops the captured graphs. */
+int qwc_engine_set_weight_global_scale(qwc_engine* engine, const char* name, int layer, float value);
+int qwc_engine_weight_global_scale(qwc_engine* engine, const char* name, int layer, float* value);
 int qwc_engine_read(qwc_engine* engine, const char* name, int layer, void* host, size_t bytes);
 int qwc_engine_write(qwc_engine* engine, const char* name, int layer, const void* host, size_t bytes);
 

@@ -66,6 +66,7 @@ KERNEL_SYMBOLS = {
     "qwc_rmsnorm_bf16_staged": (c_int, [P, P, P, P, P, c_int, c_int, c_float, P]),
     "qwc_nvfp4_split_count": (c_int, [c_int, c_int]),
     # latency mode: rows exchanged between ranks (P: a qwc_exchange_row*)
+    "qwc_fp8_quantize_rows": (c_int, [P, P, P, c_int, c_int, c_int, P]),
     "qwc_exchange_advance": (c_int, [P, P]),
     "qwc_exchange_row_bytes": (c_size_t, [c_int]),
     "qwc_exchange_candidate_bytes": (c_size_t, [c_int]),

@@ -1367,6 +1367,52 @@ void qwc_engine_traffic(const qwc_engine* e, int rows, double context_tokens, qw
     out->kernel_launches_per_step = kernels;
 }
 
+namespace {
+LinearW* find_linear(qwc_engine* e, const char* name, int layer) {
+    if (e == nullptr || name == nullptr || layer < 0 || layer >= e->cfg.num_layers) {
+        return nullptr;
+    }
+    Layer& l = e->layers[layer];
+    const std::string n(name);
+    if (n == "gate") return &l.gate;
+    if (n == "up") return &l.up;
+    if (n == "down") return &l.down;
+    if (!l.full && n == "in_proj") return &l.in_proj;
+    if (!l.full && n == "la_out") return &l.la_out;
+    if (l.full && n == "qkv") return &l.qkv;
+    if (l.full && n == "o") return &l.o;
+    return nullptr;
+}
+}  // namespace
+
+// The fp32 global divisor of an NVFP4 matrix (the checkpoint's weight_global_scale,
+// crates/qwc-engine/src/weights.rs:470-476): synthetic weights carry 1; a loader sets the real one.
+// The value is a launch argument, so captured graphs are dropped.
+int qwc_engine_set_weight_global_scale(qwc_engine* e, const char* name, int layer, float value) {
+    LinearW* w = find_linear(e, name, layer);
+    if (w == nullptr || !(value > 0.0f) || !std::isfinite(value)) {
+        return cudaErrorInvalidValue;
+    }
+    QWC_TRY(cudaStreamSynchronize(e->stream));
+    w->global_scale = value;
+    for (cudaGraphExec_t& exec : e->graphs) {
+        if (exec != nullptr) {
+            cudaGraphExecDestroy(exec);
+            exec = nullptr;
+        }
+    }
+    return 0;
+}
+
+int qwc_engine_weight_global_scale(qwc_engine* e, const char* name, int layer, float* value) {
+    LinearW* w = find_linear(e, name, layer);
+    if (w == nullptr || value == nullptr) {
+        return cudaErrorInvalidValue;
+    }
+    *value = w->global_scale;
+    return 0;
+}
+
 int qwc_engine_apply_edits(qwc_engine* e, const qwc_table_edit* edits, size_t count) {
     if (e == nullptr || (count > 0 && edits == nullptr)) {
         return cudaErrorInvalidValue;

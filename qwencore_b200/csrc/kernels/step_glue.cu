@@ -66,6 +66,85 @@ __global__ void embedding_gather_kernel(const uint8_t* __restrict__ table, const
     }
 }
 
+// ---- bf16 rows -> e4m3 rows with one fp32 scale per row (cuda/vocab_fp8.cu:70-111) -----
+// The weight loader's step for the vocabulary tables: scale = max|x| / 448 (1 for an all-zero row),
+// code = e4m3(x / scale), round to nearest even, saturating.  A warp per row, eight rows per CTA: 16
+// bytes per lane and load, the second pass over the row (10 KB at 5120 columns) comes from L1, and the
+// codes leave eight bytes per lane.
+
+__global__ void __launch_bounds__(kThreads) quantize_rows_kernel(const __nv_bfloat16* __restrict__ input,
+                                                                 uint8_t* __restrict__ output,
+                                                                 float* __restrict__ row_scales, int rows, int cols,
+                                                                 int first_row) {
+    const int lane = threadIdx.x & 31;
+    const int local_row = blockIdx.x * (kThreads / 32) + (threadIdx.x >> 5);
+    if (local_row >= rows) {
+        return;
+    }
+    const __nv_bfloat16* in = input + static_cast<size_t>(local_row) * cols;
+    uint8_t* out = output + static_cast<size_t>(first_row + local_row) * cols;
+    const int vectors = cols / 8;  // the launcher sends other widths to the scalar form below
+    float peak = 0.0f;
+    for (int v = lane; v < vectors; v += 32) {
+        const uint4 raw = *reinterpret_cast<const uint4*>(in + 8 * v);
+        const uint32_t words[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            peak = fmaxf(peak, fmaxf(fabsf(__uint_as_float(words[j] << 16)), fabsf(__uint_as_float(words[j] & 0xffff0000u))));
+        }
+    }
+    peak = warp_max(peak);
+    const float scale = peak > 0.0f ? peak / 448.0f : 1.0f;
+    if (lane == 0) {
+        row_scales[first_row + local_row] = scale;
+    }
+    const float inverse = 1.0f / scale;
+    for (int v = lane; v < vectors; v += 32) {
+        const uint4 raw = *reinterpret_cast<const uint4*>(in + 8 * v);
+        const uint32_t words[4] = {raw.x, raw.y, raw.z, raw.w};
+        uint32_t packed[2] = {0u, 0u};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const float2 pair = make_float2(__uint_as_float(words[j] << 16) * inverse,
+                                            __uint_as_float(words[j] & 0xffff0000u) * inverse);
+            const uint32_t codes = __nv_cvt_float2_to_fp8x2(pair, __NV_SATFINITE, __NV_E4M3);
+            packed[j >> 1] |= codes << (16 * (j & 1));
+        }
+        *reinterpret_cast<uint2*>(out + 8 * v) = make_uint2(packed[0], packed[1]);
+    }
+}
+
+// ... any width, one column per thread step (rows whose width is not a multiple of eight)
+__global__ void __launch_bounds__(kThreads) quantize_rows_scalar_kernel(const __nv_bfloat16* __restrict__ input,
+                                                                        uint8_t* __restrict__ output,
+                                                                        float* __restrict__ row_scales, int cols,
+                                                                        int first_row) {
+    __shared__ float scratch[kThreads / 32];
+    const __nv_bfloat16* in = input + static_cast<size_t>(blockIdx.x) * cols;
+    uint8_t* out = output + static_cast<size_t>(first_row + blockIdx.x) * cols;
+    float peak = 0.0f;
+    for (int c = threadIdx.x; c < cols; c += kThreads) {
+        peak = fmaxf(peak, fabsf(__bfloat162float(in[c])));
+    }
+    peak = warp_max(peak);
+    if ((threadIdx.x & 31) == 0) {
+        scratch[threadIdx.x >> 5] = peak;
+    }
+    __syncthreads();
+    peak = 0.0f;
+    for (int w = 0; w < kThreads / 32; ++w) {
+        peak = fmaxf(peak, scratch[w]);
+    }
+    const float scale = peak > 0.0f ? peak / 448.0f : 1.0f;
+    if (threadIdx.x == 0) {
+        row_scales[first_row + blockIdx.x] = scale;
+    }
+    const float inverse = 1.0f / scale;
+    for (int c = threadIdx.x; c < cols; c += kThreads) {
+        out[c] = static_cast<uint8_t>(__nv_cvt_float_to_fp8(__bfloat162float(in[c]) * inverse, __NV_SATFINITE, __NV_E4M3));
+    }
+}
+
 // ---- residual RMSNorm (cuda/rmsnorm.cu:85-149) --------------------------------------
 // One CTA per row; the rounded bf16 row stays in registers between the two passes.
 constexpr int kNormMaxPerThread = 10;  // 8 * 256 * 10 = 20480 columns at most
@@ -895,6 +974,25 @@ constexpr int kMaxLogitsRows = 32;
 }  // namespace qwc
 
 using namespace qwc;
+
+extern "C" int qwc_fp8_quantize_rows(const void* input, void* output, void* row_scales, int rows, int cols,
+                                     int first_row, cudaStream_t stream) {
+    if (input == nullptr || output == nullptr || row_scales == nullptr || rows <= 0 || cols <= 0 || first_row < 0) {
+        return cudaErrorInvalidValue;
+    }
+    const bool vector = cols % 8 == 0 && (reinterpret_cast<uintptr_t>(input) & 15) == 0 &&
+                        (reinterpret_cast<uintptr_t>(output) & 7) == 0;
+    if (vector) {
+        quantize_rows_kernel<<<(rows + kThreads / 32 - 1) / (kThreads / 32), kThreads, 0, stream>>>(
+            static_cast<const __nv_bfloat16*>(input), static_cast<uint8_t*>(output), static_cast<float*>(row_scales),
+            rows, cols, first_row);
+    } else {
+        quantize_rows_scalar_kernel<<<rows, kThreads, 0, stream>>>(
+            static_cast<const __nv_bfloat16*>(input), static_cast<uint8_t*>(output), static_cast<float*>(row_scales),
+            cols, first_row);
+    }
+    return cudaGetLastError();
+}
 
 extern "C" int qwc_fp8_embedding_gather(const void* table, const void* row_scales, const void* token_ids,
                                         void* output, int batch, int cols, int vocab, cudaStream_t stream) {

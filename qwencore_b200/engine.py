@@ -97,6 +97,8 @@ ENGINE_SYMBOLS = {
     "qwc_engine_profile_waits": (c_int, [P, c_int]),
     "qwc_engine_tensor": (c_int, [P, c_char_p, c_int, POINTER(P), POINTER(c_size_t)]),
     "qwc_engine_trace_layers": (c_int, [P, c_int]),
+    "qwc_engine_set_weight_global_scale": (c_int, [P, c_char_p, c_int, c_float]),
+    "qwc_engine_weight_global_scale": (c_int, [P, c_char_p, c_int, POINTER(c_float)]),
     "qwc_engine_read": (c_int, [P, c_char_p, c_int, P, c_size_t]),
     "qwc_engine_write": (c_int, [P, c_char_p, c_int, P, c_size_t]),
     "qwc_engine_traffic": (None, [P, c_int, c_double, POINTER(StepTraffic)]),
@@ -340,6 +342,17 @@ class Engine:
         values = np.ascontiguousarray(values)
         abi.check(lib.qwc_engine_write(self._handle, name.encode(), layer, values.ctypes.data_as(P), values.nbytes),
                   "qwc_engine_write")
+
+    def set_weight_global_scale(self, name: str, layer: int, value: float) -> None:
+        """The fp32 global divisor of an NVFP4 matrix ("gate", "in_proj", ...): what a weight loader sets."""
+        abi.check(lib.qwc_engine_set_weight_global_scale(self._handle, name.encode(), layer, c_float(value)),
+                  "qwc_engine_set_weight_global_scale")
+
+    def weight_global_scale(self, name: str, layer: int) -> float:
+        value = c_float()
+        abi.check(lib.qwc_engine_weight_global_scale(self._handle, name.encode(), layer, byref(value)),
+                  "qwc_engine_weight_global_scale")
+        return value.value
 
     def trace_layers(self, enable: bool = True) -> None:
         """Per-layer copies of the mixer output and the residual stream into the tensor "trace" (tests)."""
