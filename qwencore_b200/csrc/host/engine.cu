@@ -715,7 +715,7 @@ int decode_forward(qwc_engine* e, int batch) {
         if (staged) {
             if (index + 1 < e->layers.size()) {
                 const Layer& following = e->layers[index + 1];
-                hint_next(e, following.full ? following.qkv : following.in_proj);
+                hint_next_split(e, following.full ? following.qkv : following.in_proj);  // both run as K splits
             } else {
                 (void)qwc_nvfp4_prefetch_next(e->lm_head, nullptr, nullptr, nullptr, e->vocab_local, c.hidden, 2);
             }
