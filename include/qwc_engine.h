@@ -39,6 +39,31 @@ void qwc_cache_release(qwc_cache* cache, uint32_t id);
  * most `max_blocks` page ids; *num_blocks the real count. */
 int qwc_cache_sequence(const qwc_cache* cache, uint32_t id, uint32_t* state_slot, size_t* tokens,
                        uint32_t* blocks, size_t max_blocks, size_t* num_blocks);
+/* Prefix cache, bookkeeping only (crates/qwc-runtime/src/cache.rs:193-310, :328-365, :451-569): an
+ * entry is a snapshot NUMBER plus references to the KV pages that cover a prompt prefix; the state
+ * snapshots themselves would be the executor's.  admit_prompt continues the longest cached proper
+ * prefix of at least one page: full pages are shared by reference, an incomplete last page is to be
+ * copied (copy_from -> copy_to), the entry stays pinned until finish_restore.  reserve_snapshot
+ * returns a free snapshot number (evicting the least valuable unpinned entry when none is free) or
+ * -1; commit_snapshot records sequence `id`'s first `num_tokens` tokens under it. */
+typedef struct qwc_admission {
+    size_t reused;
+    int has_restore;
+    uint32_t snapshot;
+    int copy;
+    uint32_t copy_from;
+    uint32_t copy_to;
+} qwc_admission;
+void qwc_cache_enable_prefix_cache(qwc_cache* cache, size_t snapshots);
+int qwc_cache_admit_prompt(qwc_cache* cache, uint32_t id, const uint32_t* prompt, size_t prompt_tokens,
+                           qwc_admission* admission);
+void qwc_cache_finish_restore(qwc_cache* cache, uint32_t snapshot);
+long long qwc_cache_reserve_snapshot(qwc_cache* cache);
+void qwc_cache_cancel_snapshot(qwc_cache* cache, uint32_t snapshot);
+void qwc_cache_commit_snapshot(qwc_cache* cache, uint32_t snapshot, uint32_t id, const uint32_t* tokens,
+                               size_t num_tokens);
+size_t qwc_cache_prefix_entries(const qwc_cache* cache);
+void qwc_cache_prefix_stats(const qwc_cache* cache, uint64_t* lookups_hits_reused_evictions);
 size_t qwc_cache_free_blocks(const qwc_cache* cache);
 size_t qwc_cache_states_in_use(const qwc_cache* cache);
 size_t qwc_cache_active(const qwc_cache* cache);

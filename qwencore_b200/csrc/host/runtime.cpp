@@ -2,6 +2,7 @@
 #include "runtime.h"
 
 #include <algorithm>
+#include <tuple>
 #include <unordered_map>
 #include <limits>
 #include <unordered_set>
@@ -80,22 +81,226 @@ Rejected CacheManager::admit(SeqId id, size_t prompt_tokens) {
         return Rejected::NoStateSlot;
     }
     std::vector<uint32_t> blocks;
-    if (!kv_.acquire(need, &blocks)) {
+    if (!acquire_blocks(need, &blocks)) {
         last_need_ = need;
         last_free_ = kv_.free_blocks();
         return Rejected::NoKvBlocks;
     }
     const uint32_t slot = *states_.acquire();
-    for (size_t i = 0; i < blocks.size(); ++i) {
-        edits_.push_back({slot, static_cast<uint32_t>(i), blocks[i], 0});
-    }
-    edits_.push_back({slot, 0, static_cast<uint32_t>(prompt_tokens), 1});
+    record_admission(slot, blocks, prompt_tokens);
     Sequence seq;
     seq.state_slot = slot;
     seq.blocks = std::move(blocks);
     seq.tokens = prompt_tokens;
     seqs_.emplace(id, std::move(seq));
     return Rejected::None;
+}
+
+void CacheManager::record_admission(uint32_t slot, const std::vector<uint32_t>& blocks, size_t tokens) {
+    for (size_t i = 0; i < blocks.size(); ++i) {
+        edits_.push_back({slot, static_cast<uint32_t>(i), blocks[i], 0});
+    }
+    edits_.push_back({slot, 0, static_cast<uint32_t>(tokens), 1});
+}
+
+// ---- prefix cache (crates/qwc-runtime/src/cache.rs:240-310, :328-365, :451-569) ----------------
+
+void CacheManager::enable_prefix_cache(size_t snapshots) {
+    prefix_capacity_ = snapshots;
+    free_snapshots_.clear();
+    for (size_t i = snapshots; i > 0; --i) {
+        free_snapshots_.push_back(static_cast<uint32_t>(i - 1));  // popped from the back: 0, 1, 2, ...
+    }
+}
+
+std::optional<size_t> CacheManager::entry_position(uint32_t snapshot) const {
+    for (size_t i = 0; i < entries_.size(); ++i) {
+        if (entries_[i].snapshot == snapshot) {
+            return i;
+        }
+    }
+    return std::nullopt;
+}
+
+// The longest entry that is a proper prefix of the prompt (one prompt token at least must be run to
+// have logits for the first response token) and at least `min_tokens` long.
+std::optional<uint32_t> CacheManager::best_match(const std::vector<uint32_t>& prompt, size_t min_tokens) const {
+    const PrefixEntry* best = nullptr;
+    for (const PrefixEntry& entry : entries_) {
+        const size_t length = entry.tokens.size();
+        if (length < min_tokens || length >= prompt.size() ||
+            !std::equal(entry.tokens.begin(), entry.tokens.end(), prompt.begin())) {
+            continue;
+        }
+        if (best == nullptr || length >= best->tokens.size()) {  // max_by_key keeps the last of equal keys
+            best = &entry;
+        }
+    }
+    return best == nullptr ? std::nullopt : std::optional<uint32_t>(best->snapshot);
+}
+
+// Evicts the least valuable unpinned entry: entries nested in a longer one first, then entries no
+// live sequence holds pages of, then by age.  `for_pages`: the caller wants KV pages, so an entry all
+// of whose pages live sequences hold is left alone (it would free nothing and be lost).
+bool CacheManager::evict_one(bool for_pages) {
+    std::vector<uint32_t> holders(kv_.capacity(), 0);
+    for (const PrefixEntry& entry : entries_) {
+        for (uint32_t block : entry.blocks) {
+            holders[block] += 1;
+        }
+    }
+    const auto live = [&](uint32_t block) { return kv_.refs(block) > holders[block]; };
+    std::optional<size_t> chosen;
+    bool chosen_not_superseded = false, chosen_in_use = false;
+    uint64_t chosen_age = 0;
+    for (size_t i = 0; i < entries_.size(); ++i) {
+        const PrefixEntry& entry = entries_[i];
+        if (entry.pins != 0) {
+            continue;
+        }
+        const bool all_live = std::all_of(entry.blocks.begin(), entry.blocks.end(), live);
+        if (for_pages && all_live) {
+            continue;
+        }
+        bool superseded = false;
+        for (const PrefixEntry& other : entries_) {
+            if (other.tokens.size() > entry.tokens.size() &&
+                std::equal(entry.tokens.begin(), entry.tokens.end(), other.tokens.begin())) {
+                superseded = true;
+                break;
+            }
+        }
+        const bool in_use = std::any_of(entry.blocks.begin(), entry.blocks.end(), live);
+        const bool not_superseded = !superseded;
+        // min_by_key over (not superseded, in use, last used); the first of equal keys wins
+        const bool smaller = !chosen || std::make_tuple(not_superseded, in_use, entry.last_used) <
+                                            std::make_tuple(chosen_not_superseded, chosen_in_use, chosen_age);
+        if (smaller) {
+            chosen = i;
+            chosen_not_superseded = not_superseded;
+            chosen_in_use = in_use;
+            chosen_age = entry.last_used;
+        }
+    }
+    if (!chosen) {
+        return false;
+    }
+    PrefixEntry entry = std::move(entries_[*chosen]);
+    entries_[*chosen] = std::move(entries_.back());  // swap_remove
+    entries_.pop_back();
+    kv_.release(entry.blocks);
+    free_snapshots_.push_back(entry.snapshot);
+    prefix_stats_.evictions += 1;
+    return true;
+}
+
+// Blocks from the pool; when short, at the cost of prefix-cache entries (live sequences matter more).
+bool CacheManager::acquire_blocks(size_t n, std::vector<uint32_t>* out) {
+    for (;;) {
+        if (kv_.free_blocks() >= n) {
+            return kv_.acquire(n, out);
+        }
+        if (!evict_one(true)) {
+            return false;
+        }
+    }
+}
+
+Rejected CacheManager::admit_prompt(SeqId id, const std::vector<uint32_t>& prompt, Admission* admission) {
+    *admission = Admission{};
+    if (seqs_.count(id)) {
+        return Rejected::AlreadyAdmitted;
+    }
+    prefix_stats_.lookups += 1;
+    const std::optional<uint32_t> snapshot = best_match(prompt, kv_.block_size());
+    if (!snapshot) {
+        return admit(id, prompt.size());
+    }
+    if (states_.empty()) {
+        return Rejected::NoStateSlot;
+    }
+    const size_t index = *entry_position(*snapshot);
+    entries_[index].pins += 1;
+    const size_t reused = entries_[index].tokens.size();
+    const size_t full = reused / kv_.block_size();
+    std::vector<uint32_t> shared(entries_[index].blocks.begin(), entries_[index].blocks.begin() + full);
+    const bool has_tail = reused % kv_.block_size() != 0;
+    const uint32_t tail = has_tail ? entries_[index].blocks[full] : 0;
+    // the prompt is longer than the prefix, so there is always a page of its own; with an incomplete
+    // tail the first own page is a copy of the shared one
+    const size_t need = kv_.blocks_for(prompt.size()) - shared.size();
+    std::vector<uint32_t> fresh;
+    if (!acquire_blocks(need, &fresh)) {
+        finish_restore(*snapshot);
+        last_need_ = need;
+        last_free_ = kv_.free_blocks();
+        return Rejected::NoKvBlocks;
+    }
+    const uint32_t slot = *states_.acquire();
+    kv_.retain(shared);
+    Sequence seq;
+    seq.state_slot = slot;
+    seq.blocks = shared;
+    seq.blocks.insert(seq.blocks.end(), fresh.begin(), fresh.end());
+    seq.tokens = prompt.size();
+    record_admission(slot, seq.blocks, seq.tokens);
+    seqs_.emplace(id, std::move(seq));
+
+    const uint64_t now = ++prefix_clock_;
+    if (const std::optional<size_t> again = entry_position(*snapshot)) {  // eviction above may have moved entries
+        entries_[*again].last_used = now;
+    }
+    prefix_stats_.hits += 1;
+    prefix_stats_.reused_tokens += reused;
+    admission->reused = reused;
+    admission->has_restore = true;
+    admission->restore.snapshot = *snapshot;
+    admission->restore.copy = has_tail;
+    admission->restore.copy_from = tail;
+    admission->restore.copy_to = has_tail ? fresh[0] : 0;
+    return Rejected::None;
+}
+
+void CacheManager::finish_restore(uint32_t snapshot) {
+    if (const std::optional<size_t> index = entry_position(snapshot)) {
+        if (entries_[*index].pins > 0) {
+            entries_[*index].pins -= 1;
+        }
+    }
+}
+
+std::optional<uint32_t> CacheManager::reserve_snapshot() {
+    if (prefix_capacity_ == 0) {
+        return std::nullopt;
+    }
+    if (free_snapshots_.empty() && !evict_one(false)) {
+        return std::nullopt;
+    }
+    const uint32_t snapshot = free_snapshots_.back();
+    free_snapshots_.pop_back();
+    return snapshot;
+}
+
+void CacheManager::cancel_snapshot(uint32_t snapshot) { free_snapshots_.push_back(snapshot); }
+
+void CacheManager::commit_snapshot(uint32_t snapshot, SeqId id, std::vector<uint32_t> tokens) {
+    auto it = seqs_.find(id);
+    if (it == seqs_.end()) {
+        cancel_snapshot(snapshot);
+        return;
+    }
+    const uint64_t now = ++prefix_clock_;
+    for (PrefixEntry& existing : entries_) {
+        if (existing.tokens == tokens) {
+            existing.last_used = now;
+            free_snapshots_.push_back(snapshot);
+            return;
+        }
+    }
+    const size_t covered = kv_.blocks_for(tokens.size());
+    std::vector<uint32_t> blocks(it->second.blocks.begin(), it->second.blocks.begin() + covered);
+    kv_.retain(blocks);
+    entries_.push_back({std::move(tokens), std::move(blocks), snapshot, now, 0});
 }
 
 Rejected CacheManager::append_token(SeqId id) {
@@ -108,7 +313,7 @@ Rejected CacheManager::append_token(SeqId id) {
     if (need > seq.blocks.size()) {
         const size_t extra = need - seq.blocks.size();
         std::vector<uint32_t> more;
-        if (!kv_.acquire(extra, &more)) {
+        if (!acquire_blocks(extra, &more)) {
             last_need_ = extra;
             last_free_ = kv_.free_blocks();
             return Rejected::NoKvBlocks;

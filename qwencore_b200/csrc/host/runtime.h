@@ -2,8 +2,10 @@
 // CSR batch layout.  C++ restatement of the reference's CUDA-free `qwc-runtime` crate
 // (crates/qwc-runtime/src/{cache,scheduler,layout}.rs) with the same names, argument
 // meaning and error behaviour, so that the decode step keeps the scheduler / KV-cache /
-// slot API it is driven by.  Prefix-cache snapshots (cache.rs:457-569) belong to the
-// prefill path and are not carried over.
+// slot API it is driven by.  The prefix cache (cache.rs:193-310, :451-569) is the bookkeeping only:
+// which pages an entry shares and which snapshot number it holds; the snapshots themselves (DeltaNet
+// state at a prefix boundary) would be the executor's, and the prefill path that takes them is not
+// part of this library.
 #pragma once
 
 #include <cstddef>
@@ -56,6 +58,7 @@ public:
     bool acquire(size_t n, std::vector<uint32_t>* out);
     void retain(const std::vector<uint32_t>& blocks);
     void release(const std::vector<uint32_t>& blocks);
+    uint32_t refs(uint32_t block) const { return refs_[block]; }
 
 private:
     size_t block_size_;
@@ -69,6 +72,28 @@ struct Sequence {
     uint32_t state_slot = 0;
     std::vector<uint32_t> blocks;
     size_t tokens = 0;
+};
+
+// crates/qwc-runtime/src/cache.rs:193-210: how to continue a cached prefix.
+struct PrefixRestore {
+    uint32_t snapshot = 0;
+    bool copy = false;  // the prefix ends inside a page: copy page `copy_from` into `copy_to`
+    uint32_t copy_from = 0;
+    uint32_t copy_to = 0;
+};
+
+struct Admission {
+    size_t reused = 0;  // prompt tokens that are already computed
+    bool has_restore = false;
+    PrefixRestore restore;
+};
+
+// crates/qwc-runtime/src/cache.rs:231-238
+struct PrefixStats {
+    uint64_t lookups = 0;
+    uint64_t hits = 0;
+    uint64_t reused_tokens = 0;
+    uint64_t evictions = 0;
 };
 
 // One change of the device-resident tables caused by a cache operation
@@ -99,13 +124,42 @@ public:
     // Edits accumulated since the last drain, in order.
     std::vector<TableEdit> drain_edits();
 
+    // ---- prefix cache (cache.rs:328-365, :451-569) ----
+    void enable_prefix_cache(size_t snapshots);
+    size_t prefix_capacity() const { return prefix_capacity_; }
+    size_t prefix_entries() const { return entries_.size(); }
+    const PrefixStats& prefix_stats() const { return prefix_stats_; }
+    Rejected admit_prompt(SeqId id, const std::vector<uint32_t>& prompt, Admission* admission);
+    void finish_restore(uint32_t snapshot);
+    std::optional<uint32_t> reserve_snapshot();
+    void cancel_snapshot(uint32_t snapshot);
+    void commit_snapshot(uint32_t snapshot, SeqId id, std::vector<uint32_t> tokens);
+
 private:
+    struct PrefixEntry {
+        std::vector<uint32_t> tokens;
+        std::vector<uint32_t> blocks;
+        uint32_t snapshot;
+        uint64_t last_used;
+        uint32_t pins;  // admitted sequences waiting to restore this snapshot: not evictable
+    };
+    bool acquire_blocks(size_t n, std::vector<uint32_t>* out);
+    bool evict_one(bool for_pages);
+    std::optional<size_t> entry_position(uint32_t snapshot) const;
+    std::optional<uint32_t> best_match(const std::vector<uint32_t>& prompt, size_t min_tokens) const;
+    void record_admission(uint32_t slot, const std::vector<uint32_t>& blocks, size_t tokens);
+
     StatePool states_;
     KvPool kv_;
     std::unordered_map<SeqId, Sequence> seqs_;
     std::vector<TableEdit> edits_;
     size_t last_need_ = 0;
     size_t last_free_ = 0;
+    std::vector<PrefixEntry> entries_;
+    std::vector<uint32_t> free_snapshots_;
+    size_t prefix_capacity_ = 0;
+    uint64_t prefix_clock_ = 0;
+    PrefixStats prefix_stats_;
 };
 
 // crates/qwc-runtime/src/scheduler.rs:12-35

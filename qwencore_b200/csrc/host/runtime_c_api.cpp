@@ -59,6 +59,49 @@ int qwc_cache_sequence(const qwc_cache* cache, uint32_t id, uint32_t* state_slot
     return 0;
 }
 
+// ---- prefix cache (cache.rs:328-365, :451-569) ----
+void qwc_cache_enable_prefix_cache(qwc_cache* cache, size_t snapshots) { cache->cache->enable_prefix_cache(snapshots); }
+
+int qwc_cache_admit_prompt(qwc_cache* cache, uint32_t id, const uint32_t* prompt, size_t prompt_tokens,
+                           qwc_admission* admission) {
+    Admission result;
+    const Rejected rejected =
+        cache->cache->admit_prompt(id, std::vector<uint32_t>(prompt, prompt + prompt_tokens), &result);
+    if (admission != nullptr) {
+        admission->reused = result.reused;
+        admission->has_restore = result.has_restore ? 1 : 0;
+        admission->snapshot = result.restore.snapshot;
+        admission->copy = result.restore.copy ? 1 : 0;
+        admission->copy_from = result.restore.copy_from;
+        admission->copy_to = result.restore.copy_to;
+    }
+    return static_cast<int>(rejected);
+}
+
+void qwc_cache_finish_restore(qwc_cache* cache, uint32_t snapshot) { cache->cache->finish_restore(snapshot); }
+
+long long qwc_cache_reserve_snapshot(qwc_cache* cache) {
+    const std::optional<uint32_t> snapshot = cache->cache->reserve_snapshot();
+    return snapshot ? static_cast<long long>(*snapshot) : -1;
+}
+
+void qwc_cache_cancel_snapshot(qwc_cache* cache, uint32_t snapshot) { cache->cache->cancel_snapshot(snapshot); }
+
+void qwc_cache_commit_snapshot(qwc_cache* cache, uint32_t snapshot, uint32_t id, const uint32_t* tokens,
+                               size_t num_tokens) {
+    cache->cache->commit_snapshot(snapshot, id, std::vector<uint32_t>(tokens, tokens + num_tokens));
+}
+
+size_t qwc_cache_prefix_entries(const qwc_cache* cache) { return cache->cache->prefix_entries(); }
+
+void qwc_cache_prefix_stats(const qwc_cache* cache, uint64_t* lookups_hits_reused_evictions) {
+    const PrefixStats& stats = cache->cache->prefix_stats();
+    lookups_hits_reused_evictions[0] = stats.lookups;
+    lookups_hits_reused_evictions[1] = stats.hits;
+    lookups_hits_reused_evictions[2] = stats.reused_tokens;
+    lookups_hits_reused_evictions[3] = stats.evictions;
+}
+
 size_t qwc_cache_free_blocks(const qwc_cache* cache) { return cache->cache->kv().free_blocks(); }
 size_t qwc_cache_states_in_use(const qwc_cache* cache) { return cache->cache->states().in_use(); }
 size_t qwc_cache_active(const qwc_cache* cache) { return cache->cache->active(); }

@@ -67,6 +67,14 @@ ENGINE_SYMBOLS = {
     "qwc_cache_rollback_token": (c_int, [P, c_uint32]),
     "qwc_cache_release": (None, [P, c_uint32]),
     "qwc_cache_sequence": (c_int, [P, c_uint32, POINTER(c_uint32), POINTER(c_size_t), P, c_size_t, POINTER(c_size_t)]),
+    "qwc_cache_enable_prefix_cache": (None, [P, c_size_t]),
+    "qwc_cache_admit_prompt": (c_int, [P, c_uint32, P, c_size_t, P]),
+    "qwc_cache_finish_restore": (None, [P, c_uint32]),
+    "qwc_cache_reserve_snapshot": (c_longlong, [P]),
+    "qwc_cache_cancel_snapshot": (None, [P, c_uint32]),
+    "qwc_cache_commit_snapshot": (None, [P, c_uint32, c_uint32, P, c_size_t]),
+    "qwc_cache_prefix_entries": (c_size_t, [P]),
+    "qwc_cache_prefix_stats": (None, [P, P]),
     "qwc_cache_free_blocks": (c_size_t, [P]),
     "qwc_cache_states_in_use": (c_size_t, [P]),
     "qwc_cache_active": (c_size_t, [P]),
@@ -120,6 +128,11 @@ def _u32(values) -> np.ndarray:
     return np.ascontiguousarray(values, dtype=np.uint32)
 
 
+class Admission(ctypes.Structure):
+    _fields_ = [("reused", c_size_t), ("has_restore", c_int), ("snapshot", c_uint32), ("copy", c_int),
+                ("copy_from", c_uint32), ("copy_to", c_uint32)]
+
+
 class CacheManager:
     """crates/qwc-runtime/src/cache.rs:300-449,571-594"""
 
@@ -161,6 +174,44 @@ class CacheManager:
         lib.qwc_cache_sequence(self._handle, seq_id, byref(slot), byref(tokens), blocks.ctypes.data_as(P),
                                blocks.size, byref(count))
         return {"state_slot": slot.value, "tokens": tokens.value, "blocks": blocks[:count.value].tolist()}
+
+    # ---- prefix cache (cache.rs:328-365, :451-569) ----
+    def enable_prefix_cache(self, snapshots: int) -> None:
+        lib.qwc_cache_enable_prefix_cache(self._handle, snapshots)
+
+    def admit_prompt(self, seq_id: int, prompt) -> dict:
+        """{"reused": tokens, "restore": None | {"snapshot": n, "copy_block": None | (from, to)}}"""
+        tokens = _u32(list(prompt))
+        admission = Admission()
+        self._check(lib.qwc_cache_admit_prompt(self._handle, seq_id, tokens.ctypes.data_as(P), tokens.size,
+                                               byref(admission)))
+        restore = None
+        if admission.has_restore:
+            restore = {"snapshot": admission.snapshot,
+                       "copy_block": (admission.copy_from, admission.copy_to) if admission.copy else None}
+        return {"reused": admission.reused, "restore": restore}
+
+    def finish_restore(self, snapshot: int) -> None:
+        lib.qwc_cache_finish_restore(self._handle, snapshot)
+
+    def reserve_snapshot(self):
+        value = lib.qwc_cache_reserve_snapshot(self._handle)
+        return None if value < 0 else int(value)
+
+    def cancel_snapshot(self, snapshot: int) -> None:
+        lib.qwc_cache_cancel_snapshot(self._handle, snapshot)
+
+    def commit_snapshot(self, snapshot: int, seq_id: int, tokens) -> None:
+        values = _u32(list(tokens))
+        lib.qwc_cache_commit_snapshot(self._handle, snapshot, seq_id, values.ctypes.data_as(P), values.size)
+
+    def prefix_entries(self) -> int:
+        return lib.qwc_cache_prefix_entries(self._handle)
+
+    def prefix_stats(self) -> dict:
+        values = (ctypes.c_uint64 * 4)()
+        lib.qwc_cache_prefix_stats(self._handle, values)
+        return dict(zip(("lookups", "hits", "reused_tokens", "evictions"), (int(v) for v in values)))
 
     def free_blocks(self) -> int:
         return lib.qwc_cache_free_blocks(self._handle)

@@ -126,6 +126,184 @@ def test_cache_operations_are_mirrored_as_table_edits(built_library):
     assert m.drain_edits().shape == (0, 4)
 
 
+# ---- cache.rs, prefix cache (:773-968) -------------------------------------------------------
+
+def prompt(length, start=0):
+    return list(range(start, start + length))
+
+
+def snapshot(m, seq, tokens):
+    """A snapshot at the end of prompt `tokens` for sequence `seq` (cache.rs:777-782)."""
+    number = m.reserve_snapshot()
+    assert number is not None
+    m.commit_snapshot(number, seq, tokens)
+    return number
+
+
+def test_prefix_hit_shares_full_pages_and_copies_the_tail(built_library):
+    # cache.rs:784-806
+    m = CacheManager(4, 100, 64)
+    m.enable_prefix_cache(2)
+    assert m.admit_prompt(1, prompt(150)) == {"reused": 0, "restore": None}
+    snap = snapshot(m, 1, prompt(150))
+    owner = m.sequence(1)["blocks"]
+    m.release(1)
+    admission = m.admit_prompt(2, prompt(200))
+    assert admission["reused"] == 150 and admission["restore"]["snapshot"] == snap
+    blocks = m.sequence(2)["blocks"]
+    # two full pages are shared, the third (tail 150 - 128) is a copy
+    assert blocks[:2] == owner[:2]
+    assert admission["restore"]["copy_block"] == (owner[2], blocks[2]) and blocks[2] != owner[2]
+    assert len(blocks) == 4 and m.prefix_stats()["hits"] == 1
+    # the device tables follow: every page of the new sequence and its length were recorded
+    edits = m.drain_edits()
+    slot = m.sequence(2)["state_slot"]
+    mine = [e for e in edits.tolist() if e[0] == slot]
+    assert [e[2] for e in mine if e[3] == 0][-4:] == blocks and [slot, 0, 200, 1] in mine
+
+
+def test_aligned_prefix_needs_no_copy(built_library):
+    # cache.rs:808-818
+    m = CacheManager(4, 100, 64)
+    m.enable_prefix_cache(1)
+    m.admit_prompt(1, prompt(128))
+    snapshot(m, 1, prompt(128))
+    m.release(1)
+    admission = m.admit_prompt(2, prompt(130))
+    assert admission["reused"] == 128 and admission["restore"]["copy_block"] is None
+
+
+def test_identical_prompt_does_not_hit(built_library):
+    # cache.rs:820-830: at least one prompt token has to be run
+    m = CacheManager(4, 100, 64)
+    m.enable_prefix_cache(1)
+    m.admit_prompt(1, prompt(100))
+    snapshot(m, 1, prompt(100))
+    m.release(1)
+    assert m.admit_prompt(2, prompt(100))["reused"] == 0
+
+
+def test_different_prefix_misses(built_library):
+    # cache.rs:832-842
+    m = CacheManager(4, 100, 64)
+    m.enable_prefix_cache(1)
+    m.admit_prompt(1, prompt(100))
+    snapshot(m, 1, prompt(100))
+    m.release(1)
+    other = prompt(150)
+    other[10] = 999_999
+    assert m.admit_prompt(2, other)["reused"] == 0
+
+
+def test_shared_pages_return_to_the_pool_only_after_every_owner(built_library):
+    # cache.rs:844-864
+    m = CacheManager(4, 20, 64)
+    m.enable_prefix_cache(1)
+    total = m.free_blocks()
+    m.admit_prompt(1, prompt(150))
+    snapshot(m, 1, prompt(150))
+    m.release(1)
+    assert m.free_blocks() == total - 3  # the entry holds three pages after the owner leaves
+    m.admit_prompt(2, prompt(200))
+    m.finish_restore(0)
+    m.release(2)
+    assert m.free_blocks() == total - 3
+    m.admit(3, 20 * 64)                  # pool pressure evicts the entry and returns its pages
+    assert m.prefix_entries() == 0 and m.prefix_stats()["evictions"] == 1
+    m.release(3)
+    assert m.free_blocks() == total
+
+
+def test_page_pressure_skips_entry_held_by_live_sequence(built_library):
+    # cache.rs:870-888
+    m = CacheManager(4, 10, 64)
+    m.enable_prefix_cache(2)
+    m.admit_prompt(1, prompt(150))
+    snapshot(m, 1, prompt(150))
+    idle = prompt(150, 1000)
+    m.admit_prompt(2, idle)
+    snapshot(m, 2, idle)
+    m.release(2)
+    assert m.free_blocks() == 4
+    m.admit(3, 6 * 64)
+    assert m.prefix_stats()["evictions"] == 1 and m.prefix_entries() == 1
+    m.release(3)
+    assert m.admit_prompt(4, prompt(200))["reused"] == 150
+
+
+def test_page_pressure_fails_without_evicting_live_entries(built_library):
+    # cache.rs:890-899
+    m = CacheManager(4, 4, 64)
+    m.enable_prefix_cache(1)
+    m.admit_prompt(1, prompt(150))
+    snapshot(m, 1, prompt(150))
+    with rejected("NoKvBlocks"):
+        m.admit(2, 2 * 64)
+    assert m.prefix_entries() == 1 and m.prefix_stats()["evictions"] == 0
+
+
+def test_snapshot_pressure_keeps_entry_of_running_sequence(built_library):
+    # cache.rs:901-917
+    m = CacheManager(4, 100, 64)
+    m.enable_prefix_cache(2)
+    m.admit_prompt(1, prompt(150))
+    snapshot(m, 1, prompt(150))
+    idle = prompt(150, 1000)
+    m.admit_prompt(2, idle)
+    snapshot(m, 2, idle)
+    m.release(2)
+    fresh = prompt(100, 5000)            # no slots: the idle entry goes, even though it is newer
+    m.admit_prompt(3, fresh)
+    snapshot(m, 3, fresh)
+    assert m.admit_prompt(4, prompt(200, 1000))["reused"] == 0
+    assert m.admit_prompt(5, prompt(200))["reused"] == 150
+
+
+def test_snapshot_pressure_evicts_superseded_entry_first(built_library):
+    # cache.rs:919-944
+    m = CacheManager(4, 100, 64)
+    m.enable_prefix_cache(2)
+    m.admit_prompt(1, prompt(100))       # turn N and turn N + 1 of one dialog: N lies inside N + 1
+    snapshot(m, 1, prompt(100))
+    m.release(1)
+    admission = m.admit_prompt(2, prompt(200))
+    m.finish_restore(admission["restore"]["snapshot"])
+    snapshot(m, 2, prompt(180))
+    m.release(2)
+    branch = prompt(100) + [999_999]     # N was touched last - by age N + 1 would have gone
+    admission = m.admit_prompt(3, branch)
+    assert admission["reused"] == 100
+    m.finish_restore(admission["restore"]["snapshot"])
+    m.release(3)
+    other = prompt(100, 5000)
+    m.admit_prompt(4, other)
+    snapshot(m, 4, other)
+    m.release(4)
+    assert m.admit_prompt(5, prompt(250))["reused"] == 180
+
+
+def test_pinned_entry_survives_until_restored(built_library):
+    # cache.rs:946-959
+    m = CacheManager(4, 100, 64)
+    m.enable_prefix_cache(1)
+    m.admit_prompt(1, prompt(100))
+    snap = snapshot(m, 1, prompt(100))
+    m.release(1)
+    m.admit_prompt(2, prompt(120))
+    assert m.reserve_snapshot() is None  # the only snapshot slot is pinned
+    m.finish_restore(snap)
+    assert m.reserve_snapshot() == snap and m.prefix_entries() == 0
+
+
+def test_disabled_cache_is_plain_admission(built_library):
+    # cache.rs:961-966
+    m = CacheManager(4, 100, 64)
+    assert m.reserve_snapshot() is None
+    assert m.admit_prompt(1, prompt(100)) == {"reused": 0, "restore": None}
+    with rejected("AlreadyAdmitted"):
+        m.admit_prompt(1, prompt(100))
+
+
 # ---- scheduler.rs ----------------------------------------------------------------------------
 
 def scheduler(states, blocks, max_seqs, tokens):
