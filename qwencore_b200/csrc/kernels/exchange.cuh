@@ -16,12 +16,13 @@
 // match, for at most a second: when it gives up it stores kStatusPeerWait in the sticky status word,
 // uses zero, and every later wait of the step gives up at once.
 //
-// Measured alternatives (two B200s, 64 layers, ms per step; the form above: 4.45): consumers that
-// read each column from its owner's block over NVLink instead (stores stay local): 12.7 - a polling
-// load of a peer's memory takes a link round trip and was slow to see new values; a system-scope
-// fence per storing warp after the stores: 7.0 - the fence costs 4 - 10 us at the end of every
-// projection and buys nothing, the stores arrive without it.  (Neither a rotated order of
-// destinations per rank nor a longer back-off between polls changed the step time on four GPUs.)  A per-exchange wait profile (an atomic
+// Measured alternatives (64 layers, ms per step; the form above: 4.3 on two GPUs, 4.0 on four):
+// consumers that read each column from its owner's block over NVLink instead (stores stay local):
+// 12.7 on two - a polling load of a peer's memory takes a link round trip; a system-scope fence per
+// storing warp after the stores: 7.0 on two - the fence costs 4 - 10 us at the end of every projection
+// and buys nothing, the stores arrive without it; 256-byte bulk copies from shared memory instead of
+// 8-byte stores, a rotated order of destinations, a longer back-off between polls: no change.  What
+// did matter is how a consumer waits (see tagged_sums below).  A per-exchange wait profile (an atomic
 // maximum per word that was waited for) is available for diagnosis but lengthens the waits it
 // measures by an order of magnitude; it is off unless asked for.
 //
@@ -129,26 +130,51 @@ static __device__ __noinline__ float await_tagged(const uint2* at, uint32_t tag,
     return 0.0f;
 }
 
+// A consumer's first look usually comes a link latency before its peers' words: then the whole batch
+// of loads is issued again (one round trip whatever the number of words), a bounded number of times,
+// before the words that are still missing are waited for one by one (which is where the time limit
+// and the status word are handled).  Re-reading late words one after another cost a round trip per
+// word: 32 words per thread made every exchange 10 - 25 us slower on four and eight GPUs.
+constexpr int kQuickRetries = 512;
+
+__device__ __forceinline__ bool keep_retrying(int attempt, const int* status) {
+    return attempt < kQuickRetries &&
+           ((attempt & 15) != 15 || *reinterpret_cast<const volatile int*>(status) == kStatusOk);
+}
+
 // Sums over slices (in slice order) of kValues columns at once: every word of up to eight slices of
 // every column is asked for before the first is looked at, so the sum costs one round trip per eight
 // slices whatever the number of columns.
 template <int kValues>
 __device__ __forceinline__ void tagged_sums(const TaggedRow& row, uint32_t tag, const int (&columns)[kValues],
                                             float (&totals)[kValues]) {
-    const uint2* at[kValues];
 #pragma unroll
     for (int v = 0; v < kValues; ++v) {
         totals[v] = 0.0f;
-        at[v] = row.words + columns[v];
     }
     for (int first = 0; first < row.slices; first += 8) {
         uint2 part[kValues][8];
+        for (int attempt = 0;; ++attempt) {
+            bool complete = true;
 #pragma unroll
-        for (int v = 0; v < kValues; ++v) {
+            for (int v = 0; v < kValues; ++v) {
 #pragma unroll
-            for (int j = 0; j < 8; ++j) {
-                part[v][j] = load_tagged(at[v] + static_cast<size_t>(min(first + j, row.slices - 1)) * row.width);
+                for (int j = 0; j < 8; ++j) {
+                    part[v][j] = load_tagged(row.words + static_cast<size_t>(min(first + j, row.slices - 1)) * row.width +
+                                             columns[v]);
+                }
             }
+#pragma unroll
+            for (int v = 0; v < kValues; ++v) {
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    complete = complete && ((part[v][j].y ^ tag) & row.tag_mask) == 0;
+                }
+            }
+            if (complete || !keep_retrying(attempt, row.status)) {
+                break;
+            }
+            __nanosleep(100);
         }
 #pragma unroll
         for (int v = 0; v < kValues; ++v) {
@@ -157,8 +183,8 @@ __device__ __forceinline__ void tagged_sums(const TaggedRow& row, uint32_t tag, 
                 if (first + j < row.slices) {
                     totals[v] += ((part[v][j].y ^ tag) & row.tag_mask) == 0
                                      ? __uint_as_float(part[v][j].x)
-                                     : await_tagged(at[v] + static_cast<size_t>(first + j) * row.width, tag, row.status,
-                                                    row.wait_profile);
+                                     : await_tagged(row.words + static_cast<size_t>(first + j) * row.width + columns[v],
+                                                    tag, row.status, row.wait_profile);
                 }
             }
         }
@@ -178,11 +204,24 @@ __device__ __forceinline__ float4 tagged_sum4(const TaggedRow& row, uint32_t tag
     float total[4] = {0.0f, 0.0f, 0.0f, 0.0f};
     for (int first = 0; first < row.slices; first += 8) {
         uint4 part[8][2];
+        for (int attempt = 0;; ++attempt) {
+            bool complete = true;
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
-            const uint2* from = at + static_cast<size_t>(min(first + j, row.slices - 1)) * row.width;
-            part[j][0] = load_tagged_pair(from);
-            part[j][1] = load_tagged_pair(from + 2);
+            for (int j = 0; j < 8; ++j) {
+                const uint2* from = at + static_cast<size_t>(min(first + j, row.slices - 1)) * row.width;
+                part[j][0] = load_tagged_pair(from);
+                part[j][1] = load_tagged_pair(from + 2);
+            }
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                complete = complete && (((part[j][0].y ^ tag) | (part[j][0].w ^ tag) | (part[j][1].y ^ tag) |
+                                         (part[j][1].w ^ tag)) &
+                                        row.tag_mask) == 0;
+            }
+            if (complete || !keep_retrying(attempt, row.status)) {
+                break;
+            }
+            __nanosleep(100);
         }
 #pragma unroll
         for (int j = 0; j < 8; ++j) {

@@ -1293,6 +1293,7 @@ LaunchShape shape_of(int out_features, int in_features, bool swiglu, bool fp8, b
         splits = splits < 1 ? 1 : splits;
         splits = splits > shape.stages_in_k ? shape.stages_in_k : splits;
         splits = splits > kMaxKSlices ? kMaxKSlices : splits;
+
         shape.splits = splits;
         shape.ctas = shape.pair_tiles * splits;
         return shape;
