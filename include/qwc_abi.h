@@ -96,7 +96,8 @@ int qwc_nvfp4_swiglu_w4a16(const void* gate_packed, const void* gate_scales, con
  * matrix once its own last bytes are on their way, so HBM keeps streaming across the kernel
  * boundary.  kind: 0 = NVFP4 matrix (packed0, scales0), 1 = SwiGLU pair (packed0/scales0 = gate,
  * packed1/scales1 = up), 2 = e4m3 rows of the vocabulary head (packed0 = table; no scales),
- * 3 = an NVFP4 matrix that will run through qwc_nvfp4_w4a16_split.
+ * 3 = an NVFP4 matrix that will run through qwc_nvfp4_w4a16_split (or qwc_nvfp4_w4a16_exchange),
+ * 4 = a SwiGLU pair that will run through qwc_nvfp4_swiglu_w4a16_exchange.
  * Pure hint: host-side only (no launch, no sync, capture-legal), good for one launch of this
  * thread, ignored when that launch does not take the tcgen05 path; wrong or stale hints cost
  * bandwidth, never correctness (prefetches do not fault on valid device memory and write nothing).

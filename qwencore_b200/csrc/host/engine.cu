@@ -439,6 +439,15 @@ int decode_forward_exchange(qwc_engine* e) {
     const qwc_table_edit* edits = reinterpret_cast<const qwc_table_edit*>(e->in_dev + 2 * c.max_batch);
     const int batch = 1;
     uint32_t instance = 0;
+    // names the projection after the one about to be launched, so that the launch asks L2 for its first
+    // stages (every projection of this mode runs as a regular K split: hint kinds 3 and 4)
+    const auto hint_matrix = [](const LinearW& next) {
+        (void)qwc_nvfp4_prefetch_next(next.packed, next.scales, nullptr, nullptr, next.out_features, next.in_features, 3);
+    };
+    const auto hint_pair = [](const LinearW& gate, const LinearW& up) {
+        (void)qwc_nvfp4_prefetch_next(gate.packed, gate.scales, up.packed, up.scales, gate.out_features,
+                                      gate.in_features, 4);
+    };
 
     if (e->phase_filter == nullptr) {
         QWC_TRY(qwc_exchange_advance(e->epoch, s));
@@ -482,6 +491,7 @@ int decode_forward_exchange(qwc_engine* e) {
             const qwc_exchange_row row = exchange_row(e, e->row_wide, instance++, e->mixer_width);
             const int slices = qwc_nvfp4_exchange_slices(in.out_features, in.in_features, 0);
             if (phase(e, "gemm.la_in")) {
+                hint_matrix(layer.la_out);
                 QWC_TRY(qwc_nvfp4_w4a16_exchange(in.packed, in.scales, e->normed_staged, &row, in.out_features,
                                                  in.in_features, s));
             }
@@ -501,6 +511,7 @@ int decode_forward_exchange(qwc_engine* e) {
                 QWC_TRY(qwc_delta_gated_rmsnorm_exchanged(e->delta_out, &row, slices, in.global_scale, e->z_offset,
                                                           layer.out_norm, nullptr, e->delta_normed_staged, kEps, s));
             }
+            hint_pair(layer.gate, layer.up);
             QWC_TRY(finish_with_norm(layer.la_out, e->delta_normed_staged, 0, e->mixer_out, layer.post_norm,
                                      "gemm.la_out"));
         } else {
@@ -526,6 +537,7 @@ int decode_forward_exchange(qwc_engine* e) {
                     layer.v_scale, nullptr, e->attention_out_staged, e->attention_workspace, e->attention_workspace_bytes,
                     batch, 0, e->max_blocks, c.kv_page_size, e->qkv_width, e->partitions, 1.0f / 16.0f, s));
             }
+            hint_pair(layer.gate, layer.up);
             QWC_TRY(finish_with_norm(layer.o, e->attention_out_staged, 0, e->mixer_out, layer.post_norm,
                                      "gemm.attn_out"));
         }
@@ -537,6 +549,7 @@ int decode_forward_exchange(qwc_engine* e) {
         {
             const qwc_exchange_row row = exchange_row(e, e->row_swiglu, instance++, 2 * c.intermediate);
             if (phase(e, "gemm.mlp_gate_up")) {
+                hint_matrix(layer.down);
                 QWC_TRY(qwc_nvfp4_swiglu_w4a16_exchange(layer.gate.packed, layer.gate.scales, layer.up.packed,
                                                         layer.up.scales, e->normed_staged, &row, layer.gate.out_features,
                                                         layer.gate.in_features, s));
@@ -548,6 +561,12 @@ int decode_forward_exchange(qwc_engine* e) {
             }
         }
         const __nv_bfloat16* next_norm = index + 1 < e->layers.size() ? e->layers[index + 1].input_norm : e->final_norm;
+        if (index + 1 < e->layers.size()) {
+            const Layer& following = e->layers[index + 1];
+            hint_matrix(following.full ? following.qkv : following.in_proj);
+        } else {
+            (void)qwc_nvfp4_prefetch_next(e->lm_head, nullptr, nullptr, nullptr, e->vocab_local, c.hidden, 2);
+        }
         QWC_TRY(finish_with_norm(layer.down, e->mlp_hidden_staged, 1, e->mlp_out, next_norm, "gemm.mlp_down"));
         if (e->trace != nullptr && e->phase_filter == nullptr) {
             QWC_TRY(cudaMemcpyAsync(e->trace + (2 * index + 1) * trace_row, e->residual, trace_row * 2,

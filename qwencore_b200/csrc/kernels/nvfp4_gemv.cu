@@ -712,9 +712,9 @@ namespace {
 
 extern "C" int qwc_nvfp4_prefetch_next(const void* packed0, const void* scales0, const void* packed1,
                                        const void* scales1, int out_features, int in_features, int kind) {
-    const bool pair = kind == 1;
+    const bool pair = kind == 1 || kind == 4;
     const bool rows = kind == 2;
-    if (kind < 0 || kind > 3 || packed0 == nullptr || (!rows && scales0 == nullptr) ||
+    if (kind < 0 || kind > 4 || packed0 == nullptr || (!rows && scales0 == nullptr) ||
         (pair && (packed1 == nullptr || scales1 == nullptr)) || out_features <= 0 || in_features <= 0 ||
         in_features % 256 != 0 ||
         ((reinterpret_cast<uintptr_t>(packed0) | reinterpret_cast<uintptr_t>(scales0) |

@@ -1358,10 +1358,12 @@ cudaError_t launch_streamk(StreamKParams p, const void* packed0, const void* pac
     const NextProjection hint = take_next_projection();
     if (hint.packed[0] != nullptr && hint.out_features > 0 && hint.in_features > 0) {
         const bool next_fp8 = hint.kind == 2;
-        const bool next_swiglu = hint.kind == 1;
+        const bool next_swiglu = hint.kind == 1 || hint.kind == 4;
         const int next_row_bytes = next_fp8 ? hint.in_features : hint.in_features / 2;
-        // kind 3: an NVFP4 matrix that will run as a regular K split (qwc_nvfp4_w4a16_split)
-        const LaunchShape next = shape_of(hint.out_features, hint.in_features, next_swiglu, next_fp8, hint.kind == 3);
+        // kinds 3 and 4: a matrix / a SwiGLU pair that will run as a regular K split (qwc_nvfp4_w4a16_split,
+        // the latency-mode projections)
+        const LaunchShape next =
+            shape_of(hint.out_features, hint.in_features, next_swiglu, next_fp8, hint.kind == 3 || hint.kind == 4);
         if (next.units > 0 &&
             encode_weight_map(&next_map0, hint.packed[0], hint.out_features, next_row_bytes) == cudaSuccess &&
             encode_weight_map(&next_map1, hint.packed[next_swiglu ? 1 : 0], hint.out_features, next_row_bytes) ==

@@ -869,7 +869,7 @@ cudaError_t launch_umma(UmmaParams p, const void* x, int out_features, int in_fe
     const NextProjection hint = take_next_projection();
     if (hint.packed[0] != nullptr && hint.out_features > 0 && hint.in_features > 0) {
         const bool next_fp8 = hint.kind == 2;
-        const bool next_swiglu = hint.kind == 1;
+        const bool next_swiglu = hint.kind == 1 || hint.kind == 4;
         const int next_row_bytes = next_fp8 ? hint.in_features : hint.in_features / 2;
         const int next_rows_per_group = next_swiglu ? kTileRows : kTiles * kTileRows;
         const int next_groups = (hint.out_features + next_rows_per_group - 1) / next_rows_per_group;

@@ -585,35 +585,70 @@ __global__ void __launch_bounds__(kThreads) sum_slices_kernel(const SplitSource 
 // The gate and up projections of a rank's columns ran as one K-split launch whose slices every rank
 // received ([slice][gate | up] tagged words); this sums them and applies the epilogue of the fused
 // one-GPU kernel (gate and up scaled in fp32, silu(gate) * up rounded once to bf16,
-// cuda/nvfp4.cu:292-318), four outputs per thread, into the staged operand of the down projection.
+// cuda/nvfp4.cu:292-318), two outputs per thread, into the staged operand of the down projection.
 __global__ void __launch_bounds__(kThreads) swiglu_combine_kernel(const TaggedRow row, float gate_scale, float up_scale,
                                                                   __nv_bfloat16* __restrict__ output,
                                                                   __half* __restrict__ staged, int intermediate) {
     pdl_launch_dependents();
     pdl_wait();
     const uint32_t tag = exchange_tag(row.epoch, row.instance);
-    const int quad = blockIdx.x * kThreads + threadIdx.x;
-    if (4 * quad >= intermediate) {
+    // two outputs per thread: their gate and up words of every slice are one batch of 16-byte loads
+    const int pair = blockIdx.x * kThreads + threadIdx.x;
+    if (2 * pair >= intermediate) {
         return;
     }
-    const float4 gate = tagged_sum4(row, tag, 4 * quad);
-    const float4 up = tagged_sum4(row, tag, intermediate + 4 * quad);
-    const float g[4] = {gate.x * gate_scale, gate.y * gate_scale, gate.z * gate_scale, gate.w * gate_scale};
-    const float u[4] = {up.x * up_scale, up.y * up_scale, up.z * up_scale, up.w * up_scale};
-    __nv_bfloat16 rounded[4];
+    const uint2* gate_at = row.words + 2 * pair;
+    const uint2* up_at = row.words + intermediate + 2 * pair;
+    float gate[2] = {0.0f, 0.0f}, up[2] = {0.0f, 0.0f};
+    for (int first = 0; first < row.slices; first += 8) {
+        uint4 g[8], u[8];
+        for (int attempt = 0;; ++attempt) {
+            bool complete = true;
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        rounded[i] = __float2bfloat16(__fdividef(g[i], 1.0f + __expf(-g[i])) * u[i]);
+            for (int j = 0; j < 8; ++j) {
+                const size_t slice = static_cast<size_t>(min(first + j, row.slices - 1)) * row.width;
+                g[j] = load_tagged_pair(gate_at + slice);
+                u[j] = load_tagged_pair(up_at + slice);
+            }
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                complete = complete &&
+                           (((g[j].y ^ tag) | (g[j].w ^ tag) | (u[j].y ^ tag) | (u[j].w ^ tag)) & row.tag_mask) == 0;
+            }
+            if (complete || !keep_retrying(attempt, row.status)) {
+                break;
+            }
+            __nanosleep(100);
+        }
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            if (first + j < row.slices) {
+                const size_t slice = static_cast<size_t>(first + j) * row.width;
+                const auto take = [&](uint32_t bits, uint32_t word_tag, const uint2* at) {
+                    return ((word_tag ^ tag) & row.tag_mask) == 0 ? __uint_as_float(bits)
+                                                                  : await_tagged(at, tag, row.status, row.wait_profile);
+                };
+                gate[0] += take(g[j].x, g[j].y, gate_at + slice);
+                gate[1] += take(g[j].z, g[j].w, gate_at + slice + 1);
+                up[0] += take(u[j].x, u[j].y, up_at + slice);
+                up[1] += take(u[j].z, u[j].w, up_at + slice + 1);
+            }
+        }
     }
-    __nv_bfloat162 lo = __halves2bfloat162(rounded[0], rounded[1]);
-    __nv_bfloat162 hi = __halves2bfloat162(rounded[2], rounded[3]);
-    const uint2 out = make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
+    __nv_bfloat16 rounded[2];
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+        const float gated = gate[i] * gate_scale;
+        rounded[i] = __float2bfloat16(__fdividef(gated, 1.0f + __expf(-gated)) * (up[i] * up_scale));
+    }
+    __nv_bfloat162 both = __halves2bfloat162(rounded[0], rounded[1]);
+    const uint32_t out = *reinterpret_cast<uint32_t*>(&both);
     if (output != nullptr) {
-        *reinterpret_cast<uint2*>(output + 4 * quad) = out;
+        *reinterpret_cast<uint32_t*>(output + 2 * pair) = out;
     }
     if (staged != nullptr) {  // one row of [intermediate / 8][16][8]
-        *reinterpret_cast<uint2*>(staged + static_cast<size_t>(quad >> 1) * 16 * 8 + (quad & 1) * 4) =
-            make_uint2(bf16x2_to_f16x2(out.x), bf16x2_to_f16x2(out.y));
+        *reinterpret_cast<uint32_t*>(staged + static_cast<size_t>(pair >> 2) * 16 * 8 + (pair & 3) * 2) =
+            bf16x2_to_f16x2(out);
     }
 }
 
@@ -1286,7 +1321,7 @@ extern "C" int qwc_swiglu_combine_exchanged(const qwc_exchange_row* row, int sli
         return cudaErrorInvalidValue;
     }
     const TaggedRow tagged = tagged_row(*row, slices, status);
-    const int blocks = (intermediate / 4 + kThreads - 1) / kThreads;
+    const int blocks = (intermediate / 2 + kThreads - 1) / kThreads;
     return qwc::launch_chained(swiglu_combine_kernel, dim3(blocks), dim3(kThreads), 0, stream, tagged,
                                1.0f / gate_global_scale, 1.0f / up_global_scale,
                                static_cast<__nv_bfloat16*>(output), static_cast<__half*>(staged_output), intermediate);

@@ -167,7 +167,7 @@ def test_prefetch_next_hint_changes_no_result_and_rejects_bad_arguments(cuda, op
     assert abi.lib.qwc_nvfp4_prefetch_next(good[0], good[1], None, None, 12352, 5120, 1) == invalid
     assert abi.lib.qwc_nvfp4_prefetch_next(good[0], good[1], None, None, 12352, 5000, 0) == invalid
     assert abi.lib.qwc_nvfp4_prefetch_next(good[0], good[1], None, None, 0, 5120, 0) == invalid
-    assert abi.lib.qwc_nvfp4_prefetch_next(good[0], good[1], None, None, 12352, 5120, 4) == invalid
+    assert abi.lib.qwc_nvfp4_prefetch_next(good[0], good[1], None, None, 12352, 5120, 5) == invalid
     assert abi.lib.qwc_nvfp4_prefetch_next(good[0] + 8, good[1], None, None, 12352, 5120, 0) == invalid
     assert abi.lib.qwc_device_status() == 0
 
