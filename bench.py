@@ -327,7 +327,7 @@ def traffic_launches(engine):
 
 
 def time_latency_engine(args, group, local_rank, fused):
-    """One latency-mode engine (fused peer loads, or the library all-gather): ms per step as the max
+    """One latency-mode engine (fused peer stores, or the library all-gather): ms per step as the max
     over ranks, every rank's tokens of the warm-up steps, and the traffic model."""
     import torch
 
@@ -415,15 +415,14 @@ def time_latency_engine(args, group, local_rank, fused):
 def run_latency_mode(args, group, local_rank, single_gpu_ms):
     """Batch 1 with every projection column-split over all ranks of the launch (one sequence, context
     2048): milliseconds per step, max over ranks, and the ranks' sampled tokens compared.  The headline
-    is the fused form (every projection leaves its partial sums in its rank's block, the consumers read
-    each column from its owner over NVLink); the same split with an ncclAllGather after every
-    projection is timed beside it."""
+    is the fused form (projections store their partial sums into the peers' memory, consumers sum
+    them); the same split with an ncclAllGather after every projection is timed beside it."""
     world = group.world
     ms, produced, tokens_of_ranks, traffic, status, phases = time_latency_engine(args, group, local_rank, True)
     library_ms, _, library_tokens, _, _, _ = time_latency_engine(args, group, local_rank, False)
     return {"ms_per_step": ms, "tok_s": 1e3 / ms, "vs_1gpu": single_gpu_ms / ms, "gpus": world,
-            "exchange": "partial sums kept by the rank that computed them as 8-byte tagged words; the consuming "
-                        "kernel reads every column from its owner over NVLink and sums after a bounded wait; no "
+            "exchange": "partial sums stored into every rank's memory by the projection's epilogue (8-byte "
+                        "tagged words over NVLink), summed by the consuming kernel after a bounded wait; no "
                         "library collective in the step",
             "exchanges_per_step": int(traffic.gemv_launches_per_step + 1),
             "kernel_launches_per_step": int(traffic.kernel_launches_per_step),
