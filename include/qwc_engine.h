@@ -113,6 +113,33 @@ int qwc_scheduler_complete_batch_multi(qwc_scheduler* scheduler, const uint32_t*
                                        const uint32_t* produced_ids, const uint32_t* produced_tokens,
                                        size_t num_produced, qwc_completion* completed, size_t max_completed,
                                        size_t* num_completed);
+/* Prefix cache through the scheduler (crates/qwc-runtime/src/scheduler.rs:52-68, :226-261).  A request
+ * submitted with its prompt tokens can continue a cached prefix and leave its own: the prefill chunk is
+ * cut at `snapshot_at` (the history boundary), and the batch then carries a save op; an admitted request
+ * that continues a prefix carries a restore op with its first chunk.  prompt_tokens must equal the
+ * request's prompt length and snapshot_at must not exceed it (SubmitError 2 otherwise). */
+typedef struct qwc_prefix_restore_op {
+    uint32_t id;
+    uint32_t state_slot;
+    uint32_t snapshot;
+    uint32_t copy; /* 1: copy page copy_from into copy_to before the step (the prefix ends inside a page) */
+    uint32_t copy_from;
+    uint32_t copy_to;
+} qwc_prefix_restore_op;
+
+typedef struct qwc_prefix_save_op {
+    uint32_t id;
+    uint32_t state_slot;
+    uint32_t snapshot;
+} qwc_prefix_save_op;
+
+void qwc_scheduler_enable_prefix_cache(qwc_scheduler* scheduler, size_t snapshots);
+int qwc_scheduler_submit_prompt(qwc_scheduler* scheduler, uint32_t id, const uint32_t* prompt, size_t prompt_tokens,
+                                size_t max_new_tokens, size_t snapshot_at);
+/* The prefix work of the batch in flight (restore before the pass, capture inside it after the chunk's
+ * scan).  Buffers must hold max_num_seqs entries; SchedulerError 2 when no batch is in flight. */
+int qwc_scheduler_batch_prefix_ops(const qwc_scheduler* scheduler, qwc_prefix_restore_op* restores,
+                                   size_t* num_restores, qwc_prefix_save_op* saves, size_t* num_saves);
 int qwc_scheduler_abort_batch(qwc_scheduler* scheduler);
 /* *removed receives 1 when the request existed. */
 int qwc_scheduler_cancel(qwc_scheduler* scheduler, uint32_t id, int* removed);

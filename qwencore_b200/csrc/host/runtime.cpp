@@ -428,6 +428,18 @@ SubmitError Scheduler::submit(Request request) {
     return SubmitError::None;
 }
 
+SubmitError Scheduler::submit_prompt(Request request, std::vector<uint32_t> prompt, size_t snapshot_at) {
+    if (prompt.size() != request.prompt_tokens || snapshot_at > prompt.size()) {
+        return SubmitError::EmptyPrompt;  // the reference asserts; a C caller gets an error instead
+    }
+    const SubmitError submitted = submit(request);
+    if (submitted != SubmitError::None) {
+        return submitted;
+    }
+    prompts_[request.id] = PromptTokens{std::move(prompt), snapshot_at};
+    return SubmitError::None;
+}
+
 SchedulerError Scheduler::set_phase(SeqId id, Phase expected, Phase next) {
     auto it = active_.find(id);
     if (it == active_.end() || it->second.phase != expected) {
@@ -450,13 +462,21 @@ SchedulerError Scheduler::admit_one(std::optional<SeqId>* admitted) {
             waiting_.push_back(request);
             continue;
         }
-        const Rejected outcome = cache_.admit(request.id, request.prompt_tokens);
+        Admission admission;
+        const auto prompt = prompts_.find(request.id);
+        const Rejected outcome = prompt != prompts_.end()
+                                     ? cache_.admit_prompt(request.id, prompt->second.tokens, &admission)
+                                     : cache_.admit(request.id, request.prompt_tokens);
         switch (outcome) {
-            case Rejected::None:
+            case Rejected::None: {
                 committed_kv_blocks_ += reserved;
-                active_.emplace(request.id, ActiveRequest{request, reserved, 0, 0, Phase::PrefillReady});
+                ActiveRequest active{request, reserved, admission.reused, 0, Phase::PrefillReady};
+                active.has_restore = admission.has_restore;
+                active.restore = admission.restore;
+                active_.emplace(request.id, active);
                 *admitted = request.id;
                 return SchedulerError::None;
+            }
             case Rejected::NoStateSlot:
                 waiting_.push_front(request);
                 return SchedulerError::None;
@@ -519,10 +539,31 @@ SchedulerError Scheduler::next_batch(Batch* out, bool* has_batch) {
         }
         const size_t remaining = it->second.request.prompt_tokens - it->second.prefilled;
         const size_t budget = config_.max_num_batched_tokens - batch.num_tokens();
-        const size_t tokens = std::min(remaining, budget);
+        size_t tokens = std::min(remaining, budget);
         const size_t offset = it->second.prefilled;
-        if (cache_.sequence(id) == nullptr) {
+        // the snapshot point is inside the chunk: the chunk ends at it, the rest of the prompt goes in
+        // the next step (scheduler.rs:339-349)
+        std::optional<size_t> snapshot_at;
+        const auto prompt = prompts_.find(id);
+        if (prompt != prompts_.end() && cache_.prefix_capacity() > 0 && prompt->second.snapshot_at > offset &&
+            prompt->second.snapshot_at <= offset + tokens) {
+            snapshot_at = prompt->second.snapshot_at;
+            tokens = *snapshot_at - offset;
+        }
+        const Sequence* sequence = cache_.sequence(id);
+        if (sequence == nullptr) {
             return SchedulerError::Invariant;
+        }
+        const uint32_t state_slot = sequence->state_slot;
+        if (it->second.has_restore) {
+            const PrefixRestore& restore = it->second.restore;
+            batch.restores.push_back({id, state_slot, restore.snapshot, restore.copy, restore.copy_from, restore.copy_to});
+        }
+        // the next turn of the same dialog will start with this whole history
+        if (snapshot_at && *snapshot_at >= cache_.kv().block_size()) {
+            if (const std::optional<uint32_t> snapshot = cache_.reserve_snapshot()) {
+                batch.saves.push_back({id, state_slot, *snapshot});
+            }
         }
         const SchedulerError phase = set_phase(id, Phase::PrefillReady, Phase::PrefillInFlight);
         if (phase != SchedulerError::None) {
@@ -573,6 +614,23 @@ SchedulerError Scheduler::complete_batch_multi(const std::vector<SeqId>& stopped
     }
     Batch batch = std::move(*in_flight_);
     in_flight_.reset();
+    for (const PrefixRestoreOp& op : batch.restores) {
+        auto it = active_.find(op.id);
+        if (it != active_.end()) {
+            it->second.has_restore = false;
+        }
+        cache_.finish_restore(op.snapshot);
+    }
+    for (const PrefixSaveOp& op : batch.saves) {
+        const auto prompt = prompts_.find(op.id);
+        if (prompt != prompts_.end()) {
+            cache_.commit_snapshot(op.snapshot, op.id,
+                                   std::vector<uint32_t>(prompt->second.tokens.begin(),
+                                                         prompt->second.tokens.begin() + prompt->second.snapshot_at));
+        } else {
+            cache_.cancel_snapshot(op.snapshot);
+        }
+    }
     for (const PrefillChunk& chunk : batch.prefill) {
         auto it = active_.find(chunk.id);
         if (it == active_.end() || it->second.phase != Phase::PrefillInFlight) {
@@ -606,6 +664,7 @@ SchedulerError Scheduler::complete_batch_multi(const std::vector<SeqId>& stopped
             completed->push_back({id, active.generated, was_stopped ? FinishReason::Stopped : FinishReason::Length});
             committed_kv_blocks_ -= active.reserved_blocks;
             cache_.release(id);
+            prompts_.erase(id);
             active_.erase(it);
         } else {
             active.phase = Phase::DecodeReady;
@@ -621,6 +680,11 @@ SchedulerError Scheduler::abort_batch() {
     }
     Batch batch = std::move(*in_flight_);
     in_flight_.reset();
+    // restores stay with their sequences and go with the next chunk; snapshots were not captured: their
+    // slots are free again (scheduler.rs:536-540)
+    for (const PrefixSaveOp& op : batch.saves) {
+        cache_.cancel_snapshot(op.snapshot);
+    }
     for (auto it = batch.prefill.rbegin(); it != batch.prefill.rend(); ++it) {
         const SchedulerError phase = set_phase(it->id, Phase::PrefillInFlight, Phase::PrefillReady);
         if (phase != SchedulerError::None) {
@@ -655,6 +719,7 @@ SchedulerError Scheduler::cancel(SeqId id, bool* removed) {
     auto queued = std::find_if(waiting_.begin(), waiting_.end(), [&](const Request& r) { return r.id == id; });
     if (queued != waiting_.end()) {
         waiting_.erase(queued);
+        prompts_.erase(id);
         *removed = true;
         return SchedulerError::None;
     }
@@ -663,7 +728,11 @@ SchedulerError Scheduler::cancel(SeqId id, bool* removed) {
         prefill_ready_.erase(std::remove(prefill_ready_.begin(), prefill_ready_.end(), id), prefill_ready_.end());
         decode_ready_.erase(std::remove(decode_ready_.begin(), decode_ready_.end(), id), decode_ready_.end());
         committed_kv_blocks_ -= it->second.reserved_blocks;
+        if (it->second.has_restore) {
+            cache_.finish_restore(it->second.restore.snapshot);
+        }
         cache_.release(id);
+        prompts_.erase(id);
         active_.erase(it);
         *removed = true;
     }

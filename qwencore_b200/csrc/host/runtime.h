@@ -180,9 +180,28 @@ struct PrefillChunk {
     size_t tokens;
 };
 
+// crates/qwc-runtime/src/scheduler.rs:52-68: prefix-cache work of a step.  The executor restores before
+// the pass and captures inside it, after the chunk's scan.
+struct PrefixRestoreOp {
+    SeqId id;
+    uint32_t state_slot;
+    uint32_t snapshot;
+    bool copy;  // the prefix's incomplete page must be copied before the step: copy_from -> copy_to
+    uint32_t copy_from;
+    uint32_t copy_to;
+};
+
+struct PrefixSaveOp {
+    SeqId id;
+    uint32_t state_slot;
+    uint32_t snapshot;
+};
+
 struct Batch {
     std::vector<PrefillChunk> prefill;
     std::vector<SeqId> decode;
+    std::vector<PrefixRestoreOp> restores;
+    std::vector<PrefixSaveOp> saves;
     size_t num_seqs() const { return prefill.size() + decode.size(); }
     size_t num_tokens() const;
     bool empty() const { return prefill.empty() && decode.empty(); }
@@ -224,6 +243,11 @@ class Scheduler {
 public:
     Scheduler(SchedulerConfig config, CacheManager cache);
     SubmitError submit(Request request);
+    // The same with the prompt tokens themselves: only such a request can continue a cached prefix and
+    // leave its own.  `snapshot_at`: the length of the prefix worth caching (for chat, the history
+    // boundary before the generation prompt); the prefill chunk is cut there (scheduler.rs:237-261).
+    void enable_prefix_cache(size_t snapshots) { cache_.enable_prefix_cache(snapshots); }
+    SubmitError submit_prompt(Request request, std::vector<uint32_t> prompt, size_t snapshot_at);
     // Returns None with *has_batch == false when there is nothing to run.
     SchedulerError next_batch(Batch* batch, bool* has_batch);
     SchedulerError complete_batch(const std::vector<SeqId>& stopped, std::vector<Completion>* completed);
@@ -248,6 +272,12 @@ private:
         size_t prefilled;
         size_t generated;
         Phase phase;
+        bool has_restore = false;  // the prefix snapshot has not been restored yet
+        PrefixRestore restore;
+    };
+    struct PromptTokens {
+        std::vector<uint32_t> tokens;
+        size_t snapshot_at;
     };
     SchedulerError admit_one(std::optional<SeqId>* admitted);
     SchedulerError set_phase(SeqId id, Phase expected, Phase next);
@@ -258,6 +288,7 @@ private:
     std::deque<SeqId> prefill_ready_;
     std::deque<SeqId> decode_ready_;
     std::unordered_map<SeqId, ActiveRequest> active_;
+    std::unordered_map<SeqId, PromptTokens> prompts_;
     size_t committed_kv_blocks_ = 0;
     std::optional<Batch> in_flight_;
 };

@@ -191,6 +191,36 @@ int qwc_scheduler_complete_batch_multi(qwc_scheduler* scheduler, const uint32_t*
     return static_cast<int>(error);
 }
 
+void qwc_scheduler_enable_prefix_cache(qwc_scheduler* scheduler, size_t snapshots) {
+    scheduler->scheduler.enable_prefix_cache(snapshots);
+}
+
+int qwc_scheduler_submit_prompt(qwc_scheduler* scheduler, uint32_t id, const uint32_t* prompt, size_t prompt_tokens,
+                                size_t max_new_tokens, size_t snapshot_at) {
+    return static_cast<int>(scheduler->scheduler.submit_prompt(
+        Request{id, prompt_tokens, max_new_tokens}, std::vector<uint32_t>(prompt, prompt + prompt_tokens), snapshot_at));
+}
+
+int qwc_scheduler_batch_prefix_ops(const qwc_scheduler* scheduler, qwc_prefix_restore_op* restores,
+                                   size_t* num_restores, qwc_prefix_save_op* saves, size_t* num_saves) {
+    *num_restores = 0;
+    *num_saves = 0;
+    const Batch* batch = scheduler->scheduler.in_flight();
+    if (batch == nullptr) {
+        return static_cast<int>(SchedulerError::NoBatchInFlight);
+    }
+    *num_restores = batch->restores.size();
+    *num_saves = batch->saves.size();
+    for (size_t i = 0; i < batch->restores.size(); ++i) {
+        const PrefixRestoreOp& op = batch->restores[i];
+        restores[i] = {op.id, op.state_slot, op.snapshot, op.copy ? 1u : 0u, op.copy_from, op.copy_to};
+    }
+    for (size_t i = 0; i < batch->saves.size(); ++i) {
+        saves[i] = {batch->saves[i].id, batch->saves[i].state_slot, batch->saves[i].snapshot};
+    }
+    return 0;
+}
+
 int qwc_scheduler_abort_batch(qwc_scheduler* scheduler) { return static_cast<int>(scheduler->scheduler.abort_batch()); }
 
 int qwc_scheduler_cancel(qwc_scheduler* scheduler, uint32_t id, int* removed) {

@@ -86,6 +86,9 @@ ENGINE_SYMBOLS = {
     "qwc_scheduler_next_batch": (c_int, [P, P, POINTER(c_size_t), P, POINTER(c_size_t)]),
     "qwc_scheduler_complete_batch": (c_int, [P, P, c_size_t, P, c_size_t, POINTER(c_size_t)]),
     "qwc_scheduler_complete_batch_multi": (c_int, [P, P, c_size_t, P, P, c_size_t, P, c_size_t, POINTER(c_size_t)]),
+    "qwc_scheduler_enable_prefix_cache": (None, [P, c_size_t]),
+    "qwc_scheduler_submit_prompt": (c_int, [P, c_uint32, P, c_size_t, c_size_t, c_size_t]),
+    "qwc_scheduler_batch_prefix_ops": (c_int, [P, P, POINTER(c_size_t), P, POINTER(c_size_t)]),
     "qwc_scheduler_abort_batch": (c_int, [P]),
     "qwc_scheduler_cancel": (c_int, [P, c_uint32, POINTER(c_int)]),
     "qwc_scheduler_remaining_tokens": (c_longlong, [P, c_uint32]),
@@ -131,6 +134,15 @@ def _u32(values) -> np.ndarray:
 class Admission(ctypes.Structure):
     _fields_ = [("reused", c_size_t), ("has_restore", c_int), ("snapshot", c_uint32), ("copy", c_int),
                 ("copy_from", c_uint32), ("copy_to", c_uint32)]
+
+
+class PrefixRestoreOp(ctypes.Structure):
+    _fields_ = [("id", c_uint32), ("state_slot", c_uint32), ("snapshot", c_uint32), ("copy", c_uint32),
+                ("copy_from", c_uint32), ("copy_to", c_uint32)]
+
+
+class PrefixSaveOp(ctypes.Structure):
+    _fields_ = [("id", c_uint32), ("state_slot", c_uint32), ("snapshot", c_uint32)]
 
 
 class CacheManager:
@@ -267,8 +279,34 @@ class Scheduler:
             raise RuntimeError_("SchedulerError", code, SCHEDULER_ERROR)
         if n_decode.value == 0 and n_prefill.value == 0:
             return None
+        restores = (PrefixRestoreOp * self.max_num_seqs)()
+        saves = (PrefixSaveOp * self.max_num_seqs)()
+        n_restores, n_saves = c_size_t(), c_size_t()
+        code = lib.qwc_scheduler_batch_prefix_ops(self._handle, restores, byref(n_restores), saves, byref(n_saves))
+        if code != 0:
+            raise RuntimeError_("SchedulerError", code, SCHEDULER_ERROR)
         return {"decode": decode[:n_decode.value].tolist(),
-                "prefill": [(c.id, c.offset, c.tokens) for c in prefill[:n_prefill.value]]}
+                "prefill": [(c.id, c.offset, c.tokens) for c in prefill[:n_prefill.value]],
+                "restores": [{"id": op.id, "state_slot": op.state_slot, "snapshot": op.snapshot,
+                              "copy_block": (op.copy_from, op.copy_to) if op.copy else None}
+                             for op in restores[:n_restores.value]],
+                "saves": [{"id": op.id, "state_slot": op.state_slot, "snapshot": op.snapshot}
+                          for op in saves[:n_saves.value]]}
+
+    def enable_prefix_cache(self, snapshots: int) -> None:
+        """scheduler.rs:226-228"""
+        lib.qwc_scheduler_enable_prefix_cache(self._handle, snapshots)
+
+    def submit_prompt(self, seq_id: int, prompt, max_new_tokens: int, snapshot_at: int) -> None:
+        """scheduler.rs:237-261: the request with its prompt tokens; `snapshot_at` is the length of the
+        prefix worth caching (the prefill chunk is cut there)."""
+        prompt = _u32(list(prompt))
+        if snapshot_at > prompt.size:
+            raise ValueError("the snapshot point lies beyond the prompt")
+        code = lib.qwc_scheduler_submit_prompt(self._handle, seq_id, prompt.ctypes.data_as(P), prompt.size,
+                                               max_new_tokens, snapshot_at)
+        if code != 0:
+            raise RuntimeError_("SubmitError", code, SUBMIT_ERROR)
 
     def complete_batch(self, stopped=()):
         stopped = _u32(list(stopped))

@@ -537,6 +537,118 @@ def test_invalid_prefill_range_is_rejected(built_library):
         build_layout(cache, prefill=[(1, 8, 4)])
 
 
+# ---- the scheduler's side of the prefix cache (reference tests, crates/qwc-runtime/src/scheduler.rs:877-985) ----
+
+def drain(s):
+    """Runs what is queued to the end; the batches it took."""
+    batches = []
+    while (batch := s.next_batch()) is not None:
+        s.complete_batch()
+        batches.append(batch)
+    return batches
+
+
+def test_next_turn_continues_from_the_previous_prompt(built_library):
+    s = scheduler(2, 100, 2, 512)
+    s.enable_prefix_cache(4)
+    s.submit_prompt(1, range(150), 2, 150)
+    first = drain(s)
+    # the prompt ended in the very first step: so did the snapshot
+    assert len(first[0]["saves"]) == 1 and first[0]["restores"] == []
+    assert s.cache.prefix_entries() == 1
+
+    s.submit_prompt(2, range(200), 1, 200)
+    batch = s.next_batch()
+    assert batch["prefill"] == [(2, 150, 50)]
+    assert len(batch["restores"]) == 1
+    assert batch["restores"][0]["snapshot"] == first[0]["saves"][0]["snapshot"]
+    assert batch["restores"][0]["copy_block"] is not None
+    s.complete_batch()
+    assert s.cache.prefix_stats()["reused_tokens"] == 150
+
+
+def test_aborted_step_keeps_the_restore_and_frees_the_save(built_library):
+    s = scheduler(2, 100, 2, 512)
+    s.enable_prefix_cache(1)
+    s.submit_prompt(1, range(100), 1, 100)
+    drain(s)
+
+    s.submit_prompt(2, range(130), 1, 130)
+    batch = s.next_batch()
+    assert len(batch["restores"]) == 1
+    assert batch["saves"] == []  # the only slot belongs to a pinned entry: nowhere to capture
+    s.abort_batch()
+
+    retry = s.next_batch()
+    assert retry["restores"] == batch["restores"]
+    assert retry["prefill"] == batch["prefill"]
+
+
+def test_cancelling_before_restore_unpins_the_entry(built_library):
+    s = scheduler(2, 100, 2, 512)
+    s.enable_prefix_cache(1)
+    s.submit_prompt(1, range(100), 1, 100)
+    drain(s)
+    s.submit_prompt(2, range(130), 1, 130)
+    assert s.next_batch() is not None
+    s.abort_batch()
+    assert s.cancel(2)
+    # the entry can be evicted again: a new snapshot takes its slot
+    s.submit_prompt(3, [t + 7 for t in range(64)], 1, 64)
+    assert len(s.next_batch()["saves"]) == 1
+
+
+def test_prefill_is_cut_at_the_history_boundary(built_library):
+    """150 prompt tokens of which the last 6 open the answer: the snapshot lands at 144 and the next
+    turn continues from exactly there."""
+    s = scheduler(2, 100, 2, 512)
+    s.enable_prefix_cache(2)
+    s.submit_prompt(1, range(150), 1, 144)
+    first = s.next_batch()
+    assert first["prefill"][0][2] == 144
+    assert len(first["saves"]) == 1
+    s.complete_batch()
+    tail = s.next_batch()
+    assert tail["prefill"] == [(1, 144, 6)]
+    assert tail["saves"] == []
+    s.complete_batch()
+    drain(s)
+
+    following = list(range(144)) + list(range(1000, 1100))
+    s.submit_prompt(2, following, 1, 238)
+    batch = s.next_batch()
+    assert batch["prefill"][0][1] == 144
+    assert len(batch["restores"]) == 1
+
+
+def test_aborted_save_returns_its_snapshot_slot(built_library):
+    """abort_batch cancels the step's captures: with one slot, the retry can reserve it again."""
+    s = scheduler(2, 100, 2, 512)
+    s.enable_prefix_cache(1)
+    s.submit_prompt(1, range(100), 1, 100)
+    first = s.next_batch()
+    assert len(first["saves"]) == 1
+    s.abort_batch()
+    assert s.cache.prefix_entries() == 0
+    retry = s.next_batch()
+    assert retry["saves"] == first["saves"]
+    s.complete_batch()
+    assert s.cache.prefix_entries() == 1
+
+
+def test_submit_prompt_checks_its_lengths(built_library):
+    s = scheduler(2, 100, 2, 512)
+    with pytest.raises(ValueError):
+        s.submit_prompt(1, range(10), 1, 11)
+    s.submit_prompt(1, range(10), 1, 10)
+    with pytest.raises(RuntimeError_) as error:
+        s.submit_prompt(1, range(10), 1, 10)
+    assert error.value.name == "Duplicate"
+    # without a prefix cache a prompt is plain admission: no cut, no ops
+    batch = s.next_batch()
+    assert batch["prefill"] == [(1, 0, 10)] and batch["saves"] == [] and batch["restores"] == []
+
+
 def test_host_layout_agrees_with_the_oracle_statement(built_library):
     """The C++ BatchLayout and the oracle's restatement of the same file give identical arrays."""
     from oracle import oracle
