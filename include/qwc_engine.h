@@ -312,6 +312,72 @@ int qwc_engine_time_phases(qwc_engine* engine, int rows, const char* label_prefi
 int qwc_worker_step(qwc_engine* engine, qwc_scheduler* scheduler, uint32_t eos_token, size_t* num_decoded,
                     qwc_completion* completed, size_t max_completed, size_t* num_completed);
 
+/* ---------------------------------------------------------------------------------- */
+/* Worker loop at token level (crates/qwc-engine/src/bin/serve.rs:777-1074, :1133-1156,  */
+/* :1339-1368, :1438-1442): commands in, plan, layout, one executor call per step, token  */
+/* emission with the stop rules, completion, rollback and fail-all on an error,           */
+/* cancellation of abandoned jobs.  Text (tokenizer, stop strings) and the speculative    */
+/* branch are the caller's: the token callback's return value says "stop here".           */
+/* ---------------------------------------------------------------------------------- */
+typedef struct qwc_worker qwc_worker;
+
+/* What a step hands to its executor.  Layout arrays as BatchLayout (layout.rs:54-152): decode rows
+ * first; tokens[token_offsets[i] .. token_offsets[i+1]) are the input tokens of sequence i (a decode
+ * row: the token sampled by the previous step; a prefill chunk: its slice of the prompt). */
+typedef struct qwc_step_view {
+    size_t num_sequences;
+    size_t num_decode;
+    const uint32_t* seq_ids;
+    const uint32_t* state_slots;
+    const uint32_t* position_starts;
+    const uint32_t* context_lens;
+    const uint32_t* token_offsets;       /* num_sequences + 1 */
+    const uint32_t* block_table_offsets; /* num_sequences + 1 */
+    const uint32_t* block_ids;
+    size_t num_block_ids;
+    const uint32_t* tokens;
+    size_t num_tokens;
+    const qwc_table_edit* edits; /* page-table edits the plan produced, to apply before the step */
+    size_t num_edits;
+    const qwc_prefix_restore_op* restores;
+    size_t num_restores;
+    const qwc_prefix_save_op* saves;
+    size_t num_saves;
+} qwc_step_view;
+
+/* Runs the step and writes one sampled token per sequence, layout order.  0, or an error code with
+ * which the worker fails: nothing of such a step is committed (the plan is rolled back). */
+typedef int (*qwc_execute_fn)(void* user, const qwc_step_view* step, uint32_t* sampled);
+/* kind 0 Token (value = token; a non-zero return stops the sequence after it), 1 Done (value = tokens
+ * emitted, reason 0 Length / 1 Stopped), 2 Error (value = the code the worker failed with, or
+ * 0x5000 + SubmitError for a refused request). */
+typedef int (*qwc_event_fn)(void* user, uint32_t id, uint32_t kind, uint32_t value, uint32_t reason);
+
+qwc_worker* qwc_worker_new(qwc_scheduler* scheduler, qwc_execute_fn execute, void* execute_user, qwc_event_fn event,
+                           void* event_user, const uint32_t* eos_ids, size_t num_eos);
+void qwc_worker_free(qwc_worker* worker);
+/* Thread-safe: queue a request / tell the worker that nobody listens to a request any more / tell it
+ * that no more commands will come (qwc_worker_run then returns once its jobs are finished). */
+void qwc_worker_submit(qwc_worker* worker, uint32_t id, const uint32_t* prompt, size_t prompt_tokens,
+                       size_t max_new_tokens, size_t history_tokens, int ignore_eos);
+void qwc_worker_abandon(qwc_worker* worker, uint32_t id);
+void qwc_worker_shutdown(qwc_worker* worker);
+/* One pass of the loop body (*progressed = 1 when a step ran) / the loop itself.  0, or the code the
+ * worker failed with: 0x2000 + SchedulerError, 0x3000 + LayoutError, 0x5100 a decode row without a
+ * sampled token, 0x5101 a prefill chunk without its prompt, 0x5102 an executor that returned too few
+ * tokens, or the executor's own code.  A failed worker has sent Error to every job and stays failed. */
+int qwc_worker_iterate(qwc_worker* worker, int* progressed);
+int qwc_worker_run(qwc_worker* worker);
+size_t qwc_worker_jobs(const qwc_worker* worker);
+uint64_t qwc_worker_steps(const qwc_worker* worker);
+uint64_t qwc_worker_aborted_steps(const qwc_worker* worker);
+
+/* A qwc_execute_fn over the GPU engine (`user` = the qwc_engine*): decode rows run the decode step
+ * (qwc_engine_decode); a prefill chunk is accounted, not computed (the synthetic caches already hold
+ * data for the prompt) and samples a token derived from its sequence id; prefix restores and saves are
+ * not executed.  Error codes as qwc_engine_decode. */
+int qwc_engine_execute_step(void* engine, const qwc_step_view* step, uint32_t* sampled);
+
 #ifdef __cplusplus
 }
 #endif

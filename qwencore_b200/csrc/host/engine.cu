@@ -1661,4 +1661,41 @@ int qwc_worker_step(qwc_engine* e, qwc_scheduler* scheduler, uint32_t eos_token,
     return 0;
 }
 
+// A qwc_execute_fn over this engine, for the token-level worker loop.
+int qwc_engine_execute_step(void* engine, const qwc_step_view* step, uint32_t* sampled) {
+    auto* e = static_cast<qwc_engine*>(engine);
+    if (e == nullptr || step == nullptr || sampled == nullptr || step->num_decode > step->num_sequences) {
+        return cudaErrorInvalidValue;
+    }
+    const int rows = static_cast<int>(step->num_decode);
+    if (rows > e->cfg.max_batch) {
+        return cudaErrorInvalidValue;
+    }
+    if (rows > 0) {
+        std::vector<uint32_t> tokens(rows);
+        for (int row = 0; row < rows; ++row) {
+            if (step->token_offsets[row + 1] - step->token_offsets[row] != 1) {
+                return cudaErrorInvalidValue;  // a decode row carries one token (executor.rs:898-903)
+            }
+            tokens[row] = step->tokens[step->token_offsets[row]];
+        }
+        const int status =
+            qwc_engine_decode(e, step->state_slots, tokens.data(), step->edits, step->num_edits, rows, sampled);
+        if (status != 0) {
+            return status;
+        }
+    } else if (step->num_edits > 0) {
+        const int status = qwc_engine_apply_edits(e, step->edits, step->num_edits);
+        if (status != 0) {
+            return status;
+        }
+    }
+    // Prompt tokens of a prefill chunk are taken as already resident; the chunk samples a token
+    // derived from its sequence id.
+    for (size_t row = step->num_decode; row < step->num_sequences; ++row) {
+        sampled[row] = (step->seq_ids[row] * 7919u + 1000u) % static_cast<uint32_t>(e->cfg.vocab);
+    }
+    return 0;
+}
+
 }  // extern "C"

@@ -119,6 +119,16 @@ ENGINE_SYMBOLS = {
     "qwc_engine_stream": (P, [P]),
     "qwc_engine_profile_step": (c_int, [P, c_int, POINTER(PhaseTime), c_int]),
     "qwc_engine_time_phases": (c_int, [P, c_int, ctypes.c_char_p, c_int, POINTER(ctypes.c_float), POINTER(c_int)]),
+    "qwc_worker_new": (P, [P, P, P, P, P, P, c_size_t]),
+    "qwc_worker_free": (None, [P]),
+    "qwc_worker_submit": (None, [P, c_uint32, P, c_size_t, c_size_t, c_size_t, c_int]),
+    "qwc_worker_abandon": (None, [P, c_uint32]),
+    "qwc_worker_shutdown": (None, [P]),
+    "qwc_worker_iterate": (c_int, [P, POINTER(c_int)]),
+    "qwc_worker_run": (c_int, [P]),
+    "qwc_worker_jobs": (c_size_t, [P]),
+    "qwc_worker_steps": (ctypes.c_uint64, [P]),
+    "qwc_worker_aborted_steps": (ctypes.c_uint64, [P]),
     "qwc_worker_step": (c_int, [P, P, c_uint32, POINTER(c_size_t), P, c_size_t, POINTER(c_size_t)]),
 }
 for _name, (_restype, _argtypes) in ENGINE_SYMBOLS.items():
@@ -356,6 +366,113 @@ class Scheduler:
 
     def committed_kv_blocks(self) -> int:
         return lib.qwc_scheduler_committed_kv_blocks(self._handle)
+
+
+class StepView(ctypes.Structure):
+    """qwc_step_view: what a worker step hands to its executor."""
+    _fields_ = [("num_sequences", c_size_t), ("num_decode", c_size_t), ("seq_ids", POINTER(c_uint32)),
+                ("state_slots", POINTER(c_uint32)), ("position_starts", POINTER(c_uint32)),
+                ("context_lens", POINTER(c_uint32)), ("token_offsets", POINTER(c_uint32)),
+                ("block_table_offsets", POINTER(c_uint32)), ("block_ids", POINTER(c_uint32)),
+                ("num_block_ids", c_size_t), ("tokens", POINTER(c_uint32)), ("num_tokens", c_size_t),
+                ("edits", POINTER(c_uint32)), ("num_edits", c_size_t), ("restores", POINTER(PrefixRestoreOp)),
+                ("num_restores", c_size_t), ("saves", POINTER(PrefixSaveOp)), ("num_saves", c_size_t)]
+
+    def as_dict(self) -> dict:
+        n = self.num_sequences
+        take = lambda pointer, count: [pointer[i] for i in range(count)]  # noqa: E731
+        offsets = take(self.token_offsets, n + 1)
+        tokens = take(self.tokens, self.num_tokens)
+        return {"num_decode": self.num_decode, "seq_ids": take(self.seq_ids, n),
+                "state_slots": take(self.state_slots, n), "position_starts": take(self.position_starts, n),
+                "context_lens": take(self.context_lens, n), "token_offsets": offsets,
+                "tokens": [tokens[offsets[i]:offsets[i + 1]] for i in range(n)],
+                "edits": [take(self.edits, 4 * self.num_edits)[4 * i:4 * i + 4] for i in range(self.num_edits)],
+                "restores": [(op.id, op.state_slot, op.snapshot) for op in take(self.restores, self.num_restores)],
+                "saves": [(op.id, op.state_slot, op.snapshot) for op in take(self.saves, self.num_saves)]}
+
+
+EXECUTE_FN = ctypes.CFUNCTYPE(c_int, c_void_p, POINTER(StepView), POINTER(c_uint32))
+EVENT_FN = ctypes.CFUNCTYPE(c_int, c_void_p, c_uint32, c_uint32, c_uint32, c_uint32)
+WORKER_EVENT = {0: "token", 1: "done", 2: "error"}
+
+
+class Worker:
+    """The serving worker loop at token level (crates/qwc-engine/src/bin/serve.rs:777-1074).
+
+    `executor`: an Engine (its decode step runs the decode rows) or a callable
+    `executor(step: dict) -> list of one sampled token per sequence` (raise, or return an int error
+    code, to fail the step).  `on_event(seq_id, kind, value, reason)` with kind "token" / "done" /
+    "error"; for a token, a true return value stops the sequence after it."""
+
+    def __init__(self, scheduler: Scheduler, executor, on_event, eos_ids=()):
+        self._scheduler = scheduler  # the worker borrows it
+        self.raised = None
+
+        def event(_user, seq_id, kind, value, reason):
+            try:
+                return 1 if on_event(seq_id, WORKER_EVENT[kind], value, reason) else 0
+            except BaseException as error:  # a callback must not unwind through the C loop
+                self.raised = error
+                return 1
+
+        self._event = EVENT_FN(event)
+        if callable(executor):
+            def execute(_user, view, sampled):
+                try:
+                    result = executor(view.contents.as_dict())
+                    if isinstance(result, int):
+                        return result
+                    for i, token in enumerate(result):
+                        sampled[i] = token
+                    return 0 if len(result) >= view.contents.num_sequences else 0x5102
+                except BaseException as error:
+                    self.raised = error
+                    return 0x5200
+            self._execute = EXECUTE_FN(execute)
+            execute_pointer, user = ctypes.cast(self._execute, P), None
+        else:
+            self._engine = executor
+            execute_pointer, user = ctypes.cast(lib.qwc_engine_execute_step, P), executor._handle
+        eos = _u32(list(eos_ids))
+        self._handle = lib.qwc_worker_new(scheduler._handle, execute_pointer, user, ctypes.cast(self._event, P), None,
+                                          eos.ctypes.data_as(P), eos.size)
+        if not self._handle:
+            raise ValueError("qwc_worker_new refused its arguments")
+
+    def __del__(self):
+        if getattr(self, "_handle", None):
+            lib.qwc_worker_free(self._handle)
+            self._handle = None
+
+    def submit(self, seq_id: int, prompt, max_new_tokens: int, history_tokens: int = 0, ignore_eos: bool = False):
+        prompt = _u32(list(prompt))
+        lib.qwc_worker_submit(self._handle, seq_id, prompt.ctypes.data_as(P), prompt.size, max_new_tokens,
+                              history_tokens, int(ignore_eos))
+
+    def abandon(self, seq_id: int) -> None:
+        lib.qwc_worker_abandon(self._handle, seq_id)
+
+    def shutdown(self) -> None:
+        lib.qwc_worker_shutdown(self._handle)
+
+    def iterate(self):
+        """One pass of the loop body: (status code, whether a step ran)."""
+        progressed = c_int()
+        return lib.qwc_worker_iterate(self._handle, byref(progressed)), bool(progressed.value)
+
+    def run(self) -> int:
+        """The loop; returns after shutdown() once every job is finished, or with the failure code."""
+        return lib.qwc_worker_run(self._handle)
+
+    def jobs(self) -> int:
+        return lib.qwc_worker_jobs(self._handle)
+
+    def steps(self) -> int:
+        return lib.qwc_worker_steps(self._handle)
+
+    def aborted_steps(self) -> int:
+        return lib.qwc_worker_aborted_steps(self._handle)
 
 
 def build_layout(cache: CacheManager, decode=(), prefill=(), max_block_ids: int = 1 << 16):

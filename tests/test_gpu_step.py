@@ -200,6 +200,35 @@ def test_worker_loop_drives_scheduler_and_engine(cuda, engine_module):
         engine.close()
 
 
+def test_token_level_worker_runs_on_the_engine(cuda, engine_module):
+    """The worker loop with the engine as its executor (qwc_engine_execute_step): requests queued with
+    their prompts, tokens through the event callback, both pools back at the end."""
+    config = small_config(engine_module, num_layers=4, max_batch=3, state_slots=3)
+    engine = engine_module.Engine(config)
+    try:
+        scheduler = engine_module.Scheduler(3, 64, 3, 160, 16)
+        events = []
+        worker = engine_module.Worker(scheduler, engine, lambda *event: events.append(event) and False)
+        budgets = {1: 3, 2: 5, 3: 2, 4: 4}
+        for seq, prompt in [(1, 20), (2, 33), (3, 16), (4, 8)]:
+            worker.submit(seq, range(prompt), budgets[seq])
+        for _ in range(60):
+            status, progressed = worker.iterate()
+            assert status == 0
+            if not progressed and worker.jobs() == 0:
+                break
+        for seq, budget in budgets.items():
+            tokens = [value for s, kind, value, _ in events if s == seq and kind == "token"]
+            assert len(tokens) == budget and all(token < config.vocab for token in tokens)
+            # the first token a sequence emits is the one its (accounted, not computed) prefill sampled
+            assert tokens[0] == (seq * 7919 + 1000) % config.vocab
+            assert [(value, reason) for s, kind, value, reason in events if s == seq and kind == "done"] == [(budget, 0)]
+        assert worker.aborted_steps() == 0
+        assert scheduler.cache.states_in_use() == 0 and scheduler.cache.free_blocks() == 160
+    finally:
+        engine.close()
+
+
 def test_decode_reports_packing_errors(cuda, engine_module):
     from qwencore_b200 import abi
 
