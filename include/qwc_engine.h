@@ -259,6 +259,12 @@ void qwc_engine_traffic(const qwc_engine* engine, int rows, double context_token
 /* Applies table edits (host array) to the device page table: one H2D copy and one kernel. */
 int qwc_engine_apply_edits(qwc_engine* engine, const qwc_table_edit* edits, size_t count);
 
+/* Copies KV page `from` onto page `to` in every full-attention layer, asynchronously on the engine's
+ * stream (Executor::copy_kv_block, crates/qwc-engine/src/executor.rs:825-835): a sequence that
+ * continues a cached prefix ending inside a page appends to a copy of that page
+ * (qwc_prefix_restore_op.copy_from / copy_to).  cudaErrorInvalidValue for a page outside the pool. */
+int qwc_engine_copy_kv_block(qwc_engine* engine, uint32_t from, uint32_t to);
+
 /*
  * One decode step for `rows` rows.  Host inputs: row_slots u32[rows] (batch order),
  * tokens u32[rows], optional table edits to apply first.  Copies them to the device, packs
@@ -374,8 +380,9 @@ uint64_t qwc_worker_aborted_steps(const qwc_worker* worker);
 
 /* A qwc_execute_fn over the GPU engine (`user` = the qwc_engine*): decode rows run the decode step
  * (qwc_engine_decode); a prefill chunk is accounted, not computed (the synthetic caches already hold
- * data for the prompt) and samples a token derived from its sequence id; prefix restores and saves are
- * not executed.  Error codes as qwc_engine_decode. */
+ * data for the prompt) and samples a token derived from its sequence id; of the prefix ops the page
+ * copies of the restores are executed (qwc_engine_copy_kv_block), the state snapshots, which belong to
+ * the prefill pass, are not.  Error codes as qwc_engine_decode. */
 int qwc_engine_execute_step(void* engine, const qwc_step_view* step, uint32_t* sampled);
 
 #ifdef __cplusplus

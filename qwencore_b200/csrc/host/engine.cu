@@ -1451,6 +1451,29 @@ int qwc_engine_apply_edits(qwc_engine* e, const qwc_table_edit* edits, size_t co
     return status != 0 ? status : synced;
 }
 
+// Executor::copy_kv_block (executor.rs:825-835): the tail of a cached prefix lies in an incomplete page
+// to which the new sequence will append, so it gets a copy of its own in every attention layer.
+int qwc_engine_copy_kv_block(qwc_engine* e, uint32_t from, uint32_t to) {
+    if (e == nullptr || from >= static_cast<uint32_t>(e->cfg.kv_pool_blocks) ||
+        to >= static_cast<uint32_t>(e->cfg.kv_pool_blocks)) {
+        return cudaErrorInvalidValue;
+    }
+    if (from == to) {
+        return 0;
+    }
+    const size_t page = static_cast<size_t>(kKvHeads) * e->cfg.kv_page_size * kHeadDim;
+    for (const Layer& layer : e->layers) {
+        if (!layer.full) {
+            continue;
+        }
+        QWC_TRY(cudaMemcpyAsync(layer.k_cache + to * page, layer.k_cache + from * page, page, cudaMemcpyDeviceToDevice,
+                                e->stream));
+        QWC_TRY(cudaMemcpyAsync(layer.v_cache + to * page, layer.v_cache + from * page, page, cudaMemcpyDeviceToDevice,
+                                e->stream));
+    }
+    return 0;
+}
+
 int qwc_engine_decode(qwc_engine* e, const uint32_t* row_slots, const uint32_t* tokens, const qwc_table_edit* edits,
                       size_t num_edits, int rows, uint32_t* sampled) {
     if (e == nullptr || row_slots == nullptr || tokens == nullptr || sampled == nullptr || rows <= 0 ||
@@ -1670,6 +1693,16 @@ int qwc_engine_execute_step(void* engine, const qwc_step_view* step, uint32_t* s
     const int rows = static_cast<int>(step->num_decode);
     if (rows > e->cfg.max_batch) {
         return cudaErrorInvalidValue;
+    }
+    // serve.rs:1268-1273: pages a restored prefix shares only in part are copied before the step (on
+    // the step's stream, so the step sees them)
+    for (size_t i = 0; i < step->num_restores; ++i) {
+        if (step->restores[i].copy != 0) {
+            const int copied = qwc_engine_copy_kv_block(e, step->restores[i].copy_from, step->restores[i].copy_to);
+            if (copied != 0) {
+                return copied;
+            }
+        }
     }
     if (rows > 0) {
         std::vector<uint32_t> tokens(rows);

@@ -114,6 +114,7 @@ ENGINE_SYMBOLS = {
     "qwc_engine_write": (c_int, [P, c_char_p, c_int, P, c_size_t]),
     "qwc_engine_traffic": (None, [P, c_int, c_double, POINTER(StepTraffic)]),
     "qwc_engine_apply_edits": (c_int, [P, P, c_size_t]),
+    "qwc_engine_copy_kv_block": (c_int, [P, c_uint32, c_uint32]),
     "qwc_engine_decode": (c_int, [P, P, P, P, c_size_t, c_int, P]),
     "qwc_engine_replay": (c_int, [P, c_int]),
     "qwc_engine_stream": (P, [P]),
@@ -607,6 +608,12 @@ class Engine:
         if code != 0:
             raise abi.QwcError(code if code > 0 else -code, "qwc_engine_time_phases")
         return milliseconds.value, launches.value
+
+    def copy_kv_block(self, source: int, target: int) -> None:
+        """Executor::copy_kv_block (executor.rs:825-835); asynchronous on the engine's stream."""
+        code = lib.qwc_engine_copy_kv_block(self._handle, source, target)
+        if code != 0:
+            raise abi.QwcError(code, "qwc_engine_copy_kv_block")
 
     def worker_step(self, scheduler: Scheduler, eos_token: int = 0xFFFFFFFF):
         decoded, count = c_size_t(), c_size_t()

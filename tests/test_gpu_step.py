@@ -229,6 +229,35 @@ def test_token_level_worker_runs_on_the_engine(cuda, engine_module):
         engine.close()
 
 
+def test_copy_kv_block_copies_one_page_in_every_attention_layer(cuda, engine_module):
+    """Executor::copy_kv_block (executor.rs:825-835): page `to` becomes page `from` in the K and V pools
+    of every full-attention layer; nothing else moves; a page outside the pool is refused."""
+    from qwencore_b200 import abi
+
+    config = small_config(engine_module, num_layers=8)
+    engine = engine_module.Engine(config)
+    try:
+        attention_layers = [i for i in range(config.num_layers) if (i + 1) % config.full_attention_interval == 0]
+        assert attention_layers
+        shape = (config.kv_pool_blocks, -1)
+        before = {(name, i): engine.read(name, i, np.uint8).reshape(shape).copy()
+                  for i in attention_layers for name in ("k_cache", "v_cache")}
+        engine.copy_kv_block(5, 131)
+        engine.copy_kv_block(7, 7)  # (reading a tensor waits for the engine's stream)
+        for (name, i), old in before.items():
+            new = engine.read(name, i, np.uint8).reshape(shape)
+            assert not np.array_equal(old[5], old[131])  # the seeded pools differ page by page
+            want = old.copy()
+            want[131] = old[5]
+            assert np.array_equal(new, want), (name, i)
+        for pages in ((config.kv_pool_blocks, 0), (0, config.kv_pool_blocks)):
+            with pytest.raises(abi.QwcError) as error:
+                engine.copy_kv_block(*pages)
+            assert error.value.code == abi.CUDA_ERROR_INVALID_VALUE
+    finally:
+        engine.close()
+
+
 def test_decode_reports_packing_errors(cuda, engine_module):
     from qwencore_b200 import abi
 
