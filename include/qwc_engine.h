@@ -193,6 +193,11 @@ typedef struct qwc_engine_config {
                                     into every rank's memory and the consumers sum them
                                     (qwc_engine_exchange_handle / qwc_engine_open_peers).  Needs max_batch == 1;
                                     with split_size 1 the rank exchanges with itself (tests). */
+    unsigned long long memory_limit; /* ceiling in bytes for the engine's device allocations, 0 = none
+                                    (set_memory_limit, crates/qwc-cuda/src/memory.rs:31-58): clipped to the
+                                    device's free memory less 512 MiB; an allocation that would pass it is
+                                    refused BEFORE cudaMalloc with cudaErrorMemoryAllocation (2) and
+                                    qwc_engine_create frees what it had taken */
 } qwc_engine_config;
 
 /* Fills `config` with the synthetic 27B-shaped model of the benchmark. */
@@ -202,6 +207,9 @@ void qwc_engine_default_config(qwc_engine_config* config);
  * DeltaNet state on the device.  Returns a cudaError_t. */
 int qwc_engine_create(const qwc_engine_config* config, qwc_engine** engine);
 void qwc_engine_destroy(qwc_engine* engine);
+/* Bytes the engine asked for so far and its ceiling, 0 when it has none (memory_usage,
+ * crates/qwc-cuda/src/memory.rs:73-78; requested bytes, not what the driver rounded them to). */
+void qwc_engine_memory_usage(const qwc_engine* engine, size_t* used, size_t* limit);
 
 /* Joins a NCCL communicator for the column-split mode.  `unique_id` is the 128-byte
  * ncclUniqueId made by rank 0 (qwc_engine_nccl_unique_id) and distributed by the caller.

@@ -12,7 +12,9 @@
 #include <cuda_runtime.h>
 #include <dlfcn.h>
 
+#include <algorithm>
 #include <cmath>
+#include <cstdint>
 #include <cstdio>
 #include <cstring>
 #include <string>
@@ -255,16 +257,26 @@ struct qwc_engine {
 
     // worker loop state
     std::vector<uint32_t> last_token;  // per state slot
+
+    // device bytes asked for through gpu_alloc and their ceiling
+    size_t memory_used = 0;
+    size_t memory_limit = SIZE_MAX;
 };
 
 namespace {
 
 int gpu_alloc(qwc_engine* e, void** out, size_t bytes, bool zero = false) {
     void* p = nullptr;
-    const cudaError_t err = cudaMalloc(&p, bytes == 0 ? 16 : bytes);
+    const size_t reserved = bytes == 0 ? 16 : bytes;
+    // the ceiling refuses before the driver is asked (crates/qwc-cuda/src/memory.rs:80-88)
+    if (reserved > e->memory_limit || e->memory_used > e->memory_limit - reserved) {
+        return cudaErrorMemoryAllocation;
+    }
+    const cudaError_t err = cudaMalloc(&p, reserved);
     if (err != cudaSuccess) {
         return err;
     }
+    e->memory_used += reserved;
     e->allocations.push_back(p);
     if (zero) {
         const cudaError_t cleared = cudaMemsetAsync(p, 0, bytes, e->stream);
@@ -953,6 +965,15 @@ int qwc_engine_open_peers(qwc_engine* e, const void* handles, int count) {
     return 0;
 }
 
+void qwc_engine_memory_usage(const qwc_engine* e, size_t* used, size_t* limit) {
+    if (used != nullptr) {
+        *used = e == nullptr ? 0 : e->memory_used;
+    }
+    if (limit != nullptr) {
+        *limit = e == nullptr || e->memory_limit == SIZE_MAX ? 0 : e->memory_limit;
+    }
+}
+
 int qwc_engine_create(const qwc_engine_config* config, qwc_engine** out) {
     if (config == nullptr || out == nullptr || config->num_layers <= 0 || config->full_attention_interval <= 0 ||
         config->hidden <= 0 || config->hidden % 256 != 0 || config->intermediate % 256 != 0 || config->vocab <= 0 ||
@@ -975,6 +996,20 @@ int qwc_engine_create(const qwc_engine_config* config, qwc_engine** out) {
     };
     if ((status = cudaStreamCreateWithFlags(&e->stream, cudaStreamNonBlocking)) != 0) {
         return fail(status);
+    }
+    if (c.memory_limit != 0) {
+        // Other processes live on the card too: the budget asked for may not exist, and finding that
+        // out half-way through the weights is worse than taking less (memory.rs:31-58).
+        constexpr size_t kFreeMargin = size_t{512} << 20;  // what cudaMalloc's rounding adds up to
+        size_t limit = static_cast<size_t>(c.memory_limit);
+        size_t free_bytes = 0, total_bytes = 0;
+        if (cudaMemGetInfo(&free_bytes, &total_bytes) == cudaSuccess && total_bytes > 0) {
+            limit = std::min(limit, free_bytes > kFreeMargin ? free_bytes - kFreeMargin : size_t{0});
+        }
+        if (limit == 0) {
+            return fail(cudaErrorMemoryAllocation);
+        }
+        e->memory_limit = limit;
     }
 
     e->v_heads = c.delta_value_heads;

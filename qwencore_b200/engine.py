@@ -45,7 +45,8 @@ class EngineConfig(ctypes.Structure):
                 ("intermediate", c_int), ("vocab", c_int), ("delta_value_heads", c_int), ("kv_page_size", c_int),
                 ("max_batch", c_int), ("max_context", c_int), ("kv_pool_blocks", c_int), ("state_slots", c_int),
                 ("seed", ctypes.c_ulonglong), ("split_rank", c_int), ("split_size", c_int), ("use_graph", c_int),
-                ("attention_partitions", c_int), ("write_logits", c_int), ("exchange", c_int)]
+                ("attention_partitions", c_int), ("write_logits", c_int), ("exchange", c_int),
+                ("memory_limit", ctypes.c_ulonglong)]
 
 
 class StepTraffic(ctypes.Structure):
@@ -100,6 +101,7 @@ ENGINE_SYMBOLS = {
     "qwc_engine_default_config": (None, [POINTER(EngineConfig)]),
     "qwc_engine_create": (c_int, [POINTER(EngineConfig), POINTER(P)]),
     "qwc_engine_destroy": (None, [P]),
+    "qwc_engine_memory_usage": (None, [P, POINTER(c_size_t), POINTER(c_size_t)]),
     "qwc_engine_nccl_unique_id": (c_int, [P]),
     "qwc_engine_init_split": (c_int, [P, P]),
     "qwc_engine_exchange_handle": (c_int, [P, P]),
@@ -608,6 +610,12 @@ class Engine:
         if code != 0:
             raise abi.QwcError(code if code > 0 else -code, "qwc_engine_time_phases")
         return milliseconds.value, launches.value
+
+    def memory_usage(self) -> dict:
+        """Device bytes the engine asked for and its ceiling (0: none); memory.rs:73-78."""
+        used, limit = c_size_t(), c_size_t()
+        lib.qwc_engine_memory_usage(self._handle, byref(used), byref(limit))
+        return {"used": used.value, "limit": limit.value}
 
     def copy_kv_block(self, source: int, target: int) -> None:
         """Executor::copy_kv_block (executor.rs:825-835); asynchronous on the engine's stream."""

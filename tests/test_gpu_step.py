@@ -258,6 +258,34 @@ def test_copy_kv_block_copies_one_page_in_every_attention_layer(cuda, engine_mod
         engine.close()
 
 
+def test_memory_ceiling_refuses_before_the_driver_is_asked(cuda, engine_module):
+    """The VRAM ceiling (crates/qwc-cuda/src/memory.rs:31-88, tests/memory_limit.rs): an engine whose
+    buffers do not fit its budget is refused with cudaErrorMemoryAllocation and leaves nothing behind;
+    with room it reports what it took.  The refusal is host arithmetic: nothing is driven out of memory."""
+    import torch
+
+    from qwencore_b200 import abi
+
+    free_before = torch.cuda.mem_get_info()[0]
+    with pytest.raises(abi.QwcError) as error:
+        engine_module.Engine(small_config(engine_module, num_layers=4, memory_limit=64 << 20))
+    assert error.value.code == 2
+    torch.cuda.synchronize()
+    assert torch.cuda.mem_get_info()[0] >= free_before - (8 << 20)  # what was taken came back
+
+    engine = engine_module.Engine(small_config(engine_module, num_layers=4, memory_limit=8 << 30))
+    try:
+        usage = engine.memory_usage()
+        assert 64 << 20 < usage["used"] <= usage["limit"] <= 8 << 30
+    finally:
+        engine.close()
+    unlimited = engine_module.Engine(small_config(engine_module, num_layers=4))
+    try:
+        assert unlimited.memory_usage() == {"used": usage["used"], "limit": 0}
+    finally:
+        unlimited.close()
+
+
 def test_decode_reports_packing_errors(cuda, engine_module):
     from qwencore_b200 import abi
 
