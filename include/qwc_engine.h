@@ -200,6 +200,44 @@ typedef struct qwc_engine_config {
                                     qwc_engine_create frees what it had taken */
 } qwc_engine_config;
 
+/* ---- memory plan (crates/qwc-core/src/memory.rs:99-218, crates/qwc-runtime/src/cache.rs:360-378,
+ *      :596-622): what a sequence costs, what a GPU has left for the two pools, pools sized for a
+ *      target context.  Host arithmetic only. ---- */
+typedef struct qwc_cache_geometry {
+    uint64_t kv_bytes_per_token;   /* e4m3 K and V of every full-attention layer */
+    uint64_t state_bytes_per_slot; /* int8 state rows + fp32 row scales + fp32 convolution window */
+    size_t block_size;             /* tokens per KV page */
+} qwc_cache_geometry;
+
+typedef struct qwc_budget {
+    uint64_t total_vram;
+    uint64_t reserved;  /* context, driver, other processes */
+    uint64_t weights;
+    uint64_t workspace; /* activations, exchange blocks, graphs */
+} qwc_budget;
+
+void qwc_cache_geometry_for(const qwc_engine_config* config, qwc_cache_geometry* geometry);
+/* Resident weight bytes of the engine this config describes (this rank's share under a column split):
+ * NVFP4 nibbles and block scales of every projection, the two e4m3 vocabulary tables with their row
+ * scales, the bf16 norms and gates. */
+uint64_t qwc_engine_weight_bytes(const qwc_engine_config* config);
+/* One B200: 183 359 MiB, 1 GiB reserved. */
+void qwc_budget_b200(uint64_t weights, uint64_t workspace, qwc_budget* budget);
+uint64_t qwc_budget_cache_available(const qwc_budget* budget);
+size_t qwc_budget_max_concurrency(const qwc_budget* budget, const qwc_cache_geometry* geometry, size_t context);
+size_t qwc_budget_max_context(const qwc_budget* budget, const qwc_cache_geometry* geometry, size_t concurrency);
+int qwc_budget_fits(const qwc_budget* budget, const qwc_cache_geometry* geometry, size_t concurrency,
+                    size_t context);
+size_t qwc_cache_geometry_crossover_tokens(const qwc_cache_geometry* geometry);
+/* CacheManager::from_budget: as many state slots as sequences of `target_context` fit, the rest as
+ * KV pages.  Free with qwc_cache_free. */
+qwc_cache* qwc_cache_from_budget(const qwc_budget* budget, const qwc_cache_geometry* geometry,
+                                 size_t target_context);
+size_t qwc_cache_state_capacity(const qwc_cache* cache);
+size_t qwc_cache_kv_capacity(const qwc_cache* cache);
+/* Utilisation of the two pools in [0, 1]; the larger one is the bottleneck (Pressure). */
+void qwc_cache_pressure(const qwc_cache* cache, double* states, double* kv);
+
 /* Fills `config` with the synthetic 27B-shaped model of the benchmark. */
 void qwc_engine_default_config(qwc_engine_config* config);
 

@@ -68,6 +68,60 @@ void KvPool::release(const std::vector<uint32_t>& blocks) {
 
 // ---- cache manager -------------------------------------------------------------------
 
+CacheGeometry CacheGeometry::for_model(size_t linear_layers, size_t attention_layers, size_t value_heads,
+                                       size_t block_size) {
+    constexpr uint64_t kStateDim = 128, kKeyHeads = 16, kKvHeads = 4, kHeadDim = 256, kConvWindow = 3;
+    CacheGeometry geometry;
+    geometry.block_size = block_size ? block_size : 1;
+    geometry.kv_bytes_per_token = attention_layers * kKvHeads * kHeadDim * 2;  // e4m3: one byte each
+    const uint64_t state_elements = linear_layers * value_heads * kStateDim * kStateDim;
+    const uint64_t channels = 2 * kKeyHeads * kStateDim + value_heads * kStateDim;
+    geometry.state_bytes_per_slot = state_elements + state_elements / kStateDim * 4  // codes + row scales
+                                    + linear_layers * channels * kConvWindow * 4;      // fp32 conv history
+    return geometry;
+}
+
+Budget Budget::b200(uint64_t weights, uint64_t workspace) {
+    constexpr uint64_t kMiB = 1024ull * 1024ull;
+    return Budget{183359ull * kMiB, 1024ull * kMiB, weights, workspace};
+}
+
+uint64_t Budget::cache_available() const {
+    uint64_t left = total_vram;
+    for (const uint64_t taken : {reserved, weights, workspace}) {
+        left = left > taken ? left - taken : 0;
+    }
+    return left;
+}
+
+size_t Budget::max_concurrency(const CacheGeometry& geometry, size_t context) const {
+    const uint64_t per_seq = geometry.bytes_per_seq(context);
+    return per_seq == 0 ? 0 : static_cast<size_t>(cache_available() / per_seq);
+}
+
+size_t Budget::max_context(const CacheGeometry& geometry, size_t concurrency) const {
+    if (concurrency == 0 || geometry.kv_bytes_per_token == 0) {
+        return 0;
+    }
+    const uint64_t per_seq = cache_available() / concurrency;
+    const uint64_t for_kv = per_seq > geometry.state_bytes_per_slot ? per_seq - geometry.state_bytes_per_slot : 0;
+    return static_cast<size_t>(for_kv / geometry.kv_bytes_per_token);
+}
+
+bool Budget::fits(const CacheGeometry& geometry, size_t concurrency, size_t context) const {
+    return geometry.bytes_per_seq(context) * concurrency <= cache_available();
+}
+
+CacheManager CacheManager::from_budget(const Budget& budget, const CacheGeometry& geometry, size_t target_context) {
+    const uint64_t available = budget.cache_available();
+    const uint64_t per_seq = std::max<uint64_t>(geometry.bytes_per_seq(target_context), 1);
+    const size_t slots = static_cast<size_t>(available / per_seq);
+    const uint64_t state_bytes = slots * geometry.state_bytes_per_slot;
+    const uint64_t kv_bytes = available > state_bytes ? available - state_bytes : 0;
+    const size_t blocks = static_cast<size_t>(kv_bytes / std::max<uint64_t>(geometry.kv_bytes_per_block(), 1));
+    return CacheManager(slots, blocks, geometry.block_size);
+}
+
 CacheManager::CacheManager(size_t state_slots, size_t kv_blocks, size_t block_size)
     : states_(state_slots), kv_(kv_blocks, block_size) {}
 

@@ -40,6 +40,7 @@ public:
     void release(uint32_t slot);
     size_t capacity() const { return capacity_; }
     size_t in_use() const { return capacity_ - free_.size(); }
+    double utilization() const { return static_cast<double>(in_use()) / static_cast<double>(capacity_ ? capacity_ : 1); }
     bool empty() const { return free_.empty(); }
 
 private:
@@ -55,6 +56,9 @@ public:
     size_t free_blocks() const { return free_.size(); }
     size_t capacity() const { return capacity_; }
     size_t block_size() const { return block_size_; }
+    double utilization() const {
+        return static_cast<double>(capacity_ - free_.size()) / static_cast<double>(capacity_ ? capacity_ : 1);
+    }
     bool acquire(size_t n, std::vector<uint32_t>* out);
     void retain(const std::vector<uint32_t>& blocks);
     void release(const std::vector<uint32_t>& blocks);
@@ -105,11 +109,61 @@ struct TableEdit {
     uint32_t kind;  // 0 set block, 1 set tokens, 2 add tokens
 };
 
+// What one sequence costs in device memory (crates/qwc-core/src/memory.rs:99-157): a recurrent-state
+// slot of constant size (int8 rows with an fp32 scale per row of 128, plus the fp32 convolution window)
+// and KV pages that grow with the context (e4m3, K and V, every full-attention layer).  Below
+// crossover_tokens() a sequence's state is the larger part, above it its KV pages are.
+struct CacheGeometry {
+    uint64_t kv_bytes_per_token = 0;
+    uint64_t state_bytes_per_slot = 0;
+    size_t block_size = 1;
+
+    // The decode engine's shape: `linear_layers` DeltaNet layers of `value_heads` heads (16 key heads,
+    // 128 x 128 state per value head), `attention_layers` layers of 4 KV heads x 256.
+    static CacheGeometry for_model(size_t linear_layers, size_t attention_layers, size_t value_heads, size_t block_size);
+    uint64_t kv_bytes_per_block() const { return kv_bytes_per_token * block_size; }
+    uint64_t bytes_per_seq(size_t context) const {
+        return state_bytes_per_slot + (context + block_size - 1) / block_size * kv_bytes_per_block();
+    }
+    size_t crossover_tokens() const {
+        return static_cast<size_t>(state_bytes_per_slot / (kv_bytes_per_token ? kv_bytes_per_token : 1));
+    }
+};
+
+// crates/qwc-core/src/memory.rs:163-207: what is left for the two pools once the context, the weights
+// and the workspace (activations, exchange blocks, graphs) are taken.
+struct Budget {
+    uint64_t total_vram = 0;
+    uint64_t reserved = 0;
+    uint64_t weights = 0;
+    uint64_t workspace = 0;
+
+    // One B200: 183 359 MiB as the driver reports it, 1 GiB for the context and the library.
+    static Budget b200(uint64_t weights, uint64_t workspace);
+    uint64_t cache_available() const;
+    size_t max_concurrency(const CacheGeometry& geometry, size_t context) const;
+    size_t max_context(const CacheGeometry& geometry, size_t concurrency) const;
+    bool fits(const CacheGeometry& geometry, size_t concurrency, size_t context) const;
+};
+
+// crates/qwc-runtime/src/cache.rs:604-622: which pool is closer to exhaustion.
+struct Pressure {
+    double states = 0.0;
+    double kv = 0.0;
+    bool states_bind() const { return states >= kv; }
+    double worst() const { return states > kv ? states : kv; }
+};
+
 // crates/qwc-runtime/src/cache.rs:300-449,571-594.  Every mutation is also recorded as table
 // edits so the device copy of (tokens, blocks) per slot can follow without a rebuild.
 class CacheManager {
 public:
     CacheManager(size_t state_slots, size_t kv_blocks, size_t block_size);
+    // Pools sized for a target context (cache.rs:360-378): as many state slots as sequences of that
+    // length fit, the rest of the budget as KV pages - a slot without pages is as useless as pages
+    // without a slot.
+    static CacheManager from_budget(const Budget& budget, const CacheGeometry& geometry, size_t target_context);
+    Pressure pressure() const { return Pressure{states_.utilization(), kv_.utilization()}; }
     Rejected admit(SeqId id, size_t prompt_tokens);
     Rejected append_token(SeqId id);
     Rejected rollback_token(SeqId id);

@@ -121,6 +121,97 @@ size_t qwc_cache_drain_edits(qwc_cache* cache, qwc_table_edit* edits, size_t max
     return pending.size();
 }
 
+namespace {
+
+CacheGeometry geometry_of(const qwc_cache_geometry* g) {
+    CacheGeometry geometry;
+    geometry.kv_bytes_per_token = g->kv_bytes_per_token;
+    geometry.state_bytes_per_slot = g->state_bytes_per_slot;
+    geometry.block_size = g->block_size ? g->block_size : 1;
+    return geometry;
+}
+
+Budget budget_of(const qwc_budget* b) { return Budget{b->total_vram, b->reserved, b->weights, b->workspace}; }
+
+// NVFP4 matrix as the engine keeps it: nibbles, and e4m3 block scales in the 128 x 4 swizzle (rows
+// padded to 128, 16-wide blocks padded to 4).
+uint64_t nvfp4_bytes(uint64_t rows, uint64_t cols) {
+    const uint64_t padded_rows = (rows + 127) / 128 * 128;
+    const uint64_t padded_blocks = (cols / 16 + 3) / 4 * 4;
+    return rows * cols / 2 + padded_rows * padded_blocks;
+}
+
+}  // namespace
+
+void qwc_cache_geometry_for(const qwc_engine_config* config, qwc_cache_geometry* out) {
+    const size_t attention = static_cast<size_t>(config->num_layers / config->full_attention_interval);
+    const CacheGeometry geometry =
+        CacheGeometry::for_model(static_cast<size_t>(config->num_layers) - attention, attention,
+                                 static_cast<size_t>(config->delta_value_heads), static_cast<size_t>(config->kv_page_size));
+    *out = {geometry.kv_bytes_per_token, geometry.state_bytes_per_slot, geometry.block_size};
+}
+
+uint64_t qwc_engine_weight_bytes(const qwc_engine_config* c) {
+    const uint64_t split = static_cast<uint64_t>(c->split_size > 0 ? c->split_size : 1);
+    const uint64_t hidden = c->hidden, inter = c->intermediate, heads = c->delta_value_heads, vocab = c->vocab;
+    const uint64_t attention = c->num_layers / c->full_attention_interval;
+    const uint64_t linear = c->num_layers - attention;
+    const uint64_t channels = 2 * 16 * 128 + heads * 128;
+    const uint64_t mixer_width = channels + heads * 128 + 2 * heads;  // q|k|v, z, a, b
+    const uint64_t qkv_width = 24 * 2 * 256 + 2 * 4 * 256;
+    // a column split keeps N / split rows of every projection on a rank; the K-side matrices
+    // (down, out, o) are split the same way
+    uint64_t per_layer = 2 * nvfp4_bytes(inter / split, hidden) + nvfp4_bytes(hidden / split, inter) + 2 * hidden * 2;
+    uint64_t per_linear = nvfp4_bytes(mixer_width / split, hidden) + nvfp4_bytes(hidden / split, heads * 128) +
+                          (channels * 4 + 2 * heads + 128) * 2;
+    uint64_t per_attention = nvfp4_bytes(qkv_width / split, hidden) + nvfp4_bytes(hidden / split, 24 * 256) +
+                             2 * 256 * 2 + 2 * 4 * 4;
+    const uint64_t tables = vocab * hidden + 4 * vocab + (vocab / split) * hidden + 4 * (vocab / split);
+    return c->num_layers * per_layer + linear * per_linear + attention * per_attention + tables + hidden * 2;
+}
+
+void qwc_budget_b200(uint64_t weights, uint64_t workspace, qwc_budget* out) {
+    const Budget budget = Budget::b200(weights, workspace);
+    *out = {budget.total_vram, budget.reserved, budget.weights, budget.workspace};
+}
+
+uint64_t qwc_budget_cache_available(const qwc_budget* budget) { return budget_of(budget).cache_available(); }
+
+size_t qwc_budget_max_concurrency(const qwc_budget* budget, const qwc_cache_geometry* geometry, size_t context) {
+    return budget_of(budget).max_concurrency(geometry_of(geometry), context);
+}
+
+size_t qwc_budget_max_context(const qwc_budget* budget, const qwc_cache_geometry* geometry, size_t concurrency) {
+    return budget_of(budget).max_context(geometry_of(geometry), concurrency);
+}
+
+int qwc_budget_fits(const qwc_budget* budget, const qwc_cache_geometry* geometry, size_t concurrency,
+                    size_t context) {
+    return budget_of(budget).fits(geometry_of(geometry), concurrency, context) ? 1 : 0;
+}
+
+size_t qwc_cache_geometry_crossover_tokens(const qwc_cache_geometry* geometry) {
+    return geometry_of(geometry).crossover_tokens();
+}
+
+qwc_cache* qwc_cache_from_budget(const qwc_budget* budget, const qwc_cache_geometry* geometry,
+                                 size_t target_context) {
+    auto* handle = new qwc_cache;
+    handle->owned = std::make_unique<CacheManager>(
+        CacheManager::from_budget(budget_of(budget), geometry_of(geometry), target_context));
+    handle->cache = handle->owned.get();
+    return handle;
+}
+
+size_t qwc_cache_state_capacity(const qwc_cache* cache) { return cache->cache->states().capacity(); }
+size_t qwc_cache_kv_capacity(const qwc_cache* cache) { return cache->cache->kv().capacity(); }
+
+void qwc_cache_pressure(const qwc_cache* cache, double* states, double* kv) {
+    const Pressure pressure = cache->cache->pressure();
+    *states = pressure.states;
+    *kv = pressure.kv;
+}
+
 qwc_scheduler* qwc_scheduler_new(size_t max_num_seqs, size_t max_num_batched_tokens, size_t state_slots,
                                  size_t kv_blocks, size_t block_size) {
     if (max_num_seqs == 0 || max_num_batched_tokens == 0 || block_size == 0) {

@@ -81,6 +81,18 @@ ENGINE_SYMBOLS = {
     "qwc_cache_active": (c_size_t, [P]),
     "qwc_cache_last_shortage": (None, [P, POINTER(c_size_t), POINTER(c_size_t)]),
     "qwc_cache_drain_edits": (c_size_t, [P, P, c_size_t]),
+    "qwc_cache_geometry_for": (None, [P, P]),
+    "qwc_engine_weight_bytes": (ctypes.c_uint64, [P]),
+    "qwc_budget_b200": (None, [ctypes.c_uint64, ctypes.c_uint64, P]),
+    "qwc_budget_cache_available": (ctypes.c_uint64, [P]),
+    "qwc_budget_max_concurrency": (c_size_t, [P, P, c_size_t]),
+    "qwc_budget_max_context": (c_size_t, [P, P, c_size_t]),
+    "qwc_budget_fits": (c_int, [P, P, c_size_t, c_size_t]),
+    "qwc_cache_geometry_crossover_tokens": (c_size_t, [P]),
+    "qwc_cache_from_budget": (P, [P, P, c_size_t]),
+    "qwc_cache_state_capacity": (c_size_t, [P]),
+    "qwc_cache_kv_capacity": (c_size_t, [P]),
+    "qwc_cache_pressure": (None, [P, POINTER(c_double), POINTER(c_double)]),
     "qwc_scheduler_new": (P, [c_size_t, c_size_t, c_size_t, c_size_t, c_size_t]),
     "qwc_scheduler_free": (None, [P]),
     "qwc_scheduler_submit": (c_int, [P, c_uint32, c_size_t, c_size_t]),
@@ -149,6 +161,56 @@ class Admission(ctypes.Structure):
                 ("copy_from", c_uint32), ("copy_to", c_uint32)]
 
 
+class CacheGeometry(ctypes.Structure):
+    """What one sequence costs (crates/qwc-core/src/memory.rs:99-157)."""
+    _fields_ = [("kv_bytes_per_token", ctypes.c_uint64), ("state_bytes_per_slot", ctypes.c_uint64),
+                ("block_size", c_size_t)]
+
+    @classmethod
+    def for_config(cls, config: "EngineConfig") -> "CacheGeometry":
+        geometry = cls()
+        lib.qwc_cache_geometry_for(byref(config), byref(geometry))
+        return geometry
+
+    def kv_bytes_per_block(self) -> int:
+        return self.kv_bytes_per_token * self.block_size
+
+    def bytes_per_seq(self, context: int) -> int:
+        return self.state_bytes_per_slot + -(-context // self.block_size) * self.kv_bytes_per_block()
+
+    def crossover_tokens(self) -> int:
+        return lib.qwc_cache_geometry_crossover_tokens(byref(self))
+
+
+class Budget(ctypes.Structure):
+    """What a GPU has left for the two pools (crates/qwc-core/src/memory.rs:163-218)."""
+    _fields_ = [("total_vram", ctypes.c_uint64), ("reserved", ctypes.c_uint64), ("weights", ctypes.c_uint64),
+                ("workspace", ctypes.c_uint64)]
+
+    @classmethod
+    def b200(cls, weights: int, workspace: int) -> "Budget":
+        budget = cls()
+        lib.qwc_budget_b200(weights, workspace, byref(budget))
+        return budget
+
+    def cache_available(self) -> int:
+        return lib.qwc_budget_cache_available(byref(self))
+
+    def max_concurrency(self, geometry: CacheGeometry, context: int) -> int:
+        return lib.qwc_budget_max_concurrency(byref(self), byref(geometry), context)
+
+    def max_context(self, geometry: CacheGeometry, concurrency: int) -> int:
+        return lib.qwc_budget_max_context(byref(self), byref(geometry), concurrency)
+
+    def fits(self, geometry: CacheGeometry, concurrency: int, context: int) -> bool:
+        return bool(lib.qwc_budget_fits(byref(self), byref(geometry), concurrency, context))
+
+
+def weight_bytes(config: "EngineConfig") -> int:
+    """Resident weight bytes of the engine a config describes (this rank's share under a split)."""
+    return lib.qwc_engine_weight_bytes(byref(config))
+
+
 class PrefixRestoreOp(ctypes.Structure):
     _fields_ = [("id", c_uint32), ("state_slot", c_uint32), ("snapshot", c_uint32), ("copy", c_uint32),
                 ("copy_from", c_uint32), ("copy_to", c_uint32)]
@@ -174,6 +236,27 @@ class CacheManager:
         if getattr(self, "_owned", False) and self._handle:
             lib.qwc_cache_free(self._handle)
             self._handle = None
+
+    @classmethod
+    def from_budget(cls, budget: Budget, geometry: CacheGeometry, target_context: int) -> "CacheManager":
+        """cache.rs:360-378: as many slots as sequences of the target context fit, the rest as pages."""
+        manager = cls(0, 0, 1, _borrowed=lib.qwc_cache_from_budget(byref(budget), byref(geometry), target_context))
+        manager._owned = True
+        return manager
+
+    def state_capacity(self) -> int:
+        return lib.qwc_cache_state_capacity(self._handle)
+
+    def kv_capacity(self) -> int:
+        return lib.qwc_cache_kv_capacity(self._handle)
+
+    def pressure(self) -> dict:
+        """cache.rs:596-622: utilisation of both pools and which one binds."""
+        states, kv = c_double(), c_double()
+        lib.qwc_cache_pressure(self._handle, byref(states), byref(kv))
+        return {"states": states.value, "kv": kv.value,
+                "bottleneck": "state slots" if states.value >= kv.value else "KV blocks",
+                "worst": max(states.value, kv.value)}
 
     def _check(self, code: int) -> None:
         if code != 0:

@@ -273,10 +273,17 @@ def test_memory_ceiling_refuses_before_the_driver_is_asked(cuda, engine_module):
     torch.cuda.synchronize()
     assert torch.cuda.mem_get_info()[0] >= free_before - (8 << 20)  # what was taken came back
 
-    engine = engine_module.Engine(small_config(engine_module, num_layers=4, memory_limit=8 << 30))
+    config = small_config(engine_module, num_layers=4, memory_limit=8 << 30)
+    engine = engine_module.Engine(config)
     try:
         usage = engine.memory_usage()
         assert 64 << 20 < usage["used"] <= usage["limit"] <= 8 << 30
+        # the host-side memory plan names what the engine took: weights and the two pools, the rest
+        # (activations, workspaces, tables) is what a Budget calls workspace
+        geometry = engine_module.CacheGeometry.for_config(config)
+        planned = (engine_module.weight_bytes(config) + config.state_slots * geometry.state_bytes_per_slot
+                   + config.kv_pool_blocks * geometry.kv_bytes_per_block())
+        assert planned <= usage["used"] < planned + (512 << 20), (planned, usage["used"])
     finally:
         engine.close()
     unlimited = engine_module.Engine(small_config(engine_module, num_layers=4))
