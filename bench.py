@@ -506,6 +506,19 @@ def run_ours(args):
     seconds_per_launch = gemv_ms * 1e-3 / max(1, gemv_launches)
     achieved = bytes_per_launch / seconds_per_launch / 1e9
     step_bytes = traffic.weight_bytes + traffic.state_bytes + traffic.kv_bytes
+    # per phase what it streams and how fast (stepprofile's table, crates/qwc-engine/src/bin/
+    # stepprofile.rs:86-183, :259-310): weights for the projections and the head, KV pages for
+    # attention, state read and written for the recurrent update
+    phase_bytes = {"gemm": traffic.gemv_bytes_per_step, "attn.decode": traffic.kv_bytes,
+                   "delta.scan": traffic.state_bytes, "lm_head": traffic.weight_bytes - traffic.gemv_bytes_per_step}
+    phase_rooflines = {}
+    for label, streamed in phase_bytes.items():
+        if label in graph_phases and graph_phases[label]["ms"] > 0:
+            rate = streamed / (graph_phases[label]["ms"] * 1e-3) / 1e9
+            phase_rooflines[label] = {"GB": round(streamed / 1e9, 4), "GB/s": round(rate, 1),
+                                      "frac_of_measured_peak": round(rate / peak, 4),
+                                      "share_of_step_ms": round(graph_phases[label]["ms"] /
+                                                                (device_seconds / args.steps * 1e3), 4)}
 
     # ---- c = 1: the same engine, one row of context 2048 (the other half of the metric) ----
     c1_steps = max(args.steps, 20)
@@ -574,6 +587,7 @@ def run_ours(args):
         "per_rank": [{"rank": i, "ms_per_step": round(v[0], 4), "e2e_ms_per_step": round(v[1], 4), "kv_bytes": v[2],
                       "context_tokens": v[3]} for i, v in enumerate(per_rank)],
         "phases_graph_ms_per_step": graph_phases,
+        "phase_rooflines": phase_rooflines,
         "phases_eager_ms_per_step": {label: round(total[0], 4) for label, total in sorted(phases.items())},
         "cpu_baseline": {"value": cpu_value, "unit": "tok/s", "cores": os.cpu_count() or 1, "kind": "port",
                          "sample": cpu_sample_text},
