@@ -181,7 +181,10 @@ def load_vocab(engine, name: str, table_bf16: np.ndarray, chunk_rows: int = VOCA
     stream = torch.cuda.current_stream().cuda_stream
     for first in range(0, config.vocab, chunk_rows):
         rows = min(chunk_rows, config.vocab - first)
-        staging[:rows].copy_(torch.from_numpy(table[first:first + rows].view(np.int16)))
+        chunk = table[first:first + rows].view(np.int16)
+        if not chunk.flags.writeable:  # a view of a mapped file: torch wants memory it may write to
+            chunk = np.array(chunk)
+        staging[:rows].copy_(torch.from_numpy(chunk))
         abi.check(abi.lib.qwc_fp8_quantize_rows(staging.data_ptr(), codes, scales, rows, config.hidden, first, stream),
                   "qwc_fp8_quantize_rows")
     torch.cuda.synchronize()

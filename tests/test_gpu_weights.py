@@ -141,3 +141,56 @@ def test_model_in_checkpoint_layout_loads_into_the_same_engine(cuda, built_libra
         for engine in engines:
             engine.close()
         abi.configure(*before)
+
+
+def test_model_loads_from_safetensors_files(cuda, built_library, tmp_path):
+    """The file side (qwencore_b200/checkpoint.py): an engine's tensors written as a sharded safetensors
+    checkpoint, validated against the architecture, and loaded into a second engine layer by layer with
+    the file pages dropped behind the upload; every resident weight tensor then equals the source's."""
+    from qwencore_b200 import abi, checkpoint, engine as E, weights
+
+    before = abi.get_shape()
+    engines = []
+    try:
+        def make(seed):
+            config = E.default_config(num_layers=4, vocab=4096, max_batch=2, max_context=256, kv_pool_blocks=48,
+                                      state_slots=3, seed=seed, use_graph=1)
+            engines.append(E.Engine(config))
+            return engines[-1]
+
+        source, target = make(5), make(6)
+        c = source.config
+        layers, final_norm, table, head = checkpoint_of(source, np.random.default_rng(1))
+        tensors, dtypes = checkpoint.checkpoint_tensors(c, layers, final_norm, table, head)
+        checkpoint.write_checkpoint(str(tmp_path), tensors, dtypes, tensors_per_shard=48)
+        del tensors, layers
+        model = checkpoint.Checkpoint.open(str(tmp_path))
+        problems, counted = model.validate(c)
+        assert problems == [] and counted["quantized_linears"] == 3 * 8 + 7 and counted["unused_tensors"] == 0
+        stats = checkpoint.load(target, model)
+        assert stats["projections"] == 5 * c.num_layers
+        assert stats["quantized_bytes"] >= counted["packed_bytes"] + counted["scale_bytes"]  # (+ swizzle padding)
+        assert stats["vocab_bytes"] == 2 * c.vocab * (c.hidden + 4)
+        weights.load_vocab(source, "embed", table)
+        weights.load_vocab(source, "lm_head", head)
+        for name in ("embed", "lm_head"):
+            assert np.array_equal(target.read(name), source.read(name))
+            assert np.array_equal(target.read(f"{name}_scales", 0, np.float32), source.read(f"{name}_scales", 0, np.float32))
+        assert np.array_equal(target.read("final_norm", 0, np.uint16), source.read("final_norm", 0, np.uint16))
+        shapes_k = {"gate": c.hidden, "up": c.hidden, "down": c.intermediate, "qkv": c.hidden, "o": 24 * 256,
+                    "in_proj": c.hidden, "la_out": c.delta_value_heads * 128}
+        for layer in range(c.num_layers):
+            full = (layer + 1) % c.full_attention_interval == 0
+            for name in ["gate", "up", "down"] + (["qkv", "o"] if full else ["in_proj", "la_out"]):
+                packed = target.read(f"{name}.packed", layer)
+                assert np.array_equal(packed, source.read(f"{name}.packed", layer)), (name, layer)
+                n = packed.size * 2 // shapes_k[name]
+                logical = [oracle.unswizzle_block_scales(e.read(f"{name}.scales", layer), n, shapes_k[name])
+                           for e in (target, source)]
+                assert np.array_equal(logical[0], logical[1]), (name, layer)
+            for _, (tensor, _) in weights.plain_names(c, layer).items():
+                assert np.array_equal(target.read(tensor, layer, np.uint16), source.read(tensor, layer, np.uint16))
+    finally:
+        for engine in engines:
+            engine.close()
+        abi.configure(*before)
