@@ -302,7 +302,11 @@ typedef struct qwc_step_traffic {
 } qwc_step_traffic;
 void qwc_engine_traffic(const qwc_engine* engine, int rows, double context_tokens, qwc_step_traffic* out);
 
-/* Applies table edits (host array) to the device page table: one H2D copy and one kernel. */
+/* Applies table edits (host array) to the device page table: one H2D copy and one kernel.  The edits
+ * are bounded on the host first (here and in qwc_engine_decode): a slot beyond the state pool, a table
+ * index beyond max_context, a page id beyond the KV pool or an unknown kind is refused with
+ * cudaErrorInvalidValue and nothing of the drain is applied - every page id the attention kernels
+ * follow came through here. */
 int qwc_engine_apply_edits(qwc_engine* engine, const qwc_table_edit* edits, size_t count);
 
 /* Copies KV page `from` onto page `to` in every full-attention layer, asynchronously on the engine's

@@ -832,6 +832,23 @@ int launch_decode(qwc_engine* e, int batch) {
     return cudaGraphLaunch(exec, e->stream);
 }
 
+// Every page id, state slot and table index reaches the device tables through an edit, so this is
+// where they are bounded: a page beyond the pool never gets into a block table that the attention
+// kernels (whose ABI carries no pool size) would follow.
+int check_edits(const qwc_engine* e, const qwc_table_edit* edits, size_t count) {
+    for (size_t i = 0; i < count; ++i) {
+        const qwc_table_edit& edit = edits[i];
+        if (edit.kind > 2 || edit.slot >= static_cast<uint32_t>(e->cfg.state_slots)) {
+            return cudaErrorInvalidValue;
+        }
+        if (edit.kind == 0 && (edit.index >= static_cast<uint32_t>(e->max_blocks) ||
+                               edit.value >= static_cast<uint32_t>(e->cfg.kv_pool_blocks))) {
+            return cudaErrorInvalidValue;
+        }
+    }
+    return 0;
+}
+
 int upload_inputs(qwc_engine* e, const uint32_t* row_slots, const uint32_t* tokens, const qwc_table_edit* edits,
                   size_t num_edits, int rows) {
     const qwc_engine_config& c = e->cfg;
@@ -1474,6 +1491,7 @@ int qwc_engine_apply_edits(qwc_engine* e, const qwc_table_edit* edits, size_t co
     if (count == 0) {
         return 0;
     }
+    QWC_TRY(check_edits(e, edits, count));
     qwc_table_edit* staged = nullptr;
     QWC_TRY(cudaMalloc(reinterpret_cast<void**>(&staged), count * sizeof(qwc_table_edit)));
     int status = cudaMemcpyAsync(staged, edits, count * sizeof(qwc_table_edit), cudaMemcpyHostToDevice, e->stream);
@@ -1515,6 +1533,7 @@ int qwc_engine_decode(qwc_engine* e, const uint32_t* row_slots, const uint32_t* 
         rows > e->cfg.max_batch || (num_edits > 0 && edits == nullptr)) {
         return cudaErrorInvalidValue;
     }
+    QWC_TRY(check_edits(e, edits, num_edits));
     QWC_TRY(upload_inputs(e, row_slots, tokens, edits, num_edits, rows));
     QWC_TRY(launch_decode(e, rows));
     QWC_TRY(cudaMemcpyAsync(e->out_host, e->out_dev, (e->cfg.max_batch + 2) * sizeof(uint32_t), cudaMemcpyDeviceToHost,

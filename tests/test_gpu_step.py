@@ -299,6 +299,35 @@ def test_memory_ceiling_refuses_before_the_driver_is_asked(cuda, engine_module):
         unlimited.close()
 
 
+def test_table_edits_are_bounded_on_the_host(cuda, engine_module):
+    """Slots, table indices and page ids reach the device tables only through edits, and the engine bounds
+    them before anything is copied: a page beyond the pool never gets into a block table."""
+    from qwencore_b200 import abi
+
+    config = small_config(engine_module, num_layers=4)  # 6 slots, 160 pages, 32 table entries per slot
+    engine = engine_module.Engine(config)
+    try:
+        cache = engine_module.CacheManager(6, 160, 16)
+        install(engine, cache, None, [50, 90])
+        tokens_before = engine.read("seq_tokens", 0, np.uint32)
+        blocks_before = engine.read("seq_blocks", 0, np.uint32)
+        good = [1, 3, 17, 0]
+        for bad in ([0, 0, 160, 0], [6, 0, 1, 1], [0, 32, 1, 0], [0, 0, 1, 3], [6, 0, 1, 2]):
+            for edits in ([bad], [good, bad]):  # nothing of a drain with a bad edit is applied
+                with pytest.raises(abi.QwcError) as error:
+                    engine.apply_edits(np.array(edits, dtype=np.uint32))
+                assert error.value.code == abi.CUDA_ERROR_INVALID_VALUE
+                with pytest.raises(abi.QwcError) as error:
+                    engine.decode([0, 1], [3, 4], np.array(edits, dtype=np.uint32))
+                assert error.value.code == abi.CUDA_ERROR_INVALID_VALUE
+        assert np.array_equal(engine.read("seq_tokens", 0, np.uint32), tokens_before)
+        assert np.array_equal(engine.read("seq_blocks", 0, np.uint32), blocks_before)
+        engine.apply_edits(np.array([good], dtype=np.uint32))
+        assert engine.read("seq_blocks", 0, np.uint32).reshape(6, 32)[1, 3] == 17
+    finally:
+        engine.close()
+
+
 def test_decode_reports_packing_errors(cuda, engine_module):
     from qwencore_b200 import abi
 
