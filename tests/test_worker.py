@@ -225,6 +225,40 @@ def test_the_loop_serves_requests_queued_from_another_thread(built_library):
     assert scheduler.active() == 0 and scheduler.cache.free_blocks() == 400
 
 
+def test_several_threads_can_queue_and_abandon_while_the_loop_runs(built_library):
+    scheduler = Scheduler(8, 256, 8, 800, 16)
+    sink = Recorder()
+    worker = Worker(scheduler, Executor(), sink)
+    result = []
+    loop = threading.Thread(target=lambda: result.append(worker.run()))
+    loop.start()
+
+    def client(first):
+        for seq in range(first, first + 25):
+            worker.submit(seq, range(seq % 7, seq % 7 + 20 + seq % 13), 1 + seq % 6)
+            if seq % 5 == 0:
+                worker.abandon(seq)
+
+    clients = [threading.Thread(target=client, args=(1 + 100 * i,)) for i in range(4)]
+    try:
+        for thread in clients:
+            thread.start()
+        for thread in clients:
+            thread.join(timeout=30)
+    finally:
+        worker.shutdown()
+        loop.join(timeout=60)
+    assert not loop.is_alive() and result == [0]
+    for first in (1, 101, 201, 301):
+        for seq in range(first, first + 25):
+            done, tokens = sink.of(seq, "done"), sink.tokens(seq)
+            assert sink.of(seq, "error") == []
+            if seq % 5 == 0 and not done:
+                continue  # left before it finished: no terminal event, by design
+            assert done == [(1 + seq % 6, 0)] and len(tokens) == 1 + seq % 6
+    assert scheduler.active() == 0 and scheduler.waiting() == 0 and scheduler.cache.free_blocks() == 800
+
+
 def test_the_next_turn_carries_the_restore_of_the_previous_prompt(built_library):
     scheduler = Scheduler(2, 512, 2, 100, 64)
     scheduler.enable_prefix_cache(4)
