@@ -411,6 +411,8 @@ typedef int (*qwc_event_fn)(void* user, uint32_t id, uint32_t kind, uint32_t val
 
 qwc_worker* qwc_worker_new(qwc_scheduler* scheduler, qwc_execute_fn execute, void* execute_user, qwc_event_fn event,
                            void* event_user, const uint32_t* eos_ids, size_t num_eos);
+/* Free only after qwc_worker_run has returned (and no other thread still calls into the worker); the
+ * scheduler is borrowed and outlives the worker. */
 void qwc_worker_free(qwc_worker* worker);
 /* Thread-safe: queue a request / tell the worker that nobody listens to a request any more / tell it
  * that no more commands will come (qwc_worker_run then returns once its jobs are finished). */
